@@ -1,0 +1,91 @@
+// C interface of the sm_100a kernels. Everything here takes raw device pointers and a stream,
+// allocates nothing and returns a BDH_* code; the torch binding (bindings.cpp) is one caller,
+// any C/C++ program that links the library is another.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  BDH_OK = 0,
+  BDH_ERR_DRIVER = 1,       // could not resolve a driver entry point
+  BDH_ERR_ALIGNMENT = 2,    // pointer not 16-byte aligned or leading dimension not a multiple of 8
+  BDH_ERR_TMAP = 3,         // tensor-map encoding rejected the matrix
+  BDH_ERR_LAUNCH = 4,
+  BDH_ERR_ARGUMENT = 5,
+  BDH_ERR_UNSUPPORTED = 6,  // no kernel instantiation for this (majors, epilogue, tile)
+  BDH_ERR_TOO_LARGE = 7,
+};
+
+// bf16 row-major 2-D matrix view: element (r, c) at ptr[r*ld + c].
+typedef struct {
+  const void* ptr;
+  long long rows, cols, ld;
+} BdhMat;
+
+// One batched GEMM  C[z][m,n] = epi(sum_k A[z][m,k] B[z][n,k]),  z = (z0, z1).
+// a_off/b_off = {mn per z0, mn per z1, k per z0, k per z1} element offsets into the 2-D views;
+// c_off = {row per z0, row per z1, col per z0, col per z1}; o1_off = {col per z0, col per z1,
+// imag distance} for the second output of the rotary epilogue.
+typedef struct {
+  int M, N, K, nz0, nz1;
+  long long a_off[4], b_off[4], c_off[4], o1_off[3];
+  int epi, flags, bn;
+  int causal_tiles, causal_k;
+  void* out0;
+  void* out1;
+  const void* in0;
+  const void* in1;
+  long long ld_out0, ld_out1, ld_in0, ld_in1;
+  float alpha, theta;
+  int T, pos0, n_per_head;
+  const float* freqs;
+  const float* slopes;
+  int* status;   // device word that receives a STATUS_* code if an in-kernel wait gives up
+  int max_ctas;  // 0: one CTA per SM
+} BdhGemmDesc;
+
+int bdh_gemm_bf16(const BdhMat* A, int a_mn_major, const BdhMat* B, int b_mn_major,
+                  const BdhGemmDesc* desc, cudaStream_t stream);
+
+// ---- row-wise kernels (rows of length D <= 2048, D % 8 == 0) ---------------------------------
+// y = LayerNorm(x) without affine, eps 1e-5, biased variance (reference: src/model/bdh.rs:86-89).
+int bdh_layernorm_fwd(const void* x_bf16, void* y_bf16, long long rows, int D, cudaStream_t s);
+// dx (+)= LayerNorm backward given x and dy.
+int bdh_layernorm_bwd(const void* x_bf16, const void* dy_bf16, void* dx_bf16, long long rows, int D,
+                      int accumulate, cudaStream_t s);
+// cur = LayerNorm(embedding[token]); tokens int64.
+int bdh_embed_ln_fwd(const long long* tokens, const void* emb_bf16, void* cur_bf16, long long rows,
+                     int D, int vocab, cudaStream_t s);
+// d_emb[token] += LayerNorm backward(dcur) with fp32 atomics.
+int bdh_embed_ln_bwd(const long long* tokens, const void* emb_bf16, const float* dcur_f32,
+                     float* demb_f32, long long rows, int D, int vocab, cudaStream_t s);
+// out = LayerNorm(cur + LayerNorm(mlp))  (reference: src/model/bdh.rs:436-441).
+int bdh_block_out_fwd(const void* cur_bf16, const void* mlp_bf16, void* out_bf16, long long rows,
+                      int D, cudaStream_t s);
+// Given d_out (fp32): d_cur_f32 (=) du, d_mlp_bf16 = LNbwd(mlp, du) where u = cur + LN(mlp).
+int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* dout_f32,
+                      float* dcur_f32, void* dmlp_bf16, long long rows, int D, cudaStream_t s);
+
+// ---- loss ------------------------------------------------------------------------------------
+// Mean cross-entropy over rows of fp32 logits [rows, V] (V <= 1024); writes per-row loss and
+// dlogits (bf16) = (softmax - onehot) * grad_scale.  (reference: src/model/loss.rs:5-18)
+int bdh_cross_entropy(const float* logits, const long long* targets, float* row_loss,
+                      void* dlogits_bf16, long long rows, int V, float grad_scale, cudaStream_t s);
+
+// ---- optimizer -------------------------------------------------------------------------------
+// Decoupled-weight-decay Adam over a flat fp32 master buffer; also refreshes the bf16 copy.
+int bdh_adamw(float* master, const float* grad, float* m, float* v, void* param_bf16, long long n,
+              float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+              float grad_scale, cudaStream_t s);
+
+// ---- misc elementwise ------------------------------------------------------------------------
+int bdh_cast_f32_to_bf16(const float* in, void* out_bf16, long long n, cudaStream_t s);
+int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cudaStream_t s);
+
+#ifdef __cplusplus
+}
+#endif

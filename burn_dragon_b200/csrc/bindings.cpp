@@ -1,0 +1,172 @@
+// torch.ops.bdh.* : thin argument-checking shims from torch tensors to the C kernel interface.
+// All outputs are allocated by the Python caller; nothing here allocates device memory except
+// the one-word status buffer created on first use.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "bdh_kernels.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == BDH_OK, "bdh kernel '", what, "' failed with code ", rc);
+}
+
+Tensor& status_word() {
+  static Tensor t;
+  if (!t.defined()) t = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA));
+  return t;
+}
+
+BdhMat as_mat(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1,
+              name, ": expected a 2-D bf16 CUDA tensor with unit column stride");
+  return BdhMat{t.data_ptr(), t.size(0), t.size(1), t.stride(0)};
+}
+
+const void* opt_ptr(const optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+long long opt_ld(const optional<Tensor>& t) {
+  return (t.has_value() && t->dim() >= 2) ? t->stride(t->dim() - 2) : 0;
+}
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int64_t N, int64_t K,
+          int64_t nz0, int64_t nz1, at::IntArrayRef a_off, at::IntArrayRef b_off, int64_t epi,
+          int64_t flags, const optional<Tensor>& out0, const optional<Tensor>& out1,
+          const optional<Tensor>& in0, const optional<Tensor>& in1, at::IntArrayRef c_off,
+          at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
+          int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
+          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas) {
+  c10::cuda::CUDAGuard guard(a.device());
+  BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
+  TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
+              "offset lists must have 4/4/4/3 entries");
+  BdhGemmDesc d{};
+  d.M = M; d.N = N; d.K = K; d.nz0 = nz0; d.nz1 = nz1;
+  for (int i = 0; i < 4; ++i) { d.a_off[i] = a_off[i]; d.b_off[i] = b_off[i]; d.c_off[i] = c_off[i]; }
+  for (int i = 0; i < 3; ++i) d.o1_off[i] = o1_off[i];
+  d.epi = epi; d.flags = flags; d.bn = bn;
+  d.causal_tiles = causal_tiles; d.causal_k = causal_k;
+  d.out0 = const_cast<void*>(opt_ptr(out0)); d.out1 = const_cast<void*>(opt_ptr(out1));
+  d.in0 = opt_ptr(in0); d.in1 = opt_ptr(in1);
+  d.ld_out0 = opt_ld(out0); d.ld_out1 = opt_ld(out1); d.ld_in0 = opt_ld(in0); d.ld_in1 = opt_ld(in1);
+  d.alpha = alpha; d.theta = theta; d.T = T; d.pos0 = pos0; d.n_per_head = n_per_head;
+  d.freqs = freqs.has_value() ? freqs->data_ptr<float>() : nullptr;
+  d.slopes = slopes.has_value() ? slopes->data_ptr<float>() : nullptr;
+  d.status = status_word().data_ptr<int>();
+  d.max_ctas = max_ctas;
+  check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
+}
+
+void check_rows(const Tensor& t, int64_t D, at::ScalarType st, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == st && t.size(-1) == D, name,
+              ": expected a contiguous CUDA tensor with last dim ", D);
+}
+
+void layernorm_fwd(const Tensor& x, Tensor& y) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t D = x.size(-1);
+  check_rows(x, D, at::kBFloat16, "x"); check_rows(y, D, at::kBFloat16, "y");
+  check_rc(bdh_layernorm_fwd(x.data_ptr(), y.data_ptr(), x.numel() / D, D, cur_stream()), "layernorm_fwd");
+}
+void layernorm_bwd(const Tensor& x, const Tensor& dy, Tensor& dx, bool accumulate) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t D = x.size(-1);
+  check_rows(x, D, at::kBFloat16, "x"); check_rows(dy, D, at::kBFloat16, "dy"); check_rows(dx, D, at::kBFloat16, "dx");
+  check_rc(bdh_layernorm_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel() / D, D, accumulate, cur_stream()),
+           "layernorm_bwd");
+}
+void embed_ln_fwd(const Tensor& tokens, const Tensor& emb, Tensor& cur) {
+  c10::cuda::CUDAGuard guard(emb.device());
+  const int64_t D = emb.size(1);
+  TORCH_CHECK(tokens.scalar_type() == at::kLong && tokens.is_contiguous() && tokens.is_cuda());
+  check_rows(emb, D, at::kBFloat16, "emb"); check_rows(cur, D, at::kBFloat16, "cur");
+  check_rc(bdh_embed_ln_fwd(tokens.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()) : nullptr,
+                            emb.data_ptr(), cur.data_ptr(), tokens.numel(), D, emb.size(0), cur_stream()),
+           "embed_ln_fwd");
+}
+void embed_ln_bwd(const Tensor& tokens, const Tensor& emb, const Tensor& dcur, Tensor& demb) {
+  c10::cuda::CUDAGuard guard(emb.device());
+  const int64_t D = emb.size(1);
+  TORCH_CHECK(tokens.scalar_type() == at::kLong && tokens.is_contiguous() && tokens.is_cuda());
+  check_rows(emb, D, at::kBFloat16, "emb"); check_rows(dcur, D, at::kFloat, "dcur"); check_rows(demb, D, at::kFloat, "demb");
+  check_rc(bdh_embed_ln_bwd(reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()), emb.data_ptr(),
+                            dcur.data_ptr<float>(), demb.data_ptr<float>(), tokens.numel(), D, emb.size(0), cur_stream()),
+           "embed_ln_bwd");
+}
+void block_out_fwd(const Tensor& cur, const Tensor& mlp, Tensor& out) {
+  c10::cuda::CUDAGuard guard(cur.device());
+  const int64_t D = cur.size(-1);
+  check_rows(cur, D, at::kBFloat16, "cur"); check_rows(mlp, D, at::kBFloat16, "mlp"); check_rows(out, D, at::kBFloat16, "out");
+  check_rc(bdh_block_out_fwd(cur.data_ptr(), mlp.data_ptr(), out.data_ptr(), cur.numel() / D, D, cur_stream()), "block_out_fwd");
+}
+void block_out_bwd(const Tensor& cur, const Tensor& mlp, const Tensor& dout, Tensor& dcur, Tensor& dmlp) {
+  c10::cuda::CUDAGuard guard(cur.device());
+  const int64_t D = cur.size(-1);
+  check_rows(cur, D, at::kBFloat16, "cur"); check_rows(mlp, D, at::kBFloat16, "mlp");
+  check_rows(dout, D, at::kFloat, "dout"); check_rows(dcur, D, at::kFloat, "dcur"); check_rows(dmlp, D, at::kBFloat16, "dmlp");
+  check_rc(bdh_block_out_bwd(cur.data_ptr(), mlp.data_ptr(), dout.data_ptr<float>(), dcur.data_ptr<float>(), dmlp.data_ptr(),
+                             cur.numel() / D, D, cur_stream()), "block_out_bwd");
+}
+void cross_entropy(const Tensor& logits, const Tensor& targets, Tensor& row_loss, const optional<Tensor>& dlogits,
+                   double grad_scale) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t V = logits.size(-1);
+  check_rows(logits, V, at::kFloat, "logits");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.is_cuda());
+  TORCH_CHECK(row_loss.scalar_type() == at::kFloat && row_loss.is_contiguous() && row_loss.numel() == targets.numel());
+  if (dlogits.has_value()) check_rows(*dlogits, V, at::kBFloat16, "dlogits");
+  check_rc(bdh_cross_entropy(logits.data_ptr<float>(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
+                             row_loss.data_ptr<float>(), const_cast<void*>(opt_ptr(dlogits)), targets.numel(), V,
+                             grad_scale, cur_stream()), "cross_entropy");
+}
+void adamw(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, const optional<Tensor>& p16, double lr, double beta1,
+           double beta2, double eps, double wd, int64_t step, double grad_scale) {
+  c10::cuda::CUDAGuard guard(master.device());
+  const int64_t n = master.numel();
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&master, &grad, &m, &v})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat && t->numel() == n);
+  if (p16.has_value()) TORCH_CHECK(p16->is_contiguous() && p16->scalar_type() == at::kBFloat16 && p16->numel() == n);
+  check_rc(bdh_adamw(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                     const_cast<void*>(opt_ptr(p16)), n, lr, beta1, beta2, eps, wd, step, grad_scale, cur_stream()), "adamw");
+}
+
+Tensor status() { return status_word(); }
+
+}  // namespace
+
+TORCH_LIBRARY(bdh, m) {
+  m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
+        "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
+        "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas) -> ()");
+  m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
+  m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
+  m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
+  m.def("embed_ln_bwd(Tensor tokens, Tensor emb, Tensor dcur, Tensor(a!) demb) -> ()");
+  m.def("block_out_fwd(Tensor cur, Tensor mlp, Tensor(a!) out) -> ()");
+  m.def("block_out_bwd(Tensor cur, Tensor mlp, Tensor dout, Tensor(a!) dcur, Tensor(b!) dmlp) -> ()");
+  m.def("cross_entropy(Tensor logits, Tensor targets, Tensor(a!) row_loss, Tensor(b!)? dlogits, float grad_scale) -> ()");
+  m.def("adamw(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p16, float lr, float beta1, "
+        "float beta2, float eps, float wd, int step, float grad_scale) -> ()");
+  m.def("status() -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
+  m.impl("gemm", &gemm);
+  m.impl("layernorm_fwd", &layernorm_fwd);
+  m.impl("layernorm_bwd", &layernorm_bwd);
+  m.impl("embed_ln_fwd", &embed_ln_fwd);
+  m.impl("embed_ln_bwd", &embed_ln_bwd);
+  m.impl("block_out_fwd", &block_out_fwd);
+  m.impl("block_out_bwd", &block_out_bwd);
+  m.impl("cross_entropy", &cross_entropy);
+  m.impl("adamw", &adamw);
+}
+TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) { m.impl("status", &status); }

@@ -1,0 +1,495 @@
+// Row-wise kernels of the BDH layer: affine-free LayerNorm (eps 1e-5, biased variance; reference
+// src/model/bdh.rs:86-89), the embedding gather fused with its LayerNorm (bdh.rs:319-320), the
+// layer tail cur' = LN(cur + LN(mlp)) (bdh.rs:436-441), mean cross-entropy (src/model/loss.rs:5-18)
+// and the AdamW update. One warp owns one row; a row of D bf16 values is held in registers as
+// 16-byte vectors, so each row is read once and written once.
+#include "bdh_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace bdh {
+
+constexpr int ROW_MAX_CHUNKS = 8;  // 8 chunks * 32 lanes * 8 elements = 2048 columns
+constexpr float LN_EPS = 1e-5f;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int NC>
+struct Row {
+  float v[NC][8];
+};
+
+template <int NC>
+__device__ __forceinline__ void row_load_bf16(Row<NC>& r, const __nv_bfloat16* p, int D, int lane) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+    if (c < D) {
+      uint4 u = *reinterpret_cast<const uint4*>(p + c);
+      float2 f;
+      f = unpack_bf16x2(u.x); r.v[j][0] = f.x; r.v[j][1] = f.y;
+      f = unpack_bf16x2(u.y); r.v[j][2] = f.x; r.v[j][3] = f.y;
+      f = unpack_bf16x2(u.z); r.v[j][4] = f.x; r.v[j][5] = f.y;
+      f = unpack_bf16x2(u.w); r.v[j][6] = f.x; r.v[j][7] = f.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r.v[j][i] = 0.f;
+    }
+  }
+}
+template <int NC>
+__device__ __forceinline__ void row_load_f32(Row<NC>& r, const float* p, int D, int lane) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+    if (c < D) {
+      float4 a = *reinterpret_cast<const float4*>(p + c);
+      float4 b = *reinterpret_cast<const float4*>(p + c + 4);
+      r.v[j][0] = a.x; r.v[j][1] = a.y; r.v[j][2] = a.z; r.v[j][3] = a.w;
+      r.v[j][4] = b.x; r.v[j][5] = b.y; r.v[j][6] = b.z; r.v[j][7] = b.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) r.v[j][i] = 0.f;
+    }
+  }
+}
+template <int NC>
+__device__ __forceinline__ void row_store_bf16(const Row<NC>& r, __nv_bfloat16* p, int D, int lane) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+    if (c < D) {
+      uint4 u;
+      u.x = pack_bf16x2(r.v[j][0], r.v[j][1]);
+      u.y = pack_bf16x2(r.v[j][2], r.v[j][3]);
+      u.z = pack_bf16x2(r.v[j][4], r.v[j][5]);
+      u.w = pack_bf16x2(r.v[j][6], r.v[j][7]);
+      *reinterpret_cast<uint4*>(p + c) = u;
+    }
+  }
+}
+template <int NC>
+__device__ __forceinline__ void row_store_f32(const Row<NC>& r, float* p, int D, int lane, bool accum) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+    if (c < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) p[c + i] = accum ? p[c + i] + r.v[j][i] : r.v[j][i];
+    }
+  }
+}
+
+// In place: r <- (r - mean) * rstd. Columns >= D hold zeros and are restored to zero.
+template <int NC>
+__device__ __forceinline__ void row_layernorm(Row<NC>& r, int D, int lane) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += r.v[j][i];
+  const float mean = warp_sum(s) / D;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float d = (c < D) ? r.v[j][i] - mean : 0.f;
+      r.v[j][i] = d;
+      q += d * d;
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / D + LN_EPS);
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.v[j][i] *= rstd;
+}
+
+// Given y = LN(x) in `y` (already normalised) and upstream grad in `dy`, overwrite dy with dx.
+// rstd must be recomputed by the caller from x; here we take it as an argument.
+template <int NC>
+__device__ __forceinline__ void row_layernorm_bwd(const Row<NC>& y, Row<NC>& dy, float rstd, int D, int lane) {
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      s1 += dy.v[j][i];
+      s2 += dy.v[j][i] * y.v[j][i];
+    }
+  const float m1 = warp_sum(s1) / D, m2 = warp_sum(s2) / D;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      dy.v[j][i] = (c < D) ? rstd * (dy.v[j][i] - m1 - y.v[j][i] * m2) : 0.f;
+  }
+}
+
+// LayerNorm that also returns rstd (needed by the backward).
+template <int NC>
+__device__ __forceinline__ float row_layernorm_rstd(Row<NC>& r, int D, int lane) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += r.v[j][i];
+  const float mean = warp_sum(s) / D;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    int c = (j * 32 + lane) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float d = (c < D) ? r.v[j][i] - mean : 0.f;
+      r.v[j][i] = d;
+      q += d * d;
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / D + LN_EPS);
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.v[j][i] *= rstd;
+  return rstd;
+}
+
+constexpr int ROW_WARPS = 8;
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_fwd_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> r;
+    row_load_bf16(r, x + row * D, D, lane);
+    row_layernorm(r, D, lane);
+    row_store_bf16(r, y + row * D, D, lane);
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* dx,
+                     long long rows, int D, int accumulate) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> y, g;
+    row_load_bf16(y, x + row * D, D, lane);
+    const float rstd = row_layernorm_rstd(y, D, lane);
+    row_load_bf16(g, dy + row * D, D, lane);
+    row_layernorm_bwd(y, g, rstd, D, lane);
+    if (accumulate) {
+      Row<NC> o;
+      row_load_bf16(o, dx + row * D, D, lane);
+#pragma unroll
+      for (int j = 0; j < NC; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g.v[j][i] += o.v[j][i];
+    }
+    row_store_bf16(g, dx + row * D, D, lane);
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+embed_ln_fwd_kernel(const long long* tokens, const __nv_bfloat16* emb, __nv_bfloat16* cur,
+                    long long rows, int D, int vocab) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    long long tok = tokens[row];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    Row<NC> r;
+    row_load_bf16(r, emb + tok * D, D, lane);
+    row_layernorm(r, D, lane);
+    row_store_bf16(r, cur + row * D, D, lane);
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+embed_ln_bwd_kernel(const long long* tokens, const __nv_bfloat16* emb, const float* dcur,
+                    float* demb, long long rows, int D, int vocab) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    long long tok = tokens[row];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    Row<NC> y, g;
+    row_load_bf16(y, emb + tok * D, D, lane);
+    const float rstd = row_layernorm_rstd(y, D, lane);
+    row_load_f32(g, dcur + row * D, D, lane);
+    row_layernorm_bwd(y, g, rstd, D, lane);
+    float* dst = demb + tok * D;
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      int c = (j * 32 + lane) * 8;
+      if (c < D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(dst + c + i, g.v[j][i]);
+      }
+    }
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+block_out_fwd_kernel(const __nv_bfloat16* cur, const __nv_bfloat16* mlp, __nv_bfloat16* out,
+                     long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> u, c;
+    row_load_bf16(u, mlp + row * D, D, lane);
+    row_layernorm(u, D, lane);
+    row_load_bf16(c, cur + row * D, D, lane);
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) u.v[j][i] += c.v[j][i];
+    row_layernorm(u, D, lane);
+    row_store_bf16(u, out + row * D, D, lane);
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+block_out_bwd_kernel(const __nv_bfloat16* cur, const __nv_bfloat16* mlp, const float* dout,
+                     float* dcur, __nv_bfloat16* dmlp, long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> lm, u, g;
+    row_load_bf16(lm, mlp + row * D, D, lane);
+    const float rstd_m = row_layernorm_rstd(lm, D, lane);  // lm = LN(mlp)
+    row_load_bf16(u, cur + row * D, D, lane);
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) u.v[j][i] += lm.v[j][i];
+    const float rstd_u = row_layernorm_rstd(u, D, lane);   // u = LN(cur + LN(mlp))
+    row_load_f32(g, dout + row * D, D, lane);
+    row_layernorm_bwd(u, g, rstd_u, D, lane);              // g = d(cur + LN(mlp))
+    row_store_f32(g, dcur + row * D, D, lane, false);
+    row_layernorm_bwd(lm, g, rstd_m, D, lane);             // g = d mlp
+    row_store_bf16(g, dmlp + row * D, D, lane);
+  }
+}
+
+// One warp per row of fp32 logits, V <= 1024.
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+cross_entropy_kernel(const float* logits, const long long* targets, float* row_loss,
+                     __nv_bfloat16* dlogits, long long rows, int V, float grad_scale) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    const float* p = logits + row * V;
+    float v[32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      int c = j * 32 + lane;
+      v[j] = (c < V) ? p[c] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      int c = j * 32 + lane;
+      if (c < V) {
+        v[j] = __expf(v[j] - mx);
+        s += v[j];
+      }
+    }
+    s = warp_sum(s);
+    const float inv = 1.f / s;
+    long long tgt = targets[row];
+    const bool ignore = tgt < 0 || tgt >= V;
+    if (lane == 0) row_loss[row] = ignore ? 0.f : (logf(s) + mx - p[tgt]);
+    if (dlogits) {
+      __nv_bfloat16* d = dlogits + row * V;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        int c = j * 32 + lane;
+        if (c < V) {
+          float gr = ignore ? 0.f : (v[j] * inv - (c == tgt ? 1.f : 0.f)) * grad_scale;
+          d[c] = __float2bfloat16_rn(gr);
+        }
+      }
+    }
+  }
+}
+
+__global__ void adamw_kernel(float* __restrict__ master, const float* __restrict__ grad,
+                             float* __restrict__ m, float* __restrict__ v,
+                             __nv_bfloat16* __restrict__ p16, long long n, float lr, float b1,
+                             float b2, float eps, float wd, float bc1, float bc2, float gscale) {
+  long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
+  for (; i < n; i += stride) {
+    if (i + 4 <= n) {
+      float4 w = *reinterpret_cast<float4*>(master + i);
+      float4 g = *reinterpret_cast<const float4*>(grad + i);
+      float4 mm = *reinterpret_cast<float4*>(m + i);
+      float4 vv = *reinterpret_cast<float4*>(v + i);
+      float* wp = &w.x; float* gp = &g.x; float* mp = &mm.x; float* vp = &vv.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float gk = gp[k] * gscale;
+        mp[k] = b1 * mp[k] + (1.f - b1) * gk;
+        vp[k] = b2 * vp[k] + (1.f - b2) * gk * gk;
+        float upd = (mp[k] / bc1) / (sqrtf(vp[k] / bc2) + eps);
+        wp[k] = wp[k] * (1.f - lr * wd) - lr * upd;
+      }
+      *reinterpret_cast<float4*>(master + i) = w;
+      *reinterpret_cast<float4*>(m + i) = mm;
+      *reinterpret_cast<float4*>(v + i) = vv;
+      if (p16) {
+        uint2 u;
+        u.x = pack_bf16x2(w.x, w.y);
+        u.y = pack_bf16x2(w.z, w.w);
+        *reinterpret_cast<uint2*>(p16 + i) = u;
+      }
+    } else {
+      for (long long k = i; k < n; ++k) {
+        float gk = grad[k] * gscale;
+        float mk = b1 * m[k] + (1.f - b1) * gk;
+        float vk = b2 * v[k] + (1.f - b2) * gk * gk;
+        m[k] = mk; v[k] = vk;
+        float wk = master[k] * (1.f - lr * wd) - lr * (mk / bc1) / (sqrtf(vk / bc2) + eps);
+        master[k] = wk;
+        if (p16) p16[k] = __float2bfloat16_rn(wk);
+      }
+    }
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* in, __nv_bfloat16* out, long long n) {
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) out[i] = __float2bfloat16_rn(in[i]);
+}
+__global__ void add_f32_kernel(const float* in, float* inout, long long n) {
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) inout[i] += in[i];
+}
+
+static int row_grid(long long rows) {
+  long long b = (rows + ROW_WARPS - 1) / ROW_WARPS;
+  const long long cap = 148 * 16;
+  return static_cast<int>(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+static int flat_grid(long long n, int per_block) {
+  long long b = (n + per_block - 1) / per_block;
+  const long long cap = 148 * 8;
+  return static_cast<int>(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+static bool row_ok(int D) { return D > 0 && D <= ROW_MAX_CHUNKS * 256 && (D % 8) == 0; }
+static int launch_rc() { return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH; }
+
+#define ROW_DISPATCH(D, KERNEL, ...)                                                   \
+  do {                                                                                 \
+    if ((D) <= 256) KERNEL<1><<<row_grid(rows), ROW_WARPS * 32, 0, s>>>(__VA_ARGS__);       \
+    else if ((D) <= 512) KERNEL<2><<<row_grid(rows), ROW_WARPS * 32, 0, s>>>(__VA_ARGS__);  \
+    else if ((D) <= 1024) KERNEL<4><<<row_grid(rows), ROW_WARPS * 32, 0, s>>>(__VA_ARGS__); \
+    else KERNEL<8><<<row_grid(rows), ROW_WARPS * 32, 0, s>>>(__VA_ARGS__);                  \
+  } while (0)
+
+}  // namespace bdh
+
+using namespace bdh;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int bdh_layernorm_fwd(const void* x, void* y, long long rows, int D, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, layernorm_fwd_kernel, (const bf16*)x, (bf16*)y, rows, D);
+  return launch_rc();
+}
+extern "C" int bdh_layernorm_bwd(const void* x, const void* dy, void* dx, long long rows, int D,
+                                 int accumulate, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, layernorm_bwd_kernel, (const bf16*)x, (const bf16*)dy, (bf16*)dx, rows, D, accumulate);
+  return launch_rc();
+}
+extern "C" int bdh_embed_ln_fwd(const long long* tokens, const void* emb, void* cur, long long rows,
+                                int D, int vocab, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, embed_ln_fwd_kernel, tokens, (const bf16*)emb, (bf16*)cur, rows, D, vocab);
+  return launch_rc();
+}
+extern "C" int bdh_embed_ln_bwd(const long long* tokens, const void* emb, const float* dcur,
+                                float* demb, long long rows, int D, int vocab, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, embed_ln_bwd_kernel, tokens, (const bf16*)emb, dcur, demb, rows, D, vocab);
+  return launch_rc();
+}
+extern "C" int bdh_block_out_fwd(const void* cur, const void* mlp, void* out, long long rows, int D,
+                                 cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, block_out_fwd_kernel, (const bf16*)cur, (const bf16*)mlp, (bf16*)out, rows, D);
+  return launch_rc();
+}
+extern "C" int bdh_block_out_bwd(const void* cur, const void* mlp, const float* dout, float* dcur,
+                                 void* dmlp, long long rows, int D, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, block_out_bwd_kernel, (const bf16*)cur, (const bf16*)mlp, dout, dcur, (bf16*)dmlp, rows, D);
+  return launch_rc();
+}
+extern "C" int bdh_cross_entropy(const float* logits, const long long* targets, float* row_loss,
+                                 void* dlogits, long long rows, int V, float grad_scale,
+                                 cudaStream_t s) {
+  if (V <= 0 || V > 1024) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  cross_entropy_kernel<<<row_grid(rows), ROW_WARPS * 32, 0, s>>>(logits, targets, row_loss,
+                                                                 (bf16*)dlogits, rows, V, grad_scale);
+  return launch_rc();
+}
+extern "C" int bdh_adamw(float* master, const float* grad, float* m, float* v, void* p16,
+                         long long n, float lr, float beta1, float beta2, float eps, float wd,
+                         int step, float grad_scale, cudaStream_t s) {
+  if (n == 0) return BDH_OK;
+  if (step < 1) return BDH_ERR_ARGUMENT;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  adamw_kernel<<<flat_grid(n, 1024), 256, 0, s>>>(master, grad, m, v, (bf16*)p16, n, lr, beta1, beta2,
+                                                  eps, wd, bc1, bc2, grad_scale);
+  return launch_rc();
+}
+extern "C" int bdh_cast_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t s) {
+  if (n == 0) return BDH_OK;
+  cast_f32_bf16_kernel<<<flat_grid(n, 256), 256, 0, s>>>(in, (bf16*)out, n);
+  return launch_rc();
+}
+extern "C" int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cudaStream_t s) {
+  if (n == 0) return BDH_OK;
+  add_f32_kernel<<<flat_grid(n, 256), 256, 0, s>>>(in, inout, n);
+  return launch_rc();
+}

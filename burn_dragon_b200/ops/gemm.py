@@ -1,0 +1,166 @@
+"""Front end of the tcgen05 GEMM with fused epilogues (`csrc/gemm_sm100.cuh`).
+
+`gemm(...)` launches the kernel; `gemm_reference(...)` is the same contract written with plain
+fp32 torch ops (any device) and is what the GPU tests compare against.
+
+Contract:  for z0 < nz[0], z1 < nz[1]:
+    C[z][m, n] = epilogue( sum_k A[z][m, k] * B[z][n, k] ),  m < M, n < N, k < K
+Operands are 2-D bf16 matrices. A K-major operand is indexed [mn, k], an MN-major one [k, mn].
+`a_off = (mn per z0, mn per z1, k per z0, k per z1)` shifts the window inside the 2-D matrix for
+each batch index; `c_off = (row per z0, row per z1, col per z0, col per z1)` does the same for
+the outputs and the auxiliary inputs (which share C's coordinates).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import native
+
+EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
+F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_HAS_IN1 = 1, 2, 4, 8, 16, 32, 64
+
+_SUPPORTED = {
+    (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
+    (256, False, False, EPI_CAUSAL), (256, False, False, EPI_GATE_BWD), (256, False, True, EPI_STORE),
+    (256, False, True, EPI_DQ_BWD), (256, True, True, EPI_STORE), (256, True, False, EPI_STORE),
+    (128, False, False, EPI_STORE), (128, False, False, EPI_CAUSAL), (128, False, True, EPI_STORE),
+    (128, True, True, EPI_STORE),
+}
+
+
+def supported(bn: int, a_mn: bool, b_mn: bool, epi: int) -> bool:
+    return (bn, bool(a_mn), bool(b_mn), epi) in _SUPPORTED
+
+
+def operand_ok(t: torch.Tensor) -> bool:
+    """TMA requirements for a 2-D bf16 operand: unit column stride, 16-byte aligned rows."""
+    return (t.dim() == 2 and t.dtype == torch.bfloat16 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
+         nz: Sequence[int] = (1, 1), a_off: Sequence[int] = (0, 0, 0, 0), b_off: Sequence[int] = (0, 0, 0, 0),
+         epi: int = EPI_STORE, flags: int = 0, out0: Optional[torch.Tensor] = None,
+         out1: Optional[torch.Tensor] = None, in0: Optional[torch.Tensor] = None,
+         in1: Optional[torch.Tensor] = None, c_off: Sequence[int] = (0, 0, 0, 0),
+         o1_off: Sequence[int] = (0, 0, 0), alpha: float = 1.0, theta: float = 0.0, T: int = 1, pos0: int = 0,
+         n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+         causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0) -> None:
+    if not native.available():
+        raise RuntimeError("bdh gemm: the sm_100a extension is not available")
+    torch.ops.bdh.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
+                       in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
+                       slopes, causal_tiles, causal_k, bn, max_ctas)
+
+
+# ------------------------------------------------------------------------------------------------
+# fp32 torch statement of the same contract
+# ------------------------------------------------------------------------------------------------
+def _window(t, mn_major, mn_lo, mn_n, k_lo, k_n):
+    if mn_major:
+        return t[k_lo:k_lo + k_n, mn_lo:mn_lo + mn_n].float().t()
+    return t[mn_lo:mn_lo + mn_n, k_lo:k_lo + k_n].float()
+
+
+def rot_phases(pos: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
+    """2*pi*frac(pos*freq) (reference: src/model/attention.rs:342-343). pos [T], freqs [N] -> [T, N]."""
+    raw = pos.float()[:, None] * freqs.float()[None, :]
+    return (raw - raw.floor()) * (2.0 * math.pi)
+
+
+def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """Interleaved-pair rotation (reference: src/model/attention.rs:305-321). x, phases [..., N]."""
+    cos, sin = phases.cos(), phases.sin()
+    if inverse:
+        sin = -sin
+    pairs = x.reshape(*x.shape[:-1], -1, 2)
+    rotated = torch.stack((-pairs[..., 1], pairs[..., 0]), dim=-1).reshape(x.shape)
+    return x * cos + rotated * sin
+
+
+def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0, 0, 0, 0), b_off=(0, 0, 0, 0),
+                   epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
+                   o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
+                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0) -> None:
+    """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
+    dev = a.device
+    for z1 in range(nz[1]):
+        for z0 in range(nz[0]):
+            A = _window(a, a_mn, a_off[0] * z0 + a_off[1] * z1, M, a_off[2] * z0 + a_off[3] * z1, K)
+            B = _window(b, b_mn, b_off[0] * z0 + b_off[1] * z1, N, b_off[2] * z0 + b_off[3] * z1, K)
+            if causal_k:
+                # row block mb only contracts k < mb*128 + 128
+                acc = torch.zeros(M, N, device=dev)
+                for m0 in range(0, M, 128):
+                    ke = min(K, m0 + 128)
+                    acc[m0:m0 + 128] = A[m0:m0 + 128, :ke] @ B[:, :ke].t()
+            else:
+                acc = A @ B.t()
+            r0 = c_off[0] * z0 + c_off[1] * z1
+            c0 = c_off[2] * z0 + c_off[3] * z1
+            rs, cs = slice(r0, r0 + M), slice(c0, c0 + N)
+            mm = torch.arange(M, device=dev)
+            nn = torch.arange(N, device=dev)
+            if epi == EPI_STORE:
+                v = acc * alpha
+                if flags & F_ACCUM:
+                    v = v + out0[rs, cs].float()
+                out0[rs, cs] = v.to(out0.dtype)
+            elif epi == EPI_RELU:
+                x = torch.relu(acc - theta)
+                out0[rs, cs] = x.to(out0.dtype)
+                if flags & (F_ROPE | F_POPE):
+                    pos = pos0 + (mm % T)
+                    ph = rot_phases(pos, freqs[(nn % n_per_head)])
+                    c1 = o1_off[0] * z0 + o1_off[1] * z1
+                    if flags & F_ROPE:
+                        out1[rs, c1:c1 + N] = rope_rotate(x, ph).to(out1.dtype)
+                    else:
+                        mag = torch.nn.functional.softplus(x)
+                        out1[rs, c1:c1 + N] = (mag * ph.cos()).to(out1.dtype)
+                        out1[rs, c1 + o1_off[2]:c1 + o1_off[2] + N] = (mag * ph.sin()).to(out1.dtype)
+            elif epi == EPI_RELU_GATE:
+                y = torch.relu(acc - theta)
+                if not (flags & F_NO_OUT0):
+                    out0[rs, cs] = y.to(out0.dtype)
+                out1[rs, cs] = (y * in0[rs, cs].float()).to(out1.dtype)
+            elif epi == EPI_CAUSAL:
+                slope = float(slopes[z0]) if slopes is not None else 0.0
+                dist = (mm[:, None] - nn[None, :]).float()
+                if flags & F_UPPER:
+                    mask = dist < 0
+                    val = acc * alpha * torch.exp(-slope * dist.abs())
+                    cur = out0[rs, cs].float()
+                    if causal_tiles == 2:
+                        # tiles entirely below the diagonal are never visited
+                        pass
+                    out0[rs, cs] = torch.where(mask, val, cur).to(out0.dtype)
+                else:
+                    val = torch.where(dist > 0, acc * alpha * torch.exp(-slope * dist.abs()), torch.zeros_like(acc))
+                    if causal_tiles == 1:
+                        # tiles with n0 >= m0 + 128 are never written: keep what is there
+                        m0 = (mm // 128) * 128
+                        n0 = (nn // bn) * bn
+                        visited = n0[None, :] <= (m0[:, None] + 127)
+                        val = torch.where(visited, val, out0[rs, cs].float())
+                    out0[rs, cs] = val.to(out0.dtype)
+            elif epi == EPI_GATE_BWD:
+                x = in0[rs, cs].float()
+                y = in1[rs, cs].float()
+                out0[rs, cs] = torch.where(y > 0, acc * x, torch.zeros_like(acc)).to(out0.dtype)
+                out1[rs, cs] = (acc * y).to(out1.dtype)
+            elif epi == EPI_DQ_BWD:
+                x = in0[rs, cs].float()
+                v = acc
+                if flags & F_ROPE:
+                    pos = pos0 + (mm % T)
+                    ph = rot_phases(pos, freqs[(nn % n_per_head)])
+                    v = rope_rotate(v, ph, inverse=True)
+                if flags & F_HAS_IN1:
+                    v = v + in1[rs, cs].float()
+                out0[rs, cs] = torch.where(x > 0, v * alpha, torch.zeros_like(v)).to(out0.dtype)
+            else:
+                raise ValueError(f"unknown epilogue {epi}")

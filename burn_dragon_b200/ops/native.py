@@ -1,0 +1,61 @@
+"""Loader for the compiled sm_100a extension (`torch.ops.bdh.*`).
+
+`available()` is True only when a CUDA device is present and the library loaded. On a machine
+with a GPU a missing or unloadable library is an error, never a silent fallback: the torch
+definitions in `ops.reference` exist for CPU runs and as numerical oracles, not as a GPU path.
+"""
+from __future__ import annotations
+
+import os
+import threading
+
+import torch
+
+_lock = threading.Lock()
+_state = {"loaded": False, "error": None}
+
+
+def load(build_if_missing: bool = True) -> bool:
+    """Load `_C.so` into the process (idempotent). Returns True when torch.ops.bdh is usable."""
+    with _lock:
+        if _state["loaded"]:
+            return True
+        from .. import build as _build
+
+        try:
+            if build_if_missing:
+                path = _build.ensure_built()
+            else:
+                path = _build.LIB
+                if not path.exists():
+                    raise FileNotFoundError(path)
+            torch.ops.load_library(str(path))
+            _state["loaded"] = True
+        except Exception as e:  # noqa: BLE001 - reported to the caller below
+            _state["error"] = e
+            if torch.cuda.is_available() and os.environ.get("BDH_ALLOW_NO_NATIVE", "0") != "1":
+                raise RuntimeError(
+                    "burn_dragon_b200: the sm_100a extension could not be loaded on a machine with a GPU; "
+                    "run `python -m burn_dragon_b200.build`"
+                ) from e
+            return False
+        return True
+
+
+def available() -> bool:
+    """True when kernels can actually run: a CUDA device exists and the extension is loaded."""
+    if not torch.cuda.is_available():
+        return False
+    return load()
+
+
+def status_code() -> int:
+    """Read the device status word (synchronises). Non-zero means an in-kernel wait gave up."""
+    if not available():
+        return 0
+    return int(torch.ops.bdh.status()[0].item())
+
+
+def clear_status() -> None:
+    if available():
+        torch.ops.bdh.status().zero_()

@@ -1,0 +1,157 @@
+"""tcgen05 GEMM and its fused epilogues against the fp32 torch statement of the same contract."""
+import pytest
+import torch
+
+from burn_dragon_b200.ops import gemm as G
+from burn_dragon_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(r, c, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(r, c, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def _check(got, want, tol=2e-2):
+    got, want = got.float(), want.float()
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item() + 1e-6
+    assert err <= tol * ref + 1e-3, f"max abs err {err} (ref max {ref})"
+
+
+def _run_both(kw, outs):
+    """Run kernel and reference on clones of the outputs; return list of (kernel, reference)."""
+    native.clear_status()
+    k_outs = {n: t.clone() for n, t in outs.items()}
+    r_outs = {n: t.clone() for n, t in outs.items()}
+    G.gemm(**kw, **k_outs)
+    torch.cuda.synchronize()
+    assert native.status_code() == 0, "kernel reported a wait timeout"
+    G.gemm_reference(**kw, **r_outs)
+    return [(k_outs[n], r_outs[n]) for n in outs]
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 192), (200, 328, 136)])
+def test_store_majors(a_mn, b_mn, M, N, K):
+    a = _rand(K, M, seed=1) if a_mn else _rand(M, K, seed=1)
+    b = _rand(K, N, seed=2) if b_mn else _rand(N, K, seed=2)
+    kw = dict(a=a, b=b, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, epi=G.EPI_STORE)
+    for k, r in _run_both(kw, dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))):
+        _check(k, r)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_store_f32_accumulate(bn):
+    M, N, K = 256, 256, 512
+    a, b = _rand(K, M, seed=3), _rand(K, N, seed=4)
+    out = torch.randn(M, N, device="cuda")
+    kw = dict(a=a, b=b, M=M, N=N, K=K, a_mn=True, b_mn=True, epi=G.EPI_STORE, flags=G.F_OUT_F32 | G.F_ACCUM,
+              alpha=0.5, bn=bn)
+    for k, r in _run_both(kw, dict(out0=out)):
+        _check(k, r, tol=1e-2)
+
+
+def test_long_k_pipeline():
+    # many k-blocks and many tiles per CTA exercise the smem ring and both accumulators
+    M, N, K = 1024, 1024, 4096
+    a, b = _rand(M, K, 0.1, seed=5), _rand(N, K, 0.1, seed=6)
+    kw = dict(a=a, b=b, M=M, N=N, K=K, epi=G.EPI_STORE, max_ctas=3)
+    for k, r in _run_both(kw, dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))):
+        _check(k, r)
+
+
+def test_batched_offsets():
+    # z0 = head (column window of A, row window of B), z1 = batch (row window of A)
+    H, Bb, T, Nh, D = 2, 3, 128, 256, 64
+    a = _rand(Bb * T, D, seed=7)            # cur [M, D]
+    w = _rand(H * Nh, D, seed=8)            # weights [H*N, D]
+    out = torch.zeros(Bb * T, H * Nh, device="cuda", dtype=torch.bfloat16)
+    kw = dict(a=a, b=w, M=T, N=Nh, K=D, nz=(H, Bb), a_off=(0, T, 0, 0), b_off=(Nh, 0, 0, 0),
+              c_off=(0, T, Nh, 0), epi=G.EPI_STORE)
+    for k, r in _run_both(kw, dict(out0=out)):
+        _check(k, r)
+    _check(out.copy_(_run_both(kw, dict(out0=out))[0][0]), (a.float() @ w.float().t()))
+
+
+@pytest.mark.parametrize("rot", ["none", "rope", "pope"])
+def test_relu_rotary(rot):
+    M, N, K, T, Nh = 256, 512, 128, 64, 256
+    a, w = _rand(M, K, seed=9), _rand(N, K, 0.2, seed=10)
+    freqs = (1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh))) / 6.283185307
+    flags = {"none": 0, "rope": G.F_ROPE, "pope": G.F_POPE}[rot]
+    outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
+    kw = dict(a=a, b=w, M=M, N=N, K=K, epi=G.EPI_RELU, flags=flags, theta=0.1, T=T, pos0=5, n_per_head=Nh,
+              freqs=freqs.float().contiguous())
+    if rot == "rope":
+        outs["out1"] = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    if rot == "pope":
+        # per-head layout [real Nh | imag Nh]; run one head per z0
+        outs["out1"] = torch.zeros(M, 2 * N, device="cuda", dtype=torch.bfloat16)
+        kw.update(N=Nh, nz=(N // Nh, 1), b_off=(Nh, 0, 0, 0), c_off=(0, 0, Nh, 0), o1_off=(2 * Nh, 0, Nh))
+    for k, r in _run_both(kw, outs):
+        _check(k, r)
+
+
+def test_relu_gate():
+    M, N, K = 256, 512, 128
+    a, w, x = _rand(M, K, seed=11), _rand(N, K, 0.2, seed=12), _rand(M, N, seed=13).relu()
+    kw = dict(a=a, b=w, M=M, N=N, K=K, epi=G.EPI_RELU_GATE, in0=x)
+    outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16),
+                out1=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
+    for k, r in _run_both(kw, outs):
+        _check(k, r)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("upper", [False, True])
+def test_causal_decay(bn, upper):
+    H, Bb, T, Nh = 2, 2, 512, 128
+    q = _rand(Bb * T, H * Nh, 0.3, seed=14)
+    slopes = torch.tensor([0.05, 0.02], device="cuda")
+    out = torch.full((Bb * H * T, T), 7.0, device="cuda", dtype=torch.bfloat16)
+    kw = dict(a=q, b=q, M=T, N=T, K=Nh, nz=(H, Bb), a_off=(0, T, Nh, 0), b_off=(0, T, Nh, 0),
+              c_off=(T, H * T, 0, 0), epi=G.EPI_CAUSAL, flags=G.F_UPPER if upper else 0, slopes=slopes,
+              causal_tiles=2 if upper else 1, bn=bn)
+    for k, r in _run_both(kw, dict(out0=out)):
+        _check(k, r)
+
+
+def test_causal_k_value_product():
+    # a = S V with S lower-triangular: only k < m0+128 is contracted
+    Bb, T, D = 2, 512, 256
+    S = torch.tril(_rand(Bb * T, T, 0.2, seed=15).float().reshape(Bb, T, T), -1).reshape(Bb * T, T).to(torch.bfloat16)
+    V = _rand(Bb * T, D, seed=16)
+    out = torch.zeros(Bb * T, D, device="cuda", dtype=torch.bfloat16)
+    kw = dict(a=S, b=V, M=T, N=D, K=T, b_mn=True, nz=(1, Bb), a_off=(0, T, 0, 0), b_off=(0, 0, 0, T),
+              c_off=(0, T, 0, 0), epi=G.EPI_STORE, causal_k=1)
+    for k, r in _run_both(kw, dict(out0=out)):
+        _check(k, r)
+    want = torch.bmm(S.float().reshape(Bb, T, T), V.float().reshape(Bb, T, D)).reshape(Bb * T, D)
+    G.gemm(**kw, out0=out)
+    _check(out, want)
+
+
+def test_gate_bwd():
+    M, N, K = 256, 512, 128
+    g, w = _rand(M, K, seed=17), _rand(N, K, 0.2, seed=18)
+    x, y = _rand(M, N, seed=19).relu(), _rand(M, N, seed=20).relu()
+    kw = dict(a=g, b=w, M=M, N=N, K=K, epi=G.EPI_GATE_BWD, in0=x, in1=y)
+    outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16),
+                out1=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
+    for k, r in _run_both(kw, outs):
+        _check(k, r)
+
+
+@pytest.mark.parametrize("rope", [False, True])
+def test_dq_bwd(rope):
+    T, N, Nh = 256, 512, 256
+    gs = _rand(T, T, 0.2, seed=21)
+    q = _rand(T, N, seed=22)
+    x, dxg = _rand(T, N, seed=23).relu(), _rand(T, N, seed=24)
+    freqs = (1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh))) / 6.283185307
+    kw = dict(a=gs, b=q, M=T, N=N, K=T, b_mn=True, epi=G.EPI_DQ_BWD, flags=(G.F_ROPE if rope else 0) | G.F_HAS_IN1,
+              in0=x, in1=dxg, T=T, pos0=3, n_per_head=Nh, freqs=freqs.float().contiguous())
+    for k, r in _run_both(kw, dict(out0=torch.zeros(T, N, device="cuda", dtype=torch.bfloat16))):
+        _check(k, r)
