@@ -1,0 +1,226 @@
+#!/usr/bin/env python
+"""Headline benchmark: BDH base training throughput (tokens/s) on N B200s.
+
+Config (the named benchmark config): L=6 shared-weight layers, D=256, 4 heads, N=8192 neurons per
+head, byte vocab 256, RoPE causal linear attention, T=512, B=32 per GPU, bf16 compute with fp32
+master weights, AdamW lr 1e-3, data-parallel over N GPUs (weak scaling). Tokens are synthetic
+uniform random bytes from a per-rank seeded generator; weights are random-init.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+      --master-port P bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints one JSON line. `value` is device-timed (CUDA events around exactly K steps, barrier +
+synchronize on both sides, max over ranks). `e2e` repeats the measurement through the public
+Trainer API with a pinned-host -> device copy of every step's batch and a device -> host read of
+every step's loss inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(n_layer=6, n_embd=256, n_head=4, n_latent_per_head=8192, vocab_size=256, dropout=0.0,
+             rotary_embedding="rope")
+SEQ_LEN = 512
+BATCH_PER_GPU = 32
+
+
+def reference_arm(args) -> int:
+    """The reference is a Rust crate (Burn 0.19); there is no Rust toolchain or vendored crate set
+    in this image and `pip install /root/reference` has nothing to install, so it cannot run."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is a Rust/Burn crate: no cargo/rustc in the image, crates not vendored, "
+                      "and it has no setup.py/pyproject.toml for pip to install"}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            parts = [p.strip() for p in r.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        # median over samples taken under load (the upper half of the sorted clocks covers idle gaps)
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nccl-only", action="store_true", help="NCCL all-reduce instead of the fused NVLink path")
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU)
+    ap.add_argument("--seq", type=int, default=SEQ_LEN)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel import dist_utils
+
+    world = dist_utils.env_world()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch multi-GPU runs with torch.distributed.run (one process per GPU)")
+    dist_utils.init_distributed()
+    rank, local = dist_utils.rank(), dist_utils.env_local_rank()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    native.load()
+
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+    B, T = args.batch, args.seq
+    torch.manual_seed(1337)
+    model = BDH(BDHConfig(**MODEL)).to(dev)
+    trainer = Trainer(model, lr=1e-3, weight_decay=0.1, parallel="ddp" if world > 1 else "single",
+                      fused_collectives=not args.nccl_only)
+
+    # synthetic uniform bytes, per-rank seed; one pinned host buffer per step so e2e copies real data
+    gen = torch.Generator().manual_seed(1000 + rank)
+    n_batches = W + K
+    host = [torch.randint(0, 256, (B, T + 1), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
+    dev_batches = [h.to(dev) for h in host]
+
+    def device_step(i):
+        b = dev_batches[i % n_batches]
+        return trainer.train_step(b[:, :-1], b[:, 1:])
+
+    # ---------------- device-timed region ----------------
+    for i in range(W):
+        device_step(i)
+    torch.cuda.synchronize()
+    dist_utils.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        loss = device_step(W + i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist_utils.barrier()
+    torch.cuda.synchronize()
+    launches = native.launch_count() - launches0
+    ms = dist_utils.max_over_ranks(e0.elapsed_time(e1), dev)
+    clocks = sampler.stop() if rank == 0 else None
+    final_loss = float(loss.item())
+
+    # ---------------- end-to-end region (pinned H2D of inputs + D2H of loss every step) ----------------
+    stage = torch.empty(B, T + 1, dtype=torch.int64, device=dev)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def e2e_step(i):
+        stage.copy_(host[i % n_batches], non_blocking=True)
+        l = trainer.train_step(stage[:, :-1], stage[:, 1:])
+        loss_host.copy_(l, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(loss_host)
+
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    dist_utils.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(K):
+        e2e_step(W + i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist_utils.barrier()
+    ms_e2e = dist_utils.max_over_ranks(e0.elapsed_time(e1), dev)
+
+    tokens = B * T * world * K
+    value = tokens / (ms / 1e3)
+    e2e_value = tokens / (ms_e2e / 1e3)
+    status = native.status_code()
+    if rank == 0:
+        out = {
+            "metric": "BDH train tokens/s (device-timed, max over ranks)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform random bytes, random-init weights",
+            "config": {"model": "bdh-base L6 D256 H4 N8192 V256 rope", "global_batch": B * world, "seq_len": T,
+                       "parallelism": f"dp{world}" if world > 1 else "single",
+                       "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
+                       "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
+                       "allreduce": ("nccl" if args.nccl_only else "fused-nvlink") if world > 1 else "none"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
+                    "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "final_loss": final_loss,
+            "kernel_status": status,
+            "model_flops_per_step": 3 * model.config.flops_per_token_forward(T) * B * T,
+        }
+        print(json.dumps(out))
+    if dist_utils.world_size() > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

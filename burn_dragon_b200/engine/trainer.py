@@ -1,0 +1,77 @@
+"""Training engine: one object that owns model, optimizer, parallel wrapper and the step function.
+
+`Trainer.train_step(tokens, targets)` is the public per-step call (what `train` and `bench.py` use):
+zero grads -> loss -> backward -> gradient reduction -> AdamW with the scheduled LR. It mirrors the
+reference's TrainStep (src/bin/train.rs:134-146) plus what burn-train's Learner does around it
+(optimizer step, LR scheduler step, src/bin/train.rs:380-419).
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Dict, Optional
+
+import torch
+
+from ..parallel import dist_utils
+from ..parallel.ddp import DataParallel
+from .optim import FlatAdamW, FlatParams, LRSchedule
+
+
+class Trainer:
+    def __init__(self, model: torch.nn.Module, lr: float = 1e-3, weight_decay: float = 0.1, beta1: float = 0.9,
+                 beta2: float = 0.999, eps: float = 1e-5, schedule: Optional[LRSchedule] = None,
+                 parallel: str = "single", fused_collectives: bool = True, fast_train: bool = False,
+                 grad_clip: Optional[float] = None, wrapper=None):
+        self.model = model
+        self.fast_train = fast_train
+        self.grad_clip = grad_clip
+        self.schedule = schedule
+        self.parallel = parallel
+        self.step_index = 0
+        self.wrapper = wrapper
+        if wrapper is not None:
+            # FSDP / TP wrappers own parameter storage, gradient reduction and the optimizer
+            self.opt = wrapper.optimizer
+            self.dp = None
+        else:
+            shadow = next(model.parameters()).is_cuda
+            self.opt = FlatAdamW(model, lr, weight_decay, beta1, beta2, eps, shadow_bf16=shadow)
+            self.dp = DataParallel(self.opt.flat, mode="fused" if fused_collectives else "nccl") \
+                if parallel == "ddp" and dist_utils.world_size() > 1 else None
+            if self.dp is not None:
+                self.dp.broadcast_parameters()
+        self.base_lr = lr
+
+    def current_lr(self) -> float:
+        return self.schedule(self.step_index) if self.schedule is not None else self.base_lr
+
+    def loss_fn(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        if self.fast_train and hasattr(self.model, "forward_fast"):
+            return self.model.forward_fast(tokens, targets)
+        return self.model(tokens, targets)
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One optimizer step. Returns the (local) loss as a 0-d device tensor; no host sync."""
+        if self.wrapper is not None:
+            loss = self.wrapper.train_step(tokens, targets, self.current_lr())
+            self.step_index += 1
+            return loss
+        self.opt.zero_grad()
+        loss = self.loss_fn(tokens, targets)
+        loss.backward()
+        scale = self.dp.reduce_gradients() if self.dp is not None else 1.0
+        if self.grad_clip:
+            gn = (self.opt.flat.grad.norm() * scale)
+            scale = scale * float(torch.clamp(self.grad_clip / (gn + 1e-6), max=1.0))
+        self.opt.step(lr=self.current_lr(), grad_scale=scale)
+        self.step_index += 1
+        return loss.detach()
+
+    @torch.no_grad()
+    def eval_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        was = self.model.training
+        self.model.eval()
+        try:
+            return self.loss_fn(tokens, targets).detach()
+        finally:
+            self.model.train(was)

@@ -1,0 +1,293 @@
+"""BDH forward / backward on the sm_100a kernels.
+
+The whole stack (embedding+LN, L shared-weight layers, LM head, cross-entropy) is one
+`torch.autograd.Function`; its forward and backward are explicit sequences of tcgen05 GEMM
+launches with fused epilogues plus a few row-wise kernels. The math is the canonical recurrent
+semantics of the reference (src/model/bdh.rs:309-450) in its exact parallel form
+    a_t = sum_{s<t} g^(t-s) (q_t . q_s) v_s
+evaluated as  S = causal_decay(Q Q^T),  A = S V  per (batch, head).
+
+Activation layouts (all bf16, row-major 2-D):
+  cur  [M, D]          M = B*T tokens, row b*T + t
+  x,q,y,xy [M, H*N']   column h*N' + n
+  S    [B*H*T, T]      row (b*H + h)*T + t, column s
+  a    [H*M, D]        row (h*B + b)*T + t   (head-major so each head's rows are contiguous)
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from . import gemm as G
+from . import native
+from . import reference as R
+
+ops = native.ops
+
+
+# ------------------------------------------------------------------------------------------------
+# eligibility
+# ------------------------------------------------------------------------------------------------
+def can_run(model, tokens: torch.Tensor, state) -> bool:
+    """True when the kernel path computes exactly what the torch path defines for this call."""
+    if not getattr(model, "use_native", True) or not tokens.is_cuda or not native.available():
+        return False
+    c = model.config
+    B, T = tokens.shape
+    if T % 64 or c.n_embd % 8 or c.n_embd > 2048 or c.latent_per_head % 64:
+        return False
+    if c.dropout > 0 and model.training:
+        return False
+    if c.block_sparse is not None and (c.block_sparse.latent.is_sparse() or c.block_sparse.time.is_sparse()):
+        return False
+    if c.vocab_size > 1024:
+        return False
+    if state is not None:
+        has_rho = any(l.rho is not None for l in state.layers)
+        if has_rho and c.rotary_embedding == "alibi":
+            return False       # decayed carry-in needs a per-row scale; the torch path handles it
+        if has_rho and any(l.rho is None or l.rho.shape[0] != B for l in state.layers):
+            return False
+    return True
+
+
+def _weights(model) -> Dict[str, torch.Tensor]:
+    """bf16 working copies of the parameters. An optimizer that keeps a bf16 shadow registers it as
+    `model._bf16_shadow`; otherwise the weights are cast here."""
+    sh = getattr(model, "_bf16_shadow", None)
+    if sh is not None:
+        return sh
+    return {n: p.detach().to(torch.bfloat16) for n, p in
+            (("embed", model.embed.weight), ("encoder", model.encoder), ("encoder_v", model.encoder_v),
+             ("decoder", model.decoder), ("lm_head", model.lm_head))}
+
+
+class _Dims:
+    def __init__(self, model, B, T):
+        c = model.config
+        self.B, self.T, self.M = B, T, B * T
+        self.D, self.H, self.N = c.n_embd, c.n_head, c.latent_per_head
+        self.Np = c.state_latent
+        self.HN, self.HNp = self.H * self.N, self.H * self.Np
+        self.V = c.vocab_size
+        self.L = c.n_layer
+        self.rot = c.rotary_embedding
+        self.theta = float(c.relu_threshold)
+        self.freqs = model.freqs.float().contiguous() if self.rot != "alibi" else None
+        self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
+
+
+def _bf16(rows, cols, dev):
+    return torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------------
+# one layer forward
+# ------------------------------------------------------------------------------------------------
+def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool):
+    dev = cur.device
+    M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
+    x = _bf16(M, d.HN, dev)
+    if d.rot == "rope":
+        q = _bf16(M, d.HN, dev)
+        G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, flags=G.F_ROPE, out0=x, out1=q, theta=d.theta,
+               T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
+    elif d.rot == "pope":
+        q = _bf16(M, d.HNp, dev)
+        G.gemm(cur, W["encoder"], M=M, N=N, K=D, nz=(H, 1), b_off=(N, 0, 0, 0), c_off=(0, 0, N, 0),
+               o1_off=(Np, 0, N), epi=G.EPI_RELU, flags=G.F_POPE, out0=x, out1=q, theta=d.theta, T=T, pos0=pos0,
+               n_per_head=N, freqs=d.freqs)
+    else:
+        q = x
+        G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, out0=x, theta=d.theta)
+
+    S = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)   # tiles above the diagonal stay zero
+    G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
+           epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
+    a = _bf16(H * M, D, dev)
+    G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
+           c_off=(M, T, 0, 0), causal_k=1, out0=a)
+    if rho_in is not None:
+        # carry-in (no decay): a += q . rho_in
+        rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
+        G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
+               c_off=(M, T, 0, 0), flags=G.F_ACCUM, out0=a)
+    rho_out = None
+    if want_rho:
+        rho_out = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
+        if d.slopes is not None:
+            t = torch.arange(T, device=dev, dtype=torch.float32)
+            w = torch.exp(-d.slopes.view(H, 1) * (T - t).view(1, T))                     # g^(T-s)
+            vw = (cur.view(1, B, T, D).float() * w.view(H, 1, T, 1)).to(torch.bfloat16).reshape(H * M, D)
+            b_off = (0, 0, M, T)
+        else:
+            vw, b_off = cur, (0, 0, 0, T)
+        G.gemm(q, vw, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=b_off,
+               c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho_out.view(B * H * Np, D))
+        if rho_in is not None:
+            rho_out += rho_in
+    lna = torch.empty_like(a)
+    ops.layernorm_fwd(a, lna)
+    y = _bf16(M, d.HN, dev)
+    xy = _bf16(M, d.HN, dev)
+    G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
+           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, in0=x, out0=y, out1=xy, theta=d.theta)
+    mlp = _bf16(M, D, dev)
+    G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
+    out = torch.empty_like(cur)
+    ops.block_out_fwd(cur, mlp, out)
+    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, y=y, xy=xy, mlp=mlp)
+    return out, saved, rho_out
+
+
+def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
+    """dout: fp32 [M, D] gradient of the layer output. Returns fp32 [M, D] gradient of the layer input.
+    Weight gradients are accumulated into grads['encoder'|'encoder_v'|'decoder'] (fp32)."""
+    dev = dout.device
+    M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
+    cur, x, q, S, a, lna, y, xy, mlp = (sv[k] for k in ("cur", "x", "q", "S", "a", "lna", "y", "xy", "mlp"))
+    dcur = torch.empty(M, D, device=dev, dtype=torch.float32)
+    dmlp = _bf16(M, D, dev)
+    ops.block_out_bwd(cur, mlp, dout, dcur, dmlp)
+    # gate
+    dy = _bf16(M, d.HN, dev)
+    dxg = _bf16(M, d.HN, dev)
+    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=y, out0=dy, out1=dxg)
+    G.gemm(xy, dmlp, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["decoder"])
+    # y = relu(LN(a) E_v)
+    G.gemm(dy, lna, M=N, N=D, K=M, a_mn=True, b_mn=True, nz=(H, 1), a_off=(N, 0, 0, 0), b_off=(0, 0, M, 0),
+           c_off=(N, 0, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder_v"])
+    dlna = _bf16(H * M, D, dev)
+    G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
+           c_off=(M, 0, 0, 0), out0=dlna)
+    del dy
+    da = _bf16(H * M, D, dev)
+    ops.layernorm_bwd(a, dlna, da, False)
+    # attention: Gs = causal(dA V^T) + causal(dA V^T)^T with the decay mask
+    Gs = _bf16(B * H * T, T, dev)
+    G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
+           epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=Gs)
+    G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
+           epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
+    # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h ; heads run as separate launches
+    for h in range(H):
+        G.gemm(S[h * T:], da[h * M:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),
+               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=dcur)
+    # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
+    dx = _bf16(M, d.HN, dev)
+    if d.rot == "pope":
+        dq = _bf16(M, d.HNp, dev)
+        G.gemm(Gs, q, M=T, N=Np, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(Np, 0, 0, T),
+               c_off=(0, T, Np, 0), out0=dq)
+        pos = torch.arange(pos0, pos0 + T, device=dev)
+        ph = R.phases(pos, d.freqs)                                          # [T, N]
+        dq4 = dq.view(B, T, H, 2, N).float()
+        xf = x.view(B, T, H, N).float()
+        dmag = dq4[:, :, :, 0] * ph.cos().view(1, T, 1, N) + dq4[:, :, :, 1] * ph.sin().view(1, T, 1, N)
+        dxv = dmag * torch.sigmoid(xf) + dxg.view(B, T, H, N).float()
+        dx.copy_(torch.where(xf > 0, dxv, torch.zeros_like(dxv)).view(M, d.HN))
+    else:
+        flags = G.F_HAS_IN1 | (G.F_ROPE if d.rot == "rope" else 0)
+        G.gemm(Gs, q, M=T, N=N, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(N, 0, 0, T),
+               c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=flags, in0=x, in1=dxg, out0=dx, T=T, pos0=pos0,
+               n_per_head=N, freqs=d.freqs)
+    del dxg
+    G.gemm(dx, cur, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder"])
+    G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=dcur)
+    return dcur
+
+
+# ------------------------------------------------------------------------------------------------
+# whole model
+# ------------------------------------------------------------------------------------------------
+def _embed(d, W, tokens):
+    cur = _bf16(d.M, d.D, tokens.device)
+    ops.embed_ln_fwd(tokens.reshape(-1).contiguous(), W["embed"], cur)
+    return cur
+
+
+def _head_logits(d, W, cur):
+    dev = cur.device
+    if d.V % 8 == 0:
+        logits = torch.empty(d.M, d.V, device=dev, dtype=torch.float32)
+        G.gemm(cur, W["lm_head"], M=d.M, N=d.V, K=d.D, b_mn=True, flags=G.F_OUT_F32, out0=logits)
+        return logits
+    return cur.float() @ W["lm_head"].float()
+
+
+def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: bool):
+    cur = _embed(d, W, tokens)
+    pos0 = state.position if state is not None else 0
+    saved: List[dict] = []
+    for l in range(d.L):
+        rho_in = state.layers[l].rho if state is not None else None
+        out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None)
+        if state is not None:
+            state.layers[l].rho = rho_out
+        if save:
+            saved.append(dict(cur=cur) if recompute else sv)
+        cur = out
+    if state is not None:
+        state.position += d.T
+    return cur, saved
+
+
+@torch.no_grad()
+def forward_logits(model, tokens: torch.Tensor, state) -> torch.Tensor:
+    B, T = tokens.shape
+    d = _Dims(model, B, T)
+    W = _weights(model)
+    cur, _ = _stack_forward(model, d, W, tokens, state, save=False, recompute=False)
+    return _head_logits(d, W, cur).view(B, T, d.V)
+
+
+class _FusedLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, targets, embed_w, encoder, encoder_v, decoder, lm_head, model):
+        B, T = tokens.shape
+        d = _Dims(model, B, T)
+        W = _weights(model)
+        recompute = bool(getattr(model, "recompute", False))
+        cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute)
+        logits = _head_logits(d, W, cur)
+        row_loss = torch.empty(d.M, device=tokens.device, dtype=torch.float32)
+        dlogits = _bf16(d.M, d.V, tokens.device)
+        ops.cross_entropy(logits, targets.reshape(-1).contiguous(), row_loss, dlogits, 1.0 / d.M)
+        ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits = d, W, saved, cur, dlogits
+        ctx.tokens = tokens
+        ctx.recompute = recompute
+        return row_loss.sum() / d.M
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        d, W, saved, cur, dlogits = ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits
+        dev = cur.device
+        grads = {k: torch.zeros(d.HN, d.D, device=dev, dtype=torch.float32)
+                 for k in ("encoder", "encoder_v", "decoder")}
+        # head
+        if d.V % 8 == 0:
+            g_head = torch.empty(d.D, d.V, device=dev, dtype=torch.float32)
+            G.gemm(cur, dlogits, M=d.D, N=d.V, K=d.M, a_mn=True, b_mn=True, flags=G.F_OUT_F32, out0=g_head)
+            dcur = torch.empty(d.M, d.D, device=dev, dtype=torch.float32)
+            G.gemm(dlogits, W["lm_head"], M=d.M, N=d.D, K=d.V, flags=G.F_OUT_F32, out0=dcur)
+        else:
+            g_head = cur.float().t() @ dlogits.float()
+            dcur = dlogits.float() @ W["lm_head"].float().t()
+        for l in reversed(range(d.L)):
+            sv = saved[l]
+            if ctx.recompute:
+                _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False)
+            dcur = _layer_backward(d, W, sv, dcur, grads, 0)
+            saved[l] = None
+        g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)
+        ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)
+        s = grad_out.to(torch.float32)
+        return (None, None, g_emb * s, grads["encoder"] * s, grads["encoder_v"] * s, grads["decoder"] * s,
+                g_head * s, None)
+
+
+def loss(model, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Mean cross-entropy of the canonical forward, differentiable w.r.t. the model parameters."""
+    return _FusedLoss.apply(tokens, targets, model.embed.weight, model.encoder, model.encoder_v, model.decoder,
+                            model.lm_head, model)

@@ -51,7 +51,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
-    torch.ops.bdh.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
+    native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas)
 

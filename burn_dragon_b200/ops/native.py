@@ -59,3 +59,28 @@ def status_code() -> int:
 def clear_status() -> None:
     if available():
         torch.ops.bdh.status().zero_()
+
+
+class _CountingOps:
+    """`torch.ops.bdh` with a launch counter: every call through this proxy launches exactly one of
+    this library's kernels, so `launch_count()` is the number of own kernels launched so far."""
+
+    def __init__(self):
+        self.count = 0
+
+    def __getattr__(self, name):
+        fn = getattr(torch.ops.bdh, name)
+
+        def call(*a, **k):
+            self.count += 1
+            return fn(*a, **k)
+
+        self.__dict__[name] = call
+        return call
+
+
+ops = _CountingOps()
+
+
+def launch_count() -> int:
+    return ops.count

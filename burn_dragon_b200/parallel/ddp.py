@@ -1,0 +1,53 @@
+"""Data parallelism over a flat gradient buffer.
+
+The reference trains on a single device only (src/bin/train.rs:395); this is new capability.
+Because every parameter's gradient lives in one contiguous fp32 buffer (engine.optim.FlatParams)
+and the BDH weights are shared by all layers (their gradients are complete only when the whole
+backward has finished), gradient reduction is one collective over one pointer, followed by the
+AdamW kernel that folds in the 1/world scale.
+
+Two reductions are available:
+  nccl   torch.distributed all_reduce (the measured baseline)
+  fused  the in-kernel NVLink reduction of parallel.symm (peer loads, or multimem through NVSwitch)
+         fused with the 1/world scale; falls back to nccl when symmetric memory is unavailable
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import dist_utils
+
+
+class DataParallel:
+    def __init__(self, flat, mode: str = "fused", group=None):
+        self.flat = flat
+        self.group = group
+        self.world = dist_utils.world_size()
+        self.mode = mode if self.world > 1 else "none"
+        self._symm = None
+        if self.mode == "fused":
+            try:
+                from . import symm
+                self._symm = symm.SymmetricAllReduce(flat.grad, group=group)
+            except Exception as e:  # noqa: BLE001 - recorded, baseline path is used instead
+                self.fallback_reason = repr(e)
+                self.mode = "nccl"
+
+    def broadcast_parameters(self) -> None:
+        """Make every rank start from rank 0's weights."""
+        if self.world > 1:
+            dist.broadcast(self.flat.master, src=0, group=self.group)
+            self.flat.refresh_shadow()
+
+    def reduce_gradients(self) -> float:
+        """Sum gradients over ranks in place. Returns the scale the optimizer must apply (1/world)."""
+        if self.world == 1:
+            return 1.0
+        if self.mode == "fused" and self._symm is not None:
+            self._symm.all_reduce_(scale=1.0 / self.world)
+            return 1.0
+        dist.all_reduce(self.flat.grad, op=dist.ReduceOp.SUM, group=self.group)
+        return 1.0 / self.world
