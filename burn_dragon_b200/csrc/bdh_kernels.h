@@ -46,6 +46,7 @@ typedef struct {
   const float* slopes;
   int* status;   // device word that receives a STATUS_* code if an in-kernel wait gives up
   int max_ctas;  // 0: one CTA per SM
+  int no_tma_epilogue;  // 1: force the per-thread global-memory epilogue
 } BdhGemmDesc;
 
 int bdh_gemm_bf16(const BdhMat* A, int a_mn_major, const BdhMat* B, int b_mn_major,

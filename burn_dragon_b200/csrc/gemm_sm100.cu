@@ -4,6 +4,7 @@
 #include "gemm_sm100.cuh"
 
 #include <mutex>
+#include <string.h>
 
 namespace bdh {
 
@@ -41,6 +42,20 @@ static int make_tmap(CUtensorMap* out, const BdhMat& m, int box_rows) {
   return r == CUDA_SUCCESS ? BDH_OK : BDH_ERR_TMAP;
 }
 
+// bf16 output / auxiliary-input tensor -> tensor map with 32 x 32 boxes and the 64-byte swizzle.
+static int make_epi_tmap(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return BDH_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {32u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? BDH_OK : BDH_ERR_TMAP;
+}
+
 static int num_sms() {
   static int n = 0;
   if (!n) {
@@ -51,12 +66,19 @@ static int num_sms() {
   return n;
 }
 
-template <int BN, int A_MN, int B_MN, int EPI>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int max_ctas,
-                  cudaStream_t stream) {
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
-  using L = GemmSmem<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, STAGES>;
+template <int BN, int A_MN, int B_MN, int EPI, bool TMA_EPI>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& em, const GemmArgs& g,
+                  int max_ctas, cudaStream_t stream) {
+  // Staged epilogues run 8 epilogue warps; the mainloop ring gets what shared memory is left.
+  constexpr int EW = TMA_EPI ? 8 : 4;
+  constexpr int STAGE_BYTES = (GEMM_BM + BN) * GEMM_BK * 2;
+  constexpr int EPI_BYTES = TMA_EPI ? EW * 2 * (epi_num_in(EPI) + epi_num_out(EPI)) * EPI_BOX_BYTES : 0;
+  constexpr int BUDGET = 227 * 1024 - 2048 - EPI_BYTES;
+  constexpr int FIT = BUDGET / STAGE_BYTES;
+  constexpr int STAGES = FIT > 6 ? 6 : FIT;
+  static_assert(STAGES >= 2, "not enough shared memory for the mainloop ring");
+  using L = GemmSmem<BN, STAGES, TMA_EPI, EW, EPI>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, STAGES, TMA_EPI, EW>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
@@ -69,7 +91,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
   long long tiles = tiles_m * tiles_n * g.nz0 * g.nz1;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
   if (grid < 1) grid = 1;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, g);
+  kern<<<grid, gemm_threads(EW), L::TOTAL, stream>>>(ta, tb, em, g);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 
@@ -108,9 +130,46 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   const int max_ctas = d->max_ctas > 0 ? d->max_ctas : num_sms();
   const int key = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
 
-#define BDH_CASE(BN_, AMN, BMN, EPI_)                                                 \
-  if (bn == BN_ && key == ((AMN) | ((BMN) << 1)) && d->epi == EPI_)                   \
-    return launch<BN_, AMN, BMN, EPI_>(ta, tb, g, max_ctas, stream);
+  // Decide whether the outputs / auxiliary inputs can move through the staged TMA epilogue.
+  EpiMaps em;
+  memset(&em, 0, sizeof(em));
+  bool tma_epi = !d->no_tma_epilogue && epi_tma_capable(d->epi, d->flags);
+  const int io = epi_io_mask(d->epi, d->flags);
+  const bool batched = d->nz0 * d->nz1 > 1;
+  if (batched && ((d->M % GEMM_BM) || (d->N % bn))) tma_epi = false;
+  for (int i = 0; i < 4; ++i) if (d->c_off[i] % 8) tma_epi = false;
+  if (d->o1_off[0] % 8 || d->o1_off[1] % 8) tma_epi = false;
+  if (tma_epi) {
+    const long long rows = d->c_off[0] * (d->nz0 - 1) + d->c_off[1] * (d->nz1 - 1) + d->M;
+    const long long cols = d->c_off[2] * (d->nz0 - 1) + d->c_off[3] * (d->nz1 - 1) + d->N;
+    const long long cols1 = (d->epi == EPI_RELU)
+                                ? d->o1_off[0] * (d->nz0 - 1) + d->o1_off[1] * (d->nz1 - 1) + d->N
+                                : cols;
+    // the rotary table (in0 of EPI_RELU, in1 of EPI_DQ_BWD) is a [T, n_per_head] tensor of its own
+    const bool tab0 = d->epi == EPI_RELU, tab1 = d->epi == EPI_DQ_BWD;
+    if ((io & (tab0 ? IO_IN0 : 0)) || (io & (tab1 ? IO_IN1 : 0)))
+      if ((e.T % 32) || (e.n_per_head % 32)) tma_epi = false;
+    struct { int bit; const void* p; long long ld; long long rows; long long cols; CUtensorMap* m; } t[4] = {
+        {IO_OUT0, d->out0, d->ld_out0, rows, cols, &em.out0},
+        {IO_OUT1, d->out1, d->ld_out1, rows, cols1, &em.out1},
+        {IO_IN0, d->in0, d->ld_in0, tab0 ? e.T : rows, tab0 ? e.n_per_head : cols, &em.in0},
+        {IO_IN1, d->in1, d->ld_in1, tab1 ? e.T : rows, tab1 ? e.n_per_head : cols, &em.in1}};
+    for (auto& x : t) {
+      if (!tma_epi) break;
+      if (!(io & x.bit)) continue;
+      if (!x.p || (reinterpret_cast<uintptr_t>(x.p) & 15) || (x.ld % 8) ||
+          make_epi_tmap(x.m, x.p, x.rows, x.cols, x.ld) != BDH_OK) {
+        tma_epi = false;
+        break;
+      }
+    }
+  }
+
+#define BDH_CASE(BN_, AMN, BMN, EPI_)                                                   \
+  if (bn == BN_ && key == ((AMN) | ((BMN) << 1)) && d->epi == EPI_) {                   \
+    if (tma_epi) return launch<BN_, AMN, BMN, EPI_, true>(ta, tb, em, g, max_ctas, stream); \
+    return launch<BN_, AMN, BMN, EPI_, false>(ta, tb, em, g, max_ctas, stream);           \
+  }
 
   BDH_CASE(256, 0, 0, EPI_STORE)
   BDH_CASE(256, 0, 0, EPI_RELU)

@@ -20,16 +20,17 @@ namespace bdh {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_EPI_WARPS = 4;
-constexpr int GEMM_THREADS = 32 * (2 + GEMM_EPI_WARPS);
+// Epilogue warps: 4 (one per TMEM lane quarter) or 8 (two per quarter, each taking half of the
+// tile's columns) - the second keeps two warps per scheduler busy when the epilogue is heavy.
+constexpr int gemm_threads(int epi_warps) { return 32 * (2 + epi_warps); }
 
 enum EpiKind : int {
   EPI_STORE = 0,       // out0 = alpha*acc (+ beta*out0); bf16 or fp32 by flag
   EPI_RELU = 1,        // x = relu(acc - theta) -> out0 ; optional q = rot(x) -> out1
   EPI_RELU_GATE = 2,   // y = relu(acc - theta) -> out0 (optional) ; xy = y * in0 -> out1
   EPI_CAUSAL = 3,      // out0 = mask(t, s) * acc * exp(-slope*|t-s|)
-  EPI_GATE_BWD = 4,    // g = acc ; out0 = g*in0*(in1>0) ; out1 = g*in1
-  EPI_DQ_BWD = 5,      // dq = rot^-1(acc) ; out0 = (dq + in1) * (in0 > 0)
+  EPI_GATE_BWD = 4,    // g = acc ; in0 = x, in1 = x*y ; out0 = g*x*[y>0] ; out1 = g*y*[x>0] (-0.0 marks closed)
+  EPI_DQ_BWD = 5,      // dq = rot^-1(acc) ; in0 = marked gate gradient ; out0 = open ? dq + in0 : 0
 };
 
 enum EpiFlags : int {
@@ -39,7 +40,7 @@ enum EpiFlags : int {
   EPI_F_POPE = 8,          // EPI_RELU: write softplus(x)*[cos, sin] to out1 (real | imag halves)
   EPI_F_UPPER = 16,        // EPI_CAUSAL: write only s > t (else: write everything, zero where s >= t)
   EPI_F_NO_OUT0 = 32,      // EPI_RELU_GATE: skip storing y
-  EPI_F_HAS_IN1 = 64,      // EPI_DQ_BWD: add in1
+  EPI_F_TABLE = 128,       // rotary (cos, sin) come from an fp16-pair table [T, n_per_head] instead of sincos
 };
 
 struct OperandOffsets {
@@ -149,16 +150,208 @@ __device__ __forceinline__ void rot_sincos(float pos, float freq, float& s, floa
   __sincosf(ph, &s, &c);
 }
 
+// RoPE frequencies arrive as a pair table (one entry per (2i, 2i+1) column pair, n_per_head/2
+// entries); a 32-column chunk starting at column `col` uses 16 consecutive entries.
+__device__ __forceinline__ void load_pair_freqs(const float* freqs, int col, float (&fr)[16]) {
+  const float4* p = reinterpret_cast<const float4*>(freqs + (col >> 1));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 f = __ldg(p + i);
+    fr[4 * i] = f.x; fr[4 * i + 1] = f.y; fr[4 * i + 2] = f.z; fr[4 * i + 3] = f.w;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
-// Epilogue: v holds columns [n, n+32) of row m (both relative to the batch's C block).
+// Epilogue math on registers. `acc` holds columns [n, n+32) of row m (both relative to the batch's
+// C block); r0 / r1 are the matching 32 auxiliary values as packed bf16 pairs (or fp16 cos/sin
+// pairs for the rotary table); results go to o0 / o1. Which of the four are live for an
+// (EPI, flags) pair is given by epi_io_mask().
+//
+// Gradient encoding shared by EPI_GATE_BWD and EPI_DQ_BWD: the gate gradient w.r.t. x is stored
+// with the bf16 bit pattern of -0.0 wherever the ReLU that produced x is closed (x <= 0). The
+// consumer masks by that marker instead of re-reading x.
 // ------------------------------------------------------------------------------------------------
+enum : int { IO_IN0 = 1, IO_IN1 = 2, IO_OUT0 = 4, IO_OUT1 = 8 };
+constexpr uint32_t BF16_NEG_ZERO = 0x8000u;
+
+__host__ __device__ inline int epi_io_mask(int epi, int flags) {
+  switch (epi) {
+    case EPI_STORE: return IO_OUT0;
+    case EPI_RELU:
+      return IO_OUT0 | ((flags & (EPI_F_ROPE | EPI_F_POPE)) ? IO_OUT1 : 0) |
+             (((flags & EPI_F_ROPE) && (flags & EPI_F_TABLE)) ? IO_IN0 : 0);
+    case EPI_RELU_GATE: return IO_IN0 | IO_OUT1 | ((flags & EPI_F_NO_OUT0) ? 0 : IO_OUT0);
+    case EPI_CAUSAL: return IO_OUT0;
+    case EPI_GATE_BWD: return IO_IN0 | IO_IN1 | IO_OUT0 | IO_OUT1;
+    case EPI_DQ_BWD:
+      return IO_IN0 | IO_OUT0 | (((flags & EPI_F_ROPE) && (flags & EPI_F_TABLE)) ? IO_IN1 : 0);
+  }
+  return 0;
+}
+
+// Epilogues whose outputs are plain bf16 tiles at C's coordinates can be staged through shared
+// memory and moved with TMA; the others (fp32 / accumulate / PoPE layout / partial upper writes)
+// use per-thread global accesses.
+__host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
+  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM));
+  if (epi == EPI_RELU) return !(flags & EPI_F_POPE);
+  if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
+  return true;
+}
+
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t u) {
+  __half2 h = *reinterpret_cast<__half2*>(&u);
+  return __half22float2(h);
+}
+
+// (cos, sin) of the rotary phase for the 16 column pairs of a chunk: from the table (fp16 pairs in
+// `tab`) or computed from the pair-frequency list.
+template <bool TABLE>
+__device__ __forceinline__ void rot_pair(const EpiParams& e, const uint32_t (&tab)[16], const float (&fr)[16],
+                                         float pos, int i, float& s, float& co) {
+  if (TABLE) {
+    float2 cs = unpack_f16x2(tab[i]);
+    co = cs.x;
+    s = cs.y;
+  } else {
+    rot_sincos(pos, fr[i], s, co);
+  }
+}
+
 template <int EPI>
-__device__ __forceinline__ void epilogue_apply(const EpiParams& e, int z0, int z1, int m, int n,
-                                               float (&v)[32], int M, int N) {
+__device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, int n, float (&acc)[32],
+                                            const uint32_t (&r0)[16], const uint32_t (&r1)[16],
+                                            float (&o0)[32], float (&o1)[32]) {
+  if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o0[i] = acc[i] * e.alpha;
+  } else if constexpr (EPI == EPI_RELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o0[i] = fmaxf(acc[i] - e.theta, 0.f);
+    if (e.flags & EPI_F_ROPE) {
+      if (e.flags & EPI_F_TABLE) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float2 cs = unpack_f16x2(r0[i]);
+          float a = o0[2 * i], b = o0[2 * i + 1];
+          o1[2 * i] = a * cs.x - b * cs.y;
+          o1[2 * i + 1] = b * cs.x + a * cs.y;
+        }
+      } else {
+        const float pos = static_cast<float>(e.pos0 + (m % e.T));
+        float fr[16];
+        load_pair_freqs(e.freqs, n % e.n_per_head, fr);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a = o0[2 * i], b = o0[2 * i + 1];
+          if (a != 0.f || b != 0.f) {
+            float s, co;
+            rot_sincos(pos, fr[i], s, co);
+            o1[2 * i] = a * co - b * s;
+            o1[2 * i + 1] = b * co + a * s;
+          } else {
+            o1[2 * i] = 0.f;
+            o1[2 * i + 1] = 0.f;
+          }
+        }
+      }
+    }
+  } else if constexpr (EPI == EPI_RELU_GATE) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 x = unpack_bf16x2(r0[i]);
+      o0[2 * i] = fmaxf(acc[2 * i] - e.theta, 0.f);
+      o0[2 * i + 1] = fmaxf(acc[2 * i + 1] - e.theta, 0.f);
+      o1[2 * i] = o0[2 * i] * x.x;
+      o1[2 * i + 1] = o0[2 * i + 1] * x.y;
+    }
+  } else if constexpr (EPI == EPI_CAUSAL) {
+    const float slope = e.slopes ? __ldg(e.slopes + z0) : 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      int s = n + i;
+      float w = (s < m) ? __expf(-slope * static_cast<float>(m - s)) : 0.f;
+      o0[i] = acc[i] * w * e.alpha;
+    }
+  } else if constexpr (EPI == EPI_GATE_BWD) {
+    // r0 = x, r1 = x*y (y itself is never stored: y = xy / x where the x gate is open).
+    //   o0 = d(pre-activation of y) = g * x where y > 0   (y > 0  <=>  xy > 0 because x >= 0)
+    //   o1 = gate gradient w.r.t. x = g * y where x > 0, else the -0.0 marker
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 x = unpack_bf16x2(r0[i]);
+      float2 xy = unpack_bf16x2(r1[i]);
+      o0[2 * i] = (xy.x > 0.f) ? acc[2 * i] * x.x : 0.f;
+      o0[2 * i + 1] = (xy.y > 0.f) ? acc[2 * i + 1] * x.y : 0.f;
+      float g0 = acc[2 * i] * __fdividef(xy.x, x.x), g1 = acc[2 * i + 1] * __fdividef(xy.y, x.y);
+      // +0.0 keeps "open gate, zero gradient" distinct from the marker
+      o1[2 * i] = (x.x > 0.f) ? (g0 == 0.f ? 0.f : g0) : -0.f;
+      o1[2 * i + 1] = (x.y > 0.f) ? (g1 == 0.f ? 0.f : g1) : -0.f;
+    }
+  } else if constexpr (EPI == EPI_DQ_BWD) {
+    // r0 = gate gradient with -0.0 markers; r1 = rotary table (optional)
+    if (e.flags & EPI_F_ROPE) {
+      // q = R(pos) x  =>  dx = R(pos)^T dq
+      const bool table = e.flags & EPI_F_TABLE;
+      const float pos = static_cast<float>(e.pos0 + (m % e.T));
+      float fr[16];
+      if (!table) load_pair_freqs(e.freqs, n % e.n_per_head, fr);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const bool closed = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) && ((r0[i] >> 16) == BF16_NEG_ZERO);
+        if (!closed) {
+          float s, co;
+          if (table) {
+            float2 cs = unpack_f16x2(r1[i]);
+            co = cs.x;
+            s = cs.y;
+          } else {
+            rot_sincos(pos, fr[i], s, co);
+          }
+          float a = acc[2 * i], b = acc[2 * i + 1];
+          acc[2 * i] = a * co + b * s;
+          acc[2 * i + 1] = b * co - a * s;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float2 g = unpack_bf16x2(r0[i]);
+      o0[2 * i] = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) ? 0.f : acc[2 * i] * e.alpha + g.x;
+      o0[2 * i + 1] = ((r0[i] >> 16) == BF16_NEG_ZERO) ? 0.f : acc[2 * i + 1] * e.alpha + g.y;
+    }
+  }
+}
+
+__device__ __forceinline__ void load_raw_32(const __nv_bfloat16* base, long long ld, long long r, long long c,
+                                            uint32_t (&u)[16], int valid) {
+  const __nv_bfloat16* p = base + r * ld + c;
+  if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+    const uint4* p4 = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 w = __ldg(p4 + i);
+      u[4 * i] = w.x; u[4 * i + 1] = w.y; u[4 * i + 2] = w.z; u[4 * i + 3] = w.w;
+    }
+  } else {
+    const unsigned short* ps = reinterpret_cast<const unsigned short*>(p);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      uint32_t lo = (2 * i < valid) ? ps[2 * i] : 0u, hi = (2 * i + 1 < valid) ? ps[2 * i + 1] : 0u;
+      u[i] = lo | (hi << 16);
+    }
+  }
+}
+
+// Per-thread global-memory epilogue (any shape, any alignment, every flag).
+template <int EPI>
+__device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int z1, int m, int n,
+                                                float (&v)[32], int M, int N) {
   if (m >= M || n >= N) return;
   const int valid = min(32, N - n);
   const long long r = e.c_m0 * z0 + e.c_m1 * z1 + m;
   const long long c = e.c_n0 * z0 + e.c_n1 * z1 + n;
+  typedef __nv_bfloat16 bf;
 
   if constexpr (EPI == EPI_STORE) {
 #pragma unroll
@@ -168,130 +361,95 @@ __device__ __forceinline__ void epilogue_apply(const EpiParams& e, int z0, int z
     } else {
       if (e.flags & EPI_F_ACCUM) {
         float o[32];
-        load_bf16_32(static_cast<const __nv_bfloat16*>(e.out0), e.ld_out0, r, c, o, valid);
+        load_bf16_32(static_cast<const bf*>(e.out0), e.ld_out0, r, c, o, valid);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] += o[i];
       }
-      store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
+      store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, v, valid);
     }
-  } else if constexpr (EPI == EPI_RELU) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i] - e.theta, 0.f);
-    store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
-    if (e.flags & (EPI_F_ROPE | EPI_F_POPE)) {
+    return;
+  }
+  if constexpr (EPI == EPI_RELU) {
+    if (e.flags & EPI_F_POPE) {
       const float pos = static_cast<float>(e.pos0 + (m % e.T));
       const int fcol = n % e.n_per_head;
       const long long c1 = e.o1_n0 * z0 + e.o1_n1 * z1 + n;
-      if (e.flags & EPI_F_ROPE) {
-        float q[32];
+      float re[32], im[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = v[i], b = v[i + 1];
-          if (a != 0.f || b != 0.f) {
-            float s, co;
-            rot_sincos(pos, __ldg(e.freqs + fcol + i), s, co);
-            q[i] = a * co - b * s;
-            q[i + 1] = b * co + a * s;
-          } else {
-            q[i] = 0.f;
-            q[i + 1] = 0.f;
-          }
-        }
-        store_bf16_32(static_cast<__nv_bfloat16*>(e.out1), e.ld_out1, r, c1, q, valid);
-      } else {
-        float re[32], im[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s, co;
-          rot_sincos(pos, __ldg(e.freqs + fcol + i), s, co);
-          // softplus of a non-negative value: x + log1p(exp(-x))
-          float mag = v[i] + log1pf(__expf(-v[i]));
-          re[i] = mag * co;
-          im[i] = mag * s;
-        }
-        store_bf16_32(static_cast<__nv_bfloat16*>(e.out1), e.ld_out1, r, c1, re, valid);
-        store_bf16_32(static_cast<__nv_bfloat16*>(e.out1), e.ld_out1, r, c1 + e.o1_imag, im, valid);
+      for (int i = 0; i < 32; ++i) {
+        v[i] = fmaxf(v[i] - e.theta, 0.f);
+        float s, co;
+        rot_sincos(pos, __ldg(e.freqs + fcol + i), s, co);
+        float mag = v[i] + log1pf(__expf(-v[i]));  // softplus of a non-negative value
+        re[i] = mag * co;
+        im[i] = mag * s;
       }
+      store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, v, valid);
+      store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1, re, valid);
+      store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1 + e.o1_imag, im, valid);
+      return;
     }
-  } else if constexpr (EPI == EPI_RELU_GATE) {
-    float x[32];
-    load_bf16_32(static_cast<const __nv_bfloat16*>(e.in0), e.ld_in0, r, c, x, valid);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i] - e.theta, 0.f);
-    if (!(e.flags & EPI_F_NO_OUT0))
-      store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= x[i];
-    store_bf16_32(static_cast<__nv_bfloat16*>(e.out1), e.ld_out1, r, c, v, valid);
-  } else if constexpr (EPI == EPI_CAUSAL) {
-    const float slope = e.slopes ? __ldg(e.slopes + z0) : 0.f;
-    const bool upper = e.flags & EPI_F_UPPER;
-    if (!upper) {
+  }
+  if constexpr (EPI == EPI_CAUSAL) {
+    if (e.flags & EPI_F_UPPER) {
+      if (n + 31 <= m) return;  // nothing above the diagonal in this chunk
+      const float slope = e.slopes ? __ldg(e.slopes + z0) : 0.f;
+      bf* p = static_cast<bf*>(e.out0) + r * e.ld_out0 + c;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         int s = n + i;
-        float w = (s < m) ? __expf(-slope * static_cast<float>(m - s)) : 0.f;
-        v[i] *= w * e.alpha;
+        if (i < valid && s > m)
+          p[i] = __float2bfloat16_rn(v[i] * e.alpha * __expf(-slope * static_cast<float>(s - m)));
       }
-      store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
-    } else {
-      if (n + 31 <= m) return;  // nothing above the diagonal in this chunk
-      __nv_bfloat16* p = static_cast<__nv_bfloat16*>(e.out0) + r * e.ld_out0 + c;
-      if (n > m && valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          v[i] *= e.alpha * __expf(-slope * static_cast<float>(n + i - m));
-        store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          int s = n + i;
-          if (i < valid && s > m)
-            p[i] = __float2bfloat16_rn(v[i] * e.alpha * __expf(-slope * static_cast<float>(s - m)));
-        }
-      }
+      return;
     }
-  } else if constexpr (EPI == EPI_GATE_BWD) {
-    float x[32], y[32];
-    load_bf16_32(static_cast<const __nv_bfloat16*>(e.in0), e.ld_in0, r, c, x, valid);
-    load_bf16_32(static_cast<const __nv_bfloat16*>(e.in1), e.ld_in1, r, c, y, valid);
-    float dy[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      dy[i] = (y[i] > 0.f) ? v[i] * x[i] : 0.f;
-      v[i] *= y[i];
-    }
-    store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, dy, valid);
-    store_bf16_32(static_cast<__nv_bfloat16*>(e.out1), e.ld_out1, r, c, v, valid);
-  } else if constexpr (EPI == EPI_DQ_BWD) {
-    float x[32];
-    load_bf16_32(static_cast<const __nv_bfloat16*>(e.in0), e.ld_in0, r, c, x, valid);
-    if (e.flags & EPI_F_ROPE) {
-      // q = R(pos) x  =>  dx = R(pos)^T dq
-      const float pos = static_cast<float>(e.pos0 + (m % e.T));
-      const int fcol = n % e.n_per_head;
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        if (x[i] > 0.f || x[i + 1] > 0.f) {
-          float s, co;
-          rot_sincos(pos, __ldg(e.freqs + fcol + i), s, co);
-          float a = v[i], b = v[i + 1];
-          v[i] = a * co + b * s;
-          v[i + 1] = b * co - a * s;
-        }
-      }
-    }
-    if (e.flags & EPI_F_HAS_IN1) {
-      float g[32];
-      load_bf16_32(static_cast<const __nv_bfloat16*>(e.in1), e.ld_in1, r, c, g, valid);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] += g[i];
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = (x[i] > 0.f) ? v[i] * e.alpha : 0.f;
-    store_bf16_32(static_cast<__nv_bfloat16*>(e.out0), e.ld_out0, r, c, v, valid);
+  }
+  const int io = epi_io_mask(EPI, e.flags);
+  uint32_t r0[16], r1[16];
+  float o0[32], o1[32];
+  const bool tab0 = (EPI == EPI_RELU), tab1 = (EPI == EPI_DQ_BWD);   // which input is the rotary table
+  const long long tr = m % e.T, tcn = n % e.n_per_head;
+  if (io & IO_IN0)
+    load_raw_32(static_cast<const bf*>(e.in0), e.ld_in0, tab0 ? tr : r, tab0 ? tcn : c, r0, valid);
+  if (io & IO_IN1)
+    load_raw_32(static_cast<const bf*>(e.in1), e.ld_in1, tab1 ? tr : r, tab1 ? tcn : c, r1, valid);
+  epi_compute<EPI>(e, z0, m, n, v, r0, r1, o0, o1);
+  if (io & IO_OUT0) store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, o0, valid);
+  if (io & IO_OUT1) {
+    const long long c1 = (EPI == EPI_RELU) ? e.o1_n0 * z0 + e.o1_n1 * z1 + n : c;
+    store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1, o1, valid);
   }
 }
+
+// ---- shared-memory staging for the TMA epilogue ------------------------------------------------
+// One [32 rows][32 bf16] box per (tensor, buffer): 64-byte rows with the 64-byte TMA swizzle
+// (16-byte chunk index XOR bits 7-8 of the address). Thread `row` reads / writes its own row.
+constexpr int EPI_BOX_BYTES = 32 * 64;
+__device__ __forceinline__ uint32_t epi_box_off(int row, int chunk) {
+  return static_cast<uint32_t>(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
+}
+__device__ __forceinline__ void box_read_raw(const uint8_t* box, int row, uint32_t (&u)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 w = *reinterpret_cast<const uint4*>(box + epi_box_off(row, j));
+    u[4 * j] = w.x; u[4 * j + 1] = w.y; u[4 * j + 2] = w.z; u[4 * j + 3] = w.w;
+  }
+}
+__device__ __forceinline__ void box_write_row(uint8_t* box, int row, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 u;
+    u.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+    u.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+    u.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+    u.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(box + epi_box_off(row, j)) = u;
+  }
+}
+
+struct EpiMaps {
+  CUtensorMap out0, out1, in0, in1;   // boxes of 32 columns x 32 rows, 64-byte swizzle
+};
 
 // ------------------------------------------------------------------------------------------------
 // Tile enumeration shared by the three roles (they must agree on the sequence).
@@ -347,20 +505,35 @@ struct TileWalker {
   }
 };
 
-template <int BN, int STAGES>
+// Boxes of staging per epilogue warp: double-buffered inputs and outputs.
+__host__ __device__ constexpr int epi_num_in(int epi) {
+  return (epi == EPI_RELU_GATE || epi == EPI_RELU) ? 1 : (epi == EPI_GATE_BWD || epi == EPI_DQ_BWD) ? 2 : 0;
+}
+__host__ __device__ constexpr int epi_num_out(int epi) {
+  return (epi == EPI_RELU || epi == EPI_RELU_GATE || epi == EPI_GATE_BWD) ? 2 : 1;
+}
+
+template <int BN, int STAGES, bool TMA_EPI, int EW, int EPI>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 5) * 8 + 16 + 1024;  // +1024: manual alignment slack
+  static constexpr int NIN = epi_num_in(EPI);
+  static constexpr int NOUT = epi_num_out(EPI);
+  static constexpr int EPI_WARP_BYTES = TMA_EPI ? 2 * (NIN + NOUT) * EPI_BOX_BYTES : 0;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EW * EPI_WARP_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 5 + 2 * EW;
+  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024: manual alignment slack
 };
 
-template <int BN, int A_MN, int B_MN, int EPI, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int BN, int A_MN, int B_MN, int EPI, int STAGES, bool TMA_EPI, int EW>
+__global__ void __launch_bounds__(gemm_threads(EW), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs g) {
-  using L = GemmSmem<BN, STAGES>;
+                 const __grid_constant__ EpiMaps em, const GemmArgs g) {
+  using L = GemmSmem<BN, STAGES, TMA_EPI, EW, EPI>;
+  static_assert(EW == 4 || EW == 8, "4 or 8 epilogue warps");
+  constexpr int CHUNKS = (BN / 32) / (EW / 4);   // 32-column chunks per epilogue warp per tile
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
   constexpr uint32_t TMEM_COLS = 2 * BN;
 
@@ -372,7 +545,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint64_t* drain_bar = tempty_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* in_bar = drain_bar + 1;  // [EW][2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 2 * EW);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -385,9 +559,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], GEMM_EPI_WARPS);
+      mbar_init(&tempty_bar[a], EW);
     }
     mbar_init(drain_bar, 1);
+    for (int i = 0; i < 2 * EW; ++i) mbar_init(&in_bar[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -514,28 +689,143 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ---------------- epilogue ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int ew = warp - 2;           // epilogue warp index
+    const int cbase = (ew >> 2) * CHUNKS;   // first 32-column chunk of this warp inside a tile
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < walker.total; t += gridDim.x) {
-      const TileCoord tc = walker.decode(t);
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, g.status, STATUS_TIMEOUT_TMEM_FULL))
-        break;
-      tc_fence_after();
-      const int m = tc.m0 + q * 32 + lane;
-      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+    if constexpr (!TMA_EPI) {
+      for (int t = blockIdx.x; t < walker.total; t += gridDim.x) {
+        const TileCoord tc = walker.decode(t);
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, g.status, STATUS_TIMEOUT_TMEM_FULL))
+          break;
+        tc_fence_after();
+        const int m = tc.m0 + q * 32 + lane;
+        const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld_32x32(tbase + c * 32, v);
-        tmem_ld_wait();
-        epilogue_apply<EPI>(g.epi, tc.z0, tc.z1, m, tc.n0 + c * 32, v, g.M, g.N);
+        for (int c = cbase; c < cbase + CHUNKS; ++c) {
+          float v[32];
+          tmem_ld_32x32(tbase + c * 32, v);
+          tmem_ld_wait();
+          epilogue_direct<EPI>(g.epi, tc.z0, tc.z1, m, tc.n0 + c * 32, v, g.M, g.N);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+    } else {
+      // Staged epilogue: auxiliary inputs arrive by TMA one 32-column chunk ahead, results leave by
+      // TMA store; each warp owns its 32 rows end to end, so no cross-warp synchronisation is needed.
+      const EpiParams& e = g.epi;
+      const int io = epi_io_mask(EPI, e.flags);
+      uint8_t* wbase = smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES;
+      uint8_t* in_box = wbase;                                   // [tensor][buf 0..1]
+      uint8_t* out_box = wbase + 2 * L::NIN * EPI_BOX_BYTES;     // [tensor][buf 0..1]
+      uint64_t* ibar = in_bar + 2 * ew;
+      const uint32_t in_bytes = ((io & IO_IN0) ? EPI_BOX_BYTES : 0) + ((io & IO_IN1) ? EPI_BOX_BYTES : 0);
+      const bool has_in = in_bytes != 0;
+      uint32_t gchunk = 0;   // running chunk counter of this warp: buffer = gchunk & 1, parity = (gchunk >> 1) & 1
+      uint32_t issued = 0;   // chunks whose input loads were issued
+
+      auto issue_in = [&](const TileCoord& tc, int c) {
+        // called by lane 0 only
+        const int buf = issued & 1;
+        const int row = static_cast<int>(e.c_m0 * tc.z0 + e.c_m1 * tc.z1 + tc.m0 + q * 32);
+        const int col = static_cast<int>(e.c_n0 * tc.z0 + e.c_n1 * tc.z1 + tc.n0 + (cbase + c) * 32);
+        // the rotary table is indexed by (position, column within the head), not by C coordinates
+        const int trow = (tc.m0 + q * 32) % e.T;
+        const int tcol = (tc.n0 + (cbase + c) * 32) % e.n_per_head;
+        mbar_arrive_expect_tx(&ibar[buf], in_bytes);
+        if (io & IO_IN0)
+          tma_load_2d(in_box + (0 * 2 + buf) * EPI_BOX_BYTES, &em.in0, &ibar[buf],
+                      (EPI == EPI_RELU) ? tcol : col, (EPI == EPI_RELU) ? trow : row);
+        if (io & IO_IN1)
+          tma_load_2d(in_box + (1 * 2 + buf) * EPI_BOX_BYTES, &em.in1, &ibar[buf],
+                      (EPI == EPI_DQ_BWD) ? tcol : col, (EPI == EPI_DQ_BWD) ? trow : row);
+      };
+
+      int t = blockIdx.x;
+      TileCoord tc{0, 0, 0, 0};
+      if (t < walker.total) {
+        tc = walker.decode(t);
+        if (has_in && lane == 0) issue_in(tc, 0);
+        if (has_in) ++issued;
+      }
+      bool ok = true;
+      while (t < walker.total && ok) {
+        const int t_next = t + gridDim.x;
+        TileCoord tc_next{0, 0, 0, 0};
+        if (t_next < walker.total) tc_next = walker.decode(t_next);
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, g.status, STATUS_TIMEOUT_TMEM_FULL))
+          break;
+        tc_fence_after();
+        const int m = tc.m0 + q * 32 + lane;
+        const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+        const int row0 = static_cast<int>(e.c_m0 * tc.z0 + e.c_m1 * tc.z1 + tc.m0 + q * 32);
+        const int col0 = static_cast<int>(e.c_n0 * tc.z0 + e.c_n1 * tc.z1 + tc.n0) + cbase * 32;
+        const int col1 = (EPI == EPI_RELU) ? static_cast<int>(e.o1_n0 * tc.z0 + e.o1_n1 * tc.z1 + tc.n0) + cbase * 32 : col0;
+#pragma unroll 1
+        for (int c = 0; c < CHUNKS; ++c, ++gchunk) {
+          const int buf = gchunk & 1;
+          float v[32], o0[32], o1[32];
+          uint32_t a0[16], a1[16];
+          tmem_ld_32x32(tbase + (cbase + c) * 32, v);
+          if (has_in) {
+            if (!mbar_wait(&ibar[buf], (gchunk >> 1) & 1, abort_flag, g.status, STATUS_TIMEOUT_SMEM_FULL)) {
+              ok = false;
+              tmem_ld_wait();
+              break;
+            }
+            if (io & IO_IN0) box_read_raw(in_box + (0 * 2 + buf) * EPI_BOX_BYTES, lane, a0);
+            if (io & IO_IN1) box_read_raw(in_box + (1 * 2 + buf) * EPI_BOX_BYTES, lane, a1);
+            __syncwarp();
+            // prefetch the next chunk (possibly the next tile's first) into the other buffer
+            const bool more = (c + 1 < CHUNKS) || (t_next < walker.total);
+            if (more) {
+              if (lane == 0) {
+                if (c + 1 < CHUNKS) issue_in(tc, c + 1);
+                else issue_in(tc_next, 0);
+              }
+              ++issued;
+            }
+          }
+          tmem_ld_wait();
+          epi_compute<EPI>(e, tc.z0, m, tc.n0 + (cbase + c) * 32, v, a0, a1, o0, o1);
+          // the store issued two chunks ago must have finished reading this output buffer
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          if (io & IO_OUT0) box_write_row(out_box + (0 * 2 + buf) * EPI_BOX_BYTES, lane, o0);
+          if (io & IO_OUT1) box_write_row(out_box + (1 * 2 + buf) * EPI_BOX_BYTES, lane, o1);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (io & IO_OUT0)
+              tma_store_2d(&em.out0, out_box + (0 * 2 + buf) * EPI_BOX_BYTES, col0 + c * 32, row0);
+            if (io & IO_OUT1)
+              tma_store_2d(&em.out1, out_box + (1 * 2 + buf) * EPI_BOX_BYTES, col1 + c * 32, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        if (!ok) break;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        t = t_next;
+        tc = tc_next;
+      }
+      if (lane == 0) {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (*abort_flag && has_in && issued > gchunk) {
+          // an input load may still be in flight: let it land (bounded)
+          const uint32_t pending = issued - 1;
+          for (int it = 0; it < (1 << 16); ++it)
+            if (mbar_try_wait(&ibar[pending & 1], (pending >> 1) & 1)) break;
+        }
+      }
     }
   }
 

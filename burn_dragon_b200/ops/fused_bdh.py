@@ -64,7 +64,14 @@ def _weights(model) -> Dict[str, torch.Tensor]:
 
 
 class _Dims:
+    def table(self, pos0: int) -> torch.Tensor:
+        """RoPE (cos, sin) table for positions [pos0, pos0 + T), cached per start position."""
+        if self._table is None or self._table[0] != pos0:
+            self._table = (pos0, G.rope_table(pos0, self.T, self.freqs))
+        return self._table[1]
+
     def __init__(self, model, B, T):
+        self._table = None
         c = model.config
         self.B, self.T, self.M = B, T, B * T
         self.D, self.H, self.N = c.n_embd, c.n_head, c.latent_per_head
@@ -74,7 +81,14 @@ class _Dims:
         self.L = c.n_layer
         self.rot = c.rotary_embedding
         self.theta = float(c.relu_threshold)
-        self.freqs = model.freqs.float().contiguous() if self.rot != "alibi" else None
+        # the RoPE epilogues take one frequency per (2i, 2i+1) column pair, PoPE one per column
+        if self.rot == "rope":
+            self.freqs = model.freqs.float()[0::2].contiguous()
+            self.freqs_full = model.freqs.float().contiguous()
+        elif self.rot == "pope":
+            self.freqs = self.freqs_full = model.freqs.float().contiguous()
+        else:
+            self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
 
 
@@ -91,8 +105,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     x = _bf16(M, d.HN, dev)
     if d.rot == "rope":
         q = _bf16(M, d.HN, dev)
-        G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, flags=G.F_ROPE, out0=x, out1=q, theta=d.theta,
-               T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
+        G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, flags=G.F_ROPE | G.F_TABLE, in0=d.table(pos0),
+               out0=x, out1=q, theta=d.theta, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     elif d.rot == "pope":
         q = _bf16(M, d.HNp, dev)
         G.gemm(cur, W["encoder"], M=M, N=N, K=D, nz=(H, 1), b_off=(N, 0, 0, 0), c_off=(0, 0, N, 0),
@@ -129,15 +143,15 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
             rho_out += rho_in
     lna = torch.empty_like(a)
     ops.layernorm_fwd(a, lna)
-    y = _bf16(M, d.HN, dev)
+    # y is not stored: the backward recovers it as xy / x
     xy = _bf16(M, d.HN, dev)
     G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
-           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, in0=x, out0=y, out1=xy, theta=d.theta)
+           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta)
     mlp = _bf16(M, D, dev)
     G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
-    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, y=y, xy=xy, mlp=mlp)
+    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp)
     return out, saved, rho_out
 
 
@@ -146,14 +160,14 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     Weight gradients are accumulated into grads['encoder'|'encoder_v'|'decoder'] (fp32)."""
     dev = dout.device
     M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
-    cur, x, q, S, a, lna, y, xy, mlp = (sv[k] for k in ("cur", "x", "q", "S", "a", "lna", "y", "xy", "mlp"))
+    cur, x, q, S, a, lna, xy, mlp = (sv[k] for k in ("cur", "x", "q", "S", "a", "lna", "xy", "mlp"))
     dcur = torch.empty(M, D, device=dev, dtype=torch.float32)
     dmlp = _bf16(M, D, dev)
     ops.block_out_bwd(cur, mlp, dout, dcur, dmlp)
     # gate
     dy = _bf16(M, d.HN, dev)
     dxg = _bf16(M, d.HN, dev)
-    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=y, out0=dy, out1=dxg)
+    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg)
     G.gemm(xy, dmlp, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["decoder"])
     # y = relu(LN(a) E_v)
     G.gemm(dy, lna, M=N, N=D, K=M, a_mn=True, b_mn=True, nz=(H, 1), a_off=(N, 0, 0, 0), b_off=(0, 0, M, 0),
@@ -181,17 +195,17 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
         G.gemm(Gs, q, M=T, N=Np, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(Np, 0, 0, T),
                c_off=(0, T, Np, 0), out0=dq)
         pos = torch.arange(pos0, pos0 + T, device=dev)
-        ph = R.phases(pos, d.freqs)                                          # [T, N]
+        ph = R.phases(pos, d.freqs_full)                                     # [T, N]
         dq4 = dq.view(B, T, H, 2, N).float()
         xf = x.view(B, T, H, N).float()
         dmag = dq4[:, :, :, 0] * ph.cos().view(1, T, 1, N) + dq4[:, :, :, 1] * ph.sin().view(1, T, 1, N)
         dxv = dmag * torch.sigmoid(xf) + dxg.view(B, T, H, N).float()
         dx.copy_(torch.where(xf > 0, dxv, torch.zeros_like(dxv)).view(M, d.HN))
     else:
-        flags = G.F_HAS_IN1 | (G.F_ROPE if d.rot == "rope" else 0)
+        rope = d.rot == "rope"
         G.gemm(Gs, q, M=T, N=N, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(N, 0, 0, T),
-               c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=flags, in0=x, in1=dxg, out0=dx, T=T, pos0=pos0,
-               n_per_head=N, freqs=d.freqs)
+               c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=(G.F_ROPE | G.F_TABLE) if rope else 0, in0=dxg,
+               in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     del dxg
     G.gemm(dx, cur, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder"])
     G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=dcur)

@@ -20,7 +20,7 @@ import torch
 from . import native
 
 EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
-F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_HAS_IN1 = 1, 2, 4, 8, 16, 32, 64
+F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE = 1, 2, 4, 8, 16, 32, 128
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -48,12 +48,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          in1: Optional[torch.Tensor] = None, c_off: Sequence[int] = (0, 0, 0, 0),
          o1_off: Sequence[int] = (0, 0, 0), alpha: float = 1.0, theta: float = 0.0, T: int = 1, pos0: int = 0,
          n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
-         causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0) -> None:
+         causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
+         tma_epilogue: bool = True) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
-                       slopes, causal_tiles, causal_k, bn, max_ctas)
+                       slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -71,6 +72,15 @@ def rot_phases(pos: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
     return (raw - raw.floor()) * (2.0 * math.pi)
 
 
+def rope_table(pos0: int, T: int, pair_freqs: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of the rotary phase as fp16 pairs, returned bit-cast to a bf16 [T, 2*len(pair_freqs)]
+    tensor (the layout the kernels read with TMA): element 2i = cos, 2i+1 = sin of pair i."""
+    pos = torch.arange(pos0, pos0 + T, device=pair_freqs.device)
+    ph = rot_phases(pos, pair_freqs)
+    tab = torch.stack((ph.cos(), ph.sin()), dim=-1).to(torch.float16).reshape(T, -1)
+    return tab.view(torch.bfloat16)
+
+
 def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) -> torch.Tensor:
     """Interleaved-pair rotation (reference: src/model/attention.rs:305-321). x, phases [..., N]."""
     cos, sin = phases.cos(), phases.sin()
@@ -84,7 +94,7 @@ def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) ->
 def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0, 0, 0, 0), b_off=(0, 0, 0, 0),
                    epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
                    o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
-                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0) -> None:
+                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True) -> None:
     """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
     dev = a.device
     for z1 in range(nz[1]):
@@ -114,7 +124,9 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                 out0[rs, cs] = x.to(out0.dtype)
                 if flags & (F_ROPE | F_POPE):
                     pos = pos0 + (mm % T)
-                    ph = rot_phases(pos, freqs[(nn % n_per_head)])
+                    # RoPE passes one frequency per column pair, PoPE one per column
+                    fr = freqs.repeat_interleave(2) if flags & F_ROPE else freqs
+                    ph = rot_phases(pos, fr[(nn % n_per_head)])
                     c1 = o1_off[0] * z0 + o1_off[1] * z1
                     if flags & F_ROPE:
                         out1[rs, c1:c1 + N] = rope_rotate(x, ph).to(out1.dtype)
@@ -148,19 +160,24 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                         val = torch.where(visited, val, out0[rs, cs].float())
                     out0[rs, cs] = val.to(out0.dtype)
             elif epi == EPI_GATE_BWD:
+                # in0 = x, in1 = x*y. y is recovered as xy/x where x > 0; closed x gates get -0.0
                 x = in0[rs, cs].float()
-                y = in1[rs, cs].float()
-                out0[rs, cs] = torch.where(y > 0, acc * x, torch.zeros_like(acc)).to(out0.dtype)
-                out1[rs, cs] = (acc * y).to(out1.dtype)
+                xy = in1[rs, cs].float()
+                out0[rs, cs] = torch.where(xy > 0, acc * x, torch.zeros_like(acc)).to(out0.dtype)
+                y = torch.where(x > 0, xy / x.clamp(min=1e-30), torch.zeros_like(x))
+                g = acc * y
+                g = torch.where(g == 0, torch.zeros_like(g), g)          # +0.0 for open gates
+                out1[rs, cs] = torch.where(x > 0, g, torch.full_like(g, -0.0)).to(out1.dtype)
             elif epi == EPI_DQ_BWD:
-                x = in0[rs, cs].float()
+                # in0 = gate gradient whose -0.0 entries mark closed ReLU gates
+                g_raw = in0[rs, cs]
+                closed = g_raw.contiguous().view(torch.int16) == -32768
                 v = acc
                 if flags & F_ROPE:
                     pos = pos0 + (mm % T)
-                    ph = rot_phases(pos, freqs[(nn % n_per_head)])
+                    ph = rot_phases(pos, freqs.repeat_interleave(2)[(nn % n_per_head)])
                     v = rope_rotate(v, ph, inverse=True)
-                if flags & F_HAS_IN1:
-                    v = v + in1[rs, cs].float()
-                out0[rs, cs] = torch.where(x > 0, v * alpha, torch.zeros_like(v)).to(out0.dtype)
+                v = v * alpha + g_raw.float()
+                out0[rs, cs] = torch.where(closed, torch.zeros_like(v), v).to(out0.dtype)
             else:
                 raise ValueError(f"unknown epilogue {epi}")

@@ -21,15 +21,19 @@ def _check(got, want, tol=2e-2):
 
 
 def _run_both(kw, outs):
-    """Run kernel and reference on clones of the outputs; return list of (kernel, reference)."""
-    native.clear_status()
-    k_outs = {n: t.clone() for n, t in outs.items()}
+    """Run the kernel (staged-TMA epilogue where eligible, then the per-thread epilogue) and the
+    reference on clones of the outputs; return list of (kernel, reference) pairs for both runs."""
     r_outs = {n: t.clone() for n, t in outs.items()}
-    G.gemm(**kw, **k_outs)
-    torch.cuda.synchronize()
-    assert native.status_code() == 0, "kernel reported a wait timeout"
     G.gemm_reference(**kw, **r_outs)
-    return [(k_outs[n], r_outs[n]) for n in outs]
+    pairs = []
+    for tma in (True, False):
+        native.clear_status()
+        k_outs = {n: t.clone() for n, t in outs.items()}
+        G.gemm(**kw, **k_outs, tma_epilogue=tma)
+        torch.cuda.synchronize()
+        assert native.status_code() == 0, "kernel reported a wait timeout"
+        pairs += [(k_outs[n], r_outs[n]) for n in outs]
+    return pairs
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
@@ -75,16 +79,18 @@ def test_batched_offsets():
     _check(out.copy_(_run_both(kw, dict(out0=out))[0][0]), (a.float() @ w.float().t()))
 
 
-@pytest.mark.parametrize("rot", ["none", "rope", "pope"])
+@pytest.mark.parametrize("rot", ["none", "rope", "rope_table", "pope"])
 def test_relu_rotary(rot):
     M, N, K, T, Nh = 256, 512, 128, 64, 256
     a, w = _rand(M, K, seed=9), _rand(N, K, 0.2, seed=10)
     freqs = (1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh))) / 6.283185307
-    flags = {"none": 0, "rope": G.F_ROPE, "pope": G.F_POPE}[rot]
+    flags = {"none": 0, "rope": G.F_ROPE, "rope_table": G.F_ROPE | G.F_TABLE, "pope": G.F_POPE}[rot]
     outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
     kw = dict(a=a, b=w, M=M, N=N, K=K, epi=G.EPI_RELU, flags=flags, theta=0.1, T=T, pos0=5, n_per_head=Nh,
-              freqs=freqs.float().contiguous())
-    if rot == "rope":
+              freqs=(freqs[0::2] if rot.startswith("rope") else freqs).float().contiguous())
+    if rot == "rope_table":
+        kw["in0"] = G.rope_table(5, T, kw["freqs"])
+    if rot.startswith("rope"):
         outs["out1"] = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
     if rot == "pope":
         # per-head layout [real Nh | imag Nh]; run one head per z0
@@ -137,21 +143,33 @@ def test_gate_bwd():
     M, N, K = 256, 512, 128
     g, w = _rand(M, K, seed=17), _rand(N, K, 0.2, seed=18)
     x, y = _rand(M, N, seed=19).relu(), _rand(M, N, seed=20).relu()
-    kw = dict(a=g, b=w, M=M, N=N, K=K, epi=G.EPI_GATE_BWD, in0=x, in1=y)
+    xy = (x.float() * y.float()).to(torch.bfloat16)
+    kw = dict(a=g, b=w, M=M, N=N, K=K, epi=G.EPI_GATE_BWD, in0=x, in1=xy)
     outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16),
                 out1=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
-    for k, r in _run_both(kw, outs):
+    pairs = _run_both(kw, outs)
+    for k, r in pairs:
         _check(k, r)
+    # closed gates carry the -0.0 marker, open ones never do
+    dxg = pairs[1][0]
+    marker = dxg.view(torch.int16) == -32768
+    assert torch.equal(marker, x <= 0)
+    # and the result equals the definition with the true y
+    want = torch.where(x > 0, (g.float() @ w.float().t()) * y.float(), torch.zeros(M, N, device="cuda"))
+    _check(dxg, want, tol=3e-2)
 
 
-@pytest.mark.parametrize("rope", [False, True])
+@pytest.mark.parametrize("rope", ["none", "sincos", "table"])
 def test_dq_bwd(rope):
     T, N, Nh = 256, 512, 256
     gs = _rand(T, T, 0.2, seed=21)
     q = _rand(T, N, seed=22)
     x, dxg = _rand(T, N, seed=23).relu(), _rand(T, N, seed=24)
-    freqs = (1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh))) / 6.283185307
-    kw = dict(a=gs, b=q, M=T, N=N, K=T, b_mn=True, epi=G.EPI_DQ_BWD, flags=(G.F_ROPE if rope else 0) | G.F_HAS_IN1,
-              in0=x, in1=dxg, T=T, pos0=3, n_per_head=Nh, freqs=freqs.float().contiguous())
+    dxg = torch.where(x > 0, dxg, torch.full_like(dxg, -0.0))
+    freqs = ((1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh)))
+             / 6.283185307)[0::2].float().contiguous()
+    flags = {"none": 0, "sincos": G.F_ROPE, "table": G.F_ROPE | G.F_TABLE}[rope]
+    kw = dict(a=gs, b=q, M=T, N=N, K=T, b_mn=True, epi=G.EPI_DQ_BWD, flags=flags, in0=dxg,
+              in1=G.rope_table(3, T, freqs) if rope == "table" else None, T=T, pos0=3, n_per_head=Nh, freqs=freqs)
     for k, r in _run_both(kw, dict(out0=torch.zeros(T, N, device="cuda", dtype=torch.bfloat16))):
         _check(k, r)
