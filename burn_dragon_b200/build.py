@@ -21,6 +21,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "_obj"
 LIB = PKG / "_C.so"
+HOST_LIB = PKG / "_host.so"
+HOST_SRC = CSRC / "host"
 STAMP = PKG / "_C.hash"
 
 NVCC_FLAGS = [
@@ -39,7 +41,7 @@ def _sources():
 def source_hash() -> str:
     cu, cpp, hdr = _sources()
     h = hashlib.sha256()
-    for p in cu + cpp + hdr:
+    for p in cu + cpp + hdr + sorted(HOST_SRC.glob("*.cpp")):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
@@ -47,7 +49,8 @@ def source_hash() -> str:
 
 
 def is_current() -> bool:
-    return LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == source_hash()
+    return (LIB.exists() and HOST_LIB.exists() and STAMP.exists()
+            and STAMP.read_text().strip() == source_hash())
 
 
 def _nvcc() -> str:
@@ -96,6 +99,9 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart",
             f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{cuda_lib}"]
     _run(link, OBJ / "link.log")
+    # host-only helpers: plain C ABI, no torch / CUDA dependency
+    _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", str(HOST_LIB),
+          *[str(p) for p in sorted(HOST_SRC.glob("*.cpp"))]], OBJ / "host.log")
     STAMP.write_text(source_hash())
     if verbose:
         print(f"built {LIB}")

@@ -277,6 +277,8 @@ def from_dict(value: Dict[str, Any]) -> TrainingConfig:
     tr_ctx = _context(tr.pop("context_strategy", None), "training.context_strategy")
     training = _build(TrainingHyperparameters, tr, "training")
     training.context_strategy = tr_ctx
+    if training.epochs is not None and training.epochs <= 0:
+        training.epochs = None      # `epochs = 0` in an overlay switches back to max_iters
 
     op = value["optimizer"]
     sched = op.pop("lr_schedule", None)

@@ -1,0 +1,122 @@
+// Host-side native helpers (no CUDA): batch window gathering for the data loader and the
+// bincode-2 varint scanner / writer used by the Burn record codec. Plain C ABI, loaded with ctypes.
+//
+// The reference's counterparts are Rust: the window sampler of src/dataset/scheduler.rs:72-110 and
+// the external BinFileRecorder used at src/bin/infer.rs:177-186 and src/bin/quantize.rs:44-63.
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+extern "C" {
+
+// out[b, :] = tokens[starts[b] : starts[b] + width]; rows are split over a few threads.
+int bdh_gather_windows(const int64_t* tokens, int64_t n_tokens, const int64_t* starts, int64_t n_rows,
+                       int64_t width, int64_t* out, int n_threads) {
+  for (int64_t b = 0; b < n_rows; ++b)
+    if (starts[b] < 0 || starts[b] + width > n_tokens) return 1;
+  if (n_threads < 1) n_threads = 1;
+  if (n_threads > 16) n_threads = 16;
+  if (n_rows * width < (1 << 16)) n_threads = 1;
+  auto work = [&](int64_t lo, int64_t hi) {
+    for (int64_t b = lo; b < hi; ++b)
+      std::memcpy(out + b * width, tokens + starts[b], static_cast<size_t>(width) * sizeof(int64_t));
+  };
+  if (n_threads == 1) {
+    work(0, n_rows);
+    return 0;
+  }
+  std::vector<std::thread> th;
+  const int64_t per = (n_rows + n_threads - 1) / n_threads;
+  for (int t = 0; t < n_threads; ++t) {
+    int64_t lo = t * per, hi = lo + per < n_rows ? lo + per : n_rows;
+    if (lo >= hi) break;
+    th.emplace_back(work, lo, hi);
+  }
+  for (auto& x : th) x.join();
+  return 0;
+}
+
+// bincode 2 "varint" unsigned integer: < 251 one byte; 251 + u16; 252 + u32; 253 + u64 (little endian).
+// Returns the number of bytes consumed, 0 on error.
+int bdh_varint_read(const uint8_t* buf, int64_t len, int64_t pos, uint64_t* value) {
+  if (pos >= len) return 0;
+  uint8_t b = buf[pos];
+  if (b < 251) { *value = b; return 1; }
+  int n = b == 251 ? 2 : b == 252 ? 4 : b == 253 ? 8 : 0;
+  if (!n || pos + 1 + n > len) return 0;
+  uint64_t v = 0;
+  for (int i = 0; i < n; ++i) v |= static_cast<uint64_t>(buf[pos + 1 + i]) << (8 * i);
+  *value = v;
+  return 1 + n;
+}
+
+int bdh_varint_write(uint64_t v, uint8_t* out) {
+  if (v < 251) { out[0] = static_cast<uint8_t>(v); return 1; }
+  int n; uint8_t tag;
+  if (v <= 0xFFFFull) { n = 2; tag = 251; }
+  else if (v <= 0xFFFFFFFFull) { n = 4; tag = 252; }
+  else { n = 8; tag = 253; }
+  out[0] = tag;
+  for (int i = 0; i < n; ++i) out[1 + i] = static_cast<uint8_t>(v >> (8 * i));
+  return 1 + n;
+}
+
+// One serialized parameter: String id, Vec<u8> bytes, Vec<usize> shape, enum dtype.
+// Fills {id_off, id_len, data_off, data_len, ndim, d0..d7, dtype}; returns the position after it or -1.
+int64_t bdh_record_scan_param(const uint8_t* buf, int64_t len, int64_t pos, int64_t* out /* [13] */) {
+  uint64_t v;
+  int n = bdh_varint_read(buf, len, pos, &v);
+  if (!n || v > 64) return -1;
+  out[0] = pos + n; out[1] = static_cast<int64_t>(v);
+  pos += n + static_cast<int64_t>(v);
+  n = bdh_varint_read(buf, len, pos, &v);
+  if (!n || pos + n + static_cast<int64_t>(v) > len) return -1;
+  out[2] = pos + n; out[3] = static_cast<int64_t>(v);
+  pos += n + static_cast<int64_t>(v);
+  n = bdh_varint_read(buf, len, pos, &v);
+  if (!n || v > 8) return -1;
+  out[4] = static_cast<int64_t>(v);
+  pos += n;
+  for (uint64_t i = 0; i < 8; ++i) out[5 + i] = 1;
+  for (uint64_t i = 0; i < static_cast<uint64_t>(out[4]); ++i) {
+    uint64_t d;
+    n = bdh_varint_read(buf, len, pos, &d);
+    if (!n) return -1;
+    out[5 + i] = static_cast<int64_t>(d);
+    pos += n;
+  }
+  n = bdh_varint_read(buf, len, pos, &v);
+  if (!n) return -1;
+  out[12 + 1 - 1] = static_cast<int64_t>(v);
+  return pos + n;
+}
+
+// fp32 -> fp16 (round to nearest even) for the quantize tool, and back.
+static inline uint16_t f32_to_f16(float f) {
+  uint32_t x; std::memcpy(&x, &f, 4);
+  uint32_t sign = (x >> 16) & 0x8000u;
+  int32_t e = static_cast<int32_t>((x >> 23) & 0xFF) - 127 + 15;
+  uint32_t m = x & 0x7FFFFFu;
+  if (((x >> 23) & 0xFF) == 0xFF) return static_cast<uint16_t>(sign | 0x7C00u | (m ? 0x200u : 0));
+  if (e >= 31) return static_cast<uint16_t>(sign | 0x7C00u);
+  if (e <= 0) {
+    if (e < -10) return static_cast<uint16_t>(sign);
+    m |= 0x800000u;
+    uint32_t shift = static_cast<uint32_t>(14 - e);
+    uint32_t half = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1), mid = 1u << (shift - 1);
+    if (rem > mid || (rem == mid && (half & 1))) ++half;
+    return static_cast<uint16_t>(sign | half);
+  }
+  uint32_t half = (static_cast<uint32_t>(e) << 10) | (m >> 13);
+  uint32_t rem = m & 0x1FFFu;
+  if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) ++half;
+  return static_cast<uint16_t>(sign | half);
+}
+
+void bdh_f32_to_f16(const float* in, uint16_t* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = f32_to_f16(in[i]);
+}
+
+}  // extern "C"

@@ -44,6 +44,7 @@ class FlatParams:
             view.copy_(p.data)
             p.data = view
             p.grad = self.grad[off:off + p.numel()].view_as(p)
+        module._flat_params = self
         self.refresh_shadow()
 
     def view(self, buf: torch.Tensor, i: int) -> torch.Tensor:

@@ -1,0 +1,65 @@
+"""ctypes front end of the host-side native library (`_host.so`): window gathering for the data
+loader, bincode varints and parameter scanning for the Burn record codec, fp32->fp16 conversion.
+Built by `burn_dragon_b200.build`; every caller has a numpy fallback, so a missing library only
+costs speed."""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import numpy as np
+
+_LIB = None
+_PATH = Path(__file__).resolve().parent.parent / "_host.so"
+
+
+def _load():
+    global _LIB
+    if _LIB is None and _PATH.exists():
+        try:
+            lib = ctypes.CDLL(str(_PATH))
+            lib.bdh_gather_windows.restype = ctypes.c_int
+            lib.bdh_record_scan_param.restype = ctypes.c_int64
+            lib.bdh_varint_read.restype = ctypes.c_int
+            lib.bdh_varint_write.restype = ctypes.c_int
+            _LIB = lib
+        except OSError:
+            _LIB = False
+    return _LIB or None
+
+
+def available() -> bool:
+    return _load() is not None
+
+
+def gather_windows(tokens: np.ndarray, starts: np.ndarray, width: int, out) -> None:
+    """out (torch int64 [rows, width], contiguous host tensor) <- token windows."""
+    lib = _load()
+    starts = np.ascontiguousarray(starts, dtype=np.int64)
+    rc = lib.bdh_gather_windows(ctypes.c_void_p(tokens.ctypes.data), ctypes.c_int64(len(tokens)),
+                                ctypes.c_void_p(starts.ctypes.data), ctypes.c_int64(len(starts)),
+                                ctypes.c_int64(width), ctypes.c_void_p(out.data_ptr()),
+                                ctypes.c_int(min(8, os.cpu_count() or 1)))
+    if rc != 0:
+        raise IndexError("window start out of range")
+
+
+def scan_param(buf: bytes, pos: int):
+    """Parse one serialized parameter at `pos`. Returns (next_pos, id, data_off, data_len, shape, dtype)."""
+    lib = _load()
+    out = (ctypes.c_int64 * 13)()
+    nxt = lib.bdh_record_scan_param(ctypes.c_char_p(buf), ctypes.c_int64(len(buf)), ctypes.c_int64(pos), out)
+    if nxt < 0:
+        raise ValueError("malformed parameter record")
+    pid = buf[out[0]:out[0] + out[1]].decode("utf-8")
+    shape = [int(out[5 + i]) for i in range(int(out[4]))]
+    return int(nxt), pid, int(out[2]), int(out[3]), shape, int(out[12])
+
+
+def f32_to_f16(a: np.ndarray) -> np.ndarray:
+    lib = _load()
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib.bdh_f32_to_f16(ctypes.c_void_p(a.ctypes.data), ctypes.c_void_p(out.ctypes.data), ctypes.c_int64(a.size))
+    return out.view(np.float16)
