@@ -1,0 +1,343 @@
+"""Command line entry points: `python -m burn_dragon_b200 <train|infer|bench|quantize|build-vocab|ckpt>`.
+
+The flags mirror the reference's binaries (src/bin/train.rs:52-81, src/bin/infer.rs:631-687,
+src/bin/quantize.rs): `-c/--config` is repeatable and every file is merged over `config/base.toml`;
+`infer` finds the newest run through `runs/latest` and applies its `config.json` when no `-c` is
+given. `bench` is an addition (the reference only has criterion benches).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+from typing import List, Optional
+
+import torch
+
+from . import config as C
+
+
+def _load_config(paths: List[str], base: Optional[str] = None) -> C.TrainingConfig:
+    base_path = Path(base) if base else C.preset_path("base")
+    return C.load_training_config([base_path] + [Path(p) for p in paths])
+
+
+def _device(name: Optional[str] = None) -> torch.device:
+    if name:
+        return torch.device(name)
+    if torch.cuda.is_available():
+        from .parallel import dist_utils
+        return torch.device("cuda", dist_utils.env_local_rank())
+    return torch.device("cpu")
+
+
+# ------------------------------------------------------------------------------------------------
+# train
+# ------------------------------------------------------------------------------------------------
+def resolve_train_schedule(training, steps_per_epoch: int):
+    """(steps_per_epoch, total_steps, total_epochs, source): `epochs` wins over `max_iters`
+    (src/bin/train.rs:508-542)."""
+    spe = max(1, steps_per_epoch)
+    if training.epochs is not None:
+        ep = max(1, training.epochs)
+        return spe, max(1, spe * ep), ep, "epochs"
+    total = max(1, training.max_iters)
+    return spe, total, max(1, -(-total // spe)), "max_iters"
+
+
+def cmd_build_vocab(cfg: C.TrainingConfig) -> int:
+    """Fit / load the tokenizer of the configured dataset and report it (train.rs:585-594)."""
+    from .data import dataset as D
+    ds = D.build_dataset(cfg.dataset, cfg.training)
+    print(f"tokenizer `{cfg.dataset.tokenizer.type}` with {len(ds.tokenizer)} tokens; corpus {len(ds.tokens)} tokens")
+    return 0
+
+
+def cmd_train(args) -> int:
+    from .data import dataset as D
+    from .engine import checkpoint as CK
+    from .engine.metrics import MetricsLogger, theoretical_profile
+    from .engine.optim import LRSchedule
+    from .engine.trainer import Trainer
+    from .models.factory import build_model
+    from .parallel import dist_utils
+
+    cfg = _load_config(args.config, args.base)
+    if args.synthetic:
+        cfg.dataset.type = "synthetic"
+        cfg.dataset.tokenizer = C.TokenizerConfig(type="byte", add_special_tokens=False)
+    if args.max_iters is not None:
+        cfg.training.max_iters, cfg.training.epochs = args.max_iters, None
+    if args.command == "build-vocab":
+        return cmd_build_vocab(cfg)
+    dist_utils.init_distributed()
+    rank, world = dist_utils.rank(), dist_utils.world_size()
+    dev = _device(args.device)
+    torch.manual_seed(cfg.training.seed)
+    ds = D.build_dataset(cfg.dataset, cfg.training)
+    ds.rng = __import__("numpy").random.default_rng(cfg.training.seed + rank)
+    model = build_model(cfg, vocab_size=len(ds.tokenizer)).to(dev)
+    model.recompute = cfg.training.recompute
+    if cfg.precision.compute != "bf16":
+        model.use_native = False
+    spe, total_steps, total_epochs, source = resolve_train_schedule(cfg.training, ds.steps_per_epoch(D.TRAIN))
+    if rank == 0:
+        print(f"train schedule: steps_per_epoch={spe}, total_steps={total_steps}, epochs={total_epochs}, "
+              f"source={source}", flush=True)
+    sched = LRSchedule(cfg.optimizer.lr_schedule, cfg.optimizer.learning_rate, total_steps,
+                       getattr(getattr(model, "config", None), "n_embd", 256))
+    strategy = cfg.parallel.strategy if world > 1 else "single"
+    wrapper = None
+    if strategy in ("fsdp", "tp"):
+        from .parallel import build_wrapper
+        wrapper = build_wrapper(model, cfg, strategy)
+    trainer = Trainer(model, cfg.optimizer.learning_rate, cfg.optimizer.weight_decay, cfg.optimizer.beta1,
+                      cfg.optimizer.beta2, cfg.optimizer.eps, sched, strategy, cfg.parallel.fused_collectives,
+                      cfg.training.fast_train, cfg.training.grad_clip, wrapper)
+    train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe, total_steps)
+    val_spe = ds.steps_per_epoch(D.VAL)
+    valid_steps = max(1, min(max(1, total_steps // max(1, cfg.training.log_frequency)), val_spe))
+    valid_loader = D.RandomDataLoader(ds, D.VAL, dev, valid_steps, None)
+
+    run_root = Path(args.runs)
+    start_epoch = 0
+    if args.resume:
+        run_dir = CK.resolve_run_dir(None if args.resume == "latest" else args.resume, run_root)
+        run_name = run_dir.name
+        mp, sp, start_epoch = CK.resolve_checkpoint(str(run_dir))
+        CK.load_checkpoint(model, mp, sp, trainer, train_loader)
+        if rank == 0:
+            print(f"resumed {run_name} at epoch {start_epoch}, step {trainer.step_index}", flush=True)
+    else:
+        run_dir, run_name = CK.create_run_dir(run_root)
+    if rank == 0:
+        run_dir.mkdir(parents=True, exist_ok=True)
+        CK.write_latest_run(run_root, run_name)
+        CK.write_run_config(cfg, run_dir, run_name)
+        tok = ds.tokenizer
+        if hasattr(tok, "save"):
+            tok.save(run_dir / "vocab.json")
+    log = MetricsLogger(run_dir if rank == 0 else None, cfg.training.log_frequency, rank)
+
+    tokens_per_step = cfg.training.batch_size * cfg.training.block_size * world
+    epoch = start_epoch
+    while trainer.step_index < total_steps:
+        epoch += 1
+        model.train()
+        before = trainer.step_index
+        for batch in train_loader:
+            t0 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
+            t1 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
+            wall = time.perf_counter()
+            if t0 is not None:
+                t0.record()
+            lr = trainer.current_lr()
+            loss = trainer.train_step(batch.inputs, batch.targets)
+            step = trainer.step_index
+            if step % cfg.training.log_frequency == 0 or step == total_steps:
+                if t1 is not None:
+                    t1.record()
+                    torch.cuda.synchronize()
+                    ms = dist_utils.max_over_ranks(t0.elapsed_time(t1), dev)
+                else:
+                    ms = (time.perf_counter() - wall) * 1e3
+                log.log("train", step, loss=float(loss), lr=lr, step_ms=ms, tokens_per_s=tokens_per_step / ms * 1e3)
+        if trainer.step_index == before:
+            break           # the loader's global step cap is exhausted
+        vloss = [float(trainer.eval_step(b.inputs, b.targets)) for b in valid_loader]
+        log.log("valid", trainer.step_index, loss=sum(vloss) / len(vloss), epoch=epoch)
+        logical = wrapper.gather_state_dict() if wrapper is not None else None
+        if rank == 0:
+            CK.save_checkpoint(run_dir, epoch, model, trainer, train_loader, logical_state=logical)
+        dist_utils.barrier()
+        if trainer.step_index >= total_steps:
+            break
+    if rank == 0:
+        print(log.summary())
+        mc = getattr(model, "config", None)
+        if hasattr(mc, "flops_per_token_forward"):
+            prof = theoretical_profile(mc, cfg.training.batch_size, cfg.training.block_size)
+            print("theoretical profile: " + json.dumps(prof))
+        print(f"run directory: {run_dir}")
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------
+# infer
+# ------------------------------------------------------------------------------------------------
+def apply_run_config(cfg: C.TrainingConfig, run_cfg: dict) -> None:
+    """Apply `runs/<name>/config.json` over a config (src/bin/infer.rs:534-605)."""
+    ov = run_cfg.get("overrides", {})
+    for k, v in ov.items():
+        if v is not None and hasattr(cfg.model, k):
+            setattr(cfg.model, k, v)
+    if run_cfg.get("block_size"):
+        cfg.training.block_size = int(run_cfg["block_size"])
+
+
+def cmd_infer(args) -> int:
+    from .data import tokenizer as T
+    from .engine import checkpoint as CK
+    from .engine import generation as GEN
+    from .models.factory import build_model
+
+    cfg = _load_config(args.config, args.base)
+    model_path, state_path, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    ckpt_dir = model_path.parent
+    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    run_cfg_path = run_dir / "config.json"
+    if not args.config and run_cfg_path.exists():
+        apply_run_config(cfg, json.loads(run_cfg_path.read_text()))
+    # generation overrides (src/bin/infer.rs:408-433)
+    g = cfg.generation
+    if args.prompt is not None:
+        g.prompt = args.prompt
+    if args.max_tokens is not None:
+        g.max_tokens = args.max_tokens
+    if args.temperature is not None:
+        g.temperature = args.temperature
+    if args.top_k is not None:
+        g.top_k = args.top_k
+    if args.greedy:
+        g.greedy = True
+    if args.context_mode:
+        g.context_strategy = C.ContextStrategyConfig(args.context_mode, args.context_window)
+    # tokenizer: the run's vocab.json, else the dataset cache
+    vocab = run_dir / "vocab.json"
+    if cfg.dataset.tokenizer.type == "char":
+        vp = vocab if vocab.exists() else T.storage_path(cfg.dataset.tokenizer, cfg.dataset.cache_dir)
+        tok = T.CharVocab.load(vp)
+    else:
+        tok = T.ByteTokenizer(cfg.dataset.tokenizer.add_special_tokens)
+    dev = _device(args.device)
+    model = build_model(cfg, vocab_size=len(tok)).to(dev).eval()
+    CK.load_checkpoint(model, model_path, state_path)
+    if args.fp32:
+        model.use_native = False
+    print(f"loaded {model_path} (epoch {epoch}) on {dev}", file=sys.stderr)
+
+    strategy = GEN.resolve_context_strategy(g.context_strategy, cfg.training.block_size)
+    ids = tok.encode(g.prompt, False, False)
+    if strategy.kind == "sliding" and len(ids) > strategy.window:
+        ids = ids[-strategy.window:]
+    max_new = GEN.normalize_max_tokens(g.max_tokens)
+    if max_new is None:
+        max_new = 256
+    settings = GEN.GenerationSettings(max_new, g.temperature, g.top_k, strategy, g.greedy, g.seed)
+    viz = None
+    if args.viz:
+        from .viz.encoder import VizConfig, VizEncoder
+        model.capture_viz = True
+        model.use_native = False
+        viz = VizEncoder(VizConfig(history=args.viz_history), model.config, dev)
+    if args.streaming:
+        sys.stdout.write(g.prompt)
+        sys.stdout.flush()
+        printer = GEN.StreamPrinter(tok)
+        state, last = GEN.prefill_state(model, ids, dev)
+        gen = torch.Generator(device=dev).manual_seed(g.seed) if g.seed is not None and not g.greedy else None
+        for _ in range(max_new):
+            nxt, last = GEN.sample_next_token(model, state, last, g.temperature, g.top_k, g.greedy, gen)
+            printer.push(int(nxt[0]))
+            if viz is not None:
+                frame = state.take_viz()
+                if frame is not None and viz.should_capture():
+                    viz.step(frame)
+        sys.stdout.write("\n")
+        if viz is not None and args.viz_out:
+            viz.save(args.viz_out)
+    else:
+        toks = GEN.generate_tokens(model, ids, dev, settings)
+        print(tok.decode([int(t) for t in toks[0].tolist()]))
+    return 0
+
+
+def cmd_quantize(args) -> int:
+    """f32 checkpoint -> f16 checkpoint next to it (src/bin/quantize.rs:36-86)."""
+    from .engine import burn_record as BR
+    from .engine import checkpoint as CK
+    model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    out = BR.quantize_file(model_path, args.output)
+    print(f"wrote {out} ({out.stat().st_size} bytes, from epoch {epoch})")
+    return 0
+
+
+def cmd_ckpt(args) -> int:
+    """Inspect a checkpoint file: metadata, tensor names, shapes."""
+    from .engine import burn_record as BR
+    rec = BR.load(args.file)
+    print("metadata:", rec.metadata)
+    for k, p in rec.params.items():
+        print(f"  {k:<14} id={p.id} shape={tuple(p.data.shape)} dtype={p.data.dtype}")
+    print("dims:", BR.infer_dims(rec))
+    return 0
+
+
+def cmd_bench(args) -> int:
+    from .engine import bench as B
+    res = B.run(args.what, args.preset, steps=args.steps, warmup=args.warmup, streams=args.streams,
+                prompt=args.prompt_len, new_tokens=args.new_tokens)
+    print(json.dumps(res))
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="burn_dragon_b200")
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    def common(p):
+        p.add_argument("-c", "--config", action="append", default=[], help="TOML overlay (repeatable)")
+        p.add_argument("--base", default=None, help="base TOML (default: config/base.toml)")
+        p.add_argument("--device", default=None)
+        p.add_argument("--runs", default="runs", help="run root directory")
+
+    for name in ("train", "build-vocab"):
+        p = sub.add_parser(name)
+        common(p)
+        p.add_argument("--synthetic", action="store_true", help="train on uniform random bytes")
+        p.add_argument("--max-iters", type=int, default=None)
+        p.add_argument("--resume", default=None, help="run name / path, or `latest`")
+        p.set_defaults(fn=cmd_train)
+    p = sub.add_parser("infer")
+    common(p)
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--epoch", type=int, default=None)
+    p.add_argument("--prompt", default=None)
+    p.add_argument("--max-tokens", type=int, default=None)
+    p.add_argument("--temperature", type=float, default=None)
+    p.add_argument("--top-k", type=int, default=None)
+    p.add_argument("--greedy", action="store_true")
+    p.add_argument("--context-mode", choices=["infinite", "sliding"], default=None)
+    p.add_argument("--context-window", type=int, default=None)
+    p.add_argument("--streaming", action="store_true")
+    p.add_argument("--fp32", action="store_true", help="plain torch fp32 path instead of the bf16 kernels")
+    p.add_argument("--viz", action="store_true", help="capture activation images (headless)")
+    p.add_argument("--viz-history", type=int, default=256)
+    p.add_argument("--viz-out", default=None, help="write the captured images to this .npz file")
+    p.set_defaults(fn=cmd_infer)
+    p = sub.add_parser("quantize")
+    common(p)
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--epoch", type=int, default=None)
+    p.add_argument("--output", default=None)
+    p.set_defaults(fn=cmd_quantize)
+    p = sub.add_parser("ckpt")
+    p.add_argument("file")
+    p.set_defaults(fn=cmd_ckpt)
+    p = sub.add_parser("bench")
+    p.add_argument("what", choices=["train", "decode", "reference-shapes"])
+    p.add_argument("--preset", default="b200_base")
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--streams", type=int, default=64)
+    p.add_argument("--prompt-len", type=int, default=1024)
+    p.add_argument("--new-tokens", type=int, default=2048)
+    p.set_defaults(fn=cmd_bench)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
