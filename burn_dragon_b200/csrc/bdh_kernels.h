@@ -87,6 +87,23 @@ int bdh_adamw(float* master, const float* grad, float* m, float* v, void* param_
 int bdh_cast_f32_to_bf16(const float* in, void* out_bf16, long long n, cudaStream_t s);
 int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cudaStream_t s);
 
+// ---- NVLink collectives over symmetric memory (collectives.cu) --------------------------------
+// buf_ptrs / flag_ptrs: this process's mappings of every rank's data / flag buffer (world entries);
+// mc_ptr: NVSwitch multicast mapping of the data buffer or 0; n_floats % (4*world) == 0;
+// `epoch` must grow by one per call on every rank; flag buffer >= ctas*world uint32, zeroed once.
+int bdh_allreduce_scale(const long long* buf_ptrs, const long long* flag_ptrs, long long mc_ptr, int rank,
+                        int world, long long n_floats, float scale, unsigned epoch, int ctas, int* status,
+                        cudaStream_t s);
+// Reduce-scatter of fp32 gradients + AdamW on the owned slice + all-gather of bf16 parameters.
+// master / m / v hold only the owned slice (n_floats/world elements, last rank takes the remainder).
+int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag_ptrs, long long grad_mc,
+                    const long long* shadow_ptrs, int rank, int world, long long n_floats, float* master,
+                    float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, int step,
+                    float grad_scale, unsigned epoch, int ctas, int* status, cudaStream_t s);
+// Waits (at most limit_ns) for *flag to reach `value`; on expiry writes the timeout status and returns.
+int bdh_wait_timeout_probe(const unsigned* flag, unsigned value, unsigned long long limit_ns, int* status,
+                           cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,6 +6,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <vector>
+
 #include "bdh_kernels.h"
 
 namespace {
@@ -140,6 +142,41 @@ void adamw(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, const optio
 
 Tensor status() { return status_word(); }
 
+std::vector<long long> as_ptrs(at::IntArrayRef v) { return std::vector<long long>(v.begin(), v.end()); }
+
+// `anchor` only selects the device / stream; the buffers are addressed through the pointer lists.
+void allreduce_scale(const Tensor& anchor, at::IntArrayRef buf_ptrs, at::IntArrayRef flag_ptrs, int64_t mc_ptr,
+                     int64_t rank, int64_t world, int64_t n_floats, double scale, int64_t epoch, int64_t ctas) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world);
+  auto b = as_ptrs(buf_ptrs), f = as_ptrs(flag_ptrs);
+  check_rc(bdh_allreduce_scale(b.data(), f.data(), mc_ptr, rank, world, n_floats, scale, (unsigned)epoch, ctas,
+                               status_word().data_ptr<int>(), cur_stream()), "allreduce_scale");
+}
+
+void rs_adamw_ag(const Tensor& anchor, at::IntArrayRef grad_ptrs, at::IntArrayRef flag_ptrs, int64_t grad_mc,
+                 at::IntArrayRef shadow_ptrs, int64_t rank, int64_t world, int64_t n_floats, Tensor& master,
+                 Tensor& m, Tensor& v, double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+                 double grad_scale, int64_t epoch, int64_t ctas) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  TORCH_CHECK((int64_t)grad_ptrs.size() == world && (int64_t)flag_ptrs.size() == world &&
+              (int64_t)shadow_ptrs.size() == world);
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&master, &m, &v})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat);
+  auto g = as_ptrs(grad_ptrs), f = as_ptrs(flag_ptrs), sh = as_ptrs(shadow_ptrs);
+  check_rc(bdh_rs_adamw_ag(g.data(), f.data(), grad_mc, sh.data(), rank, world, n_floats, master.data_ptr<float>(),
+                           m.data_ptr<float>(), v.data_ptr<float>(), lr, beta1, beta2, eps, wd, step, grad_scale,
+                           (unsigned)epoch, ctas, status_word().data_ptr<int>(), cur_stream()), "rs_adamw_ag");
+}
+
+void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
+  c10::cuda::CUDAGuard guard(flag.device());
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
+  check_rc(bdh_wait_timeout_probe(reinterpret_cast<const unsigned*>(flag.data_ptr<int>()), (unsigned)value,
+                                  (unsigned long long)limit_ns, status_word().data_ptr<int>(), cur_stream()),
+           "wait_timeout_probe");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(bdh, m) {
@@ -157,6 +194,12 @@ TORCH_LIBRARY(bdh, m) {
   m.def("adamw(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p16, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale) -> ()");
   m.def("status() -> Tensor");
+  m.def("allreduce_scale(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int rank, int world, "
+        "int n_floats, float scale, int epoch, int ctas) -> ()");
+  m.def("rs_adamw_ag(Tensor anchor, int[] grad_ptrs, int[] flag_ptrs, int grad_mc, int[] shadow_ptrs, int rank, "
+        "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
+        "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
+  m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
@@ -169,5 +212,8 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("block_out_bwd", &block_out_bwd);
   m.impl("cross_entropy", &cross_entropy);
   m.impl("adamw", &adamw);
+  m.impl("allreduce_scale", &allreduce_scale);
+  m.impl("rs_adamw_ag", &rs_adamw_ag);
+  m.impl("wait_timeout_probe", &wait_timeout_probe);
 }
 TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) { m.impl("status", &status); }

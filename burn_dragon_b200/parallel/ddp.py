@@ -32,6 +32,9 @@ class DataParallel:
             try:
                 from . import symm
                 self._symm = symm.SymmetricAllReduce(flat.grad, group=group)
+                # gradients now accumulate directly in symmetric memory, so the reduction needs no copy
+                flat.grad = self._symm.tensor[:flat.numel]
+                flat.zero_grad()
             except Exception as e:  # noqa: BLE001 - recorded, baseline path is used instead
                 self.fallback_reason = repr(e)
                 self.mode = "nccl"

@@ -1,0 +1,107 @@
+"""Host-side failure detection.
+
+The reference has no multi-rank mode, so no failure detection either (its only liveness code is a
+stop flag for the visualiser thread, src/bin/infer.rs:356-397). Here:
+
+* `Heartbeat` - every rank publishes a timestamp in the process group's key-value store from a
+  background thread; `dead_ranks()` lists peers whose heartbeat is older than the timeout or that
+  announced their departure. Trainers call `check()` between steps, i.e. before they launch a
+  kernel or collective that would wait for the peer.
+* `device_status()` - turns a non-zero kernel status word (a bounded in-kernel wait that gave up)
+  into a Python exception, leaving the CUDA context usable.
+
+Nothing here makes a GPU fault, trap or hang; failures are injected on the host (a rank that
+raises, exits or stops publishing).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import List, Optional
+
+import torch.distributed as dist
+
+STATUS_NAMES = {0: "ok", 1: "smem-full wait timed out", 2: "smem-empty wait timed out",
+                3: "tmem-full wait timed out", 4: "tmem-empty wait timed out", 5: "peer flag wait timed out",
+                6: "bad argument"}
+
+
+class RankFailure(RuntimeError):
+    def __init__(self, ranks: List[int]):
+        super().__init__(f"ranks {ranks} stopped responding")
+        self.ranks = ranks
+
+
+class KernelTimeout(RuntimeError):
+    pass
+
+
+class Heartbeat:
+    def __init__(self, rank: int, world: int, interval_s: float = 1.0, timeout_s: float = 10.0, store=None,
+                 prefix: str = "bdh_hb"):
+        self.rank, self.world = rank, world
+        self.interval, self.timeout = interval_s, timeout_s
+        self.store = store if store is not None else dist.distributed_c10d._get_default_store()
+        self.prefix = prefix
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    def _key(self, r: int) -> str:
+        return f"{self.prefix}/{r}"
+
+    def _publish(self, value: str) -> None:
+        self.store.set(self._key(self.rank), value)
+
+    def start(self) -> None:
+        self._publish(repr(time.time()))
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.interval):
+            try:
+                self._publish(repr(time.time()))
+            except Exception:  # noqa: BLE001 - the store went away: nothing left to tell
+                return
+
+    def stop(self, leave: bool = False) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2 * self.interval + 1)
+        if leave:
+            try:
+                self._publish("left")
+            except Exception:  # noqa: BLE001
+                pass
+
+    def dead_ranks(self) -> List[int]:
+        now, dead = time.time(), []
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            key = self._key(r)
+            try:
+                if not self.store.check([key]):
+                    continue            # not started yet
+                val = self.store.get(key).decode()
+            except Exception:  # noqa: BLE001
+                dead.append(r)
+                continue
+            if val == "left" or now - float(val) > self.timeout:
+                dead.append(r)
+        return dead
+
+    def check(self) -> None:
+        dead = self.dead_ranks()
+        if dead:
+            raise RankFailure(dead)
+
+
+def device_status(raise_on_error: bool = True) -> int:
+    """Read the kernels' status word (synchronises the device)."""
+    from ..ops import native
+    code = native.status_code()
+    if code and raise_on_error:
+        native.clear_status()
+        raise KernelTimeout(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+    return code

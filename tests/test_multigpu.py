@@ -1,0 +1,24 @@
+"""Fused NVLink collectives and data-parallel equality on >= 2 GPUs (child processes, one per GPU)."""
+import pytest
+
+from test_parallel_cpu import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+@pytest.mark.parametrize("no_multimem", ["0", "1"])
+def test_symmetric_allreduce(no_multimem):
+    run_ranks("allreduce", cpu=False, env={"BDH_NO_MULTIMEM": no_multimem})
+
+
+def test_sharded_adamw_kernel():
+    run_ranks("sharded_adamw", cpu=False)
+
+
+@pytest.mark.parametrize("case", ["ddp", "ddp_nccl"])
+def test_ddp_equals_single_gpu(case):
+    run_ranks(case, cpu=False)
+
+
+def test_rank_exit_detected_without_gpu_fault():
+    run_ranks("rank_exit", cpu=False, env={"NCCL_NVLS_ENABLE": "0", "BDH_NO_MULTIMEM": "1"})
