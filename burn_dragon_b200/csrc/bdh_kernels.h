@@ -87,6 +87,22 @@ int bdh_adamw(float* master, const float* grad, float* m, float* v, void* param_
 int bdh_cast_f32_to_bf16(const float* in, void* out_bf16, long long n, cudaStream_t s);
 int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cudaStream_t s);
 
+// ---- cached decode (decode.cu) -------------------------------------------------------------------
+// a[h*B+b,:] += sum_n q[b,h*Np+n] rho[b,h,n,:] ; rho = (rho + q^T v) * exp(-slope_h). `a` must be
+// zeroed by the caller. slopes == nullptr: no decay, rows with q == 0 are skipped entirely.
+int bdh_decode_state_update(const void* q_bf16, const void* v_bf16, float* rho, float* a, const float* slopes,
+                            int B, int H, int Np, int D, cudaStream_t s);
+// One token per row of fp32 logits [B, V <= 1024]; step_dev (optional) is a device counter mixed
+// into the random stream so a captured graph draws fresh numbers every replay.
+int bdh_sample_tokens(const float* logits, long long* out, int B, int V, float temperature, int top_k,
+                      int greedy, unsigned seed, const int* step_dev, int step_host, cudaStream_t s);
+// Column `cursor` of an fp32 RGBA ring-buffer image [units, history, 4] from `units` activations.
+int bdh_viz_encode_units(const float* values, float* image, int units, int history, int cursor, float gain,
+                         float gamma, const float* lo_rgb, const float* hi_rgb, cudaStream_t s);
+// fp16 (cos, sin) pairs of the rotary phase at device-resident position *pos; and counter += by.
+int bdh_rope_table_step(const int* pos, const float* pair_freqs, void* table_f16, int n_pairs, cudaStream_t s);
+int bdh_bump_counter(int* counter, int by, cudaStream_t s);
+
 // ---- NVLink collectives over symmetric memory (collectives.cu) --------------------------------
 // buf_ptrs / flag_ptrs: this process's mappings of every rank's data / flag buffer (world entries);
 // mc_ptr: NVSwitch multicast mapping of the data buffer or 0; n_floats % (4*world) == 0;

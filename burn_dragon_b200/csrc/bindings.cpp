@@ -169,6 +169,50 @@ void rs_adamw_ag(const Tensor& anchor, at::IntArrayRef grad_ptrs, at::IntArrayRe
                            (unsigned)epoch, ctas, status_word().data_ptr<int>(), cur_stream()), "rs_adamw_ag");
 }
 
+void decode_state_update(const Tensor& q, const Tensor& v, Tensor& rho, Tensor& a, const optional<Tensor>& slopes) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(rho.dim() == 4 && rho.is_contiguous() && rho.scalar_type() == at::kFloat);
+  const int64_t B = rho.size(0), H = rho.size(1), Np = rho.size(2), D = rho.size(3);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.numel() == B * H * Np);
+  TORCH_CHECK(v.scalar_type() == at::kBFloat16 && v.is_contiguous() && v.numel() == B * D);
+  TORCH_CHECK(a.scalar_type() == at::kFloat && a.is_contiguous() && a.numel() == H * B * D);
+  check_rc(bdh_decode_state_update(q.data_ptr(), v.data_ptr(), rho.data_ptr<float>(), a.data_ptr<float>(),
+                                   slopes.has_value() ? slopes->data_ptr<float>() : nullptr, B, H, Np, D, cur_stream()),
+           "decode_state_update");
+}
+void sample_tokens(const Tensor& logits, Tensor& out, double temperature, int64_t top_k, bool greedy, int64_t seed,
+                   int64_t step, const optional<Tensor>& step_dev) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kFloat);
+  TORCH_CHECK(out.scalar_type() == at::kLong && out.is_contiguous() && out.numel() == logits.size(0));
+  check_rc(bdh_sample_tokens(logits.data_ptr<float>(), reinterpret_cast<long long*>(out.data_ptr<int64_t>()),
+                             logits.size(0), logits.size(1), temperature, top_k, greedy, (unsigned)seed,
+                             step_dev.has_value() ? step_dev->data_ptr<int>() : nullptr, step, cur_stream()),
+           "sample_tokens");
+}
+void viz_encode_units(const Tensor& values, Tensor& image, int64_t cursor, double gain, double gamma,
+                      at::ArrayRef<double> lo, at::ArrayRef<double> hi) {
+  c10::cuda::CUDAGuard guard(values.device());
+  TORCH_CHECK(values.scalar_type() == at::kFloat && values.is_contiguous());
+  TORCH_CHECK(image.scalar_type() == at::kFloat && image.is_contiguous() && image.dim() == 3 && image.size(2) == 4 &&
+              image.size(0) == values.numel() && lo.size() == 3 && hi.size() == 3);
+  float l[3] = {(float)lo[0], (float)lo[1], (float)lo[2]}, h[3] = {(float)hi[0], (float)hi[1], (float)hi[2]};
+  check_rc(bdh_viz_encode_units(values.data_ptr<float>(), image.data_ptr<float>(), values.numel(), image.size(1), cursor,
+                                gain, gamma, l, h, cur_stream()), "viz_encode_units");
+}
+void rope_table_step(const Tensor& pos, const Tensor& pair_freqs, Tensor& table) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  TORCH_CHECK(pos.scalar_type() == at::kInt && pair_freqs.scalar_type() == at::kFloat && pair_freqs.is_contiguous());
+  TORCH_CHECK(table.is_contiguous() && table.element_size() == 2 && table.numel() == 2 * pair_freqs.numel());
+  check_rc(bdh_rope_table_step(pos.data_ptr<int>(), pair_freqs.data_ptr<float>(), table.data_ptr(), pair_freqs.numel(),
+                               cur_stream()), "rope_table_step");
+}
+void bump_counter(Tensor& counter, int64_t by) {
+  c10::cuda::CUDAGuard guard(counter.device());
+  TORCH_CHECK(counter.scalar_type() == at::kInt);
+  check_rc(bdh_bump_counter(counter.data_ptr<int>(), by, cur_stream()), "bump_counter");
+}
+
 void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
   c10::cuda::CUDAGuard guard(flag.device());
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
@@ -200,6 +244,12 @@ TORCH_LIBRARY(bdh, m) {
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
+  m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
+  m.def("sample_tokens(Tensor logits, Tensor(a!) out, float temperature, int top_k, bool greedy, int seed, int step, "
+        "Tensor? step_dev) -> ()");
+  m.def("viz_encode_units(Tensor values, Tensor(a!) image, int cursor, float gain, float gamma, float[] lo, float[] hi) -> ()");
+  m.def("rope_table_step(Tensor pos, Tensor pair_freqs, Tensor(a!) table) -> ()");
+  m.def("bump_counter(Tensor(a!) counter, int by) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
@@ -215,5 +265,10 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
+  m.impl("decode_state_update", &decode_state_update);
+  m.impl("sample_tokens", &sample_tokens);
+  m.impl("viz_encode_units", &viz_encode_units);
+  m.impl("rope_table_step", &rope_table_step);
+  m.impl("bump_counter", &bump_counter);
 }
 TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) { m.impl("status", &status); }

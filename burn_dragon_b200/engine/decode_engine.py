@@ -1,0 +1,182 @@
+"""Batched cached decoding for BDH on the sm_100a kernels.
+
+One decode step for B independent streams = sample -> embed+LN -> L x (encoder GEMM with ReLU and
+rotation, recurrent state update, LN, gated E_v GEMM, split-K decoder GEMM, layer tail) -> LM head.
+Everything stays on the device: the sampled tokens feed the next step's embedding directly (the
+reference copies logits to the host and samples there for every token, src/generation.rs:106-129),
+and the step is captured once in a CUDA graph and replayed, with the position and the random-stream
+counter held in device memory so the graph needs no new arguments.
+
+The recurrent state is fp32 [B, H, N', D] per layer, exactly `LayerState.rho`.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+
+from ..ops import gemm as G
+from ..ops import native
+from ..ops.fused_bdh import _Dims, _weights
+
+
+class DecodeEngine:
+    def __init__(self, model, use_graph: bool = True, split_k: int = 32):
+        self.model = model
+        self.use_graph = use_graph
+        self.split_k = split_k
+        self._graph = None
+        self._graph_key = None
+
+    # ---- eligibility ---------------------------------------------------------------------------
+    def can_run(self, toks: torch.Tensor, settings) -> bool:
+        c = self.model.config
+        if not toks.is_cuda or not native.available() or not getattr(self.model, "use_native", True):
+            return False
+        if c.n_embd % 64 or c.n_embd > 1024 or c.latent_per_head % 64 or c.vocab_size > 1024 or c.vocab_size % 8:
+            return False
+        if c.block_sparse is not None and c.block_sparse.latent.is_sparse():
+            return False
+        if settings.max_new_tokens is None:
+            return False
+        return True
+
+    # ---- buffers ---------------------------------------------------------------------------------
+    def _alloc(self, B: int, dev):
+        c = self.model.config
+        d = _Dims(self.model, B, 1)
+        S = self.split_k
+        while d.HN % (S * 64):
+            S //= 2
+        S = max(S, 1)
+        bf = dict(device=dev, dtype=torch.bfloat16)
+        f32 = dict(device=dev, dtype=torch.float32)
+        buf = dict(
+            d=d, S=S,
+            tok=torch.zeros(B, device=dev, dtype=torch.int64),
+            logits=torch.zeros(B, d.V, **f32),
+            cur=torch.zeros(B, d.D, **bf), nxt=torch.zeros(B, d.D, **bf),
+            x=torch.zeros(B, d.HN, **bf),
+            q=torch.zeros(B, d.HNp, **bf) if d.rot != "alibi" else None,
+            a=torch.zeros(d.H * B, d.D, **f32), a16=torch.zeros(d.H * B, d.D, **bf),
+            lna=torch.zeros(d.H * B, d.D, **bf),
+            xy=torch.zeros(B, d.HN, **bf),
+            part=torch.zeros(S * B, d.D, **f32), mlp=torch.zeros(B, d.D, **bf),
+            pos=torch.zeros(1, device=dev, dtype=torch.int32),
+            step=torch.zeros(1, device=dev, dtype=torch.int32),
+            table=(torch.zeros(1, d.N, **bf) if d.rot == "rope" else None),
+        )
+        return buf
+
+    # ---- one step (all launches on the current stream) -------------------------------------------
+    def _step(self, buf, W, rho: List[torch.Tensor], settings, seed: int, pos_host: Optional[int]):
+        ops = native.ops
+        d, S = buf["d"], buf["S"]
+        B = buf["tok"].shape[0]
+        ops.sample_tokens(buf["logits"], buf["tok"], float(settings.temperature), int(settings.top_k or 0),
+                          bool(settings.greedy), seed, 0, buf["step"])
+        ops.embed_ln_fwd(buf["tok"], W["embed"], buf["cur"])
+        if d.rot == "rope":
+            ops.rope_table_step(buf["pos"], d.freqs, buf["table"])
+        cur, nxt = buf["cur"], buf["nxt"]
+        for l in range(d.L):
+            if d.rot == "rope":
+                G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, flags=G.F_ROPE | G.F_TABLE,
+                       in0=buf["table"], out0=buf["x"], out1=buf["q"], theta=d.theta, T=1, n_per_head=d.N,
+                       freqs=d.freqs)
+                q = buf["q"]
+            elif d.rot == "pope":
+                G.gemm(cur, W["encoder"], M=B, N=d.N, K=d.D, nz=(d.H, 1), b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0),
+                       o1_off=(d.Np, 0, d.N), epi=G.EPI_RELU, flags=G.F_POPE, out0=buf["x"], out1=buf["q"],
+                       theta=d.theta, T=1, pos0=int(pos_host), n_per_head=d.N, freqs=d.freqs)
+                q = buf["q"]
+            else:
+                G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, out0=buf["x"], theta=d.theta)
+                q = buf["x"]
+            buf["a"].zero_()
+            ops.decode_state_update(q, cur, rho[l], buf["a"], d.slopes)
+            buf["a16"].copy_(buf["a"])
+            ops.layernorm_fwd(buf["a16"], buf["lna"])
+            G.gemm(buf["lna"], W["encoder_v"], M=B, N=d.N, K=d.D, nz=(d.H, 1), a_off=(B, 0, 0, 0),
+                   b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=buf["x"],
+                   out1=buf["xy"], theta=d.theta)
+            ks = d.HN // S
+            G.gemm(buf["xy"], W["decoder"], M=B, N=d.D, K=ks, b_mn=True, nz=(S, 1), a_off=(0, 0, ks, 0),
+                   b_off=(0, 0, ks, 0), c_off=(B, 0, 0, 0), flags=G.F_OUT_F32, out0=buf["part"])
+            torch.sum(buf["part"].view(S, B, d.D), dim=0, out=buf["a"][:B])      # reuse `a` rows as fp32 scratch
+            buf["mlp"].copy_(buf["a"][:B])
+            ops.block_out_fwd(cur, buf["mlp"], nxt)
+            cur, nxt = nxt, cur
+        G.gemm(cur, W["lm_head"], M=B, N=d.V, K=d.D, b_mn=True, flags=G.F_OUT_F32, out0=buf["logits"])
+        ops.bump_counter(buf["pos"], 1)
+        ops.bump_counter(buf["step"], 1)
+
+    # ---- public ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, toks: torch.Tensor, settings, generator=None,
+                 on_token: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
+        from . import generation as GEN
+        model = self.model
+        dev = toks.device
+        B, P = toks.shape
+        state, last = GEN.prefill_state(model, toks, dev)
+        c = model.config
+        rho = []
+        for ls in state.layers:
+            r = ls.rho
+            if r is None:
+                r = torch.zeros(B, c.n_head, c.state_latent, c.n_embd, device=dev)
+            rho.append(r.float().contiguous())
+        buf = self._alloc(B, dev)
+        d = buf["d"]
+        W = _weights(model)
+        buf["logits"].copy_(last.float())
+        buf["pos"].fill_(state.position)
+        seed = int(settings.seed if settings.seed is not None else torch.initial_seed() & 0x7FFFFFFF) & 0xFFFFFFFF
+        graph_ok = self.use_graph and d.rot != "pope"
+        out = [toks]
+        n = int(settings.max_new_tokens)
+        if graph_ok:
+            # warm up once on a side stream (allocations, lazy initialisation), rewind, then capture
+            snap = [r.clone() for r in rho]
+            logits0 = buf["logits"].clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._step(buf, W, rho, settings, seed, None)
+            torch.cuda.current_stream().wait_stream(s)
+            for r, r0 in zip(rho, snap):
+                r.copy_(r0)
+            del snap
+            buf["logits"].copy_(logits0)
+            buf["pos"].fill_(state.position)
+            buf["step"].zero_()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._step(buf, W, rho, settings, seed, None)
+            for _ in range(n):
+                graph.replay()
+                t = buf["tok"].clone()
+                out.append(t.view(-1, 1))
+                if on_token is not None:
+                    on_token(t)
+        else:
+            for i in range(n):
+                self._step(buf, W, rho, settings, seed, state.position + i)
+                t = buf["tok"].clone()
+                out.append(t.view(-1, 1))
+                if on_token is not None:
+                    on_token(t)
+        # the last sampled token has been consumed by the model inside the step that followed it,
+        # except for the final one: logits for it sit in buf["logits"]; expose state for callers
+        for ls, r in zip(state.layers, rho):
+            ls.rho = r
+        state.position += n
+        self.last_state, self.last_logits = state, buf["logits"]
+        return torch.cat(out, dim=1)
+
+
+def attach(model, **kw) -> DecodeEngine:
+    """Give `model` a decode engine; `engine.generation.generate_tokens` uses it when eligible."""
+    model.decode_engine = DecodeEngine(model, **kw)
+    return model.decode_engine

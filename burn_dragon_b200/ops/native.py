@@ -69,6 +69,7 @@ class _CountingOps:
         self.count = 0
 
     def __getattr__(self, name):
+        load()
         fn = getattr(torch.ops.bdh, name)
 
         def call(*a, **k):

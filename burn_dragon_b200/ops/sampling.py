@@ -25,6 +25,6 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] 
         out = torch.empty(B, dtype=torch.int64, device=logits.device)
         _counter[0] += 1
         native.ops.sample_tokens(logits.float().contiguous(), out, float(temperature), int(top_k or 0), bool(greedy),
-                                 int(seed if seed is not None else 0x9E3779B9), _counter[0])
+                                 int(seed if seed is not None else 0x9E3779B9), _counter[0], None)
         return out
     return R.sample_logits(logits, temperature, top_k, greedy, generator)
