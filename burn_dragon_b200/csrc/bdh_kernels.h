@@ -96,12 +96,21 @@ int bdh_decode_state_update(const void* q_bf16, const void* v_bf16, float* rho, 
 // into the random stream so a captured graph draws fresh numbers every replay.
 int bdh_sample_tokens(const float* logits, long long* out, int B, int V, float temperature, int top_k,
                       int greedy, unsigned seed, const int* step_dev, int step_host, cudaStream_t s);
-// Column `cursor` of an fp32 RGBA ring-buffer image [units, history, 4] from `units` activations.
-int bdh_viz_encode_units(const float* values, float* image, int units, int history, int cursor, float gain,
-                         float gamma, const float* lo_rgb, const float* hi_rgb, cudaStream_t s);
+// Column `cursor` of an fp32 RGBA ring-buffer image [rows, history, 4] from `units` activations.
+// Rows [row0, row0+units) of the image; colours are linear RGB; units_per_head > 0 draws separators.
+int bdh_viz_encode_units(const float* values, float* image, int units, int history, int cursor, int row0,
+                         float gain, const float* lo_rgb, const float* hi_rgb, const float* sep_rgb,
+                         int units_per_head, cudaStream_t s);
 // fp16 (cos, sin) pairs of the rotary phase at device-resident position *pos; and counter += by.
 int bdh_rope_table_step(const int* pos, const float* pair_freqs, void* table_f16, int n_pairs, cudaStream_t s);
 int bdh_bump_counter(int* counter, int by, cudaStream_t s);
+
+// ---- SSD chunk scan for the Mamba paths (ssd.cu) -------------------------------------------------
+// h_t = exp(loga_t) h_{t-1} + B_t (x) xw_t ; y_t = C_t . h_t, chunk 64, head dim 64, state dim 128.
+// xw [B,T,H,64], loga [B,T,H], Bm/Cm [B,T,128], h [B,H,128,64] in/out, y [B,T,H,64]; T % 64 == 0.
+// Scratch supplied by the caller: states [B,T/64,H,128,64] and decay [B,T/64,H] (fp32).
+int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
+                       float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s);
 
 // ---- NVLink collectives over symmetric memory (collectives.cu) --------------------------------
 // buf_ptrs / flag_ptrs: this process's mappings of every rank's data / flag buffer (world entries);

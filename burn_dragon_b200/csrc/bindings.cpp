@@ -190,15 +190,16 @@ void sample_tokens(const Tensor& logits, Tensor& out, double temperature, int64_
                              step_dev.has_value() ? step_dev->data_ptr<int>() : nullptr, step, cur_stream()),
            "sample_tokens");
 }
-void viz_encode_units(const Tensor& values, Tensor& image, int64_t cursor, double gain, double gamma,
-                      at::ArrayRef<double> lo, at::ArrayRef<double> hi) {
+void viz_encode_units(const Tensor& values, Tensor& image, int64_t cursor, int64_t row0, double gain,
+                      at::ArrayRef<double> lo, at::ArrayRef<double> hi, at::ArrayRef<double> sep, int64_t units_per_head) {
   c10::cuda::CUDAGuard guard(values.device());
   TORCH_CHECK(values.scalar_type() == at::kFloat && values.is_contiguous());
   TORCH_CHECK(image.scalar_type() == at::kFloat && image.is_contiguous() && image.dim() == 3 && image.size(2) == 4 &&
-              image.size(0) == values.numel() && lo.size() == 3 && hi.size() == 3);
+              row0 + values.numel() <= image.size(0) && lo.size() == 3 && hi.size() == 3 && sep.size() == 3);
   float l[3] = {(float)lo[0], (float)lo[1], (float)lo[2]}, h[3] = {(float)hi[0], (float)hi[1], (float)hi[2]};
+  float sp[3] = {(float)sep[0], (float)sep[1], (float)sep[2]};
   check_rc(bdh_viz_encode_units(values.data_ptr<float>(), image.data_ptr<float>(), values.numel(), image.size(1), cursor,
-                                gain, gamma, l, h, cur_stream()), "viz_encode_units");
+                                row0, gain, l, h, sp, units_per_head, cur_stream()), "viz_encode_units");
 }
 void rope_table_step(const Tensor& pos, const Tensor& pair_freqs, Tensor& table) {
   c10::cuda::CUDAGuard guard(pos.device());
@@ -211,6 +212,20 @@ void bump_counter(Tensor& counter, int64_t by) {
   c10::cuda::CUDAGuard guard(counter.device());
   TORCH_CHECK(counter.scalar_type() == at::kInt);
   check_rc(bdh_bump_counter(counter.data_ptr<int>(), by, cur_stream()), "bump_counter");
+}
+
+void ssd_chunk_scan(const Tensor& xw, const Tensor& loga, const Tensor& Bm, const Tensor& Cm, Tensor& h, Tensor& states,
+                    Tensor& decay, Tensor& y) {
+  c10::cuda::CUDAGuard guard(xw.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&xw, &loga, &Bm, &Cm, &h, &states, &decay, &y})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat);
+  const int64_t B = xw.size(0), T = xw.size(1), H = xw.size(2);
+  TORCH_CHECK(xw.size(3) == 64 && Bm.size(2) == 128 && Cm.size(2) == 128 && T % 64 == 0);
+  TORCH_CHECK(h.numel() == B * H * 128 * 64 && y.numel() == xw.numel() && states.numel() == B * (T / 64) * H * 128 * 64 &&
+              decay.numel() == B * (T / 64) * H);
+  check_rc(bdh_ssd_chunk_scan(xw.data_ptr<float>(), loga.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                              h.data_ptr<float>(), states.data_ptr<float>(), decay.data_ptr<float>(), y.data_ptr<float>(),
+                              B, T, H, cur_stream()), "ssd_chunk_scan");
 }
 
 void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
@@ -244,10 +259,13 @@ TORCH_LIBRARY(bdh, m) {
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
+  m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
+        "Tensor(d!) y) -> ()");
   m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
   m.def("sample_tokens(Tensor logits, Tensor(a!) out, float temperature, int top_k, bool greedy, int seed, int step, "
         "Tensor? step_dev) -> ()");
-  m.def("viz_encode_units(Tensor values, Tensor(a!) image, int cursor, float gain, float gamma, float[] lo, float[] hi) -> ()");
+  m.def("viz_encode_units(Tensor values, Tensor(a!) image, int cursor, int row0, float gain, float[] lo, float[] hi, "
+        "float[] sep, int units_per_head) -> ()");
   m.def("rope_table_step(Tensor pos, Tensor pair_freqs, Tensor(a!) table) -> ()");
   m.def("bump_counter(Tensor(a!) counter, int by) -> ()");
 }
@@ -265,6 +283,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
+  m.impl("ssd_chunk_scan", &ssd_chunk_scan);
   m.impl("decode_state_update", &decode_state_update);
   m.impl("sample_tokens", &sample_tokens);
   m.impl("viz_encode_units", &viz_encode_units);

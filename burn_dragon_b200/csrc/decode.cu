@@ -202,24 +202,28 @@ sample_tokens_kernel(const float* __restrict__ logits, long long* __restrict__ o
 }
 
 // ---- activation images ------------------------------------------------------------------------------
-// One column of a [units, history, 4] fp32 RGBA ring buffer per call: value -> soft-clipped,
-// gamma-shaped intensity -> colour ramp between two palette colours, sRGB -> linear
-// (behaviour of the reference's encoder: src/viz/encoder.rs:234-278).
-__device__ __forceinline__ float srgb_to_linear(float c) {
-  return c <= 0.04045f ? c / 12.92f : powf((c + 0.055f) / 1.055f, 2.4f);
-}
+// One column of a [rows, history, 4] fp32 RGBA ring-buffer image per call, rows [row0, row0+units):
+//   v = max(value, 0); mag = g*v / (g*v + 0.35); mask = v / (v + 0.004); i = (mag*mask)^1.15
+//   rgb = (low + (high - low) * i) * i ; alpha = 1 ; head boundaries take max(rgb, separator)
+// with low / high / separator already in linear colour (behaviour of the reference's encoder,
+// src/viz/encoder.rs:234-298). Rendering it is somebody else's job: the buffer stays on the device
+// or is written to a file.
 __global__ void viz_encode_units_kernel(const float* __restrict__ values, float* __restrict__ image, int units,
-                                        int history, int cursor, float gain, float gamma, float4 lo, float4 hi) {
+                                        int history, int cursor, int row0, float gain, float3 lo, float3 hi,
+                                        float3 sep, int units_per_head) {
   const int u = blockIdx.x * blockDim.x + threadIdx.x;
   if (u >= units) return;
-  const float v = fabsf(values[u]) * gain;
-  float t = v / (1.f + v);                 // soft clip to [0, 1)
-  t = powf(t, gamma);
-  float* px = image + (static_cast<long long>(u) * history + cursor) * 4;
-  px[0] = srgb_to_linear(lo.x + (hi.x - lo.x) * t);
-  px[1] = srgb_to_linear(lo.y + (hi.y - lo.y) * t);
-  px[2] = srgb_to_linear(lo.z + (hi.z - lo.z) * t);
-  px[3] = 1.f;
+  const float v = fmaxf(values[u], 0.f);
+  const float sc = v * gain;
+  const float mag = sc / (sc + 0.35f);
+  const float mask = v / (v + 0.004f);
+  const float t = powf(mag * mask, 1.15f);
+  float r = (lo.x + (hi.x - lo.x) * t) * t, g = (lo.y + (hi.y - lo.y) * t) * t, b = (lo.z + (hi.z - lo.z) * t) * t;
+  if (units_per_head > 0 && u > 0 && u % units_per_head == 0) {
+    r = fmaxf(r, sep.x); g = fmaxf(g, sep.y); b = fmaxf(b, sep.z);
+  }
+  float* px = image + (static_cast<long long>(row0 + u) * history + cursor) * 4;
+  px[0] = r; px[1] = g; px[2] = b; px[3] = 1.f;
 }
 
 // RoPE table row for graph-captured decoding: table[2i] = cos, table[2i+1] = sin (fp16) of
@@ -271,11 +275,13 @@ extern "C" int bdh_sample_tokens(const float* logits, long long* out, int B, int
 }
 
 extern "C" int bdh_viz_encode_units(const float* values, float* image, int units, int history, int cursor,
-                                    float gain, float gamma, const float* lo_rgb, const float* hi_rgb,
-                                    cudaStream_t s) {
-  if (units <= 0 || history <= 0 || cursor < 0 || cursor >= history) return BDH_ERR_ARGUMENT;
-  float4 lo = make_float4(lo_rgb[0], lo_rgb[1], lo_rgb[2], 1.f), hi = make_float4(hi_rgb[0], hi_rgb[1], hi_rgb[2], 1.f);
-  viz_encode_units_kernel<<<(units + 255) / 256, 256, 0, s>>>(values, image, units, history, cursor, gain, gamma, lo, hi);
+                                    int row0, float gain, const float* lo_rgb, const float* hi_rgb,
+                                    const float* sep_rgb, int units_per_head, cudaStream_t s) {
+  if (units <= 0 || history <= 0 || cursor < 0 || cursor >= history || row0 < 0) return BDH_ERR_ARGUMENT;
+  float3 lo = make_float3(lo_rgb[0], lo_rgb[1], lo_rgb[2]), hi = make_float3(hi_rgb[0], hi_rgb[1], hi_rgb[2]);
+  float3 sep = make_float3(sep_rgb[0], sep_rgb[1], sep_rgb[2]);
+  viz_encode_units_kernel<<<(units + 255) / 256, 256, 0, s>>>(values, image, units, history, cursor, row0, gain, lo,
+                                                              hi, sep, units_per_head);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 

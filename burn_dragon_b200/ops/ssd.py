@@ -1,0 +1,113 @@
+"""State-space duality (SSD) scan used by the Mamba-2 / Mamba-3 model paths.
+
+    h_t = exp(loga_t) * h_{t-1} + B_t (x) xw_t          h: [N, P] per (batch, head)
+    y_t = C_t . h_t                                      (the current input is included)
+
+`xw` is the input already multiplied by its step weight (dt for Mamba-2; the two trapezoidal
+weights for Mamba-3). B and C are shared by all heads of a group (one group here).
+
+Three statements of the same function: the literal recurrence (oracle), the chunked form in torch
+(differentiable; what training uses), and the CUDA chunk-scan kernels (forward; prefill / eval).
+The reference has no Mamba path; the spec is Mamba-2's SSD algorithm (Dao & Gu, 2024).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import native
+
+
+def ssd_sequential(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                   h0: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """xw [B,T,H,P], loga [B,T,H], Bm/Cm [B,T,N], h0 [B,H,N,P] -> (y [B,T,H,P], hT [B,H,N,P])."""
+    Bsz, T, H, P = xw.shape
+    N = Bm.shape[-1]
+    h = h0 if h0 is not None else torch.zeros(Bsz, H, N, P, dtype=xw.dtype, device=xw.device)
+    ys = []
+    for t in range(T):
+        h = h * torch.exp(loga[:, t]).view(Bsz, H, 1, 1) + Bm[:, t].view(Bsz, 1, N, 1) * xw[:, t].view(Bsz, H, 1, P)
+        ys.append(torch.einsum("bn,bhnp->bhp", Cm[:, t], h))
+    return torch.stack(ys, dim=1), h
+
+
+def ssd_chunked(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                h0: Optional[torch.Tensor] = None, chunk: int = 64) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same function, O(T*chunk) work per head: quadratic inside a chunk, state hand-off between."""
+    Bsz, T, H, P = xw.shape
+    N = Bm.shape[-1]
+    pad = (-T) % chunk
+    if pad:
+        xw = torch.nn.functional.pad(xw, (0, 0, 0, 0, 0, pad))
+        loga = torch.nn.functional.pad(loga, (0, 0, 0, pad))
+        Bm = torch.nn.functional.pad(Bm, (0, 0, 0, pad))
+        Cm = torch.nn.functional.pad(Cm, (0, 0, 0, pad))
+    Tp = T + pad
+    C = Tp // chunk
+    x_ = xw.view(Bsz, C, chunk, H, P)
+    a_ = loga.view(Bsz, C, chunk, H).permute(0, 3, 1, 2)              # [B,H,C,Q]
+    B_ = Bm.view(Bsz, C, chunk, N)
+    C_ = Cm.view(Bsz, C, chunk, N)
+    cum = torch.cumsum(a_, dim=-1)                                     # inclusive: sum_{r<=i} loga_r
+    # intra-chunk: y_i += sum_{j<=i} exp(cum_i - cum_j) (C_i . B_j) xw_j
+    diff = cum.unsqueeze(-1) - cum.unsqueeze(-2)                       # [B,H,C,Q,Q]  (i, j)
+    tri = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=xw.device))
+    L = torch.where(tri, torch.exp(diff.masked_fill(~tri, 0.0)), torch.zeros_like(diff))
+    CB = torch.einsum("bcin,bcjn->bcij", C_, B_)                       # [B,C,Q,Q]
+    y = torch.einsum("bhcij,bcij,bcjhp->bcihp", L, CB, x_)
+    # chunk states: S_c = sum_j exp(cum_last - cum_j) B_j (x) xw_j
+    decay_to_end = torch.exp(cum[..., -1:] - cum)                      # [B,H,C,Q]
+    S = torch.einsum("bhcj,bcjn,bcjhp->bchnp", decay_to_end, B_, x_)   # [B,C,H,N,P]
+    chunk_decay = torch.exp(cum[..., -1])                              # [B,H,C]
+    h = h0 if h0 is not None else torch.zeros(Bsz, H, N, P, dtype=xw.dtype, device=xw.device)
+    prev = []
+    for c in range(C):
+        prev.append(h)
+        h = h * chunk_decay[:, :, c].view(Bsz, H, 1, 1) + S[:, c]
+    prev = torch.stack(prev, dim=1)                                    # [B,C,H,N,P] state entering each chunk
+    # inter-chunk: y_i += exp(cum_i) C_i . prev
+    y = y + torch.einsum("bhci,bcin,bchnp->bcihp", torch.exp(cum), C_, prev)
+    y = y.reshape(Bsz, Tp, H, P)[:, :T]
+    if pad:
+        # the padded steps have loga = 0 and zero input, so the state after T is h unchanged
+        pass
+    return y, h
+
+
+def ssd_step(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+             h: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One decode step. xw [B,H,P], loga [B,H], Bm/Cm [B,N], h [B,H,N,P] (updated in place)."""
+    h.mul_(torch.exp(loga).view(*loga.shape, 1, 1)).add_(Bm.view(Bm.shape[0], 1, -1, 1) * xw.unsqueeze(2))
+    return torch.einsum("bn,bhnp->bhp", Cm, h), h
+
+
+def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
+    """Dispatch: CUDA chunk-scan kernels when no gradient is needed, else the torch chunked form."""
+    need_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (xw, loga, Bm, Cm))
+    if (xw.is_cuda and not need_grad and native.available() and hasattr(torch.ops.bdh, "ssd_chunk_scan")
+            and xw.shape[-1] == 64 and Bm.shape[-1] == 128 and chunk == 64):
+        return ssd_cuda(xw, loga, Bm, Cm, h0)
+    return ssd_chunked(xw, loga, Bm, Cm, h0, chunk)
+
+
+def ssd_cuda(xw, loga, Bm, Cm, h0=None):
+    Bsz, T, H, P = xw.shape
+    N = Bm.shape[-1]
+    chunk = 64
+    pad = (-T) % chunk
+    f = lambda t: t.float().contiguous()
+    if pad:
+        xw = torch.nn.functional.pad(xw, (0, 0, 0, 0, 0, pad))
+        loga = torch.nn.functional.pad(loga, (0, 0, 0, pad))
+        Bm = torch.nn.functional.pad(Bm, (0, 0, 0, pad))
+        Cm = torch.nn.functional.pad(Cm, (0, 0, 0, pad))
+    xw, loga, Bm, Cm = f(xw), f(loga), f(Bm), f(Cm)
+    Tp = T + pad
+    C = Tp // chunk
+    y = torch.empty(Bsz, Tp, H, P, device=xw.device, dtype=torch.float32)
+    states = torch.empty(Bsz, C, H, N, P, device=xw.device, dtype=torch.float32)   # scratch: per-chunk states
+    h = h0.float().clone().contiguous() if h0 is not None else torch.zeros(Bsz, H, N, P, device=xw.device)
+    decay = torch.empty(Bsz, C, H, device=xw.device, dtype=torch.float32)                 # scratch: per-chunk decay
+    native.ops.ssd_chunk_scan(xw, loga, Bm, Cm, h, states, decay, y)
+    return y[:, :T], h
