@@ -112,6 +112,12 @@ int bdh_bump_counter(int* counter, int by, cudaStream_t s);
 int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
                        float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s);
 
+// ---- block-ELL neuron graph (graph.cu) ------------------------------------------------------------
+// y[M, Ntot] = relu(x[M, D] . W[Ntot, D]^T - theta) touching only the 64x64 blocks listed in
+// ell_cols [ceil(Ntot/64), ell_width] (column-block indices, -1 padded).
+int bdh_graph_spmm_relu(const void* x_bf16, const void* w_bf16, const int* ell_cols, void* y_bf16, int M, int Ntot,
+                        int D, int ell_width, float theta, cudaStream_t s);
+
 // ---- NVLink collectives over symmetric memory (collectives.cu) --------------------------------
 // buf_ptrs / flag_ptrs: this process's mappings of every rank's data / flag buffer (world entries);
 // mc_ptr: NVSwitch multicast mapping of the data buffer or 0; n_floats % (4*world) == 0;
@@ -125,6 +131,8 @@ int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag_ptrs, long
                     const long long* shadow_ptrs, int rank, int world, long long n_floats, float* master,
                     float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, int step,
                     float grad_scale, unsigned epoch, int ctas, int* status, cudaStream_t s);
+// Device-side barrier over all ranks (bounded wait); uses slot 0 of the symmetric flag buffer.
+int bdh_rank_barrier(const long long* flag_ptrs, int rank, int world, unsigned epoch, int* status, cudaStream_t s);
 // Waits (at most limit_ns) for *flag to reach `value`; on expiry writes the timeout status and returns.
 int bdh_wait_timeout_probe(const unsigned* flag, unsigned value, unsigned long long limit_ns, int* status,
                            cudaStream_t s);

@@ -44,7 +44,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           const optional<Tensor>& in0, const optional<Tensor>& in1, at::IntArrayRef c_off,
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
-          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue) {
+          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -64,6 +64,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   d.status = status_word().data_ptr<int>();
   d.max_ctas = max_ctas;
   d.no_tma_epilogue = tma_epilogue ? 0 : 1;
+  if (mc_out != 0) d.out0 = reinterpret_cast<void*>(mc_out);   // multicast mapping of out0 (EPI_F_MC_RED)
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
 
@@ -228,6 +229,23 @@ void ssd_chunk_scan(const Tensor& xw, const Tensor& loga, const Tensor& Bm, cons
                               B, T, H, cur_stream()), "ssd_chunk_scan");
 }
 
+void graph_spmm_relu(const Tensor& x, const Tensor& w, const Tensor& ell, Tensor& y, double theta) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1) && x.is_contiguous() && w.is_contiguous());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && y.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(ell.scalar_type() == at::kInt && ell.is_contiguous() && ell.dim() == 2 && ell.size(0) == (w.size(0) + 63) / 64);
+  TORCH_CHECK(y.is_contiguous() && y.size(0) == x.size(0) && y.size(1) == w.size(0));
+  check_rc(bdh_graph_spmm_relu(x.data_ptr(), w.data_ptr(), ell.data_ptr<int>(), y.data_ptr(), x.size(0), w.size(0), x.size(1),
+                               ell.size(1), theta, cur_stream()), "graph_spmm_relu");
+}
+
+void rank_barrier(const Tensor& anchor, at::IntArrayRef flag_ptrs, int64_t rank, int64_t world, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  auto f = as_ptrs(flag_ptrs);
+  check_rc(bdh_rank_barrier(f.data(), rank, world, (unsigned)epoch, status_word().data_ptr<int>(), cur_stream()),
+           "rank_barrier");
+}
+
 void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
   c10::cuda::CUDAGuard guard(flag.device());
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
@@ -242,7 +260,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out) -> ()");
   m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
   m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
@@ -259,6 +277,8 @@ TORCH_LIBRARY(bdh, m) {
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
+  m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
+  m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
         "Tensor(d!) y) -> ()");
   m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
@@ -283,6 +303,8 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
+  m.impl("rank_barrier", &rank_barrier);
+  m.impl("graph_spmm_relu", &graph_spmm_relu);
   m.impl("ssd_chunk_scan", &ssd_chunk_scan);
   m.impl("decode_state_update", &decode_state_update);
   m.impl("sample_tokens", &sample_tokens);

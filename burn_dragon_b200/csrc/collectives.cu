@@ -162,6 +162,12 @@ rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, 
   cta_barrier_all_ranks(p, 2 * epoch + 2, status);
 }
 
+// All ranks meet here (one CTA per rank): everything each rank launched before it on the stream is
+// complete and visible to the others when it returns.
+__global__ void rank_barrier_kernel(CollPeers p, uint32_t epoch, int* status) {
+  cta_barrier_all_ranks(p, 2 * epoch + 1, status);
+}
+
 // Test hook for the bounded wait: waits on a flag slot that nothing writes, with a short limit,
 // and reports the timeout through the status word. Touches no peer memory.
 __global__ void wait_timeout_probe_kernel(const uint32_t* flag, uint32_t value, unsigned long long limit_ns,
@@ -213,6 +219,15 @@ extern "C" int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag
   AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
              grad_scale};
   rs_adamw_ag_kernel<<<ctas, COLL_THREADS, 0, s>>>(p, q, master, m, v, n_floats / 4, a, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
+extern "C" int bdh_rank_barrier(const long long* flag_ptrs, int rank, int world, unsigned epoch, int* status,
+                                cudaStream_t s) {
+  if (world < 1 || world > COLL_MAX_RANKS) return BDH_ERR_ARGUMENT;
+  CollPeers p;
+  fill_peers(p, flag_ptrs, flag_ptrs, 0, rank, world);
+  rank_barrier_kernel<<<1, 32, 0, s>>>(p, epoch, status);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 

@@ -41,6 +41,8 @@ enum EpiFlags : int {
   EPI_F_UPPER = 16,        // EPI_CAUSAL: write only s > t (else: write everything, zero where s >= t)
   EPI_F_NO_OUT0 = 32,      // EPI_RELU_GATE: skip storing y
   EPI_F_TABLE = 128,       // rotary (cos, sin) come from an fp16-pair table [T, n_per_head] instead of sincos
+  EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
+                           // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
 };
 
 struct OperandOffsets {
@@ -193,7 +195,7 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // memory and moved with TMA; the others (fp32 / accumulate / PoPE layout / partial upper writes)
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
-  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM));
+  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED));
   if (epi == EPI_RELU) return !(flags & EPI_F_POPE);
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -356,7 +358,22 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
   if constexpr (EPI == EPI_STORE) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] *= e.alpha;
-    if (e.flags & EPI_F_OUT_F32) {
+    if (e.flags & EPI_F_MC_RED) {
+      // partial sums of all ranks meet in the switch: one reduction-add per 16 bytes, no local read
+      float* p = static_cast<float*>(e.out0) + r * e.ld_out0 + c;
+      if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + 4 * i),
+                       "f"(v[4 * i]), "f"(v[4 * i + 1]), "f"(v[4 * i + 2]), "f"(v[4 * i + 3])
+                       : "memory");
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < valid)
+            asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
+      }
+    } else if (e.flags & EPI_F_OUT_F32) {
       store_f32_32(static_cast<float*>(e.out0), e.ld_out0, r, c, v, valid, e.flags & EPI_F_ACCUM);
     } else {
       if (e.flags & EPI_F_ACCUM) {

@@ -72,6 +72,7 @@ class _Dims:
 
     def __init__(self, model, B, T):
         self._table = None
+        self.comm = None           # set by the neuron-sharded tensor-parallel wrapper
         c = model.config
         self.B, self.T, self.M = B, T, B * T
         self.D, self.H, self.N = c.n_embd, c.n_head, c.latent_per_head
@@ -90,6 +91,9 @@ class _Dims:
         else:
             self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
+        hook = getattr(model, "_dims_hook", None)
+        if hook is not None:
+            hook(self)
 
 
 def _bf16(rows, cols, dev):
@@ -119,14 +123,27 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     S = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)   # tiles above the diagonal stay zero
     G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
            epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
-    a = _bf16(H * M, D, dev)
-    G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
-           c_off=(M, T, 0, 0), causal_k=1, out0=a)
-    if rho_in is not None:
-        # carry-in (no decay): a += q . rho_in
-        rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
-        G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
-               c_off=(M, T, 0, 0), flags=G.F_ACCUM, out0=a)
+    comm = d.comm
+    if comm is None:
+        a = _bf16(H * M, D, dev)
+        G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
+               c_off=(M, T, 0, 0), causal_k=1, out0=a)
+        if rho_in is not None:
+            # carry-in (no decay): a += q . rho_in
+            rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
+            G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
+                   c_off=(M, T, 0, 0), flags=G.F_ACCUM, out0=a)
+    else:
+        # neuron-sharded: this rank's scores cover its slice of the neurons, so S V is a partial sum;
+        # the GEMM epilogue adds it into every rank's replica through the switch
+        buf = comm.begin("a", H * M, D)
+        G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
+               c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, mc_out=buf.mc)
+        if rho_in is not None:
+            rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
+            G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
+                   c_off=(M, T, 0, 0), flags=comm.flags, out0=buf.view, mc_out=buf.mc)
+        a = comm.end(buf).to(torch.bfloat16)
     rho_out = None
     if want_rho:
         rho_out = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
@@ -147,8 +164,13 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     xy = _bf16(M, d.HN, dev)
     G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
            c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta)
-    mlp = _bf16(M, D, dev)
-    G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
+    if comm is None:
+        mlp = _bf16(M, D, dev)
+        G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
+    else:
+        buf = comm.begin("mlp", M, D)
+        G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, flags=comm.flags, out0=buf.view, mc_out=buf.mc)
+        mlp = comm.end(buf).to(torch.bfloat16)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
     saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp)
@@ -172,9 +194,16 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     # y = relu(LN(a) E_v)
     G.gemm(dy, lna, M=N, N=D, K=M, a_mn=True, b_mn=True, nz=(H, 1), a_off=(N, 0, 0, 0), b_off=(0, 0, M, 0),
            c_off=(N, 0, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder_v"])
-    dlna = _bf16(H * M, D, dev)
-    G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
-           c_off=(M, 0, 0, 0), out0=dlna)
+    comm = d.comm
+    if comm is None:
+        dlna = _bf16(H * M, D, dev)
+        G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
+               c_off=(M, 0, 0, 0), out0=dlna)
+    else:
+        buf = comm.begin("dlna", H * M, D)
+        G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
+               c_off=(M, 0, 0, 0), flags=comm.flags, out0=buf.view, mc_out=buf.mc)
+        dlna = comm.end(buf).to(torch.bfloat16)
     del dy
     da = _bf16(H * M, D, dev)
     ops.layernorm_bwd(a, dlna, da, False)
@@ -185,9 +214,14 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
            epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
     # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h ; heads run as separate launches
+    if comm is None:
+        part, pflags, pmc = dcur, G.F_OUT_F32 | G.F_ACCUM, 0
+    else:
+        pbuf = comm.begin("dcur", M, D)        # partial sums over the neuron shards: dV and the encoder path
+        part, pflags, pmc = pbuf.view, comm.flags, pbuf.mc
     for h in range(H):
         G.gemm(S[h * T:], da[h * M:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),
-               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=dcur)
+               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=pflags, out0=part, mc_out=pmc)
     # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
     dx = _bf16(M, d.HN, dev)
     if d.rot == "pope":
@@ -208,7 +242,9 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
                in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     del dxg
     G.gemm(dx, cur, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder"])
-    G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=dcur)
+    G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=pflags, out0=part, mc_out=pmc)
+    if comm is not None:
+        dcur += comm.end(pbuf)
     return dcur
 
 

@@ -20,7 +20,7 @@ import torch
 from . import native
 
 EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
-F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE = 1, 2, 4, 8, 16, 32, 128
+F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED = 1, 2, 4, 8, 16, 32, 128, 256
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -49,12 +49,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          o1_off: Sequence[int] = (0, 0, 0), alpha: float = 1.0, theta: float = 0.0, T: int = 1, pos0: int = 0,
          n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
-         tma_epilogue: bool = True) -> None:
+         tma_epilogue: bool = True, mc_out: int = 0) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
-                       slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue)
+                       slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out))
 
 
 # ------------------------------------------------------------------------------------------------
@@ -94,7 +94,7 @@ def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) ->
 def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0, 0, 0, 0), b_off=(0, 0, 0, 0),
                    epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
                    o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
-                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True) -> None:
+                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True, mc_out=0) -> None:
     """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
     dev = a.device
     for z1 in range(nz[1]):

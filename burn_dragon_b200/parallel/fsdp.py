@@ -1,0 +1,130 @@
+"""Sharded data parallelism (ZeRO / FSDP style) for the BDH stack.
+
+Every rank computes full local gradients into a symmetric fp32 buffer. One kernel per step then
+(`csrc/collectives.cu: rs_adamw_ag`) reduce-scatters the gradients over NVLink (peer loads or
+multimem.ld_reduce), applies AdamW to the 1/world slice of fp32 master weights and moments this
+rank owns, and writes the refreshed bf16 parameters into every rank's symmetric parameter buffer -
+so gradients, master weights and both moments are sharded, and the only replicated thing is the
+bf16 working copy the GEMMs read. The NCCL-only baseline (`fused=False`) does the same with
+`reduce_scatter_tensor` + the local AdamW kernel + `all_gather_into_tensor`.
+
+The reference is single-device (src/bin/train.rs:395); nothing here has a counterpart there.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..engine.optim import FlatParams
+from ..ops import native
+
+
+class _ShardedOptimizerFacade:
+    """What checkpointing needs from an optimizer: logical (unsharded) state in, logical state out."""
+
+    def __init__(self, owner):
+        self.owner = owner
+
+    @property
+    def step_count(self):
+        return self.owner.step_count
+
+    def logical_state_dict(self) -> Dict:
+        o = self.owner
+        return dict(step=o.step_count, m=o._gather(o.m), v=o._gather(o.v), names=o.flat.names,
+                    offsets=o.flat.offsets, numel=o.flat.numel)
+
+    def load_logical_state_dict(self, sd: Dict) -> None:
+        o = self.owner
+        o.step_count = int(sd["step"])
+        o.m.copy_(sd["m"][o.lo:o.hi].to(o.m.device))
+        o.v.copy_(sd["v"][o.lo:o.hi].to(o.v.device))
+
+
+class FSDP:
+    def __init__(self, model, lr=1e-3, weight_decay=0.1, beta1=0.9, beta2=0.999, eps=1e-5, fused: bool = True,
+                 group=None):
+        self.model, self.group = model, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.lr, self.weight_decay, self.beta1, self.beta2, self.eps = lr, weight_decay, beta1, beta2, eps
+        self.flat = FlatParams(model, shadow_bf16=True, align=64)
+        dist.broadcast(self.flat.master, src=0, group=group)
+        self.step_count = 0
+        n = self.flat.numel
+        self.pad = (-n) % (4 * self.world)
+        self.numel = n + self.pad
+        per = self.numel // self.world
+        self.lo, self.hi = per * self.rank, (self.numel if self.rank == self.world - 1 else per * (self.rank + 1))
+        dev = self.flat.master.device
+        self.fused = bool(fused and dev.type == "cuda" and native.available())
+        self.sharded = None
+        if self.fused:
+            try:
+                from . import symm
+                self.sharded = symm.ShardedAdamW(self.flat.master, group, lr, weight_decay, beta1, beta2, eps)
+                # gradients and the bf16 working copy now live in symmetric memory
+                self.flat.grad = self.sharded.grad[:n]
+                self.flat.shadow = self.sharded.shadow[:n]
+                self.flat.zero_grad()
+                self.flat.register_shadow()
+                self.master, self.m, self.v = self.sharded.master, self.sharded.m, self.sharded.v
+            except Exception as e:  # noqa: BLE001 - recorded; the NCCL path is used instead
+                self.fallback_reason = repr(e)
+                self.fused = False
+        if not self.fused:
+            full = torch.zeros(self.numel, dtype=torch.float32, device=dev)
+            full[:n].copy_(self.flat.master)
+            self.master = full[self.lo:self.hi].clone()
+            self.m, self.v = torch.zeros_like(self.master), torch.zeros_like(self.master)
+            self._grad_pad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
+            self._shard_grad = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
+            self.flat.refresh_shadow()
+        self.optimizer = _ShardedOptimizerFacade(self)
+
+    # ---- step -----------------------------------------------------------------------------------
+    def train_step(self, tokens, targets, lr: Optional[float] = None) -> torch.Tensor:
+        self.flat.zero_grad()
+        loss = self.model(tokens, targets)
+        loss.backward()
+        self.step_count += 1
+        lr = self.lr if lr is None else lr
+        if self.fused:
+            self.sharded.step(lr)
+            return loss.detach()
+        # NCCL baseline: reduce-scatter, local AdamW on the shard, all-gather of fp32 then cast
+        n = self.flat.numel
+        self._grad_pad[:n].copy_(self.flat.grad)
+        per = self.numel // self.world
+        if (self.numel % self.world) == 0 and dist.get_backend(self.group) == "nccl":
+            dist.reduce_scatter_tensor(self._shard_grad, self._grad_pad, group=self.group)
+        else:
+            dist.all_reduce(self._grad_pad, group=self.group)
+            self._shard_grad.copy_(self._grad_pad[self.lo:self.hi])
+        g = self._shard_grad / self.world
+        self.m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
+        self.v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
+        bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count
+        self.master.mul_(1 - lr * self.weight_decay)
+        self.master.addcdiv_(self.m / bc1, (self.v / bc2).sqrt_().add_(self.eps), value=-lr)
+        full = self._gather(self.master)
+        self.flat.master.copy_(full[:n])
+        self.flat.refresh_shadow()
+        return loss.detach()
+
+    # ---- logical (unsharded) views --------------------------------------------------------------------
+    def _gather(self, shard: torch.Tensor) -> torch.Tensor:
+        # the padded length is a multiple of the world size, so every rank's slice has the same length
+        parts = [torch.empty_like(shard) for _ in range(self.world)]
+        dist.all_gather(parts, shard.contiguous(), group=self.group)
+        return torch.cat(parts)
+
+    def sync_params(self) -> None:
+        """Bring the module's fp32 parameters up to date with the sharded master weights."""
+        full = self._gather(self.master)
+        self.flat.master.copy_(full[:self.flat.numel])
+
+    def gather_state_dict(self) -> Dict[str, torch.Tensor]:
+        self.sync_params()
+        return {k: v.detach().cpu().clone() for k, v in self.model.state_dict().items()}

@@ -22,3 +22,13 @@ def test_ddp_equals_single_gpu(case):
 
 def test_rank_exit_detected_without_gpu_fault():
     run_ranks("rank_exit", cpu=False, env={"NCCL_NVLS_ENABLE": "0", "BDH_NO_MULTIMEM": "1"})
+
+
+def test_fsdp_sharded_optimizer_equals_single_gpu():
+    out = run_ranks("fsdp", cpu=False)
+    assert "fused=True" in out
+
+
+def test_neuron_tensor_parallel_equals_single_gpu():
+    out = run_ranks("tp", cpu=False, timeout=600)
+    assert "rope:fused" in out

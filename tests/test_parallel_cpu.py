@@ -27,3 +27,7 @@ def test_ddp_equals_single_process_gloo():
 
 def test_rank_exit_is_detected_on_host():
     run_ranks("rank_exit")
+
+
+def test_fsdp_host_logic_gloo():
+    run_ranks("fsdp")
