@@ -200,3 +200,64 @@ extern "C" int bdh_ssd_chunk_scan(const float* xw, const float* loga, const floa
   ssd_chunk_out_kernel<<<grid, SSD_THREADS, smem_c, s>>>(xw, loga, Bm, Cm, states, y, T, H);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant: the per-chunk scratch is a fixed array owned by the library.
+// ------------------------------------------------------------------------------------------------
+#include "bdh_static_scratch.h"
+
+#include <mutex>
+#include <stdio.h>
+
+namespace {
+
+constexpr long long STATIC_STATE_FLOATS =
+    static_cast<long long>(BDH_SSD_STATIC_MAX_CHUNK_HEADS) * bdh::SSD_N * bdh::SSD_P;
+constexpr long long STATIC_TOTAL_FLOATS = STATIC_STATE_FLOATS + BDH_SSD_STATIC_MAX_CHUNK_HEADS;
+
+// In host code this name is only a handle for the runtime; its device address is obtained below.
+static __device__ __align__(256) float g_ssd_static_scratch[STATIC_TOTAL_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[MAX_DEVICES] = {};
+
+// Device address of the scratch array on the current device, resolved once per device.
+int static_scratch_ptr(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return BDH_ERR_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t rc = cudaGetSymbolAddress(&p, g_ssd_static_scratch);
+    if (rc != cudaSuccess || !p) {
+      fprintf(stderr, "bdh_ssd_chunk_scan_static: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(rc));
+      return BDH_ERR_DRIVER;
+    }
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return BDH_OK;
+}
+
+}  // namespace
+
+extern "C" int bdh_ssd_chunk_scan_static(const float* xw, const float* loga, const float* Bm, const float* Cm,
+                                         float* h, float* y, int B, int T, int H, cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || T <= 0 || (T % bdh::SSD_Q)) return BDH_ERR_ARGUMENT;
+  const long long chunk_heads = static_cast<long long>(B) * (T / bdh::SSD_Q) * H;
+  if (chunk_heads > BDH_SSD_STATIC_MAX_CHUNK_HEADS) {
+    fprintf(stderr,
+            "bdh_ssd_chunk_scan_static: B*(T/64)*H = %lld exceeds the built-in scratch for %d chunk-heads; "
+            "use bdh_ssd_chunk_scan with caller-provided scratch\n",
+            chunk_heads, BDH_SSD_STATIC_MAX_CHUNK_HEADS);
+    return BDH_ERR_TOO_LARGE;
+  }
+  float* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != BDH_OK) return rc;
+  float* states = scratch;                          // [B, T/64, H, 128, 64]
+  float* decay = scratch + STATIC_STATE_FLOATS;     // [B, T/64, H]
+  return bdh_ssd_chunk_scan(xw, loga, Bm, Cm, h, states, decay, y, B, T, H, stream);
+}
