@@ -84,7 +84,15 @@ def ssd_step(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.T
 
 def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
     """Dispatch: CUDA chunk-scan kernels when no gradient is needed, else the torch chunked form."""
+    ct = torch.promote_types(torch.promote_types(xw.dtype, loga.dtype), torch.promote_types(Bm.dtype, Cm.dtype))
+    xw, loga, Bm, Cm = xw.to(ct), loga.to(ct), Bm.to(ct), Cm.to(ct)
+    if h0 is not None:
+        h0 = h0.to(ct)
     need_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (xw, loga, Bm, Cm))
+    if xw.shape[1] == 1 and h0 is not None and not need_grad:
+        # single-token decode: one recurrence step on a private copy of the state
+        y, h = ssd_step(xw[:, 0], loga[:, 0], Bm[:, 0], Cm[:, 0], h0.clone())
+        return y.unsqueeze(1), h
     if (xw.is_cuda and not need_grad and native.available() and hasattr(torch.ops.bdh, "ssd_chunk_scan")
             and xw.shape[-1] == 64 and Bm.shape[-1] == 128 and chunk == 64):
         return ssd_cuda(xw, loga, Bm, Cm, h0)
