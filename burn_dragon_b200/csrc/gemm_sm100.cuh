@@ -41,6 +41,7 @@ enum EpiFlags : int {
   EPI_F_UPPER = 16,        // EPI_CAUSAL: write only s > t (else: write everything, zero where s >= t)
   EPI_F_NO_OUT0 = 32,      // EPI_RELU_GATE: skip storing y
   EPI_F_TABLE = 128,       // rotary (cos, sin) come from an fp16-pair table [T, n_per_head] instead of sincos
+  EPI_F_ATOMIC = 512,      // EPI_STORE fp32: out0 += tile with red.global.add (split-K partial sums)
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
 };
@@ -195,7 +196,7 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // memory and moved with TMA; the others (fp32 / accumulate / PoPE layout / partial upper writes)
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
-  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED));
+  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC));
   if (epi == EPI_RELU) return !(flags & EPI_F_POPE);
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -373,6 +374,19 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
           if (i < valid)
             asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
       }
+    } else if (e.flags & EPI_F_ATOMIC) {
+      float* p = static_cast<float*>(e.out0) + r * e.ld_out0 + c;
+      if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + 4 * i), "f"(v[4 * i]),
+                       "f"(v[4 * i + 1]), "f"(v[4 * i + 2]), "f"(v[4 * i + 3])
+                       : "memory");
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < valid) atomicAdd(p + i, v[i]);
+      }
     } else if (e.flags & EPI_F_OUT_F32) {
       store_f32_32(static_cast<float*>(e.out0), e.ld_out0, r, c, v, valid, e.flags & EPI_F_ACCUM);
     } else {
@@ -412,6 +426,13 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
       if (n + 31 <= m) return;  // nothing above the diagonal in this chunk
       const float slope = e.slopes ? __ldg(e.slopes + z0) : 0.f;
       bf* p = static_cast<bf*>(e.out0) + r * e.ld_out0 + c;
+      if (n > m && valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+        // the whole chunk lies above the diagonal: vector stores
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= e.alpha * __expf(-slope * static_cast<float>(n + i - m));
+        store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, v, valid);
+        return;
+      }
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         int s = n + i;

@@ -107,6 +107,9 @@ def bench_reference_shapes(steps: int, warmup: int) -> Dict:
         ms = _timed(lambda: tr.train_step(b[:, :-1], b[:, 1:]), steps, max(3, warmup))
         out["train"][name] = dict(ms_per_step=ms, sequences_per_s=B / ms * 1e3, tokens_per_s=B * T / ms * 1e3)
     m = BDH(BDHConfig(dropout=0.0)).to(dev).eval()
+    if dev.type == "cuda":
+        from . import decode_engine as DE
+        DE.attach(m)
     for P, n in ((128, 8), (512, 16), (1024, 16)):
         toks = torch.randint(0, 256, (1, P), device=dev)
         s = GEN.GenerationSettings(n, 1.0, None, seed=0)

@@ -25,8 +25,7 @@ class DecodeEngine:
         self.model = model
         self.use_graph = use_graph
         self.split_k = split_k
-        self._graph = None
-        self._graph_key = None
+        self._cache = {}       # (streams, device, sampling settings) -> buffers, state storage, captured graph
 
     # ---- eligibility ---------------------------------------------------------------------------
     def can_run(self, toks: torch.Tensor, settings) -> bool:
@@ -121,39 +120,52 @@ class DecodeEngine:
         B, P = toks.shape
         state, last = GEN.prefill_state(model, toks, dev)
         c = model.config
-        rho = []
-        for ls in state.layers:
-            r = ls.rho
-            if r is None:
-                r = torch.zeros(B, c.n_head, c.state_latent, c.n_embd, device=dev)
-            rho.append(r.float().contiguous())
-        buf = self._alloc(B, dev)
+        seed = int(settings.seed if settings.seed is not None else torch.initial_seed() & 0x7FFFFFFF) & 0xFFFFFFFF
+        key = (B, str(dev), float(settings.temperature), int(settings.top_k or 0), bool(settings.greedy), seed)
+        ctx = self._cache.get(key)
+        if ctx is None:
+            buf = self._alloc(B, dev)
+            rho = [torch.zeros(B, c.n_head, c.state_latent, c.n_embd, device=dev) for _ in range(c.n_layer)]
+            ctx = dict(buf=buf, rho=rho, graph=None)
+            self._cache.clear()            # one resident configuration: the state buffers are large
+            self._cache[key] = ctx
+        buf, rho = ctx["buf"], ctx["rho"]
         d = buf["d"]
         W = _weights(model)
-        buf["logits"].copy_(last.float())
-        buf["pos"].fill_(state.position)
-        seed = int(settings.seed if settings.seed is not None else torch.initial_seed() & 0x7FFFFFFF) & 0xFFFFFFFF
+
+        def load_state():
+            for r, ls in zip(rho, state.layers):
+                if ls.rho is None:
+                    r.zero_()
+                else:
+                    r.copy_(ls.rho)
+            buf["logits"].copy_(last.float())
+            buf["pos"].fill_(state.position)
+            buf["step"].zero_()
+
+        load_state()
         graph_ok = self.use_graph and d.rot != "pope"
         out = [toks]
         n = int(settings.max_new_tokens)
         if graph_ok:
-            # warm up once on a side stream (allocations, lazy initialisation), rewind, then capture
-            snap = [r.clone() for r in rho]
-            logits0 = buf["logits"].clone()
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._step(buf, W, rho, settings, seed, None)
-            torch.cuda.current_stream().wait_stream(s)
-            for r, r0 in zip(rho, snap):
-                r.copy_(r0)
-            del snap
-            buf["logits"].copy_(logits0)
-            buf["pos"].fill_(state.position)
-            buf["step"].zero_()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._step(buf, W, rho, settings, seed, None)
+            if ctx["graph"] is None:
+                # warm up once on a side stream (lazy initialisation, allocator), rewind, then capture
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._step(buf, W, rho, settings, seed, None)
+                torch.cuda.current_stream().wait_stream(s)
+                load_state()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._step(buf, W, rho, settings, seed, None)
+                ctx["graph"], ctx["weights"] = graph, W
+                load_state()
+            elif any(ctx["weights"][k].data_ptr() != W[k].data_ptr() for k in W):
+                # the captured graph reads the weight buffers it was captured with
+                for k in W:
+                    ctx["weights"][k].copy_(W[k])
+            graph = ctx["graph"]
             for _ in range(n):
                 graph.replay()
                 t = buf["tok"].clone()
@@ -167,8 +179,6 @@ class DecodeEngine:
                 out.append(t.view(-1, 1))
                 if on_token is not None:
                     on_token(t)
-        # the last sampled token has been consumed by the model inside the step that followed it,
-        # except for the final one: logits for it sit in buf["logits"]; expose state for callers
         for ls, r in zip(state.layers, rho):
             ls.rho = r
         state.position += n

@@ -96,6 +96,27 @@ class _Dims:
             hook(self)
 
 
+_SM_COUNT = {}
+
+
+def _split_k(tiles: int, K: int, dev) -> int:
+    """Split factor for a GEMM with few output tiles and a long K: the persistent kernel runs one
+    CTA per SM, so `tiles` that are not close to a multiple of the SM count leave SMs idle in the
+    last wave. Splitting K multiplies the tile count; partial sums meet through fp32 atomics."""
+    sms = _SM_COUNT.get(dev)
+    if sms is None:
+        sms = _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    best, best_eff = 1, tiles / (-(-tiles // sms) * sms)
+    for s in (2, 3, 4, 6, 8):
+        if K % (s * 64) or K // s < 1024:
+            continue
+        t = tiles * s
+        eff = t / (-(-t // sms) * sms)
+        if eff > best_eff + 0.03:
+            best, best_eff = s, eff
+    return best
+
+
 def _bf16(rows, cols, dev):
     return torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
 
@@ -165,8 +186,16 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
            c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta)
     if comm is None:
-        mlp = _bf16(M, D, dev)
-        G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
+        sk = _split_k(-(-M // 128) * -(-D // 256), d.HN, dev)
+        if sk > 1:
+            mlp32 = torch.zeros(M, D, device=dev, dtype=torch.float32)
+            ks = d.HN // sk
+            G.gemm(xy, W["decoder"], M=M, N=D, K=ks, b_mn=True, nz=(sk, 1), a_off=(0, 0, ks, 0), b_off=(0, 0, ks, 0),
+                   flags=G.F_OUT_F32 | G.F_ATOMIC, out0=mlp32)
+            mlp = mlp32.to(torch.bfloat16)
+        else:
+            mlp = _bf16(M, D, dev)
+            G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
     else:
         buf = comm.begin("mlp", M, D)
         G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, flags=comm.flags, out0=buf.view, mc_out=buf.mc)
@@ -190,10 +219,15 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     dy = _bf16(M, d.HN, dev)
     dxg = _bf16(M, d.HN, dev)
     G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg)
-    G.gemm(xy, dmlp, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["decoder"])
+    wtiles = -(-d.HN // 128) * -(-D // 256)
+    sk = _split_k(wtiles, M, dev)
+    wflags = G.F_OUT_F32 | (G.F_ATOMIC if sk > 1 else G.F_ACCUM)
+    km = M // sk
+    G.gemm(xy, dmlp, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
+           flags=wflags, out0=grads["decoder"])
     # y = relu(LN(a) E_v)
-    G.gemm(dy, lna, M=N, N=D, K=M, a_mn=True, b_mn=True, nz=(H, 1), a_off=(N, 0, 0, 0), b_off=(0, 0, M, 0),
-           c_off=(N, 0, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder_v"])
+    G.gemm(dy, lna, M=N, N=D, K=km, a_mn=True, b_mn=True, nz=(H, sk), a_off=(N, 0, 0, km), b_off=(0, 0, M, km),
+           c_off=(N, 0, 0, 0), flags=wflags, out0=grads["encoder_v"])
     comm = d.comm
     if comm is None:
         dlna = _bf16(H * M, D, dev)
@@ -241,8 +275,15 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
                c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=(G.F_ROPE | G.F_TABLE) if rope else 0, in0=dxg,
                in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     del dxg
-    G.gemm(dx, cur, M=d.HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM, out0=grads["encoder"])
-    G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=pflags, out0=part, mc_out=pmc)
+    G.gemm(dx, cur, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
+           flags=wflags, out0=grads["encoder"])
+    if comm is None:
+        sk2 = _split_k(-(-M // 128) * -(-D // 256), d.HN, dev)
+        k2 = d.HN // sk2
+        G.gemm(dx, W["encoder"], M=M, N=D, K=k2, b_mn=True, nz=(sk2, 1), a_off=(0, 0, k2, 0), b_off=(0, 0, k2, 0),
+               flags=G.F_OUT_F32 | (G.F_ATOMIC if sk2 > 1 else G.F_ACCUM), out0=part)
+    else:
+        G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=pflags, out0=part, mc_out=pmc)
     if comm is not None:
         dcur += comm.end(pbuf)
     return dcur

@@ -20,7 +20,7 @@ import torch
 from . import native
 
 EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
-F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED = 1, 2, 4, 8, 16, 32, 128, 256
+F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED, F_ATOMIC = 1, 2, 4, 8, 16, 32, 128, 256, 512
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -116,7 +116,7 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
             nn = torch.arange(N, device=dev)
             if epi == EPI_STORE:
                 v = acc * alpha
-                if flags & F_ACCUM:
+                if flags & (F_ACCUM | F_ATOMIC):
                     v = v + out0[rs, cs].float()
                 out0[rs, cs] = v.to(out0.dtype)
             elif epi == EPI_RELU:
