@@ -296,24 +296,29 @@ __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, i
     if (e.flags & EPI_F_ROPE) {
       // q = R(pos) x  =>  dx = R(pos)^T dq
       const bool table = e.flags & EPI_F_TABLE;
-      const float pos = static_cast<float>(e.pos0 + (m % e.T));
-      float fr[16];
-      if (!table) load_pair_freqs(e.freqs, n % e.n_per_head, fr);
+      if (table) {
+        // branch-free: four FMAs per pair are cheaper than a divergent skip
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const bool closed = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) && ((r0[i] >> 16) == BF16_NEG_ZERO);
-        if (!closed) {
-          float s, co;
-          if (table) {
-            float2 cs = unpack_f16x2(r1[i]);
-            co = cs.x;
-            s = cs.y;
-          } else {
+        for (int i = 0; i < 16; ++i) {
+          const float2 cs = unpack_f16x2(r1[i]);
+          const float a = acc[2 * i], b = acc[2 * i + 1];
+          acc[2 * i] = a * cs.x + b * cs.y;
+          acc[2 * i + 1] = b * cs.x - a * cs.y;
+        }
+      } else {
+        const float pos = static_cast<float>(e.pos0 + (m % e.T));
+        float fr[16];
+        load_pair_freqs(e.freqs, n % e.n_per_head, fr);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool closed = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) && ((r0[i] >> 16) == BF16_NEG_ZERO);
+          if (!closed) {
+            float s, co;
             rot_sincos(pos, fr[i], s, co);
+            float a = acc[2 * i], b = acc[2 * i + 1];
+            acc[2 * i] = a * co + b * s;
+            acc[2 * i + 1] = b * co - a * s;
           }
-          float a = acc[2 * i], b = acc[2 * i + 1];
-          acc[2 * i] = a * co + b * s;
-          acc[2 * i + 1] = b * co - a * s;
         }
       }
     }

@@ -1,0 +1,99 @@
+"""Small, self-terminating workloads for kernel profiling and roofline timing:
+
+    python -m burn_dragon_b200.engine.profile_cases --case dq_bwd [--launches 3] [--time]
+
+Each case launches one kernel of the BDH layer a few times on a reduced batch of the base
+configuration (8 sequences instead of 32: inputs still exceed the 126 MB L2, the device holds a few
+GB). With `--time` the case is timed with CUDA events (after warm-up, L2 flushed by the size of the
+working set) and a JSON line with achieved bytes/s and FLOP/s against the measured peaks is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from ..ops import gemm as G
+from ..ops import native
+
+B, T, H, N, D = 8, 512, 4, 8192, 256
+M, HN = B * T, H * N
+
+
+def _rnd(r, c, s=1.0):
+    return (torch.randn(r, c, device="cuda") * s).to(torch.bfloat16)
+
+
+def build(case: str):
+    """-> (callable, flops, algorithmic bytes)"""
+    cur, W = _rnd(M, D), _rnd(HN, D, 0.02)
+    x = torch.zeros(M, HN, device="cuda", dtype=torch.bfloat16)
+    q = torch.zeros_like(x)
+    act = _rnd(M, HN, 0.1).relu()
+    freqs = ((1.0 / (65536.0 ** (torch.arange(N, device="cuda").div(2, rounding_mode="floor") * 2 / N)))
+             / 6.283185307).float()[0::2].contiguous()
+    tab = G.rope_table(0, T, freqs)
+    S = _rnd(B * H * T, T, 0.1)
+    big = 2.0 * M * HN          # bytes of one [M, H*N] bf16 tensor
+    gemm_fl = 2.0 * M * HN * D
+    att_fl = 2.0 * B * H * T * T * N
+    cases = {
+        "enc_rope": (lambda: G.gemm(cur, W, M=M, N=HN, K=D, epi=G.EPI_RELU, flags=G.F_ROPE | G.F_TABLE, in0=tab,
+                                    out0=x, out1=q, T=T, n_per_head=N, freqs=freqs), gemm_fl, 2 * big),
+        "ygate": (lambda: G.gemm(cur, W, M=M, N=HN, K=D, epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=act, out1=q),
+                  gemm_fl, 2 * big),
+        "gate_bwd": (lambda: G.gemm(cur, W, M=M, N=HN, K=D, epi=G.EPI_GATE_BWD, in0=act, in1=act, out0=x, out1=q),
+                     gemm_fl, 4 * big),
+        "dq_bwd": (lambda: G.gemm(S, act, M=T, N=N, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0),
+                                  b_off=(N, 0, 0, T), c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD,
+                                  flags=G.F_ROPE | G.F_TABLE, in0=act, in1=tab, T=T, n_per_head=N, freqs=freqs,
+                                  out0=x), att_fl, 3 * big),
+        "scores": (lambda: G.gemm(act, act, M=T, N=T, K=N, nz=(H, B), a_off=(0, T, N, 0), b_off=(0, T, N, 0),
+                                  c_off=(T, H * T, 0, 0), epi=G.EPI_CAUSAL, causal_tiles=1, out0=S),
+                   att_fl / 2, big),
+        "decoder": (lambda: G.gemm(act, W, M=M, N=D, K=HN, b_mn=True, out0=cur), gemm_fl, big),
+        "wgrad": (lambda: G.gemm(act, cur, M=HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM,
+                                 out0=torch.zeros(HN, D, device="cuda")), gemm_fl, big),
+    }
+    return cases[case]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True)
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--time", action="store_true")
+    args = ap.parse_args()
+    native.load()
+    torch.manual_seed(0)
+    fn, flops, nbytes = build(args.case)
+    for _ in range(args.launches):
+        fn()
+    torch.cuda.synchronize()
+    assert native.status_code() == 0
+    if args.time:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for a, b in evs:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        ms = sorted(a.elapsed_time(b) for a, b in evs)[5]
+        peaks = {}
+        p = os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            peaks = json.load(open(p))
+        hbm, tf = peaks.get("hbm_gbs", 6650.0), peaks.get("bf16_tflops", 1590.0)
+        print(json.dumps(dict(case=args.case, ms=ms, gbs=nbytes / ms / 1e6, tflops=flops / ms / 1e9,
+                              frac_hbm=nbytes / ms / 1e6 / hbm, frac_tensor=flops / ms / 1e9 / tf,
+                              peaks="measured" if peaks else "fallback")))
+    else:
+        print("ok")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
