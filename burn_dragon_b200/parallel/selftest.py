@@ -137,7 +137,46 @@ def case_rank_exit(dev):
     return "detected"
 
 
-CASES = dict(allreduce=case_allreduce, sharded_adamw=case_sharded_adamw, ddp=case_ddp,
+def case_allreduce_bw(dev):
+    """Device-timed all-reduce of the BDH-base gradient buffer (25.3 M fp32 = 101 MB) and of 1 GiB:
+    this library's kernel against NCCL, max over ranks, with the NVLink roofline fraction
+    (bytes each GPU must send, 2*(W-1)/W * size, over 770 GB/s per direction)."""
+    import json
+    from . import symm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    out = {}
+    for name, n in (("bdh_base_grads", 25_297_920), ("1GiB", 1 << 28)):
+        n = n + (-n) % (4 * world)
+        ar = symm.SymmetricAllReduce(torch.empty(n, device=dev))
+        ar.tensor.normal_()
+        ref = torch.randn(n, device=dev)
+
+        def timed(fn, iters=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return dist_utils.max_over_ranks(e0.elapsed_time(e1) / iters, dev)
+
+        ms_f = timed(lambda: ar.all_reduce_(1.0 / world))
+        ms_n = timed(lambda: dist.all_reduce(ref))
+        sent = 2.0 * (world - 1) / world * n * 4
+        out[name] = dict(bytes=n * 4, fused_ms=ms_f, nccl_ms=ms_n, fused_busbw_gbs=sent / ms_f / 1e6,
+                         nccl_busbw_gbs=sent / ms_n / 1e6, fused_frac_of_770=sent / ms_f / 1e6 / 770.0)
+        mc = bool(ar.buf.multicast_ptr)
+        del ar
+    if rank == 0:
+        print("ALLREDUCE_BW " + json.dumps(dict(world=world, multicast=mc, results=out)), flush=True)
+    return ""
+
+
+CASES = dict(allreduce=case_allreduce, allreduce_bw=case_allreduce_bw, sharded_adamw=case_sharded_adamw, ddp=case_ddp,
              ddp_nccl=lambda d: case_ddp(d, fused=False), rank_exit=case_rank_exit)
 
 
