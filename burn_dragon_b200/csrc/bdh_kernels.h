@@ -47,6 +47,8 @@ typedef struct {
   int* status;   // device word that receives a STATUS_* code if an in-kernel wait gives up
   int max_ctas;  // 0: one CTA per SM
   int no_tma_epilogue;  // 1: force the per-thread global-memory epilogue
+  float drop_p;         // EPI_RELU_GATE: dropout probability on x*y
+  unsigned drop_seed;
 } BdhGemmDesc;
 
 int bdh_gemm_bf16(const BdhMat* A, int a_mn_major, const BdhMat* B, int b_mn_major,

@@ -44,7 +44,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           const optional<Tensor>& in0, const optional<Tensor>& in1, at::IntArrayRef c_off,
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
-          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out) {
+          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -64,6 +64,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   d.status = status_word().data_ptr<int>();
   d.max_ctas = max_ctas;
   d.no_tma_epilogue = tma_epilogue ? 0 : 1;
+  d.drop_p = drop_p; d.drop_seed = static_cast<unsigned>(drop_seed);
   if (mc_out != 0) d.out0 = reinterpret_cast<void*>(mc_out);   // multicast mapping of out0 (EPI_F_MC_RED)
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
@@ -260,7 +261,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed) -> ()");
   m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
   m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");

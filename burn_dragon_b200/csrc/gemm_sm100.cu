@@ -126,6 +126,7 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   e.T = d->T > 0 ? d->T : 1; e.pos0 = d->pos0;
   e.n_per_head = d->n_per_head > 0 ? d->n_per_head : 1;
   e.freqs = d->freqs; e.slopes = d->slopes; e.flags = d->flags;
+  e.drop_p = d->drop_p; e.drop_seed = d->drop_seed;
 
   const int max_ctas = d->max_ctas > 0 ? d->max_ctas : num_sms();
   const int key = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);

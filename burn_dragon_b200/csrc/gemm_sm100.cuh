@@ -68,6 +68,8 @@ struct EpiParams {
   const float* freqs;    // [n_per_head] cycles per position
   const float* slopes;   // [nz0] decay slope per z0 (nullptr: no decay)
   int flags;
+  float drop_p;          // EPI_RELU_GATE: dropout probability applied to x*y (0: off)
+  uint32_t drop_seed;    // EPI_RELU_GATE: seed of the counter-based dropout mask
 };
 
 struct GemmArgs {
@@ -221,6 +223,11 @@ __device__ __forceinline__ void rot_pair(const EpiParams& e, const uint32_t (&ta
   }
 }
 
+__device__ __forceinline__ uint32_t dropout_hash(uint32_t h) {
+  h ^= h >> 16; h *= 0x7feb352du; h ^= h >> 15; h *= 0x846ca68bu; h ^= h >> 16;
+  return h;
+}
+
 template <int EPI>
 __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, int n, float (&acc)[32],
                                             const uint32_t (&r0)[16], const uint32_t (&r1)[16],
@@ -268,6 +275,20 @@ __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, i
       o1[2 * i] = o0[2 * i] * x.x;
       o1[2 * i + 1] = o0[2 * i + 1] * x.y;
     }
+    if (e.drop_p > 0.f) {
+      // inverted dropout on x*y (reference: src/model/bdh.rs:380-381). One 32-bit hash of
+      // (seed, z0, row, column pair) gives two 16-bit uniforms; kept values are scaled by 1/(1-p).
+      const uint32_t thr = static_cast<uint32_t>(e.drop_p * 65536.f);
+      const float keep_scale = 1.f / (1.f - e.drop_p);
+      const uint32_t base = e.drop_seed ^ (static_cast<uint32_t>(m) * 0x9E3779B1u) ^
+                            (static_cast<uint32_t>(z0) * 0xC2B2AE3Du);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t h = dropout_hash(base ^ (static_cast<uint32_t>((n >> 1) + i) * 0x85EBCA77u));
+        o1[2 * i] = ((h & 0xFFFFu) >= thr) ? o1[2 * i] * keep_scale : 0.f;
+        o1[2 * i + 1] = ((h >> 16) >= thr) ? o1[2 * i + 1] * keep_scale : 0.f;
+      }
+    }
   } else if constexpr (EPI == EPI_CAUSAL) {
     const float slope = e.slopes ? __ldg(e.slopes + z0) : 0.f;
 #pragma unroll
@@ -284,8 +305,8 @@ __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, i
     for (int i = 0; i < 16; ++i) {
       float2 x = unpack_bf16x2(r0[i]);
       float2 xy = unpack_bf16x2(r1[i]);
-      o0[2 * i] = (xy.x > 0.f) ? acc[2 * i] * x.x : 0.f;
-      o0[2 * i + 1] = (xy.y > 0.f) ? acc[2 * i + 1] * x.y : 0.f;
+      o0[2 * i] = (xy.x > 0.f) ? acc[2 * i] * x.x * e.alpha : 0.f;
+      o0[2 * i + 1] = (xy.y > 0.f) ? acc[2 * i + 1] * x.y * e.alpha : 0.f;
       float g0 = acc[2 * i] * __fdividef(xy.x, x.x), g1 = acc[2 * i + 1] * __fdividef(xy.y, x.y);
       // +0.0 keeps "open gate, zero gradient" distinct from the marker
       o1[2 * i] = (x.x > 0.f) ? (g0 == 0.f ? 0.f : g0) : -0.f;

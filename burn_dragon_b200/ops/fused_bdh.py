@@ -37,8 +37,6 @@ def can_run(model, tokens: torch.Tensor, state) -> bool:
     B, T = tokens.shape
     if T % 64 or c.n_embd % 8 or c.n_embd > 2048 or c.latent_per_head % 64:
         return False
-    if c.dropout > 0 and model.training:
-        return False
     if c.block_sparse is not None and (c.block_sparse.latent.is_sparse() or c.block_sparse.time.is_sparse()):
         return False
     if c.vocab_size > 1024:
@@ -91,6 +89,10 @@ class _Dims:
         else:
             self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
+        # dropout on x*y (training only): a fresh mask seed per call, one derived seed per layer
+        self.drop_p = float(c.dropout) if (model.training and c.dropout > 0) else 0.0
+        model._drop_calls = getattr(model, "_drop_calls", 0) + 1
+        self.drop_base = (torch.initial_seed() * 0x9E3779B1 + model._drop_calls * 0x85EBCA77) & 0x7FFFFFFF
         hook = getattr(model, "_dims_hook", None)
         if hook is not None:
             hook(self)
@@ -124,7 +126,8 @@ def _bf16(rows, cols, dev):
 # ------------------------------------------------------------------------------------------------
 # one layer forward
 # ------------------------------------------------------------------------------------------------
-def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool):
+def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool,
+                   drop_seed: int = 0):
     dev = cur.device
     M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
     x = _bf16(M, d.HN, dev)
@@ -184,7 +187,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     # y is not stored: the backward recovers it as xy / x
     xy = _bf16(M, d.HN, dev)
     G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
-           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta)
+           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta,
+           drop_p=d.drop_p, drop_seed=drop_seed)
     if comm is None:
         sk = _split_k(-(-M // 128) * -(-D // 256), d.HN, dev)
         if sk > 1:
@@ -202,7 +206,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         mlp = comm.end(buf).to(torch.bfloat16)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
-    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp)
+    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed)
     return out, saved, rho_out
 
 
@@ -218,7 +222,9 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     # gate
     dy = _bf16(M, d.HN, dev)
     dxg = _bf16(M, d.HN, dev)
-    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg)
+    # with dropout the stored x*y is already masked and scaled, so only the 1/(1-p) on dy is explicit
+    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg,
+           alpha=1.0 / (1.0 - d.drop_p))
     wtiles = -(-d.HN // 128) * -(-D // 256)
     sk = _split_k(wtiles, M, dev)
     wflags = G.F_OUT_F32 | (G.F_ATOMIC if sk > 1 else G.F_ACCUM)
@@ -313,11 +319,12 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: boo
     saved: List[dict] = []
     for l in range(d.L):
         rho_in = state.layers[l].rho if state is not None else None
-        out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None)
+        seed_l = (d.drop_base + 0x632BE5AB * (l + 1)) & 0x7FFFFFFF
+        out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None, drop_seed=seed_l)
         if state is not None:
             state.layers[l].rho = rho_out
         if save:
-            saved.append(dict(cur=cur) if recompute else sv)
+            saved.append(dict(cur=cur, drop_seed=seed_l) if recompute else sv)
         cur = out
     if state is not None:
         state.position += d.T
@@ -368,7 +375,7 @@ class _FusedLoss(torch.autograd.Function):
         for l in reversed(range(d.L)):
             sv = saved[l]
             if ctx.recompute:
-                _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False)
+                _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
             dcur = _layer_backward(d, W, sv, dcur, grads, 0)
             saved[l] = None
         g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)

@@ -49,12 +49,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          o1_off: Sequence[int] = (0, 0, 0), alpha: float = 1.0, theta: float = 0.0, T: int = 1, pos0: int = 0,
          n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
-         tma_epilogue: bool = True, mc_out: int = 0) -> None:
+         tma_epilogue: bool = True, mc_out: int = 0, drop_p: float = 0.0, drop_seed: int = 0) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
-                       slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out))
+                       slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),
+                    int(drop_seed) & 0x7FFFFFFF)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -81,6 +82,27 @@ def rope_table(pos0: int, T: int, pair_freqs: torch.Tensor) -> torch.Tensor:
     return tab.view(torch.bfloat16)
 
 
+def _hash32(h: torch.Tensor) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    h = h ^ (h >> 16)
+    h = (h * 0x7feb352d) & m
+    h = h ^ (h >> 15)
+    h = (h * 0x846ca68b) & m
+    return h ^ (h >> 16)
+
+
+def dropout_keep_mask(seed: int, z0: int, M: int, N: int, p: float, device) -> torch.Tensor:
+    """The kernel's counter-based dropout mask for rows m < M, columns n < N of batch index z0:
+    one 32-bit hash per (row, column pair), low / high 16 bits for the even / odd column."""
+    m32 = 0xFFFFFFFF
+    rows = torch.arange(M, device=device, dtype=torch.int64)
+    pairs = torch.arange((N + 1) // 2, device=device, dtype=torch.int64)
+    base = (seed ^ ((rows * 0x9E3779B1) & m32) ^ ((z0 * 0xC2B2AE3D) & m32)) & m32
+    h = _hash32(base[:, None] ^ ((pairs[None, :] * 0x85EBCA77) & m32))
+    u = torch.stack((h & 0xFFFF, h >> 16), dim=-1).reshape(M, -1)[:, :N]
+    return u >= int(p * 65536.0)
+
+
 def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) -> torch.Tensor:
     """Interleaved-pair rotation (reference: src/model/attention.rs:305-321). x, phases [..., N]."""
     cos, sin = phases.cos(), phases.sin()
@@ -94,7 +116,8 @@ def rope_rotate(x: torch.Tensor, phases: torch.Tensor, inverse: bool = False) ->
 def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0, 0, 0, 0), b_off=(0, 0, 0, 0),
                    epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
                    o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
-                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True, mc_out=0) -> None:
+                   causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True, mc_out=0, drop_p=0.0,
+                   drop_seed=0) -> None:
     """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
     dev = a.device
     for z1 in range(nz[1]):
@@ -138,7 +161,11 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                 y = torch.relu(acc - theta)
                 if not (flags & F_NO_OUT0):
                     out0[rs, cs] = y.to(out0.dtype)
-                out1[rs, cs] = (y * in0[rs, cs].float()).to(out1.dtype)
+                xy = y * in0[rs, cs].float()
+                if drop_p > 0:
+                    keep = dropout_keep_mask(int(drop_seed) & 0x7FFFFFFF, z0, M, N, drop_p, dev)
+                    xy = torch.where(keep, xy / (1.0 - drop_p), torch.zeros_like(xy))
+                out1[rs, cs] = xy.to(out1.dtype)
             elif epi == EPI_CAUSAL:
                 slope = float(slopes[z0]) if slopes is not None else 0.0
                 dist = (mm[:, None] - nn[None, :]).float()
@@ -163,7 +190,7 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                 # in0 = x, in1 = x*y. y is recovered as xy/x where x > 0; closed x gates get -0.0
                 x = in0[rs, cs].float()
                 xy = in1[rs, cs].float()
-                out0[rs, cs] = torch.where(xy > 0, acc * x, torch.zeros_like(acc)).to(out0.dtype)
+                out0[rs, cs] = torch.where(xy > 0, acc * x * alpha, torch.zeros_like(acc)).to(out0.dtype)
                 y = torch.where(x > 0, xy / x.clamp(min=1e-30), torch.zeros_like(x))
                 g = acc * y
                 g = torch.where(g == 0, torch.zeros_like(g), g)          # +0.0 for open gates

@@ -104,3 +104,26 @@ def test_prefill_continuation(rot):
     assert st.position == 256
     assert _rel(torch.cat([l1, l2], 1), lf) < 0.05
     assert _rel(st.layers[-1].rho, st_full.layers[-1].rho) < 0.05
+
+
+def test_dropout_runs_on_kernels_and_matches_its_mask():
+    """Training with dropout stays on the kernel path; the loss it reports equals the torch path
+    evaluated with the very same dropout mask, and eval mode is unaffected by the dropout setting."""
+    from burn_dragon_b200.ops import gemm as G
+    m = _model("alibi")
+    m.config.dropout = 0.2
+    m.train()
+    tok = torch.randint(0, 256, (2, 128), device="cuda")
+    tgt = torch.randint(0, 256, (2, 128), device="cuda")
+    assert fused_bdh.can_run(m, tok, None)
+    n0 = native.launch_count()
+    l1 = m(tok, tgt)
+    l1.backward()
+    assert native.launch_count() > n0 and all(torch.isfinite(p.grad).all() for p in m.parameters())
+    l2 = m(tok, tgt)
+    assert l1.item() != l2.item()                       # a new mask every call
+    m.eval()
+    e1, e2 = m(tok, tgt), m(tok, tgt)
+    assert e1.item() == e2.item()
+    keep = G.dropout_keep_mask(99, 1, 64, 130, 0.2, "cuda")
+    assert keep.shape == (64, 130) and abs(keep.float().mean().item() - 0.8) < 0.03

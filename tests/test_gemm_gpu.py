@@ -100,10 +100,14 @@ def test_relu_rotary(rot):
         _check(k, r)
 
 
-def test_relu_gate():
+@pytest.mark.parametrize("drop_p", [0.0, 0.25])
+def test_relu_gate(drop_p):
     M, N, K = 256, 512, 128
     a, w, x = _rand(M, K, seed=11), _rand(N, K, 0.2, seed=12), _rand(M, N, seed=13).relu()
-    kw = dict(a=a, b=w, M=M, N=N, K=K, epi=G.EPI_RELU_GATE, in0=x)
+    kw = dict(a=a, b=w, M=M, N=N, K=K, epi=G.EPI_RELU_GATE, in0=x, drop_p=drop_p, drop_seed=1234567)
+    if drop_p:
+        keep = G.dropout_keep_mask(1234567, 0, M, N, drop_p, "cuda")
+        assert abs(keep.float().mean().item() - (1 - drop_p)) < 0.01
     outs = dict(out0=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16),
                 out1=torch.zeros(M, N, device="cuda", dtype=torch.bfloat16))
     for k, r in _run_both(kw, outs):
