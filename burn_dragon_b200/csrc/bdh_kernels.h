@@ -73,6 +73,11 @@ int bdh_block_out_fwd(const void* cur_bf16, const void* mlp_bf16, void* out_bf16
 int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* dout_f32,
                       float* dcur_f32, void* dmlp_bf16, long long rows, int D, cudaStream_t s);
 
+// PoPE backward: dx = (dq_re cos + dq_im sin) sigmoid(x) + gate gradient where x > 0, else 0.
+// dq bf16 [M, H*2N] (per head [real N | imag N]); x, dxg, dx bf16 [M, H*N]; freqs [N]; N % 8 == 0.
+int bdh_pope_bwd(const void* dq_bf16, const void* x_bf16, const void* dxg_bf16, const float* freqs, void* dx_bf16,
+                 long long M, int H, int N, int T, int pos0, cudaStream_t s);
+
 // ---- loss ------------------------------------------------------------------------------------
 // Mean cross-entropy over rows of fp32 logits [rows, V] (V <= 1024); writes per-row loss and
 // dlogits (bf16) = (softmax - onehot) * grad_scale.  (reference: src/model/loss.rs:5-18)

@@ -247,6 +247,18 @@ void rank_barrier(const Tensor& anchor, at::IntArrayRef flag_ptrs, int64_t rank,
            "rank_barrier");
 }
 
+void pope_bwd(const Tensor& dq, const Tensor& x, const Tensor& dxg, const Tensor& freqs, Tensor& dx, int64_t H, int64_t T,
+              int64_t pos0) {
+  c10::cuda::CUDAGuard guard(x.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&dq, &x, &dxg, &dx})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kBFloat16 && t->dim() == 2);
+  const int64_t M = x.size(0), HN = x.size(1);
+  TORCH_CHECK(HN % H == 0 && dq.size(0) == M && dq.size(1) == 2 * HN && dxg.sizes() == x.sizes() && dx.sizes() == x.sizes());
+  TORCH_CHECK(freqs.scalar_type() == at::kFloat && freqs.is_contiguous() && freqs.numel() == HN / H);
+  check_rc(bdh_pope_bwd(dq.data_ptr(), x.data_ptr(), dxg.data_ptr(), freqs.data_ptr<float>(), dx.data_ptr(), M, H, HN / H, T,
+                        pos0, cur_stream()), "pope_bwd");
+}
+
 void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
   c10::cuda::CUDAGuard guard(flag.device());
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
@@ -278,6 +290,7 @@ TORCH_LIBRARY(bdh, m) {
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
+  m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
@@ -304,6 +317,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
+  m.impl("pope_bwd", &pope_bwd);
   m.impl("rank_barrier", &rank_barrier);
   m.impl("graph_spmm_relu", &graph_spmm_relu);
   m.impl("ssd_chunk_scan", &ssd_chunk_scan);

@@ -139,12 +139,13 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   const bool batched = d->nz0 * d->nz1 > 1;
   if (batched && ((d->M % GEMM_BM) || (d->N % bn))) tma_epi = false;
   for (int i = 0; i < 4; ++i) if (d->c_off[i] % 8) tma_epi = false;
-  if (d->o1_off[0] % 8 || d->o1_off[1] % 8) tma_epi = false;
+  if (d->o1_off[0] % 8 || d->o1_off[1] % 8 || d->o1_off[2] % 8) tma_epi = false;
   if (tma_epi) {
     const long long rows = d->c_off[0] * (d->nz0 - 1) + d->c_off[1] * (d->nz1 - 1) + d->M;
     const long long cols = d->c_off[2] * (d->nz0 - 1) + d->c_off[3] * (d->nz1 - 1) + d->N;
     const long long cols1 = (d->epi == EPI_RELU)
-                                ? d->o1_off[0] * (d->nz0 - 1) + d->o1_off[1] * (d->nz1 - 1) + d->N
+                                ? d->o1_off[0] * (d->nz0 - 1) + d->o1_off[1] * (d->nz1 - 1) + d->N +
+                                      ((d->flags & EPI_F_POPE) ? d->o1_off[2] : 0)
                                 : cols;
     // the rotary table (in0 of EPI_RELU, in1 of EPI_DQ_BWD) is a [T, n_per_head] tensor of its own
     const bool tab0 = d->epi == EPI_RELU, tab1 = d->epi == EPI_DQ_BWD;

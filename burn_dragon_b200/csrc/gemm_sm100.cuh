@@ -176,14 +176,14 @@ __device__ __forceinline__ void load_pair_freqs(const float* freqs, int col, flo
 // with the bf16 bit pattern of -0.0 wherever the ReLU that produced x is closed (x <= 0). The
 // consumer masks by that marker instead of re-reading x.
 // ------------------------------------------------------------------------------------------------
-enum : int { IO_IN0 = 1, IO_IN1 = 2, IO_OUT0 = 4, IO_OUT1 = 8 };
+enum : int { IO_IN0 = 1, IO_IN1 = 2, IO_OUT0 = 4, IO_OUT1 = 8, IO_OUT2 = 16 };   // OUT2: PoPE imaginary half (in out1)
 constexpr uint32_t BF16_NEG_ZERO = 0x8000u;
 
 __host__ __device__ inline int epi_io_mask(int epi, int flags) {
   switch (epi) {
     case EPI_STORE: return IO_OUT0;
     case EPI_RELU:
-      return IO_OUT0 | ((flags & (EPI_F_ROPE | EPI_F_POPE)) ? IO_OUT1 : 0) |
+      return IO_OUT0 | ((flags & (EPI_F_ROPE | EPI_F_POPE)) ? IO_OUT1 : 0) | ((flags & EPI_F_POPE) ? IO_OUT2 : 0) |
              (((flags & EPI_F_ROPE) && (flags & EPI_F_TABLE)) ? IO_IN0 : 0);
     case EPI_RELU_GATE: return IO_IN0 | IO_OUT1 | ((flags & EPI_F_NO_OUT0) ? 0 : IO_OUT0);
     case EPI_CAUSAL: return IO_OUT0;
@@ -199,7 +199,7 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
   if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC));
-  if (epi == EPI_RELU) return !(flags & EPI_F_POPE);
+  if (epi == EPI_RELU) return true;
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
 }
@@ -231,14 +231,32 @@ __device__ __forceinline__ uint32_t dropout_hash(uint32_t h) {
 template <int EPI>
 __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, int n, float (&acc)[32],
                                             const uint32_t (&r0)[16], const uint32_t (&r1)[16],
-                                            float (&o0)[32], float (&o1)[32]) {
+                                            float (&o0)[32], float (&o1)[32], float (&o2)[32]) {
   if constexpr (EPI == EPI_STORE) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) o0[i] = acc[i] * e.alpha;
   } else if constexpr (EPI == EPI_RELU) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) o0[i] = fmaxf(acc[i] - e.theta, 0.f);
-    if (e.flags & EPI_F_ROPE) {
+    if (e.flags & EPI_F_POPE) {
+      // q = softplus(x) * (cos, sin): real half -> o1, imaginary half -> o2
+      const float pos = static_cast<float>(e.pos0 + (m % e.T));
+      const float4* fp = reinterpret_cast<const float4*>(e.freqs + (n % e.n_per_head));
+#pragma unroll
+      for (int i4 = 0; i4 < 8; ++i4) {
+        const float4 f = __ldg(fp + i4);
+        const float fr[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = 4 * i4 + j;
+          float s, co;
+          rot_sincos(pos, fr[j], s, co);
+          const float mag = o0[i] + __logf(1.f + __expf(-o0[i]));   // softplus of a non-negative value
+          o1[i] = mag * co;
+          o2[i] = mag * s;
+        }
+      }
+    } else if (e.flags & EPI_F_ROPE) {
       if (e.flags & EPI_F_TABLE) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -426,27 +444,6 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
     }
     return;
   }
-  if constexpr (EPI == EPI_RELU) {
-    if (e.flags & EPI_F_POPE) {
-      const float pos = static_cast<float>(e.pos0 + (m % e.T));
-      const int fcol = n % e.n_per_head;
-      const long long c1 = e.o1_n0 * z0 + e.o1_n1 * z1 + n;
-      float re[32], im[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        v[i] = fmaxf(v[i] - e.theta, 0.f);
-        float s, co;
-        rot_sincos(pos, __ldg(e.freqs + fcol + i), s, co);
-        float mag = v[i] + log1pf(__expf(-v[i]));  // softplus of a non-negative value
-        re[i] = mag * co;
-        im[i] = mag * s;
-      }
-      store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, v, valid);
-      store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1, re, valid);
-      store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1 + e.o1_imag, im, valid);
-      return;
-    }
-  }
   if constexpr (EPI == EPI_CAUSAL) {
     if (e.flags & EPI_F_UPPER) {
       if (n + 31 <= m) return;  // nothing above the diagonal in this chunk
@@ -470,18 +467,19 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
   }
   const int io = epi_io_mask(EPI, e.flags);
   uint32_t r0[16], r1[16];
-  float o0[32], o1[32];
+  float o0[32], o1[32], o2[32];
   const bool tab0 = (EPI == EPI_RELU), tab1 = (EPI == EPI_DQ_BWD);   // which input is the rotary table
   const long long tr = m % e.T, tcn = n % e.n_per_head;
   if (io & IO_IN0)
     load_raw_32(static_cast<const bf*>(e.in0), e.ld_in0, tab0 ? tr : r, tab0 ? tcn : c, r0, valid);
   if (io & IO_IN1)
     load_raw_32(static_cast<const bf*>(e.in1), e.ld_in1, tab1 ? tr : r, tab1 ? tcn : c, r1, valid);
-  epi_compute<EPI>(e, z0, m, n, v, r0, r1, o0, o1);
+  epi_compute<EPI>(e, z0, m, n, v, r0, r1, o0, o1, o2);
   if (io & IO_OUT0) store_bf16_32(static_cast<bf*>(e.out0), e.ld_out0, r, c, o0, valid);
   if (io & IO_OUT1) {
     const long long c1 = (EPI == EPI_RELU) ? e.o1_n0 * z0 + e.o1_n1 * z1 + n : c;
     store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1, o1, valid);
+    if (io & IO_OUT2) store_bf16_32(static_cast<bf*>(e.out1), e.ld_out1, r, c1 + e.o1_imag, o2, valid);
   }
 }
 
@@ -574,7 +572,8 @@ __host__ __device__ constexpr int epi_num_in(int epi) {
   return (epi == EPI_RELU_GATE || epi == EPI_RELU) ? 1 : (epi == EPI_GATE_BWD || epi == EPI_DQ_BWD) ? 2 : 0;
 }
 __host__ __device__ constexpr int epi_num_out(int epi) {
-  return (epi == EPI_RELU || epi == EPI_RELU_GATE || epi == EPI_GATE_BWD) ? 2 : 1;
+  if (epi == EPI_RELU) return 3;       // x, rotated copy, PoPE imaginary half
+  return (epi == EPI_RELU_GATE || epi == EPI_GATE_BWD) ? 2 : 1;
 }
 
 template <int BN, int STAGES, bool TMA_EPI, int EW, int EPI>
@@ -833,7 +832,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < CHUNKS; ++c, ++gchunk) {
           const int buf = gchunk & 1;
-          float v[32], o0[32], o1[32];
+          float v[32], o0[32], o1[32], o2[32];
           uint32_t a0[16], a1[16];
           tmem_ld_32x32(tbase + (cbase + c) * 32, v);
           if (has_in) {
@@ -856,12 +855,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
           tmem_ld_wait();
-          epi_compute<EPI>(e, tc.z0, m, tc.n0 + (cbase + c) * 32, v, a0, a1, o0, o1);
+          epi_compute<EPI>(e, tc.z0, m, tc.n0 + (cbase + c) * 32, v, a0, a1, o0, o1, o2);
           // the store issued two chunks ago must have finished reading this output buffer
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           __syncwarp();
           if (io & IO_OUT0) box_write_row(out_box + (0 * 2 + buf) * EPI_BOX_BYTES, lane, o0);
           if (io & IO_OUT1) box_write_row(out_box + (1 * 2 + buf) * EPI_BOX_BYTES, lane, o1);
+          if constexpr (EPI == EPI_RELU) {
+            if (io & IO_OUT2) box_write_row(out_box + (2 * 2 + buf) * EPI_BOX_BYTES, lane, o2);
+          }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -869,6 +871,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_store_2d(&em.out0, out_box + (0 * 2 + buf) * EPI_BOX_BYTES, col0 + c * 32, row0);
             if (io & IO_OUT1)
               tma_store_2d(&em.out1, out_box + (1 * 2 + buf) * EPI_BOX_BYTES, col1 + c * 32, row0);
+            if constexpr (EPI == EPI_RELU) {
+              if (io & IO_OUT2)
+                tma_store_2d(&em.out1, out_box + (2 * 2 + buf) * EPI_BOX_BYTES,
+                             col1 + c * 32 + static_cast<int>(e.o1_imag), row0);
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }

@@ -493,3 +493,61 @@ extern "C" int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cu
   add_f32_kernel<<<flat_grid(n, 256), 256, 0, s>>>(in, inout, n);
   return launch_rc();
 }
+
+// ---- PoPE backward ---------------------------------------------------------------------------------
+// q = softplus(x) * (cos(ph), sin(ph))  (reference: src/model/attention.rs:323-330), so
+//   dx = (dq_re * cos + dq_im * sin) * sigmoid(x) + gate gradient, zero where the ReLU of x is closed.
+// dq: bf16 [M, H*2N] with per-head layout [real N | imag N]; x, dxg, dx: bf16 [M, H*N]; the gate
+// gradient carries the closed-gate marker (bf16 -0.0). One thread handles 8 consecutive neurons.
+namespace bdh {
+__global__ void pope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ dxg, const float* __restrict__ freqs,
+                                __nv_bfloat16* __restrict__ dx, long long M, int H, int N, int T, int pos0) {
+  const long long per_row = static_cast<long long>(H) * N / 8;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = M * per_row, stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (; i < total; i += stride) {
+    const long long m = i / per_row;
+    const int c = static_cast<int>(i % per_row) * 8;     // column in [0, H*N)
+    const int h = c / N, n = c % N;
+    const float pos = static_cast<float>(pos0 + static_cast<int>(m % T));
+    const long long off = m * H * N + c;
+    const long long qoff = m * 2 * H * N + static_cast<long long>(h) * 2 * N + n;
+    uint4 ux = *reinterpret_cast<const uint4*>(x + off);
+    uint4 ug = *reinterpret_cast<const uint4*>(dxg + off);
+    uint4 ur = *reinterpret_cast<const uint4*>(dq + qoff);
+    uint4 ui = *reinterpret_cast<const uint4*>(dq + qoff + N);
+    const uint32_t* px = &ux.x; const uint32_t* pg = &ug.x; const uint32_t* pr = &ur.x; const uint32_t* pi = &ui.x;
+    uint4 out;
+    uint32_t* po = &out.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 xv = unpack_bf16x2(px[k]), gv = unpack_bf16x2(pg[k]), rv = unpack_bf16x2(pr[k]), iv = unpack_bf16x2(pi[k]);
+      float res[2];
+      const float xs[2] = {xv.x, xv.y}, gs[2] = {gv.x, gv.y}, rs[2] = {rv.x, rv.y}, is[2] = {iv.x, iv.y};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float raw = pos * __ldg(freqs + n + 2 * k + j);
+        float ph = (raw - floorf(raw)) * 6.283185307179586f;
+        float s, co;
+        __sincosf(ph, &s, &co);
+        const float sig = 1.f / (1.f + __expf(-xs[j]));
+        res[j] = (xs[j] > 0.f) ? (rs[j] * co + is[j] * s) * sig + gs[j] : 0.f;
+      }
+      po[k] = pack_bf16x2(res[0], res[1]);
+    }
+    *reinterpret_cast<uint4*>(dx + off) = out;
+  }
+}
+}  // namespace bdh
+
+extern "C" int bdh_pope_bwd(const void* dq, const void* x, const void* dxg, const float* freqs, void* dx, long long M,
+                            int H, int N, int T, int pos0, cudaStream_t s) {
+  if (M <= 0 || H <= 0 || N <= 0 || (N % 8) || T <= 0) return BDH_ERR_ARGUMENT;
+  const long long total = M * H * N / 8;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  bdh::pope_bwd_kernel<<<static_cast<int>(blocks), 256, 0, s>>>((const bf16*)dq, (const bf16*)x, (const bf16*)dxg, freqs,
+                                                               (bf16*)dx, M, H, N, T, pos0);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}

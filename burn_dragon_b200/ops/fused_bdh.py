@@ -268,13 +268,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
         dq = _bf16(M, d.HNp, dev)
         G.gemm(Gs, q, M=T, N=Np, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(Np, 0, 0, T),
                c_off=(0, T, Np, 0), out0=dq)
-        pos = torch.arange(pos0, pos0 + T, device=dev)
-        ph = R.phases(pos, d.freqs_full)                                     # [T, N]
-        dq4 = dq.view(B, T, H, 2, N).float()
-        xf = x.view(B, T, H, N).float()
-        dmag = dq4[:, :, :, 0] * ph.cos().view(1, T, 1, N) + dq4[:, :, :, 1] * ph.sin().view(1, T, 1, N)
-        dxv = dmag * torch.sigmoid(xf) + dxg.view(B, T, H, N).float()
-        dx.copy_(torch.where(xf > 0, dxv, torch.zeros_like(dxv)).view(M, d.HN))
+        ops.pope_bwd(dq, x, dxg, d.freqs_full, dx, H, T, pos0)
     else:
         rope = d.rot == "rope"
         G.gemm(Gs, q, M=T, N=N, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(N, 0, 0, T),
