@@ -104,8 +104,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nccl-only", action="store_true", help="NCCL all-reduce instead of the fused NVLink path")
-    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU)
-    ap.add_argument("--seq", type=int, default=SEQ_LEN)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--seq", type=int, default=None)
+    ap.add_argument("--preset", default="base", choices=["base", "large", "tp"],
+                    help="base: BDH base, DDP (the headline config); large: L8 D512 H8 N16384 PoPE T2048 B8/GPU, "
+                         "sharded optimizer (FSDP); tp: L12 D1024 H16 N16384 RoPE T4096 B4, neuron-sharded TP")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -129,14 +132,32 @@ def main() -> int:
 
     W = max(3, args.warmup)
     K = max(1, args.steps)
-    B, T = args.batch, args.seq
+    presets = {
+        "base": (MODEL, BATCH_PER_GPU, SEQ_LEN, "ddp", False, "bdh-base L6 D256 H4 N8192 V256 rope"),
+        "large": (dict(n_layer=8, n_embd=512, n_head=8, n_latent_per_head=16384, vocab_size=256, dropout=0.0,
+                       rotary_embedding="pope"), 8, 2048, "fsdp", True, "bdh-large L8 D512 H8 N16384 V256 pope"),
+        "tp": (dict(n_layer=12, n_embd=1024, n_head=16, n_latent_per_head=16384, vocab_size=256, dropout=0.0,
+                    rotary_embedding="rope"), 4, 4096, "tp", True, "bdh-tp L12 D1024 H16 N16384 V256 rope"),
+    }
+    mcfg, B0, T0, strategy, recompute, model_name = presets[args.preset]
+    B, T = args.batch or B0, args.seq or T0
     torch.manual_seed(1337)
-    model = BDH(BDHConfig(**MODEL)).to(dev)
-    trainer = Trainer(model, lr=1e-3, weight_decay=0.1, parallel="ddp" if world > 1 else "single",
-                      fused_collectives=not args.nccl_only)
+    model = BDH(BDHConfig(**mcfg)).to(dev)
+    model.recompute = recompute
+    wrapper = None
+    if world > 1 and strategy == "fsdp":
+        from burn_dragon_b200.parallel.fsdp import FSDP
+        wrapper = FSDP(model, lr=1e-3, weight_decay=0.1, fused=not args.nccl_only)
+    elif world > 1 and strategy == "tp":
+        from burn_dragon_b200.parallel.tp import NeuronTP
+        wrapper = NeuronTP(model, lr=1e-3, weight_decay=0.1, fused=not args.nccl_only)
+    trainer = Trainer(model, lr=1e-3, weight_decay=0.1, parallel="ddp" if (world > 1 and strategy == "ddp") else "single",
+                      fused_collectives=not args.nccl_only, wrapper=wrapper)
+    # tensor parallel ranks work on the same batch; data-parallel ranks on different ones
+    data_world = 1 if strategy == "tp" else world
 
     # synthetic uniform bytes, per-rank seed; one pinned host buffer per step so e2e copies real data
-    gen = torch.Generator().manual_seed(1000 + rank)
+    gen = torch.Generator().manual_seed(1000 + (0 if strategy == "tp" else rank))
     n_batches = W + K
     host = [torch.randint(0, 256, (B, T + 1), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
     dev_batches = [h.to(dev) for h in host]
@@ -192,7 +213,7 @@ def main() -> int:
     dist_utils.barrier()
     ms_e2e = dist_utils.max_over_ranks(e0.elapsed_time(e1), dev)
 
-    tokens = B * T * world * K
+    tokens = B * T * data_world * K
     value = tokens / (ms / 1e3)
     e2e_value = tokens / (ms_e2e / 1e3)
     status = native.status_code()
@@ -200,10 +221,11 @@ def main() -> int:
         out = {
             "metric": "BDH train tokens/s (device-timed, max over ranks)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if strategy == "tp" else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform random bytes, random-init weights",
-            "config": {"model": "bdh-base L6 D256 H4 N8192 V256 rope", "global_batch": B * world, "seq_len": T,
-                       "parallelism": f"dp{world}" if world > 1 else "single",
+            "config": {"model": model_name, "global_batch": B * data_world, "seq_len": T,
+                       "parallelism": (f"{'dp' if strategy == 'ddp' else strategy}{world}" if world > 1 else "single"),
+                       "recompute": recompute,
                        "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
                        "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
                        "allreduce": ("nccl" if args.nccl_only else "fused-nvlink") if world > 1 else "none"},

@@ -44,7 +44,8 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           const optional<Tensor>& in0, const optional<Tensor>& in1, at::IntArrayRef c_off,
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
-          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed) {
+          int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed,
+          at::IntArrayRef peer_ptrs, int64_t peer_rows) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -66,6 +67,12 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   d.no_tma_epilogue = tma_epilogue ? 0 : 1;
   d.drop_p = drop_p; d.drop_seed = static_cast<unsigned>(drop_seed);
   if (mc_out != 0) d.out0 = reinterpret_cast<void*>(mc_out);   // multicast mapping of out0 (EPI_F_MC_RED)
+  long long peers[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (!peer_ptrs.empty()) {                                      // reduce-scatter epilogue (EPI_F_PEER_RED)
+    TORCH_CHECK(peer_ptrs.size() <= 8, "at most 8 peers");
+    for (size_t i = 0; i < peer_ptrs.size(); ++i) peers[i] = peer_ptrs[i];
+    d.peer_out = peers; d.peer_world = static_cast<int>(peer_ptrs.size()); d.peer_rows = peer_rows;
+  }
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
 
@@ -154,6 +161,18 @@ void allreduce_scale(const Tensor& anchor, at::IntArrayRef buf_ptrs, at::IntArra
   auto b = as_ptrs(buf_ptrs), f = as_ptrs(flag_ptrs);
   check_rc(bdh_allreduce_scale(b.data(), f.data(), mc_ptr, rank, world, n_floats, scale, (unsigned)epoch, ctas,
                                status_word().data_ptr<int>(), cur_stream()), "allreduce_scale");
+}
+
+void gather_blocks(const Tensor& anchor, at::IntArrayRef buf_ptrs, at::IntArrayRef flag_ptrs, int64_t mc_ptr,
+                   at::IntArrayRef out_ptrs, int64_t out_mc, int64_t rank, int64_t world, int64_t n_floats,
+                   int64_t block_floats, int64_t epoch, int64_t ctas) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world);
+  TORCH_CHECK(out_ptrs.empty() || (int64_t)out_ptrs.size() == world);
+  auto b = as_ptrs(buf_ptrs), f = as_ptrs(flag_ptrs), o = as_ptrs(out_ptrs);
+  check_rc(bdh_gather_blocks(b.data(), f.data(), mc_ptr, o.empty() ? nullptr : o.data(), out_mc, rank, world,
+                             n_floats, block_floats, (unsigned)epoch, ctas, status_word().data_ptr<int>(),
+                             cur_stream()), "gather_blocks");
 }
 
 void rs_adamw_ag(const Tensor& anchor, at::IntArrayRef grad_ptrs, at::IntArrayRef flag_ptrs, int64_t grad_mc,
@@ -273,7 +292,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows) -> ()");
   m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
   m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
@@ -286,6 +305,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("status() -> Tensor");
   m.def("allreduce_scale(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int rank, int world, "
         "int n_floats, float scale, int epoch, int ctas) -> ()");
+  m.def("gather_blocks(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int[] out_ptrs, int out_mc, "
+        "int rank, int world, int n_floats, int block_floats, int epoch, int ctas) -> ()");
   m.def("rs_adamw_ag(Tensor anchor, int[] grad_ptrs, int[] flag_ptrs, int grad_mc, int[] shadow_ptrs, int rank, "
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
@@ -315,6 +336,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("cross_entropy", &cross_entropy);
   m.impl("adamw", &adamw);
   m.impl("allreduce_scale", &allreduce_scale);
+  m.impl("gather_blocks", &gather_blocks);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
   m.impl("pope_bwd", &pope_bwd);

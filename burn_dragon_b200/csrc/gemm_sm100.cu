@@ -72,7 +72,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& e
   // Staged epilogues run 8 epilogue warps; the mainloop ring gets what shared memory is left.
   constexpr int EW = TMA_EPI ? 8 : 4;
   constexpr int STAGE_BYTES = (GEMM_BM + BN) * GEMM_BK * 2;
-  constexpr int EPI_BYTES = TMA_EPI ? EW * 2 * (epi_num_in(EPI) + epi_num_out(EPI)) * EPI_BOX_BYTES : 0;
+  constexpr int EPI_BYTES = TMA_EPI ? EW * 2 * (epi_num_in(EPI) + epi_num_out(EPI)) * EPI_BOX_BYTES
+                                    : (EPI == EPI_STORE ? EW * EPI_RED_TILE_BYTES : 0);
   constexpr int BUDGET = 227 * 1024 - 2048 - EPI_BYTES;
   constexpr int FIT = BUDGET / STAGE_BYTES;
   constexpr int STAGES = FIT > 6 ? 6 : FIT;
@@ -127,6 +128,15 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   e.n_per_head = d->n_per_head > 0 ? d->n_per_head : 1;
   e.freqs = d->freqs; e.slopes = d->slopes; e.flags = d->flags;
   e.drop_p = d->drop_p; e.drop_seed = d->drop_seed;
+  e.peer_rows = d->peer_rows > 0 ? d->peer_rows : 1;
+  e.peer_world = d->peer_world;
+  for (int i = 0; i < GEMM_MAX_PEERS; ++i)
+    e.peer_out[i] = (d->peer_out && i < d->peer_world) ? reinterpret_cast<float*>(d->peer_out[i]) : nullptr;
+  if (d->flags & EPI_F_PEER_RED) {
+    if (d->epi != EPI_STORE || !d->peer_out || d->peer_world < 1 || d->peer_world > GEMM_MAX_PEERS ||
+        d->peer_rows < 1)
+      return BDH_ERR_ARGUMENT;
+  }
 
   const int max_ctas = d->max_ctas > 0 ? d->max_ctas : num_sms();
   const int key = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);

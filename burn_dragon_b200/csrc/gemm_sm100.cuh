@@ -44,7 +44,12 @@ enum EpiFlags : int {
   EPI_F_ATOMIC = 512,      // EPI_STORE fp32: out0 += tile with red.global.add (split-K partial sums)
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
+  EPI_F_PEER_RED = 1024,   // EPI_STORE fp32: reduce-scatter epilogue. Output rows are split into blocks of
+                           // peer_rows; the tile is added (red.sys) into the buffer of the rank that owns
+                           // its rows, through that rank's peer mapping peer_out[owner]
 };
+
+constexpr int GEMM_MAX_PEERS = 8;
 
 struct OperandOffsets {
   long long mn0, mn1;  // element offsets along the m/n dimension per unit of z0, z1
@@ -70,6 +75,9 @@ struct EpiParams {
   int flags;
   float drop_p;          // EPI_RELU_GATE: dropout probability applied to x*y (0: off)
   uint32_t drop_seed;    // EPI_RELU_GATE: seed of the counter-based dropout mask
+  float* peer_out[GEMM_MAX_PEERS];   // EPI_F_PEER_RED: every rank's mapping of the (symmetric) output buffer
+  long long peer_rows;               // EPI_F_PEER_RED: rows per owner block
+  int peer_world;
 };
 
 struct GemmArgs {
@@ -198,7 +206,8 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // memory and moved with TMA; the others (fp32 / accumulate / PoPE layout / partial upper writes)
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
-  if (epi == EPI_STORE) return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC));
+  if (epi == EPI_STORE)
+    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RED));
   if (epi == EPI_RELU) return true;
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -390,6 +399,51 @@ __device__ __forceinline__ void load_raw_32(const __nv_bfloat16* base, long long
   }
 }
 
+constexpr int EPI_RED_FLAGS = EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RED;
+
+__device__ __forceinline__ float* peer_row_base(const EpiParams& e, long long row) {
+  long long owner = row / e.peer_rows;
+  if (owner >= e.peer_world) owner = e.peer_world - 1;
+  return e.peer_out[owner];
+}
+
+__device__ __forceinline__ void red_add_f32x4(float* p, const float4& u, int flags) {
+  if (flags & EPI_F_MC_RED)
+    asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y),
+                 "f"(u.z), "f"(u.w)
+                 : "memory");
+  else if (flags & EPI_F_PEER_RED)
+    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y), "f"(u.z),
+                 "f"(u.w)
+                 : "memory");
+  else
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y), "f"(u.z), "f"(u.w)
+                 : "memory");
+}
+
+// Adds one warp's full 32x32 fp32 tile (thread = row, v = its 32 columns) into global, multicast or
+// peer memory. The tile is transposed through 4 KB of shared memory (16-byte slots, XOR-swizzled by
+// row) so that 8 lanes cover one 128-byte row segment: every reduction request that leaves the SM -
+// and, for peer and multicast targets, every NVLink packet - carries a full 128 bytes instead of 16.
+// r0 = output row of lane 0, c = first output column; the caller has checked 16-byte alignment.
+__device__ __forceinline__ void red_tile_coalesced(const EpiParams& e, long long r0, long long c,
+                                                   const float (&v)[32], float4* scratch, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    scratch[lane * 8 + (i ^ (lane & 7))] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  __syncwarp();
+  const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int row = 4 * j + sub;
+    const float4 u = scratch[row * 8 + (ch ^ (row & 7))];
+    const long long rr = r0 + row;
+    float* base = (e.flags & EPI_F_PEER_RED) ? peer_row_base(e, rr) : static_cast<float*>(e.out0);
+    red_add_f32x4(base + rr * e.ld_out0 + c + 4 * ch, u, e.flags);
+  }
+  __syncwarp();
+}
+
 // Per-thread global-memory epilogue (any shape, any alignment, every flag).
 template <int EPI>
 __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int z1, int m, int n,
@@ -417,6 +471,17 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
         for (int i = 0; i < 32; ++i)
           if (i < valid)
             asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
+      }
+    } else if (e.flags & EPI_F_PEER_RED) {
+      float* p = peer_row_base(e, r) + r * e.ld_out0 + c;
+      if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          red_add_f32x4(p + 4 * i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]), e.flags);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < valid) asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
       }
     } else if (e.flags & EPI_F_ATOMIC) {
       float* p = static_cast<float*>(e.out0) + r * e.ld_out0 + c;
@@ -576,6 +641,8 @@ __host__ __device__ constexpr int epi_num_out(int epi) {
   return (epi == EPI_RELU_GATE || epi == EPI_GATE_BWD) ? 2 : 1;
 }
 
+constexpr int EPI_RED_TILE_BYTES = 32 * 32 * 4;
+
 template <int BN, int STAGES, bool TMA_EPI, int EW, int EPI>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
@@ -583,7 +650,10 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int NIN = epi_num_in(EPI);
   static constexpr int NOUT = epi_num_out(EPI);
-  static constexpr int EPI_WARP_BYTES = TMA_EPI ? 2 * (NIN + NOUT) * EPI_BOX_BYTES : 0;
+  // staged epilogue: double-buffered 32x32 bf16 boxes; direct EPI_STORE: one 32x32 fp32 transposition
+  // tile per warp for the coalesced reduction-add paths
+  static constexpr int EPI_WARP_BYTES =
+      TMA_EPI ? 2 * (NIN + NOUT) * EPI_BOX_BYTES : (EPI == EPI_STORE ? EPI_RED_TILE_BYTES : 0);
   static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = EPI_OFFSET + EW * EPI_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5 + 2 * EW;
@@ -770,6 +840,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           float v[32];
           tmem_ld_32x32(tbase + c * 32, v);
           tmem_ld_wait();
+          if constexpr (EPI == EPI_STORE) {
+            const EpiParams& e = g.epi;
+            const int n = tc.n0 + c * 32;
+            if ((e.flags & EPI_RED_FLAGS) && m - lane + 32 <= g.M && n + 32 <= g.N && (e.ld_out0 & 3) == 0) {
+              const long long r0 = e.c_m0 * tc.z0 + e.c_m1 * tc.z1 + (m - lane);
+              const long long cc = e.c_n0 * tc.z0 + e.c_n1 * tc.z1 + n;
+              if (((reinterpret_cast<uintptr_t>(e.out0) + 4 * static_cast<uintptr_t>(cc)) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] *= e.alpha;
+                red_tile_coalesced(e, r0, cc, v,
+                                   reinterpret_cast<float4*>(smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES), lane);
+                continue;
+              }
+            }
+          }
           epilogue_direct<EPI>(g.epi, tc.z0, tc.z1, m, tc.n0 + c * 32, v, g.M, g.N);
         }
         tc_fence_before();

@@ -162,12 +162,12 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         # the GEMM epilogue adds it into every rank's replica through the switch
         buf = comm.begin("a", H * M, D)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
-               c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, mc_out=buf.mc)
+               c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, **buf.kw)
         if rho_in is not None:
             rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
             G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
-                   c_off=(M, T, 0, 0), flags=comm.flags, out0=buf.view, mc_out=buf.mc)
-        a = comm.end(buf).to(torch.bfloat16)
+                   c_off=(M, T, 0, 0), flags=comm.flags, out0=buf.view, **buf.kw)
+        a = comm.end(buf, bf16=True)
     rho_out = None
     if want_rho:
         rho_out = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
@@ -202,8 +202,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
             G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, out0=mlp)
     else:
         buf = comm.begin("mlp", M, D)
-        G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, flags=comm.flags, out0=buf.view, mc_out=buf.mc)
-        mlp = comm.end(buf).to(torch.bfloat16)
+        G.gemm(xy, W["decoder"], M=M, N=D, K=d.HN, b_mn=True, flags=comm.flags, out0=buf.view, **buf.kw)
+        mlp = comm.end(buf, bf16=True)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
     saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed)
@@ -242,8 +242,8 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     else:
         buf = comm.begin("dlna", H * M, D)
         G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
-               c_off=(M, 0, 0, 0), flags=comm.flags, out0=buf.view, mc_out=buf.mc)
-        dlna = comm.end(buf).to(torch.bfloat16)
+               c_off=(M, 0, 0, 0), flags=comm.flags, out0=buf.view, **buf.kw)
+        dlna = comm.end(buf, bf16=True)
     del dy
     da = _bf16(H * M, D, dev)
     ops.layernorm_bwd(a, dlna, da, False)
@@ -255,13 +255,13 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
            epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
     # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h ; heads run as separate launches
     if comm is None:
-        part, pflags, pmc = dcur, G.F_OUT_F32 | G.F_ACCUM, 0
+        part, pflags, pkw = dcur, G.F_OUT_F32 | G.F_ACCUM, {}
     else:
         pbuf = comm.begin("dcur", M, D)        # partial sums over the neuron shards: dV and the encoder path
-        part, pflags, pmc = pbuf.view, comm.flags, pbuf.mc
+        part, pflags, pkw = pbuf.view, comm.flags, pbuf.kw
     for h in range(H):
         G.gemm(S[h * T:], da[h * M:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),
-               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=pflags, out0=part, mc_out=pmc)
+               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=pflags, out0=part, **pkw)
     # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
     dx = _bf16(M, d.HN, dev)
     if d.rot == "pope":
@@ -283,7 +283,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
         G.gemm(dx, W["encoder"], M=M, N=D, K=k2, b_mn=True, nz=(sk2, 1), a_off=(0, 0, k2, 0), b_off=(0, 0, k2, 0),
                flags=G.F_OUT_F32 | (G.F_ATOMIC if sk2 > 1 else G.F_ACCUM), out0=part)
     else:
-        G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=pflags, out0=part, mc_out=pmc)
+        G.gemm(dx, W["encoder"], M=M, N=D, K=d.HN, b_mn=True, flags=pflags, out0=part, **pkw)
     if comm is not None:
         dcur += comm.end(pbuf)
     return dcur

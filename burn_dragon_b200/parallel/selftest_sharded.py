@@ -28,7 +28,7 @@ def case_fsdp(dev):
     data = torch.randint(0, 256, (world * B, T + 1), generator=g).to(dev)
     mine = data[rank * B:(rank + 1) * B]
     notes = []
-    for fused in ((True, False) if dev.type == "cuda" else (False,)):
+    for fused in ((True, "mc_red", "allreduce", False) if dev.type == "cuda" else (False,)):
         m = _bdh(dev)
         w = FSDP(m, lr=1e-2, fused=fused)
         if fused:
@@ -62,7 +62,7 @@ def case_tp(dev):
     x, y = data[:, :-1], data[:, 1:]
     notes = []
     for rot in ("rope", "alibi", "pope"):
-        for fused in ((True, False) if dev.type == "cuda" else (False,)):
+        for fused in ((True, "mc_red", "allreduce", False) if dev.type == "cuda" else (False,)):
             full = _bdh(dev, rot, N=128 * world)
             one = _bdh(dev, rot, N=128 * world)
             with torch.no_grad():
@@ -97,5 +97,83 @@ def case_tp(dev):
             assert abs(a.item() - b.item()) < 3e-2 * max(1.0, abs(b.item())), (rot, fused, a.item(), b.item())
             sd = w.gather_state_dict()
             assert sd["encoder"].shape == one.encoder.shape
-            notes.append(f"{rot}:{'fused' if w.fused else 'nccl'}{'+mc' if w.comm.multicast else ''}")
+            notes.append(f"{rot}:{w.comm.mode}{'+mc' if w.comm.multicast else ''}")
     return " ".join(notes)
+
+
+def _tp_reduce_once(comm, A, Bm, rows, cols, K, bf16):
+    from ..ops import gemm as G
+    buf = comm.begin("t", rows, cols)
+    G.gemm(A, Bm, M=rows, N=cols, K=K, flags=comm.flags, out0=buf.view, **buf.kw)
+    return comm.end(buf, bf16=bf16)
+
+
+def case_tp_reduce(dev):
+    """GEMM whose epilogue is the cross-rank reduction, every mode against an fp32 matmul + NCCL sum:
+    full tiles, ragged rows and columns, fp32 and bf16 results, repeated on the same buffers."""
+    from ..ops import native
+    from .tp import TPComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    notes = []
+    for mode in ("rs", "mc_red", "allreduce", False):
+        comm = TPComm(dev, None, mode)
+        for rows, cols, K in ((1024, 256, 128), (300, 64, 64), (128 * world + 40, 200, 192)):
+            for rep in range(2):
+                torch.manual_seed(11 * rank + rep + rows)
+                A = (torch.randn(rows, K, device=dev) * 0.5).to(torch.bfloat16)
+                Bm = (torch.randn(cols, K, device=dev) * 0.5).to(torch.bfloat16)
+                want = A.float() @ Bm.float().t()
+                dist.all_reduce(want)
+                for bf16 in (False, True):
+                    native.clear_status()
+                    got = _tp_reduce_once(comm, A, Bm, rows, cols, K, bf16).float()
+                    torch.cuda.synchronize()
+                    assert native.status_code() == 0, "peer flag wait timed out"
+                    tol = 6e-2 if bf16 else 2e-3
+                    err = (got - want).abs().max().item()
+                    assert err < tol * max(1.0, want.abs().max().item()), (mode, rows, cols, K, bf16, err)
+        notes.append(str(comm.mode))
+    return " ".join(notes)
+
+
+def case_tp_reduce_bw(dev):
+    """Device-timed GEMM + cross-rank reduction of its [rows, D] fp32 partial sums (bf16 result), the
+    shape of one attention-output reduction: every mode, max over ranks, with the GEMM alone for
+    reference and the NVLink roofline (bytes a GPU must receive for an fp32 reduce-scatter plus a
+    bf16 all-gather, over 770 GB/s)."""
+    import json
+    from ..ops import gemm as G
+    from . import dist_utils
+    from .tp import TPComm
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rows, cols, K = 65536, 1024, 1024
+    torch.manual_seed(rank)
+    A = (torch.randn(rows, K, device=dev) * 0.1).to(torch.bfloat16)
+    Bm = (torch.randn(cols, K, device=dev) * 0.1).to(torch.bfloat16)
+    local = torch.zeros(rows, cols, device=dev)
+
+    def timed(fn, iters=8):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return dist_utils.max_over_ranks(e0.elapsed_time(e1) / iters, dev)
+
+    out = dict(world=world, rows=rows, cols=cols, K=K,
+               gemm_only_ms=timed(lambda: G.gemm(A, Bm, M=rows, N=cols, K=K, flags=G.F_OUT_F32, out0=local)))
+    for mode in ("rs", "mc_red", "allreduce", False):
+        comm = TPComm(dev, None, mode)
+        out[str(comm.mode) + "_ms"] = timed(lambda: _tp_reduce_once(comm, A, Bm, rows, cols, K, True))
+        del comm
+    nbytes = rows * cols * (4 + 2) * (world - 1) / world
+    out["nvlink_roof_ms"] = nbytes / 770e9 * 1e3
+    out["gemm_flops"] = 2.0 * rows * cols * K
+    if rank == 0:
+        print("TP_REDUCE_BW " + json.dumps(out), flush=True)
+    return ""

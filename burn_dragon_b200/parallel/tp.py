@@ -10,10 +10,12 @@ sums over the neuron shards and have to be reduced across ranks:
     backward  d LN(a) = dy E_v    [H*M, D]
               d cur  = S^T dA + dx E   [M, D]
 
-In the fused mode the GEMM that produces each of them adds its tiles straight into every rank's
-replica through the NVSwitch (`multimem.red` in the GEMM epilogue, EPI_F_MC_RED), bracketed by
-device-side rank barriers; without multicast the partials are written locally and reduced by the
-peer-load all-reduce kernel; `fused=False` is the NCCL baseline. Weight gradients are local to the
+In the fused mode the GEMM that produces each of them is also the reduce-scatter: its epilogue
+adds every tile into the buffer of the rank that owns the tile's rows (`red.sys` through the peer
+mapping, EPI_F_PEER_RED), and a gather kernel broadcasts the finished blocks (`multimem.st`), as
+bf16 where the consumer is bf16. `fused="mc_red"` instead adds tiles into every replica at once
+with `multimem.red`, `fused="allreduce"` runs the peer-load all-reduce kernel on locally written
+partial sums, and `fused=False` is the NCCL baseline. Weight gradients are local to the
 shard (no reduction inside a TP group). The reference has no tensor parallelism.
 """
 from __future__ import annotations
@@ -32,72 +34,132 @@ from ..ops import reference as R
 
 
 class _Buf:
-    def __init__(self, view, mc, sym):
-        self.view, self.mc, self.sym = view, mc, sym
+    """One reduction in flight: `view` is the local fp32 [rows, cols] partial-sum buffer the GEMM writes
+    through, `kw` are the extra GEMM arguments (multicast address or peer pointers) for this mode."""
+
+    def __init__(self, view, sym, kw, rows, cols, block_rows=0, out16=None):
+        self.view, self.sym, self.kw = view, sym, kw
+        self.rows, self.cols, self.block_rows, self.out16 = rows, cols, block_rows, out16
 
 
 class TPComm:
-    """Reduction of [rows, D] fp32 partial sums across the TP group."""
+    """Reduction of [rows, D] fp32 partial sums across the TP group. Modes:
 
-    def __init__(self, device, group=None, fused: bool = True):
+    rs         the producing GEMM's epilogue adds each tile into the buffer of the rank that owns
+               its rows (reduce-scatter over peer mappings, overlapped with the GEMM tile by tile);
+               a gather kernel then sends every owner's finished block to all ranks, as bf16 when
+               the consumer wants bf16. Per GPU this moves (w-1)/w of the tensor in and at most as
+               much out - the all-reduce minimum - at any group size.
+    mc_red     the epilogue adds each tile into every rank's replica with one `multimem.red`
+               through the switch. Every GPU receives w copies of the tensor: only for w = 2.
+    allreduce  partial sums are written locally and reduced by the peer-load all-reduce kernel.
+    nccl       partial sums are written locally and reduced by NCCL (the baseline).
+    """
+
+    def __init__(self, device, group=None, fused=True):
         self.device, self.group = device, group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.fused = bool(fused and device.type == "cuda" and native.available())
+        mode = fused if isinstance(fused, str) else ("rs" if fused else "nccl")
+        if not (device.type == "cuda" and native.available()):
+            mode = "nccl"
         self.multicast = False
         self._bufs: Dict = {}
         self._flags = None
-        if self.fused:
+        if mode != "nccl":
             try:
                 from . import symm
                 self._symm = symm
                 self._flags = symm._Flags.get(device, group if group is not None else dist.group.WORLD)
             except Exception as e:  # noqa: BLE001
                 self.fallback_reason = repr(e)
-                self.fused = False
+                mode = "nccl"
+        self.mode = mode
+        self.fused = mode != "nccl"
         self.flags = G.F_OUT_F32 | G.F_ACCUM
 
+    def _epoch(self) -> int:
+        self._flags["epoch"] += 1
+        return self._flags["epoch"]
+
     def _barrier(self, anchor):
-        f = self._flags
-        f["epoch"] += 1
-        native.ops.rank_barrier(anchor, f["buf"].ptrs, self.rank, self.world, f["epoch"])
+        native.ops.rank_barrier(anchor, self._flags["buf"].ptrs, self.rank, self.world, self._epoch())
+
+    def _make(self, key, rows, cols) -> _Buf:
+        n = rows * cols
+        if not self.fused:
+            return _Buf(torch.zeros(rows, cols, device=self.device), None, {}, rows, cols)
+        # owner blocks of whole rows, an even number of them, so that a block is a multiple of 8 floats
+        block_rows = -(-rows // self.world)
+        block_rows += block_rows % 2
+        total = max(n, block_rows * cols * self.world)
+        total += (-total) % (8 * self.world)
+        sym = self._symm.SymmetricBuffer(total, torch.float32, self.device, self.group)
+        sym.tensor.zero_()
+        out16 = None
+        if self.mode == "rs":
+            out16 = self._symm.SymmetricBuffer(total, torch.bfloat16, self.device, self.group)
+        sym.barrier()
+        if sym.multicast_ptr:
+            self.multicast = True
+        mode = self.mode
+        if mode == "mc_red" and not sym.multicast_ptr:
+            mode = "allreduce"
+        kw = {}
+        if mode == "mc_red":
+            kw = dict(mc_out=sym.multicast_ptr)
+        elif mode == "rs":
+            kw = dict(peer_ptrs=sym.ptrs, peer_rows=block_rows)
+        b = _Buf(sym.tensor[:n].view(rows, cols), sym, kw, rows, cols, block_rows, out16)
+        b.mode = mode
+        return b
 
     def begin(self, key: str, rows: int, cols: int) -> _Buf:
         k = (key, rows, cols)
         b = self._bufs.get(k)
         if b is None:
-            n = rows * cols
-            if self.fused:
-                pad = (-n) % (4 * self.world)
-                sym = self._symm.SymmetricBuffer(n + pad, torch.float32, self.device, self.group)
-                sym.tensor.zero_()
-                sym.barrier()
-                b = _Buf(sym.tensor[:n].view(rows, cols), sym.multicast_ptr, sym)
-                if sym.multicast_ptr:
-                    self.multicast = True
-            else:
-                b = _Buf(torch.zeros(rows, cols, device=self.device), 0, None)
-            self._bufs[k] = b
-        b.view.zero_()
-        if self.fused and b.mc:
-            self.flags = G.F_OUT_F32 | G.F_MC_RED
+            b = self._bufs[k] = self._make(key, rows, cols)
+        mode = getattr(b, "mode", "nccl")
+        if mode == "rs":
+            # only the owned block receives sums; it must be zero on every rank before any tile arrives
+            lo = min(self.rank * b.block_rows, rows)
+            hi = min(lo + b.block_rows, rows)
+            if hi > lo:
+                b.view[lo:hi].zero_()
+            self._barrier(b.view)
+            self.flags = G.F_OUT_F32 | G.F_PEER_RED
+        elif mode == "mc_red":
+            b.view.zero_()
             self._barrier(b.view)          # every replica is zero before anybody's tiles arrive
+            self.flags = G.F_OUT_F32 | G.F_MC_RED
         else:
+            b.view.zero_()
             self.flags = G.F_OUT_F32 | G.F_ACCUM
         return b
 
-    def end(self, b: _Buf) -> torch.Tensor:
-        if self.fused and b.mc:
+    def end(self, b: _Buf, bf16: bool = False) -> torch.Tensor:
+        """The reduced tensor: fp32 (a view of the reduction buffer, valid until the next `begin` with
+        the same key and shape) or, with `bf16`, a fresh bf16 tensor."""
+        mode = getattr(b, "mode", "nccl")
+        if mode == "rs":
+            s, f = b.sym, self._flags
+            o = b.out16
+            native.ops.gather_blocks(s.tensor, s.ptrs, f["buf"].ptrs, s.multicast_ptr,
+                                     o.ptrs if bf16 else [], o.multicast_ptr if bf16 else 0, s.rank, s.world,
+                                     s.tensor.numel(), b.block_rows * b.cols, self._epoch(), self._symm.COLL_CTAS)
+            if bf16:
+                # the gather buffer is reused by the next reduction with this key: hand out a copy
+                return o.tensor[:b.rows * b.cols].view(b.rows, b.cols).clone()
+            return b.view
+        if mode == "mc_red":
             self._barrier(b.view)          # every rank's tiles have landed in every replica
-        elif self.fused:
-            f = self._flags
-            f["epoch"] += 1
+        elif mode == "allreduce":
             s = b.sym
-            native.ops.allreduce_scale(s.tensor, s.ptrs, f["buf"].ptrs, 0, s.rank, s.world, s.tensor.numel(), 1.0,
-                                       f["epoch"], self._symm.COLL_CTAS)
+            native.ops.allreduce_scale(s.tensor, s.ptrs, self._flags["buf"].ptrs, s.multicast_ptr, s.rank, s.world,
+                                       s.tensor.numel(), 1.0, self._epoch(), self._symm.COLL_CTAS)
         else:
             dist.all_reduce(b.view, group=self.group)
-        return b.view
+        return b.view.to(torch.bfloat16) if bf16 else b.view
 
 
 def shard_rows(w: torch.Tensor, H: int, N: int, rank: int, world: int) -> torch.Tensor:
@@ -113,7 +175,7 @@ def unshard_rows(parts, H: int, N: int) -> torch.Tensor:
 
 
 class NeuronTP:
-    def __init__(self, model: BDH, lr=1e-3, weight_decay=0.1, beta1=0.9, beta2=0.999, eps=1e-5, fused: bool = True,
+    def __init__(self, model: BDH, lr=1e-3, weight_decay=0.1, beta1=0.9, beta2=0.999, eps=1e-5, fused=True,
                  group=None):
         self.full, self.group = model, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
