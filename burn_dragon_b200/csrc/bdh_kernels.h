@@ -50,9 +50,10 @@ typedef struct {
   float drop_p;         // EPI_RELU_GATE: dropout probability on x*y
   unsigned drop_seed;
   // Reduce-scatter epilogue (flag 1024, fp32 EPI_STORE): peer_out[r] is rank r's mapping of the
-  // symmetric output buffer; rows [r*peer_rows, (r+1)*peer_rows) are added into rank r's copy.
+  // symmetric slot buffer [peer_world][peer_rows][ld_out0]; output rows [r*peer_rows, (r+1)*peer_rows)
+  // are stored into slot peer_rank of rank r's buffer.
   const long long* peer_out;
-  int peer_world;
+  int peer_world, peer_rank;
   long long peer_rows;
 } BdhGemmDesc;
 
@@ -137,13 +138,13 @@ int bdh_graph_spmm_relu(const void* x_bf16, const void* w_bf16, const int* ell_c
 int bdh_allreduce_scale(const long long* buf_ptrs, const long long* flag_ptrs, long long mc_ptr, int rank,
                         int world, long long n_floats, float scale, unsigned epoch, int ctas, int* status,
                         cudaStream_t s);
-// All-gather half of a reduce-scatter done by GEMM epilogues (flag 1024): rank r sends floats
-// [r*block_floats, (r+1)*block_floats) of its fp32 buffer to every rank - in place as fp32
-// (out_ptrs == nullptr) or rounded to bf16 into the symmetric buffer out_ptrs / out_mc.
-// n_floats % 8 == 0 and block_floats % 8 == 0. The reference has no multi-device path.
-int bdh_gather_blocks(const long long* buf_ptrs, const long long* flag_ptrs, long long mc_ptr,
-                      const long long* out_ptrs, long long out_mc, int rank, int world, long long n_floats,
-                      long long block_floats, unsigned epoch, int ctas, int* status, cudaStream_t s);
+// Second half of a reduce-scatter done by GEMM epilogues (flag 1024): rank r adds up the `world`
+// slots of block_floats fp32 partial sums in its slot buffer and sends the result to position
+// r*block_floats of every rank's output buffer (out_ptrs / out_mc, world*block_floats elements),
+// as fp32 or rounded to bf16. block_floats % 8 == 0. The reference has no multi-device path.
+int bdh_gather_blocks(const long long* slot_ptrs, const long long* flag_ptrs, const long long* out_ptrs,
+                      long long out_mc, int out_bf16, int rank, int world, long long block_floats,
+                      unsigned epoch, int ctas, int* status, cudaStream_t s);
 // Reduce-scatter of fp32 gradients + AdamW on the owned slice + all-gather of bf16 parameters.
 // master / m / v hold only the owned slice (n_floats/world elements, last rank takes the remainder).
 int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag_ptrs, long long grad_mc,

@@ -45,7 +45,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
           int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed,
-          at::IntArrayRef peer_ptrs, int64_t peer_rows) {
+          at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -68,10 +68,10 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   d.drop_p = drop_p; d.drop_seed = static_cast<unsigned>(drop_seed);
   if (mc_out != 0) d.out0 = reinterpret_cast<void*>(mc_out);   // multicast mapping of out0 (EPI_F_MC_RED)
   long long peers[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  if (!peer_ptrs.empty()) {                                      // reduce-scatter epilogue (EPI_F_PEER_RED)
+  if (!peer_ptrs.empty()) {                                      // reduce-scatter epilogue (EPI_F_PEER_RS)
     TORCH_CHECK(peer_ptrs.size() <= 8, "at most 8 peers");
     for (size_t i = 0; i < peer_ptrs.size(); ++i) peers[i] = peer_ptrs[i];
-    d.peer_out = peers; d.peer_world = static_cast<int>(peer_ptrs.size()); d.peer_rows = peer_rows;
+    d.peer_out = peers; d.peer_world = static_cast<int>(peer_ptrs.size()); d.peer_rows = peer_rows; d.peer_rank = static_cast<int>(peer_rank);
   }
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
@@ -163,16 +163,15 @@ void allreduce_scale(const Tensor& anchor, at::IntArrayRef buf_ptrs, at::IntArra
                                status_word().data_ptr<int>(), cur_stream()), "allreduce_scale");
 }
 
-void gather_blocks(const Tensor& anchor, at::IntArrayRef buf_ptrs, at::IntArrayRef flag_ptrs, int64_t mc_ptr,
-                   at::IntArrayRef out_ptrs, int64_t out_mc, int64_t rank, int64_t world, int64_t n_floats,
+void gather_blocks(const Tensor& anchor, at::IntArrayRef slot_ptrs, at::IntArrayRef flag_ptrs,
+                   at::IntArrayRef out_ptrs, int64_t out_mc, bool out_bf16, int64_t rank, int64_t world,
                    int64_t block_floats, int64_t epoch, int64_t ctas) {
   c10::cuda::CUDAGuard guard(anchor.device());
-  TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world);
-  TORCH_CHECK(out_ptrs.empty() || (int64_t)out_ptrs.size() == world);
-  auto b = as_ptrs(buf_ptrs), f = as_ptrs(flag_ptrs), o = as_ptrs(out_ptrs);
-  check_rc(bdh_gather_blocks(b.data(), f.data(), mc_ptr, o.empty() ? nullptr : o.data(), out_mc, rank, world,
-                             n_floats, block_floats, (unsigned)epoch, ctas, status_word().data_ptr<int>(),
-                             cur_stream()), "gather_blocks");
+  TORCH_CHECK((int64_t)slot_ptrs.size() == world && (int64_t)flag_ptrs.size() == world &&
+              (int64_t)out_ptrs.size() == world);
+  auto b = as_ptrs(slot_ptrs), f = as_ptrs(flag_ptrs), o = as_ptrs(out_ptrs);
+  check_rc(bdh_gather_blocks(b.data(), f.data(), o.data(), out_mc, out_bf16 ? 1 : 0, rank, world, block_floats,
+                             (unsigned)epoch, ctas, status_word().data_ptr<int>(), cur_stream()), "gather_blocks");
 }
 
 void rs_adamw_ag(const Tensor& anchor, at::IntArrayRef grad_ptrs, at::IntArrayRef flag_ptrs, int64_t grad_mc,
@@ -292,7 +291,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank) -> ()");
   m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
   m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
@@ -305,8 +304,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("status() -> Tensor");
   m.def("allreduce_scale(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int rank, int world, "
         "int n_floats, float scale, int epoch, int ctas) -> ()");
-  m.def("gather_blocks(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int[] out_ptrs, int out_mc, "
-        "int rank, int world, int n_floats, int block_floats, int epoch, int ctas) -> ()");
+  m.def("gather_blocks(Tensor anchor, int[] slot_ptrs, int[] flag_ptrs, int[] out_ptrs, int out_mc, bool out_bf16, "
+        "int rank, int world, int block_floats, int epoch, int ctas) -> ()");
   m.def("rs_adamw_ag(Tensor anchor, int[] grad_ptrs, int[] flag_ptrs, int grad_mc, int[] shadow_ptrs, int rank, "
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");

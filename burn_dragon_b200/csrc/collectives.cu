@@ -162,45 +162,58 @@ rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, 
   cta_barrier_all_ranks(p, 2 * epoch + 2, status);
 }
 
-// Second half of a reduce-scatter done by GEMM epilogues (EPI_F_PEER_RED): after every rank's
-// tiles have been added into the owners' blocks, rank r holds the finished sums of float4 elements
-// [r*per4, min(n4, (r+1)*per4)) of the fp32 buffer `p`. This kernel sends that block to every rank:
-// as fp32 in place (OUT_BF16 = false), or rounded to bf16 into the symmetric buffer `q` (half the
-// NVLink bytes, and the consumer's conversion pass disappears). One multimem.st through the switch
-// when the destination has a multicast mapping, else one store per peer.
+// Second half of a reduce-scatter done by GEMM epilogues (EPI_F_PEER_RS): slot s of this rank's
+// buffer `p` holds rank s's partial sums for the block of rows this rank owns (per4 float4 each).
+// The owner adds the slots up (local reads, fixed order: the result does not depend on timing) and
+// sends its block to position rank*per4 of every rank's output buffer `q`: as fp32, or rounded to
+// bf16 (half the NVLink bytes, and the consumer's conversion pass disappears). One multimem.st
+// through the switch when the output has a multicast mapping, else one store per peer.
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(COLL_THREADS)
-gather_blocks_kernel(CollPeers p, CollPeers q, long long n4, long long per4, uint32_t epoch, int* status) {
+gather_blocks_kernel(CollPeers p, CollPeers q, long long per4, uint32_t epoch, int* status) {
   if (!cta_barrier_all_ranks(p, 2 * epoch + 1, status)) return;
-  const long long lo = per4 * p.rank < n4 ? per4 * p.rank : n4;
-  const long long hi = lo + per4 < n4 ? lo + per4 : n4;
   const float4* src = static_cast<const float4*>(p.buf[p.rank]);
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
+  auto slot_sum = [&](long long j) {
+    float4 v[COLL_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < COLL_MAX_RANKS; ++r)
+      if (r < p.world) v[r] = __ldcs(src + r * per4 + j);
+    float4 s = v[0];
+#pragma unroll
+    for (int r = 1; r < COLL_MAX_RANKS; ++r)
+      if (r < p.world) {
+        s.x += v[r].x; s.y += v[r].y; s.z += v[r].z; s.w += v[r].w;
+      }
+    return s;
+  };
   if constexpr (OUT_BF16) {
-    // two float4 -> 8 bf16 = one 16-byte store (lo, hi and per4 are even: the host checks)
-    for (long long i = lo / 2 + tid; i < hi / 2; i += nth) {
-      const float4 a = src[2 * i], b = src[2 * i + 1];
+    // two float4 -> 8 bf16 = one 16-byte store (per4 is even: the host checks)
+    const long long base = p.rank * (per4 / 2);
+    for (long long i = tid; i < per4 / 2; i += nth) {
+      const float4 a = slot_sum(2 * i), b = slot_sum(2 * i + 1);
       uint4 u;
       u.x = pack_bf16x2(a.x, a.y); u.y = pack_bf16x2(a.z, a.w);
       u.z = pack_bf16x2(b.x, b.y); u.w = pack_bf16x2(b.z, b.w);
       if (q.mc) {
-        multimem_st_b32x4(static_cast<uint4*>(q.mc) + i, u);
+        multimem_st_b32x4(static_cast<uint4*>(q.mc) + base + i, u);
       } else {
 #pragma unroll
         for (int r = 0; r < COLL_MAX_RANKS; ++r)
-          if (r < q.world) static_cast<uint4*>(q.buf[r])[i] = u;
+          if (r < q.world) static_cast<uint4*>(q.buf[r])[base + i] = u;
       }
     }
   } else {
-    for (long long i = lo + tid; i < hi; i += nth) {
-      const float4 a = src[i];
-      if (p.mc) {
-        multimem_st_f32x4(static_cast<float4*>(p.mc) + i, a);
+    const long long base = p.rank * per4;
+    for (long long i = tid; i < per4; i += nth) {
+      const float4 a = slot_sum(i);
+      if (q.mc) {
+        multimem_st_f32x4(static_cast<float4*>(q.mc) + base + i, a);
       } else {
 #pragma unroll
         for (int r = 0; r < COLL_MAX_RANKS; ++r)
-          if (r < p.world && r != p.rank) static_cast<float4*>(p.buf[r])[i] = a;
+          if (r < q.world) static_cast<float4*>(q.buf[r])[base + i] = a;
       }
     }
   }
@@ -267,20 +280,18 @@ extern "C" int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 
-extern "C" int bdh_gather_blocks(const long long* buf_ptrs, const long long* flag_ptrs, long long mc_ptr,
-                                 const long long* out_ptrs, long long out_mc, int rank, int world,
-                                 long long n_floats, long long block_floats, unsigned epoch, int ctas, int* status,
-                                 cudaStream_t s) {
-  if (world < 1 || world > COLL_MAX_RANKS || (n_floats % 8) || (block_floats % 8) || block_floats < 8 || ctas < 1)
+extern "C" int bdh_gather_blocks(const long long* slot_ptrs, const long long* flag_ptrs, const long long* out_ptrs,
+                                 long long out_mc, int out_bf16, int rank, int world, long long block_floats,
+                                 unsigned epoch, int ctas, int* status, cudaStream_t s) {
+  if (world < 1 || world > COLL_MAX_RANKS || (block_floats % 8) || block_floats < 8 || ctas < 1 || !out_ptrs)
     return BDH_ERR_ARGUMENT;
   CollPeers p, q;
-  fill_peers(p, buf_ptrs, flag_ptrs, mc_ptr, rank, world);
-  if (out_ptrs) {
-    fill_peers(q, out_ptrs, nullptr, out_mc, rank, world);
-    gather_blocks_kernel<true><<<ctas, COLL_THREADS, 0, s>>>(p, q, n_floats / 4, block_floats / 4, epoch, status);
-  } else {
-    gather_blocks_kernel<false><<<ctas, COLL_THREADS, 0, s>>>(p, p, n_floats / 4, block_floats / 4, epoch, status);
-  }
+  fill_peers(p, slot_ptrs, flag_ptrs, 0, rank, world);
+  fill_peers(q, out_ptrs, nullptr, out_mc, rank, world);
+  if (out_bf16)
+    gather_blocks_kernel<true><<<ctas, COLL_THREADS, 0, s>>>(p, q, block_floats / 4, epoch, status);
+  else
+    gather_blocks_kernel<false><<<ctas, COLL_THREADS, 0, s>>>(p, q, block_floats / 4, epoch, status);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 

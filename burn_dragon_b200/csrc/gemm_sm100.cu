@@ -117,6 +117,7 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   g.b = {d->b_off[0], d->b_off[1], d->b_off[2], d->b_off[3]};
   g.causal_tiles = d->causal_tiles;
   g.causal_k = d->causal_k;
+  g.tile_shift = 0;
   g.status = d->status;
   EpiParams& e = g.epi;
   e.out0 = d->out0; e.out1 = d->out1; e.in0 = d->in0; e.in1 = d->in1;
@@ -130,12 +131,22 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   e.drop_p = d->drop_p; e.drop_seed = d->drop_seed;
   e.peer_rows = d->peer_rows > 0 ? d->peer_rows : 1;
   e.peer_world = d->peer_world;
+  e.peer_rank = d->peer_rank;
   for (int i = 0; i < GEMM_MAX_PEERS; ++i)
     e.peer_out[i] = (d->peer_out && i < d->peer_world) ? reinterpret_cast<float*>(d->peer_out[i]) : nullptr;
-  if (d->flags & EPI_F_PEER_RED) {
+  if (d->flags & EPI_F_PEER_RS) {
     if (d->epi != EPI_STORE || !d->peer_out || d->peer_world < 1 || d->peer_world > GEMM_MAX_PEERS ||
-        d->peer_rows < 1)
+        d->peer_rows < 1 || d->peer_rank < 0 || d->peer_rank >= d->peer_world)
       return BDH_ERR_ARGUMENT;
+    if (d->causal_tiles == 0) {
+      // Tiles are walked with z1 slowest, then z0, then rows. One pass over all owners takes `cycle`
+      // consecutive tiles; rank r starts r/world of a cycle ahead, so at any moment the ranks store
+      // into different owners instead of all into the same one.
+      const long long per_z = ((d->M + GEMM_BM - 1) / GEMM_BM) * ((d->N + bn - 1) / bn);
+      const long long total = per_z * d->nz0 * d->nz1;
+      const long long cycle = (d->c_off[0] >= d->c_off[1] || d->nz1 == 1) ? per_z * d->nz0 : total;
+      g.tile_shift = static_cast<int>((d->peer_rank * (cycle / d->peer_world)) % total);
+    }
   }
 
   const int max_ctas = d->max_ctas > 0 ? d->max_ctas : num_sms();

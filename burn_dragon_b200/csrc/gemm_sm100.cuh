@@ -44,9 +44,11 @@ enum EpiFlags : int {
   EPI_F_ATOMIC = 512,      // EPI_STORE fp32: out0 += tile with red.global.add (split-K partial sums)
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
-  EPI_F_PEER_RED = 1024,   // EPI_STORE fp32: reduce-scatter epilogue. Output rows are split into blocks of
-                           // peer_rows; the tile is added (red.sys) into the buffer of the rank that owns
-                           // its rows, through that rank's peer mapping peer_out[owner]
+  EPI_F_PEER_RS = 1024,    // EPI_STORE fp32: reduce-scatter epilogue. Output rows are split into blocks of
+                           // peer_rows, block b is owned by rank b. The tile is stored through the owner's
+                           // peer mapping peer_out[owner] into the slot this rank has there: the owner's
+                           // buffer is [world slots][peer_rows][ld] and slot s receives rank s's partial
+                           // sums, which the owner adds up afterwards (collectives.cu: gather_blocks)
 };
 
 constexpr int GEMM_MAX_PEERS = 8;
@@ -75,9 +77,9 @@ struct EpiParams {
   int flags;
   float drop_p;          // EPI_RELU_GATE: dropout probability applied to x*y (0: off)
   uint32_t drop_seed;    // EPI_RELU_GATE: seed of the counter-based dropout mask
-  float* peer_out[GEMM_MAX_PEERS];   // EPI_F_PEER_RED: every rank's mapping of the (symmetric) output buffer
-  long long peer_rows;               // EPI_F_PEER_RED: rows per owner block
-  int peer_world;
+  float* peer_out[GEMM_MAX_PEERS];   // EPI_F_PEER_RS: every rank's mapping of the (symmetric) slot buffer
+  long long peer_rows;               // EPI_F_PEER_RS: rows per owner block
+  int peer_world, peer_rank;
 };
 
 struct GemmArgs {
@@ -86,6 +88,8 @@ struct GemmArgs {
   OperandOffsets a, b;
   int causal_tiles;  // 0: all tiles; 1: only tiles that touch s < t (n0 <= m0+BM-1); 2: only tiles with s > t
   int causal_k;      // 1: contract only k < m0 + BM
+  int tile_shift;    // tiles are visited in the order (t + tile_shift) mod total (reduce-scatter epilogue:
+                     // each rank starts at another owner's rows so that no GPU is everybody's target)
   EpiParams epi;
   int* status;
 };
@@ -207,7 +211,7 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
   if (epi == EPI_STORE)
-    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RED));
+    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS));
   if (epi == EPI_RELU) return true;
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -399,12 +403,13 @@ __device__ __forceinline__ void load_raw_32(const __nv_bfloat16* base, long long
   }
 }
 
-constexpr int EPI_RED_FLAGS = EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RED;
+constexpr int EPI_RED_FLAGS = EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS;
 
-__device__ __forceinline__ float* peer_row_base(const EpiParams& e, long long row) {
+// Address of output row `row` inside the slot this rank owns in the buffer of the row's owner.
+__device__ __forceinline__ float* peer_slot_row(const EpiParams& e, long long row) {
   long long owner = row / e.peer_rows;
   if (owner >= e.peer_world) owner = e.peer_world - 1;
-  return e.peer_out[owner];
+  return e.peer_out[owner] + (e.peer_rank * e.peer_rows + (row - owner * e.peer_rows)) * e.ld_out0;
 }
 
 __device__ __forceinline__ void red_add_f32x4(float* p, const float4& u, int flags) {
@@ -412,22 +417,19 @@ __device__ __forceinline__ void red_add_f32x4(float* p, const float4& u, int fla
     asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y),
                  "f"(u.z), "f"(u.w)
                  : "memory");
-  else if (flags & EPI_F_PEER_RED)
-    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y), "f"(u.z),
-                 "f"(u.w)
-                 : "memory");
   else
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(u.x), "f"(u.y), "f"(u.z), "f"(u.w)
                  : "memory");
 }
 
-// Adds one warp's full 32x32 fp32 tile (thread = row, v = its 32 columns) into global, multicast or
-// peer memory. The tile is transposed through 4 KB of shared memory (16-byte slots, XOR-swizzled by
-// row) so that 8 lanes cover one 128-byte row segment: every reduction request that leaves the SM -
-// and, for peer and multicast targets, every NVLink packet - carries a full 128 bytes instead of 16.
+// Sends one warp's full 32x32 fp32 tile (thread = row, v = its 32 columns) to global, multicast or
+// peer memory: a reduction-add (EPI_F_ATOMIC, EPI_F_MC_RED) or a plain store into the owner's slot
+// (EPI_F_PEER_RS). The tile is transposed through 4 KB of shared memory (16-byte slots, XOR-swizzled
+// by row) so that 8 lanes cover one 128-byte row segment: every request that leaves the SM - and,
+// for peer and multicast targets, every NVLink packet - carries a full 128 bytes instead of 16.
 // r0 = output row of lane 0, c = first output column; the caller has checked 16-byte alignment.
-__device__ __forceinline__ void red_tile_coalesced(const EpiParams& e, long long r0, long long c,
-                                                   const float (&v)[32], float4* scratch, int lane) {
+__device__ __forceinline__ void send_tile_coalesced(const EpiParams& e, long long r0, long long c,
+                                                    const float (&v)[32], float4* scratch, int lane) {
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     scratch[lane * 8 + (i ^ (lane & 7))] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -438,8 +440,10 @@ __device__ __forceinline__ void red_tile_coalesced(const EpiParams& e, long long
     const int row = 4 * j + sub;
     const float4 u = scratch[row * 8 + (ch ^ (row & 7))];
     const long long rr = r0 + row;
-    float* base = (e.flags & EPI_F_PEER_RED) ? peer_row_base(e, rr) : static_cast<float*>(e.out0);
-    red_add_f32x4(base + rr * e.ld_out0 + c + 4 * ch, u, e.flags);
+    if (e.flags & EPI_F_PEER_RS)
+      *reinterpret_cast<float4*>(peer_slot_row(e, rr) + c + 4 * ch) = u;
+    else
+      red_add_f32x4(static_cast<float*>(e.out0) + rr * e.ld_out0 + c + 4 * ch, u, e.flags);
   }
   __syncwarp();
 }
@@ -472,16 +476,16 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
           if (i < valid)
             asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
       }
-    } else if (e.flags & EPI_F_PEER_RED) {
-      float* p = peer_row_base(e, r) + r * e.ld_out0 + c;
+    } else if (e.flags & EPI_F_PEER_RS) {
+      float* p = peer_slot_row(e, r) + c;
       if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          red_add_f32x4(p + 4 * i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]), e.flags);
+          reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (i < valid) asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
+          if (i < valid) p[i] = v[i];
       }
     } else if (e.flags & EPI_F_ATOMIC) {
       float* p = static_cast<float*>(e.out0) + r * e.ld_out0 + c;
@@ -587,8 +591,9 @@ struct TileCoord {
 
 template <int BN>
 struct TileWalker {
-  int tiles_m, tiles_n, per_z, total, nz0, mode;
+  int tiles_m, tiles_n, per_z, total, nz0, mode, shift;
   __device__ TileWalker(const GemmArgs& g) {
+    shift = g.tile_shift;
     tiles_m = (g.M + GEMM_BM - 1) / GEMM_BM;
     tiles_n = (g.N + BN - 1) / BN;
     nz0 = g.nz0;
@@ -611,6 +616,8 @@ struct TileWalker {
   }
   __device__ __forceinline__ TileCoord decode(int t) const {
     TileCoord tc;
+    t += shift;
+    if (t >= total) t -= total;
     int z = t / per_z, r = t - z * per_z;
     tc.z0 = z % nz0;
     tc.z1 = z / nz0;
@@ -849,7 +856,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (((reinterpret_cast<uintptr_t>(e.out0) + 4 * static_cast<uintptr_t>(cc)) & 15) == 0) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] *= e.alpha;
-                red_tile_coalesced(e, r0, cc, v,
+                send_tile_coalesced(e, r0, cc, v,
                                    reinterpret_cast<float4*>(smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES), lane);
                 continue;
               }

@@ -160,7 +160,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     else:
         # neuron-sharded: this rank's scores cover its slice of the neurons, so S V is a partial sum;
         # the GEMM epilogue adds it into every rank's replica through the switch
-        buf = comm.begin("a", H * M, D)
+        buf = comm.begin("a", H * M, D, launches=1 if rho_in is None else 2)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
                c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, **buf.kw)
         if rho_in is not None:
@@ -257,7 +257,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     if comm is None:
         part, pflags, pkw = dcur, G.F_OUT_F32 | G.F_ACCUM, {}
     else:
-        pbuf = comm.begin("dcur", M, D)        # partial sums over the neuron shards: dV and the encoder path
+        pbuf = comm.begin("dcur", M, D, launches=H + 1)        # partial sums over the neuron shards: dV and the encoder path
         part, pflags, pkw = pbuf.view, comm.flags, pbuf.kw
     for h in range(H):
         G.gemm(S[h * T:], da[h * M:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),

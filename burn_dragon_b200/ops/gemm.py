@@ -21,7 +21,7 @@ from . import native
 
 EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
 F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED, F_ATOMIC = 1, 2, 4, 8, 16, 32, 128, 256, 512
-F_PEER_RED = 1024
+F_PEER_RS = 1024
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -51,13 +51,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
          tma_epilogue: bool = True, mc_out: int = 0, drop_p: float = 0.0, drop_seed: int = 0,
-         peer_ptrs: Sequence[int] = (), peer_rows: int = 0) -> None:
+         peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),
-                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows))
+                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank))
 
 
 # ------------------------------------------------------------------------------------------------

@@ -11,9 +11,9 @@ sums over the neuron shards and have to be reduced across ranks:
               d cur  = S^T dA + dx E   [M, D]
 
 In the fused mode the GEMM that produces each of them is also the reduce-scatter: its epilogue
-adds every tile into the buffer of the rank that owns the tile's rows (`red.sys` through the peer
-mapping, EPI_F_PEER_RED), and a gather kernel broadcasts the finished blocks (`multimem.st`), as
-bf16 where the consumer is bf16. `fused="mc_red"` instead adds tiles into every replica at once
+stores every tile through the peer mapping of the rank that owns the tile's rows (EPI_F_PEER_RS),
+and a gather kernel adds up each owner's slots and broadcasts the finished blocks (`multimem.st`),
+as bf16 where the consumer is bf16. `fused="mc_red"` instead adds tiles into every replica at once
 with `multimem.red`, `fused="allreduce"` runs the peer-load all-reduce kernel on locally written
 partial sums, and `fused=False` is the NCCL baseline. Weight gradients are local to the
 shard (no reduction inside a TP group). The reference has no tensor parallelism.
@@ -34,26 +34,32 @@ from ..ops import reference as R
 
 
 class _Buf:
-    """One reduction in flight: `view` is the local fp32 [rows, cols] partial-sum buffer the GEMM writes
-    through, `kw` are the extra GEMM arguments (multicast address or peer pointers) for this mode."""
+    """One reduction in flight: `view` is the fp32 [rows, cols] tensor handed to the GEMM as out0 (the
+    local partial-sum buffer, or - reduce-scatter mode - only the carrier of the leading dimension),
+    `kw` are the extra GEMM arguments of the mode (multicast address or peer pointers)."""
 
-    def __init__(self, view, sym, kw, rows, cols, block_rows=0, out16=None):
-        self.view, self.sym, self.kw = view, sym, kw
-        self.rows, self.cols, self.block_rows, self.out16 = rows, cols, block_rows, out16
+    def __init__(self, mode, view, sym, kw, rows, cols, block_rows=0):
+        self.mode, self.view, self.sym, self.kw = mode, view, sym, kw
+        self.rows, self.cols, self.block_rows = rows, cols, block_rows
+        self.out = {}       # dtype -> symmetric output buffer of the gather (reduce-scatter mode)
 
 
 class TPComm:
     """Reduction of [rows, D] fp32 partial sums across the TP group. Modes:
 
-    rs         the producing GEMM's epilogue adds each tile into the buffer of the rank that owns
-               its rows (reduce-scatter over peer mappings, overlapped with the GEMM tile by tile);
-               a gather kernel then sends every owner's finished block to all ranks, as bf16 when
-               the consumer wants bf16. Per GPU this moves (w-1)/w of the tensor in and at most as
-               much out - the all-reduce minimum - at any group size.
+    rs         the producing GEMM is also the reduce-scatter: its epilogue stores each tile through
+               the peer mapping of the rank that owns the tile's rows, into the slot this rank has
+               in the owner's buffer, tile by tile while the GEMM runs. A gather kernel then adds up
+               each owner's slots and sends the finished block to all ranks, as bf16 when the
+               consumer wants bf16. Per GPU this moves (w-1)/w of the tensor in fp32 and (w-1)/w of
+               it in the output type, with no atomics, no zero-fill and a fixed summation order.
+               Needs a single producing launch per reduction; buffers that several launches add
+               into (`launches > 1`) use `allreduce`.
     mc_red     the epilogue adds each tile into every rank's replica with one `multimem.red`
-               through the switch. Every GPU receives w copies of the tensor: only for w = 2.
-    allreduce  partial sums are written locally and reduced by the peer-load all-reduce kernel.
-    nccl       partial sums are written locally and reduced by NCCL (the baseline).
+               through the switch. Every GPU receives w copies of the tensor: only sensible for w = 2.
+    allreduce  partial sums are accumulated locally and reduced by the all-reduce kernel
+               (`multimem.ld_reduce` + `multimem.st`, or peer loads and stores).
+    nccl       partial sums are accumulated locally and reduced by NCCL (the baseline).
     """
 
     def __init__(self, device, group=None, fused=True):
@@ -85,50 +91,42 @@ class TPComm:
     def _barrier(self, anchor):
         native.ops.rank_barrier(anchor, self._flags["buf"].ptrs, self.rank, self.world, self._epoch())
 
-    def _make(self, key, rows, cols) -> _Buf:
+    def _make(self, rows, cols, launches) -> _Buf:
         n = rows * cols
-        if not self.fused:
-            return _Buf(torch.zeros(rows, cols, device=self.device), None, {}, rows, cols)
+        mode = self.mode
+        if mode == "rs" and launches > 1:
+            mode = "allreduce"
+        if mode == "nccl":
+            return _Buf(mode, torch.zeros(rows, cols, device=self.device), None, {}, rows, cols)
         # owner blocks of whole rows, an even number of them, so that a block is a multiple of 8 floats
         block_rows = -(-rows // self.world)
         block_rows += block_rows % 2
-        total = max(n, block_rows * cols * self.world)
+        total = block_rows * cols * self.world
         total += (-total) % (8 * self.world)
         sym = self._symm.SymmetricBuffer(total, torch.float32, self.device, self.group)
         sym.tensor.zero_()
-        out16 = None
-        if self.mode == "rs":
-            out16 = self._symm.SymmetricBuffer(total, torch.bfloat16, self.device, self.group)
         sym.barrier()
         if sym.multicast_ptr:
             self.multicast = True
-        mode = self.mode
         if mode == "mc_red" and not sym.multicast_ptr:
             mode = "allreduce"
         kw = {}
         if mode == "mc_red":
             kw = dict(mc_out=sym.multicast_ptr)
         elif mode == "rs":
-            kw = dict(peer_ptrs=sym.ptrs, peer_rows=block_rows)
-        b = _Buf(sym.tensor[:n].view(rows, cols), sym, kw, rows, cols, block_rows, out16)
-        b.mode = mode
-        return b
+            kw = dict(peer_ptrs=sym.ptrs, peer_rows=block_rows, peer_rank=self.rank)
+        return _Buf(mode, sym.tensor[:n].view(rows, cols), sym, kw, rows, cols, block_rows)
 
-    def begin(self, key: str, rows: int, cols: int) -> _Buf:
-        k = (key, rows, cols)
+    def begin(self, key: str, rows: int, cols: int, launches: int = 1) -> _Buf:
+        k = (key, rows, cols, launches > 1)
         b = self._bufs.get(k)
         if b is None:
-            b = self._bufs[k] = self._make(key, rows, cols)
-        mode = getattr(b, "mode", "nccl")
-        if mode == "rs":
-            # only the owned block receives sums; it must be zero on every rank before any tile arrives
-            lo = min(self.rank * b.block_rows, rows)
-            hi = min(lo + b.block_rows, rows)
-            if hi > lo:
-                b.view[lo:hi].zero_()
-            self._barrier(b.view)
-            self.flags = G.F_OUT_F32 | G.F_PEER_RED
-        elif mode == "mc_red":
+            b = self._bufs[k] = self._make(rows, cols, launches)
+        if b.mode == "rs":
+            # nothing to prepare: every slot is overwritten, and the previous gather's closing barrier
+            # has already ordered this step's stores after the owners' reads
+            self.flags = G.F_OUT_F32 | G.F_PEER_RS
+        elif b.mode == "mc_red":
             b.view.zero_()
             self._barrier(b.view)          # every replica is zero before anybody's tiles arrive
             self.flags = G.F_OUT_F32 | G.F_MC_RED
@@ -138,22 +136,23 @@ class TPComm:
         return b
 
     def end(self, b: _Buf, bf16: bool = False) -> torch.Tensor:
-        """The reduced tensor: fp32 (a view of the reduction buffer, valid until the next `begin` with
+        """The reduced tensor: fp32 (a view of a reduction buffer, valid until the next `begin` with
         the same key and shape) or, with `bf16`, a fresh bf16 tensor."""
-        mode = getattr(b, "mode", "nccl")
-        if mode == "rs":
-            s, f = b.sym, self._flags
-            o = b.out16
-            native.ops.gather_blocks(s.tensor, s.ptrs, f["buf"].ptrs, s.multicast_ptr,
-                                     o.ptrs if bf16 else [], o.multicast_ptr if bf16 else 0, s.rank, s.world,
-                                     s.tensor.numel(), b.block_rows * b.cols, self._epoch(), self._symm.COLL_CTAS)
-            if bf16:
-                # the gather buffer is reused by the next reduction with this key: hand out a copy
-                return o.tensor[:b.rows * b.cols].view(b.rows, b.cols).clone()
-            return b.view
-        if mode == "mc_red":
+        if b.mode == "rs":
+            dt = torch.bfloat16 if bf16 else torch.float32
+            o = b.out.get(dt)
+            if o is None:
+                o = b.out[dt] = self._symm.SymmetricBuffer(b.sym.tensor.numel(), dt, self.device, self.group)
+                o.barrier()
+            s = b.sym
+            native.ops.gather_blocks(s.tensor, s.ptrs, self._flags["buf"].ptrs, o.ptrs, o.multicast_ptr, bf16,
+                                     s.rank, s.world, b.block_rows * b.cols, self._epoch(), self._symm.COLL_CTAS)
+            res = o.tensor[:b.rows * b.cols].view(b.rows, b.cols)
+            # the gather buffer is reused by the next reduction with this key: hand out a copy
+            return res.clone() if bf16 else res
+        if b.mode == "mc_red":
             self._barrier(b.view)          # every rank's tiles have landed in every replica
-        elif mode == "allreduce":
+        elif b.mode == "allreduce":
             s = b.sym
             native.ops.allreduce_scale(s.tensor, s.ptrs, self._flags["buf"].ptrs, s.multicast_ptr, s.rank, s.world,
                                        s.tensor.numel(), 1.0, self._epoch(), self._symm.COLL_CTAS)
