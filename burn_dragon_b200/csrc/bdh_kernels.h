@@ -84,6 +84,13 @@ int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* d
 int bdh_pope_bwd(const void* dq_bf16, const void* x_bf16, const void* dxg_bf16, const float* freqs, void* dx_bf16,
                  long long M, int H, int N, int T, int pos0, cudaStream_t s);
 
+// L1 row normalisation of strictly causal scores S [rows, T] (row = (batch, head, t); columns
+// s < t), the `forward_fast` attention (reference: src/model/attention.rs:142-175):
+// forward S <- S / r with r = sum|S| + 1e-6 (stored); backward G <- (G - sign(Sn) sum(G Sn)) / r.
+int bdh_rownorm_fwd(void* scores_bf16, float* rnorm, long long rows, int T, int ld, cudaStream_t s);
+int bdh_rownorm_bwd(void* grad_bf16, const void* normed_bf16, const float* rnorm, long long rows, int T, int ld,
+                    cudaStream_t s);
+
 // ---- loss ------------------------------------------------------------------------------------
 // Mean cross-entropy over rows of fp32 logits [rows, V] (V <= 1024); writes per-row loss and
 // dlogits (bf16) = (softmax - onehot) * grad_scale.  (reference: src/model/loss.rs:5-18)

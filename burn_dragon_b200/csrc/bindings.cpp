@@ -76,6 +76,22 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
 
+void rownorm_fwd(Tensor& scores, Tensor& rnorm, int64_t T) {
+  c10::cuda::CUDAGuard guard(scores.device());
+  TORCH_CHECK(scores.is_cuda() && scores.dim() == 2 && scores.scalar_type() == at::kBFloat16 && scores.stride(1) == 1);
+  TORCH_CHECK(rnorm.is_cuda() && rnorm.is_contiguous() && rnorm.scalar_type() == at::kFloat && rnorm.numel() == scores.size(0));
+  check_rc(bdh_rownorm_fwd(scores.data_ptr(), rnorm.data_ptr<float>(), scores.size(0), T, scores.stride(0), cur_stream()),
+           "rownorm_fwd");
+}
+void rownorm_bwd(Tensor& grad, const Tensor& normed, const Tensor& rnorm, int64_t T) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  TORCH_CHECK(grad.is_cuda() && grad.dim() == 2 && grad.scalar_type() == at::kBFloat16 && grad.stride(1) == 1);
+  TORCH_CHECK(normed.scalar_type() == at::kBFloat16 && normed.sizes() == grad.sizes() && normed.stride(0) == grad.stride(0));
+  TORCH_CHECK(rnorm.is_contiguous() && rnorm.scalar_type() == at::kFloat && rnorm.numel() == grad.size(0));
+  check_rc(bdh_rownorm_bwd(grad.data_ptr(), normed.data_ptr(), rnorm.data_ptr<float>(), grad.size(0), T, grad.stride(0),
+                           cur_stream()), "rownorm_bwd");
+}
+
 void check_rows(const Tensor& t, int64_t D, at::ScalarType st, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == st && t.size(-1) == D, name,
               ": expected a contiguous CUDA tensor with last dim ", D);
@@ -302,6 +318,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("adamw(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p16, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale) -> ()");
   m.def("status() -> Tensor");
+  m.def("rownorm_fwd(Tensor(a!) scores, Tensor(b!) rnorm, int T) -> ()");
+  m.def("rownorm_bwd(Tensor(a!) grad, Tensor normed, Tensor rnorm, int T) -> ()");
   m.def("allreduce_scale(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int rank, int world, "
         "int n_floats, float scale, int epoch, int ctas) -> ()");
   m.def("gather_blocks(Tensor anchor, int[] slot_ptrs, int[] flag_ptrs, int[] out_ptrs, int out_mc, bool out_bf16, "
@@ -334,6 +352,8 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("block_out_bwd", &block_out_bwd);
   m.impl("cross_entropy", &cross_entropy);
   m.impl("adamw", &adamw);
+  m.impl("rownorm_fwd", &rownorm_fwd);
+  m.impl("rownorm_bwd", &rownorm_bwd);
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("gather_blocks", &gather_blocks);
   m.impl("rs_adamw_ag", &rs_adamw_ag);

@@ -40,6 +40,7 @@ enum EpiFlags : int {
   EPI_F_POPE = 8,          // EPI_RELU: write softplus(x)*[cos, sin] to out1 (real | imag halves)
   EPI_F_UPPER = 16,        // EPI_CAUSAL: write only s > t (else: write everything, zero where s >= t)
   EPI_F_NO_OUT0 = 32,      // EPI_RELU_GATE: skip storing y
+  EPI_F_BIAS = 64,         // EPI_CAUSAL: additive distance bias, acc + slope*(s-t), instead of the decay factor
   EPI_F_TABLE = 128,       // rotary (cos, sin) come from an fp16-pair table [T, n_per_head] instead of sincos
   EPI_F_ATOMIC = 512,      // EPI_STORE fp32: out0 += tile with red.global.add (split-K partial sums)
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
@@ -325,8 +326,12 @@ __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, i
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       int s = n + i;
-      float w = (s < m) ? __expf(-slope * static_cast<float>(m - s)) : 0.f;
-      o0[i] = acc[i] * w * e.alpha;
+      if (e.flags & EPI_F_BIAS) {
+        o0[i] = (s < m) ? acc[i] * e.alpha - slope * static_cast<float>(m - s) : 0.f;
+      } else {
+        float w = (s < m) ? __expf(-slope * static_cast<float>(m - s)) : 0.f;
+        o0[i] = acc[i] * w * e.alpha;
+      }
     }
   } else if constexpr (EPI == EPI_GATE_BWD) {
     // r0 = x, r1 = x*y (y itself is never stored: y = xy / x where the x gate is open).

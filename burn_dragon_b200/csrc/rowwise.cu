@@ -551,3 +551,94 @@ extern "C" int bdh_pope_bwd(const void* dq, const void* x, const void* dxg, cons
                                                                (bf16*)dx, M, H, N, T, pos0);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
+
+// ---- L1 row normalisation of strictly causal scores (the `forward_fast` attention) -------------
+// S is bf16 [rows, T] with rows = (batch, head, t); only columns s < t of row t carry scores
+// (reference: src/model/attention.rs:142-175: tril(-1), then S / (sum_j |S_ij| + 1e-6)).
+//   forward : S <- S / r,  r = sum_{s<t} |S| + 1e-6           (r is kept for the backward pass)
+//   backward: G <- (G - sign(Sn) * sum_{s<t} G Sn) / r         (Sn = normalised scores)
+// One warp per row, 8 columns per lane per step; columns s >= t are left untouched.
+namespace bdh {
+template <bool BWD>
+__global__ void __launch_bounds__(256)
+rownorm_kernel(__nv_bfloat16* __restrict__ S, const __nv_bfloat16* __restrict__ Sn, float* __restrict__ rnorm,
+               long long rows, int T, int ld) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int t = static_cast<int>(row % T);
+  __nv_bfloat16* p = S + row * ld;
+  const __nv_bfloat16* pn = BWD ? Sn + row * ld : nullptr;
+  float acc = 0.f;
+  for (int s0 = lane * 8; s0 < t; s0 += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p + s0);
+    const uint32_t* w = &u.x;
+    uint4 un = make_uint4(0, 0, 0, 0);
+    if (BWD) un = *reinterpret_cast<const uint4*>(pn + s0);
+    const uint32_t* wn = &un.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16x2(w[k]);
+      const bool in0 = s0 + 2 * k < t, in1 = s0 + 2 * k + 1 < t;
+      if (BWD) {
+        const float2 b = unpack_bf16x2(wn[k]);
+        acc += (in0 ? a.x * b.x : 0.f) + (in1 ? a.y * b.y : 0.f);
+      } else {
+        acc += (in0 ? fabsf(a.x) : 0.f) + (in1 ? fabsf(a.y) : 0.f);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  float r;
+  if (BWD) {
+    r = rnorm[row];
+  } else {
+    r = acc + 1e-6f;
+    if (lane == 0) rnorm[row] = r;
+  }
+  const float inv = 1.f / r;
+  for (int s0 = lane * 8; s0 < t; s0 += 256) {
+    uint4 u = *reinterpret_cast<const uint4*>(p + s0);
+    uint32_t* w = &u.x;
+    uint4 un = make_uint4(0, 0, 0, 0);
+    if (BWD) un = *reinterpret_cast<const uint4*>(pn + s0);
+    const uint32_t* wn = &un.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_bf16x2(w[k]);
+      const bool in0 = s0 + 2 * k < t, in1 = s0 + 2 * k + 1 < t;
+      if (BWD) {
+        const float2 b = unpack_bf16x2(wn[k]);
+        const float s0v = (b.x > 0.f) ? 1.f : (b.x < 0.f ? -1.f : 0.f);
+        const float s1v = (b.y > 0.f) ? 1.f : (b.y < 0.f ? -1.f : 0.f);
+        a.x = in0 ? (a.x - s0v * acc) * inv : a.x;
+        a.y = in1 ? (a.y - s1v * acc) * inv : a.y;
+      } else {
+        a.x = in0 ? a.x * inv : a.x;
+        a.y = in1 ? a.y * inv : a.y;
+      }
+      w[k] = pack_bf16x2(a.x, a.y);
+    }
+    *reinterpret_cast<uint4*>(p + s0) = u;
+  }
+}
+}  // namespace bdh
+
+extern "C" int bdh_rownorm_fwd(void* scores_bf16, float* rnorm, long long rows, int T, int ld, cudaStream_t s) {
+  if (rows <= 0 || T <= 0 || (ld % 8) || ld < T) return BDH_ERR_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(scores_bf16) & 15) return BDH_ERR_ALIGNMENT;
+  const long long blocks = (rows + 7) / 8;
+  bdh::rownorm_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, s>>>((bf16*)scores_bf16, nullptr, rnorm, rows, T, ld);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
+extern "C" int bdh_rownorm_bwd(void* grad_bf16, const void* normed_bf16, const float* rnorm, long long rows, int T,
+                               int ld, cudaStream_t s) {
+  if (rows <= 0 || T <= 0 || (ld % 8) || ld < T) return BDH_ERR_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(grad_bf16) | reinterpret_cast<uintptr_t>(normed_bf16)) & 15) return BDH_ERR_ALIGNMENT;
+  const long long blocks = (rows + 7) / 8;
+  bdh::rownorm_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, s>>>((bf16*)grad_bf16, (const bf16*)normed_bf16,
+                                                                        const_cast<float*>(rnorm), rows, T, ld);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}

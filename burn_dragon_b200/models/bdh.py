@@ -172,7 +172,11 @@ class BDH(nn.Module):
             if c.block_sparse is not None and c.block_sparse.time.is_sparse():
                 block = c.block_sparse.time.block_size
                 pairs = c.block_sparse.time.pairs((cur.shape[2] + block - 1) // block)
-            a = R.attention_rownorm(q, cur, self._slopes(), pairs, block)
+            from ..ops import rownorm_attention as RA
+            if pairs is None and getattr(self, "use_native", True) and RA.can_run(q, cur):
+                a = RA.attention_rownorm(q, cur, self._slopes())
+            else:
+                a = R.attention_rownorm(q, cur, self._slopes(), pairs, block)
         else:
             q = R.rotate(x, c.rotary_embedding, self.freqs, start)
             if mode == "recurrent":

@@ -22,6 +22,7 @@ from . import native
 EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range(6)
 F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED, F_ATOMIC = 1, 2, 4, 8, 16, 32, 128, 256, 512
 F_PEER_RS = 1024
+F_BIAS = 64
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -180,7 +181,10 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                         pass
                     out0[rs, cs] = torch.where(mask, val, cur).to(out0.dtype)
                 else:
-                    val = torch.where(dist > 0, acc * alpha * torch.exp(-slope * dist.abs()), torch.zeros_like(acc))
+                    if flags & F_BIAS:
+                        val = torch.where(dist > 0, acc * alpha - slope * dist, torch.zeros_like(acc))
+                    else:
+                        val = torch.where(dist > 0, acc * alpha * torch.exp(-slope * dist.abs()), torch.zeros_like(acc))
                     if causal_tiles == 1:
                         # tiles with n0 >= m0 + 128 are never written: keep what is there
                         m0 = (mm // 128) * 128
