@@ -135,9 +135,9 @@ def main() -> int:
     presets = {
         "base": (MODEL, BATCH_PER_GPU, SEQ_LEN, "ddp", False, "bdh-base L6 D256 H4 N8192 V256 rope"),
         "large": (dict(n_layer=8, n_embd=512, n_head=8, n_latent_per_head=16384, vocab_size=256, dropout=0.0,
-                       rotary_embedding="pope"), 8, 2048, "fsdp", True, "bdh-large L8 D512 H8 N16384 V256 pope"),
+                       rotary_embedding="pope"), 8, 2048, "fsdp", "auto", "bdh-large L8 D512 H8 N16384 V256 pope"),
         "tp": (dict(n_layer=12, n_embd=1024, n_head=16, n_latent_per_head=16384, vocab_size=256, dropout=0.0,
-                    rotary_embedding="rope"), 4, 4096, "tp", True, "bdh-tp L12 D1024 H16 N16384 V256 rope"),
+                    rotary_embedding="rope"), 4, 4096, "tp", "auto", "bdh-tp L12 D1024 H16 N16384 V256 rope"),
     }
     mcfg, B0, T0, strategy, recompute, model_name = presets[args.preset]
     B, T = args.batch or B0, args.seq or T0
@@ -225,7 +225,7 @@ def main() -> int:
             "dtype": "bf16", "data": "synthetic uniform random bytes, random-init weights",
             "config": {"model": model_name, "global_batch": B * data_world, "seq_len": T,
                        "parallelism": (f"{'dp' if strategy == 'ddp' else strategy}{world}" if world > 1 else "single"),
-                       "recompute": recompute,
+                       "recompute": recompute, "recomputed_layers": getattr(getattr(wrapper, "shard", model), "_recomputed_layers", None),
                        "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
                        "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
                        "allreduce": ("nccl" if args.nccl_only else "fused-nvlink") if world > 1 else "none"},

@@ -121,7 +121,8 @@ class TrainingHyperparameters:
     seed: int = 1337
     grad_clip: Optional[float] = None
     checkpoint_every: Optional[int] = None   # steps; None = once per epoch like the reference
-    recompute: bool = False                  # re-run each layer's forward in backward instead of saving x/y
+    recompute: Any = False                   # layers that re-run their forward in backward instead of saving
+                                             # activations: false / true (none / all), a count, or "auto"
 
 
 @dataclass

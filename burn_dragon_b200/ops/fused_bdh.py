@@ -307,7 +307,38 @@ def _head_logits(d, W, cur):
     return cur.float() @ W["lm_head"].float()
 
 
-def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: bool):
+def layer_activation_bytes(d: _Dims) -> int:
+    """Bytes one layer keeps for its backward pass when it is not recomputed."""
+    wide = d.M * (2 * d.HN + (d.HNp if d.rot != "alibi" else 0)) * 2          # x, x*y, rotated copy
+    scores = d.B * d.H * d.T * d.T * 2
+    narrow = (2 * d.H * d.M * d.D + 3 * d.M * d.D) * 2                        # a, LN(a); cur, mlp, out
+    return wide + scores + narrow
+
+
+def recompute_count(model, d: _Dims) -> int:
+    """How many of the L layers re-run their forward in the backward pass. `model.recompute`:
+    False / True (none / all), an int (that many, counted from the first layer), or "auto": as few as
+    fit in 80 % of the free device memory, after setting aside the backward pass's own working set
+    (about five [tokens, H*N'] bf16 tensors and one recomputed layer)."""
+    r = getattr(model, "recompute", False)
+    if r is True:
+        return d.L
+    if r is False or r is None:
+        return 0
+    if isinstance(r, int):
+        return max(0, min(d.L, r))
+    if r == "auto":
+        free, _ = torch.cuda.mem_get_info()
+        free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()   # cached blocks are reusable
+        per = layer_activation_bytes(d)
+        working = 5 * d.M * max(d.HN, d.HNp) * 2 + per
+        keep = int((0.8 * free - working) // per)
+        return max(0, min(d.L, d.L - keep))
+    raise ValueError(f"recompute must be a bool, an int or 'auto', not {r!r}")
+
+
+def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int):
+    """`recompute` = number of leading layers that keep only their input (and dropout seed)."""
     cur = _embed(d, W, tokens)
     pos0 = state.position if state is not None else 0
     saved: List[dict] = []
@@ -318,7 +349,7 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: boo
         if state is not None:
             state.layers[l].rho = rho_out
         if save:
-            saved.append(dict(cur=cur, drop_seed=seed_l) if recompute else sv)
+            saved.append(dict(cur=cur, drop_seed=seed_l) if l < recompute else sv)
         cur = out
     if state is not None:
         state.position += d.T
@@ -330,7 +361,7 @@ def forward_logits(model, tokens: torch.Tensor, state) -> torch.Tensor:
     B, T = tokens.shape
     d = _Dims(model, B, T)
     W = _weights(model)
-    cur, _ = _stack_forward(model, d, W, tokens, state, save=False, recompute=False)
+    cur, _ = _stack_forward(model, d, W, tokens, state, save=False, recompute=0)
     return _head_logits(d, W, cur).view(B, T, d.V)
 
 
@@ -340,7 +371,8 @@ class _FusedLoss(torch.autograd.Function):
         B, T = tokens.shape
         d = _Dims(model, B, T)
         W = _weights(model)
-        recompute = bool(getattr(model, "recompute", False))
+        recompute = recompute_count(model, d)
+        model._recomputed_layers = recompute
         cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute)
         logits = _head_logits(d, W, cur)
         row_loss = torch.empty(d.M, device=tokens.device, dtype=torch.float32)
@@ -368,7 +400,7 @@ class _FusedLoss(torch.autograd.Function):
             dcur = dlogits.float() @ W["lm_head"].float().t()
         for l in reversed(range(d.L)):
             sv = saved[l]
-            if ctx.recompute:
+            if "x" not in sv:
                 _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
             dcur = _layer_backward(d, W, sv, dcur, grads, 0)
             saved[l] = None

@@ -64,12 +64,14 @@ def test_recompute_matches_saved(rot):
     tgt = torch.randint(0, 256, (B, T), device="cuda")
     m(tok, tgt).backward()
     g0 = {n: p.grad.clone() for n, p in m.named_parameters()}
-    m.zero_grad()
-    m.recompute = True
-    m(tok, tgt).backward()
-    for n, p in m.named_parameters():
-        # the embedding gradient is summed with fp32 atomics, so its rounding depends on the order
-        assert torch.allclose(g0[n], p.grad, rtol=1e-3, atol=1e-5), n
+    for mode, layers in ((True, m.config.n_layer), (1, 1), ("auto", 0)):
+        m.zero_grad()
+        m.recompute = mode
+        m(tok, tgt).backward()
+        assert m._recomputed_layers == layers
+        for n, p in m.named_parameters():
+            # the embedding gradient is summed with fp32 atomics, so its rounding depends on the order
+            assert torch.allclose(g0[n], p.grad, rtol=1e-3, atol=1e-5), (mode, n)
 
 
 @pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
