@@ -119,4 +119,47 @@ void bdh_f32_to_f16(const float* in, uint16_t* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) out[i] = f32_to_f16(in[i]);
 }
 
+// Character tokenizer over UTF-8 text (reference: src/tokenizer/char_vocab.rs:150-174): decodes code
+// points and maps each through `table` (code point -> id, -1 = not in the vocabulary; code points
+// >= table_len are unknown). Unknown characters become unk_id, or, when unk_id < 0, stop the scan:
+// the offending code point is stored in *bad and -1 is returned. Returns the number of ids written
+// (out must hold n_bytes entries). Malformed UTF-8 bytes decode as U+FFFD.
+int64_t bdh_encode_utf8_chars(const uint8_t* s, int64_t n_bytes, const int32_t* table, int64_t table_len,
+                              int32_t unk_id, int64_t* out, int64_t* bad) {
+  int64_t i = 0, n = 0;
+  while (i < n_bytes) {
+    uint32_t c = s[i], cp;
+    int len = c < 0x80 ? 1 : (c >> 5) == 0x6 ? 2 : (c >> 4) == 0xE ? 3 : (c >> 3) == 0x1E ? 4 : 0;
+    if (len == 0 || i + len > n_bytes) {
+      cp = 0xFFFD;
+      len = 1;
+    } else if (len == 1) {
+      cp = c;
+    } else {
+      cp = c & (0xFFu >> (len + 1));
+      bool ok = true;
+      for (int k = 1; k < len; ++k) {
+        uint32_t cc = s[i + k];
+        if ((cc >> 6) != 0x2) { ok = false; break; }
+        cp = (cp << 6) | (cc & 0x3F);
+      }
+      if (!ok) {
+        cp = 0xFFFD;
+        len = 1;
+      }
+    }
+    int32_t id = (static_cast<int64_t>(cp) < table_len) ? table[cp] : -1;
+    if (id < 0) {
+      if (unk_id < 0) {
+        if (bad) *bad = cp;
+        return -1;
+      }
+      id = unk_id;
+    }
+    out[n++] = id;
+    i += len;
+  }
+  return n;
+}
+
 }  // extern "C"

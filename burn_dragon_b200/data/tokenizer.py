@@ -152,7 +152,23 @@ class CharVocab(Tokenizer):
             ids.append(self.eos_id)
         return ids
 
+    def _table(self) -> np.ndarray:
+        t = getattr(self, "_cp_table", None)
+        if t is None:
+            t = np.full(max(ord(c) for c in self.id2ch) + 1, -1, dtype=np.int32)
+            for ch, i in self.ch2id.items():
+                t[ord(ch)] = i
+            self._cp_table = t
+        return t
+
     def encode_array(self, text):
+        from ..utils import hostlib
+        if hostlib.available():
+            # native scan of the UTF-8 bytes (the whole-corpus path of the dataset builders)
+            try:
+                return hostlib.encode_utf8_chars(text.encode("utf-8", "surrogatepass"), self._table(), self.unk_id)
+            except KeyError as e:
+                raise KeyError(f"character {e.args[0]!r} missing from vocabulary and no <unk> token configured") from None
         cps = np.frombuffer(text.encode("utf-32-le"), dtype=np.uint32)
         if cps.size == 0:
             return np.zeros(0, dtype=np.int64)

@@ -23,6 +23,7 @@ def _load():
             lib.bdh_record_scan_param.restype = ctypes.c_int64
             lib.bdh_varint_read.restype = ctypes.c_int
             lib.bdh_varint_write.restype = ctypes.c_int
+            lib.bdh_encode_utf8_chars.restype = ctypes.c_int64
             _LIB = lib
         except OSError:
             _LIB = False
@@ -63,3 +64,18 @@ def f32_to_f16(a: np.ndarray) -> np.ndarray:
     out = np.empty(a.shape, dtype=np.uint16)
     lib.bdh_f32_to_f16(ctypes.c_void_p(a.ctypes.data), ctypes.c_void_p(out.ctypes.data), ctypes.c_int64(a.size))
     return out.view(np.float16)
+
+
+def encode_utf8_chars(data: bytes, table: np.ndarray, unk_id) -> np.ndarray:
+    """Character ids of UTF-8 `data` through `table` (int32, code point -> id or -1). Raises KeyError
+    with the first character that is not in the vocabulary when `unk_id` is None."""
+    lib = _load()
+    table = np.ascontiguousarray(table, dtype=np.int32)
+    out = np.empty(len(data), dtype=np.int64)
+    bad = ctypes.c_int64(0)
+    n = lib.bdh_encode_utf8_chars(ctypes.c_char_p(data), ctypes.c_int64(len(data)), ctypes.c_void_p(table.ctypes.data),
+                                  ctypes.c_int64(table.size), ctypes.c_int32(-1 if unk_id is None else int(unk_id)),
+                                  ctypes.c_void_p(out.ctypes.data), ctypes.byref(bad))
+    if n < 0:
+        raise KeyError(chr(bad.value))
+    return out[:n]

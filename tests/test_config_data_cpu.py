@@ -196,3 +196,17 @@ def test_hf_dataset_offline_from_cache(tmp_path, monkeypatch):
     f.write_text("\n".join("sample text number %d" % i for i in range(50)))
     ds = D.huggingface_dataset(tmp_path, 8, 2, 0.9, C.TokenizerConfig("byte", True, False, None), spec)
     assert len(ds.tokens) > 500 and ds.sample_batch().inputs.shape == (2, 8)
+
+
+def test_char_vocab_native_encode_matches_python():
+    from burn_dragon_b200.data.tokenizer import CharVocab
+    from burn_dragon_b200.utils import hostlib
+    text = "héllo wörld — ∑ 🙂 abc\nline two"
+    v = CharVocab.fit([text], include_unknown=True)
+    assert hostlib.available()
+    for s in (text, "", "zzz 🙂 qq", "abc"):
+        assert v.encode_array(s).tolist() == v.encode(s)
+    strict = CharVocab.fit(["abc"], include_unknown=False)
+    import pytest
+    with pytest.raises(KeyError):
+        strict.encode_array("abd")
