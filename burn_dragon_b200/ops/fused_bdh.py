@@ -253,15 +253,16 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
            epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=Gs)
     G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
            epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
-    # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h ; heads run as separate launches
+    # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h
     if comm is None:
         part, pflags, pkw = dcur, G.F_OUT_F32 | G.F_ACCUM, {}
     else:
-        pbuf = comm.begin("dcur", M, D, launches=H + 1)        # partial sums over the neuron shards: dV and the encoder path
+        pbuf = comm.begin("dcur", M, D, launches=2)        # partial sums over the neuron shards: dV and the encoder path
         part, pflags, pkw = pbuf.view, comm.flags, pbuf.kw
-    for h in range(H):
-        G.gemm(S[h * T:], da[h * M:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),
-               b_off=(0, 0, 0, T), c_off=(0, T, 0, 0), flags=pflags, out0=part, **pkw)
+    # all heads in one launch: every (head, batch) problem adds its [T, D] tile into the rows of its batch
+    G.gemm(S, da, M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(0, 0, T, H * T), b_off=(0, 0, M, T),
+           c_off=(0, T, 0, 0), flags=(pflags & ~G.F_ACCUM) | (G.F_ATOMIC if pflags & G.F_ACCUM else 0), out0=part,
+           **pkw)
     # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
     dx = _bf16(M, d.HN, dev)
     if d.rot == "pope":

@@ -59,11 +59,10 @@ class _RowNormAttention(torch.autograd.Function):
         B, H, T, N, D = ctx.shape
         dev = da.device
         da16 = da.to(torch.bfloat16).contiguous().view(B * H * T, D)
-        # dv[b, s] = sum_h sum_t Sn[t, s] dA[t]: one launch per head adds into the fp32 result
+        # dv[b, s] = sum_h sum_t Sn[t, s] dA[t]: every (head, batch) problem adds into the rows of its batch
         dv = torch.zeros(B * T, D, device=dev, dtype=torch.float32)
-        for h in range(H):
-            G.gemm(S[h * T:], da16[h * T:], M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(1, B), a_off=(0, 0, 0, H * T),
-                   b_off=(0, 0, 0, H * T), c_off=(0, T, 0, 0), flags=G.F_OUT_F32 | G.F_ACCUM, out0=dv)
+        G.gemm(S, da16, M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(0, 0, T, H * T),
+               b_off=(0, 0, T, H * T), c_off=(0, T, 0, 0), flags=G.F_OUT_F32 | G.F_ATOMIC, out0=dv)
         # G = tril(dA v^T, -1), then through the normalisation
         Gm = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)
         G.gemm(da16, v16, M=T, N=T, K=D, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
