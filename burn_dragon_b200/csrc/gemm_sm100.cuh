@@ -45,6 +45,7 @@ enum EpiFlags : int {
   EPI_F_ATOMIC = 512,      // EPI_STORE fp32: out0 += tile with red.global.add (split-K partial sums)
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
+  EPI_F_ROWDECAY = 2048,   // EPI_STORE: scale row m by exp(-slopes[z0] * m) (decayed carry-in of a recurrent state)
   EPI_F_PEER_RS = 1024,    // EPI_STORE fp32: reduce-scatter epilogue. Output rows are split into blocks of
                            // peer_rows, block b is owned by rank b. The tile is stored through the owner's
                            // peer mapping peer_out[owner] into the slot this rank has there: the owner's
@@ -212,7 +213,7 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
   if (epi == EPI_STORE)
-    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS));
+    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS | EPI_F_ROWDECAY));
   if (epi == EPI_RELU) return true;
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -410,6 +411,13 @@ __device__ __forceinline__ void load_raw_32(const __nv_bfloat16* base, long long
 
 constexpr int EPI_RED_FLAGS = EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS;
 
+// Scale applied by EPI_STORE to row m of problem (z0, .): alpha, times the row decay when asked for.
+__device__ __forceinline__ float epi_store_scale(const EpiParams& e, int z0, int m) {
+  float a = e.alpha;
+  if (e.flags & EPI_F_ROWDECAY) a *= __expf(-(e.slopes ? __ldg(e.slopes + z0) : 0.f) * static_cast<float>(m));
+  return a;
+}
+
 // Address of output row `row` inside the slot this rank owns in the buffer of the row's owner.
 __device__ __forceinline__ float* peer_slot_row(const EpiParams& e, long long row) {
   long long owner = row / e.peer_rows;
@@ -464,8 +472,9 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
   typedef __nv_bfloat16 bf;
 
   if constexpr (EPI == EPI_STORE) {
+    const float scale = epi_store_scale(e, z0, m);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= e.alpha;
+    for (int i = 0; i < 32; ++i) v[i] *= scale;
     if (e.flags & EPI_F_MC_RED) {
       // partial sums of all ranks meet in the switch: one reduction-add per 16 bytes, no local read
       float* p = static_cast<float*>(e.out0) + r * e.ld_out0 + c;
@@ -859,8 +868,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const long long r0 = e.c_m0 * tc.z0 + e.c_m1 * tc.z1 + (m - lane);
               const long long cc = e.c_n0 * tc.z0 + e.c_n1 * tc.z1 + n;
               if (((reinterpret_cast<uintptr_t>(e.out0) + 4 * static_cast<uintptr_t>(cc)) & 15) == 0) {
+                const float scale = epi_store_scale(e, tc.z0, m);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] *= e.alpha;
+                for (int i = 0; i < 32; ++i) v[i] *= scale;
                 send_tile_coalesced(e, r0, cc, v,
                                    reinterpret_cast<float4*>(smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES), lane);
                 continue;

@@ -57,15 +57,26 @@ def _as_batch(prompt_tokens, device) -> torch.Tensor:
     return t
 
 
+PREFILL_SEGMENT = 4096
+
+
 @torch.no_grad()
-def prefill_state(model, prompt_tokens, device=None):
-    """Run the prompt, return (state, last_logits [B, V]) (src/generation.rs:74-104)."""
+def prefill_state(model, prompt_tokens, device=None, segment: Optional[int] = None):
+    """Run the prompt, return (state, last_logits [B, V]) (src/generation.rs:74-104). Prompts longer
+    than `segment` tokens (default PREFILL_SEGMENT) are run segment by segment with the recurrent
+    state carried across, so score memory is O(segment^2) whatever the prompt length; the result is
+    the same function of the prompt."""
     device = device if device is not None else next(model.parameters()).device
     toks = _as_batch(prompt_tokens, device)
     state = model.init_state()
-    logits = model.forward_with_state(toks, state)
-    if logits.shape[1] != toks.shape[1]:
-        raise RuntimeError(f"prefill produced mismatched length: expected {toks.shape[1]}, got {logits.shape[1]}")
+    seg = int(segment or PREFILL_SEGMENT)
+    P = toks.shape[1]
+    logits = None
+    for lo in range(0, max(P, 1), seg):
+        part = toks[:, lo:lo + seg]
+        logits = model.forward_with_state(part, state)
+        if logits.shape[1] != part.shape[1]:
+            raise RuntimeError(f"prefill produced mismatched length: expected {part.shape[1]}, got {logits.shape[1]}")
     state.viz = None
     return state, logits[:, -1]
 

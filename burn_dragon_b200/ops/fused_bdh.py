@@ -43,8 +43,6 @@ def can_run(model, tokens: torch.Tensor, state) -> bool:
         return False
     if state is not None:
         has_rho = any(l.rho is not None for l in state.layers)
-        if has_rho and c.rotary_embedding == "alibi":
-            return False       # decayed carry-in needs a per-row scale; the torch path handles it
         if has_rho and any(l.rho is None or l.rho.shape[0] != B for l in state.layers):
             return False
     return True
@@ -148,15 +146,16 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
            epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
     comm = d.comm
+    carry_flags = G.F_ROWDECAY if d.slopes is not None else 0
     if comm is None:
         a = _bf16(H * M, D, dev)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
                c_off=(M, T, 0, 0), causal_k=1, out0=a)
         if rho_in is not None:
-            # carry-in (no decay): a += q . rho_in
+            # carry-in: a_t += g^t (q_t . rho_in); the row decay g^t is applied in the epilogue
             rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
             G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
-                   c_off=(M, T, 0, 0), flags=G.F_ACCUM, out0=a)
+                   c_off=(M, T, 0, 0), flags=G.F_ACCUM | carry_flags, slopes=d.slopes, out0=a)
     else:
         # neuron-sharded: this rank's scores cover its slice of the neurons, so S V is a partial sum;
         # the GEMM epilogue adds it into every rank's replica through the switch
@@ -166,7 +165,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         if rho_in is not None:
             rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
             G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
-                   c_off=(M, T, 0, 0), flags=comm.flags, out0=buf.view, **buf.kw)
+                   c_off=(M, T, 0, 0), flags=comm.flags | carry_flags, slopes=d.slopes, out0=buf.view, **buf.kw)
         a = comm.end(buf, bf16=True)
     rho_out = None
     if want_rho:
@@ -181,7 +180,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         G.gemm(q, vw, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=b_off,
                c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho_out.view(B * H * Np, D))
         if rho_in is not None:
-            rho_out += rho_in
+            # the carried state has decayed by g^T over this segment
+            rho_out += rho_in if d.slopes is None else rho_in * torch.exp(-d.slopes * T).view(1, H, 1, 1)
     lna = torch.empty_like(a)
     ops.layernorm_fwd(a, lna)
     # y is not stored: the backward recovers it as xy / x

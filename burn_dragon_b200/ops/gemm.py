@@ -23,6 +23,7 @@ EPI_STORE, EPI_RELU, EPI_RELU_GATE, EPI_CAUSAL, EPI_GATE_BWD, EPI_DQ_BWD = range
 F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED, F_ATOMIC = 1, 2, 4, 8, 16, 32, 128, 256, 512
 F_PEER_RS = 1024
 F_BIAS = 64
+F_ROWDECAY = 2048
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -142,6 +143,9 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
             nn = torch.arange(N, device=dev)
             if epi == EPI_STORE:
                 v = acc * alpha
+                if flags & F_ROWDECAY:
+                    slope = float(slopes[z0]) if slopes is not None else 0.0
+                    v = v * torch.exp(-slope * mm.float())[:, None]
                 if flags & (F_ACCUM | F_ATOMIC):
                     v = v + out0[rs, cs].float()
                 out0[rs, cs] = v.to(out0.dtype)

@@ -92,7 +92,7 @@ def test_prefill_logits_and_state(rot):
         assert _rel(a.rho, b.rho) < 0.05
 
 
-@pytest.mark.parametrize("rot", ["rope", "pope"])
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
 def test_prefill_continuation(rot):
     """Two kernel-path calls with a carried state equal one call over the concatenation."""
     m = _model(rot).eval()

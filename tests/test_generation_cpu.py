@@ -77,3 +77,22 @@ def test_stream_printer_utf8_safe():
     for i in cv.encode("cab"):
         sp2.push(i)
     assert "".join(got2) == "cab"
+
+
+def test_segmented_prefill_equals_one_shot():
+    """A prompt run in segments with the state carried across gives the same last logits and state."""
+    import torch
+    from burn_dragon_b200.engine import generation as GEN
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+    for rot in ("alibi", "rope", "pope"):
+        torch.manual_seed(0)
+        m = BDH(BDHConfig(n_layer=2, n_embd=32, n_head=2, n_latent_per_head=16, vocab_size=64, dropout=0.0,
+                          rotary_embedding=rot)).eval()
+        toks = torch.randint(0, 64, (2, 50))
+        with torch.no_grad():
+            s1, l1 = GEN.prefill_state(m, toks)
+            s2, l2 = GEN.prefill_state(m, toks, segment=16)
+        assert s1.position == s2.position == 50
+        assert torch.allclose(l1, l2, rtol=1e-4, atol=1e-5), rot
+        for a, b in zip(s1.layers, s2.layers):
+            assert torch.allclose(a.rho, b.rho, rtol=1e-4, atol=1e-5), rot
