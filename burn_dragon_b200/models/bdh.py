@@ -182,6 +182,15 @@ class BDH(nn.Module):
             if mode == "recurrent":
                 decay = torch.exp(-self.slopes) if self.use_alibi else None
                 a, new_rho = R.linear_attention_recurrent(q, cur, decay, rho)
+            elif getattr(self, "_cp", None) is not None:
+                # context parallel: local part, state exchange between the ranks, then the carried part
+                fn = R.linear_attention_chunked if mode == "chunked" else R.linear_attention_parallel
+                a, rho_loc = fn(q, cur, self._slopes(), None)
+                sl = self._slopes()
+                g_T = torch.exp(-sl.to(q.dtype) * q.shape[2]).view(1, -1, 1, 1) if sl is not None else 1.0
+                rho_in, new_rho = self._cp.scan(rho_loc, rho, g_T)
+                if rho_in is not None:
+                    a = a + R.carry_in(q, rho_in, sl)
             elif mode == "chunked":
                 a, new_rho = R.linear_attention_chunked(q, cur, self._slopes(), rho)
             else:

@@ -87,6 +87,7 @@ class _Dims:
         else:
             self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
+        self.cp = getattr(model, "_cp", None)        # context-parallel hook (parallel/cp.py)
         # dropout on x*y (training only): a fresh mask seed per call, one derived seed per layer
         self.drop_p = float(c.dropout) if (model.training and c.dropout > 0) else 0.0
         model._drop_calls = getattr(model, "_drop_calls", 0) + 1
@@ -124,6 +125,23 @@ def _bf16(rows, cols, dev):
 # ------------------------------------------------------------------------------------------------
 # one layer forward
 # ------------------------------------------------------------------------------------------------
+def _segment_state(d: "_Dims", q, cur) -> torch.Tensor:
+    """State this segment adds, sum_s g^(T-s) q_s^T v_s, fp32 [B, H, N', D]."""
+    B, H, T, M, D, Np = d.B, d.H, d.T, d.M, d.D, d.Np
+    dev = q.device
+    rho = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
+    if d.slopes is not None:
+        t = torch.arange(T, device=dev, dtype=torch.float32)
+        w = torch.exp(-d.slopes.view(H, 1) * (T - t).view(1, T))                     # g^(T-s)
+        vw = (cur.view(1, B, T, D).float() * w.view(H, 1, T, 1)).to(torch.bfloat16).reshape(H * M, D)
+        b_off = (0, 0, M, T)
+    else:
+        vw, b_off = cur, (0, 0, 0, T)
+    G.gemm(q, vw, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=b_off,
+           c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho.view(B * H * Np, D))
+    return rho
+
+
 def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool,
                    drop_seed: int = 0):
     dev = cur.device
@@ -147,6 +165,12 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
            epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
     comm = d.comm
     carry_flags = G.F_ROWDECAY if d.slopes is not None else 0
+    cp = d.cp
+    rho_total = None
+    if cp is not None:
+        # context parallel: exchange the segment states, continue from what the earlier ranks left
+        g_T = torch.exp(-d.slopes * T).view(1, H, 1, 1) if d.slopes is not None else 1.0
+        rho_in, rho_total = cp.scan(_segment_state(d, q, cur), rho_in, g_T)
     if comm is None:
         a = _bf16(H * M, D, dev)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
@@ -168,17 +192,10 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
                    c_off=(M, T, 0, 0), flags=comm.flags | carry_flags, slopes=d.slopes, out0=buf.view, **buf.kw)
         a = comm.end(buf, bf16=True)
     rho_out = None
-    if want_rho:
-        rho_out = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
-        if d.slopes is not None:
-            t = torch.arange(T, device=dev, dtype=torch.float32)
-            w = torch.exp(-d.slopes.view(H, 1) * (T - t).view(1, T))                     # g^(T-s)
-            vw = (cur.view(1, B, T, D).float() * w.view(H, 1, T, 1)).to(torch.bfloat16).reshape(H * M, D)
-            b_off = (0, 0, M, T)
-        else:
-            vw, b_off = cur, (0, 0, 0, T)
-        G.gemm(q, vw, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=b_off,
-               c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho_out.view(B * H * Np, D))
+    if cp is not None:
+        rho_out = rho_total
+    elif want_rho:
+        rho_out = _segment_state(d, q, cur)
         if rho_in is not None:
             # the carried state has decayed by g^T over this segment
             rho_out += rho_in if d.slopes is None else rho_in * torch.exp(-d.slopes * T).view(1, H, 1, 1)

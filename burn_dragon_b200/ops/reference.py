@@ -134,6 +134,16 @@ def linear_attention_parallel(q: torch.Tensor, v: torch.Tensor, slopes: Optional
     return a, rho_out
 
 
+def carry_in(q: torch.Tensor, rho_in: torch.Tensor, slopes: Optional[torch.Tensor]) -> torch.Tensor:
+    """What a state carried into the segment adds to the attention output: g^t (q_t . rho_in)."""
+    B, H, T, N = q.shape
+    a = torch.matmul(q, rho_in.to(q.dtype))
+    if slopes is not None:
+        t = torch.arange(T, device=q.device, dtype=q.dtype)
+        a = a * torch.exp(-slopes.to(q.dtype).view(1, H, 1, 1) * t.view(1, 1, T, 1))
+    return a
+
+
 def linear_attention_chunked(q: torch.Tensor, v: torch.Tensor, slopes: Optional[torch.Tensor],
                              rho: Optional[torch.Tensor] = None, chunk: int = 64) -> Tuple[torch.Tensor, torch.Tensor]:
     """Chunk-state form: quadratic inside a chunk, state hand-off between chunks. Same result as the

@@ -1,0 +1,79 @@
+"""Context (sequence) parallelism for BDH: rank r holds tokens [r*T, (r+1)*T) of every sequence.
+
+Linear attention makes this a state hand-off rather than a ring of key/value blocks: inside a layer
+every rank computes its local causal part and the state its segment would add,
+
+    rho_loc^r = sum_s g^(T-s) q_s^T v_s                                   [B, H, N', D]
+
+the ranks exchange these (one all-gather per layer), and rank r continues from the state all
+earlier tokens left behind,
+
+    rho_in^r = g^(rT) rho_0 + sum_{r' < r} g^((r-1-r') T) rho_loc^{r'},    a_t += g^t q_t . rho_in^r
+
+so the result equals the single-device forward over the concatenated sequence. After the call
+every rank holds the state of the whole sequence, so decoding can continue on any of them. The
+message is the state itself (33 MB fp32 per layer for the base model), so this pays when the
+per-rank segment is much longer than the state is wide. The reference has no sequence parallelism
+(its long-context mechanism is the recurrence alone, src/model/state.rs:5-16).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class ContextParallel:
+    def __init__(self, model, group=None):
+        self.model, self.group = model, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    # ---- collective used inside every layer --------------------------------------------------------
+    def scan(self, rho_loc: torch.Tensor, rho0: Optional[torch.Tensor], g_T) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        """rho_loc [B, H, N', D]: this rank's segment state; rho0: state before the whole sequence (same
+        on every rank) or None; g_T: per-head decay over one segment, broadcastable to rho ([1, H, 1, 1])
+        or 1.0. Returns (state this rank starts from - None if it is exactly zero -, state after the
+        whole sequence)."""
+        parts = [torch.empty_like(rho_loc) for _ in range(self.world)]
+        dist.all_gather(parts, rho_loc.contiguous(), group=self.group)
+        run = rho0.to(rho_loc.dtype) if rho0 is not None else None
+        rho_in = None
+        for r in range(self.world):
+            if r == self.rank:
+                rho_in = run
+            run = parts[r] if run is None else run * g_T + parts[r]
+        return rho_in, run
+
+    # ---- public ------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_with_state(self, tokens_local: torch.Tensor, state, mode: str = "auto") -> torch.Tensor:
+        """Logits [B, T, V] of this rank's segment; `state` (same on every rank) is advanced over the
+        whole sequence of world * T tokens."""
+        T = tokens_local.shape[1]
+        p0 = state.position
+        model = self.model
+        model._cp = self
+        try:
+            state.position = p0 + self.rank * T
+            logits = model.forward_with_state(tokens_local, state, mode)
+        finally:
+            model._cp = None
+        state.position = p0 + self.world * T
+        return logits
+
+    @torch.no_grad()
+    def prefill(self, tokens_full: torch.Tensor):
+        """Split a [B, P] prompt (P divisible by the group size) over the ranks, run it, and return
+        (state after the prompt, logits of the last prompt token [B, V]) on every rank."""
+        P = tokens_full.shape[1]
+        if P % self.world:
+            raise ValueError("prompt length must be a multiple of the context-parallel group size")
+        T = P // self.world
+        state = self.model.init_state()
+        logits = self.forward_with_state(tokens_full[:, self.rank * T:(self.rank + 1) * T].contiguous(), state)
+        last = logits[:, -1].contiguous()
+        dist.broadcast(last, src=dist.get_global_rank(self.group, self.world - 1) if self.group is not None
+                       else self.world - 1, group=self.group)
+        return state, last

@@ -177,3 +177,38 @@ def case_tp_reduce_bw(dev):
     if rank == 0:
         print("TP_REDUCE_BW " + json.dumps(out), flush=True)
     return ""
+
+
+def case_cp(dev):
+    """Context parallel forward == single-device forward over the concatenated sequence: logits of
+    every segment, the state after the sequence, and a second call that continues from that state."""
+    from .cp import ContextParallel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    T = 64
+    notes = []
+    for rot in ("alibi", "rope", "pope"):
+        m = _bdh(dev, rot).eval()
+        for p in m.parameters():
+            dist.broadcast(p.data, src=0)
+        g = torch.Generator().manual_seed(3)
+        toks = torch.randint(0, 256, (2, 2 * world * T), generator=g).to(dev)
+        half = world * T
+        with torch.no_grad():
+            ref_state = m.init_state()
+            ref1 = m.forward_with_state(toks[:, :half], ref_state)
+            ref2 = m.forward_with_state(toks[:, half:], ref_state)
+            cp = ContextParallel(m)
+            st = m.init_state()
+            mine1 = cp.forward_with_state(toks[:, rank * T:(rank + 1) * T].contiguous(), st)
+            assert st.position == half
+            mine2 = cp.forward_with_state(toks[:, half + rank * T:half + (rank + 1) * T].contiguous(), st)
+            assert st.position == 2 * half
+            st_p, last = cp.prefill(toks[:, :half])
+        tol = 5e-2 if dev.type == "cuda" else 1e-4
+        assert _rel(mine1, ref1[:, rank * T:(rank + 1) * T]) < tol, (rot, "first", _rel(mine1, ref1[:, rank * T:(rank + 1) * T]))
+        assert _rel(mine2, ref2[:, rank * T:(rank + 1) * T]) < tol, (rot, "second", _rel(mine2, ref2[:, rank * T:(rank + 1) * T]))
+        for a, b in zip(st.layers, ref_state.layers):
+            assert _rel(a.rho, b.rho) < tol, (rot, "state", _rel(a.rho, b.rho))
+        assert _rel(last, ref1[:, -1]) < tol and st_p.position == half
+        notes.append(rot)
+    return " ".join(notes)

@@ -31,4 +31,13 @@ def test_fsdp_sharded_optimizer_equals_single_gpu():
 
 def test_neuron_tensor_parallel_equals_single_gpu():
     out = run_ranks("tp", cpu=False, timeout=600)
-    assert "rope:fused" in out
+    assert "rope:rs" in out and "pope:nccl" in out
+
+
+def test_gemm_with_reduction_epilogue_every_mode():
+    out = run_ranks("tp_reduce", cpu=False)
+    assert "rs" in out
+
+
+def test_context_parallel_equals_single_gpu():
+    run_ranks("cp", cpu=False)

@@ -31,3 +31,7 @@ def test_rank_exit_is_detected_on_host():
 
 def test_fsdp_host_logic_gloo():
     run_ranks("fsdp")
+
+
+def test_context_parallel_equals_single_process_gloo():
+    run_ranks("cp")
