@@ -36,7 +36,7 @@ BATCH_PER_GPU = 32
 
 def reference_arm(args) -> int:
     """The reference is a Rust crate (Burn 0.19); there is no Rust toolchain or vendored crate set
-    in this image and `pip install /root/reference` has nothing to install, so it cannot run."""
+    in this image and `pip install` of the reference tree has nothing to install, so it cannot run."""
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust/Burn crate: no cargo/rustc in the image, crates not vendored, "
                       "and it has no setup.py/pyproject.toml for pip to install"}))

@@ -10,7 +10,9 @@ from burn_dragon_b200.data.tokenizer import CharVocab
 from burn_dragon_b200.engine import burn_record as BR
 from burn_dragon_b200.models.bdh import BDH, BDHConfig
 
-ASSET = Path("/root/reference/www/assets/model/tiny_shakespeare")
+# the reference checkout sits beside this repository (or where BDH_REFERENCE_DIR points)
+_REF = Path(os.environ.get("BDH_REFERENCE_DIR", Path(__file__).resolve().parents[2] / "reference"))
+ASSET = _REF / "www" / "assets" / "model" / "tiny_shakespeare"
 needs_asset = pytest.mark.skipif(not (ASSET / "model.bin").exists(), reason="reference checkpoint not mounted")
 
 SNIPPET = ("First Citizen:\nBefore we proceed any further, hear me speak.\n\nAll:\nSpeak, speak.\n\n"
