@@ -279,7 +279,9 @@ def cmd_bench(args) -> int:
     from .engine import bench as B
     res = B.run(args.what, args.preset, steps=args.steps, warmup=args.warmup, streams=args.streams,
                 prompt=args.prompt_len, new_tokens=args.new_tokens)
-    print(json.dumps(res))
+    from .parallel import dist_utils
+    if dist_utils.rank() == 0:
+        print(json.dumps(res))
     return 0
 
 

@@ -72,13 +72,21 @@ def bench_train(preset: str, steps: int, warmup: int) -> Dict:
 
 def bench_decode(preset: str, streams: int, prompt: int, new_tokens: int) -> Dict:
     from . import decode_engine as DE
+    from ..parallel import dist_utils
     cfg = C.load_preset(preset)
-    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    # under torch.distributed.run every rank serves its own `streams` streams on its own GPU
+    # (decode streams are independent, so the ranks never talk during generation)
+    world = dist_utils.env_world()
+    if world > 1:
+        dist_utils.init_distributed()
+        torch.cuda.set_device(dist_utils.env_local_rank())
+    dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     torch.manual_seed(0)
     model = build_model(cfg, vocab_size=cfg.model.vocab_size or 256).to(dev).eval()
     V = model.config.vocab_size
     toks = torch.randint(0, V, (streams, prompt), device=dev)
-    res = dict(bench="decode", preset=preset, kind=cfg.model.kind, streams=streams, prompt=prompt, new_tokens=new_tokens)
+    res = dict(bench="decode", preset=preset, kind=cfg.model.kind, streams=streams, prompt=prompt, new_tokens=new_tokens,
+               n_gpus=world, total_streams=streams * world)
     if isinstance(model, BDH) and dev.type == "cuda":
         DE.attach(model)
     for name, s in (("greedy", GEN.GenerationSettings(new_tokens, greedy=True)),
@@ -86,12 +94,16 @@ def bench_decode(preset: str, streams: int, prompt: int, new_tokens: int) -> Dic
         # prefill alone (device-timed), then the whole call; decode time is the difference
         def prefill():
             GEN.prefill_state(model, toks, dev)
+        dist_utils.barrier()
         ms_prefill = _timed(prefill, 1, 1)
         ms_total = _timed(lambda: GEN.generate_tokens(model, toks, dev, s), 1, 0)
+        if world > 1:       # the job is as slow as its slowest rank
+            ms_prefill = dist_utils.max_over_ranks(ms_prefill, dev)
+            ms_total = dist_utils.max_over_ranks(ms_total, dev)
         ms_decode = max(ms_total - ms_prefill, 1e-6)
-        res[name] = dict(prefill_ms=ms_prefill, prefill_tokens_per_s=streams * prompt / ms_prefill * 1e3,
+        res[name] = dict(prefill_ms=ms_prefill, prefill_tokens_per_s=world * streams * prompt / ms_prefill * 1e3,
                          decode_ms_per_token=ms_decode / new_tokens,
-                         decode_tokens_per_s=streams * new_tokens / ms_decode * 1e3)
+                         decode_tokens_per_s=world * streams * new_tokens / ms_decode * 1e3)
     res["kernel_status"] = native.status_code()
     return res
 
