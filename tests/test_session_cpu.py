@@ -1,0 +1,92 @@
+"""Headless inference sessions (the reference's web-page interface as a Python API)."""
+import json
+import os
+from pathlib import Path
+
+import pytest
+import torch
+
+from burn_dragon_b200.data.tokenizer import CharVocab
+from burn_dragon_b200.engine import burn_record as BR
+from burn_dragon_b200.engine import generation as GEN
+from burn_dragon_b200.engine import session as S
+from burn_dragon_b200.models.bdh import BDH, BDHConfig
+
+_REF = Path(os.environ.get("BDH_REFERENCE_DIR", Path(__file__).resolve().parents[2] / "reference"))
+ASSET = _REF / "www" / "assets" / "model" / "tiny_shakespeare"
+
+
+def _artefacts(rot="rope", half=False):
+    torch.manual_seed(0)
+    vocab = CharVocab.fit(["hello world, this is a tiny corpus."], include_unknown=True)
+    m = BDH(BDHConfig(n_layer=2, n_embd=32, n_head=2, mlp_internal_dim_multiplier=2, vocab_size=len(vocab),
+                      dropout=0.0, rotary_embedding=rot)).eval()
+    blob = BR.serialize(BR.from_model(m, half=half))
+    cfg = json.dumps(dict(run_name="t", block_size=32, overrides=dict(
+        n_layer=2, n_embd=32, n_head=2, mlp_internal_dim_multiplier=2, rotary_embedding=rot)))
+    return m, vocab, blob, json.dumps(vocab.to_record()), cfg
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_session_greedy_equals_generate_tokens(half):
+    m, vocab, blob, vjson, cjson = _artefacts(half=half)
+    sess = S.load_model(blob, vjson, cjson, device="cpu")
+    assert sess.block_size == 32 and sess.model.config.n_layer == 2
+    sess.start_stream("hello", max_tokens=12, greedy=True)
+    text = ""
+    chunks = 0
+    while not sess.done:
+        text += sess.next_chunk(max_tokens=4)
+        chunks += 1
+    assert chunks >= 3
+    ids = torch.tensor([vocab.encode("hello")])
+    want = GEN.generate_tokens(sess.model, ids, "cpu", GEN.GenerationSettings(12, greedy=True))[0, 5:].tolist()
+    eos = vocab.eos_id
+    if eos in want:
+        want = want[:want.index(eos)]
+    assert text == vocab.decode(want)
+
+
+def test_session_serves_several_streams_and_respects_limits():
+    m, vocab, blob, vjson, cjson = _artefacts("alibi")
+    sess = S.load_model(blob, vjson, cjson, device="cpu")
+    sess.start_stream(["hello", "world"], max_tokens=6, temperature=1.0, top_k=5, seed=3)
+    out = ["", ""]
+    while not sess.done:
+        a, b = sess.next_chunk(max_tokens=2)
+        out[0] += a
+        out[1] += b
+    assert sess.generated <= 6
+    # same seed, same text
+    sess.start_stream(["hello", "world"], max_tokens=6, temperature=1.0, top_k=5, seed=3)
+    again = ["", ""]
+    while not sess.done:
+        a, b = sess.next_chunk(max_tokens=2)
+        again[0] += a
+        again[1] += b
+    assert again == out
+    with pytest.raises(ValueError):
+        sess.start_stream(["hello", "hi"], max_tokens=2)
+
+
+def test_load_model_rejects_mismatched_artefacts():
+    m, vocab, blob, vjson, cjson = _artefacts()
+    other = CharVocab.fit(["abc"], include_unknown=True)
+    with pytest.raises(ValueError):
+        S.load_model(blob, json.dumps(other.to_record()), cjson, device="cpu")
+    bad = json.loads(cjson)
+    bad["overrides"]["mlp_internal_dim_multiplier"] = 8
+    with pytest.raises(ValueError):
+        S.load_model(blob, vjson, json.dumps(bad), device="cpu")
+
+
+@pytest.mark.skipif(not (ASSET / "model.bin").exists(), reason="reference checkpoint not mounted")
+def test_shipped_checkpoint_streams_text():
+    sess = S.load_model((ASSET / "model.bin").read_bytes(), (ASSET / "vocab.json").read_text(),
+                        (ASSET / "config.json").read_text(), device="cpu")
+    assert sess.model.config.n_layer == 4 and sess.model.config.rotary_embedding == "alibi"
+    sess.start_stream("First Citizen:\n", max_tokens=24, greedy=True)
+    text = ""
+    while not sess.done:
+        text += sess.next_chunk()
+    assert len(text) > 0 and all(ch in sess.tokenizer.ch2id or ch == "?" for ch in text)
