@@ -317,7 +317,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--fp32", action="store_true", help="plain torch fp32 path instead of the bf16 kernels")
     p.add_argument("--viz", action="store_true", help="capture activation images (headless)")
     p.add_argument("--viz-history", type=int, default=256)
-    p.add_argument("--viz-out", default=None, help="write the captured images to this .npz file")
+    p.add_argument("--viz-out", default=None, help="write the captured images to this file (.npz: four arrays; .png: 2x2 panel grid)")
     p.set_defaults(fn=cmd_infer)
     p = sub.add_parser("quantize")
     common(p)

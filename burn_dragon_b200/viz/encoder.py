@@ -141,11 +141,28 @@ class VizEncoder:
         self.token_index = t + 1
         return VizFrame(self.units_x, self.units_y, self.units_xy, self.units_rho, cursor, t)
 
+    def panel_grid(self, gap: int = 8) -> torch.Tensor:
+        """The four images as one 2x2 grid (x | y over x*y | rho), the arrangement of the reference's
+        window (src/viz/bevy_app.rs:538-641), linear RGBA float [2h + gap, 2w + gap, 4]."""
+        h, w, _ = self.units_x.shape
+        grid = torch.zeros(2 * h + gap, 2 * w + gap, 4, device=self.units_x.device)
+        grid[..., 3] = 1.0
+        grid[:h, :w] = self.units_x
+        grid[:h, w + gap:] = self.units_y
+        grid[h + gap:, :w] = self.units_xy
+        grid[h + gap:, w + gap:] = self.units_rho
+        return grid
+
     def save(self, path) -> None:
-        """Write the four images to an .npz file (or, for `.ppm`, the x image as 8-bit RGB)."""
+        """Write the four images to an .npz file; `.png` writes the 2x2 panel grid as 8-bit sRGB
+        (the headless stand-in for the reference's window), `.ppm` the x image alone."""
         import numpy as np
         path = str(path)
         imgs = dict(x=self.units_x, y=self.units_y, xy=self.units_xy, rho=self.units_rho)
+        if path.endswith(".png"):
+            from .image import linear_to_srgb8, write_png
+            write_png(path, linear_to_srgb8(self.panel_grid()[..., :3].cpu().numpy()))
+            return
         if path.endswith(".ppm"):
             a = (self.units_x[..., :3].clamp(0, 1).pow(1 / 2.2) * 255).byte().cpu().numpy()
             with open(path, "wb") as f:

@@ -44,3 +44,26 @@ def test_mailbox_keeps_latest():
     tx.try_send(1)
     tx.try_send(2)
     assert rx.drain_latest() == 2 and rx.drain_latest() is None
+
+
+def test_panel_grid_png_roundtrip(tmp_path):
+    import numpy as np
+    import torch
+    from burn_dragon_b200.viz.encoder import VizConfig, VizEncoder, srgb_to_linear
+    from burn_dragon_b200.viz.image import linear_to_srgb8, read_png_rgb8
+    enc = VizEncoder(VizConfig(history=8), layers=2, heads=2, latent_per_head=4)
+    torch.manual_seed(0)
+    for t in range(5):
+        enc.step([dict(x_last=torch.rand(1, 2, 4), y_last=torch.rand(1, 2, 4), xy_last=torch.rand(1, 2, 4),
+                       rho_last=torch.rand(1, 2, 4)) for _ in range(2)])
+    h, w, _ = enc.units_x.shape
+    grid = enc.panel_grid(gap=3)
+    assert tuple(grid.shape) == (2 * h + 3, 2 * w + 3, 4)
+    assert torch.equal(grid[:h, :w], enc.units_x) and torch.equal(grid[h + 3:, w + 3:], enc.units_rho)
+    enc.save(tmp_path / "panels.png")
+    img = read_png_rgb8(tmp_path / "panels.png")
+    assert img.shape == (2 * h + 8, 2 * w + 8, 3)
+    assert np.array_equal(img[:h, :w], linear_to_srgb8(enc.units_x[..., :3].numpy()))
+    # sRGB transfer is the inverse of the encoder's linearisation
+    for v in (0.0, 0.02, 0.5, 1.0):
+        assert abs(int(linear_to_srgb8(np.array([[srgb_to_linear(v)] * 3]))[0, 0]) - round(v * 255)) <= 1
