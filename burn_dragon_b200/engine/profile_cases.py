@@ -58,6 +58,26 @@ def build(case: str):
         "wgrad": (lambda: G.gemm(act, cur, M=HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM,
                                  out0=torch.zeros(HN, D, device="cuda")), gemm_fl, big),
     }
+    if case in ("rownorm_fwd", "fast_attention"):
+        # forward_fast attention at T = 2048 (B 8, H 4, N 2048, D 256): scores are 268 MB in bf16
+        from ..ops import rownorm_attention as RA
+        Bf, Tf, Nf = 8, 2048, 2048
+        if case == "rownorm_fwd":
+            Sc = _rnd(Bf * H * Tf, Tf, 0.1)
+            rn = torch.empty(Bf * H * Tf, device="cuda")
+            # strictly causal rows: half of the matrix is read and written once
+            return (lambda: native.ops.rownorm_fwd(Sc, rn, Tf)), 0.0, 2.0 * Sc.numel()
+        qf = (_rnd(Bf * H * Tf, Nf, 0.1).relu().view(Bf, H, Tf, Nf)).requires_grad_(True)
+        vf = _rnd(Bf * Tf, D).view(Bf, 1, Tf, D).requires_grad_(True)
+        sl = torch.tensor([1.0, 0.5, 0.25, 0.125], device="cuda")
+        go = torch.randn(Bf, H, Tf, D, device="cuda", dtype=torch.bfloat16)
+
+        def fwd_bwd():
+            qf.grad = vf.grad = None
+            RA.attention_rownorm(qf, vf, sl).backward(go)
+        # scores + G (causal halves) and the four T x T x N products of dq count as executed FLOPs
+        fl = 2.0 * Bf * H * Tf * Tf * (Nf + D) + 2.0 * Bf * H * Tf * Tf * (D + D) + 2.0 * 2.0 * Bf * H * Tf * Tf * Nf
+        return fwd_bwd, fl, 0.0
     return cases[case]
 
 
