@@ -164,6 +164,15 @@ class BDH(nn.Module):
         """One layer. cur [B,1,T,D]. mode: 'recurrent' | 'parallel' | 'chunked' | 'fast'."""
         c = self.config
         mask = self._latent_mask(cur.device, cur.dtype)
+        # neuron-sharded tensor parallelism (parallel/tp.py): `cur` and LN(a) are replicated inputs of
+        # sharded products (their gradients are summed over the ranks), `a` and the decoder output are
+        # partial sums over the neuron shards (summed in the forward pass); the residual uses `cur` as is
+        tp = getattr(self, "_tp", None)
+        res = cur
+        if tp is not None:
+            if mode == "fast":
+                raise NotImplementedError("the row-normalised path is not neuron-sharded")
+            cur = tp.copy(cur)
         x = R.relu_lowrank(cur, self._enc(self.encoder).to(cur.dtype), None, c.relu_threshold, mask)
         new_rho = None
         if mode == "fast":
@@ -195,13 +204,19 @@ class BDH(nn.Module):
                 a, new_rho = R.linear_attention_chunked(q, cur, self._slopes(), rho)
             else:
                 a, new_rho = R.linear_attention_parallel(q, cur, self._slopes(), rho)
+        if tp is not None:
+            a = tp.reduce(a)
         a = R.layer_norm(a)
+        if tp is not None:
+            a = tp.copy(a)
         y = R.relu_lowrank(a, self._enc(self.encoder_v).to(cur.dtype), None, c.relu_threshold, mask)
         xy = F.dropout(x * y, c.dropout, self.training)
         B, H, T, N = xy.shape
         mlp = xy.transpose(1, 2).reshape(B * T, H * N) @ self.decoder.to(cur.dtype)
+        if tp is not None:
+            mlp = tp.reduce(mlp)
         mlp = R.layer_norm(mlp.view(B, 1, T, c.n_embd))
-        out = R.layer_norm(cur + mlp)
+        out = R.layer_norm(res + mlp)
         return out, new_rho, (x, y, xy)
 
     def _forward_torch(self, tokens, state: Optional[ModelState], mode: str):

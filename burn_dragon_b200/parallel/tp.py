@@ -161,6 +161,50 @@ class TPComm:
         return b.view.to(torch.bfloat16) if bf16 else b.view
 
 
+class _CopyToShards(torch.autograd.Function):
+    """Replicated tensor entering a neuron-sharded product: identity forward, sum of the ranks'
+    partial gradients backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromShards(torch.autograd.Function):
+    """Partial sums over the neuron shards: summed forward, identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous().clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class TorchTP:
+    """The two collectives of neuron sharding for the torch path of the model (any device, any
+    backend): what the kernel path fuses into GEMM epilogues, stated with `all_reduce`."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def copy(self, x):
+        return _CopyToShards.apply(x, self.group)
+
+    def reduce(self, x):
+        return _ReduceFromShards.apply(x, self.group)
+
+
 def shard_rows(w: torch.Tensor, H: int, N: int, rank: int, world: int) -> torch.Tensor:
     """[H*N, D] -> this rank's [H*N/world, D] (neurons [rank*N/world, (rank+1)*N/world) of every head)."""
     Nl = N // world
@@ -208,6 +252,11 @@ class NeuronTP:
                 d.freqs = d.freqs_full = full_freqs[self.rank * Nl:(self.rank + 1) * Nl].contiguous()
 
         self.shard._dims_hook = dims_hook
+        # the torch path of the shard (CPU ranks, shapes the kernels do not take): same sharding, with
+        # this rank's slice of the rotary frequencies and all_reduce where the partial sums meet
+        self.shard._tp = TorchTP(group)
+        if c.rotary_embedding in ("rope", "pope"):
+            self.shard.freqs.data = full_freqs[self.rank * Nl:(self.rank + 1) * Nl].clone()
         self.opt = FlatAdamW(self.shard, lr, weight_decay, beta1, beta2, eps, shadow_bf16=dev.type == "cuda")
         self.optimizer = self.opt
         self.lr = lr

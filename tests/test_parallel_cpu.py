@@ -35,3 +35,8 @@ def test_fsdp_host_logic_gloo():
 
 def test_context_parallel_equals_single_process_gloo():
     run_ranks("cp")
+
+
+def test_neuron_tensor_parallel_equals_single_process_gloo():
+    out = run_ranks("tp")
+    assert "rope:nccl" in out and "alibi:nccl" in out and "pope:nccl" in out
