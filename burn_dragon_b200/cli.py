@@ -108,6 +108,8 @@ def cmd_train(args) -> int:
         run_name = run_dir.name
         mp, sp, start_epoch = CK.resolve_checkpoint(str(run_dir))
         CK.load_checkpoint(model, mp, sp, trainer, train_loader)
+        if wrapper is not None:
+            wrapper.sync_from_model()
         if rank == 0:
             print(f"resumed {run_name} at epoch {start_epoch}, step {trainer.step_index}", flush=True)
     else:
@@ -148,9 +150,10 @@ def cmd_train(args) -> int:
             break           # the loader's global step cap is exhausted
         vloss = [float(trainer.eval_step(b.inputs, b.targets)) for b in valid_loader]
         log.log("valid", trainer.step_index, loss=sum(vloss) / len(vloss), epoch=epoch)
-        logical = wrapper.gather_state_dict() if wrapper is not None else None
+        logical, opt_state = CK.gather_for_checkpoint(trainer, wrapper)      # collective under FSDP / TP
         if rank == 0:
-            CK.save_checkpoint(run_dir, epoch, model, trainer, train_loader, logical_state=logical)
+            CK.save_checkpoint(run_dir, epoch, model, trainer, train_loader, logical_state=logical,
+                               optimizer_state=opt_state)
         dist_utils.barrier()
         if trainer.step_index >= total_steps:
             break

@@ -25,6 +25,7 @@ from pathlib import Path
 from typing import Any, Dict, Optional, Tuple
 
 import torch
+import torch.distributed as dist
 
 from . import burn_record as BR
 
@@ -106,10 +107,24 @@ def resolve_checkpoint(spec: Optional[str], epoch: Optional[int] = None, run_roo
     return model, (state if state.exists() else None), ep
 
 
+def gather_for_checkpoint(trainer, wrapper=None):
+    """The collective half of a checkpoint under a sharded wrapper: EVERY rank calls this, then rank 0
+    alone passes the two results to `save_checkpoint`. Returns (weights, optimizer state) in the
+    unsharded layout, or (None, None) without a wrapper."""
+    if wrapper is None:
+        return None, None
+    weights = wrapper.gather_state_dict()
+    opt = getattr(trainer, "opt", None)
+    opt_state = opt.logical_state_dict() if opt is not None and hasattr(opt, "logical_state_dict") else None
+    return weights, opt_state
+
+
 def save_checkpoint(run_dir, epoch: int, model, trainer=None, loader=None, extra: Optional[Dict[str, Any]] = None,
-                    logical_state: Optional[Dict[str, torch.Tensor]] = None) -> Path:
-    """Write model-<epoch>.bin (BDH) and state-<epoch>.pt. `logical_state` overrides the model's
-    own state dict (sharded wrappers pass the gathered tensors; call on rank 0 only)."""
+                    logical_state: Optional[Dict[str, torch.Tensor]] = None,
+                    optimizer_state: Optional[Dict[str, Any]] = None) -> Path:
+    """Write model-<epoch>.bin (BDH) and state-<epoch>.pt. Under a sharded wrapper `logical_state` and
+    `optimizer_state` come from `gather_for_checkpoint` (nothing in here talks to other ranks, so
+    calling it on rank 0 alone is safe)."""
     ckpt = Path(run_dir) / "checkpoint"
     ckpt.mkdir(parents=True, exist_ok=True)
     sd = logical_state if logical_state is not None else {k: v.detach().cpu() for k, v in model.state_dict().items()}
@@ -127,7 +142,12 @@ def save_checkpoint(run_dir, epoch: int, model, trainer=None, loader=None, extra
     if trainer is not None:
         state["step_index"] = trainer.step_index
         opt = getattr(trainer, "opt", None)
-        if opt is not None and hasattr(opt, "logical_state_dict"):
+        if optimizer_state is not None:
+            state["optimizer"] = optimizer_state
+        elif opt is not None and hasattr(opt, "logical_state_dict"):
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                raise RuntimeError("sharded optimizer state must be gathered on every rank first "
+                                   "(gather_for_checkpoint)")
             state["optimizer"] = opt.logical_state_dict()
         elif opt is not None:
             f = opt.flat

@@ -69,9 +69,13 @@ class Trainer:
 
     @torch.no_grad()
     def eval_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        was = self.model.training
-        self.model.eval()
+        # a tensor-parallel wrapper evaluates its shard (the full module's weights are stale while it trains)
+        m = getattr(self.wrapper, "eval_model", None) or self.model
+        was = m.training
+        m.eval()
         try:
-            return self.loss_fn(tokens, targets).detach()
+            if self.fast_train and hasattr(m, "forward_fast"):
+                return m.forward_fast(tokens, targets).detach()
+            return m(tokens, targets).detach()
         finally:
-            self.model.train(was)
+            m.train(was)

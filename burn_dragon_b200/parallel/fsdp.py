@@ -125,6 +125,16 @@ class FSDP:
         full = self._gather(self.master)
         self.flat.master.copy_(full[:self.flat.numel])
 
+    @torch.no_grad()
+    def sync_from_model(self) -> None:
+        """Re-shard after the module's weights were replaced (checkpoint load): the parameters are
+        views of the flat fp32 buffer, this rank's master slice and the bf16 copy follow it."""
+        n = self.flat.numel
+        full = torch.zeros(self.numel, dtype=torch.float32, device=self.flat.master.device)
+        full[:n].copy_(self.flat.master)
+        self.master.copy_(full[self.lo:self.hi])
+        self.flat.refresh_shadow()
+
     def gather_state_dict(self) -> Dict[str, torch.Tensor]:
         self.sync_params()
         return {k: v.detach().cpu().clone() for k, v in self.model.state_dict().items()}

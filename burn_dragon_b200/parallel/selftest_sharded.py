@@ -212,3 +212,58 @@ def case_cp(dev):
         assert _rel(last, ref1[:, -1]) < tol and st_p.position == half
         notes.append(rot)
     return " ".join(notes)
+
+
+def case_ckpt(dev):
+    """Checkpoint / resume under the sharded wrappers: two steps, save (weights and optimizer state in
+    the unsharded layout, gathered by all ranks, written by rank 0), load into a fresh differently
+    initialised model + wrapper, one more step == three uninterrupted steps."""
+    import tempfile
+    from ..engine import checkpoint as CK
+    from ..engine.trainer import Trainer
+    from .fsdp import FSDP
+    from .tp import NeuronTP
+    rank, world = dist.get_rank(), dist.get_world_size()
+    g = torch.Generator().manual_seed(11)
+    data = torch.randint(0, 256, (2, 65), generator=g).to(dev)
+    x, y = data[:, :-1], data[:, 1:]
+    notes = []
+    for kind in ("fsdp", "tp"):
+        def make(seed):
+            torch.manual_seed(seed)
+            m = _bdh(dev, "rope", N=128 * world)
+            if seed:
+                with torch.no_grad():
+                    for p in m.parameters():
+                        p.add_(torch.randn_like(p) * 0.01)
+            w = FSDP(m, lr=1e-2) if kind == "fsdp" else NeuronTP(m, lr=1e-2)
+            return m, w, Trainer(m, lr=1e-2, wrapper=w)
+
+        m_a, w_a, t_a = make(0)
+        for _ in range(3):
+            loss_a = t_a.train_step(x, y)
+        want = w_a.gather_state_dict()
+
+        m_b, w_b, t_b = make(0)
+        for _ in range(2):
+            t_b.train_step(x, y)
+        weights, opt_state = CK.gather_for_checkpoint(t_b, w_b)
+        box = [tempfile.mkdtemp() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        if rank == 0:
+            CK.save_checkpoint(box[0], 1, m_b, t_b, None, logical_state=weights, optimizer_state=opt_state)
+        dist.barrier()
+        m_c, w_c, t_c = make(5)
+        mp, sp, ep = CK.resolve_checkpoint(box[0])
+        CK.load_checkpoint(m_c, mp, sp, t_c, None)
+        w_c.sync_from_model()
+        assert t_c.step_index == 2 and ep == 1
+        loss_c = t_c.train_step(x, y)
+        got = w_c.gather_state_dict()
+        tol = 2e-2 if dev.type == "cuda" else 1e-5
+        assert abs(loss_a.item() - loss_c.item()) < tol * max(1.0, abs(loss_a.item())), (kind, loss_a.item(), loss_c.item())
+        for k in want:
+            assert _rel(got[k].float(), want[k].float()) < tol, (kind, k, _rel(got[k].float(), want[k].float()))
+        notes.append(kind)
+        dist.barrier()
+    return " ".join(notes)

@@ -217,6 +217,48 @@ def unshard_rows(parts, H: int, N: int) -> torch.Tensor:
     return torch.cat([p.view(H, Nl, -1) for p in parts], dim=1).reshape(H * N, -1)
 
 
+class _TPOptimizerFacade:
+    """The shard's optimizer as the trainer and the checkpoint code see it: steps go to the local
+    FlatAdamW, state goes in and out in the unsharded layout (one full-size tensor per parameter,
+    the same record a single-device run writes), so a run can resume under another group size."""
+
+    def __init__(self, owner: "NeuronTP"):
+        self.owner = owner
+        self.inner = owner.opt
+
+    def __getattr__(self, name):
+        return getattr(self.inner, name)
+
+    def _full(self, buf) -> Dict[str, torch.Tensor]:
+        o, f = self.owner, self.inner.flat
+        c = o.full.config
+        out = {}
+        for i, n in enumerate(f.names):
+            local = f.view(buf, i).detach().contiguous()
+            if n in ("encoder", "encoder_v", "decoder"):
+                parts = [torch.empty_like(local) for _ in range(o.world)]
+                dist.all_gather(parts, local, group=o.group)
+                out[n] = unshard_rows(parts, c.n_head, c.latent_per_head).cpu()
+            else:
+                out[n] = local.cpu().clone()
+        return out
+
+    def logical_state_dict(self) -> Dict:
+        """Collective: every rank of the group calls it."""
+        return dict(step=self.inner.step_count, m=self._full(self.inner.m), v=self._full(self.inner.v))
+
+    def load_logical_state_dict(self, sd: Dict) -> None:
+        o, f = self.owner, self.inner.flat
+        c = o.full.config
+        for buf, key in ((self.inner.m, "m"), (self.inner.v, "v")):
+            for i, n in enumerate(f.names):
+                t = sd[key][n]
+                if n in ("encoder", "encoder_v", "decoder"):
+                    t = shard_rows(t, c.n_head, c.latent_per_head, o.rank, o.world)
+                f.view(buf, i).copy_(t.to(buf.device))
+        self.inner.step_count = int(sd["step"])
+
+
 class NeuronTP:
     def __init__(self, model: BDH, lr=1e-3, weight_decay=0.1, beta1=0.9, beta2=0.999, eps=1e-5, fused=True,
                  group=None):
@@ -258,7 +300,8 @@ class NeuronTP:
         if c.rotary_embedding in ("rope", "pope"):
             self.shard.freqs.data = full_freqs[self.rank * Nl:(self.rank + 1) * Nl].clone()
         self.opt = FlatAdamW(self.shard, lr, weight_decay, beta1, beta2, eps, shadow_bf16=dev.type == "cuda")
-        self.optimizer = self.opt
+        self.optimizer = _TPOptimizerFacade(self)
+        self.eval_model = self.shard        # evaluating the shard under its hooks gives the full model's loss
         self.lr = lr
         self._replicated = [self.shard.embed.weight, self.shard.lm_head]
 
@@ -273,6 +316,17 @@ class NeuronTP:
             p.grad.div_(self.world)
         self.opt.step(lr=self.lr if lr is None else lr)
         return loss.detach()
+
+    @torch.no_grad()
+    def sync_from_model(self) -> None:
+        """Re-shard after the full model's weights were replaced (checkpoint load)."""
+        c = self.full.config
+        self.shard.embed.weight.copy_(self.full.embed.weight)
+        self.shard.lm_head.copy_(self.full.lm_head)
+        for name in ("encoder", "encoder_v", "decoder"):
+            getattr(self.shard, name).copy_(shard_rows(getattr(self.full, name).data, c.n_head, c.latent_per_head,
+                                                       self.rank, self.world))
+        self.opt.flat.refresh_shadow()
 
     def gather_state_dict(self) -> Dict[str, torch.Tensor]:
         c = self.full.config

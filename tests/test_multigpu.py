@@ -41,3 +41,7 @@ def test_gemm_with_reduction_epilogue_every_mode():
 
 def test_context_parallel_equals_single_gpu():
     run_ranks("cp", cpu=False)
+
+
+def test_checkpoint_resume_under_fsdp_and_tp():
+    run_ranks("ckpt", cpu=False)

@@ -40,3 +40,8 @@ def test_context_parallel_equals_single_process_gloo():
 def test_neuron_tensor_parallel_equals_single_process_gloo():
     out = run_ranks("tp")
     assert "rope:nccl" in out and "alibi:nccl" in out and "pope:nccl" in out
+
+
+def test_checkpoint_resume_under_fsdp_and_tp_gloo():
+    out = run_ranks("ckpt")
+    assert "fsdp tp" in out
