@@ -77,7 +77,9 @@ def cmd_train(args) -> int:
     dev = _device(args.device)
     torch.manual_seed(cfg.training.seed)
     ds = D.build_dataset(cfg.dataset, cfg.training)
-    ds.rng = __import__("numpy").random.default_rng(cfg.training.seed + rank)
+    # data-parallel ranks draw different windows; the ranks of a tensor-parallel group work on the same batch
+    data_rank = 0 if (world > 1 and cfg.parallel.strategy == "tp") else rank
+    ds.rng = __import__("numpy").random.default_rng(cfg.training.seed + data_rank)
     model = build_model(cfg, vocab_size=len(ds.tokenizer)).to(dev)
     model.recompute = cfg.training.recompute
     if cfg.precision.compute != "bf16":
@@ -123,7 +125,7 @@ def cmd_train(args) -> int:
             tok.save(run_dir / "vocab.json")
     log = MetricsLogger(run_dir if rank == 0 else None, cfg.training.log_frequency, rank)
 
-    tokens_per_step = cfg.training.batch_size * cfg.training.block_size * world
+    tokens_per_step = cfg.training.batch_size * cfg.training.block_size * (1 if strategy == "tp" else world)
     epoch = start_epoch
     while trainer.step_index < total_steps:
         epoch += 1

@@ -45,3 +45,37 @@ def test_neuron_tensor_parallel_equals_single_process_gloo():
 def test_checkpoint_resume_under_fsdp_and_tp_gloo():
     out = run_ranks("ckpt")
     assert "fsdp tp" in out
+
+
+@pytest.mark.parametrize("strategy", ["fsdp", "tp"])
+def test_cli_train_and_resume_on_two_ranks(tmp_path, strategy):
+    """`train` end to end on two gloo ranks under a sharded wrapper: a run, its checkpoint, a resume."""
+    cfg = tmp_path / "par.toml"
+    cfg.write_text(f"""
+[training]
+batch_size = 4
+block_size = 32
+log_frequency = 2
+
+[model]
+n_layer = 2
+n_embd = 64
+n_head = 2
+mlp_internal_dim_multiplier = 4
+dropout = 0.0
+
+[parallel]
+strategy = "{strategy}"
+""")
+    runs = tmp_path / "runs"
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+            "127.0.0.1"]
+    tail = ["-m", "burn_dragon_b200", "train", "-c", str(cfg), "--synthetic", "--device", "cpu", "--runs", str(runs)]
+    e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
+    port = 29300 + (os.getpid() + len(strategy)) % 200
+    r = subprocess.run(base + ["--master-port", str(port)] + tail + ["--max-iters", "4"], capture_output=True,
+                       text=True, timeout=300, env=e, cwd=ROOT)
+    assert r.returncode == 0 and "[valid       4]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    r = subprocess.run(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"],
+                       capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
+    assert r.returncode == 0 and "step 4" in r.stdout and "[valid       6]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
