@@ -138,16 +138,27 @@ def cmd_train(args) -> int:
             if t0 is not None:
                 t0.record()
             lr = trainer.current_lr()
+            # the steps that get logged also measure gradient norm and activation sparsity
+            logged = (trainer.step_index + 1) % cfg.training.log_frequency == 0 or trainer.step_index + 1 == total_steps
+            probe = getattr(wrapper, "eval_model", None) or model
+            trainer.track_grad_norm = probe.measure_sparsity = logged
             loss = trainer.train_step(batch.inputs, batch.targets)
             step = trainer.step_index
-            if step % cfg.training.log_frequency == 0 or step == total_steps:
+            if logged:
                 if t1 is not None:
                     t1.record()
                     torch.cuda.synchronize()
                     ms = dist_utils.max_over_ranks(t0.elapsed_time(t1), dev)
                 else:
                     ms = (time.perf_counter() - wall) * 1e3
-                log.log("train", step, loss=float(loss), lr=lr, step_ms=ms, tokens_per_s=tokens_per_step / ms * 1e3)
+                extra = {}
+                if trainer.last_grad_norm is not None and wrapper is None:
+                    extra["grad_norm"] = float(trainer.last_grad_norm)
+                sp = getattr(probe, "last_sparsity", None)
+                if sp:
+                    extra.update(x_active=float(sp["x"]), xy_active=float(sp["xy"]))
+                log.log("train", step, loss=float(loss), lr=lr, step_ms=ms, tokens_per_s=tokens_per_step / ms * 1e3,
+                        **extra)
         if trainer.step_index == before:
             break           # the loader's global step cap is exhausted
         vloss = [float(trainer.eval_step(b.inputs, b.targets)) for b in valid_loader]

@@ -14,6 +14,7 @@
 // only grow (the host passes a new epoch each call). Every wait is bounded by BDH_WAIT_LIMIT_NS;
 // a wait that runs out writes STATUS_TIMEOUT_PEER_FLAG to the status word and the kernel returns.
 #include "bdh_kernels.h"
+#include "flag_protocol.h"
 #include "sm100_ptx.cuh"
 
 namespace bdh {
@@ -46,11 +47,11 @@ __device__ bool cta_barrier_all_ranks(const CollPeers& p, uint32_t value, int* s
   __threadfence_system();
   if (threadIdx.x < p.world) {
     const int peer = threadIdx.x;
-    st_release_sys(p.flags[peer] + blockIdx.x * p.world + p.rank, value);
-    const uint32_t* mine = p.flags[p.rank] + blockIdx.x * p.world + peer;
+    st_release_sys(p.flags[peer] + flag_slot(blockIdx.x, p.world, p.rank), value);
+    const uint32_t* mine = p.flags[p.rank] + flag_slot(blockIdx.x, p.world, peer);
     const uint64_t t0 = global_timer_ns();
     uint32_t it = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
+    while (!flag_reached(ld_acquire_sys(mine), value)) {
       if ((++it & 255u) == 0 && global_timer_ns() - t0 > BDH_WAIT_LIMIT_NS) {
         atomicCAS(status, STATUS_OK, STATUS_TIMEOUT_PEER_FLAG);
         failed = 1;
@@ -101,7 +102,7 @@ __device__ __forceinline__ float4 reduce_f32x4(const CollPeers& p, long long i) 
 // n4 = number of float4 elements (the buffer is padded to a multiple of 4 * world floats).
 __global__ void __launch_bounds__(COLL_THREADS)
 allreduce_scale_kernel(CollPeers p, long long n4, float scale, uint32_t epoch, int* status) {
-  if (!cta_barrier_all_ranks(p, 2 * epoch + 1, status)) return;
+  if (!cta_barrier_all_ranks(p, flag_value(epoch, 1), status)) return;
   const long long per = n4 / p.world;
   const long long lo = per * p.rank;
   const long long hi = (p.rank == p.world - 1) ? n4 : lo + per;
@@ -117,7 +118,7 @@ allreduce_scale_kernel(CollPeers p, long long n4, float scale, uint32_t epoch, i
         if (r < p.world) static_cast<float4*>(p.buf[r])[i] = s;
     }
   }
-  cta_barrier_all_ranks(p, 2 * epoch + 2, status);
+  cta_barrier_all_ranks(p, flag_value(epoch, 2), status);
 }
 
 struct AdamArgs {
@@ -129,7 +130,7 @@ struct AdamArgs {
 __global__ void __launch_bounds__(COLL_THREADS)
 rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, long long n4, AdamArgs a,
                    uint32_t epoch, int* status) {
-  if (!cta_barrier_all_ranks(p, 2 * epoch + 1, status)) return;
+  if (!cta_barrier_all_ranks(p, flag_value(epoch, 1), status)) return;
   const long long per = n4 / p.world;
   const long long lo = per * p.rank;
   const long long hi = (p.rank == p.world - 1) ? n4 : lo + per;
@@ -159,7 +160,7 @@ rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, 
     for (int r = 0; r < COLL_MAX_RANKS; ++r)
       if (r < q.world) static_cast<uint2*>(q.buf[r])[i] = u;
   }
-  cta_barrier_all_ranks(p, 2 * epoch + 2, status);
+  cta_barrier_all_ranks(p, flag_value(epoch, 2), status);
 }
 
 // Second half of a reduce-scatter done by GEMM epilogues (EPI_F_PEER_RS): slot s of this rank's
@@ -171,7 +172,7 @@ rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, 
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(COLL_THREADS)
 gather_blocks_kernel(CollPeers p, CollPeers q, long long per4, uint32_t epoch, int* status) {
-  if (!cta_barrier_all_ranks(p, 2 * epoch + 1, status)) return;
+  if (!cta_barrier_all_ranks(p, flag_value(epoch, 1), status)) return;
   const float4* src = static_cast<const float4*>(p.buf[p.rank]);
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -217,13 +218,13 @@ gather_blocks_kernel(CollPeers p, CollPeers q, long long per4, uint32_t epoch, i
       }
     }
   }
-  cta_barrier_all_ranks(p, 2 * epoch + 2, status);
+  cta_barrier_all_ranks(p, flag_value(epoch, 2), status);
 }
 
 // All ranks meet here (one CTA per rank): everything each rank launched before it on the stream is
 // complete and visible to the others when it returns.
 __global__ void rank_barrier_kernel(CollPeers p, uint32_t epoch, int* status) {
-  cta_barrier_all_ranks(p, 2 * epoch + 1, status);
+  cta_barrier_all_ranks(p, flag_value(epoch, 1), status);
 }
 
 // Test hook for the bounded wait: waits on a flag slot that nothing writes, with a short limit,
@@ -231,7 +232,7 @@ __global__ void rank_barrier_kernel(CollPeers p, uint32_t epoch, int* status) {
 __global__ void wait_timeout_probe_kernel(const uint32_t* flag, uint32_t value, unsigned long long limit_ns,
                                           int* status) {
   const uint64_t t0 = global_timer_ns();
-  while (static_cast<int32_t>(ld_acquire_sys(flag) - value) < 0) {
+  while (!flag_reached(ld_acquire_sys(flag), value)) {
     if (global_timer_ns() - t0 > limit_ns) {
       atomicCAS(status, STATUS_OK, STATUS_TIMEOUT_PEER_FLAG);
       return;

@@ -1,12 +1,16 @@
-// Host-side native helpers (no CUDA): batch window gathering for the data loader and the
-// bincode-2 varint scanner / writer used by the Burn record codec. Plain C ABI, loaded with ctypes.
+// Host-side native helpers (no CUDA): batch window gathering for the data loader, the bincode-2
+// varint scanner / writer used by the Burn record codec, the UTF-8 character tokenizer scan, and a
+// threaded simulation of the cross-rank flag barrier. Plain C ABI, loaded with ctypes.
 //
 // The reference's counterparts are Rust: the window sampler of src/dataset/scheduler.rs:72-110 and
 // the external BinFileRecorder used at src/bin/infer.rs:177-186 and src/bin/quantize.rs:44-63.
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <thread>
 #include <vector>
+
+#include "../flag_protocol.h"
 
 extern "C" {
 
@@ -160,6 +164,66 @@ int64_t bdh_encode_utf8_chars(const uint8_t* s, int64_t n_bytes, const int32_t* 
     i += len;
   }
   return n;
+}
+
+// Stress test of the cross-rank flag barrier (flag_protocol.h) with one real thread per (rank, CTA):
+// every call `e` each thread publishes a payload, passes the opening barrier, checks that it sees
+// exactly call e's payload of every peer (not an older one: ordering; not a newer one: nobody ran
+// ahead), publishes a result, passes the closing barrier and checks the peers' results. Threads
+// yield at random points so the interleavings differ from run to run. `first_epoch` lets the test
+// start just below the sign bit or the wrap of the 32-bit counter. Returns 0 when all checks held,
+// 1 on a wrong payload, 2 when a wait exceeded `spin_limit` polls (a deadlock in the protocol).
+int bdh_sim_flag_barrier(int world, int ctas, int calls, uint32_t first_epoch, uint64_t seed, int64_t spin_limit) {
+  if (world < 1 || world > 8 || ctas < 1 || calls < 1) return -1;
+  const int slots = ctas * world;
+  std::vector<std::atomic<uint32_t>> flags(static_cast<size_t>(world) * slots);
+  std::vector<std::atomic<uint32_t>> payload(static_cast<size_t>(world) * ctas), result(static_cast<size_t>(world) * ctas);
+  for (auto& f : flags) f.store(first_epoch == 0 ? 0u : flag_value(first_epoch - 1, 2), std::memory_order_relaxed);
+  for (auto& x : payload) x.store(0xFFFFFFFFu, std::memory_order_relaxed);
+  for (auto& x : result) x.store(0xFFFFFFFFu, std::memory_order_relaxed);
+  std::atomic<int> verdict{0};
+
+  auto worker = [&](int rank, int cta) {
+    uint64_t rng = seed * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(rank * 131 + cta) * 0xBF58476D1CE4E5B9ull + 1;
+    auto jitter = [&]() {
+      rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17;
+      if ((rng & 3u) == 0) std::this_thread::yield();
+    };
+    auto barrier = [&](uint32_t value) -> bool {
+      for (int peer = 0; peer < world; ++peer) {
+        jitter();
+        flags[static_cast<size_t>(peer) * slots + flag_slot(cta, world, rank)].store(value, std::memory_order_release);
+      }
+      for (int peer = 0; peer < world; ++peer) {
+        int64_t spins = 0;
+        while (!flag_reached(flags[static_cast<size_t>(rank) * slots + flag_slot(cta, world, peer)].load(std::memory_order_acquire), value)) {
+          if (verdict.load(std::memory_order_relaxed) != 0) return false;
+          if (++spins > spin_limit) { verdict.store(2); return false; }
+          if ((spins & 63) == 0) std::this_thread::yield();
+        }
+      }
+      return true;
+    };
+    for (int c = 0; c < calls; ++c) {
+      const uint32_t epoch = first_epoch + static_cast<uint32_t>(c);
+      jitter();
+      payload[static_cast<size_t>(rank) * ctas + cta].store(epoch, std::memory_order_relaxed);
+      if (!barrier(flag_value(epoch, 1))) return;
+      for (int peer = 0; peer < world; ++peer) {
+        jitter();
+        if (payload[static_cast<size_t>(peer) * ctas + cta].load(std::memory_order_relaxed) != epoch) { verdict.store(1); return; }
+      }
+      result[static_cast<size_t>(rank) * ctas + cta].store(epoch ^ 0x5A5A5A5Au, std::memory_order_relaxed);
+      if (!barrier(flag_value(epoch, 2))) return;
+      for (int peer = 0; peer < world; ++peer)
+        if (result[static_cast<size_t>(peer) * ctas + cta].load(std::memory_order_relaxed) != (epoch ^ 0x5A5A5A5Au)) { verdict.store(1); return; }
+    }
+  };
+  std::vector<std::thread> threads;
+  for (int r = 0; r < world; ++r)
+    for (int c = 0; c < ctas; ++c) threads.emplace_back(worker, r, c);
+  for (auto& t : threads) t.join();
+  return verdict.load();
 }
 
 }  // extern "C"

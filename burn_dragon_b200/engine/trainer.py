@@ -14,6 +14,7 @@ import torch
 
 from ..parallel import dist_utils
 from ..parallel.ddp import DataParallel
+from ..utils import profiling as prof
 from .optim import FlatAdamW, FlatParams, LRSchedule
 
 
@@ -28,6 +29,8 @@ class Trainer:
         self.schedule = schedule
         self.parallel = parallel
         self.step_index = 0
+        self.track_grad_norm = False      # set by the metrics logger on the steps it logs
+        self.last_grad_norm = None
         self.wrapper = wrapper
         if wrapper is not None:
             # FSDP / TP wrappers own parameter storage, gradient reduction and the optimizer
@@ -53,17 +56,25 @@ class Trainer:
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One optimizer step. Returns the (local) loss as a 0-d device tensor; no host sync."""
         if self.wrapper is not None:
-            loss = self.wrapper.train_step(tokens, targets, self.current_lr())
+            with prof.phase("step"):
+                loss = self.wrapper.train_step(tokens, targets, self.current_lr())
             self.step_index += 1
             return loss
-        self.opt.zero_grad()
-        loss = self.loss_fn(tokens, targets)
-        loss.backward()
-        scale = self.dp.reduce_gradients() if self.dp is not None else 1.0
-        if self.grad_clip:
-            gn = (self.opt.flat.grad.norm() * scale)
-            scale = scale * float(torch.clamp(self.grad_clip / (gn + 1e-6), max=1.0))
-        self.opt.step(lr=self.current_lr(), grad_scale=scale)
+        with prof.phase("step"):
+            self.opt.zero_grad()
+            with prof.phase("forward"):
+                loss = self.loss_fn(tokens, targets)
+            with prof.phase("backward"):
+                loss.backward()
+            with prof.phase("grad_reduce"):
+                scale = self.dp.reduce_gradients() if self.dp is not None else 1.0
+            if self.grad_clip or self.track_grad_norm:
+                # norm of the averaged gradient, kept on the device (read it with `.item()` when logging)
+                self.last_grad_norm = self.opt.flat.grad.norm() * scale
+            if self.grad_clip:
+                scale = scale * float(torch.clamp(self.grad_clip / (self.last_grad_norm + 1e-6), max=1.0))
+            with prof.phase("optimizer"):
+                self.opt.step(lr=self.current_lr(), grad_scale=scale)
         self.step_index += 1
         return loss.detach()
 

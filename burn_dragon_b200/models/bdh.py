@@ -227,6 +227,9 @@ class BDH(nn.Module):
         for l in range(c.n_layer):
             rho = state.layers[l].rho if state is not None else None
             cur, new_rho, acts = self._layer_torch(cur, start, rho, mode)
+            if l == c.n_layer - 1 and getattr(self, "measure_sparsity", False):
+                self.last_sparsity = dict(x=(acts[0] != 0).float().mean().detach(),
+                                          xy=(acts[2] != 0).float().mean().detach())
             if state is not None and mode != "fast":
                 state.layers[l].rho = new_rho
                 if self.capture_viz:

@@ -22,6 +22,7 @@ import torch
 from . import gemm as G
 from . import native
 from . import reference as R
+from ..utils import profiling as prof
 
 ops = native.ops
 
@@ -363,11 +364,15 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int
     for l in range(d.L):
         rho_in = state.layers[l].rho if state is not None else None
         seed_l = (d.drop_base + 0x632BE5AB * (l + 1)) & 0x7FFFFFFF
-        out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None, drop_seed=seed_l)
+        with prof.phase("layer.forward"):
+            out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None, drop_seed=seed_l)
         if state is not None:
             state.layers[l].rho = rho_out
         if save:
             saved.append(dict(cur=cur, drop_seed=seed_l) if l < recompute else sv)
+        if l == d.L - 1 and getattr(model, "measure_sparsity", False):
+            # fraction of active neurons in the last layer, left on the device for the metrics logger
+            model.last_sparsity = dict(x=(sv["x"] != 0).float().mean(), xy=(sv["xy"] != 0).float().mean())
         cur = out
     if state is not None:
         state.position += d.T
@@ -392,10 +397,11 @@ class _FusedLoss(torch.autograd.Function):
         recompute = recompute_count(model, d)
         model._recomputed_layers = recompute
         cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute)
-        logits = _head_logits(d, W, cur)
-        row_loss = torch.empty(d.M, device=tokens.device, dtype=torch.float32)
-        dlogits = _bf16(d.M, d.V, tokens.device)
-        ops.cross_entropy(logits, targets.reshape(-1).contiguous(), row_loss, dlogits, 1.0 / d.M)
+        with prof.phase("head.loss"):
+            logits = _head_logits(d, W, cur)
+            row_loss = torch.empty(d.M, device=tokens.device, dtype=torch.float32)
+            dlogits = _bf16(d.M, d.V, tokens.device)
+            ops.cross_entropy(logits, targets.reshape(-1).contiguous(), row_loss, dlogits, 1.0 / d.M)
         ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits = d, W, saved, cur, dlogits
         ctx.tokens = tokens
         ctx.recompute = recompute
@@ -419,8 +425,10 @@ class _FusedLoss(torch.autograd.Function):
         for l in reversed(range(d.L)):
             sv = saved[l]
             if "x" not in sv:
-                _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
-            dcur = _layer_backward(d, W, sv, dcur, grads, 0)
+                with prof.phase("layer.recompute"):
+                    _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
+            with prof.phase("layer.backward"):
+                dcur = _layer_backward(d, W, sv, dcur, grads, 0)
             saved[l] = None
         g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)
         ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)

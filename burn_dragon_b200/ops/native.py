@@ -11,6 +11,8 @@ import threading
 
 import torch
 
+from ..utils import profiling as prof
+
 _lock = threading.Lock()
 _state = {"loaded": False, "error": None}
 
@@ -74,6 +76,12 @@ class _CountingOps:
 
         def call(*a, **k):
             self.count += 1
+            if prof.nvtx_on():
+                torch.cuda.nvtx.range_push("bdh." + name)
+                try:
+                    return fn(*a, **k)
+                finally:
+                    torch.cuda.nvtx.range_pop()
             return fn(*a, **k)
 
         self.__dict__[name] = call

@@ -24,6 +24,7 @@ def _load():
             lib.bdh_varint_read.restype = ctypes.c_int
             lib.bdh_varint_write.restype = ctypes.c_int
             lib.bdh_encode_utf8_chars.restype = ctypes.c_int64
+            lib.bdh_sim_flag_barrier.restype = ctypes.c_int
             _LIB = lib
         except OSError:
             _LIB = False
@@ -79,3 +80,13 @@ def encode_utf8_chars(data: bytes, table: np.ndarray, unk_id) -> np.ndarray:
     if n < 0:
         raise KeyError(chr(bad.value))
     return out[:n]
+
+
+def simulate_flag_barrier(world: int, ctas: int, calls: int, first_epoch: int = 0, seed: int = 0,
+                          spin_limit: int = 50_000_000) -> int:
+    """Run the cross-rank flag barrier protocol on real threads (one per rank and CTA) with random
+    yields; 0 = every ordering check held, 1 = a stale or early payload was seen, 2 = a wait ran out."""
+    lib = _load()
+    return int(lib.bdh_sim_flag_barrier(ctypes.c_int(world), ctypes.c_int(ctas), ctypes.c_int(calls),
+                                        ctypes.c_uint32(first_epoch & 0xFFFFFFFF), ctypes.c_uint64(seed),
+                                        ctypes.c_int64(spin_limit)))

@@ -210,3 +210,24 @@ def test_char_vocab_native_encode_matches_python():
     import pytest
     with pytest.raises(KeyError):
         strict.encode_array("abd")
+
+
+def test_profiling_hooks_are_noops_without_cuda_and_metrics_fields(tmp_path):
+    import json
+    import torch
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.utils import profiling as prof
+    prof.enable(nvtx=True, timers=True)
+    try:
+        m = BDH(BDHConfig(n_layer=1, n_embd=32, n_head=2, n_latent_per_head=16, vocab_size=64, dropout=0.0))
+        tr = Trainer(m, lr=1e-3)
+        tr.track_grad_norm = m.measure_sparsity = True
+        tok = torch.randint(0, 64, (2, 17))
+        tr.train_step(tok[:, :-1], tok[:, 1:])
+        assert float(tr.last_grad_norm) > 0
+        assert 0.0 < float(m.last_sparsity["xy"]) <= float(m.last_sparsity["x"]) <= 1.0
+        if not torch.cuda.is_available():
+            assert prof.report() == {}
+    finally:
+        prof.enable(nvtx=False, timers=False)

@@ -129,3 +129,23 @@ def test_dropout_runs_on_kernels_and_matches_its_mask():
     assert e1.item() == e2.item()
     keep = G.dropout_keep_mask(99, 1, 64, 130, 0.2, "cuda")
     assert keep.shape == (64, 130) and abs(keep.float().mean().item() - 0.8) < 0.03
+
+
+def test_phase_timers_cover_the_step():
+    """CUDA-event phase timers: forward + backward + optimizer account for the step they are nested in."""
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.utils import profiling as prof
+    m = _model("rope")
+    tr = Trainer(m, lr=1e-3)
+    tok = torch.randint(0, 256, (2, 129), device="cuda")
+    tr.train_step(tok[:, :-1], tok[:, 1:])
+    prof.enable(timers=True)
+    try:
+        for _ in range(2):
+            tr.train_step(tok[:, :-1], tok[:, 1:])
+        rep = prof.report()
+    finally:
+        prof.enable(timers=False)
+    assert rep["step"]["calls"] == 2 and rep["layer.forward"]["calls"] == 2 * m.config.n_layer
+    inner = rep["forward"]["ms"] + rep["backward"]["ms"] + rep["optimizer"]["ms"] + rep["grad_reduce"]["ms"]
+    assert 0.5 * rep["step"]["ms"] < inner <= rep["step"]["ms"] * 1.05

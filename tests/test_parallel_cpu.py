@@ -79,3 +79,15 @@ strategy = "{strategy}"
     r = subprocess.run(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"],
                        capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
     assert r.returncode == 0 and "step 4" in r.stdout and "[valid       6]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("world,ctas", [(2, 4), (4, 3), (8, 2)])
+def test_flag_barrier_protocol_simulation(world, ctas):
+    """The arithmetic the collectives kernels use for their cross-rank barrier (slot layout, epoch
+    values, wrap-safe comparison), run by real threads with randomised interleavings: no stale or
+    early reads, no deadlock - also across the sign bit and the wrap of the 32-bit counter."""
+    from burn_dragon_b200.utils import hostlib
+    assert hostlib.available()
+    for first in (0, 2 ** 30 - 3, 2 ** 31 - 3):        # 2*epoch+phase crosses 2^31 and 2^32
+        for seed in range(3):
+            assert hostlib.simulate_flag_barrier(world, ctas, 40, first, seed) == 0, (first, seed)
