@@ -39,6 +39,8 @@ class _ShardedOptimizerFacade:
     def load_logical_state_dict(self, sd: Dict) -> None:
         o = self.owner
         o.step_count = int(sd["step"])
+        if o.sharded is not None:
+            o.sharded.step_count = o.step_count      # the fused kernel's bias correction counts steps itself
         o.m.copy_(sd["m"][o.lo:o.hi].to(o.m.device))
         o.v.copy_(sd["v"][o.lo:o.hi].to(o.v.device))
 
