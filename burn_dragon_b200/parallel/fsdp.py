@@ -32,17 +32,26 @@ class _ShardedOptimizerFacade:
         return self.owner.step_count
 
     def logical_state_dict(self) -> Dict:
-        o = self.owner
-        return dict(step=o.step_count, m=o._gather(o.m), v=o._gather(o.v), names=o.flat.names,
-                    offsets=o.flat.offsets, numel=o.flat.numel)
+        """Collective: every rank calls it. One full-size tensor per parameter and moment - the record a
+        single-device run writes - so the run can resume under any strategy or group size."""
+        o, f = self.owner, self.owner.flat
+        out = dict(step=o.step_count, m={}, v={})
+        for key, shard in (("m", o.m), ("v", o.v)):
+            full = o._gather(shard)
+            for i, n in enumerate(f.names):
+                out[key][n] = f.view(full, i).detach().cpu().clone()
+        return out
 
     def load_logical_state_dict(self, sd: Dict) -> None:
-        o = self.owner
+        o, f = self.owner, self.owner.flat
         o.step_count = int(sd["step"])
         if o.sharded is not None:
             o.sharded.step_count = o.step_count      # the fused kernel's bias correction counts steps itself
-        o.m.copy_(sd["m"][o.lo:o.hi].to(o.m.device))
-        o.v.copy_(sd["v"][o.lo:o.hi].to(o.v.device))
+        for key, shard in (("m", o.m), ("v", o.v)):
+            full = torch.zeros(o.numel, dtype=torch.float32, device=shard.device)
+            for i, n in enumerate(f.names):
+                f.view(full, i).copy_(sd[key][n].to(shard.device))
+            shard.copy_(full[o.lo:o.hi])
 
 
 class FSDP:

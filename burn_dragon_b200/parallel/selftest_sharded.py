@@ -28,7 +28,7 @@ def case_fsdp(dev):
     data = torch.randint(0, 256, (world * B, T + 1), generator=g).to(dev)
     mine = data[rank * B:(rank + 1) * B]
     notes = []
-    for fused in ((True, "mc_red", "allreduce", False) if dev.type == "cuda" else (False,)):
+    for fused in ((True, False) if dev.type == "cuda" else (False,)):
         m = _bdh(dev)
         w = FSDP(m, lr=1e-2, fused=fused)
         if fused:
@@ -44,8 +44,14 @@ def case_fsdp(dev):
         for k, v in one.state_dict().items():
             assert _rel(sd[k], v.cpu()) < tol, (fused, k, _rel(sd[k], v.cpu()))
         osd = w.optimizer.logical_state_dict()
-        assert osd["m"].numel() == w.numel and osd["step"] == 3
+        # one full-size moment per parameter, equal to the unsharded optimizer's
+        assert osd["step"] == 3 and set(osd["m"]) == {n for n, _ in one.named_parameters()}
+        f1 = tr1.opt.flat
+        for i, n in enumerate(f1.names):
+            assert _rel(osd["m"][n], f1.view(tr1.opt.m, i).cpu()) < 10 * tol, (fused, n)
+        before = w.m.clone()
         w.optimizer.load_logical_state_dict(osd)
+        assert torch.equal(before, w.m)
         notes.append(f"fused={w.fused}")
     return " ".join(notes)
 

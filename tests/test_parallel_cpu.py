@@ -79,6 +79,10 @@ strategy = "{strategy}"
     r = subprocess.run(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"],
                        capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
     assert r.returncode == 0 and "step 4" in r.stdout and "[valid       6]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    # the checkpoint is layout-free: the same run continues as a single process
+    r = subprocess.run([sys.executable] + tail + ["--resume", "latest", "--max-iters", "8"], capture_output=True,
+                       text=True, timeout=300, env=e, cwd=ROOT)
+    assert r.returncode == 0 and "step 6" in r.stdout and "[valid       8]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
 @pytest.mark.parametrize("world,ctas", [(2, 4), (4, 3), (8, 2)])
