@@ -105,8 +105,17 @@ def cmd_train(args) -> int:
 
     run_root = Path(args.runs)
     start_epoch = 0
-    if args.resume:
-        run_dir = CK.resolve_run_dir(None if args.resume == "latest" else args.resume, run_root)
+    resume = args.resume
+    if resume == "auto":
+        # continue the newest run if it has a checkpoint, else start a new one (what a launcher that
+        # restarts failed groups needs: the same command line works for the first start and every restart)
+        try:
+            CK.resolve_checkpoint(str(CK.resolve_run_dir(None, run_root)))
+            resume = "latest"
+        except (FileNotFoundError, ValueError):
+            resume = None
+    if resume:
+        run_dir = CK.resolve_run_dir(None if resume == "latest" else resume, run_root)
         run_name = run_dir.name
         mp, sp, start_epoch = CK.resolve_checkpoint(str(run_dir))
         CK.load_checkpoint(model, mp, sp, trainer, train_loader)
@@ -115,7 +124,11 @@ def cmd_train(args) -> int:
         if rank == 0:
             print(f"resumed {run_name} at epoch {start_epoch}, step {trainer.step_index}", flush=True)
     else:
-        run_dir, run_name = CK.create_run_dir(run_root)
+        # one run directory for the whole job: rank 0 names it
+        box = [CK.create_run_dir(run_root) if rank == 0 else None]
+        if world > 1:
+            torch.distributed.broadcast_object_list(box, src=0)
+        run_dir, run_name = Path(box[0][0]), box[0][1]
     if rank == 0:
         run_dir.mkdir(parents=True, exist_ok=True)
         CK.write_latest_run(run_root, run_name)
@@ -127,11 +140,27 @@ def cmd_train(args) -> int:
 
     tokens_per_step = cfg.training.batch_size * cfg.training.block_size * (1 if strategy == "tp" else world)
     epoch = start_epoch
+    every = cfg.training.checkpoint_every
+    from .parallel.watchdog import HostFaultInjector
+    faults = HostFaultInjector(rank)
+
+    ckpt_index = start_epoch       # number of the newest checkpoint of this run (model-<n>.bin)
+
+    def checkpoint() -> None:
+        nonlocal ckpt_index
+        ckpt_index += 1
+        logical, opt_state = CK.gather_for_checkpoint(trainer, wrapper)      # collective under FSDP / TP
+        if rank == 0:
+            CK.save_checkpoint(run_dir, ckpt_index, model, trainer, train_loader, logical_state=logical,
+                               optimizer_state=opt_state)
+        dist_utils.barrier()
+
     while trainer.step_index < total_steps:
         epoch += 1
         model.train()
         before = trainer.step_index
         for batch in train_loader:
+            faults.before_step(trainer.step_index + 1)
             t0 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
             t1 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
             wall = time.perf_counter()
@@ -159,15 +188,13 @@ def cmd_train(args) -> int:
                     extra.update(x_active=float(sp["x"]), xy_active=float(sp["xy"]))
                 log.log("train", step, loss=float(loss), lr=lr, step_ms=ms, tokens_per_s=tokens_per_step / ms * 1e3,
                         **extra)
+            if every and step % every == 0 and step < total_steps:
+                checkpoint()           # periodic checkpoint inside an epoch (`training.checkpoint_every` steps)
         if trainer.step_index == before:
             break           # the loader's global step cap is exhausted
         vloss = [float(trainer.eval_step(b.inputs, b.targets)) for b in valid_loader]
         log.log("valid", trainer.step_index, loss=sum(vloss) / len(vloss), epoch=epoch)
-        logical, opt_state = CK.gather_for_checkpoint(trainer, wrapper)      # collective under FSDP / TP
-        if rank == 0:
-            CK.save_checkpoint(run_dir, epoch, model, trainer, train_loader, logical_state=logical,
-                               optimizer_state=opt_state)
-        dist_utils.barrier()
+        checkpoint()
         if trainer.step_index >= total_steps:
             break
     if rank == 0:
@@ -316,7 +343,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         common(p)
         p.add_argument("--synthetic", action="store_true", help="train on uniform random bytes")
         p.add_argument("--max-iters", type=int, default=None)
-        p.add_argument("--resume", default=None, help="run name / path, or `latest`")
+        p.add_argument("--resume", default=None, help="run name / path, `latest`, or `auto` (latest if it has a checkpoint, else a new run)")
         p.set_defaults(fn=cmd_train)
     p = sub.add_parser("infer")
     common(p)
@@ -354,7 +381,21 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--new-tokens", type=int, default=2048)
     p.set_defaults(fn=cmd_bench)
     args = ap.parse_args(argv)
-    return args.fn(args)
+    try:
+        return args.fn(args)
+    except BaseException as e:  # noqa: BLE001
+        # A rank that fails inside a multi-rank job must die at once: the normal interpreter exit would
+        # first tear the process group down, which waits for peers that are themselves blocked in a
+        # collective waiting for this rank - and the launcher would never learn of the failure.
+        import torch.distributed as dist
+        if isinstance(e, SystemExit) or not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+            raise
+        import os
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        sys.stdout.flush()
+        os._exit(1)
 
 
 if __name__ == "__main__":

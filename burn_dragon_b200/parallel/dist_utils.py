@@ -38,7 +38,18 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
         torch.cuda.set_device(env_local_rank())
         if backend == "nccl":
             kw["device_id"] = torch.device("cuda", env_local_rank())
-    dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    timeout = datetime.timedelta(seconds=timeout_s)
+    restart = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") or 0)
+    if restart > 0:
+        # A launcher that restarts a failed group keeps its key-value store: the addresses the previous
+        # incarnation's ranks published are still in it under the same keys, and a new rank would try
+        # to connect to a process that no longer exists. Give every incarnation its own key space.
+        store, rank_, world_ = next(dist.rendezvous("env://", timeout=timeout))
+        store.set_timeout(timeout)
+        dist.init_process_group(backend=backend, store=dist.PrefixStore(f"restart{restart}", store), rank=rank_,
+                                world_size=world_, timeout=timeout, **kw)
+    else:
+        dist.init_process_group(backend=backend, timeout=timeout, **kw)
     return True
 
 

@@ -10,13 +10,19 @@ stop flag for the visualiser thread, src/bin/infer.rs:356-397). Here:
 * `device_status()` - turns a non-zero kernel status word (a bounded in-kernel wait that gave up)
   into a Python exception, leaving the CUDA context usable.
 
+* `HostFaultInjector` - test hook that makes one rank raise between two steps (no kernel or
+  collective of its own in flight), once per marker file, so that restart-from-checkpoint can be
+  exercised under a launcher that restarts failed groups.
+
 Nothing here makes a GPU fault, trap or hang; failures are injected on the host (a rank that
 raises, exits or stops publishing).
 """
 from __future__ import annotations
 
+import os
 import threading
 import time
+from pathlib import Path
 from typing import List, Optional
 
 import torch.distributed as dist
@@ -105,3 +111,37 @@ def device_status(raise_on_error: bool = True) -> int:
         native.clear_status()
         raise KernelTimeout(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
     return code
+
+
+class InjectedFault(RuntimeError):
+    pass
+
+
+class HostFaultInjector:
+    """`BDH_INJECT_FAULT="rank=1,step=3,once=/path/to/marker"`: rank 1 raises `InjectedFault` when it
+    is about to run step 3 - unless the marker file exists; the file is created first, so a restarted
+    job passes the same point. Unset (the default) the injector does nothing."""
+
+    def __init__(self, rank: int, spec: Optional[str] = None):
+        spec = os.environ.get("BDH_INJECT_FAULT", "") if spec is None else spec
+        self.rank, self.fail_rank, self.fail_step, self.marker = rank, None, None, None
+        for part in filter(None, (p.strip() for p in spec.split(","))):
+            k, _, v = part.partition("=")
+            if k == "rank":
+                self.fail_rank = int(v)
+            elif k == "step":
+                self.fail_step = int(v)
+            elif k == "once":
+                self.marker = Path(v)
+            else:
+                raise ValueError(f"BDH_INJECT_FAULT: unknown key {k!r}")
+
+    def before_step(self, step: int) -> None:
+        if self.fail_rank != self.rank or self.fail_step != step:
+            return
+        if self.marker is not None:
+            if self.marker.exists():
+                return
+            self.marker.parent.mkdir(parents=True, exist_ok=True)
+            self.marker.write_text(f"rank {self.rank} failed before step {step}\n")
+        raise InjectedFault(f"injected host fault on rank {self.rank} before step {step}")

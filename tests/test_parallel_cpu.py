@@ -8,6 +8,21 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def run_job(cmd, env, timeout):
+    """Run a launcher command in its own session; if it does not finish in time, end that session's
+    process group (the launcher and the ranks it started - nothing else) and fail."""
+    import signal
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=ROOT,
+                            start_new_session=True)
+    try:
+        so, se = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        so, se = proc.communicate()
+        raise AssertionError(f"job did not finish in {timeout} s:\n" + (so + se)[-4000:])
+    return subprocess.CompletedProcess(cmd, proc.returncode, so, se)
+
+
 def run_ranks(case, n=2, cpu=True, env=None, timeout=300):
     port = 29600 + (os.getpid() + hash(case)) % 300
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
@@ -15,7 +30,7 @@ def run_ranks(case, n=2, cpu=True, env=None, timeout=300):
            "--case", case] + (["--cpu"] if cpu else [])
     e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
     e.update(env or {})
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e, cwd=ROOT)
+    r = run_job(cmd, e, timeout)
     assert r.returncode == 0 and f"PASS {case}" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
     return r.stdout
 
@@ -73,15 +88,12 @@ strategy = "{strategy}"
     tail = ["-m", "burn_dragon_b200", "train", "-c", str(cfg), "--synthetic", "--device", "cpu", "--runs", str(runs)]
     e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
     port = 29300 + (os.getpid() + len(strategy)) % 200
-    r = subprocess.run(base + ["--master-port", str(port)] + tail + ["--max-iters", "4"], capture_output=True,
-                       text=True, timeout=300, env=e, cwd=ROOT)
+    r = run_job(base + ["--master-port", str(port)] + tail + ["--max-iters", "4"], e, 300)
     assert r.returncode == 0 and "[valid       4]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
-    r = subprocess.run(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"],
-                       capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
+    r = run_job(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"], e, 300)
     assert r.returncode == 0 and "step 4" in r.stdout and "[valid       6]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
     # the checkpoint is layout-free: the same run continues as a single process
-    r = subprocess.run([sys.executable] + tail + ["--resume", "latest", "--max-iters", "8"], capture_output=True,
-                       text=True, timeout=300, env=e, cwd=ROOT)
+    r = run_job([sys.executable] + tail + ["--resume", "latest", "--max-iters", "8"], e, 300)
     assert r.returncode == 0 and "step 6" in r.stdout and "[valid       8]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
@@ -95,3 +107,43 @@ def test_flag_barrier_protocol_simulation(world, ctas):
     for first in (0, 2 ** 30 - 3, 2 ** 31 - 3):        # 2*epoch+phase crosses 2^31 and 2^32
         for seed in range(3):
             assert hostlib.simulate_flag_barrier(world, ctas, 40, first, seed) == 0, (first, seed)
+
+
+def test_restart_from_checkpoint_after_injected_rank_failure(tmp_path):
+    """Failure on the host, recovery from the last checkpoint: rank 1 raises before step 4 (once); the
+    launcher restarts the group with the same command line; `--resume auto` continues from the
+    checkpoint written at step 2 and the run completes."""
+    cfg = tmp_path / "par.toml"
+    cfg.write_text("""
+[training]
+batch_size = 4
+block_size = 32
+log_frequency = 1
+checkpoint_every = 2
+
+[model]
+n_layer = 2
+n_embd = 64
+n_head = 2
+mlp_internal_dim_multiplier = 4
+dropout = 0.0
+
+[parallel]
+strategy = "fsdp"
+""")
+    runs = tmp_path / "runs"
+    port = 29500 + os.getpid() % 90
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--max-restarts=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "burn_dragon_b200", "train", "-c", str(cfg),
+           "--synthetic", "--device", "cpu", "--runs", str(runs), "--max-iters", "6", "--resume", "auto"]
+    e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2",
+             BDH_INJECT_FAULT=f"rank=1,step=4,once={tmp_path / 'failed_once'}")
+    r = run_job(cmd, e, 300)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-4000:]
+    assert (tmp_path / "failed_once").exists() and "injected host fault on rank 1 before step 4" in out
+    assert "resumed" in r.stdout and "step 2" in r.stdout and "[valid       6]" in r.stdout, out[-4000:]
+    run_dirs = [p for p in runs.iterdir() if p.is_dir()]
+    assert len(run_dirs) == 1                      # the restart continued the same run
+    names = sorted(p.name for p in (run_dirs[0] / "checkpoint").glob("model-*.bin"))
+    assert names == ["model-1.bin", "model-2.bin", "model-3.bin"], names
