@@ -141,8 +141,15 @@ def cmd_train(args) -> int:
     tokens_per_step = cfg.training.batch_size * cfg.training.block_size * (1 if strategy == "tp" else world)
     epoch = start_epoch
     every = cfg.training.checkpoint_every
-    from .parallel.watchdog import HostFaultInjector
+    from .parallel.watchdog import Heartbeat, HostFaultInjector
     faults = HostFaultInjector(rank)
+    # every rank publishes a heartbeat; a peer that left or went silent is noticed on the host before
+    # this rank launches a step whose collectives would wait for it
+    hb = None
+    if world > 1 and cfg.parallel.heartbeat_timeout_s > 0:
+        hb = Heartbeat(rank, world, interval_s=min(1.0, cfg.parallel.heartbeat_timeout_s / 4),
+                       timeout_s=cfg.parallel.heartbeat_timeout_s)
+        hb.start()
 
     ckpt_index = start_epoch       # number of the newest checkpoint of this run (model-<n>.bin)
 
@@ -161,6 +168,8 @@ def cmd_train(args) -> int:
         before = trainer.step_index
         for batch in train_loader:
             faults.before_step(trainer.step_index + 1)
+            if hb is not None:
+                hb.check()
             t0 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
             t1 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
             wall = time.perf_counter()
@@ -197,6 +206,8 @@ def cmd_train(args) -> int:
         checkpoint()
         if trainer.step_index >= total_steps:
             break
+    if hb is not None:
+        hb.stop(leave=False)
     if rank == 0:
         print(log.summary())
         mc = getattr(model, "config", None)

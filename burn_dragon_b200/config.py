@@ -195,6 +195,7 @@ class ParallelConfig:
     tp: int = 1
     fused_collectives: bool = True  # in-kernel NVLink paths; False = NCCL-only baseline
     bucket_mb: int = 64
+    heartbeat_timeout_s: float = 60.0   # a peer silent for this long is reported before the next step; 0 = off
 
 
 @dataclass
