@@ -1,4 +1,4 @@
-"""Command line entry points: `python -m burn_dragon_b200 <train|infer|bench|quantize|build-vocab|ckpt>`.
+"""Command line entry points: `python -m burn_dragon_b200 <train|infer|serve|bench|quantize|build-vocab|ckpt>`.
 
 The flags mirror the reference's binaries (src/bin/train.rs:52-81, src/bin/infer.rs:631-687,
 src/bin/quantize.rs): `-c/--config` is repeatable and every file is merged over `config/base.toml`;
@@ -329,6 +329,21 @@ def cmd_ckpt(args) -> int:
     return 0
 
 
+def cmd_serve(args) -> int:
+    """Serve a trained run over HTTP (engine/server.py)."""
+    from .engine import checkpoint as CK
+    from .engine import server, session
+    model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    ckpt_dir = model_path.parent
+    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
+    sess = session.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
+                              run_cfg.read_text() if run_cfg.exists() else None, args.device)
+    print(f"serving {model_path} (checkpoint {epoch}) on http://{args.host}:{args.port} [{sess.device}]", flush=True)
+    server.serve(sess, args.host, args.port)
+    return 0
+
+
 def cmd_bench(args) -> int:
     from .engine import bench as B
     res = B.run(args.what, args.preset, steps=args.steps, warmup=args.warmup, streams=args.streams,
@@ -382,6 +397,15 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("ckpt")
     p.add_argument("file")
     p.set_defaults(fn=cmd_ckpt)
+    p = sub.add_parser("serve", help="HTTP front end for streaming generation from a trained run")
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--epoch", type=int, default=None)
+    p.add_argument("--runs", default="runs")
+    p.add_argument("--device", default=None)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080)
+    p.set_defaults(fn=cmd_serve)
+
     p = sub.add_parser("bench")
     p.add_argument("what", choices=["train", "decode", "reference-shapes"])
     p.add_argument("--preset", default="b200_base")

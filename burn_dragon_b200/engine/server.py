@@ -1,0 +1,119 @@
+"""A small HTTP front end for inference sessions: the headless counterpart of the reference's web page
+(www/index.html loads the checkpoint and pumps a few tokens per animation frame; here a client pumps
+chunks over HTTP). Standard library only.
+
+    python -m burn_dragon_b200 serve --checkpoint runs/latest --port 8080
+
+    GET  /health                          -> {"status": "ok", "model": {...}, "device": "cuda:0"}
+    POST /generate  {"prompt": "ROMEO:", "max_tokens": 200, "temperature": 0.8, "top_k": 40,
+                     "greedy": false, "seed": 1, "stream": true, "chunk_tokens": 4}
+         stream=false -> {"text": "...", "tokens": 200}
+         stream=true  -> application/x-ndjson, one {"text": "..."} line per chunk, then {"done": true, "tokens": n}
+    "prompt" may be a list of equally long strings: the streams are decoded together (one recurrent
+    state each) and "text" becomes a list.
+
+Requests are served one at a time (a lock around the session): the GPU decode step is already
+batched over the streams of one request.
+"""
+from __future__ import annotations
+
+import json
+import threading
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Optional
+
+from .session import InferenceSession
+
+MAX_BODY = 1 << 20
+
+
+def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
+    lock = threading.Lock()
+
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, fmt, *args):  # quiet by default; errors still reach the client
+            pass
+
+        def _json(self, code: int, obj) -> None:
+            body = (json.dumps(obj) + "\n").encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path != "/health":
+                return self._json(404, {"error": "unknown path"})
+            c = session.model.config
+            self._json(200, {"status": "ok", "device": str(session.device), "block_size": session.block_size,
+                             "model": {"n_layer": c.n_layer, "n_embd": c.n_embd, "n_head": c.n_head,
+                                       "n_latent_per_head": c.latent_per_head, "vocab_size": c.vocab_size,
+                                       "rotary_embedding": c.rotary_embedding}})
+
+        def _chunk(self, data: bytes) -> None:
+            self.wfile.write(f"{len(data):x}\r\n".encode() + data + b"\r\n")
+            self.wfile.flush()
+
+        def do_POST(self):
+            if self.path != "/generate":
+                return self._json(404, {"error": "unknown path"})
+            try:
+                n = int(self.headers.get("Content-Length", "0"))
+                if n <= 0 or n > MAX_BODY:
+                    raise ValueError("missing or oversized body")
+                req = json.loads(self.rfile.read(n))
+                prompt = req["prompt"]
+                if not (isinstance(prompt, str) or (isinstance(prompt, list) and all(isinstance(p, str) for p in prompt))):
+                    raise ValueError("prompt must be a string or a list of strings")
+                kw = dict(max_tokens=int(req.get("max_tokens", 128)), temperature=float(req.get("temperature", 1.0)),
+                          top_k=(int(req["top_k"]) if req.get("top_k") is not None else None),
+                          greedy=bool(req.get("greedy", False)),
+                          seed=(int(req["seed"]) if req.get("seed") is not None else None),
+                          context_window=(int(req["context_window"]) if req.get("context_window") else None))
+                chunk_tokens = max(1, int(req.get("chunk_tokens", 4)))
+                stream = bool(req.get("stream", False))
+            except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+                return self._json(400, {"error": str(e)})
+            many = isinstance(prompt, list)
+            with lock:
+                try:
+                    session.start_stream(prompt, **kw)
+                except (ValueError, KeyError) as e:
+                    return self._json(400, {"error": str(e)})
+                if not stream:
+                    text = ["" for _ in prompt] if many else ""
+                    while not session.done:
+                        piece = session.next_chunk(chunk_tokens)
+                        text = [a + b for a, b in zip(text, piece)] if many else text + piece
+                    return self._json(200, {"text": text, "tokens": session.generated})
+                self.send_response(200)
+                self.send_header("Content-Type", "application/x-ndjson")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+                try:
+                    while not session.done:
+                        piece = session.next_chunk(chunk_tokens)
+                        if piece if not many else any(piece):
+                            self._chunk((json.dumps({"text": piece}) + "\n").encode())
+                    self._chunk((json.dumps({"done": True, "tokens": session.generated}) + "\n").encode())
+                    self.wfile.write(b"0\r\n\r\n")
+                except (BrokenPipeError, ConnectionResetError):
+                    pass        # the client went away: drop the stream, keep serving
+
+    return ThreadingHTTPServer((host, port), Handler)
+
+
+def serve(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080,
+          ready: Optional[threading.Event] = None) -> None:
+    srv = make_server(session, host, port)
+    if ready is not None:
+        ready.set()
+    try:
+        srv.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        srv.server_close()

@@ -90,3 +90,46 @@ def test_shipped_checkpoint_streams_text():
     while not sess.done:
         text += sess.next_chunk()
     assert len(text) > 0 and all(ch in sess.tokenizer.ch2id or ch == "?" for ch in text)
+
+
+def test_http_server_generate_and_stream():
+    """The HTTP front end returns what the session API returns: whole text, and the same text in chunks."""
+    import threading
+    import urllib.request
+    from burn_dragon_b200.engine import server as SV
+    m, vocab, blob, vjson, cjson = _artefacts("alibi")
+    sess = S.load_model(blob, vjson, cjson, device="cpu")
+    srv = SV.make_server(sess, "127.0.0.1", 0)
+    port = srv.server_address[1]
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    try:
+        base = f"http://127.0.0.1:{port}"
+        health = json.loads(urllib.request.urlopen(base + "/health", timeout=30).read())
+        assert health["status"] == "ok" and health["model"]["n_layer"] == 2
+
+        def post(body):
+            req = urllib.request.Request(base + "/generate", data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json"})
+            return urllib.request.urlopen(req, timeout=60)
+
+        whole = json.loads(post(dict(prompt="hello", max_tokens=10, greedy=True)).read())
+        lines = [json.loads(l) for l in post(dict(prompt="hello", max_tokens=10, greedy=True, stream=True,
+                                                  chunk_tokens=3)).read().decode().splitlines() if l.strip()]
+        assert lines[-1]["done"] is True and lines[-1]["tokens"] == whole["tokens"] <= 10
+        assert "".join(l["text"] for l in lines[:-1]) == whole["text"]
+        ref = S.load_model(blob, vjson, cjson, device="cpu")
+        ref.start_stream("hello", max_tokens=10, greedy=True)
+        text = ""
+        while not ref.done:
+            text += ref.next_chunk()
+        assert whole["text"] == text
+        two = json.loads(post(dict(prompt=["hello", "world"], max_tokens=4, greedy=True)).read())
+        assert isinstance(two["text"], list) and len(two["text"]) == 2
+        import urllib.error
+        with pytest.raises(urllib.error.HTTPError) as err:
+            post(dict(prompt=["hello", "hi"], max_tokens=4))
+        assert err.value.code == 400
+    finally:
+        srv.shutdown()
+        srv.server_close()
