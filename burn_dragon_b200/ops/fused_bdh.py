@@ -183,7 +183,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
                    c_off=(M, T, 0, 0), flags=G.F_ACCUM | carry_flags, slopes=d.slopes, out0=a)
     else:
         # neuron-sharded: this rank's scores cover its slice of the neurons, so S V is a partial sum;
-        # the GEMM epilogue adds it into every rank's replica through the switch
+        # the GEMM's epilogue is the cross-rank reduction (parallel/tp.py: TPComm)
         buf = comm.begin("a", H * M, D, launches=1 if rho_in is None else 2)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
                c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, **buf.kw)
