@@ -12,7 +12,7 @@ from __future__ import annotations
 import codecs
 import sys
 from dataclasses import dataclass
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import Callable, List, Optional
 
 import torch
 

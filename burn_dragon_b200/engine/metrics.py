@@ -10,7 +10,7 @@ import json
 import math
 import time
 from pathlib import Path
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 
 class MetricsLogger:

@@ -14,7 +14,7 @@ learning rate, `num_iters` to the total number of steps.
 from __future__ import annotations
 
 import math
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, List, Optional
 
 import torch
 

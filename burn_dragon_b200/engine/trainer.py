@@ -7,15 +7,14 @@ reference's TrainStep (src/bin/train.rs:134-146) plus what burn-train's Learner 
 """
 from __future__ import annotations
 
-import time
-from typing import Callable, Dict, Optional
+from typing import Optional
 
 import torch
 
 from ..parallel import dist_utils
 from ..parallel.ddp import DataParallel
 from ..utils import profiling as prof
-from .optim import FlatAdamW, FlatParams, LRSchedule
+from .optim import FlatAdamW, LRSchedule
 
 
 class Trainer:

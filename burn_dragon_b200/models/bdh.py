@@ -17,7 +17,7 @@ GEMMs consume directly. `engine.burn_record` converts to and from the reference'
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, List, Optional, Tuple
+from typing import Callable, List, Optional
 
 import torch
 import torch.nn as nn

@@ -20,7 +20,7 @@ from typing import Optional
 import torch
 
 from ..ops import native
-from ..ops.block_sparse import BlockPattern1d, BlockPattern2d, BlockSparseConfig
+from ..ops.block_sparse import BlockPattern1d
 from .bdh import BDH, BDHConfig, build_model_config
 
 

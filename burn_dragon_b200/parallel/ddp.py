@@ -13,7 +13,6 @@ Two reductions are available:
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist
