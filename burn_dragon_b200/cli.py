@@ -95,10 +95,15 @@ def cmd_train(args) -> int:
     if strategy in ("fsdp", "tp"):
         from .parallel import build_wrapper
         wrapper = build_wrapper(model, cfg, strategy)
+    accum = max(1, cfg.training.grad_accum_steps)
+    if wrapper is not None and accum > 1:
+        if rank == 0:
+            print("grad_accum_steps is ignored under the FSDP / TP wrappers", flush=True)
+        accum = 1
     trainer = Trainer(model, cfg.optimizer.learning_rate, cfg.optimizer.weight_decay, cfg.optimizer.beta1,
                       cfg.optimizer.beta2, cfg.optimizer.eps, sched, strategy, cfg.parallel.fused_collectives,
-                      cfg.training.fast_train, cfg.training.grad_clip, wrapper)
-    train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe, total_steps)
+                      cfg.training.fast_train, cfg.training.grad_clip, wrapper, accum)
+    train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum)   # batches = micro-batches
     val_spe = ds.steps_per_epoch(D.VAL)
     valid_steps = max(1, min(max(1, total_steps // max(1, cfg.training.log_frequency)), val_spe))
     valid_loader = D.RandomDataLoader(ds, D.VAL, dev, valid_steps, None)
@@ -138,7 +143,7 @@ def cmd_train(args) -> int:
             tok.save(run_dir / "vocab.json")
     log = MetricsLogger(run_dir if rank == 0 else None, cfg.training.log_frequency, rank)
 
-    tokens_per_step = cfg.training.batch_size * cfg.training.block_size * (1 if strategy == "tp" else world)
+    tokens_per_step = cfg.training.batch_size * cfg.training.block_size * (1 if strategy == "tp" else world) * accum
     epoch = start_epoch
     every = cfg.training.checkpoint_every
     from .parallel.watchdog import Heartbeat, HostFaultInjector
@@ -170,18 +175,22 @@ def cmd_train(args) -> int:
             faults.before_step(trainer.step_index + 1)
             if hb is not None:
                 hb.check()
-            t0 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
-            t1 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
-            wall = time.perf_counter()
-            if t0 is not None:
-                t0.record()
+            if trainer._micro == 0:        # the clock of a step starts at its first micro-batch
+                t0 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
+                t1 = torch.cuda.Event(enable_timing=True) if dev.type == "cuda" else None
+                wall = time.perf_counter()
+                if t0 is not None:
+                    t0.record()
             lr = trainer.current_lr()
             # the steps that get logged also measure gradient norm and activation sparsity
             logged = (trainer.step_index + 1) % cfg.training.log_frequency == 0 or trainer.step_index + 1 == total_steps
             probe = getattr(wrapper, "eval_model", None) or model
             trainer.track_grad_norm = probe.measure_sparsity = logged
+            prev = trainer.step_index
             loss = trainer.train_step(batch.inputs, batch.targets)
             step = trainer.step_index
+            if step == prev:
+                continue               # a micro-batch of an accumulated step: no update yet
             if logged:
                 if t1 is not None:
                     t1.record()

@@ -120,6 +120,7 @@ class TrainingHyperparameters:
     # additions
     seed: int = 1337
     grad_clip: Optional[float] = None
+    grad_accum_steps: int = 1                # micro-batches of batch_size sequences per optimizer step
     checkpoint_every: Optional[int] = None   # steps; None = once per epoch like the reference
     recompute: Any = False                   # layers that re-run their forward in backward instead of saving
                                              # activations: false / true (none / all), a count, or "auto"

@@ -21,13 +21,19 @@ class Trainer:
     def __init__(self, model: torch.nn.Module, lr: float = 1e-3, weight_decay: float = 0.1, beta1: float = 0.9,
                  beta2: float = 0.999, eps: float = 1e-5, schedule: Optional[LRSchedule] = None,
                  parallel: str = "single", fused_collectives: bool = True, fast_train: bool = False,
-                 grad_clip: Optional[float] = None, wrapper=None):
+                 grad_clip: Optional[float] = None, wrapper=None, grad_accum: int = 1):
         self.model = model
         self.fast_train = fast_train
         self.grad_clip = grad_clip
         self.schedule = schedule
         self.parallel = parallel
         self.step_index = 0
+        # micro-batches per optimizer step: gradients of `grad_accum` calls are summed in the flat
+        # gradient buffer, reduced across ranks once and applied with scale 1/grad_accum
+        self.grad_accum = max(1, int(grad_accum))
+        self._micro = 0
+        if wrapper is not None and self.grad_accum > 1:
+            raise ValueError("gradient accumulation is not available under the FSDP / TP wrappers")
         self.track_grad_norm = False      # set by the metrics logger on the steps it logs
         self.last_grad_norm = None
         self.wrapper = wrapper
@@ -60,13 +66,18 @@ class Trainer:
             self.step_index += 1
             return loss
         with prof.phase("step"):
-            self.opt.zero_grad()
+            if self._micro == 0:
+                self.opt.zero_grad()
             with prof.phase("forward"):
                 loss = self.loss_fn(tokens, targets)
             with prof.phase("backward"):
                 loss.backward()
+            self._micro += 1
+            if self._micro < self.grad_accum:
+                return loss.detach()           # more micro-batches to come: no reduction, no update
+            self._micro = 0
             with prof.phase("grad_reduce"):
-                scale = self.dp.reduce_gradients() if self.dp is not None else 1.0
+                scale = (self.dp.reduce_gradients() if self.dp is not None else 1.0) / self.grad_accum
             if self.grad_clip or self.track_grad_norm:
                 # norm of the averaged gradient, kept on the device (read it with `.item()` when logging)
                 self.last_grad_norm = self.opt.flat.grad.norm() * scale

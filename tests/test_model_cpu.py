@@ -98,3 +98,25 @@ def test_build_model_config_overrides():
     cfg = build_model_config(ModelOverrides(n_layer=3, n_embd=64, n_head=4, rotary_embedding="pope"), 128, 50)
     assert (cfg.n_layer, cfg.n_embd, cfg.latent_per_head, cfg.vocab_size, cfg.block_size) == (3, 64, 64, 50, 128)
     assert cfg.state_latent == 128
+
+
+def test_gradient_accumulation_equals_one_large_batch():
+    import torch
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+
+    def make():
+        torch.manual_seed(0)
+        return BDH(BDHConfig(n_layer=2, n_embd=32, n_head=2, n_latent_per_head=16, vocab_size=64, dropout=0.0))
+
+    tok = torch.randint(0, 64, (4, 17), generator=torch.Generator().manual_seed(1))
+    a, b = make(), make()
+    ta, tb = Trainer(a, lr=1e-2), Trainer(b, lr=1e-2, grad_accum=2)
+    for _ in range(2):
+        ta.train_step(tok[:, :-1], tok[:, 1:])
+        tb.train_step(tok[:2, :-1], tok[:2, 1:])
+        assert tb.step_index == ta.step_index - 1
+        tb.train_step(tok[2:, :-1], tok[2:, 1:])
+        assert tb.step_index == ta.step_index
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.allclose(p, q, rtol=1e-4, atol=1e-6), n
