@@ -95,3 +95,40 @@ def test_varint_roundtrip():
         b = BR.write_varint(v)
         got, pos = BR.read_varint(b, 0)
         assert got == v and pos == len(b)
+
+
+def test_varint_and_string_roundtrip_property():
+    """bincode varints and length-prefixed strings: decode(encode(x)) == x over the whole u64 range."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.integers(min_value=0, max_value=2 ** 64 - 1))
+    def ints(v):
+        enc = BR.write_varint(v)
+        got, pos = BR.read_varint(enc + b"\xff", 0)
+        assert got == v and pos == len(enc)
+        assert len(enc) == (1 if v < 251 else 3 if v < 2 ** 16 else 5 if v < 2 ** 32 else 9)
+
+    @settings(max_examples=100, deadline=None)
+    @given(st.text(max_size=40))
+    def strings(s):
+        enc = BR.write_string(s)
+        got, pos = BR.read_string(enc, 0)
+        assert got == s and pos == len(enc)
+
+    ints()
+    strings()
+
+
+def test_char_vocab_roundtrip_property():
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=100, deadline=None)
+    @given(st.text(alphabet=st.characters(blacklist_categories=("Cs",), min_codepoint=4), min_size=1, max_size=60))
+    def roundtrip(text):
+        v = CharVocab.fit([text], include_unknown=True)
+        ids = v.encode(text)
+        assert v.decode(ids) == text
+        assert v.encode_array(text).tolist() == ids
+
+    roundtrip()
