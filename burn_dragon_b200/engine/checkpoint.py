@@ -98,6 +98,10 @@ def resolve_checkpoint(spec: Optional[str], epoch: Optional[int] = None, run_roo
         return p, None, int(m.group(1)) if m else 0
     ckpt = p / "checkpoint" if (p / "checkpoint").is_dir() else p
     ep = epoch if epoch is not None else find_latest_epoch(ckpt)
+    if ep is None and (ckpt / "model.bin").exists():
+        # the layout of an exported model (model.bin + vocab.json + config.json side by side), as the
+        # reference ships for its web page (www/assets/model/<name>/)
+        return ckpt / "model.bin", None, 0
     if ep is None:
         raise FileNotFoundError(f"no checkpoints in {ckpt}")
     model = ckpt / f"model-{ep}.bin"

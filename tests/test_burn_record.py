@@ -132,3 +132,15 @@ def test_char_vocab_roundtrip_property():
         assert v.encode_array(text).tolist() == ids
 
     roundtrip()
+
+
+@needs_asset
+def test_infer_cli_runs_the_shipped_model_directory(capsys):
+    """`infer --checkpoint <exported model directory>` (model.bin + vocab.json + config.json side by side)."""
+    from burn_dragon_b200 import cli
+    rc = cli.main(["infer", "--checkpoint", str(ASSET), "--prompt", "ROMEO:", "--max-tokens", "24", "--greedy",
+                   "--device", "cpu"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "ROMEO:" in out
+    tail = out.split("ROMEO:", 1)[1]
+    assert len(tail.strip()) >= 10
