@@ -1,4 +1,4 @@
-"""Command line entry points: `python -m burn_dragon_b200 <train|infer|serve|bench|quantize|build-vocab|ckpt>`.
+"""Command line entry points: `python -m burn_dragon_b200 <train|infer|serve|export|bench|quantize|build-vocab|ckpt>`.
 
 The flags mirror the reference's binaries (src/bin/train.rs:52-81, src/bin/infer.rs:631-687,
 src/bin/quantize.rs): `-c/--config` is repeatable and every file is merged over `config/base.toml`;
@@ -269,7 +269,15 @@ def cmd_infer(args) -> int:
         g.context_strategy = C.ContextStrategyConfig(args.context_mode, args.context_window)
     # tokenizer: the run's vocab.json, else the dataset cache
     vocab = run_dir / "vocab.json"
-    if cfg.dataset.tokenizer.type == "char":
+    byte_vocab = None
+    if not vocab.exists() and model_path.suffix == ".bin":
+        # a run without a vocabulary file was trained on bytes: its embedding has 256 (or 259) rows
+        from .engine import burn_record as BR
+        V = BR.infer_dims(BR.load(model_path))["vocab_size"]
+        byte_vocab = V if V in (256, 259) else None
+    if byte_vocab is not None:
+        tok = T.ByteTokenizer(byte_vocab == 259)
+    elif cfg.dataset.tokenizer.type == "char":
         vp = vocab if vocab.exists() else T.storage_path(cfg.dataset.tokenizer, cfg.dataset.cache_dir)
         tok = T.CharVocab.load(vp)
     else:
@@ -335,6 +343,29 @@ def cmd_ckpt(args) -> int:
     for k, p in rec.params.items():
         print(f"  {k:<14} id={p.id} shape={tuple(p.data.shape)} dtype={p.data.dtype}")
     print("dims:", BR.infer_dims(rec))
+    return 0
+
+
+def cmd_export(args) -> int:
+    """Write a run's newest (or chosen) checkpoint as a self-contained model directory - model.bin,
+    vocab.json, config.json side by side - the layout the reference's web page fetches
+    (www/assets/model/<name>/, www/index.html:212-260) and that `infer` / `serve` accept."""
+    import shutil
+    from .engine import burn_record as BR
+    from .engine import checkpoint as CK
+    model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    ckpt_dir = model_path.parent
+    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    out = Path(args.output)
+    out.mkdir(parents=True, exist_ok=True)
+    if args.f16:
+        BR.quantize_file(model_path, out / "model.bin")
+    else:
+        shutil.copyfile(model_path, out / "model.bin")
+    for name in ("vocab.json", "config.json"):
+        if (run_dir / name).exists():
+            shutil.copyfile(run_dir / name, out / name)
+    print(f"exported checkpoint {epoch} of {run_dir} to {out} ({'f16' if args.f16 else 'f32'})")
     return 0
 
 
@@ -406,6 +437,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("ckpt")
     p.add_argument("file")
     p.set_defaults(fn=cmd_ckpt)
+    p = sub.add_parser("export", help="write model.bin + vocab.json + config.json of a run into one directory")
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--epoch", type=int, default=None)
+    p.add_argument("--runs", default="runs")
+    p.add_argument("--output", required=True)
+    p.add_argument("--f16", action="store_true", help="half-precision record (what `quantize` writes)")
+    p.set_defaults(fn=cmd_export)
+
     p = sub.add_parser("serve", help="HTTP front end for streaming generation from a trained run")
     p.add_argument("--checkpoint", default=None)
     p.add_argument("--epoch", type=int, default=None)

@@ -60,3 +60,21 @@ def test_latest_epoch_and_explicit_file(tmp_path):
     assert ep == 2
     mp2, sp2, ep2 = CK.resolve_checkpoint(str(mp))
     assert mp2 == mp and sp2 is None and ep2 == 2
+
+
+def test_export_then_infer_from_the_exported_directory(tmp_path, capsys):
+    """train -> export (f16) -> infer from the exported directory."""
+    from burn_dragon_b200 import cli
+    cfg = tmp_path / "t.toml"
+    cfg.write_text("[training]\nbatch_size = 2\nblock_size = 16\nlog_frequency = 1\n"
+                   "[model]\nn_layer = 1\nn_embd = 32\nn_head = 2\ndropout = 0.0\n")
+    runs = tmp_path / "runs"
+    assert cli.main(["train", "-c", str(cfg), "--synthetic", "--device", "cpu", "--max-iters", "2", "--runs", str(runs)]) == 0
+    out = tmp_path / "exported"
+    assert cli.main(["export", "--runs", str(runs), "--output", str(out), "--f16"]) == 0
+    assert (out / "model.bin").exists() and (out / "config.json").exists()
+    capsys.readouterr()
+    assert cli.main(["infer", "--checkpoint", str(out), "--prompt", "ab", "--max-tokens", "5", "--greedy",
+                     "--device", "cpu"]) == 0
+    cap = capsys.readouterr()
+    assert "loaded" in cap.err and cap.out.startswith("ab")
