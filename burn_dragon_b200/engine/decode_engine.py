@@ -115,10 +115,21 @@ class DecodeEngine:
     def generate(self, toks: torch.Tensor, settings, generator=None,
                  on_token: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
         from . import generation as GEN
+        state, last = GEN.prefill_state(self.model, toks, toks.device)
+        new = self.continue_from(state, last, settings, int(settings.max_new_tokens), on_token)
+        return torch.cat([toks, new], dim=1)
+
+    @torch.no_grad()
+    def continue_from(self, state, last, settings, n: int, on_token: Optional[Callable[[torch.Tensor], None]] = None,
+                      step0: int = 0) -> torch.Tensor:
+        """Decode `n` tokens per stream from a recurrent state and the logits of the last token seen
+        (what `prefill_state` or an earlier call left). Returns the new tokens [B, n]; `state` is
+        advanced and `self.last_logits` holds the logits after the last new token. `step0` is the
+        number of tokens this stream of calls has sampled so far: the random stream of the device
+        sampler continues from there instead of repeating."""
         model = self.model
-        dev = toks.device
-        B, P = toks.shape
-        state, last = GEN.prefill_state(model, toks, dev)
+        dev = last.device
+        B = last.shape[0]
         c = model.config
         seed = int(settings.seed if settings.seed is not None else torch.initial_seed() & 0x7FFFFFFF) & 0xFFFFFFFF
         key = (B, str(dev), float(settings.temperature), int(settings.top_k or 0), bool(settings.greedy), seed)
@@ -137,16 +148,17 @@ class DecodeEngine:
             for r, ls in zip(rho, state.layers):
                 if ls.rho is None:
                     r.zero_()
-                else:
+                elif ls.rho.data_ptr() != r.data_ptr():      # a continued stream already lives in these buffers
                     r.copy_(ls.rho)
-            buf["logits"].copy_(last.float())
+            if last.data_ptr() != buf["logits"].data_ptr():
+                buf["logits"].copy_(last.float())
             buf["pos"].fill_(state.position)
-            buf["step"].zero_()
+            buf["step"].fill_(int(step0))
 
         load_state()
         graph_ok = self.use_graph and d.rot != "pope"
-        out = [toks]
-        n = int(settings.max_new_tokens)
+        out = []
+        n = int(n)
         if graph_ok:
             if ctx["graph"] is None:
                 # warm up once on a side stream (lazy initialisation, allocator), rewind, then capture
@@ -183,7 +195,7 @@ class DecodeEngine:
             ls.rho = r
         state.position += n
         self.last_state, self.last_logits = state, buf["logits"]
-        return torch.cat(out, dim=1)
+        return torch.cat(out, dim=1) if out else torch.empty(B, 0, dtype=torch.int64, device=dev)
 
 
 def attach(model, **kw) -> DecodeEngine:

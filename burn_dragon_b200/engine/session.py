@@ -99,6 +99,17 @@ class InferenceSession:
         self.pending = [[] for _ in ids]
         self.printers = [GEN.StreamPrinter(self.tokenizer, write=self.pending[i].append) for i in range(len(ids))]
 
+    def _take(self, tokens: List[int]) -> None:
+        """One new token per stream: EOS ends a stream, anything else goes to its printer."""
+        eos = self.settings.eos_id
+        for i, t in enumerate(tokens):
+            if bool(self.finished[i]):
+                continue
+            if eos is not None and t == eos:
+                self.finished[i] = True
+            else:
+                self.printers[i].push(t)
+
     @torch.no_grad()
     def next_chunk(self, max_tokens: int = 4) -> Union[str, List[str]]:
         """Sample up to `max_tokens` tokens per stream, stopping early once every live stream has
@@ -108,23 +119,32 @@ class InferenceSession:
         if self.finished is None:
             raise RuntimeError("call start_stream first")
         s = self.settings
-        for _ in range(max(1, int(max_tokens))):
-            if self.done or (s.max_new_tokens is not None and self.generated >= s.max_new_tokens):
+        eng = getattr(self.model, "decode_engine", None)
+        if eng is not None and s.max_new_tokens is not None and eng.can_run(self.logits, s):
+            # GPU: the whole chunk is decoded on the device (sampling included) by replaying the
+            # captured decode step; only the chunk's token ids come back to the host
+            n = min(max(1, int(max_tokens)), s.max_new_tokens - self.generated)
+            if self.done or n <= 0:
                 self.finished.fill_(True)
-                break
-            nxt, self.logits = GEN.sample_next_token(self.model, self.state, self.logits, s.temperature, s.top_k,
-                                                     s.greedy, self.generator)
-            self.generated += 1
-            host = nxt.tolist()
-            for i, t in enumerate(host):
-                if bool(self.finished[i]):
-                    continue
-                if s.eos_id is not None and t == s.eos_id:
-                    self.finished[i] = True
-                else:
-                    self.printers[i].push(t)
-            if all(self.pending[i] or bool(self.finished[i]) for i in range(len(host))):
-                break
+            else:
+                new = eng.continue_from(self.state, self.logits, s, n, step0=self.generated)
+                self.logits = eng.last_logits
+                self.generated += n
+                for column in new.t().tolist():
+                    self._take(column)
+                if self.generated >= s.max_new_tokens:
+                    self.finished.fill_(True)
+        else:
+            for _ in range(max(1, int(max_tokens))):
+                if self.done or (s.max_new_tokens is not None and self.generated >= s.max_new_tokens):
+                    self.finished.fill_(True)
+                    break
+                nxt, self.logits = GEN.sample_next_token(self.model, self.state, self.logits, s.temperature, s.top_k,
+                                                         s.greedy, self.generator)
+                self.generated += 1
+                self._take(nxt.tolist())
+                if all(self.pending[i] or bool(self.finished[i]) for i in range(len(self.pending))):
+                    break
         out = ["".join(p) for p in self.pending]
         for p in self.pending:
             p.clear()

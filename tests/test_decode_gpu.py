@@ -100,3 +100,55 @@ def test_engine_greedy_is_deterministic_and_streams_independent():
     assert torch.equal(a, b)
     single = GEN.generate_tokens(m, prompt[1:2], settings=s)
     assert torch.equal(single, a[1:2])
+
+
+@pytest.mark.parametrize("rot", ["rope", "alibi"])
+def test_chunked_continuation_equals_one_call(rot):
+    """`continue_from` in chunks (the streaming-session path) produces the tokens of one `generate`
+    call: greedy, and sampled with a fixed seed (the sampler's random stream continues across chunks)."""
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
+                      rotary_embedding=rot)).cuda().eval()
+    eng = DE.attach(m)
+    toks = torch.randint(0, 256, (3, 64), device="cuda")
+    for s in (GEN.GenerationSettings(12, greedy=True), GEN.GenerationSettings(12, 1.0, 40, seed=7)):
+        whole = eng.generate(toks, s)[:, 64:]
+        state, last = GEN.prefill_state(m, toks, toks.device)
+        parts, done = [], 0
+        for n in (5, 4, 3):
+            parts.append(eng.continue_from(state, last, s, n, step0=done))
+            last, done = eng.last_logits, done + n
+        assert state.position == 64 + 12
+        assert torch.equal(torch.cat(parts, dim=1), whole), s
+
+
+def test_session_streams_on_the_decode_engine():
+    import json
+    from burn_dragon_b200.data.tokenizer import CharVocab
+    from burn_dragon_b200.engine import burn_record as BR
+    from burn_dragon_b200.engine import session as S
+    torch.manual_seed(0)
+    vocab = CharVocab.fit(["hello world, this is a tiny corpus of text."], include_unknown=True)
+    V = (len(vocab) + 7) // 8 * 8
+    chars = vocab.id2ch + [chr(0x2500 + i) for i in range(V - len(vocab))]       # pad the vocabulary to a multiple of 8
+    vocab = CharVocab(chars, True)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, mlp_internal_dim_multiplier=4, vocab_size=len(vocab),
+                      dropout=0.0, rotary_embedding="rope")).eval()
+    blob = BR.serialize(BR.from_model(m))
+    cfg = json.dumps(dict(run_name="t", block_size=64, overrides=dict(n_layer=2, n_embd=64, n_head=2,
+                                                                      mlp_internal_dim_multiplier=4,
+                                                                      rotary_embedding="rope")))
+    sess = S.load_model(blob, json.dumps(vocab.to_record()), cfg, device="cuda")
+    prompt = "hello world, this is a tiny corpus of text. hello world, this is"      # 64 characters
+    assert len(prompt) == 64
+    n0 = native.launch_count()
+    sess.start_stream(prompt, max_tokens=10, greedy=True)
+    text = ""
+    while not sess.done:
+        text += sess.next_chunk(max_tokens=4)
+    assert native.launch_count() > n0 and sess.generated == 10
+    ids = torch.tensor([vocab.encode(prompt)], device="cuda")
+    want = GEN.generate_tokens(sess.model, ids, "cuda", GEN.GenerationSettings(10, greedy=True))[0, 64:].tolist()
+    if vocab.eos_id in want:
+        want = want[:want.index(vocab.eos_id)]
+    assert text == vocab.decode(want)
