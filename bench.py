@@ -92,7 +92,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         sm.sort()
-        # median over samples taken under load (the upper half of the sorted clocks covers idle gaps)
+        # median SM clock over the samples of the timed region (the sampler runs only while it is timed)
         med = sm[len(sm) // 2] if sm else None
         return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
