@@ -130,6 +130,41 @@ def bench_reference_shapes(steps: int, warmup: int) -> Dict:
     return out
 
 
+def bench_tiny_cpu(steps: int = 5, warmup: int = 2) -> Dict:
+    """The CPU reference point: the `tiny` preset's model (config/tiny.toml over config/base.toml),
+    fp32, one process, B=4 x T=64 uniform bytes (seed 0): one training step (forward, loss, backward,
+    AdamW) and 64 tokens of cached greedy generation, wall-clock on the host. This torch path is also
+    the numerical oracle of the kernels; the reference's own CPU backend cannot be built here."""
+    import time
+    dev = torch.device("cpu")
+    torch.manual_seed(0)
+    cfg = C.load_preset("tiny")
+    m = build_model(cfg, vocab_size=256).to(dev)
+    tr = Trainer(m, lr=cfg.optimizer.learning_rate, weight_decay=cfg.optimizer.weight_decay)
+    g = torch.Generator().manual_seed(0)
+    b = torch.randint(0, 256, (4, 65), generator=g)
+
+    def timed(fn, n, w):
+        for _ in range(w):
+            fn()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        return (time.perf_counter() - t0) / n * 1e3
+
+    ms_train = timed(lambda: tr.train_step(b[:, :-1], b[:, 1:]), steps, warmup)
+    m.eval()
+    s = GEN.GenerationSettings(64, greedy=True)
+    ms_gen = timed(lambda: GEN.generate_tokens(m, b[:1, :64], dev, s), max(1, steps // 2), 1)
+    mc = m.config
+    return dict(bench="tiny-cpu", dtype="fp32", threads=torch.get_num_threads(),
+                model=dict(n_layer=mc.n_layer, n_embd=mc.n_embd, n_head=mc.n_head, n_latent_per_head=mc.latent_per_head,
+                           rotary_embedding=mc.rotary_embedding, dropout=mc.dropout),
+                train_ms_per_step=ms_train,
+                train_tokens_per_s=4 * 64 / ms_train * 1e3, generate_64_ms=ms_gen,
+                decode_tokens_per_s=64 / ms_gen * 1e3, final_loss=float(tr.eval_step(b[:, :-1], b[:, 1:])))
+
+
 def run(what: str, preset: str = "b200_base", steps: int = 10, warmup: int = 3, streams: int = 64, prompt: int = 1024,
         new_tokens: int = 2048) -> Dict:
     if what == "train":
@@ -138,4 +173,6 @@ def run(what: str, preset: str = "b200_base", steps: int = 10, warmup: int = 3, 
         return bench_decode(preset, streams, prompt, new_tokens)
     if what == "reference-shapes":
         return bench_reference_shapes(steps, warmup)
+    if what == "tiny-cpu":
+        return bench_tiny_cpu(steps, warmup)
     raise ValueError(what)
