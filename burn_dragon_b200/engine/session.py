@@ -99,6 +99,40 @@ class InferenceSession:
         self.pending = [[] for _ in ids]
         self.printers = [GEN.StreamPrinter(self.tokenizer, write=self.pending[i].append) for i in range(len(ids))]
 
+    # ---- state snapshots ---------------------------------------------------------------------------
+    def snapshot(self) -> Dict:
+        """Copy of everything a stream is: the recurrent state (constant size, whatever the length of
+        the text so far), the logits of the last token and the counters. Restoring it later continues
+        from this point - e.g. prefill a long shared prefix once and branch many completions off it."""
+        if self.state is None:
+            raise RuntimeError("call start_stream first")
+        return dict(position=self.state.position,
+                    rho=[None if l.rho is None else l.rho.detach().clone() for l in self.state.layers],
+                    logits=self.logits.detach().clone(), generated=self.generated, finished=self.finished.clone(),
+                    settings=self.settings)
+
+    def restore(self, snap: Dict, max_tokens: Optional[int] = None, seed: Optional[int] = None) -> None:
+        """Continue from a snapshot (of this session or of another session of the same model).
+        `max_tokens` / `seed` replace the snapshot's limit and sampling seed."""
+        import dataclasses
+        self._reset()
+        self.state = self.model.init_state()
+        self.state.position = int(snap["position"])
+        for l, r in zip(self.state.layers, snap["rho"]):
+            l.rho = None if r is None else r.to(self.device).clone()
+        self.logits = snap["logits"].to(self.device).clone()
+        self.generated = 0 if max_tokens is not None else int(snap["generated"])
+        s = snap["settings"]
+        self.settings = dataclasses.replace(s, max_new_tokens=s.max_new_tokens if max_tokens is None else int(max_tokens),
+                                            seed=s.seed if seed is None else int(seed))
+        if self.settings.seed is not None:
+            self.generator = torch.Generator(device=self.device).manual_seed(int(self.settings.seed))
+        n = self.logits.shape[0]
+        self.finished = snap["finished"].to(self.device).clone() if max_tokens is None else \
+            torch.zeros(n, dtype=torch.bool, device=self.device)
+        self.pending = [[] for _ in range(n)]
+        self.printers = [GEN.StreamPrinter(self.tokenizer, write=self.pending[i].append) for i in range(n)]
+
     def _take(self, tokens: List[int]) -> None:
         """One new token per stream: EOS ends a stream, anything else goes to its printer."""
         eos = self.settings.eos_id

@@ -133,3 +133,26 @@ def test_http_server_generate_and_stream():
     finally:
         srv.shutdown()
         srv.server_close()
+
+
+def test_snapshot_restore_branches_from_a_shared_prefix():
+    m, vocab, blob, vjson, cjson = _artefacts("rope")
+    sess = S.load_model(blob, vjson, cjson, device="cpu")
+    sess.start_stream("hello world", max_tokens=8, greedy=True)
+    snap = sess.snapshot()
+    first = ""
+    while not sess.done:
+        first += sess.next_chunk()
+    # branch 1: same continuation from the snapshot
+    sess.restore(snap)
+    again = ""
+    while not sess.done:
+        again += sess.next_chunk()
+    assert again == first
+    # branch 2: a fresh budget from the same prefix state, in another session of the same model
+    other = S.load_model(blob, vjson, cjson, device="cpu")
+    other.restore(snap, max_tokens=3)
+    short = ""
+    while not other.done:
+        short += other.next_chunk()
+    assert other.generated == 3 and first.startswith(short)
