@@ -1,4 +1,6 @@
-"""Build a model from a TrainingConfig (`[model].kind` selects the family)."""
+"""Build a model from a TrainingConfig (`[model].kind` selects the family). The reference builds its
+one model inline (`BDH::new(config, &device)`, src/bin/train.rs:261-274, src/bin/infer.rs:168-176);
+the Mamba and sparse-graph families have no counterpart there."""
 from __future__ import annotations
 
 from typing import Optional

@@ -1,4 +1,5 @@
-"""Process-group bootstrap helpers: one process per GPU, rendezvous through the environment."""
+"""Process-group bootstrap helpers: one process per GPU, rendezvous through the environment. The
+reference trains on one device only (`LearningStrategy::SingleDevice`, src/bin/train.rs:395)."""
 from __future__ import annotations
 
 import datetime
