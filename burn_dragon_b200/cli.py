@@ -1,4 +1,4 @@
-"""Command line entry points: `python -m burn_dragon_b200 <train|infer|serve|export|bench|quantize|build-vocab|ckpt>`.
+"""Command line entry points: `python -m burn_dragon_b200 <train|infer|eval|serve|export|bench|quantize|build-vocab|ckpt>`.
 
 The flags mirror the reference's binaries (src/bin/train.rs:52-81, src/bin/infer.rs:631-687,
 src/bin/quantize.rs): `-c/--config` is repeatable and every file is merged over `config/base.toml`;
@@ -346,6 +346,44 @@ def cmd_ckpt(args) -> int:
     return 0
 
 
+def cmd_eval(args) -> int:
+    """Cross-entropy of a checkpoint on text: a file given with --text (encoded with the run's
+    tokenizer, read in windows of the run's block size with the recurrent state carried across
+    windows, so the whole file is one long context), reported in nats and bits per token. The
+    reference only evaluates inside training (src/bin/train.rs:245-247)."""
+    import math
+    from .engine import session as S
+    from .engine import checkpoint as CK
+    from .ops import reference as R
+    model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    ckpt_dir = model_path.parent
+    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
+    sess = S.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
+                        run_cfg.read_text() if run_cfg.exists() else None, args.device)
+    model, dev = sess.model, sess.device
+    ids = torch.as_tensor(sess.tokenizer.encode_array(Path(args.text).read_text()), dtype=torch.int64, device=dev)
+    if args.max_tokens:
+        ids = ids[:args.max_tokens + 1]
+    if ids.numel() < 2:
+        raise SystemExit("need at least two tokens of text")
+    window = int(args.window or sess.block_size or 512)
+    state = model.init_state()
+    total, count = 0.0, 0
+    with torch.no_grad():
+        for lo in range(0, ids.numel() - 1, window):
+            x = ids[lo:lo + window].view(1, -1)
+            y = ids[lo + 1:lo + 1 + window].view(1, -1)
+            x = x[:, :y.shape[1]]
+            logits = model.forward_with_state(x, state)
+            total += float(R.cross_entropy_mean(logits.float(), y)) * y.shape[1]
+            count += y.shape[1]
+    nats = total / count
+    print(json.dumps(dict(checkpoint=str(model_path), epoch=epoch, tokens=count, window=window, nats_per_token=nats,
+                          bits_per_token=nats / math.log(2), perplexity=math.exp(nats))))
+    return 0
+
+
 def cmd_export(args) -> int:
     """Write a run's newest (or chosen) checkpoint as a self-contained model directory - model.bin,
     vocab.json, config.json side by side - the layout the reference's web page fetches
@@ -437,6 +475,16 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("ckpt")
     p.add_argument("file")
     p.set_defaults(fn=cmd_ckpt)
+    p = sub.add_parser("eval", help="cross-entropy of a checkpoint on a text file")
+    p.add_argument("--checkpoint", default=None)
+    p.add_argument("--epoch", type=int, default=None)
+    p.add_argument("--runs", default="runs")
+    p.add_argument("--device", default=None)
+    p.add_argument("--text", required=True)
+    p.add_argument("--window", type=int, default=None, help="tokens per forward call (default: the run's block size)")
+    p.add_argument("--max-tokens", type=int, default=None)
+    p.set_defaults(fn=cmd_eval)
+
     p = sub.add_parser("export", help="write model.bin + vocab.json + config.json of a run into one directory")
     p.add_argument("--checkpoint", default=None)
     p.add_argument("--epoch", type=int, default=None)

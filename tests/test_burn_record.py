@@ -144,3 +144,21 @@ def test_infer_cli_runs_the_shipped_model_directory(capsys):
     assert rc == 0 and "ROMEO:" in out
     tail = out.split("ROMEO:", 1)[1]
     assert len(tail.strip()) >= 10
+
+
+@needs_asset
+def test_eval_cli_scores_shakespeare_text(tmp_path, capsys):
+    """`eval` on the shipped checkpoint: a Shakespeare snippet scores about 1.1-1.6 nats per character,
+    and the windowed evaluation (state carried across windows) equals one long call."""
+    import json
+    from burn_dragon_b200 import cli
+    text = tmp_path / "t.txt"
+    text.write_text(SNIPPET)
+    outs = []
+    for window in (32, 4096):
+        assert cli.main(["eval", "--checkpoint", str(ASSET), "--text", str(text), "--device", "cpu",
+                         "--window", str(window)]) == 0
+        outs.append(json.loads(capsys.readouterr().out.strip().splitlines()[-1]))
+    assert outs[0]["tokens"] == outs[1]["tokens"] == len(SNIPPET) - 1
+    assert 0.5 < outs[1]["nats_per_token"] < 1.8
+    assert abs(outs[0]["nats_per_token"] - outs[1]["nats_per_token"]) < 1e-3
