@@ -157,7 +157,13 @@ def bench_tiny_cpu(steps: int = 5, warmup: int = 2) -> Dict:
     s = GEN.GenerationSettings(64, greedy=True)
     ms_gen = timed(lambda: GEN.generate_tokens(m, b[:1, :64], dev, s), max(1, steps // 2), 1)
     mc = m.config
-    return dict(bench="tiny-cpu", dtype="fp32", threads=torch.get_num_threads(),
+    # the same forward pass through the plain C++ restatement (one thread, double accumulators)
+    from ..utils import hostlib
+    ms_cpp = None
+    if hostlib.available():
+        rows = [b[i, :64].tolist() for i in range(4)]
+        ms_cpp = timed(lambda: [hostlib.oracle_forward(m, r) for r in rows], max(1, steps // 2), 1)
+    return dict(bench="tiny-cpu", dtype="fp32", threads=torch.get_num_threads(), cpp_oracle_forward_ms=ms_cpp,
                 model=dict(n_layer=mc.n_layer, n_embd=mc.n_embd, n_head=mc.n_head, n_latent_per_head=mc.latent_per_head,
                            rotary_embedding=mc.rotary_embedding, dropout=mc.dropout),
                 train_ms_per_step=ms_train,

@@ -25,6 +25,7 @@ def _load():
             lib.bdh_varint_write.restype = ctypes.c_int
             lib.bdh_encode_utf8_chars.restype = ctypes.c_int64
             lib.bdh_sim_flag_barrier.restype = ctypes.c_int
+            lib.bdh_oracle_forward.restype = ctypes.c_int
             _LIB = lib
         except OSError:
             _LIB = False
@@ -90,3 +91,30 @@ def simulate_flag_barrier(world: int, ctas: int, calls: int, first_epoch: int = 
     return int(lib.bdh_sim_flag_barrier(ctypes.c_int(world), ctypes.c_int(ctas), ctypes.c_int(calls),
                                         ctypes.c_uint32(first_epoch & 0xFFFFFFFF), ctypes.c_uint64(seed),
                                         ctypes.c_int64(spin_limit)))
+
+
+def oracle_forward(model, tokens, pos0: int = 0, want_state: bool = False):
+    """Logits [T, V] of one token sequence through the plain C++ restatement of the canonical
+    (recurrent) BDH forward (csrc/host/oracle.cpp: fp32 weights, double accumulators). With
+    `want_state` also returns the last layer's final state [H, N', D] (float64)."""
+    import torch
+    lib = _load()
+    c = model.config
+    kind = {"alibi": 0, "rope": 1, "pope": 2}[c.rotary_embedding]
+    f32 = lambda t: np.ascontiguousarray(t.detach().cpu().to(torch.float32).numpy())
+    w = [f32(model.embed.weight), f32(model.encoder), f32(model.encoder_v), f32(model.decoder), f32(model.lm_head)]
+    freqs, slopes = f32(model.freqs), f32(model.slopes)
+    toks = np.ascontiguousarray(np.asarray(tokens, dtype=np.int64).reshape(-1))
+    T, H, N, D, V = len(toks), c.n_head, c.latent_per_head, c.n_embd, c.vocab_size
+    logits = np.empty((T, V), dtype=np.float32)
+    Np = 2 * N if kind == 2 else N
+    rho = np.empty((H, Np, D), dtype=np.float64) if want_state else None
+    ptr = lambda a: ctypes.c_void_p(a.ctypes.data)
+    rc = lib.bdh_oracle_forward(ptr(w[0]), ptr(w[1]), ptr(w[2]), ptr(w[3]), ptr(w[4]), ptr(freqs), ptr(slopes), ptr(toks),
+                                ctypes.c_int(T), ctypes.c_int(c.n_layer), ctypes.c_int(D), ctypes.c_int(H),
+                                ctypes.c_int(N), ctypes.c_int(V), ctypes.c_int(kind),
+                                ctypes.c_float(float(c.relu_threshold)), ctypes.c_int(pos0), ptr(logits),
+                                ptr(rho) if want_state else ctypes.c_void_p(0))
+    if rc != 0:
+        raise ValueError("oracle_forward: bad argument")
+    return (logits, rho) if want_state else logits

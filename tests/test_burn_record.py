@@ -162,3 +162,20 @@ def test_eval_cli_scores_shakespeare_text(tmp_path, capsys):
     assert outs[0]["tokens"] == outs[1]["tokens"] == len(SNIPPET) - 1
     assert 0.5 < outs[1]["nats_per_token"] < 1.8
     assert abs(outs[0]["nats_per_token"] - outs[1]["nats_per_token"]) < 1e-3
+
+
+@needs_asset
+def test_cpp_oracle_scores_the_shipped_checkpoint():
+    """Shipped weights through the C++ oracle: same cross-entropy as the torch recurrent path on the
+    first 150 characters of the corpus (about 1.1 nats per character)."""
+    import torch.nn.functional as F
+    from burn_dragon_b200.utils import hostlib
+    m = _load_model()
+    vocab = CharVocab.from_json_str((ASSET / "vocab.json").read_text())
+    ids = vocab.encode(SNIPPET[:150])
+    logits = torch.from_numpy(hostlib.oracle_forward(m, ids[:-1]))
+    ce_cpp = F.cross_entropy(logits, torch.tensor(ids[1:])).item()
+    with torch.no_grad():
+        ce_torch = m(torch.tensor([ids[:-1]]), torch.tensor([ids[1:]]), mode="recurrent").item()
+    assert abs(ce_cpp - ce_torch) < 1e-4
+    assert abs(ce_cpp - 1.1055) < 0.02, ce_cpp

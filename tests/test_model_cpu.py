@@ -120,3 +120,30 @@ def test_gradient_accumulation_equals_one_large_batch():
         assert tb.step_index == ta.step_index
     for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
         assert torch.allclose(p, q, rtol=1e-4, atol=1e-6), n
+
+
+def test_cpp_oracle_equals_torch_recurrent_path():
+    """The plain C++ restatement of the forward pass (no torch, no shared code) against the torch
+    recurrent path: logits and the final state, every positional mode."""
+    import numpy as np
+    import pytest
+    import torch
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.utils import hostlib
+    assert hostlib.available()
+    for rot in ("alibi", "rope", "pope"):
+        torch.manual_seed(1)
+        m = BDH(BDHConfig(n_layer=3, n_embd=24, n_head=2, n_latent_per_head=10, vocab_size=50, dropout=0.0,
+                          rotary_embedding=rot, relu_threshold=0.01)).eval()
+        with torch.no_grad():
+            for p in (m.encoder, m.encoder_v, m.decoder):
+                p.mul_(8.0)
+        toks = torch.randint(0, 50, (1, 21))
+        st = m.init_state()
+        with torch.no_grad():
+            want = m.forward_with_state(toks, st, mode="recurrent")[0].numpy()
+        got, rho = hostlib.oracle_forward(m, toks[0].tolist(), want_state=True)
+        assert np.allclose(got, want, rtol=2e-4, atol=2e-5), (rot, np.abs(got - want).max())
+        assert np.allclose(rho, st.layers[-1].rho[0].numpy(), rtol=2e-4, atol=2e-5), rot
+    with pytest.raises(ValueError):
+        hostlib.oracle_forward(m, [0, 99])
