@@ -149,3 +149,16 @@ def test_phase_timers_cover_the_step():
     assert rep["step"]["calls"] == 2 and rep["layer.forward"]["calls"] == 2 * m.config.n_layer
     inner = rep["forward"]["ms"] + rep["backward"]["ms"] + rep["optimizer"]["ms"] + rep["grad_reduce"]["ms"]
     assert 0.5 * rep["step"]["ms"] < inner <= rep["step"]["ms"] * 1.05
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_kernel_logits_against_the_cpp_oracle(rot):
+    """The kernel path against the plain C++ restatement of the recurrence (an oracle that shares no
+    code with torch): same tolerance as against the torch recurrent path."""
+    from burn_dragon_b200.utils import hostlib
+    m = _model(rot).eval()
+    tok = torch.randint(0, 256, (1, 128), device="cuda")
+    with torch.no_grad():
+        got = m.forward_with_state(tok, m.init_state())[0].float().cpu()
+    want = torch.from_numpy(hostlib.oracle_forward(m, tok[0].tolist()))
+    assert _rel(got, want) < 0.05, _rel(got, want)
