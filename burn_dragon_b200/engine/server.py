@@ -5,6 +5,7 @@ chunks over HTTP). Standard library only.
     python -m burn_dragon_b200 serve --checkpoint runs/latest --port 8080
 
     GET  /health                          -> {"status": "ok", "model": {...}, "device": "cuda:0"}
+    GET  /metrics                         -> Prometheus text format: requests, generated tokens, busy seconds
     POST /generate  {"prompt": "ROMEO:", "max_tokens": 200, "temperature": 0.8, "top_k": 40,
                      "greedy": false, "seed": 1, "stream": true, "chunk_tokens": 4}
          stream=false -> {"text": "...", "tokens": 200}
@@ -19,6 +20,7 @@ from __future__ import annotations
 
 import json
 import threading
+import time
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Optional
 
@@ -29,6 +31,7 @@ MAX_BODY = 1 << 20
 
 def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
     lock = threading.Lock()
+    stats = {"requests": 0, "errors": 0, "tokens": 0, "busy_s": 0.0}
 
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
@@ -45,6 +48,21 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
             self.wfile.write(body)
 
         def do_GET(self):
+            if self.path == "/metrics":
+                body = ("# TYPE bdh_requests_total counter\n"
+                        f"bdh_requests_total {stats['requests']}\n"
+                        "# TYPE bdh_request_errors_total counter\n"
+                        f"bdh_request_errors_total {stats['errors']}\n"
+                        "# TYPE bdh_generated_tokens_total counter\n"
+                        f"bdh_generated_tokens_total {stats['tokens']}\n"
+                        "# TYPE bdh_generate_busy_seconds_total counter\n"
+                        f"bdh_generate_busy_seconds_total {stats['busy_s']:.6f}\n").encode()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/plain; version=0.0.4")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+                return
             if self.path != "/health":
                 return self._json(404, {"error": "unknown path"})
             c = session.model.config
@@ -76,32 +94,43 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
                 chunk_tokens = max(1, int(req.get("chunk_tokens", 4)))
                 stream = bool(req.get("stream", False))
             except (KeyError, ValueError, TypeError, json.JSONDecodeError) as e:
+                stats["errors"] += 1
                 return self._json(400, {"error": str(e)})
             many = isinstance(prompt, list)
             with lock:
+                t0 = time.perf_counter()
+                stats["requests"] += 1
                 try:
-                    session.start_stream(prompt, **kw)
-                except (ValueError, KeyError) as e:
-                    return self._json(400, {"error": str(e)})
-                if not stream:
-                    text = ["" for _ in prompt] if many else ""
-                    while not session.done:
-                        piece = session.next_chunk(chunk_tokens)
-                        text = [a + b for a, b in zip(text, piece)] if many else text + piece
-                    return self._json(200, {"text": text, "tokens": session.generated})
-                self.send_response(200)
-                self.send_header("Content-Type", "application/x-ndjson")
-                self.send_header("Transfer-Encoding", "chunked")
-                self.end_headers()
-                try:
-                    while not session.done:
-                        piece = session.next_chunk(chunk_tokens)
-                        if piece if not many else any(piece):
-                            self._chunk((json.dumps({"text": piece}) + "\n").encode())
-                    self._chunk((json.dumps({"done": True, "tokens": session.generated}) + "\n").encode())
-                    self.wfile.write(b"0\r\n\r\n")
-                except (BrokenPipeError, ConnectionResetError):
-                    pass        # the client went away: drop the stream, keep serving
+                    return self._generate(prompt, kw, chunk_tokens, stream, many)
+                finally:
+                    stats["busy_s"] += time.perf_counter() - t0
+                    stats["tokens"] += session.generated * (len(prompt) if many else 1)
+
+        def _generate(self, prompt, kw, chunk_tokens, stream, many):
+            try:
+                session.start_stream(prompt, **kw)
+            except (ValueError, KeyError) as e:
+                stats["errors"] += 1
+                return self._json(400, {"error": str(e)})
+            if not stream:
+                text = ["" for _ in prompt] if many else ""
+                while not session.done:
+                    piece = session.next_chunk(chunk_tokens)
+                    text = [a + b for a, b in zip(text, piece)] if many else text + piece
+                return self._json(200, {"text": text, "tokens": session.generated})
+            self.send_response(200)
+            self.send_header("Content-Type", "application/x-ndjson")
+            self.send_header("Transfer-Encoding", "chunked")
+            self.end_headers()
+            try:
+                while not session.done:
+                    piece = session.next_chunk(chunk_tokens)
+                    if piece if not many else any(piece):
+                        self._chunk((json.dumps({"text": piece}) + "\n").encode())
+                self._chunk((json.dumps({"done": True, "tokens": session.generated}) + "\n").encode())
+                self.wfile.write(b"0\r\n\r\n")
+            except (BrokenPipeError, ConnectionResetError):
+                pass        # the client went away: drop the stream, keep serving
 
     return ThreadingHTTPServer((host, port), Handler)
 

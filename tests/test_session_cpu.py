@@ -130,6 +130,11 @@ def test_http_server_generate_and_stream():
         with pytest.raises(urllib.error.HTTPError) as err:
             post(dict(prompt=["hello", "hi"], max_tokens=4))
         assert err.value.code == 400
+        metrics = urllib.request.urlopen(base + "/metrics", timeout=30).read().decode()
+        vals = {l.split()[0]: float(l.split()[1]) for l in metrics.splitlines() if l and not l.startswith("#")}
+        assert vals["bdh_requests_total"] == 4 and vals["bdh_request_errors_total"] == 1
+        assert vals["bdh_generated_tokens_total"] == 2 * whole["tokens"] + 2 * 4
+        assert vals["bdh_generate_busy_seconds_total"] > 0
     finally:
         srv.shutdown()
         srv.server_close()
