@@ -31,9 +31,15 @@ class MetricsLogger:
         if self.path is not None:
             with open(self.path, "a") as f:
                 f.write(json.dumps(rec) + "\n")
-        if not self.quiet and self.rank == 0 and (split != "train" or step % self.freq == 0):
+        if self.rank == 0 and (split != "train" or step % self.freq == 0):
             body = "  ".join(f"{k}={v:.5g}" if isinstance(v, float) else f"{k}={v}" for k, v in values.items())
-            print(f"[{split} {step:>7}] {body}", flush=True)
+            line = f"[{split} {step:>7}] {body}"
+            if self.path is not None:
+                # the run's text log (burn-train writes `experiment.log` beside its checkpoints)
+                with open(self.path.with_name("experiment.log"), "a") as f:
+                    f.write(time.strftime("%Y-%m-%d %H:%M:%S ") + line + "\n")
+            if not self.quiet:
+                print(line, flush=True)
 
     def summary(self) -> str:
         """min / max / last of every metric, as burn-train's `.summary()` prints at the end of a run."""
