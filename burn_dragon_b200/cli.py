@@ -248,8 +248,7 @@ def cmd_infer(args) -> int:
 
     cfg = _load_config(args.config, args.base)
     model_path, state_path, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
-    ckpt_dir = model_path.parent
-    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    run_dir = CK.run_dir_of(model_path)
     run_cfg_path = run_dir / "config.json"
     if not args.config and run_cfg_path.exists():
         apply_run_config(cfg, json.loads(run_cfg_path.read_text()))
@@ -356,8 +355,7 @@ def cmd_eval(args) -> int:
     from .engine import checkpoint as CK
     from .ops import reference as R
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
-    ckpt_dir = model_path.parent
-    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    run_dir = CK.run_dir_of(model_path)
     vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
     sess = S.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
                         run_cfg.read_text() if run_cfg.exists() else None, args.device)
@@ -392,8 +390,7 @@ def cmd_export(args) -> int:
     from .engine import burn_record as BR
     from .engine import checkpoint as CK
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
-    ckpt_dir = model_path.parent
-    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    run_dir = CK.run_dir_of(model_path)
     out = Path(args.output)
     out.mkdir(parents=True, exist_ok=True)
     if args.f16:
@@ -412,8 +409,7 @@ def cmd_serve(args) -> int:
     from .engine import checkpoint as CK
     from .engine import server, session
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
-    ckpt_dir = model_path.parent
-    run_dir = ckpt_dir.parent if ckpt_dir.name == "checkpoint" else ckpt_dir
+    run_dir = CK.run_dir_of(model_path)
     vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
     sess = session.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
                               run_cfg.read_text() if run_cfg.exists() else None, args.device)

@@ -123,6 +123,13 @@ def gather_for_checkpoint(trainer, wrapper=None):
     return weights, opt_state
 
 
+def run_dir_of(model_path) -> Path:
+    """The run directory a model file belongs to: the parent of its `checkpoint/` directory, or - for
+    an exported model directory - the directory itself. `vocab.json` and `config.json` live there."""
+    d = Path(model_path).parent
+    return d.parent if d.name == "checkpoint" else d
+
+
 def save_checkpoint(run_dir, epoch: int, model, trainer=None, loader=None, extra: Optional[Dict[str, Any]] = None,
                     logical_state: Optional[Dict[str, torch.Tensor]] = None,
                     optimizer_state: Optional[Dict[str, Any]] = None) -> Path:
