@@ -269,10 +269,15 @@ def cmd_infer(args) -> int:
     # tokenizer: the run's vocab.json, else the dataset cache
     vocab = run_dir / "vocab.json"
     byte_vocab = None
-    if not vocab.exists() and model_path.suffix == ".bin":
+    if not vocab.exists():
         # a run without a vocabulary file was trained on bytes: its embedding has 256 (or 259) rows
-        from .engine import burn_record as BR
-        V = BR.infer_dims(BR.load(model_path))["vocab_size"]
+        V = None
+        if model_path.exists() and model_path.suffix == ".bin":
+            from .engine import burn_record as BR
+            V = BR.infer_dims(BR.load(model_path))["vocab_size"]
+        elif state_path is not None:
+            weights = torch.load(state_path, map_location="cpu", weights_only=False).get("model", {})
+            V = next((int(t.shape[0]) for k, t in weights.items() if "embed" in k and t.dim() == 2), None)
         byte_vocab = V if V in (256, 259) else None
     if byte_vocab is not None:
         tok = T.ByteTokenizer(byte_vocab == 259)

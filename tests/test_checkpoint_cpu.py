@@ -78,3 +78,20 @@ def test_export_then_infer_from_the_exported_directory(tmp_path, capsys):
                      "--device", "cpu"]) == 0
     cap = capsys.readouterr()
     assert "loaded" in cap.err and cap.out.startswith("ab")
+
+
+def test_train_then_infer_a_non_bdh_model_through_the_cli(tmp_path, capsys):
+    """Model families without a Burn record (weights live in state-N.pt): byte-trained run, then infer."""
+    import os
+    from burn_dragon_b200 import cli
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    over = tmp_path / "o.toml"
+    over.write_text("[training]\nbatch_size = 2\nblock_size = 64\nlog_frequency = 1\n")
+    runs = tmp_path / "runs"
+    preset = os.path.join(root, "config", "mamba2.toml")
+    assert cli.main(["train", "-c", preset, "-c", str(over), "--synthetic", "--device", "cpu", "--max-iters", "2",
+                     "--runs", str(runs)]) == 0
+    capsys.readouterr()
+    assert cli.main(["infer", "--runs", str(runs), "-c", preset, "--prompt", "ab", "--max-tokens", "6", "--greedy",
+                     "--device", "cpu"]) == 0
+    assert capsys.readouterr().out.startswith("ab")
