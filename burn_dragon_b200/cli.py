@@ -360,6 +360,7 @@ def cmd_eval(args) -> int:
     from .engine import checkpoint as CK
     from .ops import reference as R
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    CK.require_burn_record(model_path, "eval")
     run_dir = CK.run_dir_of(model_path)
     vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
     sess = S.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
@@ -395,6 +396,7 @@ def cmd_export(args) -> int:
     from .engine import burn_record as BR
     from .engine import checkpoint as CK
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    CK.require_burn_record(model_path, "export")
     run_dir = CK.run_dir_of(model_path)
     out = Path(args.output)
     out.mkdir(parents=True, exist_ok=True)
@@ -414,6 +416,7 @@ def cmd_serve(args) -> int:
     from .engine import checkpoint as CK
     from .engine import server, session
     model_path, _, epoch = CK.resolve_checkpoint(args.checkpoint, args.epoch, args.runs)
+    CK.require_burn_record(model_path, "serve")
     run_dir = CK.run_dir_of(model_path)
     vocab, run_cfg = run_dir / "vocab.json", run_dir / "config.json"
     sess = session.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,

@@ -123,6 +123,17 @@ def gather_for_checkpoint(trainer, wrapper=None):
     return weights, opt_state
 
 
+def require_burn_record(model_path, what: str) -> Path:
+    """`what` (serve / eval / export) works from a Burn record, i.e. a BDH run; the other model
+    families keep their weights in the state file only."""
+    p = Path(model_path)
+    if not p.exists():
+        raise SystemExit(f"{what}: {p} does not exist - this command needs a BDH checkpoint (Burn record); "
+                         "Mamba and sparse-graph runs store their weights in state-N.pt and are used through "
+                         "`infer`")
+    return p
+
+
 def run_dir_of(model_path) -> Path:
     """The run directory a model file belongs to: the parent of its `checkpoint/` directory, or - for
     an exported model directory - the directory itself. `vocab.json` and `config.json` live there."""
