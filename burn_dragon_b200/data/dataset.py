@@ -20,6 +20,7 @@ network, and a `synthetic` source provides uniform random bytes for benchmarks.
 from __future__ import annotations
 
 import csv
+import dataclasses
 import json
 import os
 import urllib.request
@@ -341,12 +342,43 @@ def _hf_file(cache: Path, spec: HFSpec, name: str) -> Path:
     return local
 
 
+def _token_cache_path(cache: Path, spec: HFSpec, tok_cfg, files: List[Path]) -> Path:
+    """Name of the encoded-corpus cache for this (dataset spec, tokenizer, source files) combination:
+    any change of a source file's size or time stamp, of the record template or of the tokenizer
+    settings gives another name, so a stale cache is never read."""
+    import hashlib
+    h = hashlib.sha1()
+    h.update(repr((spec.repo_id, spec.revision, spec.format, spec.train_files, spec.validation_files,
+                   spec.text_fields, spec.field_separator, spec.template, spec.max_records)).encode())
+    h.update(repr(sorted(dataclasses.asdict(tok_cfg).items()) if dataclasses.is_dataclass(tok_cfg)
+                  else repr(tok_cfg)).encode())
+    vp = T.storage_path(tok_cfg, cache)
+    for f in files + ([vp] if vp is not None else []):
+        st = f.stat() if f.exists() else None
+        h.update(repr((str(f.name), None if st is None else (st.st_size, st.st_mtime_ns))).encode())
+    return cache / f"tokens-{h.hexdigest()[:16]}.npz"
+
+
 def huggingface_dataset(cache_dir, block_size, batch_size, train_split_ratio, tok_cfg, spec: HFSpec, seed=0):
-    """Records from a Hugging Face dataset repo, concatenated (src/dataset/huggingface.rs:36-191)."""
+    """Records from a Hugging Face dataset repo, concatenated (src/dataset/huggingface.rs:36-191).
+    The encoded corpus is cached beside the downloaded files (the reference re-reads and re-encodes
+    every shard on every start); a later run with the same files and tokenizer maps it from disk."""
     if not spec.text_fields:
         raise ValueError("huggingface dataset requires at least one text field")
     cache = Path(cache_dir)
     cache.mkdir(parents=True, exist_ok=True)
+    vocab_file = T.storage_path(tok_cfg, cache)
+    local = [cache / "huggingface" / spec.repo_id.replace("/", "--") / (spec.revision or "main") / n
+             for n in list(spec.train_files) + list(spec.validation_files)]
+    if all(f.exists() for f in local) and (vocab_file is None or vocab_file.exists()):
+        cached = _token_cache_path(cache, spec, tok_cfg, local)
+        if cached.exists():
+            with np.load(cached) as z:
+                tokens, train_len = z["tokens"], int(z["train_len"])
+            tok = T.load_or_fit(tok_cfg, cache, [])
+            if len(tokens) > block_size + 1:
+                train_len = min(max(train_len, block_size + 1), len(tokens) - 1)
+                return TokenSequenceDataset(tokens, train_len, block_size, batch_size, train_split_ratio, tok, seed)
     train_records: List[str] = []
     for name in spec.train_files:
         if spec.max_records is not None and len(train_records) >= spec.max_records:
@@ -380,6 +412,11 @@ def huggingface_dataset(cache_dir, block_size, batch_size, train_split_ratio, to
         train_len = _clamp_train_len(len(tokens), train_split_ratio, block_size)
     elif train_len <= block_size:
         train_len = min(block_size + 1, len(tokens) - 1)
+    if all(f.exists() for f in local):
+        try:        # best effort: a read-only cache directory only costs the next start its speed-up
+            np.savez(_token_cache_path(cache, spec, tok_cfg, local), tokens=tokens, train_len=np.int64(train_len))
+        except OSError:
+            pass
     return TokenSequenceDataset(tokens, train_len, block_size, batch_size, train_split_ratio, tok, seed)
 
 

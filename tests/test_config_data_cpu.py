@@ -196,6 +196,18 @@ def test_hf_dataset_offline_from_cache(tmp_path, monkeypatch):
     f.write_text("\n".join("sample text number %d" % i for i in range(50)))
     ds = D.huggingface_dataset(tmp_path, 8, 2, 0.9, C.TokenizerConfig("byte", True, False, None), spec)
     assert len(ds.tokens) > 500 and ds.sample_batch().inputs.shape == (2, 8)
+    # the encoded corpus is cached; a second start reads it instead of the shards, and a changed
+    # shard gets a fresh encoding
+    caches = list(tmp_path.glob("tokens-*.npz"))
+    assert len(caches) == 1
+    monkeypatch.setattr(D, "collect_records", lambda *a, **k: (_ for _ in ()).throw(AssertionError("cache not used")))
+    again = D.huggingface_dataset(tmp_path, 8, 2, 0.9, C.TokenizerConfig("byte", True, False, None), spec)
+    assert np.array_equal(again.tokens, ds.tokens) and again.train_len == ds.train_len
+    monkeypatch.undo()
+    monkeypatch.setenv("BDH_OFFLINE", "1")
+    f.write_text("\n".join("other text %d" % i for i in range(80)))
+    fresh = D.huggingface_dataset(tmp_path, 8, 2, 0.9, C.TokenizerConfig("byte", True, False, None), spec)
+    assert len(fresh.tokens) != len(ds.tokens) and len(list(tmp_path.glob("tokens-*.npz"))) == 2
 
 
 def test_char_vocab_native_encode_matches_python():
