@@ -286,6 +286,12 @@ def cmd_infer(args) -> int:
         tok = T.CharVocab.load(vp)
     else:
         tok = T.ByteTokenizer(cfg.dataset.tokenizer.add_special_tokens)
+    from .parallel import dist_utils
+    world = dist_utils.env_world()
+    if world > 1:
+        dist_utils.init_distributed()
+        if args.streaming or args.viz:
+            raise SystemExit("infer under torch.distributed.run (context-parallel prefill) has no --streaming / --viz")
     dev = _device(args.device)
     model = build_model(cfg, vocab_size=len(tok)).to(dev).eval()
     CK.load_checkpoint(model, model_path, state_path)
@@ -293,6 +299,8 @@ def cmd_infer(args) -> int:
         model.use_native = False
     print(f"loaded {model_path} (epoch {epoch}) on {dev}", file=sys.stderr)
 
+    if getattr(args, "prompt_file", None):
+        g.prompt = Path(args.prompt_file).read_text()
     strategy = GEN.resolve_context_strategy(g.context_strategy, cfg.training.block_size)
     ids = tok.encode(g.prompt, False, False)
     if strategy.kind == "sliding" and len(ids) > strategy.window:
@@ -323,6 +331,18 @@ def cmd_infer(args) -> int:
         sys.stdout.write("\n")
         if viz is not None and args.viz_out:
             viz.save(args.viz_out)
+    elif world > 1:
+        # context parallel: the ranks split the prompt (one segment each, per-layer state exchange),
+        # end up with the same state, and decode in lockstep; rank 0 prints
+        from .parallel.cp import ContextParallel
+        state, last = ContextParallel(model).prefill_any(torch.tensor([ids], dtype=torch.int64, device=dev))
+        gen = torch.Generator(device=dev).manual_seed(g.seed if g.seed is not None else 0)
+        new = []
+        for _ in range(max_new):
+            nxt, last = GEN.sample_next_token(model, state, last, g.temperature, g.top_k, g.greedy, gen)
+            new.append(int(nxt[0]))
+        if dist_utils.rank() == 0:
+            print(tok.decode(list(ids) + new))
     else:
         toks = GEN.generate_tokens(model, ids, dev, settings)
         print(tok.decode([int(t) for t in toks[0].tolist()]))
@@ -458,6 +478,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--checkpoint", default=None)
     p.add_argument("--epoch", type=int, default=None)
     p.add_argument("--prompt", default=None)
+    p.add_argument("--prompt-file", default=None, help="read the prompt from a file (long contexts)")
     p.add_argument("--max-tokens", type=int, default=None)
     p.add_argument("--temperature", type=float, default=None)
     p.add_argument("--top-k", type=int, default=None)

@@ -64,6 +64,21 @@ class ContextParallel:
         return logits
 
     @torch.no_grad()
+    def prefill_any(self, tokens_full: torch.Tensor):
+        """`prefill` for a prompt of any length: the largest prefix that splits evenly over the ranks
+        runs context-parallel, the few tokens left over run replicated on every rank. Returns
+        (state, logits of the last prompt token [B, V]), the same on every rank."""
+        P = tokens_full.shape[1]
+        even = (P // self.world) * self.world
+        if even == 0:
+            state = self.model.init_state()
+            return state, self.model.forward_with_state(tokens_full, state)[:, -1]
+        state, last = self.prefill(tokens_full[:, :even])
+        if even < P:
+            last = self.model.forward_with_state(tokens_full[:, even:].contiguous(), state)[:, -1]
+        return state, last
+
+    @torch.no_grad()
     def prefill(self, tokens_full: torch.Tensor):
         """Split a [B, P] prompt (P divisible by the group size) over the ranks, run it, and return
         (state after the prompt, logits of the last prompt token [B, V]) on every rank."""

@@ -147,3 +147,29 @@ strategy = "fsdp"
     assert len(run_dirs) == 1                      # the restart continued the same run
     names = sorted(p.name for p in (run_dirs[0] / "checkpoint").glob("model-*.bin"))
     assert names == ["model-1.bin", "model-2.bin", "model-3.bin"], names
+
+
+def test_infer_cli_context_parallel_equals_single_process(tmp_path):
+    """`infer` under the launcher splits a long prompt over the ranks (context-parallel prefill);
+    the greedy continuation equals the single-process one. The prompt length is odd on purpose:
+    the left-over token runs replicated."""
+    cfg = tmp_path / "t.toml"
+    cfg.write_text("[training]\nbatch_size = 2\nblock_size = 16\nlog_frequency = 1\n"
+                   "[model]\nn_layer = 2\nn_embd = 32\nn_head = 2\ndropout = 0.0\nrotary_embedding = \"rope\"\n")
+    runs = tmp_path / "runs"
+    e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
+    r = run_job([sys.executable, "-m", "burn_dragon_b200", "train", "-c", str(cfg), "--synthetic", "--device", "cpu",
+                 "--max-iters", "2", "--runs", str(runs)], e, 300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    prompt = tmp_path / "p.txt"
+    prompt.write_text("the quick brown fox jumps over the lazy dog " * 3 + "x")     # 133 bytes
+    tail = ["-m", "burn_dragon_b200", "infer", "--runs", str(runs), "-c", str(cfg), "--prompt-file", str(prompt),
+            "--max-tokens", "12", "--greedy", "--device", "cpu"]
+    one = run_job([sys.executable] + tail, e, 300)
+    assert one.returncode == 0, one.stderr[-2000:]
+    port = 29250 + os.getpid() % 40
+    two = run_job([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                   "127.0.0.1", "--master-port", str(port)] + tail, e, 300)
+    assert two.returncode == 0, two.stdout[-1000:] + two.stderr[-3000:]
+    text = one.stdout.strip().splitlines()[-1]
+    assert len(text) > 133 and text in two.stdout
