@@ -92,6 +92,9 @@ def cmd_train(args) -> int:
                        getattr(getattr(model, "config", None), "n_embd", 256))
     strategy = cfg.parallel.strategy if world > 1 else "single"
     wrapper = None
+    if strategy == "tp" and cfg.parallel.tp not in (1, world):
+        raise SystemExit(f"[parallel] tp = {cfg.parallel.tp}, but the job has {world} ranks: a tensor-parallel job "
+                         "shards over all of its ranks")
     if strategy in ("fsdp", "tp"):
         from .parallel import build_wrapper
         wrapper = build_wrapper(model, cfg, strategy)

@@ -193,9 +193,8 @@ class ModelOverrides:
 @dataclass
 class ParallelConfig:
     strategy: str = "single"        # single | ddp | fsdp | tp
-    tp: int = 1
+    tp: int = 1                     # documentation of the intended group size; a tp job shards over all its ranks
     fused_collectives: bool = True  # in-kernel NVLink paths; False = NCCL-only baseline
-    bucket_mb: int = 64
     heartbeat_timeout_s: float = 60.0   # a peer silent for this long is reported before the next step; 0 = off
 
 
@@ -312,6 +311,10 @@ def from_dict(value: Dict[str, Any]) -> TrainingConfig:
     if parallel.strategy not in ("single", "ddp", "fsdp", "tp"):
         raise ConfigError("parallel.strategy must be single | ddp | fsdp | tp")
     precision = _build(PrecisionConfig, value.get("precision", {}), "precision")
+    if precision.compute not in ("bf16", "fp32"):
+        raise ConfigError("precision.compute must be bf16 (kernels) or fp32 (torch path)")
+    if precision.state != "fp32":
+        raise ConfigError("precision.state: the recurrent decode state is kept in fp32 (no other type is implemented)")
     return TrainingConfig(dataset, training, optimizer, generation, model, parallel, precision)
 
 
