@@ -32,7 +32,9 @@ ops = native.ops
 # ------------------------------------------------------------------------------------------------
 def can_run(model, tokens: torch.Tensor, state) -> bool:
     """True when the kernel path computes exactly what the torch path defines for this call."""
-    if not getattr(model, "use_native", True) or not tokens.is_cuda or not native.available():
+    if not getattr(model, "use_native", True):
+        return False
+    if not emulate.active() and (not tokens.is_cuda or not native.available()):
         return False
     c = model.config
     B, T = tokens.shape
@@ -107,7 +109,9 @@ def _split_k(tiles: int, K: int, dev) -> int:
     last wave. Splitting K multiplies the tile count; partial sums meet through fp32 atomics."""
     sms = _SM_COUNT.get(dev)
     if sms is None:
-        sms = _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+        # (the emulated path on a CPU plans as for a B200)
+        sms = _SM_COUNT[dev] = (torch.cuda.get_device_properties(dev).multi_processor_count
+                                if torch.device(dev).type == "cuda" else 148)
     best, best_eff = 1, tiles / (-(-tiles // sms) * sms)
     for s in (2, 3, 4, 6, 8):
         if K % (s * 64) or K // s < 1024:
@@ -441,3 +445,6 @@ def loss(model, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Mean cross-entropy of the canonical forward, differentiable w.r.t. the model parameters."""
     return _FusedLoss.apply(tokens, targets, model.embed.weight, model.encoder, model.encoder_v, model.decoder,
                             model.lm_head, model)
+
+
+from . import emulate  # noqa: E402  (last: with BDH_EMULATE_KERNELS=1 it re-points `ops` and `G.gemm` defined above)

@@ -5,6 +5,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from .selftest import _bf16_path
+
 
 def _bdh(dev, rot="rope", N=128):
     from ..models.bdh import BDH, BDHConfig
@@ -40,7 +42,7 @@ def case_fsdp(dev):
             tr.train_step(mine[:, :-1], mine[:, 1:])
             tr1.train_step(data[:, :-1], data[:, 1:])
         sd = w.gather_state_dict()
-        tol = 2e-2 if dev.type == "cuda" else 1e-5
+        tol = 2e-2 if _bf16_path(dev) else 1e-5
         for k, v in one.state_dict().items():
             assert _rel(sd[k], v.cpu()) < tol, (fused, k, _rel(sd[k], v.cpu()))
         osd = w.optimizer.logical_state_dict()
@@ -212,7 +214,7 @@ def case_cp(dev):
             mine2 = cp.forward_with_state(toks[:, half + rank * T:half + (rank + 1) * T].contiguous(), st)
             assert st.position == 2 * half
             st_p, last = cp.prefill(toks[:, :half])
-        tol = 5e-2 if dev.type == "cuda" else 1e-4
+        tol = 5e-2 if _bf16_path(dev) else 1e-4
         assert _rel(mine1, ref1[:, rank * T:(rank + 1) * T]) < tol, (rot, "first", _rel(mine1, ref1[:, rank * T:(rank + 1) * T]))
         assert _rel(mine2, ref2[:, rank * T:(rank + 1) * T]) < tol, (rot, "second", _rel(mine2, ref2[:, rank * T:(rank + 1) * T]))
         for a, b in zip(st.layers, ref_state.layers):
@@ -268,7 +270,7 @@ def case_ckpt(dev):
         assert t_c.step_index == 2 and ep == 1
         loss_c = t_c.train_step(x, y)
         got = w_c.gather_state_dict()
-        tol = 2e-2 if dev.type == "cuda" else 1e-5
+        tol = 2e-2 if _bf16_path(dev) else 1e-5
         assert abs(loss_a.item() - loss_c.item()) < tol * max(1.0, abs(loss_a.item())), (kind, loss_a.item(), loss_c.item())
         for k in want:
             assert _rel(got[k].float(), want[k].float()) < tol, (kind, k, _rel(got[k].float(), want[k].float()))

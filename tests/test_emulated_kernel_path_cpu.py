@@ -1,0 +1,91 @@
+"""The kernel path's orchestration on CPU: `ops.fused_bdh` with every launch replaced by the fp32
+statement of the same contract (`ops.emulate`), against the torch definition of the model."""
+import pytest
+import torch
+
+from burn_dragon_b200.models.bdh import BDH, BDHConfig
+from burn_dragon_b200.ops import emulate, fused_bdh
+
+
+def _model(rot, dropout=0.0):
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=dropout,
+                      rotary_embedding=rot))
+    with torch.no_grad():
+        m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+        for p in m.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    return m
+
+
+def _rel(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _cos(a, b):
+    a, b = a.float().flatten(), b.float().flatten()
+    return (torch.dot(a, b) / (a.norm() * b.norm() + 1e-20)).item()
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_loss_and_gradients(rot):
+    m = _model(rot)
+    tok, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    assert not fused_bdh.can_run(m, tok, None)            # no GPU, no emulation: the torch path would run
+    with emulate.kernel_path():
+        assert fused_bdh.can_run(m, tok, None)
+        loss_k = m(tok, tgt)
+        loss_k.backward()
+    gk = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    loss_t = m(tok, tgt, mode="parallel")
+    loss_t.backward()
+    assert abs(loss_k.item() - loss_t.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert _cos(gk[n], p.grad) > 0.99 and _rel(gk[n], p.grad) < 0.12, (n, _cos(gk[n], p.grad), _rel(gk[n], p.grad))
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_prefill_state_and_continuation(rot):
+    m = _model(rot).eval()
+    tok = torch.randint(0, 256, (1, 256))
+    with torch.no_grad():
+        st_t = m.init_state()
+        want = m.forward_with_state(tok, st_t, mode="recurrent")
+        with emulate.kernel_path():
+            st_a = m.init_state()
+            whole = m.forward_with_state(tok, st_a)
+            st_b = m.init_state()
+            parts = torch.cat([m.forward_with_state(tok[:, :128], st_b), m.forward_with_state(tok[:, 128:], st_b)], 1)
+    assert st_a.position == st_b.position == 256
+    assert _rel(whole, want) < 0.05 and _rel(parts, want) < 0.05
+    assert _rel(st_a.layers[-1].rho, st_t.layers[-1].rho) < 0.05
+    assert _rel(st_b.layers[-1].rho, st_t.layers[-1].rho) < 0.05
+
+
+def test_recompute_modes_and_dropout():
+    m = _model("rope")
+    tok, tgt = torch.randint(0, 256, (2, 64)), torch.randint(0, 256, (2, 64))
+    with emulate.kernel_path():
+        m(tok, tgt).backward()
+        g0 = {n: p.grad.clone() for n, p in m.named_parameters()}
+        for mode, layers in ((True, 2), (1, 1)):
+            m.zero_grad()
+            m.recompute = mode
+            m(tok, tgt).backward()
+            assert m._recomputed_layers == layers
+            for n, p in m.named_parameters():
+                assert torch.allclose(g0[n], p.grad, rtol=1e-4, atol=1e-6), (mode, n)
+        # dropout: a recomputed layer draws the same mask as its first forward
+        d = _model("alibi", dropout=0.3).train()
+        d.recompute = False
+        d(tok, tgt).backward()
+        g_saved = {n: p.grad.clone() for n, p in d.named_parameters()}
+        calls = d._drop_calls
+        d.zero_grad()
+        d.recompute = True
+        d._drop_calls = calls - 1          # same call counter, hence the same mask seeds
+        d(tok, tgt).backward()
+        for n, p in d.named_parameters():
+            assert torch.allclose(g_saved[n], p.grad, rtol=1e-4, atol=1e-6), n

@@ -173,3 +173,11 @@ def test_infer_cli_context_parallel_equals_single_process(tmp_path):
     assert two.returncode == 0, two.stdout[-1000:] + two.stderr[-3000:]
     text = one.stdout.strip().splitlines()[-1]
     assert len(text) > 133 and text in two.stdout
+
+
+@pytest.mark.parametrize("case", ["tp", "cp", "fsdp", "ckpt"])
+def test_parallel_wrappers_over_the_emulated_kernel_path(case):
+    """The same multi-rank cases with the model on the kernel path's orchestration (every launch
+    replaced by its fp32 statement, BDH_EMULATE_KERNELS=1): the tensor-parallel reductions between the
+    GEMM launches, the context-parallel state exchange and carry-in, sharded checkpoints."""
+    run_ranks(case, env={"BDH_EMULATE_KERNELS": "1"})
