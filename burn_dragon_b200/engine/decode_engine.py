@@ -30,7 +30,10 @@ class DecodeEngine:
     # ---- eligibility ---------------------------------------------------------------------------
     def can_run(self, toks: torch.Tensor, settings) -> bool:
         c = self.model.config
-        if not toks.is_cuda or not native.available() or not getattr(self.model, "use_native", True):
+        from ..ops import emulate
+        if not getattr(self.model, "use_native", True):
+            return False
+        if not emulate.active() and (not toks.is_cuda or not native.available()):
             return False
         if c.n_embd % 64 or c.n_embd > 1024 or c.latent_per_head % 64 or c.vocab_size > 1024 or c.vocab_size % 8:
             return False
@@ -156,7 +159,7 @@ class DecodeEngine:
             buf["step"].fill_(int(step0))
 
         load_state()
-        graph_ok = self.use_graph and d.rot != "pope"
+        graph_ok = self.use_graph and d.rot != "pope" and dev.type == "cuda"
         out = []
         n = int(n)
         if graph_ok:

@@ -89,9 +89,67 @@ class TorchOps:
         dx.copy_(torch.where(xf > 0, g, torch.zeros_like(g)).view(M, HN))
 
 
+    # ---- decode step (engine/decode_engine.py) ----------------------------------------------------
+    @staticmethod
+    def sample_tokens(logits, out, temperature, top_k, greedy, seed, step_host, step_dev):
+        """Greedy: lowest index among the maxima, as the kernel. Sampling: same distribution
+        (temperature, top-k threshold with ties kept), drawn from a torch generator keyed by
+        (seed, step) - not the kernel's hash stream, so sampled tokens differ from the GPU's."""
+        x = logits.float()
+        if greedy:
+            out.copy_(torch.argmax(x, dim=-1))
+            return
+        step = int(step_dev.item()) if step_dev is not None else int(step_host)
+        x = R.top_k_filter(x / max(float(temperature), 1e-8), int(top_k) if top_k else None)
+        g = torch.Generator(device="cpu").manual_seed((int(seed) * 1000003 + step) & 0x7FFFFFFF)
+        p = torch.softmax(x, dim=-1).cpu()
+        out.copy_(torch.multinomial(p, 1, generator=g)[:, 0].to(out.device))
+
+    @staticmethod
+    def rope_table_step(pos, pair_freqs, table):
+        table.copy_(G.rope_table(int(pos.item()), 1, pair_freqs))
+
+    @staticmethod
+    def bump_counter(counter, by):
+        counter.add_(int(by))
+
+    @staticmethod
+    def decode_state_update(q, v, rho, a, slopes):
+        """a[h*B + b] += q[b, h] . rho[b, h];  rho[b, h] = (rho[b, h] + q[b, h]^T v[b]) * exp(-slope_h)."""
+        B, H, Np, D = rho.shape
+        qf = q.float().view(B, H, Np)
+        a.view(H, B, D).add_(torch.einsum("bhn,bhnd->hbd", qf, rho))
+        rho.add_(qf.unsqueeze(-1) * v.float().view(B, 1, 1, D))
+        if slopes is not None:
+            rho.mul_(torch.exp(-slopes.float()).view(1, H, 1, 1))
+
+
+def _rotate_by_table(x: torch.Tensor, table: torch.Tensor, T: int, n_per_head: int) -> torch.Tensor:
+    """RoPE with (cos, sin) read from the fp16 pair table the kernels use ([T, n_per_head] viewed as
+    bf16: element 2i = cos, 2i+1 = sin of pair i): row m uses table row m % T, column n the pair of
+    n % n_per_head. The positions are whatever the table was built for."""
+    M, N = x.shape
+    tab = table.view(torch.float16).float()
+    rows = torch.arange(M, device=x.device) % T
+    pair = (torch.arange(N, device=x.device) % n_per_head) // 2
+    cos, sin = tab[rows][:, 2 * pair], tab[rows][:, 2 * pair + 1]
+    pairs = x.reshape(M, -1, 2)
+    rotated = torch.stack((-pairs[..., 1], pairs[..., 0]), dim=-1).reshape(M, N)
+    return x * cos + rotated * sin
+
+
 def _gemm(a, b, **kw):
     for k in ("peer_ptrs", "peer_rows", "peer_rank"):      # multi-GPU routing of the output: not emulated
         kw.pop(k, None)
+    flags = kw.get("flags", 0)
+    if kw.get("epi", G.EPI_STORE) == G.EPI_RELU and (flags & G.F_ROPE) and (flags & G.F_TABLE) \
+            and tuple(kw.get("nz", (1, 1))) == (1, 1):
+        # the rotation comes from the table (which carries the positions), not from pos0
+        out1 = kw.pop("out1")
+        G.gemm_reference(a, b, **{**kw, "flags": flags & ~(G.F_ROPE | G.F_TABLE), "out1": None})
+        x = kw["out0"][:kw["M"], :kw["N"]].float()
+        out1[:kw["M"], :kw["N"]] = _rotate_by_table(x, kw["in0"], kw.get("T", 1), kw.get("n_per_head", 1)).to(out1.dtype)
+        return
     G.gemm_reference(a, b, **kw)
 
 
@@ -107,12 +165,13 @@ def enable(on: bool = True) -> None:
     from . import fused_bdh
     if on == _state["on"]:
         return
+    from . import native
     if on:
-        _state["saved"] = (fused_bdh.ops, fused_bdh.G.gemm)
-        fused_bdh.ops = TorchOps
-        fused_bdh.G.gemm = _gemm
+        _state["saved"] = (fused_bdh.ops, native.ops, G.gemm)
+        fused_bdh.ops = native.ops = TorchOps          # the decode engine reads `native.ops` at call time
+        G.gemm = _gemm
     else:
-        fused_bdh.ops, fused_bdh.G.gemm = _state.pop("saved")
+        fused_bdh.ops, native.ops, G.gemm = _state.pop("saved")
     _state["on"] = on
 
 

@@ -89,3 +89,70 @@ def test_recompute_modes_and_dropout():
         d(tok, tgt).backward()
         for n, p in d.named_parameters():
             assert torch.allclose(g_saved[n], p.grad, rtol=1e-4, atol=1e-6), n
+
+
+# ---- the decode engine's step, launch by launch ---------------------------------------------------
+def _decode_model(rot):
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
+                      rotary_embedding=rot)).eval()
+    with torch.no_grad():
+        m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+        for p in m.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    return m
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_decode_engine_step_teacher_forced(rot):
+    from burn_dragon_b200.engine import decode_engine as DE
+    from burn_dragon_b200.engine import generation as GEN
+    m = _decode_model(rot)
+    prompt = torch.randint(0, 256, (3, 64))
+    with emulate.kernel_path():
+        eng = DE.attach(m)
+        assert eng.can_run(prompt, GEN.GenerationSettings(10, greedy=True))
+        out = GEN.generate_tokens(m, prompt, settings=GEN.GenerationSettings(10, 1.0, 40, seed=5))
+        assert out.shape == (3, 74) and torch.equal(out[:, :64], prompt)
+        last_logits, last_state = eng.last_logits.clone(), eng.last_state
+    st = m.init_state()
+    with torch.no_grad():
+        ref = m.forward_with_state(out, st, mode="recurrent")[:, -1]
+    assert last_state.position == st.position == 74
+    assert _rel(last_logits, ref) < 0.08
+    for a, b in zip(last_state.layers, st.layers):
+        assert _rel(a.rho, b.rho) < 0.05
+
+
+def test_decode_engine_chunks_streams_and_sessions():
+    from burn_dragon_b200.data.tokenizer import ByteTokenizer
+    from burn_dragon_b200.engine import decode_engine as DE
+    from burn_dragon_b200.engine import generation as GEN
+    from burn_dragon_b200.engine import session as S
+    m = _decode_model("rope")
+    toks = torch.randint(0, 256, (3, 64))
+    s = GEN.GenerationSettings(12, greedy=True)
+    with emulate.kernel_path():
+        eng = DE.attach(m)
+        whole = eng.generate(toks, s)[:, 64:]
+        assert torch.equal(eng.generate(toks[1:2], s)[:, 64:], whole[1:2])      # streams are independent
+        state, last = GEN.prefill_state(m, toks, toks.device)
+        parts, done = [], 0
+        for n in (5, 4, 3):
+            parts.append(eng.continue_from(state, last, s, n, step0=done))
+            last, done = eng.last_logits, done + n
+        assert torch.equal(torch.cat(parts, dim=1), whole) and state.position == 76
+        # a streaming session takes the engine route when it is eligible
+        sess = S.InferenceSession(m, ByteTokenizer(False), "cpu")
+        m.decode_engine = eng
+        prompt = "the quick brown fox jumps over the lazy dog, twice over the dog!"      # 64 bytes
+        assert len(prompt) == 64
+        sess.start_stream(prompt, max_tokens=6, greedy=True)
+        before = eng.last_state
+        text = ""
+        while not sess.done:
+            text += sess.next_chunk(max_tokens=4)
+        assert sess.generated == 6 and eng.last_state is not before          # the engine decoded the chunks
+        ids = torch.tensor([list(prompt.encode())])
+        want = GEN.generate_tokens(m, ids, settings=s.__class__(6, greedy=True))[0, 64:].tolist()
+    assert text == bytes(want).decode("utf-8", errors="replace")
