@@ -35,7 +35,7 @@ class DecodeEngine:
             return False
         if not emulate.active() and (not toks.is_cuda or not native.available()):
             return False
-        if c.n_embd % 64 or c.n_embd > 1024 or c.latent_per_head % 64 or c.vocab_size > 1024 or c.vocab_size % 8:
+        if c.n_embd % 64 or c.n_embd > 1024 or c.latent_per_head % 64 or c.vocab_size > 1024:
             return False
         if c.block_sparse is not None and c.block_sparse.latent.is_sparse():
             return False
@@ -109,7 +109,12 @@ class DecodeEngine:
             buf["mlp"].copy_(buf["a"][:B])
             ops.block_out_fwd(cur, buf["mlp"], nxt)
             cur, nxt = nxt, cur
-        G.gemm(cur, W["lm_head"], M=B, N=d.V, K=d.D, b_mn=True, flags=G.F_OUT_F32, out0=buf["logits"])
+        if d.V % 8 == 0:
+            G.gemm(cur, W["lm_head"], M=B, N=d.V, K=d.D, b_mn=True, flags=G.F_OUT_F32, out0=buf["logits"])
+        else:
+            # the TMA descriptor of the head needs 16-byte rows (V % 8 == 0 in bf16); character
+            # vocabularies rarely have that, and the head is a [B, D] x [D, V] product: library matmul
+            torch.matmul(cur.float(), W["lm_head"].float(), out=buf["logits"])
         ops.bump_counter(buf["pos"], 1)
         ops.bump_counter(buf["step"], 1)
 

@@ -156,3 +156,27 @@ def test_decode_engine_chunks_streams_and_sessions():
         ids = torch.tensor([list(prompt.encode())])
         want = GEN.generate_tokens(m, ids, settings=s.__class__(6, greedy=True))[0, 64:].tolist()
     assert text == bytes(want).decode("utf-8", errors="replace")
+
+
+def test_decode_engine_with_a_vocabulary_that_is_not_a_multiple_of_8():
+    """Character vocabularies (the shipped checkpoint has 69 tokens) decode on the engine: only the
+    LM head leaves the GEMM kernel."""
+    from burn_dragon_b200.engine import decode_engine as DE
+    from burn_dragon_b200.engine import generation as GEN
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=69, dropout=0.0,
+                      rotary_embedding="alibi")).eval()
+    with torch.no_grad():
+        m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+    prompt = torch.randint(0, 69, (2, 64))
+    s = GEN.GenerationSettings(8, greedy=True)
+    with emulate.kernel_path():
+        eng = DE.attach(m)
+        assert eng.can_run(prompt, s)
+        out = GEN.generate_tokens(m, prompt, settings=s)
+        logits = eng.last_logits.clone()
+    st = m.init_state()
+    with torch.no_grad():
+        ref = m.forward_with_state(out, st, mode="recurrent")[:, -1]
+    assert out.shape == (2, 72) and int(out.max()) < 69
+    assert _rel(logits, ref) < 0.08
