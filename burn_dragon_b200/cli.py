@@ -445,7 +445,11 @@ def cmd_serve(args) -> int:
     sess = session.load_model(model_path.read_bytes(), vocab.read_text() if vocab.exists() else None,
                               run_cfg.read_text() if run_cfg.exists() else None, args.device)
     print(f"serving {model_path} (checkpoint {epoch}) on http://{args.host}:{args.port} [{sess.device}]", flush=True)
-    server.serve(sess, args.host, args.port)
+    pool_settings = None
+    if args.pool_slots > 0:
+        from .engine import generation as GEN
+        pool_settings = GEN.GenerationSettings(None, args.temperature, args.top_k, greedy=args.greedy, seed=0)
+    server.serve(sess, args.host, args.port, pool_slots=args.pool_slots, pool_settings=pool_settings)
     return 0
 
 
@@ -528,6 +532,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--device", default=None)
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--pool-slots", type=int, default=0,
+                   help="continuous batching: this many streams share one decode step (0 = one request at a time)")
+    p.add_argument("--temperature", type=float, default=1.0, help="sampling settings of the pooled decode step")
+    p.add_argument("--top-k", type=int, default=None)
+    p.add_argument("--greedy", action="store_true")
     p.set_defaults(fn=cmd_serve)
 
     p = sub.add_parser("bench")

@@ -78,14 +78,18 @@ class DecodeEngine:
         ops.sample_tokens(buf["logits"], buf["tok"], float(settings.temperature), int(settings.top_k or 0),
                           bool(settings.greedy), seed, 0, buf["step"])
         ops.embed_ln_fwd(buf["tok"], W["embed"], buf["cur"])
+        per_stream = buf["pos"].numel() > 1        # a pool of streams at different positions (stream_pool.py)
         if d.rot == "rope":
-            ops.rope_table_step(buf["pos"], d.freqs, buf["table"])
+            if per_stream:
+                buf["table"].copy_(G.rope_table_rows(buf["pos"], d.freqs))     # one table row per stream
+            else:
+                ops.rope_table_step(buf["pos"], d.freqs, buf["table"])
         cur, nxt = buf["cur"], buf["nxt"]
         for l in range(d.L):
             if d.rot == "rope":
                 G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, flags=G.F_ROPE | G.F_TABLE,
-                       in0=buf["table"], out0=buf["x"], out1=buf["q"], theta=d.theta, T=1, n_per_head=d.N,
-                       freqs=d.freqs)
+                       in0=buf["table"], out0=buf["x"], out1=buf["q"], theta=d.theta, T=buf["table"].shape[0],
+                       n_per_head=d.N, freqs=d.freqs)       # row m reads table row m % T
                 q = buf["q"]
             elif d.rot == "pope":
                 G.gemm(cur, W["encoder"], M=B, N=d.N, K=d.D, nz=(d.H, 1), b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0),
@@ -115,7 +119,10 @@ class DecodeEngine:
             # the TMA descriptor of the head needs 16-byte rows (V % 8 == 0 in bf16); character
             # vocabularies rarely have that, and the head is a [B, D] x [D, V] product: library matmul
             torch.matmul(cur.float(), W["lm_head"].float(), out=buf["logits"])
-        ops.bump_counter(buf["pos"], 1)
+        if per_stream:
+            buf["pos"].add_(1)
+        else:
+            ops.bump_counter(buf["pos"], 1)
         ops.bump_counter(buf["step"], 1)
 
     # ---- public ------------------------------------------------------------------------------------

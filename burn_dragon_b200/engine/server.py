@@ -10,6 +10,7 @@ chunks over HTTP). Standard library only.
                      "greedy": false, "seed": 1, "stream": true, "chunk_tokens": 4}
          stream=false -> {"text": "...", "tokens": 200}
          stream=true  -> application/x-ndjson, one {"text": "..."} line per chunk, then {"done": true, "tokens": n}
+    With `--pool-slots N` concurrent single-prompt requests are decoded together (continuous batching).
     "prompt" may be a list of equally long strings: the streams are decoded together (one recurrent
     state each) and "text" becomes a list.
 
@@ -29,9 +30,26 @@ from .session import InferenceSession
 MAX_BODY = 1 << 20
 
 
-def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080) -> ThreadingHTTPServer:
+def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080, pool_slots: int = 0,
+                pool_settings=None) -> ThreadingHTTPServer:
+    """`pool_slots > 0` adds continuous batching (engine/stream_pool.py): single-prompt requests whose
+    sampling settings are the pool's (`pool_settings`: temperature, top_k, greedy, seed; default greedy
+    off, temperature 1) share one batched decode step; anything else takes the exclusive path."""
     lock = threading.Lock()
-    stats = {"requests": 0, "errors": 0, "tokens": 0, "busy_s": 0.0}
+    stats = {"requests": 0, "errors": 0, "tokens": 0, "busy_s": 0.0, "pooled": 0}
+    scheduler = None
+    if pool_slots > 0:
+        from . import generation as GEN
+        from .stream_pool import PoolScheduler, StreamPool
+        ps = pool_settings or GEN.GenerationSettings(None, 1.0, None, seed=0)
+        scheduler = PoolScheduler(StreamPool(session.model, pool_slots, ps, session.device), session.tokenizer, lock)
+
+    def pool_matches(req) -> bool:
+        ps = scheduler.pool.settings
+        return (isinstance(req.get("prompt"), str) and not req.get("context_window")
+                and float(req.get("temperature", ps.temperature)) == float(ps.temperature)
+                and (req.get("top_k", ps.top_k) or None) == (ps.top_k or None)
+                and bool(req.get("greedy", ps.greedy)) == bool(ps.greedy) and req.get("seed") is None)
 
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
@@ -97,6 +115,8 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
                 stats["errors"] += 1
                 return self._json(400, {"error": str(e)})
             many = isinstance(prompt, list)
+            if scheduler is not None and pool_matches(req):
+                return self._pooled(prompt, kw["max_tokens"], stream)
             with lock:
                 t0 = time.perf_counter()
                 stats["requests"] += 1
@@ -105,6 +125,46 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
                 finally:
                     stats["busy_s"] += time.perf_counter() - t0
                     stats["tokens"] += session.generated * (len(prompt) if many else 1)
+
+        def _pooled(self, prompt, max_tokens, stream):
+            """The request joins the shared decode step; text arrives piece by piece from the scheduler."""
+            t0 = time.perf_counter()
+            stats["requests"] += 1
+            stats["pooled"] += 1
+            try:
+                ids = session.tokenizer.encode(prompt)
+                if not ids:
+                    raise ValueError("prompt must contain at least one token")
+                h = scheduler.submit(ids, max_tokens)
+            except (ValueError, KeyError, TimeoutError) as e:
+                stats["errors"] += 1
+                return self._json(503 if isinstance(e, TimeoutError) else 400, {"error": str(e)})
+            try:
+                if not stream:
+                    text = ""
+                    while True:
+                        piece = h.queue.get()
+                        if piece is None:
+                            break
+                        text += piece
+                    return self._json(200, {"text": text, "tokens": h.tokens})
+                self.send_response(200)
+                self.send_header("Content-Type", "application/x-ndjson")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+                try:
+                    while True:
+                        piece = h.queue.get()
+                        if piece is None:
+                            break
+                        self._chunk((json.dumps({"text": piece}) + "\n").encode())
+                    self._chunk((json.dumps({"done": True, "tokens": h.tokens}) + "\n").encode())
+                    self.wfile.write(b"0\r\n\r\n")
+                except (BrokenPipeError, ConnectionResetError):
+                    h.remaining = 0          # the client went away: the stream leaves the pool at the next step
+            finally:
+                stats["busy_s"] += time.perf_counter() - t0
+                stats["tokens"] += h.tokens
 
         def _generate(self, prompt, kw, chunk_tokens, stream, many):
             try:
@@ -132,12 +192,14 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
             except (BrokenPipeError, ConnectionResetError):
                 pass        # the client went away: drop the stream, keep serving
 
-    return ThreadingHTTPServer((host, port), Handler)
+    srv = ThreadingHTTPServer((host, port), Handler)
+    srv.scheduler = scheduler
+    return srv
 
 
 def serve(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080,
-          ready: Optional[threading.Event] = None) -> None:
-    srv = make_server(session, host, port)
+          ready: Optional[threading.Event] = None, pool_slots: int = 0, pool_settings=None) -> None:
+    srv = make_server(session, host, port, pool_slots, pool_settings)
     if ready is not None:
         ready.set()
     try:
@@ -145,4 +207,6 @@ def serve(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080,
     except KeyboardInterrupt:
         pass
     finally:
+        if srv.scheduler is not None:
+            srv.scheduler.stop()
         srv.server_close()

@@ -86,6 +86,14 @@ def rope_table(pos0: int, T: int, pair_freqs: torch.Tensor) -> torch.Tensor:
     return tab.view(torch.bfloat16)
 
 
+def rope_table_rows(positions: torch.Tensor, pair_freqs: torch.Tensor) -> torch.Tensor:
+    """`rope_table` for an arbitrary position per row (positions [R] -> bf16-viewed fp16 [R, 2*pairs]):
+    a decode step over streams that sit at different positions passes one row per stream."""
+    ph = rot_phases(positions, pair_freqs)
+    tab = torch.stack((ph.cos(), ph.sin()), dim=-1).to(torch.float16).reshape(positions.shape[0], -1)
+    return tab.view(torch.bfloat16)
+
+
 def _hash32(h: torch.Tensor) -> torch.Tensor:
     m = 0xFFFFFFFF
     h = h ^ (h >> 16)

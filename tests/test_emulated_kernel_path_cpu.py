@@ -180,3 +180,85 @@ def test_decode_engine_with_a_vocabulary_that_is_not_a_multiple_of_8():
         ref = m.forward_with_state(out, st, mode="recurrent")[:, -1]
     assert out.shape == (2, 72) and int(out.max()) < 69
     assert _rel(logits, ref) < 0.08
+
+
+@pytest.mark.parametrize("rot", ["rope", "alibi"])
+def test_stream_pool_joins_and_leaves_between_steps(rot):
+    """Continuous batching: streams with prompts of different lengths join a pool at different times;
+    each one's greedy tokens equal what it produces alone."""
+    from burn_dragon_b200.engine import decode_engine as DE
+    from burn_dragon_b200.engine import generation as GEN
+    from burn_dragon_b200.engine.stream_pool import StreamPool
+    m = _decode_model(rot)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 256, (1, n), generator=g) for n in (64, 128, 64)]
+    s = GEN.GenerationSettings(64, greedy=True)
+    with emulate.kernel_path():
+        eng = DE.attach(m)
+        alone = [eng.generate(p, GEN.GenerationSettings(8, greedy=True))[0, p.shape[1]:].tolist() for p in prompts]
+        pool = StreamPool(m, slots=4, settings=s, device="cpu")
+        got = {0: [], 1: [], 2: []}
+        a = pool.add(prompts[0])
+        for _ in range(3):                               # stream 0 runs alone for three steps
+            got[0].append(int(pool.step()[a]))
+        b = pool.add(prompts[1])                         # a longer prompt joins: positions now differ
+        for _ in range(5):
+            t = pool.step()
+            got[0].append(int(t[a])); got[1].append(int(t[b]))
+        pool.release(a)                                  # stream 0 is done; its slot is reused
+        c = pool.add(prompts[2])
+        assert c == a and pool.free_slots() == 2
+        for _ in range(8):
+            t = pool.step()
+            got[1].append(int(t[b])); got[2].append(int(t[c]))
+    assert got[0] == alone[0]
+    assert got[1][:8] == alone[1]
+    assert got[2] == alone[2]
+
+
+def test_http_server_continuous_batching():
+    """Concurrent requests with prompts of different lengths share the pooled decode step; each gets
+    the text it gets when served alone."""
+    import json
+    import threading
+    import urllib.request
+    from burn_dragon_b200.data.tokenizer import ByteTokenizer
+    from burn_dragon_b200.engine import generation as GEN
+    from burn_dragon_b200.engine import server as SV
+    from burn_dragon_b200.engine import session as S
+    m = _decode_model("rope")
+    prompts = ["the quick brown fox ", "jumps over the lazy dog and keeps running far away ", "hello"]
+    with emulate.kernel_path():
+        sess = S.InferenceSession(m, ByteTokenizer(False), "cpu")
+        srv = SV.make_server(sess, "127.0.0.1", 0, pool_slots=2, pool_settings=GEN.GenerationSettings(None, greedy=True))
+        port = srv.server_address[1]
+        threading.Thread(target=srv.serve_forever, daemon=True).start()
+        try:
+            def post(body):
+                req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", data=json.dumps(body).encode(),
+                                             headers={"Content-Type": "application/json"})
+                return urllib.request.urlopen(req, timeout=120).read().decode()
+
+            alone = [json.loads(post(dict(prompt=p, max_tokens=10, greedy=True, seed=1)))["text"] for p in prompts]
+            results = [None] * 3
+
+            def worker(i):
+                if i == 1:      # one of them streams
+                    lines = [json.loads(l) for l in post(dict(prompt=prompts[i], max_tokens=10, greedy=True,
+                                                              stream=True)).splitlines() if l.strip()]
+                    results[i] = "".join(l.get("text", "") for l in lines)
+                else:
+                    results[i] = json.loads(post(dict(prompt=prompts[i], max_tokens=10, greedy=True)))["text"]
+
+            threads = [threading.Thread(target=worker, args=(i,)) for i in range(3)]     # 3 requests, 2 slots
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join(timeout=180)
+            assert results == alone
+            metrics = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=30).read().decode()
+            assert "bdh_requests_total 6" in metrics
+        finally:
+            srv.scheduler.stop()
+            srv.shutdown()
+            srv.server_close()
