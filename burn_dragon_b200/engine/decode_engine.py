@@ -89,7 +89,8 @@ class DecodeEngine:
             if d.rot == "rope":
                 G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, flags=G.F_ROPE | G.F_TABLE,
                        in0=buf["table"], out0=buf["x"], out1=buf["q"], theta=d.theta, T=buf["table"].shape[0],
-                       n_per_head=d.N, freqs=d.freqs)       # row m reads table row m % T
+                       n_per_head=d.N, freqs=d.freqs,       # row m reads table row m % T
+                       tma_epilogue=not per_stream)         # a few rows: the per-thread epilogue, as for T = 1
                 q = buf["q"]
             elif d.rot == "pope":
                 G.gemm(cur, W["encoder"], M=B, N=d.N, K=d.D, nz=(d.H, 1), b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0),
