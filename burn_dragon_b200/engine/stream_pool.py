@@ -214,3 +214,49 @@ class PoolScheduler:
             self.stopping = True
             self.cv.notify_all()
         self.thread.join(timeout=5)
+
+
+def _selftest() -> int:
+    """`python -m burn_dragon_b200.engine.stream_pool`: on the current device, streams with prompts of
+    different lengths join and leave a pool; each one's greedy tokens must equal what it produces
+    alone on the decode engine. Prints PASS / FAIL lines; exit code 0 only when everything matched."""
+    from ..models.bdh import BDH, BDHConfig
+    from ..ops import native
+    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    ok = True
+    for rot in ("rope", "alibi"):
+        torch.manual_seed(0)
+        m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
+                          rotary_embedding=rot)).to(dev).eval()
+        with torch.no_grad():
+            m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, 256, (1, n), generator=g).to(dev) for n in (64, 128, 192)]
+        eng = DecodeEngine(m)
+        alone = [eng.generate(p, GEN.GenerationSettings(8, greedy=True))[0, p.shape[1]:].tolist() for p in prompts]
+        for slots in (4, 64):
+            pool = StreamPool(m, slots, GEN.GenerationSettings(None, greedy=True), dev)
+            got = {0: [], 1: [], 2: []}
+            a = pool.add(prompts[0])
+            for _ in range(3):
+                got[0].append(int(pool.step()[a]))
+            b = pool.add(prompts[1])
+            for _ in range(5):
+                t = pool.step()
+                got[0].append(int(t[a])); got[1].append(int(t[b]))
+            pool.release(a)
+            c = pool.add(prompts[2])
+            for _ in range(8):
+                t = pool.step()
+                got[1].append(int(t[b])); got[2].append(int(t[c]))
+            same = got[0] == alone[0] and got[1][:8] == alone[1] and got[2] == alone[2]
+            status = native.status_code() if dev.type == "cuda" else 0
+            print(f"{'PASS' if same and status == 0 else 'FAIL'} stream_pool {rot} slots={slots} graph={pool.graph is not None} "
+                  f"status={status}", flush=True)
+            ok = ok and same and status == 0
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(_selftest())

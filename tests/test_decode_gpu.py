@@ -152,3 +152,17 @@ def test_session_streams_on_the_decode_engine():
     if vocab.eos_id in want:
         want = want[:want.index(vocab.eos_id)]
     assert text == vocab.decode(want)
+
+
+@pytest.mark.xfail(strict=False, reason="first GPU run of the stream pool: reports, does not gate the tier")
+def test_stream_pool_on_the_device_in_a_child_process():
+    """Continuous batching on the GPU (graph-captured step, per-stream rotary table): streams that join
+    and leave a pool produce the tokens they produce alone. Runs in a child process with its own CUDA
+    context."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "burn_dragon_b200.engine.stream_pool"], capture_output=True, text=True,
+                       timeout=300, cwd=root, env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 4, r.stdout[-1500:] + r.stderr[-1500:]
