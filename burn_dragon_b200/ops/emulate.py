@@ -89,6 +89,28 @@ class TorchOps:
         dx.copy_(torch.where(xf > 0, g, torch.zeros_like(g)).view(M, HN))
 
 
+    # ---- forward_fast attention (ops/rownorm_attention.py) -----------------------------------------
+    @staticmethod
+    def _causal(S, T):
+        rows = torch.arange(S.shape[0], device=S.device) % T
+        return torch.arange(S.shape[1], device=S.device)[None, :] < rows[:, None]        # column s < t
+
+    @staticmethod
+    def rownorm_fwd(S, rnorm, T):
+        m = TorchOps._causal(S, T)
+        x = torch.where(m, S.float(), torch.zeros((), device=S.device))
+        r = x.abs().sum(-1) + R.ROW_NORM_EPS
+        rnorm.copy_(r)
+        S.copy_(torch.where(m, x / r[:, None], S.float()))
+
+    @staticmethod
+    def rownorm_bwd(grad, normed, rnorm, T):
+        m = TorchOps._causal(grad, T)
+        g = torch.where(m, grad.float(), torch.zeros((), device=grad.device))
+        sn = torch.where(m, normed.float(), torch.zeros((), device=grad.device))
+        dot = (g * sn).sum(-1, keepdim=True)
+        grad.copy_(torch.where(m, (g - torch.sign(sn) * dot) / rnorm[:, None], grad.float()))
+
     # ---- decode step (engine/decode_engine.py) ----------------------------------------------------
     @staticmethod
     def sample_tokens(logits, out, temperature, top_k, greedy, seed, step_host, step_dev):

@@ -22,7 +22,8 @@ from . import native
 
 
 def can_run(q: torch.Tensor, v: torch.Tensor) -> bool:
-    if not (q.is_cuda and native.available()):
+    from . import emulate
+    if not emulate.active() and not (q.is_cuda and native.available()):
         return False
     B, H, T, N = q.shape
     D = v.shape[-1]

@@ -262,3 +262,27 @@ def test_http_server_continuous_batching():
             srv.scheduler.stop()
             srv.shutdown()
             srv.server_close()
+
+
+@pytest.mark.parametrize("alibi", [True, False])
+def test_rownorm_attention_op(alibi):
+    """The `forward_fast` attention as its launch sequence (scores with additive bias, row kernels,
+    value product, the four backward products) against the torch statement."""
+    from burn_dragon_b200.ops import reference as R
+    from burn_dragon_b200.ops import rownorm_attention as RA
+    torch.manual_seed(3)
+    B, H, T, N, D = 2, 3, 256, 128, 64
+    q = (torch.randn(B, H, T, N) * 0.3).relu().requires_grad_(True)
+    v = torch.randn(B, 1, T, D).requires_grad_(True)
+    slopes = torch.tensor([0.5, 0.25, 0.125]) if alibi else None
+    g = torch.randn(B, H, T, D)
+    with emulate.kernel_path():
+        assert RA.can_run(q, v)
+        a = RA.attention_rownorm(q, v, slopes)
+        a.backward(g)
+    dq, dv = q.grad.clone(), v.grad.clone()
+    qr = q.detach().to(torch.bfloat16).float().requires_grad_(True)
+    vr = v.detach().to(torch.bfloat16).float().requires_grad_(True)
+    ar = R.attention_rownorm(qr, vr, slopes)
+    ar.backward(g)
+    assert _rel(a, ar) < 2e-2 and _rel(dv, vr.grad) < 3e-2 and _rel(dq, qr.grad) < 3e-2
