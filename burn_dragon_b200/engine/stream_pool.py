@@ -178,6 +178,7 @@ class PoolScheduler:
             self.pool.release(h.slot)
         del self.handles[h.slot]
         h.queue.put(None)
+        self.cv.notify_all()          # (called with the condition held) a slot is free again
 
     def _run(self) -> None:
         while True:
@@ -189,12 +190,16 @@ class PoolScheduler:
                         h.queue.put(None)
                     return
                 for h in [h for h in self.handles.values() if h.remaining <= 0]:
-                    self._finish(h)              # (a request for zero tokens)
-                if not self.handles:
-                    continue
-                with self.gpu_lock:
-                    toks = self.pool.step().tolist()
-                for h in list(self.handles.values()):
+                    self._finish(h)              # a request for zero tokens, or a client that went away
+                seated = list(self.handles.values())
+            if not seated:
+                continue
+            # the step runs outside the condition's lock, so that new requests can queue up for the
+            # device lock meanwhile; a stream seated after this point joins from the next step on
+            with self.gpu_lock:
+                toks = self.pool.step().tolist()
+            with self.cv:
+                for h in seated:
                     t = toks[h.slot]
                     h.remaining -= 1
                     if h.eos_id is not None and t == h.eos_id:
