@@ -74,7 +74,12 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
                         "# TYPE bdh_generated_tokens_total counter\n"
                         f"bdh_generated_tokens_total {stats['tokens']}\n"
                         "# TYPE bdh_generate_busy_seconds_total counter\n"
-                        f"bdh_generate_busy_seconds_total {stats['busy_s']:.6f}\n").encode()
+                        f"bdh_generate_busy_seconds_total {stats['busy_s']:.6f}\n"
+                        "# TYPE bdh_pooled_requests_total counter\n"
+                        f"bdh_pooled_requests_total {stats['pooled']}\n"
+                        "# TYPE bdh_pool_slots_in_use gauge\n"
+                        f"bdh_pool_slots_in_use {0 if scheduler is None else scheduler.pool.slots - scheduler.pool.free_slots()}\n"
+                        ).encode()
                 self.send_response(200)
                 self.send_header("Content-Type", "text/plain; version=0.0.4")
                 self.send_header("Content-Length", str(len(body)))
