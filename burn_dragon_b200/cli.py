@@ -540,7 +540,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.set_defaults(fn=cmd_serve)
 
     p = sub.add_parser("bench")
-    p.add_argument("what", choices=["train", "decode", "reference-shapes", "tiny-cpu"])
+    p.add_argument("what", choices=["train", "decode", "decode-pool", "reference-shapes", "tiny-cpu"])
     p.add_argument("--preset", default="b200_base")
     p.add_argument("--steps", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)

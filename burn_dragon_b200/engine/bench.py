@@ -108,6 +108,29 @@ def bench_decode(preset: str, streams: int, prompt: int, new_tokens: int) -> Dic
     return res
 
 
+def bench_decode_pool(preset: str, streams: int, prompt: int, new_tokens: int) -> Dict:
+    """Continuous-batching decode: a pool of `streams` slots, every slot seated with its own prompt
+    (lengths prompt, prompt + 64, ... so the streams sit at different positions), then `new_tokens`
+    pooled steps, device-timed. Compare with `bench decode` (all streams at one position)."""
+    from .stream_pool import StreamPool
+    cfg = C.load_preset(preset)
+    dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    torch.manual_seed(0)
+    model = build_model(cfg, vocab_size=cfg.model.vocab_size or 256).to(dev).eval()
+    V = model.config.vocab_size
+    res = dict(bench="decode-pool", preset=preset, streams=streams, prompt=prompt, new_tokens=new_tokens)
+    for name, s in (("greedy", GEN.GenerationSettings(None, greedy=True)),
+                    ("t1_topk40", GEN.GenerationSettings(None, 1.0, 40, seed=1))):
+        pool = StreamPool(model, streams, s, dev)
+        for i in range(streams):
+            pool.add(torch.randint(0, V, (1, prompt + 64 * (i % 4)), device=dev))
+        ms = _timed(pool.step, new_tokens, 3)
+        res[name] = dict(step_ms=ms, decode_tokens_per_s=streams / ms * 1e3, graph=pool.graph is not None)
+        del pool
+    res["kernel_status"] = native.status_code()
+    return res
+
+
 def bench_reference_shapes(steps: int, warmup: int) -> Dict:
     dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
     out = dict(bench="reference-shapes", train={}, inference={})
@@ -177,6 +200,8 @@ def run(what: str, preset: str = "b200_base", steps: int = 10, warmup: int = 3, 
         return bench_train(preset, steps, warmup)
     if what == "decode":
         return bench_decode(preset, streams, prompt, new_tokens)
+    if what == "decode-pool":
+        return bench_decode_pool(preset, streams, prompt, new_tokens)
     if what == "reference-shapes":
         return bench_reference_shapes(steps, warmup)
     if what == "tiny-cpu":
