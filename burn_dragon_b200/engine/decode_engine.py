@@ -92,6 +92,16 @@ class DecodeEngine:
                        n_per_head=d.N, freqs=d.freqs,       # row m reads table row m % T
                        tma_epilogue=not per_stream)         # a few rows: the per-thread epilogue, as for T = 1
                 q = buf["q"]
+            elif d.rot == "pope" and per_stream:
+                # one position per stream: the encoder GEMM stops at the ReLU and the rotation
+                # q = softplus(x) * (cos, sin)(2 pi frac(pos f)) is a few elementwise ops on [streams, H*N]
+                G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, out0=buf["x"], theta=d.theta)
+                ph = G.rot_phases(buf["pos"], d.freqs)                       # [streams, N]
+                mag = torch.nn.functional.softplus(buf["x"].float()).view(B, d.H, d.N)
+                qv = buf["q"].view(B, d.H, 2, d.N)                           # per head: [real N | imaginary N]
+                qv[:, :, 0] = mag * ph.cos()[:, None]
+                qv[:, :, 1] = mag * ph.sin()[:, None]
+                q = buf["q"]
             elif d.rot == "pope":
                 G.gemm(cur, W["encoder"], M=B, N=d.N, K=d.D, nz=(d.H, 1), b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0),
                        o1_off=(d.Np, 0, d.N), epi=G.EPI_RELU, flags=G.F_POPE, out0=buf["x"], out1=buf["q"],

@@ -9,9 +9,10 @@ sequence (one CUDA-graph replay on a GPU) whatever mixture of positions the slot
 table carries one row per stream. Slots that nobody uses run along on a zero state; their tokens
 are ignored. Sampling settings belong to the pool (they are baked into the captured step).
 
-PoPE models are not pooled (their rotation takes its position from a scalar argument of the GEMM
-epilogue); they are served one request at a time. The reference decodes one stream, one token at a
-time, with host-side sampling (src/generation.rs:106-129).
+For PoPE (whose GEMM epilogue takes one scalar position) the pooled step ends the encoder GEMM at
+the ReLU and applies the rotation per stream with elementwise ops on the [slots, H*N] activations.
+The reference decodes one stream, one token at a time, with host-side sampling
+(src/generation.rs:106-129).
 """
 from __future__ import annotations
 
@@ -27,8 +28,6 @@ from .decode_engine import DecodeEngine
 class StreamPool:
     def __init__(self, model, slots: int, settings: GEN.GenerationSettings, device=None, use_graph: bool = True):
         c = model.config
-        if c.rotary_embedding == "pope":
-            raise ValueError("PoPE models cannot share a decode step across streams at different positions")
         self.model = model
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
         self.slots = int(slots)
@@ -229,7 +228,7 @@ def _selftest() -> int:
     from ..ops import native
     dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
     ok = True
-    for rot in ("rope", "alibi"):
+    for rot in ("rope", "alibi", "pope"):
         torch.manual_seed(0)
         m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
                           rotary_embedding=rot)).to(dev).eval()

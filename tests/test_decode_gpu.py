@@ -165,4 +165,4 @@ def test_stream_pool_on_the_device_in_a_child_process():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-m", "burn_dragon_b200.engine.stream_pool"], capture_output=True, text=True,
                        timeout=300, cwd=root, env=dict(os.environ, PYTHONPATH=root))
-    assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 4, r.stdout[-1500:] + r.stderr[-1500:]
+    assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 6, r.stdout[-1500:] + r.stderr[-1500:]

@@ -182,7 +182,7 @@ def test_decode_engine_with_a_vocabulary_that_is_not_a_multiple_of_8():
     assert _rel(logits, ref) < 0.08
 
 
-@pytest.mark.parametrize("rot", ["rope", "alibi"])
+@pytest.mark.parametrize("rot", ["rope", "alibi", "pope"])
 def test_stream_pool_joins_and_leaves_between_steps(rot):
     """Continuous batching: streams with prompts of different lengths join a pool at different times;
     each one's greedy tokens equal what it produces alone."""
