@@ -273,6 +273,11 @@ class BDH(nn.Module):
 
     def forward_fast(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None):
         """Row-normalised parallel path (src/model/bdh.rs:96-168). Produces no state."""
+        from ..ops import fused_bdh
+        if fused_bdh.can_run(self, tokens, None):
+            if targets is not None:
+                return fused_bdh.loss(self, tokens, targets, fast=True)
+            return fused_bdh.forward_logits(self, tokens, None, fast=True)
         logits = self._forward_torch(tokens, None, "fast")
         if targets is not None:
             return R.cross_entropy_mean(logits, targets)

@@ -69,8 +69,9 @@ class _Dims:
             self._table = (pos0, G.rope_table(pos0, self.T, self.freqs))
         return self._table[1]
 
-    def __init__(self, model, B, T):
+    def __init__(self, model, B, T, fast: bool = False):
         self._table = None
+        self.fast = bool(fast)     # `forward_fast` semantics: additive bias + L1 row normalisation, no state
         self.comm = None           # set by the neuron-sharded tensor-parallel wrapper
         c = model.config
         self.B, self.T, self.M = B, T, B * T
@@ -166,8 +167,18 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, out0=x, theta=d.theta)
 
     S = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)   # tiles above the diagonal stay zero
-    G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
-           epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
+    rnorm = None
+    if d.fast:
+        # forward_fast (src/model/attention.rs:142-175): S = tril(q q^T, -1) + m_h (s - t), rows L1-normalised
+        if d.comm is not None or d.cp is not None or rho_in is not None:
+            raise NotImplementedError("the row-normalised path has no state and is not sharded")
+        G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
+               epi=G.EPI_CAUSAL, flags=G.F_BIAS if d.slopes is not None else 0, slopes=d.slopes, causal_tiles=1, out0=S)
+        rnorm = torch.empty(B * H * T, device=dev, dtype=torch.float32)
+        ops.rownorm_fwd(S, rnorm, T)
+    else:
+        G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
+               epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
     comm = d.comm
     carry_flags = G.F_ROWDECAY if d.slopes is not None else 0
     cp = d.cp
@@ -228,7 +239,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         mlp = comm.end(buf, bf16=True)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
-    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed)
+    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed, rnorm=rnorm)
     return out, saved, rho_out
 
 
@@ -269,12 +280,23 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     del dy
     da = _bf16(H * M, D, dev)
     ops.layernorm_bwd(a, dlna, da, False)
-    # attention: Gs = causal(dA V^T) + causal(dA V^T)^T with the decay mask
-    Gs = _bf16(B * H * T, T, dev)
-    G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
-           epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=Gs)
-    G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
-           epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
+    if d.fast:
+        # through the row normalisation: dS = (tril(dA V^T) - sign(Sn) sum(tril(dA V^T) Sn)) / r, then
+        # q is both query and key: Gs = dS + dS^T
+        Gl = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)
+        G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
+               epi=G.EPI_CAUSAL, causal_tiles=1, out0=Gl)
+        ops.rownorm_bwd(Gl, S, sv["rnorm"], T)
+        Gl3 = Gl.view(B * H, T, T)
+        Gs = (Gl3 + Gl3.transpose(1, 2)).reshape(B * H * T, T)
+        del Gl, Gl3
+    else:
+        # attention: Gs = causal(dA V^T) + causal(dA V^T)^T with the decay mask
+        Gs = _bf16(B * H * T, T, dev)
+        G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
+               epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=Gs)
+        G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
+               epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
     # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h
     if comm is None:
         part, pflags, pkw = dcur, G.F_OUT_F32 | G.F_ACCUM, {}
@@ -384,9 +406,9 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int
 
 
 @torch.no_grad()
-def forward_logits(model, tokens: torch.Tensor, state) -> torch.Tensor:
+def forward_logits(model, tokens: torch.Tensor, state, fast: bool = False) -> torch.Tensor:
     B, T = tokens.shape
-    d = _Dims(model, B, T)
+    d = _Dims(model, B, T, fast)
     W = _weights(model)
     cur, _ = _stack_forward(model, d, W, tokens, state, save=False, recompute=0)
     return _head_logits(d, W, cur).view(B, T, d.V)
@@ -394,9 +416,9 @@ def forward_logits(model, tokens: torch.Tensor, state) -> torch.Tensor:
 
 class _FusedLoss(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, tokens, targets, embed_w, encoder, encoder_v, decoder, lm_head, model):
+    def forward(ctx, tokens, targets, embed_w, encoder, encoder_v, decoder, lm_head, model, fast=False):
         B, T = tokens.shape
-        d = _Dims(model, B, T)
+        d = _Dims(model, B, T, fast)
         W = _weights(model)
         recompute = recompute_count(model, d)
         model._recomputed_layers = recompute
@@ -438,13 +460,14 @@ class _FusedLoss(torch.autograd.Function):
         ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)
         s = grad_out.to(torch.float32)
         return (None, None, g_emb * s, grads["encoder"] * s, grads["encoder_v"] * s, grads["decoder"] * s,
-                g_head * s, None)
+                g_head * s, None, None)
 
 
-def loss(model, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-    """Mean cross-entropy of the canonical forward, differentiable w.r.t. the model parameters."""
+def loss(model, tokens: torch.Tensor, targets: torch.Tensor, fast: bool = False) -> torch.Tensor:
+    """Mean cross-entropy of the canonical forward (or, with `fast`, of the row-normalised
+    `forward_fast` function), differentiable w.r.t. the model parameters."""
     return _FusedLoss.apply(tokens, targets, model.embed.weight, model.encoder, model.encoder_v, model.decoder,
-                            model.lm_head, model)
+                            model.lm_head, model, fast)
 
 
 from . import emulate  # noqa: E402  (last: with BDH_EMULATE_KERNELS=1 it re-points `ops` and `G.gemm` defined above)

@@ -286,3 +286,30 @@ def test_rownorm_attention_op(alibi):
     ar = R.attention_rownorm(qr, vr, slopes)
     ar.backward(g)
     assert _rel(a, ar) < 2e-2 and _rel(dv, vr.grad) < 3e-2 and _rel(dq, qr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_forward_fast_on_the_kernel_path(rot):
+    """`forward_fast` (bias + row normalisation) as a kernel-path launch sequence, forward and backward,
+    against its torch definition."""
+    m = _model(rot)
+    tok, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    with emulate.kernel_path():
+        logits_k = m.forward_fast(tok).float()
+        loss_k = m.forward_fast(tok, tgt)
+        loss_k.backward()
+    gk = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    logits_t = m.forward_fast(tok)
+    loss_t = m.forward_fast(tok, tgt)
+    loss_t.backward()
+    assert _rel(logits_k, logits_t) < 0.05
+    assert abs(loss_k.item() - loss_t.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert _cos(gk[n], p.grad) > 0.99 and _rel(gk[n], p.grad) < 0.15, (n, _cos(gk[n], p.grad), _rel(gk[n], p.grad))
+    # With ALiBi it is a different function from the canonical one (additive bias instead of decay).
+    # Without it the two coincide: a positive per-row scale of the scores cancels in the LayerNorm
+    # that follows the attention.
+    with torch.no_grad():
+        diff = _rel(logits_t, m(tok, mode="parallel"))
+    assert diff > 1e-2 if rot == "alibi" else diff < 1e-3
