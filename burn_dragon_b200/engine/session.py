@@ -64,6 +64,7 @@ class InferenceSession:
         self.printers: List[GEN.StreamPrinter] = []
         self.pending: List[List[str]] = []
         self.generator = None
+        self._pool = None
 
     # ---- stream control --------------------------------------------------------------------------
     @property
@@ -74,7 +75,8 @@ class InferenceSession:
     def start_stream(self, prompt: Union[str, Sequence[str]], max_tokens: Optional[int] = 256, temperature: float = 1.0,
                      top_k: Optional[int] = None, greedy: bool = False, seed: Optional[int] = None,
                      context_window: Optional[int] = None) -> None:
-        """Prefill. `prompt` is one string or a list of equally long strings (one stream each).
+        """Prefill. `prompt` is one string or a list of strings (one stream each; prompts of different
+        token counts need a model / device the decode engine takes, and are decoded by a stream pool).
         `context_window` keeps only the last tokens of the prompt (the sliding context strategy,
         src/generation.rs:214-218)."""
         self._reset()
@@ -84,10 +86,10 @@ class InferenceSession:
             ids = [i[-int(context_window):] for i in ids]
         if not ids or any(len(i) == 0 for i in ids):
             raise ValueError("prompt must contain at least one token")
-        if len({len(i) for i in ids}) != 1:
-            raise ValueError("all prompts of one session call must have the same number of tokens")
-        toks = torch.tensor(ids, dtype=torch.int64, device=self.device)
         eos = getattr(self.tokenizer, "eos_id", None)
+        if len({len(i) for i in ids}) != 1:
+            return self._start_pooled(ids, max_tokens, temperature, top_k, greedy, seed, eos)
+        toks = torch.tensor(ids, dtype=torch.int64, device=self.device)
         self.settings = GEN.GenerationSettings(GEN.normalize_max_tokens(max_tokens), temperature, top_k, greedy=greedy,
                                                seed=seed, eos_id=eos)
         if self.settings.max_new_tokens is None and eos is None:
@@ -99,6 +101,27 @@ class InferenceSession:
         self.pending = [[] for _ in ids]
         self.printers = [GEN.StreamPrinter(self.tokenizer, write=self.pending[i].append) for i in range(len(ids))]
 
+    def _start_pooled(self, ids, max_tokens, temperature, top_k, greedy, seed, eos) -> None:
+        """Prompts of different lengths: every stream is prefilled on its own and seated in a stream
+        pool (engine/stream_pool.py) whose step carries one position per stream."""
+        from .stream_pool import StreamPool
+        n = GEN.normalize_max_tokens(max_tokens)
+        if n is None:
+            raise ValueError("max_tokens is required for prompts of different lengths")
+        self.settings = GEN.GenerationSettings(n, temperature, top_k, greedy=greedy, seed=seed, eos_id=eos)
+        try:
+            self._pool = StreamPool(self.model, len(ids), self.settings, self.device)
+        except ValueError as e:
+            raise ValueError("prompts of one session call must have the same number of tokens on this model / "
+                             f"device ({e})") from None
+        for i in ids:
+            self._pool.add(torch.tensor([i], dtype=torch.int64, device=self.device))
+        self.logits = self._pool.buf["logits"]
+        self.state = True              # (no single ModelState: the pool owns one state row per stream)
+        self.finished = torch.zeros(len(ids), dtype=torch.bool, device=self.device)
+        self.pending = [[] for _ in ids]
+        self.printers = [GEN.StreamPrinter(self.tokenizer, write=self.pending[i].append) for i in range(len(ids))]
+
     # ---- state snapshots ---------------------------------------------------------------------------
     def snapshot(self) -> Dict:
         """Copy of everything a stream is: the recurrent state (constant size, whatever the length of
@@ -106,6 +129,8 @@ class InferenceSession:
         from this point - e.g. prefill a long shared prefix once and branch many completions off it."""
         if self.state is None:
             raise RuntimeError("call start_stream first")
+        if self._pool is not None:
+            raise RuntimeError("snapshots are per stream: start the prompts of different lengths one by one")
         return dict(position=self.state.position,
                     rho=[None if l.rho is None else l.rho.detach().clone() for l in self.state.layers],
                     logits=self.logits.detach().clone(), generated=self.generated, finished=self.finished.clone(),
@@ -154,7 +179,14 @@ class InferenceSession:
             raise RuntimeError("call start_stream first")
         s = self.settings
         eng = getattr(self.model, "decode_engine", None)
-        if eng is not None and s.max_new_tokens is not None and eng.can_run(self.logits, s):
+        if self._pool is not None:
+            for _ in range(max(1, int(max_tokens))):
+                if self.done or self.generated >= s.max_new_tokens:
+                    self.finished.fill_(True)
+                    break
+                self._take(self._pool.step().tolist())
+                self.generated += 1
+        elif eng is not None and s.max_new_tokens is not None and eng.can_run(self.logits, s):
             # GPU: the whole chunk is decoded on the device (sampling included) by replaying the
             # captured decode step; only the chunk's token ids come back to the host
             n = min(max(1, int(max_tokens)), s.max_new_tokens - self.generated)

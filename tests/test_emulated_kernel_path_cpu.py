@@ -313,3 +313,30 @@ def test_forward_fast_on_the_kernel_path(rot):
     with torch.no_grad():
         diff = _rel(logits_t, m(tok, mode="parallel"))
     assert diff > 1e-2 if rot == "alibi" else diff < 1e-3
+
+
+def test_session_with_prompts_of_different_lengths():
+    from burn_dragon_b200.data.tokenizer import ByteTokenizer
+    from burn_dragon_b200.engine import session as S
+    m = _decode_model("rope")
+    prompts = ["short prompt", "a prompt that is quite a bit longer than the other one"]
+    with emulate.kernel_path():
+        sess = S.InferenceSession(m, ByteTokenizer(False), "cpu")
+        sess.start_stream(prompts, max_tokens=7, greedy=True)
+        both = ["", ""]
+        while not sess.done:
+            a, b = sess.next_chunk(3)
+            both[0] += a; both[1] += b
+        assert sess.generated == 7
+        alone = []
+        for p in prompts:
+            sess.start_stream(p, max_tokens=7, greedy=True)
+            t = ""
+            while not sess.done:
+                t += sess.next_chunk(3)
+            alone.append(t)
+    assert both == alone
+    # without an eligible engine (plain CPU) the equal-length rule stays
+    plain = S.InferenceSession(m, ByteTokenizer(False), "cpu")
+    with pytest.raises(ValueError):
+        plain.start_stream(prompts, max_tokens=3)
