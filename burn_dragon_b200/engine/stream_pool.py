@@ -25,11 +25,30 @@ from . import generation as GEN
 from .decode_engine import DecodeEngine
 
 
+def state_bytes_per_stream(config) -> int:
+    """fp32 recurrent state of one stream: L layers x H heads x N' x D."""
+    return 4 * config.n_layer * config.n_head * config.state_latent * config.n_embd
+
+
+def max_slots(model, device, fraction: float = 0.8) -> int:
+    """How many streams fit in `fraction` of the free device memory (the state dominates: 33.5 MB per
+    layer for the base model, 537 MB per layer for the large PoPE one)."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return 1 << 30
+    free, _ = torch.cuda.mem_get_info(device)
+    return int(fraction * free // max(1, state_bytes_per_stream(model.config)))
+
+
 class StreamPool:
     def __init__(self, model, slots: int, settings: GEN.GenerationSettings, device=None, use_graph: bool = True):
         c = model.config
         self.model = model
         self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        fit = max_slots(model, self.device)
+        if int(slots) > fit:
+            raise ValueError(f"{slots} stream slots need {slots * state_bytes_per_stream(c) / 2**30:.1f} GiB of recurrent "
+                             f"state; {fit} fit in the free memory of {self.device}")
         self.slots = int(slots)
         self.settings = settings
         self.seed = int(settings.seed if settings.seed is not None else 0) & 0xFFFFFFFF
