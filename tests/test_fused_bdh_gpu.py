@@ -162,3 +162,23 @@ def test_kernel_logits_against_the_cpp_oracle(rot):
         got = m.forward_with_state(tok, m.init_state())[0].float().cpu()
     want = torch.from_numpy(hostlib.oracle_forward(m, tok[0].tolist()))
     assert _rel(got, want) < 0.05, _rel(got, want)
+
+
+@pytest.mark.xfail(strict=False, reason="first GPU run of the row-normalised mode's backward: reports, does not gate")
+@pytest.mark.parametrize("rot", ["alibi", "rope"])
+def test_forward_fast_training_step_matches_torch(rot):
+    m = _model(rot)
+    tok = torch.randint(0, 256, (2, 128), device="cuda")
+    tgt = torch.randint(0, 256, (2, 128), device="cuda")
+    n0 = native.launch_count()
+    loss_k = m.forward_fast(tok, tgt)
+    loss_k.backward()
+    assert native.launch_count() > n0 and native.status_code() == 0
+    gk = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    m.use_native = False
+    loss_t = m.forward_fast(tok, tgt)
+    loss_t.backward()
+    assert abs(loss_k.item() - loss_t.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert _cos(gk[n], p.grad) > 0.99 and _rel(gk[n], p.grad) < 0.15, (n, _cos(gk[n], p.grad), _rel(gk[n], p.grad))
