@@ -11,6 +11,8 @@ GPU tests compare against the same statements.
         loss = model(tokens, targets)          # ops.fused_bdh, launch by launch, in torch ops
 
 `BDH_EMULATE_KERNELS=1` switches it on for a whole process (the multi-rank self tests use that).
+The reference has no counterpart: its tests run its one code path on the CPU backend
+(tests/model_paths.rs:33-91).
 """
 from __future__ import annotations
 
