@@ -197,9 +197,14 @@ class BDH(nn.Module):
                 a, rho_loc = fn(q, cur, self._slopes(), None)
                 sl = self._slopes()
                 g_T = torch.exp(-sl.to(q.dtype) * q.shape[2]).view(1, -1, 1, 1) if sl is not None else 1.0
-                rho_in, new_rho = self._cp.scan(rho_loc, rho, g_T)
-                if rho_in is not None:
-                    a = a + R.carry_in(q, rho_in, sl)
+                if torch.is_grad_enabled() and rho_loc.requires_grad:
+                    # training: the hand-off is part of the autograd graph (no state leaves the call)
+                    new_rho = None
+                    a = a + R.carry_in(q, self._cp.scan_grad(rho_loc, g_T), sl)
+                else:
+                    rho_in, new_rho = self._cp.scan(rho_loc, rho, g_T)
+                    if rho_in is not None:
+                        a = a + R.carry_in(q, rho_in, sl)
             elif mode == "chunked":
                 a, new_rho = R.linear_attention_chunked(q, cur, self._slopes(), rho)
             else:
@@ -219,10 +224,10 @@ class BDH(nn.Module):
         out = R.layer_norm(res + mlp)
         return out, new_rho, (x, y, xy)
 
-    def _forward_torch(self, tokens, state: Optional[ModelState], mode: str):
+    def _forward_torch(self, tokens, state: Optional[ModelState], mode: str, start: int = 0):
         c = self.config
         cur = R.layer_norm(self.embed(tokens)).unsqueeze(1)          # [B,1,T,D]
-        start = state.position if state is not None else 0
+        start = state.position if state is not None else start
         viz = []
         for l in range(c.n_layer):
             rho = state.layers[l].rho if state is not None else None

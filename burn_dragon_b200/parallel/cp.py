@@ -10,7 +10,10 @@ earlier tokens left behind,
 
     rho_in^r = g^(rT) rho_0 + sum_{r' < r} g^((r-1-r') T) rho_loc^{r'},    a_t += g^t q_t . rho_in^r
 
-so the result equals the single-device forward over the concatenated sequence. After the call
+so the result equals the single-device forward over the concatenated sequence. For training the
+same hand-off is an autograd function (`scan_grad`: the gradient of every later rank's starting
+state flows back to the earlier ranks' segment states), so `loss()` + `reduce_gradients()` give the
+loss and gradients of whole sequences that no single rank holds (torch path of the model). After the call
 every rank holds the state of the whole sequence, so decoding can continue on any of them. The
 message is the state itself (33 MB fp32 per layer for the base model), so this pays when the
 per-rank segment is much longer than the state is wide. The reference has no sequence parallelism
@@ -22,6 +25,38 @@ from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+class _ExclusiveStateScan(torch.autograd.Function):
+    """Differentiable state hand-off. Forward: all-gather the segment states and return what this rank
+    starts from, sum_{r' < r} g^((r-1-r') T) rho_loc^{r'}. Backward: the gradient of every later
+    rank's starting state flows back to this rank's segment state with the same decay weights
+    (one all-gather of the incoming gradients)."""
+
+    @staticmethod
+    def forward(ctx, rho_loc, g_T, rank, world, group):
+        parts = [torch.empty_like(rho_loc) for _ in range(world)]
+        dist.all_gather(parts, rho_loc.contiguous(), group=group)
+        run = torch.zeros_like(rho_loc)
+        out = run
+        for r in range(world):
+            if r == rank:
+                out = run
+            run = run * g_T + parts[r]
+        ctx.g_T, ctx.rank, ctx.world, ctx.group = g_T, rank, world, group
+        return out.clone()
+
+    @staticmethod
+    def backward(ctx, grad_in):
+        grads = [torch.empty_like(grad_in) for _ in range(ctx.world)]
+        dist.all_gather(grads, grad_in.contiguous(), group=ctx.group)
+        # rho_in^r contains g^((r-1-rank) T) rho_loc^rank for every r > rank
+        acc = torch.zeros_like(grad_in)
+        w = 1.0
+        for r in range(ctx.rank + 1, ctx.world):
+            acc = acc + grads[r] * w
+            w = w * ctx.g_T
+        return acc, None, None, None, None
 
 
 class ContextParallel:
@@ -45,6 +80,33 @@ class ContextParallel:
                 rho_in = run
             run = parts[r] if run is None else run * g_T + parts[r]
         return rho_in, run
+
+    def scan_grad(self, rho_loc: torch.Tensor, g_T) -> torch.Tensor:
+        """Differentiable `scan` for training (no state before the sequence): the state this rank
+        starts from, as a function of every earlier rank's segment state."""
+        return _ExclusiveStateScan.apply(rho_loc, g_T, self.rank, self.world, self.group)
+
+    def loss(self, tokens_local: torch.Tensor, targets_local: torch.Tensor) -> torch.Tensor:
+        """Training loss of this rank's segment of sequences that are split over the ranks (rank r
+        holds tokens [r*T, (r+1)*T) of every sequence). The gradients of later segments reach earlier
+        ranks through the state hand-off; call `reduce_gradients()` after `backward()`. The mean over
+        the ranks' losses is the loss of the whole sequences. Runs the torch path of the model."""
+        from ..ops import reference as R
+        model = self.model
+        model._cp = self
+        try:
+            logits = model._forward_torch(tokens_local, None, "parallel", start=self.rank * tokens_local.shape[1])
+        finally:
+            model._cp = None
+        return R.cross_entropy_mean(logits, targets_local)
+
+    def reduce_gradients(self) -> None:
+        """Average the parameter gradients over the group (every rank then holds the gradient of the
+        whole-sequence mean loss)."""
+        for p in self.model.parameters():
+            if p.grad is not None:
+                dist.all_reduce(p.grad, group=self.group)
+                p.grad.div_(self.world)
 
     # ---- public ------------------------------------------------------------------------------------
     @torch.no_grad()

@@ -277,3 +277,38 @@ def case_ckpt(dev):
         notes.append(kind)
         dist.barrier()
     return " ".join(notes)
+
+
+def case_cp_train(dev):
+    """Context-parallel training: sequences split over the ranks, loss and every parameter gradient equal
+    the single-process ones over the whole sequences (the gradients of later segments reach earlier
+    ranks through the differentiable state hand-off)."""
+    from .cp import ContextParallel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    T = 32
+    notes = []
+    for rot in ("alibi", "rope", "pope"):
+        m = _bdh(dev, rot)
+        m.use_native = False                    # this is a torch-path feature
+        for p in m.parameters():
+            dist.broadcast(p.data, src=0)
+        g = torch.Generator().manual_seed(9)
+        data = torch.randint(0, 256, (2, world * T + 1), generator=g).to(dev)
+        x, y = data[:, :-1], data[:, 1:]
+        m.zero_grad()
+        want = m(x, y, mode="parallel")
+        want.backward()
+        ref = {n: p.grad.clone() for n, p in m.named_parameters()}
+        m.zero_grad()
+        cp = ContextParallel(m)
+        sl = slice(rank * T, (rank + 1) * T)
+        loss = cp.loss(x[:, sl].contiguous(), y[:, sl].contiguous())
+        loss.backward()
+        cp.reduce_gradients()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        assert abs(total.item() / world - want.item()) < 1e-5, (rot, total.item() / world, want.item())
+        for n, p in m.named_parameters():
+            assert _rel(p.grad, ref[n]) < 1e-4, (rot, n, _rel(p.grad, ref[n]))
+        notes.append(rot)
+    return " ".join(notes)

@@ -181,3 +181,10 @@ def test_parallel_wrappers_over_the_emulated_kernel_path(case):
     replaced by its fp32 statement, BDH_EMULATE_KERNELS=1): the tensor-parallel reductions between the
     GEMM launches, the context-parallel state exchange and carry-in, sharded checkpoints."""
     run_ranks(case, env={"BDH_EMULATE_KERNELS": "1"})
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_context_parallel_training_gradients(n):
+    """Sequences split over the ranks: loss and all parameter gradients equal the single-process ones
+    (differentiable state hand-off, every positional mode)."""
+    run_ranks("cp_train", n=n)
