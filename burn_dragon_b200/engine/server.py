@@ -205,6 +205,10 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
 def serve(session: InferenceSession, host: str = "127.0.0.1", port: int = 8080,
           ready: Optional[threading.Event] = None, pool_slots: int = 0, pool_settings=None) -> None:
     srv = make_server(session, host, port, pool_slots, pool_settings)
+    if threading.current_thread() is threading.main_thread():
+        import signal
+        # SIGTERM (what a process supervisor sends) ends the accept loop; streams in flight finish
+        signal.signal(signal.SIGTERM, lambda *_: threading.Thread(target=srv.shutdown, daemon=True).start())
     if ready is not None:
         ready.set()
     try:
