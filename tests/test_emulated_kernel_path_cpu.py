@@ -340,3 +340,15 @@ def test_session_with_prompts_of_different_lengths():
     plain = S.InferenceSession(m, ByteTokenizer(False), "cpu")
     with pytest.raises(ValueError):
         plain.start_stream(prompts, max_tokens=3)
+
+
+def test_stream_pool_self_test_entry_runs():
+    """`python -m burn_dragon_b200.engine.stream_pool` (the device self test the GPU tier starts as a
+    child process), here on the emulated path."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "burn_dragon_b200.engine.stream_pool"], capture_output=True, text=True,
+                       timeout=600, cwd=root, env=dict(os.environ, PYTHONPATH=root, BDH_EMULATE_KERNELS="1"))
+    assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 6, r.stdout[-1500:] + r.stderr[-1500:]
