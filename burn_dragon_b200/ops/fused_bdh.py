@@ -374,7 +374,7 @@ def recompute_count(model, d: _Dims) -> int:
         return max(0, min(d.L, r))
     if r == "auto":
         if not torch.cuda.is_available():
-            return 0                      # (emulated path on a CPU: nothing to budget against)
+            return 0                      # (emulated path on a CPU: no device memory to size against)
         free, _ = torch.cuda.mem_get_info()
         free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()   # cached blocks are reusable
         per = layer_activation_bytes(d)

@@ -154,7 +154,7 @@ def test_snapshot_restore_branches_from_a_shared_prefix():
     while not sess.done:
         again += sess.next_chunk()
     assert again == first
-    # branch 2: a fresh budget from the same prefix state, in another session of the same model
+    # branch 2: a fresh token limit from the same prefix state, in another session of the same model
     other = S.load_model(blob, vjson, cjson, device="cpu")
     other.restore(snap, max_tokens=3)
     short = ""
