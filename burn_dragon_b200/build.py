@@ -5,6 +5,11 @@
 one shared object next to the package. nvcc cross-compiles, so this works on a machine without
 a GPU. A content hash of the sources is stored beside the library; `ensure_built()` rebuilds
 only when the hash differs, so a prebuilt library copied to another machine is used as is.
+
+`python -m burn_dragon_b200.build --checked` also links `_C_checked.so`: the same sources, with the
+files that include `csrc/debug_bounds.cuh` compiled under `-DBDH_DEBUG_BOUNDS` (data-dependent
+indices are checked and the first violation is recorded; nothing traps). `BDH_CHECKED_KERNELS=1`
+makes `ops.native` load that library instead of `_C.so`.
 """
 from __future__ import annotations
 
@@ -24,6 +29,9 @@ LIB = PKG / "_C.so"
 HOST_LIB = PKG / "_host.so"
 HOST_SRC = CSRC / "host"
 STAMP = PKG / "_C.hash"
+LIB_CHECKED = PKG / "_C_checked.so"
+STAMP_CHECKED = PKG / "_C_checked.hash"
+CHECK_FLAG = "-DBDH_DEBUG_BOUNDS"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -48,7 +56,10 @@ def source_hash() -> str:
     return h.hexdigest()
 
 
-def is_current() -> bool:
+def is_current(checked: bool = False) -> bool:
+    if checked:
+        return (LIB_CHECKED.exists() and STAMP_CHECKED.exists()
+                and STAMP_CHECKED.read_text().strip() == source_hash())
     return (LIB.exists() and HOST_LIB.exists() and STAMP.exists()
             and STAMP.read_text().strip() == source_hash())
 
@@ -68,10 +79,20 @@ def _run(cmd, log: Path):
     return r
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
-    """Compile and link the extension. Returns the path of the shared object."""
-    if not force and is_current():
-        return LIB
+def _instrumented(src: Path) -> bool:
+    """Does this source compile differently under the checked build?"""
+    text = src.read_text()
+    return "debug_bounds.cuh" in text or "BDH_DEBUG_BOUNDS" in text
+
+
+def build(force: bool = False, verbose: bool = True, checked: bool = False) -> Path:
+    """Compile and link the extension. Returns the path of the shared object. `checked` links the
+    bounds-checked variant: the regular objects, except that the instrumented sources are compiled
+    again with the check flag."""
+    if checked:
+        build(force=force, verbose=verbose)           # the regular objects are reused
+    if not force and is_current(checked):
+        return LIB_CHECKED if checked else LIB
     import torch
     from torch.utils import cpp_extension as ce
 
@@ -80,36 +101,47 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     inc = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC}"]
     abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
     nvcc = _nvcc()
-    jobs = []
+    jobs, objects = [], []
     for src in cu:
-        obj = OBJ / (src.stem + ".o")
-        jobs.append(([nvcc, *NVCC_FLAGS, f"-I{CSRC}", "-I/usr/local/cuda/include", "-c", str(src), "-o", str(obj)],
-                     OBJ / (src.stem + ".log"), obj))
+        again = checked and _instrumented(src)
+        obj = OBJ / (src.stem + (".checked.o" if again else ".o"))
+        objects.append(obj)
+        if checked and not again:
+            continue
+        jobs.append(([nvcc, *NVCC_FLAGS, *([CHECK_FLAG] if again else []), f"-I{CSRC}", "-I/usr/local/cuda/include",
+                      "-c", str(src), "-o", str(obj)], OBJ / (obj.stem + ".log")))
     for src in cpp:
         obj = OBJ / (src.stem + ".o")
+        objects.append(obj)
+        if checked:
+            continue
         jobs.append((["g++", "-O2", "-std=c++17", "-fPIC", abi, "-DTORCH_API_INCLUDE_EXTENSION_H", *inc, "-c", str(src),
-                      "-o", str(obj)], OBJ / (src.stem + ".log"), obj))
-    with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-        futs = [ex.submit(_run, cmd, log) for cmd, log, _ in jobs]
+                      "-o", str(obj)], OBJ / (src.stem + ".log")))
+    with cf.ThreadPoolExecutor(max_workers=max(1, min(8, len(jobs)))) as ex:
+        futs = [ex.submit(_run, cmd, log) for cmd, log in jobs]
         for f in futs:
             f.result()
     tlib = Path(torch.__file__).parent / "lib"
     cuda_lib = Path("/usr/local/cuda/lib64")
-    link = ["g++", "-shared", "-o", str(LIB), *[str(o) for _, _, o in jobs], f"-L{tlib}", f"-L{cuda_lib}",
+    lib = LIB_CHECKED if checked else LIB
+    link = ["g++", "-shared", "-o", str(lib), *[str(o) for o in objects], f"-L{tlib}", f"-L{cuda_lib}",
             "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart",
             f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{cuda_lib}"]
-    _run(link, OBJ / "link.log")
-    # host-only helpers: plain C ABI, no torch / CUDA dependency
-    _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", str(HOST_LIB),
-          *[str(p) for p in sorted(HOST_SRC.glob("*.cpp"))]], OBJ / "host.log")
-    STAMP.write_text(source_hash())
+    _run(link, OBJ / ("link_checked.log" if checked else "link.log"))
+    if checked:
+        STAMP_CHECKED.write_text(source_hash())
+    else:
+        # host-only helpers: plain C ABI, no torch / CUDA dependency
+        _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", str(HOST_LIB),
+              *[str(p) for p in sorted(HOST_SRC.glob("*.cpp"))]], OBJ / "host.log")
+        STAMP.write_text(source_hash())
     if verbose:
-        print(f"built {LIB}")
-    return LIB
+        print(f"built {lib}")
+    return lib
 
 
-def ensure_built() -> Path:
-    return build(force=False, verbose=False)
+def ensure_built(checked: bool = False) -> Path:
+    return build(force=False, verbose=False, checked=checked)
 
 
 def ptxas_report() -> str:
@@ -123,6 +155,6 @@ def ptxas_report() -> str:
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv)
+    build(force="--force" in sys.argv, checked="--checked" in sys.argv)
     if "--ptxas" in sys.argv:
         print(ptxas_report())

@@ -164,6 +164,11 @@ int bdh_rank_barrier(const long long* flag_ptrs, int rank, int world, unsigned e
 int bdh_wait_timeout_probe(const unsigned* flag, unsigned value, unsigned long long limit_ns, int* status,
                            cudaStream_t s);
 
+// Checked build (-DBDH_DEBUG_BOUNDS; csrc/debug_bounds.cuh): the first data-dependent index that was
+// out of range in the kernels of rowwise.cu / graph.cu. out5 = {checked build?, site, index, extent, where}.
+int bdh_bounds_record_rowwise(long long* out5, int clear);
+int bdh_bounds_record_graph(long long* out5, int clear);
+
 #ifdef __cplusplus
 }
 #endif

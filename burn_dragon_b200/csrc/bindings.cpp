@@ -167,6 +167,17 @@ void adamw(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, const optio
 
 Tensor status() { return status_word(); }
 
+// int64 [2, 5] on the host: rows = the kernels of rowwise.cu, of graph.cu; columns = {checked build?,
+// site, index, extent, where} of the first out-of-range data-dependent index (csrc/debug_bounds.cuh).
+// Synchronises the current device.
+Tensor bounds_records(bool clear) {
+  Tensor out = at::zeros({2, 5}, at::TensorOptions().dtype(at::kLong));
+  long long* p = reinterpret_cast<long long*>(out.data_ptr<int64_t>());
+  check_rc(bdh_bounds_record_rowwise(p, clear ? 1 : 0), "bounds_record_rowwise");
+  check_rc(bdh_bounds_record_graph(p + 5, clear ? 1 : 0), "bounds_record_graph");
+  return out;
+}
+
 std::vector<long long> as_ptrs(at::IntArrayRef v) { return std::vector<long long>(v.begin(), v.end()); }
 
 // `anchor` only selects the device / stream; the buffers are addressed through the pointer lists.
@@ -318,6 +329,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("adamw(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p16, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale) -> ()");
   m.def("status() -> Tensor");
+  m.def("bounds_records(bool clear) -> Tensor");
   m.def("rownorm_fwd(Tensor(a!) scores, Tensor(b!) rnorm, int T) -> ()");
   m.def("rownorm_bwd(Tensor(a!) grad, Tensor normed, Tensor rnorm, int T) -> ()");
   m.def("allreduce_scale(Tensor anchor, int[] buf_ptrs, int[] flag_ptrs, int mc_ptr, int rank, int world, "
@@ -368,4 +380,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("rope_table_step", &rope_table_step);
   m.impl("bump_counter", &bump_counter);
 }
-TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) { m.impl("status", &status); }
+TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) {
+  m.impl("status", &status);
+  m.impl("bounds_records", &bounds_records);
+}

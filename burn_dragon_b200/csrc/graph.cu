@@ -6,6 +6,7 @@
 // (reference semantics: src/kernel/relu_lowrank.rs:7-37). The reference has no sparse-graph path.
 #include "bdh_kernels.h"
 #include "sm100_ptx.cuh"
+#include "debug_bounds.cuh"
 
 namespace bdh {
 
@@ -24,6 +25,7 @@ graph_spmm_relu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   for (int e = 0; e < ell_width; ++e) {
     const int cb = ell_cols[nb * ell_width + e];
     if (cb < 0) break;
+    BDH_BOUNDS_CHECK(cb, (D + GB - 1) / GB, BOUNDS_GRAPH_COLUMN, static_cast<long long>(nb) * ell_width + e);
     for (int i = threadIdx.x; i < GB * GB; i += G_THREADS) {
       const int r = i / GB, c = i % GB;
       const int m = mb * GB + r, n = nb * GB + r, d = cb * GB + c;
@@ -64,3 +66,7 @@ extern "C" int bdh_graph_spmm_relu(const void* x_bf16, const void* w_bf16, const
                                                              theta);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
+
+// First data-dependent index of this file's kernels that was out of range since the last clear:
+// out = {checked build?, site, index, extent, where} (csrc/debug_bounds.cuh).
+extern "C" int bdh_bounds_record_graph(long long* out5, int clear) { return bdh::bounds_record_read(out5, clear) ? BDH_ERR_LAUNCH : BDH_OK; }

@@ -5,6 +5,7 @@
 // 16-byte vectors, so each row is read once and written once.
 #include "bdh_kernels.h"
 #include "sm100_ptx.cuh"
+#include "debug_bounds.cuh"
 
 namespace bdh {
 
@@ -215,6 +216,7 @@ embed_ln_fwd_kernel(const long long* tokens, const __nv_bfloat16* emb, __nv_bflo
   const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
   for (; row < rows; row += stride) {
     long long tok = tokens[row];
+    BDH_BOUNDS_CHECK(tok, vocab, BOUNDS_EMBED_TOKEN, row);
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
     Row<NC> r;
     row_load_bf16(r, emb + tok * D, D, lane);
@@ -232,6 +234,7 @@ embed_ln_bwd_kernel(const long long* tokens, const __nv_bfloat16* emb, const flo
   const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
   for (; row < rows; row += stride) {
     long long tok = tokens[row];
+    BDH_BOUNDS_CHECK(tok, vocab, BOUNDS_EMBED_BWD_TOKEN, row);
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
     Row<NC> y, g;
     row_load_bf16(y, emb + tok * D, D, lane);
@@ -326,6 +329,7 @@ cross_entropy_kernel(const float* logits, const long long* targets, float* row_l
     s = warp_sum(s);
     const float inv = 1.f / s;
     long long tgt = targets[row];
+    if (tgt != -100) BDH_BOUNDS_CHECK(tgt, V, BOUNDS_CE_TARGET, row);
     const bool ignore = tgt < 0 || tgt >= V;
     if (lane == 0) row_loss[row] = ignore ? 0.f : (logf(s) + mx - p[tgt]);
     if (dlogits) {
@@ -642,3 +646,7 @@ extern "C" int bdh_rownorm_bwd(void* grad_bf16, const void* normed_bf16, const f
                                                                         const_cast<float*>(rnorm), rows, T, ld);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
+
+// First data-dependent index of this file's kernels that was out of range since the last clear:
+// out = {checked build?, site, index, extent, where} (csrc/debug_bounds.cuh).
+extern "C" int bdh_bounds_record_rowwise(long long* out5, int clear) { return bdh::bounds_record_read(out5, clear) ? BDH_ERR_LAUNCH : BDH_OK; }

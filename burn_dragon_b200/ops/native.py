@@ -25,10 +25,11 @@ def load(build_if_missing: bool = True) -> bool:
         from .. import build as _build
 
         try:
+            checked = os.environ.get("BDH_CHECKED_KERNELS", "0") == "1"     # the bounds-checked build
             if build_if_missing:
-                path = _build.ensure_built()
+                path = _build.ensure_built(checked=checked)
             else:
-                path = _build.LIB
+                path = _build.LIB_CHECKED if checked else _build.LIB
                 if not path.exists():
                     raise FileNotFoundError(path)
             torch.ops.load_library(str(path))
@@ -61,6 +62,22 @@ def status_code() -> int:
 def clear_status() -> None:
     if available():
         torch.ops.bdh.status().zero_()
+
+
+BOUNDS_SITES = {1: "embed_ln_fwd: token id", 2: "embed_ln_bwd: token id", 3: "cross_entropy: target id",
+                4: "graph_spmm_relu: column block"}
+
+
+def bounds_violations(clear: bool = True) -> list:
+    """Checked build (`BDH_CHECKED_KERNELS=1`): the first out-of-range data-dependent index each group
+    of kernels has seen since the last clear, as dicts {site, index, extent, where}; empty when the
+    run was clean. Raises when the loaded library was built without the checks. Synchronises."""
+    if not available():
+        return []
+    rec = torch.ops.bdh.bounds_records(bool(clear)).tolist()
+    if not all(r[0] for r in rec):
+        raise RuntimeError("this process loaded the unchecked library; set BDH_CHECKED_KERNELS=1 before the first kernel call")
+    return [dict(site=BOUNDS_SITES.get(r[1], str(r[1])), index=r[2], extent=r[3], where=r[4]) for r in rec if r[1]]
 
 
 class _CountingOps:

@@ -1,0 +1,87 @@
+"""The bounds-checked build of the extension (`csrc/debug_bounds.cuh`, `python -m burn_dragon_b200.build
+--checked`): data-dependent indices are compared with their extents, the first violation is recorded
+for the host, nothing traps. The reference has no counterpart (safe Rust; its CI runs clippy,
+.github/workflows/clippy.yml:36-37)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_checked_library_builds_and_differs_only_in_the_instrumented_files():
+    from burn_dragon_b200 import build
+    lib = build.build(checked=True, verbose=False)
+    assert lib == build.LIB_CHECKED and lib.exists() and build.is_current(checked=True)
+    instrumented = sorted(p.stem for p in build.CSRC.glob("*.cu") if build._instrumented(p))
+    assert instrumented == ["graph", "rowwise"]
+    for stem in instrumented:
+        assert (build.OBJ / f"{stem}.checked.o").exists()
+    # the record readers, one library per process (both register `torch.ops.bdh` when loaded): the
+    # unchecked library answers zeros; the checked one, which has to synchronise, reports the failed
+    # call on a machine without a device instead of crashing
+    probe = ("import ctypes, sys, torch\nlib = ctypes.CDLL(sys.argv[1])\nout = (ctypes.c_longlong * 5)(9, 9, 9, 9, 9)\n"
+             "rc = lib.bdh_bounds_record_rowwise(out, 0)\nprint('RC', rc, list(out), int(torch.cuda.is_available()))\n")
+
+    def run(path):
+        r = subprocess.run([sys.executable, "-c", probe, str(path)], capture_output=True, text=True, timeout=600, cwd=ROOT)
+        assert r.returncode == 0, r.stderr[-1500:]
+        return r.stdout.strip().splitlines()[-1]
+    assert run(build.LIB).startswith("RC 0 [0, 0, 0, 0, 0]")
+    line = run(lib)
+    assert line.startswith("RC 0 [1, 0, 0, 0, 0]") if line.endswith(" 1") else not line.startswith("RC 0 "), line
+
+
+def test_checked_library_is_the_one_loaded_on_request():
+    code = ("import torch\nfrom burn_dragon_b200.ops import native\nassert native.load()\n"
+            "assert hasattr(torch.ops.bdh, 'bounds_records')\n"
+            "import re\nmaps = open('/proc/self/maps').read()\n"
+            "assert '_C_checked.so' in maps and not re.search(r'/_C\\.so', maps)\nprint('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=ROOT,
+                       env=dict(os.environ, PYTHONPATH=ROOT, BDH_CHECKED_KERNELS="1"))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+_DEVICE_CASE = r"""
+import torch
+from burn_dragon_b200.ops import native
+ops = native.ops
+dev = "cuda"
+V, D, rows = 64, 128, 32
+emb = torch.randn(V, D, device=dev).bfloat16()
+cur = torch.empty(rows, D, device=dev, dtype=torch.bfloat16)
+tok = torch.randint(0, V, (rows,), device=dev)
+ops.embed_ln_fwd(tok, emb, cur)
+assert native.bounds_violations() == [], "clean run"
+bad = tok.clone(); bad[3] = V + 5
+ops.embed_ln_fwd(bad, emb, cur)
+v = native.bounds_violations()
+assert len(v) == 1 and v[0]["index"] == V + 5 and v[0]["extent"] == V and v[0]["where"] == 3, v
+assert "embed_ln_fwd" in v[0]["site"]
+# the violating row was clamped exactly as the unchecked kernel clamps it
+ok = tok.clone(); ok[3] = V - 1
+want = torch.empty_like(cur); ops.embed_ln_fwd(ok, emb, want)
+assert torch.equal(cur, want)
+assert native.bounds_violations() == [], "the record was cleared"
+logits = torch.randn(rows, V, device=dev)
+tgt = torch.randint(0, V, (rows,), device=dev); tgt[5] = -100; tgt[7] = 999
+loss = torch.empty(rows, device=dev)
+ops.cross_entropy(logits, tgt, loss, None, 1.0)
+v = native.bounds_violations()
+assert len(v) == 1 and v[0]["index"] == 999 and v[0]["where"] == 7 and float(loss[7]) == 0.0 and float(loss[5]) == 0.0, v
+assert native.status_code() == 0
+print("PASS checked_build")
+"""
+
+
+@pytest.mark.gpu
+@pytest.mark.xfail(strict=False, reason="first GPU run of the checked build: reports, does not gate the tier")
+def test_checked_kernels_record_out_of_range_ids_on_the_device():
+    """Out-of-range token / target ids under the checked build: recorded with their row, handled as
+    the unchecked kernels handle them (clamped / ignored), no fault. Child process: the checked
+    library and the regular one cannot both register `torch.ops.bdh` in one process."""
+    r = subprocess.run([sys.executable, "-c", _DEVICE_CASE], capture_output=True, text=True, timeout=600, cwd=ROOT,
+                       env=dict(os.environ, PYTHONPATH=ROOT, BDH_CHECKED_KERNELS="1"))
+    assert r.returncode == 0 and "PASS checked_build" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
