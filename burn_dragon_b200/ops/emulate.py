@@ -165,6 +165,7 @@ def _rotate_by_table(x: torch.Tensor, table: torch.Tensor, T: int, n_per_head: i
 def _gemm(a, b, **kw):
     for k in ("peer_ptrs", "peer_rows", "peer_rank"):      # multi-GPU routing of the output: not emulated
         kw.pop(k, None)
+    G.check_extents(a, b, **kw)          # every emulated launch is bounds-checked on the host
     flags = kw.get("flags", 0)
     if kw.get("epi", G.EPI_STORE) == G.EPI_RELU and (flags & G.F_ROPE) and (flags & G.F_TABLE) \
             and tuple(kw.get("nz", (1, 1))) == (1, 1):

@@ -13,6 +13,7 @@ the outputs and the auxiliary inputs (which share C's coordinates).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -44,6 +45,61 @@ def operand_ok(t: torch.Tensor) -> bool:
             and t.data_ptr() % 16 == 0)
 
 
+def check_extents(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0, 0, 0, 0), b_off=(0, 0, 0, 0),
+                  epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
+                  o1_off=(0, 0, 0), T=1, n_per_head=1, **_) -> None:
+    """Host-side bounds check of one launch: for the last batch index (the offsets are linear and
+    must be non-negative) every operand window [mn_lo, mn_lo + M|N) x [k_lo, k_lo + K) and every
+    output / auxiliary window [r0, r0 + M) x [c0, c0 + N) has to lie inside its 2-D tensor. The
+    kernel itself would not fault on most of these (TMA clips and zero-fills), it would compute on
+    the wrong data; a plain-store epilogue would write outside its tensor. Runs for every launch of
+    the emulated kernel path and, with `BDH_CHECKED_KERNELS=1`, before every real launch."""
+    z0, z1 = int(nz[0]) - 1, int(nz[1]) - 1
+    if z0 < 0 or z1 < 0 or min(M, N, K) < 1:
+        raise ValueError(f"gemm: empty problem M={M} N={N} K={K} nz={tuple(nz)}")
+
+    def inside(name, t, rows_lo, rows_n, cols_lo, cols_n):
+        if t is None:
+            raise ValueError(f"gemm: epilogue {epi} needs `{name}`")
+        if t.dim() != 2:
+            raise ValueError(f"gemm: `{name}` must be 2-D, got {tuple(t.shape)}")
+        if rows_lo + rows_n > t.shape[0] or cols_lo + cols_n > t.shape[1]:
+            raise ValueError(f"gemm: window of `{name}` rows [{rows_lo}, {rows_lo + rows_n}) x cols [{cols_lo}, "
+                             f"{cols_lo + cols_n}) leaves its tensor {tuple(t.shape)} (last batch index {z0}, {z1})")
+
+    for name, off in (("a_off", a_off), ("b_off", b_off), ("c_off", c_off), ("o1_off", o1_off)):
+        if any(int(o) < 0 for o in off):
+            raise ValueError(f"gemm: negative {name} {tuple(off)}")
+    for name, t, mn_major, off, n in (("a", a, a_mn, a_off, M), ("b", b, b_mn, b_off, N)):
+        mn_lo, k_lo = off[0] * z0 + off[1] * z1, off[2] * z0 + off[3] * z1
+        if mn_major:
+            inside(name, t, k_lo, K, mn_lo, n)
+        else:
+            inside(name, t, mn_lo, n, k_lo, K)
+    r0, c0 = c_off[0] * z0 + c_off[1] * z1, c_off[2] * z0 + c_off[3] * z1
+    if not (flags & (F_NO_OUT0 | F_PEER_RS | F_MC_RED)):
+        inside("out0", out0, r0, M, c0, N)
+    if epi == EPI_RELU and flags & (F_ROPE | F_POPE):
+        c1 = o1_off[0] * z0 + o1_off[1] * z1
+        inside("out1", out1, r0, M, c1, N + (o1_off[2] if flags & F_POPE else 0))
+        if flags & F_TABLE:
+            inside("in0 (rotary table)", in0, 0, T, 0, n_per_head)
+    elif epi == EPI_RELU_GATE:
+        inside("in0", in0, r0, M, c0, N)
+        inside("out1", out1, r0, M, c0, N)
+    elif epi == EPI_GATE_BWD:
+        inside("in0", in0, r0, M, c0, N)
+        inside("in1", in1, r0, M, c0, N)
+        inside("out1", out1, r0, M, c0, N)
+    elif epi == EPI_DQ_BWD:
+        inside("in0", in0, r0, M, c0, N)
+        if flags & F_TABLE:
+            inside("in1 (rotary table)", in1, 0, T, 0, n_per_head)
+
+
+_CHECKED = os.environ.get("BDH_CHECKED_KERNELS", "0") == "1"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
          nz: Sequence[int] = (1, 1), a_off: Sequence[int] = (0, 0, 0, 0), b_off: Sequence[int] = (0, 0, 0, 0),
          epi: int = EPI_STORE, flags: int = 0, out0: Optional[torch.Tensor] = None,
@@ -56,6 +112,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
+    if _CHECKED:
+        check_extents(a, b, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, nz=nz, a_off=a_off, b_off=b_off, epi=epi, flags=flags,
+                      out0=out0, out1=out1, in0=in0, in1=in1, c_off=c_off, o1_off=o1_off, T=T, n_per_head=n_per_head)
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),

@@ -85,3 +85,33 @@ def test_checked_kernels_record_out_of_range_ids_on_the_device():
     r = subprocess.run([sys.executable, "-c", _DEVICE_CASE], capture_output=True, text=True, timeout=600, cwd=ROOT,
                        env=dict(os.environ, PYTHONPATH=ROOT, BDH_CHECKED_KERNELS="1"))
     assert r.returncode == 0 and "PASS checked_build" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+def test_host_side_extent_check_of_a_launch():
+    """`gemm.check_extents`: the operand / output windows of the last batch index must lie inside
+    their tensors (it runs for every launch of the emulated kernel path, so the CPU tests of that path
+    also prove the offsets of every launch of a training step, prefill and decode step)."""
+    import torch
+    from burn_dragon_b200.ops import gemm as G
+    H, B, T, Np, D = 2, 3, 64, 128, 32
+    q = torch.zeros(B * T, H * Np, dtype=torch.bfloat16)
+    S = torch.zeros(B * H * T, T, dtype=torch.bfloat16)
+    good = dict(M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
+                epi=G.EPI_CAUSAL, out0=S)
+    G.check_extents(q, q, **good)
+    with pytest.raises(ValueError, match="out0"):
+        G.check_extents(q, q, **{**good, "c_off": (T, H * T + 1, 0, 0)})
+    with pytest.raises(ValueError, match="window of `a`"):
+        G.check_extents(q, q, **{**good, "K": Np + 64})
+    with pytest.raises(ValueError, match="negative"):
+        G.check_extents(q, q, **{**good, "b_off": (0, -T, Np, 0)})
+    with pytest.raises(ValueError, match="needs `out1`"):
+        G.check_extents(q, q, M=B * T, N=B * T, K=H * Np, epi=G.EPI_RELU_GATE, in0=q, out0=q)
+    # an MN-major operand is indexed [k, mn]
+    v = torch.zeros(B * T, D, dtype=torch.bfloat16)
+    rho = torch.zeros(B * H * Np, D)
+    G.check_extents(q, v, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=(0, 0, 0, T),
+                    c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho)
+    with pytest.raises(ValueError, match="window of `b`"):
+        G.check_extents(q, v, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=(0, 0, 0, T + 1),
+                        c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho)
