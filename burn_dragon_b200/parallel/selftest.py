@@ -204,6 +204,14 @@ def main() -> int:
     else:
         fn = CASES[args.case]
     note = fn(dev)
+    from . import symm
+    if symm.GUARD_BYTES and args.case != "rank_exit":
+        # checked configuration: once every rank has finished its launches, no collective of this case
+        # may have written outside the window it was given
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        dist.barrier()
+        note = f"{note or ''} guards_ok={symm.check_all_canaries()}"
     if args.case != "rank_exit":
         dist.barrier()
     if dist.get_rank() == 0:

@@ -11,6 +11,7 @@ the rank-failure tests, where a dying rank must not be bound to a multicast obje
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -22,29 +23,88 @@ COLL_CTAS = 64
 _FLAG_WORDS = 8192
 
 
-class SymmetricBuffer:
-    """A tensor allocated in symmetric memory plus every rank's mapping of it."""
+GUARD_BYTES = 256 if os.environ.get("BDH_CHECKED_KERNELS", "0") == "1" else 0
+CANARY = 0x5AFEC0DE
+_LIVE = weakref.WeakSet()
 
-    def __init__(self, numel: int, dtype: torch.dtype, device, group=None):
-        import torch.distributed._symmetric_memory as symm_mem
+
+class SymmetricBuffer:
+    """A tensor allocated in symmetric memory plus every rank's mapping of it.
+
+    In the checked configuration (`BDH_CHECKED_KERNELS=1`) the allocation is `GUARD_BYTES` larger
+    at both ends and the guards hold a canary pattern: a peer (or a local kernel) that writes
+    outside the window it was given lands in a guard instead of in a neighbouring allocation, and
+    `check_canaries()` finds it afterwards. `tensor`, `ptrs` and `multicast_ptr` all address the
+    interior, so nothing else knows about the guards; with a zero guard the layout is the plain one."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group=None, guard_bytes: Optional[int] = None):
         self.group = group if group is not None else dist.group.WORLD
+        guard = GUARD_BYTES if guard_bytes is None else int(guard_bytes)
+        item = torch.empty((), dtype=dtype).element_size()
+        if guard % 16 or guard % item:
+            raise ValueError("guard_bytes must be a multiple of 16 and of the element size")
+        ge = guard // item
+        if guard:
+            numel_alloc = numel + (-numel * item % 16) // item      # the upper guard starts on a 16-byte boundary
+        else:
+            numel_alloc = numel
+        raw, ptrs, mc, self.rank, self.world = self._allocate(numel_alloc + 2 * ge, dtype, device)
+        self.raw, self.guard_bytes = raw, guard
+        self.tensor = raw[ge:ge + numel]
+        self.ptrs = [int(p) + guard for p in ptrs]
+        if os.environ.get("BDH_NO_MULTIMEM", "0") == "1":
+            mc = 0
+        self.multicast_ptr = int(mc) + guard if mc else 0
+        if guard:
+            for g in self._guards():
+                g.fill_(CANARY)
+            _LIVE.add(self)
+
+    def _allocate(self, numel: int, dtype: torch.dtype, device):
+        """-> (tensor in symmetric memory, every rank's pointer to it, multicast pointer or 0, rank, world)."""
+        import torch.distributed._symmetric_memory as symm_mem
         try:
             symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:  # noqa: BLE001 - newer torch versions do not need (or have) this call
             pass
-        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.tensor, self.group)
-        self.rank = int(self.handle.rank)
-        self.world = int(self.handle.world_size)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        if os.environ.get("BDH_NO_MULTIMEM", "0") == "1":
-            mc = 0
-        self.multicast_ptr = mc
+        raw = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(raw, self.group)
+        return (raw, [int(p) for p in self.handle.buffer_ptrs], int(getattr(self.handle, "multicast_ptr", 0) or 0),
+                int(self.handle.rank), int(self.handle.world_size))
+
+    def _guards(self):
+        ge = self.guard_bytes // self.raw.element_size()
+        if ge == 0:
+            return []
+        return [self.raw[:ge].view(torch.int32), self.raw[self.raw.numel() - ge:].view(torch.int32)]
+
+    def check_canaries(self) -> list:
+        """Guard words of THIS rank's copy that no longer hold the pattern, as (side, word index, value)."""
+        bad = []
+        for side, g in zip(("below", "above"), self._guards()):
+            for i in (g != CANARY).nonzero().flatten().tolist():
+                bad.append((side, i, int(g[i]) & 0xFFFFFFFF))
+        return bad
 
     def barrier(self) -> None:
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
+
+
+def check_all_canaries() -> int:
+    """Checked configuration: verify the guards of every live symmetric buffer of this process (after
+    a device synchronise, so that every collective launched so far has finished). Returns how many
+    buffers were checked; raises when one has been written outside its window."""
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    n = 0
+    for buf in list(_LIVE):
+        bad = buf.check_canaries()
+        if bad:
+            raise RuntimeError(f"symmetric buffer of {buf.tensor.numel()} x {buf.tensor.dtype} on rank {buf.rank}: "
+                               f"{len(bad)} guard words overwritten, first {bad[0]}")
+        n += 1
+    return n
 
 
 class _Flags:

@@ -115,3 +115,39 @@ def test_host_side_extent_check_of_a_launch():
     with pytest.raises(ValueError, match="window of `b`"):
         G.check_extents(q, v, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=(0, 0, 0, T + 1),
                         c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho)
+
+
+def test_guard_words_around_symmetric_buffers():
+    """Checked configuration of `parallel.symm.SymmetricBuffer`: guards with a canary pattern on both
+    sides of the window every rank (and every peer pointer) addresses; a write past the window is
+    found afterwards. The allocator is replaced by host memory here."""
+    import torch
+    from burn_dragon_b200.parallel import symm
+
+    class HostBuffer(symm.SymmetricBuffer):
+        def _allocate(self, numel, dtype, device):
+            raw = torch.zeros(numel, dtype=dtype)
+            return raw, [raw.data_ptr(), raw.data_ptr() + 4096], 1 << 20, 0, 2
+
+    class Group:
+        group_name = "g"
+
+    plain = HostBuffer(100, torch.float32, "cpu", Group(), guard_bytes=0)
+    assert plain.raw.numel() == 100 and plain.tensor.data_ptr() == plain.raw.data_ptr()
+    assert plain.ptrs[0] == plain.raw.data_ptr() and plain.multicast_ptr == 1 << 20 and plain.check_canaries() == []
+    for dtype, numel in ((torch.bfloat16, 101), (torch.float32, 64), (torch.int32, 7)):
+        b = HostBuffer(numel, dtype, "cpu", Group(), guard_bytes=256)
+        item = b.raw.element_size()
+        assert b.tensor.numel() == numel and b.tensor.data_ptr() == b.raw.data_ptr() + 256
+        assert b.ptrs == [b.raw.data_ptr() + 256, b.raw.data_ptr() + 4096 + 256] and b.multicast_ptr == (1 << 20) + 256
+        assert all(p % 16 == 0 for p in (b.ptrs[0] - b.raw.data_ptr(), b._guards()[1].data_ptr() - b.raw.data_ptr()))
+        b.tensor.fill_(3)
+        assert b.check_canaries() == [] and symm.check_all_canaries() >= 1
+        b.raw[b.raw.numel() - 256 // item] = 1                      # first element past the (padded) window
+        bad = b.check_canaries()
+        assert len(bad) == 1 and bad[0][:2] == ("above", 0)
+        with pytest.raises(RuntimeError, match="guard words overwritten"):
+            symm.check_all_canaries()
+        b.raw[256 // item - 1] = 1                                  # last element before the window
+        assert {x[0] for x in b.check_canaries()} == {"below", "above"}
+        del b
