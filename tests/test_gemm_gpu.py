@@ -223,3 +223,24 @@ def test_forward_fast_uses_kernels_and_matches_torch():
     m.use_native = False
     want = m.forward_fast(toks)
     assert ((got - want).norm() / want.norm()).item() < 3e-2
+
+
+@pytest.mark.xfail(strict=False, reason="first GPU run of this check: reports, does not gate the tier")
+def test_tile_to_cta_assignment_does_not_change_a_bit():
+    """Race check by schedule variation: every output tile is produced by one CTA with a fixed K order,
+    so the same launch run with the full grid, with 7 CTAs (many tiles per CTA, other neighbours in
+    time) and with 1 CTA (fully serial) has to give bit-identical outputs; a missing barrier between
+    pipeline stages or accumulator buffers would show up as a difference."""
+    M, N, K = 1024, 2048, 512
+    a, b = _rand(M, K, seed=11), _rand(N, K, seed=12)
+    x = _rand(M, N, seed=13)
+    outs = []
+    for ctas in (0, 7, 1):
+        native.clear_status()
+        y, xy = (torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+        G.gemm(a, b, M=M, N=N, K=K, epi=G.EPI_RELU_GATE, in0=x, out0=y, out1=xy, theta=0.1, max_ctas=ctas)
+        torch.cuda.synchronize()
+        assert native.status_code() == 0
+        outs.append((y, xy))
+    for y, xy in outs[1:]:
+        assert torch.equal(y, outs[0][0]) and torch.equal(xy, outs[0][1])
