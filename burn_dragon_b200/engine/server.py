@@ -4,6 +4,7 @@ chunks over HTTP). Standard library only.
 
     python -m burn_dragon_b200 serve --checkpoint runs/latest --port 8080
 
+    GET  /                                -> a prompt box (engine/www/index.html) that streams from /generate
     GET  /health                          -> {"status": "ok", "model": {...}, "device": "cuda:0"}
     GET  /metrics                         -> Prometheus text format: requests, generated tokens, busy seconds
     POST /generate  {"prompt": "ROMEO:", "max_tokens": 200, "temperature": 0.8, "top_k": 40,
@@ -66,6 +67,15 @@ def make_server(session: InferenceSession, host: str = "127.0.0.1", port: int = 
             self.wfile.write(body)
 
         def do_GET(self):
+            if self.path in ("/", "/index.html"):
+                from pathlib import Path
+                body = (Path(__file__).resolve().parent / "www" / "index.html").read_bytes()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/html; charset=utf-8")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+                return
             if self.path == "/metrics":
                 body = ("# TYPE bdh_requests_total counter\n"
                         f"bdh_requests_total {stats['requests']}\n"

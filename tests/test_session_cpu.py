@@ -107,6 +107,9 @@ def test_http_server_generate_and_stream():
         base = f"http://127.0.0.1:{port}"
         health = json.loads(urllib.request.urlopen(base + "/health", timeout=30).read())
         assert health["status"] == "ok" and health["model"]["n_layer"] == 2
+        page = urllib.request.urlopen(base + "/", timeout=30)
+        html = page.read().decode()
+        assert page.headers["Content-Type"].startswith("text/html") and '"/generate"' in html and "/health" in html
 
         def post(body):
             req = urllib.request.Request(base + "/generate", data=json.dumps(body).encode(),
