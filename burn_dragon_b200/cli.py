@@ -63,6 +63,7 @@ def cmd_train(args) -> int:
     from .engine.trainer import Trainer
     from .models.factory import build_model
     from .parallel import dist_utils
+    from .utils import profiling as prof
 
     cfg = _load_config(args.config, args.base)
     if args.synthetic:
@@ -190,6 +191,10 @@ def cmd_train(args) -> int:
             probe = getattr(wrapper, "eval_model", None) or model
             trainer.track_grad_norm = probe.measure_sparsity = logged
             prev = trainer.step_index
+            # logged steps of a multi-rank job also time their phases, for the exposed-communication column
+            timed = logged and world > 1 and not prof.timers_on()
+            if timed and trainer._micro == 0:
+                prof.enable(timers=True)
             loss = trainer.train_step(batch.inputs, batch.targets)
             step = trainer.step_index
             if step == prev:
@@ -202,6 +207,11 @@ def cmd_train(args) -> int:
                 else:
                     ms = (time.perf_counter() - wall) * 1e3
                 extra = {}
+                if timed:
+                    rep = prof.report()
+                    prof.enable(timers=False)
+                    comm = dist_utils.max_over_ranks(prof.comm_ms(rep), dev)
+                    extra.update(comm_ms=comm, comm_share=comm / max(ms, 1e-9))
                 if trainer.last_grad_norm is not None and wrapper is None:
                     extra["grad_norm"] = float(trainer.last_grad_norm)
                 sp = getattr(probe, "last_sparsity", None)

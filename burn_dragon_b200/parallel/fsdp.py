@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from ..engine.optim import FlatParams
 from ..ops import native
+from ..utils import profiling as prof
 
 
 class _ShardedOptimizerFacade:
@@ -102,24 +103,26 @@ class FSDP:
         self.step_count += 1
         lr = self.lr if lr is None else lr
         if self.fused:
-            self.sharded.step(lr)
+            with prof.phase("comm.rs_adamw_ag"):       # one kernel: reduce-scatter + AdamW + all-gather
+                self.sharded.step(lr)
             return loss.detach()
         # NCCL baseline: reduce-scatter, local AdamW on the shard, all-gather of fp32 then cast
         n = self.flat.numel
         self._grad_pad[:n].copy_(self.flat.grad)
-        per = self.numel // self.world
-        if (self.numel % self.world) == 0 and dist.get_backend(self.group) == "nccl":
-            dist.reduce_scatter_tensor(self._shard_grad, self._grad_pad, group=self.group)
-        else:
-            dist.all_reduce(self._grad_pad, group=self.group)
-            self._shard_grad.copy_(self._grad_pad[self.lo:self.hi])
+        with prof.phase("comm.reduce_scatter"):
+            if (self.numel % self.world) == 0 and dist.get_backend(self.group) == "nccl":
+                dist.reduce_scatter_tensor(self._shard_grad, self._grad_pad, group=self.group)
+            else:
+                dist.all_reduce(self._grad_pad, group=self.group)
+                self._shard_grad.copy_(self._grad_pad[self.lo:self.hi])
         g = self._shard_grad / self.world
         self.m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
         self.v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
         bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count
         self.master.mul_(1 - lr * self.weight_decay)
         self.master.addcdiv_(self.m / bc1, (self.v / bc2).sqrt_().add_(self.eps), value=-lr)
-        full = self._gather(self.master)
+        with prof.phase("comm.all_gather"):
+            full = self._gather(self.master)
         self.flat.master.copy_(full[:n])
         self.flat.refresh_shadow()
         return loss.detach()

@@ -31,6 +31,7 @@ from ..models.bdh import BDH
 from ..ops import gemm as G
 from ..ops import native
 from ..ops import reference as R
+from ..utils import profiling as prof
 
 
 class _Buf:
@@ -138,6 +139,10 @@ class TPComm:
     def end(self, b: _Buf, bf16: bool = False) -> torch.Tensor:
         """The reduced tensor: fp32 (a view of a reduction buffer, valid until the next `begin` with
         the same key and shape) or, with `bf16`, a fresh bf16 tensor."""
+        with prof.phase("comm.tp_reduce"):       # the half of the reduction that is a launch of its own
+            return self._end(b, bf16)
+
+    def _end(self, b: _Buf, bf16: bool) -> torch.Tensor:
         if b.mode == "rs":
             dt = torch.bfloat16 if bf16 else torch.float32
             o = b.out.get(dt)
@@ -173,7 +178,8 @@ class _CopyToShards(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous().clone()
-        dist.all_reduce(g, group=ctx.group)
+        with prof.phase("comm.tp_reduce"):
+            dist.all_reduce(g, group=ctx.group)
         return g, None
 
 
@@ -183,7 +189,8 @@ class _ReduceFromShards(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         x = x.contiguous().clone()
-        dist.all_reduce(x, group=group)
+        with prof.phase("comm.tp_reduce"):
+            dist.all_reduce(x, group=group)
         return x
 
     @staticmethod
@@ -311,9 +318,10 @@ class NeuronTP:
         loss.backward()
         # the replicated tensors see the same gradient on every rank up to summation order; average
         # them so the replicas cannot drift apart
-        for p in self._replicated:
-            dist.all_reduce(p.grad, group=self.group)
-            p.grad.div_(self.world)
+        with prof.phase("comm.replicated_grads"):
+            for p in self._replicated:
+                dist.all_reduce(p.grad, group=self.group)
+                p.grad.div_(self.world)
         self.opt.step(lr=self.lr if lr is None else lr)
         return loss.detach()
 

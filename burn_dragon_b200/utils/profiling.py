@@ -6,11 +6,16 @@ layer's forward / backward, head + loss, optimizer, collectives) in an NVTX rang
 tool shows the step structure. `enable(timers=True)` additionally brackets the phases with CUDA
 events on the launching stream; `report()` synchronises once and returns device milliseconds and
 call counts per phase (nested phases are reported under their own names; nothing is subtracted).
+Without a CUDA device the timers fall back to the host clock (CPU ops are synchronous), so that
+the phase structure of a step can be read on gloo ranks too. Phases named `comm.*` (and
+`grad_reduce`) are the collectives that are NOT hidden inside a compute kernel: `comm_ms()` adds
+them up for the "exposed communication" column of the metrics log.
 The reference only logs lines and an analytic FLOP count (src/bin/train.rs:635-659).
 """
 from __future__ import annotations
 
 import os
+import time
 from contextlib import contextmanager
 from typing import Dict, List, Tuple
 
@@ -39,9 +44,19 @@ def nvtx_on() -> bool:
 
 @contextmanager
 def phase(name: str):
-    """Mark a phase of the step. No-op unless tracing is enabled and a CUDA device is in use."""
-    if not active() or not torch.cuda.is_available():
+    """Mark a phase of the step. No-op unless tracing is enabled."""
+    if not active():
         yield
+        return
+    if not torch.cuda.is_available():
+        if not _cfg["timers"]:
+            yield
+            return
+        t0 = time.perf_counter()
+        try:
+            yield
+        finally:
+            _events.append((name, t0, time.perf_counter()))
         return
     ev = None
     if _cfg["timers"]:
@@ -62,12 +77,23 @@ def phase(name: str):
 def report(reset: bool = True) -> Dict[str, Dict[str, float]]:
     """{phase: {"ms": total device time, "calls": n}} for everything recorded since the last reset."""
     out: Dict[str, Dict[str, float]] = {}
-    if _events:
+    if _events and torch.cuda.is_available():
         torch.cuda.synchronize()
     for name, a, b in _events:
         d = out.setdefault(name, {"ms": 0.0, "calls": 0})
-        d["ms"] += a.elapsed_time(b)
+        d["ms"] += (b - a) * 1e3 if isinstance(a, float) else a.elapsed_time(b)
         d["calls"] += 1
     if reset:
         _events.clear()
     return out
+
+
+def timers_on() -> bool:
+    return _cfg["timers"]
+
+
+def comm_ms(rep: Dict[str, Dict[str, float]]) -> float:
+    """Exposed communication of a report: the collectives that run as launches of their own (gradient
+    all-reduce, reduce-scatter + AdamW + all-gather, the gather half of a tensor-parallel reduction,
+    NCCL calls). Communication done by a GEMM epilogue is inside the compute phases by design."""
+    return sum(v["ms"] for k, v in rep.items() if k == "grad_reduce" or k.startswith("comm."))

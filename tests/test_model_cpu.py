@@ -147,3 +147,28 @@ def test_cpp_oracle_equals_torch_recurrent_path():
         assert np.allclose(rho, st.layers[-1].rho[0].numpy(), rtol=2e-4, atol=2e-5), rot
     with pytest.raises(ValueError):
         hostlib.oracle_forward(m, [0, 99])
+
+
+def test_phase_timers_fall_back_to_the_host_clock():
+    """`utils.profiling` without a CUDA device: phases are timed with the host clock; `comm_ms` adds up
+    the collectives that are launches of their own."""
+    import time
+    from burn_dragon_b200.utils import profiling as prof
+    assert not prof.timers_on()
+    with prof.phase("ignored"):
+        pass
+    assert prof.report() == {}
+    prof.enable(timers=True)
+    try:
+        for _ in range(2):
+            with prof.phase("step"):
+                with prof.phase("comm.tp_reduce"):
+                    time.sleep(0.01)
+                with prof.phase("grad_reduce"):
+                    time.sleep(0.005)
+        rep = prof.report()
+    finally:
+        prof.enable(timers=False)
+    assert rep["step"]["calls"] == 2 and rep["comm.tp_reduce"]["calls"] == 2
+    assert 25.0 <= prof.comm_ms(rep) <= rep["step"]["ms"] + 1e-6
+    assert prof.report() == {}

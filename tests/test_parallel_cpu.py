@@ -90,6 +90,12 @@ strategy = "{strategy}"
     port = 29300 + (os.getpid() + len(strategy)) % 200
     r = run_job(base + ["--master-port", str(port)] + tail + ["--max-iters", "4"], e, 300)
     assert r.returncode == 0 and "[valid       4]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+    # logged steps of a multi-rank run carry the exposed-communication columns
+    import json
+    run = (runs / "latest").read_text().strip()
+    recs = [json.loads(l) for l in (runs / run / "metrics.jsonl").read_text().splitlines()]
+    train = [x for x in recs if x["split"] == "train"]
+    assert train and all(x["comm_ms"] > 0 and 0 < x["comm_share"] < 1 for x in train), recs
     r = run_job(base + ["--master-port", str(port + 1)] + tail + ["--resume", "latest", "--max-iters", "6"], e, 300)
     assert r.returncode == 0 and "step 4" in r.stdout and "[valid       6]" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
     # the checkpoint is layout-free: the same run continues as a single process
