@@ -192,9 +192,10 @@ def cmd_train(args) -> int:
             trainer.track_grad_norm = probe.measure_sparsity = logged
             prev = trainer.step_index
             # logged steps of a multi-rank job also time their phases, for the exposed-communication column
-            timed = logged and world > 1 and not prof.timers_on()
-            if timed and trainer._micro == 0:
-                prof.enable(timers=True)
+            if trainer._micro == 0:        # (decided at the first micro-batch of an accumulated step)
+                timed = logged and world > 1 and not prof.timers_on()
+                if timed:
+                    prof.enable(timers=True)
             loss = trainer.train_step(batch.inputs, batch.targets)
             step = trainer.step_index
             if step == prev:
