@@ -11,6 +11,7 @@ The recurrent state is fp32 [B, H, N', D] per layer, exactly `LayerState.rho`.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
@@ -21,9 +22,14 @@ from ..ops.fused_bdh import _Dims, _weights
 
 
 class DecodeEngine:
-    def __init__(self, model, use_graph: bool = True, split_k: int = 32):
+    def __init__(self, model, use_graph: bool = True, split_k: int = 32, pope_graph: Optional[bool] = None):
         self.model = model
         self.use_graph = use_graph
+        # PoPE: the fused rotation epilogue takes the position as a host argument, so a step that uses
+        # it cannot be replayed from a graph. `pope_graph` (or BDH_POPE_DECODE_GRAPH=1) ends the encoder
+        # GEMM at the ReLU instead and rotates with elementwise ops that read the position from device
+        # memory - the form the stream pool uses - which makes the single-request PoPE step capturable.
+        self.pope_graph = (os.environ.get("BDH_POPE_DECODE_GRAPH", "0") == "1") if pope_graph is None else bool(pope_graph)
         self.split_k = split_k
         self._cache = {}       # (streams, device, sampling settings) -> buffers, state storage, captured graph
 
@@ -92,11 +98,11 @@ class DecodeEngine:
                        n_per_head=d.N, freqs=d.freqs,       # row m reads table row m % T
                        tma_epilogue=not per_stream)         # a few rows: the per-thread epilogue, as for T = 1
                 q = buf["q"]
-            elif d.rot == "pope" and per_stream:
-                # one position per stream: the encoder GEMM stops at the ReLU and the rotation
+            elif d.rot == "pope" and (per_stream or self.pope_graph):
+                # the position(s) come from device memory: the encoder GEMM stops at the ReLU and the rotation
                 # q = softplus(x) * (cos, sin)(2 pi frac(pos f)) is a few elementwise ops on [streams, H*N]
                 G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, out0=buf["x"], theta=d.theta)
-                ph = G.rot_phases(buf["pos"], d.freqs)                       # [streams, N]
+                ph = G.rot_phases(buf["pos"], d.freqs)                       # [streams, N], or [1, N] shared
                 mag = torch.nn.functional.softplus(buf["x"].float()).view(B, d.H, d.N)
                 qv = buf["q"].view(B, d.H, 2, d.N)                           # per head: [real N | imaginary N]
                 qv[:, :, 0] = mag * ph.cos()[:, None]
@@ -182,7 +188,7 @@ class DecodeEngine:
             buf["step"].fill_(int(step0))
 
         load_state()
-        graph_ok = self.use_graph and d.rot != "pope" and dev.type == "cuda"
+        graph_ok = self.use_graph and (d.rot != "pope" or self.pope_graph) and dev.type == "cuda"
         out = []
         n = int(n)
         if graph_ok:

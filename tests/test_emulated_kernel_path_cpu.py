@@ -352,3 +352,26 @@ def test_stream_pool_self_test_entry_runs():
     r = subprocess.run([sys.executable, "-m", "burn_dragon_b200.engine.stream_pool"], capture_output=True, text=True,
                        timeout=600, cwd=root, env=dict(os.environ, PYTHONPATH=root, BDH_EMULATE_KERNELS="1"))
     assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 6, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+def test_pope_decode_step_with_the_position_in_device_memory():
+    """`DecodeEngine(pope_graph=True)`: the PoPE step that reads its position from a device word (the
+    graph-capturable form) produces the tokens and logits of the step with the fused rotation epilogue."""
+    from burn_dragon_b200.engine import decode_engine as DE
+    from burn_dragon_b200.engine import generation as GEN
+    m = _decode_model("pope")
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 256, (2, 64), generator=g)
+    s = GEN.GenerationSettings(12, greedy=True)
+    with emulate.kernel_path():
+        fused = DE.DecodeEngine(m, pope_graph=False)
+        want = fused.generate(prompt, s)
+        want_logits = fused.last_logits.clone()
+        eng = DE.DecodeEngine(m, pope_graph=True)
+        got = eng.generate(prompt, s)
+        # a second call continues from the state and the position the first one left
+        more = eng.continue_from(eng.last_state, eng.last_logits, s, 4, step0=12)
+        more_ref = fused.continue_from(fused.last_state, fused.last_logits, s, 4, step0=12)
+    assert torch.equal(got, want) and _rel(eng.last_logits, fused.last_logits) < 0.02
+    assert torch.equal(more, more_ref)
+    assert want_logits.shape == (2, 256)
