@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import concurrent.futures as cf
 import hashlib
-import os
 import shutil
 import subprocess
 import sys

@@ -16,7 +16,6 @@ from typing import Callable, List, Optional
 
 import torch
 
-from ..ops import reference as R
 
 
 @dataclass(frozen=True)

@@ -20,7 +20,6 @@ from typing import Optional
 import torch
 
 from ..ops import native
-from ..ops.block_sparse import BlockPattern1d
 from .bdh import BDH, BDHConfig, build_model_config
 
 

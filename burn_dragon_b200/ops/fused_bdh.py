@@ -21,7 +21,6 @@ import torch
 
 from . import gemm as G
 from . import native
-from . import reference as R
 from ..utils import profiling as prof
 
 ops = native.ops

@@ -14,7 +14,6 @@ Two reductions are available:
 from __future__ import annotations
 
 
-import torch
 import torch.distributed as dist
 
 from . import dist_utils

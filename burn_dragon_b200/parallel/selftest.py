@@ -6,7 +6,6 @@ child processes.
 from __future__ import annotations
 
 import argparse
-import os
 import sys
 
 import torch

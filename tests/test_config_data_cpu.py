@@ -224,7 +224,7 @@ def test_char_vocab_native_encode_matches_python():
         strict.encode_array("abd")
 
 
-def test_profiling_hooks_are_noops_without_cuda_and_metrics_fields(tmp_path):
+def test_profiling_hooks_without_cuda_and_metrics_fields(tmp_path):
     import json
     import torch
     from burn_dragon_b200.engine.trainer import Trainer
@@ -239,7 +239,8 @@ def test_profiling_hooks_are_noops_without_cuda_and_metrics_fields(tmp_path):
         tr.train_step(tok[:, :-1], tok[:, 1:])
         assert float(tr.last_grad_norm) > 0
         assert 0.0 < float(m.last_sparsity["xy"]) <= float(m.last_sparsity["x"]) <= 1.0
-        if not torch.cuda.is_available():
-            assert prof.report() == {}
+        rep = prof.report()
+        # (without a CUDA device NVTX is skipped and the timers use the host clock)
+        assert {"step", "forward", "backward", "optimizer"} <= set(rep) and rep["step"]["ms"] >= rep["forward"]["ms"] > 0
     finally:
         prof.enable(nvtx=False, timers=False)
