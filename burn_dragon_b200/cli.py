@@ -107,7 +107,11 @@ def cmd_train(args) -> int:
     trainer = Trainer(model, cfg.optimizer.learning_rate, cfg.optimizer.weight_decay, cfg.optimizer.beta1,
                       cfg.optimizer.beta2, cfg.optimizer.eps, sched, strategy, cfg.parallel.fused_collectives,
                       cfg.training.fast_train, cfg.training.grad_clip, wrapper, accum)
-    train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum)   # batches = micro-batches
+    if cfg.dataset.device_resident:
+        train_loader = D.ResidentDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum,
+                                            seed=cfg.training.seed + data_rank)
+    else:
+        train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum)   # batches = micro-batches
     val_spe = ds.steps_per_epoch(D.VAL)
     valid_steps = max(1, min(max(1, total_steps // max(1, cfg.training.log_frequency)), val_spe))
     valid_loader = D.RandomDataLoader(ds, D.VAL, dev, valid_steps, None)

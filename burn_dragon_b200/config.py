@@ -99,6 +99,8 @@ class DatasetConfig:
     # synthetic (uniform random bytes; what the benchmarks use)
     synthetic_tokens: int = 1 << 22
     seed: int = 0
+    # keep the token array on the training device and gather the batches there (no per-step H2D copy)
+    device_resident: bool = False
     tokenizer: TokenizerConfig = field(default_factory=TokenizerConfig)
 
 

@@ -16,6 +16,8 @@ Differences on purpose: sampling is seeded (the reference uses an unseeded threa
 are assembled by the C++ window gatherer into pinned host memory when it is built (numpy
 otherwise), downloads are refused with a clear error when the file is not cached and there is no
 network, and a `synthetic` source provides uniform random bytes for benchmarks.
+`ResidentDataLoader` is the device-side variant of the loader: the corpus lives on the training
+device and the windows are drawn and gathered there.
 """
 from __future__ import annotations
 
@@ -136,12 +138,57 @@ class RandomDataLoader:
 
     def load_state_dict(self, sd: Dict) -> None:
         self.consumed = int(sd["consumed"])
-        self.dataset.rng.bit_generator.state = sd["rng"]
+        if "rng" in sd:                    # (a checkpoint written with the device-resident loader has none)
+            self.dataset.rng.bit_generator.state = sd["rng"]
 
 
 # ------------------------------------------------------------------------------------------------
 # sources
 # ------------------------------------------------------------------------------------------------
+class ResidentDataLoader(RandomDataLoader):
+    """The same batches-per-pass contract with the token array RESIDENT on the training device: window
+    starts are drawn and the windows gathered there, so a step costs no host work and no host-to-device
+    copy (`[dataset] device_resident = true`). A corpus of n tokens takes 4 n bytes of device memory
+    (2 n for vocabularies up to 32768). The draws come from a torch generator on that device, so the
+    sequence of batches differs from the host loader's for the same seed; it is reproducible and
+    its state is checkpointed like the host loader's."""
+
+    def __init__(self, dataset: TokenSequenceDataset, split: str, device, steps_per_epoch: int = 1,
+                 total_steps: Optional[int] = None, seed: int = 0):
+        super().__init__(dataset, split, device, steps_per_epoch, total_steps, pin=False)
+        device = torch.device(device if device is not None else "cpu")
+        offset, span = dataset.split_offset_and_span(split)
+        small = int(dataset.tokens.max(initial=0)) < 32768
+        self.tokens = torch.from_numpy(np.ascontiguousarray(dataset.tokens[offset:offset + span])).to(
+            torch.int16 if small else torch.int32).to(device)
+        self.width = dataset.block_size + 1
+        self.max_start = max(0, span - self.width)
+        self.generator = torch.Generator(device=device).manual_seed(int(seed))
+        self._arange = torch.arange(self.width, device=device)
+
+    def sample_batch(self) -> SequenceBatch:
+        B = self.dataset.batch_size
+        starts = torch.randint(0, self.max_start + 1, (B,), generator=self.generator, device=self.tokens.device)
+        win = self.tokens[starts[:, None] + self._arange[None, :]].long()
+        return SequenceBatch(win[:, :-1], win[:, 1:])
+
+    def __iter__(self) -> Iterator[SequenceBatch]:
+        for _ in range(len(self)):
+            if self.total_steps is not None:
+                if self.consumed >= self.total_steps:
+                    return
+                self.consumed += 1
+            yield self.sample_batch()
+
+    def state_dict(self) -> Dict:
+        return dict(consumed=self.consumed, generator=self.generator.get_state().cpu())
+
+    def load_state_dict(self, sd: Dict) -> None:
+        self.consumed = int(sd["consumed"])
+        if "generator" in sd:              # (a checkpoint written with the host loader only carries the step count)
+            self.generator.set_state(sd["generator"].cpu())
+
+
 def _clamp_train_len(n_tokens: int, ratio: float, block_size: int) -> int:
     ratio = min(max(ratio, 0.0), 1.0)
     t = int(np.float32(n_tokens) * np.float32(ratio))

@@ -95,3 +95,25 @@ def test_train_then_infer_a_non_bdh_model_through_the_cli(tmp_path, capsys):
     assert cli.main(["infer", "--runs", str(runs), "-c", preset, "--prompt", "ab", "--max-tokens", "6", "--greedy",
                      "--device", "cpu"]) == 0
     assert capsys.readouterr().out.startswith("ab")
+
+
+def test_train_and_resume_with_the_device_resident_loader(tmp_path, capsys):
+    """`[dataset] device_resident = true`: batches gathered on the device; a resumed run continues the
+    loader's generator (and a run saved with the host loader can be continued with the resident one)."""
+    from burn_dragon_b200 import cli
+    over = tmp_path / "o.toml"
+    over.write_text("[training]\nbatch_size = 2\nblock_size = 32\nlog_frequency = 1\n\n[dataset]\ndevice_resident = true\n\n"
+                    "[model]\nn_layer = 1\nn_embd = 32\nn_head = 2\n")
+    host = tmp_path / "h.toml"
+    host.write_text(over.read_text().replace("device_resident = true", "device_resident = false"))
+    runs = tmp_path / "runs"
+    base = ["--synthetic", "--device", "cpu", "--runs", str(runs)]
+    assert cli.main(["train", "-c", str(over), "--max-iters", "3"] + base) == 0
+    assert "[valid       3]" in capsys.readouterr().out
+    assert cli.main(["train", "-c", str(over), "--max-iters", "5", "--resume", "latest"] + base) == 0
+    out = capsys.readouterr().out
+    assert "step 3" in out and "[valid       5]" in out
+    assert cli.main(["train", "-c", str(host), "--max-iters", "6", "--resume", "latest"] + base) == 0
+    assert "[valid       6]" in capsys.readouterr().out
+    assert cli.main(["train", "-c", str(over), "--max-iters", "7", "--resume", "latest"] + base) == 0
+    assert "[valid       7]" in capsys.readouterr().out

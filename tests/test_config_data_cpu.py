@@ -244,3 +244,39 @@ def test_profiling_hooks_without_cuda_and_metrics_fields(tmp_path):
         assert {"step", "forward", "backward", "optimizer"} <= set(rep) and rep["step"]["ms"] >= rep["forward"]["ms"] > 0
     finally:
         prof.enable(nvtx=False, timers=False)
+
+
+def test_device_resident_loader_contract_and_resume():
+    """`ResidentDataLoader`: batches are gathered on the device from a resident token array; same
+    contract as the host loader (shape, shifted targets, split bounds, global step cap), reproducible,
+    and its generator state survives a checkpoint."""
+    import numpy as np
+    import torch
+    from burn_dragon_b200.data import dataset as D
+    ds = D.synthetic_dataset(5000, block_size=16, batch_size=4, vocab=256, seed=1)
+    # make the two splits distinguishable: validation tokens are >= 128
+    off, span = ds.split_offset_and_span(D.VAL)
+    ds.tokens[:off] %= 128
+    ds.tokens[off:] = 128 + ds.tokens[off:] % 128
+    tr = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=7)
+    va = D.ResidentDataLoader(ds, D.VAL, "cpu", steps_per_epoch=2, seed=7)
+    assert tr.tokens.dtype == torch.int16 and tr.tokens.numel() == off
+    first = list(tr)
+    assert len(first) == 3 and all(b.inputs.shape == (4, 16) and b.inputs.dtype == torch.int64 for b in first)
+    for b in first:
+        assert torch.equal(b.inputs[:, 1:], b.targets[:, :-1]) and int(b.inputs.max()) < 128 and int(b.targets.max()) < 128
+        # every window is a contiguous slice of the corpus
+        for row_in, row_t in zip(b.inputs, b.targets):
+            w = torch.cat([row_in, row_t[-1:]]).numpy()
+            starts = np.flatnonzero(ds.tokens[:off - 16] == w[0])
+            assert any(np.array_equal(ds.tokens[s:s + 17], w) for s in starts)
+    assert all(int(b.inputs.min()) >= 128 for b in va)
+    sd = tr.state_dict()
+    rest = list(tr)
+    assert len(rest) == 2 and tr.consumed == 5 and list(tr) == []          # the global cap
+    again = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=99)
+    again.load_state_dict(sd)
+    resumed = list(again)
+    assert len(resumed) == 2 and all(torch.equal(a.inputs, b.inputs) for a, b in zip(rest, resumed))
+    same = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=7)
+    assert all(torch.equal(a.inputs, b.inputs) for a, b in zip(first, same))
