@@ -34,8 +34,10 @@ class Trainer:
         self._micro = 0
         if wrapper is not None and self.grad_accum > 1:
             raise ValueError("gradient accumulation is not available under the FSDP / TP wrappers")
-        if wrapper is not None and fast_train:
-            raise ValueError("fast_train (the row-normalised forward) is not available under the FSDP / TP wrappers")
+        if wrapper is not None:
+            if fast_train and not hasattr(model, "forward_fast"):
+                raise ValueError("fast_train needs a model with a `forward_fast` path")
+            wrapper.fast_train = bool(fast_train)
         self.track_grad_norm = False      # set by the metrics logger on the steps it logs
         self.last_grad_norm = None
         self.wrapper = wrapper

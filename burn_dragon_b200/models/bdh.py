@@ -170,8 +170,6 @@ class BDH(nn.Module):
         tp = getattr(self, "_tp", None)
         res = cur
         if tp is not None:
-            if mode == "fast":
-                raise NotImplementedError("the row-normalised path is not neuron-sharded")
             cur = tp.copy(cur)
         x = R.relu_lowrank(cur, self._enc(self.encoder).to(cur.dtype), None, c.relu_threshold, mask)
         new_rho = None
@@ -182,7 +180,12 @@ class BDH(nn.Module):
                 block = c.block_sparse.time.block_size
                 pairs = c.block_sparse.time.pairs((cur.shape[2] + block - 1) // block)
             from ..ops import rownorm_attention as RA
-            if pairs is None and getattr(self, "use_native", True) and RA.can_run(q, cur):
+            if tp is not None:
+                # neuron-sharded: the scores are partial sums over the shards and must be complete before
+                # the normalisation; S V is then the same on every rank, so V is the replicated `res`
+                # (whose gradient is NOT summed over the ranks) and `a` needs no reduction
+                a = R.attention_rownorm(q, res, self._slopes(), pairs, block, reduce_scores=tp.reduce)
+            elif pairs is None and getattr(self, "use_native", True) and RA.can_run(q, cur):
                 a = RA.attention_rownorm(q, cur, self._slopes())
             else:
                 a = R.attention_rownorm(q, cur, self._slopes(), pairs, block)
@@ -209,7 +212,7 @@ class BDH(nn.Module):
                 a, new_rho = R.linear_attention_chunked(q, cur, self._slopes(), rho)
             else:
                 a, new_rho = R.linear_attention_parallel(q, cur, self._slopes(), rho)
-        if tp is not None:
+        if tp is not None and mode != "fast":
             a = tp.reduce(a)
         a = R.layer_norm(a)
         if tp is not None:
@@ -279,7 +282,9 @@ class BDH(nn.Module):
     def forward_fast(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None):
         """Row-normalised parallel path (src/model/bdh.rs:96-168). Produces no state."""
         from ..ops import fused_bdh
-        if fused_bdh.can_run(self, tokens, None):
+        # (under neuron-sharded tensor parallelism this mode runs on the torch path: the scores have to
+        # be summed over the shards before they are normalised, which the fused stack does not do)
+        if getattr(self, "_tp", None) is None and fused_bdh.can_run(self, tokens, None):
             if targets is not None:
                 return fused_bdh.loss(self, tokens, targets, fast=True)
             return fused_bdh.forward_logits(self, tokens, None, fast=True)

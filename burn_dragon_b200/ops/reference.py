@@ -160,14 +160,18 @@ def linear_attention_chunked(q: torch.Tensor, v: torch.Tensor, slopes: Optional[
 # `forward_fast` attention: additive ALiBi bias + L1 row normalisation
 # ------------------------------------------------------------------------------------------------
 def attention_rownorm(q: torch.Tensor, v: torch.Tensor, slopes: Optional[torch.Tensor],
-                      block_pairs=None, block: Optional[int] = None) -> torch.Tensor:
+                      block_pairs=None, block: Optional[int] = None, reduce_scores=None) -> torch.Tensor:
     """S = tril(q q^T, -1) (+ m_h * tril(j - i, -1)); S /= sum_j |S_ij| + 1e-6; a = S v
     (src/model/attention.rs:142-175, 300-303). `block_pairs`/`block` restrict the score matrix to the
-    active (row-block, col-block) pairs of a BlockPattern2d (src/kernel/linear_attention.rs:54-112)."""
+    active (row-block, col-block) pairs of a BlockPattern2d (src/kernel/linear_attention.rs:54-112).
+    `reduce_scores`: when q holds only a shard of the neurons, q q^T is a partial sum; the callable
+    sums it over the shards BEFORE the bias and the (non-linear) normalisation."""
     B, H, T, N = q.shape
     D = v.shape[-1]
     v = v.expand(B, H, T, D)
     S = torch.tril(torch.matmul(q, q.transpose(-1, -2)), diagonal=-1)
+    if reduce_scores is not None:
+        S = reduce_scores(S)
     if slopes is not None:
         t = torch.arange(T, device=q.device, dtype=q.dtype)
         bias = torch.tril(t[None, :] - t[:, None], diagonal=-1)   # (j - i) <= 0 below the diagonal

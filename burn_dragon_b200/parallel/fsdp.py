@@ -94,11 +94,12 @@ class FSDP:
             self._shard_grad = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
             self.flat.refresh_shadow()
         self.optimizer = _ShardedOptimizerFacade(self)
+        self.fast_train = False             # set by the trainer: train on the row-normalised forward
 
     # ---- step -----------------------------------------------------------------------------------
     def train_step(self, tokens, targets, lr: Optional[float] = None) -> torch.Tensor:
         self.flat.zero_grad()
-        loss = self.model(tokens, targets)
+        loss = self.model.forward_fast(tokens, targets) if self.fast_train else self.model(tokens, targets)
         loss.backward()
         self.step_count += 1
         lr = self.lr if lr is None else lr

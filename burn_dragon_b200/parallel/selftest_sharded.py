@@ -108,6 +108,39 @@ def case_tp(dev):
             sd = w.gather_state_dict()
             assert sd["encoder"].shape == one.encoder.shape
             notes.append(f"{rot}:{w.comm.mode}{'+mc' if w.comm.multicast else ''}")
+        # the row-normalised forward (`fast_train`) under the same sharding: the scores are summed over
+        # the shards before they are normalised (torch path on every device)
+        full = _bdh(dev, rot, N=128 * world)
+        one = _bdh(dev, rot, N=128 * world)
+        with torch.no_grad():
+            for m in (full, one):
+                m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+        one.use_native = False
+        w = NeuronTP(full, lr=1e-3, fused=False)
+        w.opt.zero_grad()
+        l_tp = w.shard.forward_fast(x, y)
+        l_tp.backward()
+        l_one = one.forward_fast(x, y)
+        l_one.backward()
+        tol = 2e-3 if dev.type == "cpu" else 3e-2        # (other summation orders on a GPU)
+        assert abs(l_tp.item() - l_one.item()) < tol * max(1.0, abs(l_one.item())), (rot, "fast", l_tp.item(), l_one.item())
+        c = one.config
+        for name in ("encoder", "encoder_v", "decoder"):
+            local = getattr(w.shard, name).grad.detach().contiguous()
+            parts = [torch.empty_like(local) for _ in range(world)]
+            dist.all_gather(parts, local)
+            got, want = unshard_rows(parts, c.n_head, c.latent_per_head), getattr(one, name).grad
+            assert _rel(got, want) < tol, (rot, "fast", name, _rel(got, want))
+        for a, b in ((w.shard.embed.weight.grad, one.embed.weight.grad), (w.shard.lm_head.grad, one.lm_head.grad)):
+            assert _rel(a, b) < tol, (rot, "fast", _rel(a, b))
+        tr = Trainer(full, lr=1e-3, wrapper=w, fast_train=True)
+        one.zero_grad()
+        tr1 = Trainer(one, lr=1e-3, fast_train=True)
+        for _ in range(3):
+            a = tr.train_step(x, y)
+            b = tr1.train_step(x, y)
+        assert abs(a.item() - b.item()) < 3 * tol * max(1.0, abs(b.item())), (rot, "fast", a.item(), b.item())
+        notes.append(f"{rot}:fast")
     return " ".join(notes)
 
 

@@ -309,12 +309,13 @@ class NeuronTP:
         self.opt = FlatAdamW(self.shard, lr, weight_decay, beta1, beta2, eps, shadow_bf16=dev.type == "cuda")
         self.optimizer = _TPOptimizerFacade(self)
         self.eval_model = self.shard        # evaluating the shard under its hooks gives the full model's loss
+        self.fast_train = False             # set by the trainer: train on the row-normalised forward
         self.lr = lr
         self._replicated = [self.shard.embed.weight, self.shard.lm_head]
 
     def train_step(self, tokens, targets, lr: Optional[float] = None) -> torch.Tensor:
         self.opt.zero_grad()
-        loss = self.shard(tokens, targets)
+        loss = self.shard.forward_fast(tokens, targets) if self.fast_train else self.shard(tokens, targets)
         loss.backward()
         # the replicated tensors see the same gradient on every rank up to summation order; average
         # them so the replicas cannot drift apart
