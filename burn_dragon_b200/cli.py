@@ -100,10 +100,6 @@ def cmd_train(args) -> int:
         from .parallel import build_wrapper
         wrapper = build_wrapper(model, cfg, strategy)
     accum = max(1, cfg.training.grad_accum_steps)
-    if wrapper is not None and accum > 1:
-        if rank == 0:
-            print("grad_accum_steps is ignored under the FSDP / TP wrappers", flush=True)
-        accum = 1
     trainer = Trainer(model, cfg.optimizer.learning_rate, cfg.optimizer.weight_decay, cfg.optimizer.beta1,
                       cfg.optimizer.beta2, cfg.optimizer.eps, sched, strategy, cfg.parallel.fused_collectives,
                       cfg.training.fast_train, cfg.training.grad_clip, wrapper, accum)

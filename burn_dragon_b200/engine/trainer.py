@@ -32,8 +32,6 @@ class Trainer:
         # gradient buffer, reduced across ranks once and applied with scale 1/grad_accum
         self.grad_accum = max(1, int(grad_accum))
         self._micro = 0
-        if wrapper is not None and self.grad_accum > 1:
-            raise ValueError("gradient accumulation is not available under the FSDP / TP wrappers")
         if wrapper is not None:
             if fast_train and not hasattr(model, "forward_fast"):
                 raise ValueError("fast_train needs a model with a `forward_fast` path")
@@ -66,8 +64,10 @@ class Trainer:
         """One optimizer step. Returns the (local) loss as a 0-d device tensor; no host sync."""
         if self.wrapper is not None:
             with prof.phase("step"):
-                loss = self.wrapper.train_step(tokens, targets, self.current_lr())
-            self.step_index += 1
+                loss = self.wrapper.train_step(tokens, targets, self.current_lr(), micro=(self._micro, self.grad_accum))
+            self._micro = (self._micro + 1) % self.grad_accum
+            if self._micro == 0:
+                self.step_index += 1
             return loss
         with prof.phase("step"):
             if self._micro == 0:

@@ -97,15 +97,21 @@ class FSDP:
         self.fast_train = False             # set by the trainer: train on the row-normalised forward
 
     # ---- step -----------------------------------------------------------------------------------
-    def train_step(self, tokens, targets, lr: Optional[float] = None) -> torch.Tensor:
-        self.flat.zero_grad()
+    def train_step(self, tokens, targets, lr: Optional[float] = None, micro=(0, 1)) -> torch.Tensor:
+        """`micro = (i, n)`: micro-batch i of n of an accumulated step. Gradients add up locally in the
+        flat buffer; the reduction and the update happen once, after the last one, scaled by 1/n."""
+        i, n_micro = micro
+        if i == 0:
+            self.flat.zero_grad()
         loss = self.model.forward_fast(tokens, targets) if self.fast_train else self.model(tokens, targets)
         loss.backward()
+        if i + 1 < n_micro:
+            return loss.detach()
         self.step_count += 1
         lr = self.lr if lr is None else lr
         if self.fused:
             with prof.phase("comm.rs_adamw_ag"):       # one kernel: reduce-scatter + AdamW + all-gather
-                self.sharded.step(lr)
+                self.sharded.step(lr, grad_scale=1.0 / n_micro)
             return loss.detach()
         # NCCL baseline: reduce-scatter, local AdamW on the shard, all-gather of fp32 then cast
         n = self.flat.numel
@@ -116,7 +122,7 @@ class FSDP:
             else:
                 dist.all_reduce(self._grad_pad, group=self.group)
                 self._shard_grad.copy_(self._grad_pad[self.lo:self.hi])
-        g = self._shard_grad / self.world
+        g = self._shard_grad / (self.world * n_micro)
         self.m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
         self.v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
         bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count

@@ -60,6 +60,37 @@ def case_fsdp(dev):
     return " ".join(notes)
 
 
+def case_accum(dev):
+    """Gradient accumulation under the wrappers: two micro-batches of half the rows, one update, equals
+    one step on the whole batch (the loss is a mean over tokens, the halves have equal size)."""
+    from ..engine.trainer import Trainer
+    from .fsdp import FSDP
+    from .tp import NeuronTP
+    rank, world = dist.get_rank(), dist.get_world_size()
+    B, T = 4, 64
+    g = torch.Generator().manual_seed(9)
+    notes = []
+    for kind in ("fsdp", "tp"):
+        data = torch.randint(0, 256, ((world if kind == "fsdp" else 1) * B, T + 1), generator=g).to(dev)
+        mine = data[rank * B:(rank + 1) * B] if kind == "fsdp" else data      # TP ranks share the batch
+        for fused in ((True, False) if dev.type == "cuda" else (False,)):
+            sds = []
+            for accum in (2, 1):
+                m = _bdh(dev, N=128 * world)
+                w = FSDP(m, lr=1e-2, fused=fused) if kind == "fsdp" else NeuronTP(m, lr=1e-2, fused=fused)
+                tr = Trainer(m, lr=1e-2, wrapper=w, grad_accum=accum)
+                for _ in range(2):
+                    for part in mine.chunk(accum, dim=0):
+                        tr.train_step(part[:, :-1], part[:, 1:])
+                assert tr.step_index == 2
+                sds.append(w.gather_state_dict())
+            tol = 3e-2 if _bf16_path(dev) else 1e-5
+            for k in sds[0]:
+                assert _rel(sds[0][k], sds[1][k]) < tol, (kind, fused, k, _rel(sds[0][k], sds[1][k]))
+            notes.append(f"{kind}:fused={fused}")
+    return " ".join(notes)
+
+
 def case_tp(dev):
     """Neuron-sharded tensor parallelism computes the same loss and gradients as one process, and
     training with it follows the same loss curve."""

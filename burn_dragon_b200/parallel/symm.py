@@ -186,7 +186,8 @@ class ShardedAdamW:
         self.grad_buf.barrier()
 
     @torch.no_grad()
-    def step(self, lr: Optional[float] = None) -> None:
+    def step(self, lr: Optional[float] = None, grad_scale: float = 1.0) -> None:
+        """`grad_scale` multiplies the 1/world of the reduction (1/n after n accumulated micro-batches)."""
         self.step_count += 1
         f = self.flags
         f["epoch"] += 1
@@ -194,7 +195,7 @@ class ShardedAdamW:
         native.ops.rs_adamw_ag(self.grad, g.ptrs, f["buf"].ptrs, g.multicast_ptr, s.ptrs, g.rank, g.world,
                                self.numel, self.master, self.m, self.v, float(self.lr if lr is None else lr),
                                self.beta1, self.beta2, self.eps, self.weight_decay, self.step_count,
-                               1.0 / self.world, f["epoch"], COLL_CTAS)
+                               float(grad_scale) / self.world, f["epoch"], COLL_CTAS)
 
     def zero_grad(self) -> None:
         self.grad.zero_()

@@ -313,17 +313,22 @@ class NeuronTP:
         self.lr = lr
         self._replicated = [self.shard.embed.weight, self.shard.lm_head]
 
-    def train_step(self, tokens, targets, lr: Optional[float] = None) -> torch.Tensor:
-        self.opt.zero_grad()
+    def train_step(self, tokens, targets, lr: Optional[float] = None, micro=(0, 1)) -> torch.Tensor:
+        """`micro = (i, n)`: micro-batch i of n of an accumulated step (one update after the last one)."""
+        i, n_micro = micro
+        if i == 0:
+            self.opt.zero_grad()
         loss = self.shard.forward_fast(tokens, targets) if self.fast_train else self.shard(tokens, targets)
         loss.backward()
+        if i + 1 < n_micro:
+            return loss.detach()
         # the replicated tensors see the same gradient on every rank up to summation order; average
         # them so the replicas cannot drift apart
         with prof.phase("comm.replicated_grads"):
             for p in self._replicated:
                 dist.all_reduce(p.grad, group=self.group)
                 p.grad.div_(self.world)
-        self.opt.step(lr=self.lr if lr is None else lr)
+        self.opt.step(lr=self.lr if lr is None else lr, grad_scale=1.0 / n_micro)
         return loss.detach()
 
     @torch.no_grad()

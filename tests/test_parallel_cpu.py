@@ -189,6 +189,13 @@ def test_parallel_wrappers_over_the_emulated_kernel_path(case):
     run_ranks(case, env={"BDH_EMULATE_KERNELS": "1"})
 
 
+@pytest.mark.parametrize("emulated", [False, True])
+def test_gradient_accumulation_under_the_wrappers(emulated):
+    """Two micro-batches of half the rows and one update equal one step on the whole batch, under
+    FSDP and under neuron TP (torch path, and the kernel path's orchestration)."""
+    run_ranks("accum", env={"BDH_EMULATE_KERNELS": "1"} if emulated else None)
+
+
 @pytest.mark.parametrize("n", [2, 4])
 def test_context_parallel_training_gradients(n):
     """Sequences split over the ranks: loss and all parameter gradients equal the single-process ones
