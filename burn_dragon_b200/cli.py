@@ -213,7 +213,7 @@ def cmd_train(args) -> int:
                     prof.enable(timers=False)
                     comm = dist_utils.max_over_ranks(prof.comm_ms(rep), dev)
                     extra.update(comm_ms=comm, comm_share=comm / max(ms, 1e-9))
-                if trainer.last_grad_norm is not None and wrapper is None:
+                if trainer.last_grad_norm is not None:
                     extra["grad_norm"] = float(trainer.last_grad_norm)
                 sp = getattr(probe, "last_sparsity", None)
                 if sp:

@@ -36,6 +36,7 @@ class Trainer:
             if fast_train and not hasattr(model, "forward_fast"):
                 raise ValueError("fast_train needs a model with a `forward_fast` path")
             wrapper.fast_train = bool(fast_train)
+            wrapper.grad_clip = grad_clip
         self.track_grad_norm = False      # set by the metrics logger on the steps it logs
         self.last_grad_norm = None
         self.wrapper = wrapper
@@ -68,6 +69,7 @@ class Trainer:
             self._micro = (self._micro + 1) % self.grad_accum
             if self._micro == 0:
                 self.step_index += 1
+                self.last_grad_norm = self.wrapper.last_grad_norm      # (only measured when clipping)
             return loss
         with prof.phase("step"):
             if self._micro == 0:

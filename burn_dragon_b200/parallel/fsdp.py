@@ -95,6 +95,8 @@ class FSDP:
             self.flat.refresh_shadow()
         self.optimizer = _ShardedOptimizerFacade(self)
         self.fast_train = False             # set by the trainer: train on the row-normalised forward
+        self.grad_clip = None               # set by the trainer: clip the global norm of the averaged gradient
+        self.last_grad_norm = None
 
     # ---- step -----------------------------------------------------------------------------------
     def train_step(self, tokens, targets, lr: Optional[float] = None, micro=(0, 1)) -> torch.Tensor:
@@ -109,9 +111,20 @@ class FSDP:
             return loss.detach()
         self.step_count += 1
         lr = self.lr if lr is None else lr
+        clip = 1.0
         if self.fused:
+            extra = 1.0
+            if self.grad_clip:
+                # the norm of the averaged gradient is needed BEFORE the fused kernel reduces it: sum the
+                # gradients with one library all-reduce; the kernel then adds up world identical copies,
+                # which the extra 1/world below takes out again
+                with prof.phase("comm.grad_norm"):
+                    dist.all_reduce(self.flat.grad, group=self.group)
+                self.last_grad_norm = self.flat.grad.norm() / (self.world * n_micro)
+                clip = float(torch.clamp(self.grad_clip / (self.last_grad_norm + 1e-6), max=1.0))
+                extra = 1.0 / self.world
             with prof.phase("comm.rs_adamw_ag"):       # one kernel: reduce-scatter + AdamW + all-gather
-                self.sharded.step(lr, grad_scale=1.0 / n_micro)
+                self.sharded.step(lr, grad_scale=clip * extra / n_micro)
             return loss.detach()
         # NCCL baseline: reduce-scatter, local AdamW on the shard, all-gather of fp32 then cast
         n = self.flat.numel
@@ -123,6 +136,12 @@ class FSDP:
                 dist.all_reduce(self._grad_pad, group=self.group)
                 self._shard_grad.copy_(self._grad_pad[self.lo:self.hi])
         g = self._shard_grad / (self.world * n_micro)
+        if self.grad_clip:
+            sq = (g * g).sum()
+            with prof.phase("comm.grad_norm"):
+                dist.all_reduce(sq, group=self.group)          # the shards partition the gradient
+            self.last_grad_norm = sq.sqrt()
+            g = g * torch.clamp(self.grad_clip / (self.last_grad_norm + 1e-6), max=1.0)
         self.m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
         self.v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
         bc1, bc2 = 1 - self.beta1 ** self.step_count, 1 - self.beta2 ** self.step_count

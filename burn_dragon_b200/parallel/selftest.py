@@ -197,7 +197,7 @@ def main() -> int:
     else:
         dist_utils.init_distributed("nccl")
         dev = torch.device("cuda", dist_utils.env_local_rank())
-    if args.case in ("fsdp", "tp", "tp_reduce", "tp_reduce_bw", "cp", "cp_train", "ckpt", "accum"):
+    if args.case in ("fsdp", "tp", "tp_reduce", "tp_reduce_bw", "cp", "cp_train", "ckpt", "accum", "clip"):
         from . import selftest_sharded
         fn = getattr(selftest_sharded, "case_" + args.case)
     else:

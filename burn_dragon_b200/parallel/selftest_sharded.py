@@ -91,6 +91,38 @@ def case_accum(dev):
     return " ".join(notes)
 
 
+def case_clip(dev):
+    """Global-norm gradient clipping under the wrappers equals clipping in one process: same norm,
+    same weights after two clipped steps."""
+    from ..engine.trainer import Trainer
+    from .fsdp import FSDP
+    from .tp import NeuronTP
+    rank, world = dist.get_rank(), dist.get_world_size()
+    B, T, clip = 2, 64, 0.05
+    g = torch.Generator().manual_seed(11)
+    notes = []
+    for kind in ("fsdp", "tp"):
+        data = torch.randint(0, 256, ((world if kind == "fsdp" else 1) * B, T + 1), generator=g).to(dev)
+        mine = data[rank * B:(rank + 1) * B] if kind == "fsdp" else data
+        for fused in ((True, False) if dev.type == "cuda" else (False,)):
+            m, one = _bdh(dev, N=128 * world), _bdh(dev, N=128 * world)
+            w = FSDP(m, lr=1e-2, fused=fused) if kind == "fsdp" else NeuronTP(m, lr=1e-2, fused=fused)
+            tr = Trainer(m, lr=1e-2, wrapper=w, grad_clip=clip)
+            tr1 = Trainer(one, lr=1e-2, grad_clip=clip)
+            for _ in range(2):
+                tr.train_step(mine[:, :-1], mine[:, 1:])
+                tr1.train_step(data[:, :-1], data[:, 1:])
+                a, b = float(tr.last_grad_norm), float(tr1.last_grad_norm)
+                assert b > 2 * clip, b                               # the clip is active
+                assert abs(a - b) < (5e-2 if _bf16_path(dev) else 1e-4) * b, (kind, fused, a, b)
+            sd = w.gather_state_dict()
+            tol = 3e-2 if _bf16_path(dev) else 1e-5
+            for k, v in one.state_dict().items():
+                assert _rel(sd[k], v.cpu()) < tol, (kind, fused, k, _rel(sd[k], v.cpu()))
+            notes.append(f"{kind}:fused={fused}")
+    return " ".join(notes)
+
+
 def case_tp(dev):
     """Neuron-sharded tensor parallelism computes the same loss and gradients as one process, and
     training with it follows the same loss curve."""

@@ -310,6 +310,8 @@ class NeuronTP:
         self.optimizer = _TPOptimizerFacade(self)
         self.eval_model = self.shard        # evaluating the shard under its hooks gives the full model's loss
         self.fast_train = False             # set by the trainer: train on the row-normalised forward
+        self.grad_clip = None               # set by the trainer: clip the global norm of the gradient
+        self.last_grad_norm = None
         self.lr = lr
         self._replicated = [self.shard.embed.weight, self.shard.lm_head]
 
@@ -328,7 +330,18 @@ class NeuronTP:
             for p in self._replicated:
                 dist.all_reduce(p.grad, group=self.group)
                 p.grad.div_(self.world)
-        self.opt.step(lr=self.lr if lr is None else lr, grad_scale=1.0 / n_micro)
+        scale = 1.0 / n_micro
+        if self.grad_clip:
+            # global norm: the sharded tensors partition their gradients over the ranks, the replicated
+            # ones are whole (and equal) on every rank
+            rep = {id(p) for p in self._replicated}
+            sq_shard = sum((p.grad.float() ** 2).sum() for p in self.shard.parameters() if id(p) not in rep and p.grad is not None)
+            sq_rep = sum((p.grad.float() ** 2).sum() for p in self._replicated)
+            with prof.phase("comm.grad_norm"):
+                dist.all_reduce(sq_shard, group=self.group)
+            self.last_grad_norm = (sq_shard + sq_rep).sqrt() * scale
+            scale = scale * float(torch.clamp(self.grad_clip / (self.last_grad_norm + 1e-6), max=1.0))
+        self.opt.step(lr=self.lr if lr is None else lr, grad_scale=scale)
         return loss.detach()
 
     @torch.no_grad()

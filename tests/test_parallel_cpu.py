@@ -196,6 +196,11 @@ def test_gradient_accumulation_under_the_wrappers(emulated):
     run_ranks("accum", env={"BDH_EMULATE_KERNELS": "1"} if emulated else None)
 
 
+def test_gradient_clipping_under_the_wrappers():
+    """Global-norm clipping under FSDP and neuron TP: same norm and same weights as one process."""
+    run_ranks("clip")
+
+
 @pytest.mark.parametrize("n", [2, 4])
 def test_context_parallel_training_gradients(n):
     """Sequences split over the ranks: loss and all parameter gradients equal the single-process ones
