@@ -36,6 +36,8 @@ BATCH_PER_GPU = 32
 def reference_arm(args) -> int:
     """The reference is a Rust crate (Burn 0.19); there is no Rust toolchain or vendored crate set
     in this image and `pip install` of the reference tree has nothing to install, so it cannot run."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0                  # under the launcher every rank runs this file: one line, from rank 0
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust/Burn crate: no cargo/rustc in the image, crates not vendored, "
                       "and it has no setup.py/pyproject.toml for pip to install"}))
