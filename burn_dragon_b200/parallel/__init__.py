@@ -15,6 +15,10 @@ def build_wrapper(model, cfg, strategy: str):
         from .fsdp import FSDP
         return FSDP(model, **kw)
     if strategy == "tp":
+        from ..models.bdh import BDH
         from .tp import NeuronTP
+        if type(model) is not BDH:
+            raise ValueError(f"parallel.strategy = \"tp\" shards the neurons of a BDH model; {type(model).__name__} "
+                             "trains under \"ddp\" or \"fsdp\"")
         return NeuronTP(model, **kw)
     raise ValueError(f"no wrapper for strategy {strategy}")
