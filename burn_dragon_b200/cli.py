@@ -175,6 +175,7 @@ def cmd_train(args) -> int:
         epoch += 1
         model.train()
         before = trainer.step_index
+        timed = False
         for batch in train_loader:
             faults.before_step(trainer.step_index + 1)
             if hb is not None:

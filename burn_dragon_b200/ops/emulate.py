@@ -10,6 +10,9 @@ GPU tests compare against the same statements.
     with emulate.kernel_path():
         loss = model(tokens, targets)          # ops.fused_bdh, launch by launch, in torch ops
 
+Every emulated GEMM launch is also bounds-checked on the host (`gemm.check_extents`: operand and
+output windows of the last batch index against the tensor shapes).
+
 `BDH_EMULATE_KERNELS=1` switches it on for a whole process (the multi-rank self tests use that).
 The reference has no counterpart: its tests run its one code path on the CPU backend
 (tests/model_paths.rs:33-91).
