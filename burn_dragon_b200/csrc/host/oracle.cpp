@@ -1,5 +1,6 @@
 // Plain C++ restatement of the canonical (recurrent) BDH forward pass, fp32 weights, double
-// accumulators, one sequence: an oracle that shares no code with the torch path or the kernels,
+// accumulators, one sequence (one thread per head, then per block of tokens): an oracle that
+// shares no code with the torch path or the kernels,
 // and the timed CPU baseline of the tiny preset. It follows the reference step by step:
 //   cur_0[t]  = LN(embed[token_t])                                        src/model/bdh.rs:318-326
 //   x         = relu(cur E_h - theta)                                     src/kernel/relu_lowrank.rs:7-37
@@ -14,6 +15,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <thread>
 #include <vector>
 
 namespace {
@@ -48,21 +50,27 @@ int bdh_oracle_forward(const float* embed, const float* encoder, const float* en
   const int Np = rotary == 2 ? 2 * N : N;
   const double two_pi = 6.283185307179586476925287;
   std::vector<double> cur(static_cast<size_t>(T) * D), nxt(static_cast<size_t>(T) * D);
-  std::vector<double> tmp(D), a(D), lna(D), mlp(D), x(static_cast<size_t>(H) * N), xy(static_cast<size_t>(H) * N), q(Np);
-  std::vector<double> rho(static_cast<size_t>(H) * Np * D);
+  std::vector<double> tmp(D);
   for (int t = 0; t < T; ++t) {
     const int64_t tok = tokens[t];
     if (tok < 0 || tok >= V) return -1;
     for (int d = 0; d < D; ++d) tmp[d] = embed[tok * D + d];
     layer_norm(tmp.data(), &cur[static_cast<size_t>(t) * D], D);
   }
+  // Per layer, the heads are independent over the whole sequence (each owns its state); only the
+  // decoder sum joins them, per token. So: phase A runs one thread per head over all tokens and
+  // leaves x*y in `xy_all`; phase B runs over blocks of tokens. The arithmetic and its order are
+  // those of the single-threaded statement, so the result does not depend on the thread count.
+  std::vector<double> xy_all(static_cast<size_t>(T) * H * N);
+  const int hw = static_cast<int>(std::max(1u, std::thread::hardware_concurrency()));
   for (int l = 0; l < L; ++l) {
-    std::fill(rho.begin(), rho.end(), 0.0);
-    for (int t = 0; t < T; ++t) {
-      const double* c = &cur[static_cast<size_t>(t) * D];
-      const double pos = static_cast<double>(pos0 + t);
-      for (int h = 0; h < H; ++h) {
-        double* xh = &x[static_cast<size_t>(h) * N];
+    auto head_pass = [&](int h) {
+      std::vector<double> xh(N), q(Np), a(D), lna(D);
+      std::vector<double> r(static_cast<size_t>(Np) * D, 0.0);
+      const double decay = rotary == 0 ? std::exp(-static_cast<double>(slopes[h])) : 1.0;
+      for (int t = 0; t < T; ++t) {
+        const double* c = &cur[static_cast<size_t>(t) * D];
+        const double pos = static_cast<double>(pos0 + t);
         for (int n = 0; n < N; ++n) {
           const float* w = encoder + (static_cast<size_t>(h) * N + n) * D;
           double s = 0.0;
@@ -91,35 +99,59 @@ int bdh_oracle_forward(const float* embed, const float* encoder, const float* en
           }
         }
         // a = q . rho ; rho = (rho + q^T v) * decay
-        double* r = &rho[static_cast<size_t>(h) * Np * D];
-        const double decay = rotary == 0 ? std::exp(-static_cast<double>(slopes[h])) : 1.0;
         for (int d = 0; d < D; ++d) a[d] = 0.0;
         for (int n = 0; n < Np; ++n) {
           const double qn = q[n];
-          double* rn = r + static_cast<size_t>(n) * D;
+          double* rn = r.data() + static_cast<size_t>(n) * D;
           if (qn != 0.0)
             for (int d = 0; d < D; ++d) a[d] += qn * rn[d];
           for (int d = 0; d < D; ++d) rn[d] = (rn[d] + qn * c[d]) * decay;
         }
         layer_norm(a.data(), lna.data(), D);
+        double* out = &xy_all[(static_cast<size_t>(t) * H + h) * N];
         for (int n = 0; n < N; ++n) {
           const float* w = encoder_v + (static_cast<size_t>(h) * N + n) * D;
           double s = 0.0;
           for (int d = 0; d < D; ++d) s += lna[d] * w[d];
           s -= relu_threshold;
-          xy[static_cast<size_t>(h) * N + n] = (s > 0.0 ? s : 0.0) * xh[n];
+          out[n] = (s > 0.0 ? s : 0.0) * xh[n];
         }
       }
-      for (int d = 0; d < D; ++d) mlp[d] = 0.0;
-      for (size_t k = 0; k < static_cast<size_t>(H) * N; ++k) {
-        const double v = xy[k];
-        if (v == 0.0) continue;
-        const float* w = decoder + k * D;
-        for (int d = 0; d < D; ++d) mlp[d] += v * w[d];
+      if (rho_out && l == L - 1)
+        std::copy(r.begin(), r.end(), rho_out + static_cast<size_t>(h) * Np * D);
+    };
+    {
+      std::vector<std::thread> pool;
+      for (int h0 = 0; h0 < H; h0 += hw) {
+        pool.clear();
+        for (int h = h0; h < std::min(H, h0 + hw); ++h) pool.emplace_back(head_pass, h);
+        for (auto& th : pool) th.join();
       }
-      layer_norm(mlp.data(), tmp.data(), D);
-      for (int d = 0; d < D; ++d) tmp[d] += c[d];
-      layer_norm(tmp.data(), &nxt[static_cast<size_t>(t) * D], D);
+    }
+    auto token_pass = [&](int t0, int t1) {
+      std::vector<double> mlp(D), tmp(D);
+      for (int t = t0; t < t1; ++t) {
+        const double* c = &cur[static_cast<size_t>(t) * D];
+        const double* xy = &xy_all[static_cast<size_t>(t) * H * N];
+        for (int d = 0; d < D; ++d) mlp[d] = 0.0;
+        for (size_t k = 0; k < static_cast<size_t>(H) * N; ++k) {
+          const double v = xy[k];
+          if (v == 0.0) continue;
+          const float* w = decoder + k * D;
+          for (int d = 0; d < D; ++d) mlp[d] += v * w[d];
+        }
+        layer_norm(mlp.data(), tmp.data(), D);
+        for (int d = 0; d < D; ++d) tmp[d] += c[d];
+        layer_norm(tmp.data(), &nxt[static_cast<size_t>(t) * D], D);
+      }
+    };
+    {
+      const int parts = std::min(hw, T);
+      std::vector<std::thread> pool;
+      for (int p = 0; p < parts; ++p)
+        pool.emplace_back(token_pass, static_cast<int>(static_cast<long long>(T) * p / parts),
+                          static_cast<int>(static_cast<long long>(T) * (p + 1) / parts));
+      for (auto& th : pool) th.join();
     }
     cur.swap(nxt);
   }
@@ -129,8 +161,6 @@ int bdh_oracle_forward(const float* embed, const float* encoder, const float* en
       for (int d = 0; d < D; ++d) s += cur[static_cast<size_t>(t) * D + d] * lm_head[static_cast<size_t>(d) * V + v];
       logits[static_cast<size_t>(t) * V + v] = static_cast<float>(s);
     }
-  if (rho_out)
-    for (size_t i = 0; i < rho.size(); ++i) rho_out[i] = rho[i];
   return 0;
 }
 
