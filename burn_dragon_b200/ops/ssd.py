@@ -12,6 +12,7 @@ The reference has no Mamba path; the spec is Mamba-2's SSD algorithm (Dao & Gu, 
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -30,6 +31,38 @@ def ssd_sequential(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: t
         h = h * torch.exp(loga[:, t]).view(Bsz, H, 1, 1) + Bm[:, t].view(Bsz, 1, N, 1) * xw[:, t].view(Bsz, H, 1, P)
         ys.append(torch.einsum("bn,bhnp->bhp", Cm[:, t], h))
     return torch.stack(ys, dim=1), h
+
+
+def ssd_backward_sequential(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                            dy: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of `ssd_sequential` (zero initial state) for an output gradient dy [B,T,H,P], written
+    out instead of differentiated: the oracle a backward kernel is compared against. The scan is dual
+    to itself:
+      d xw     = the same scan run backwards in time with B and C exchanged and the decays shifted
+                 by one step, fed with dy;
+      d log a  = reverse cumulative sum over time of (dy_t . y_t - d xw_t . xw_t), per head;
+      d C_t[n] = sum_{h,p} dy_t[h,p] h_t[h,n,p]             (forward state, step t included);
+      d B_s[n] = sum_{h,p} xw_s[h,p] G_s[h,n,p]             (reverse state G_s = C_s (x) dy_s + a_{s+1} G_{s+1}).
+    Returns (d xw, d log a, d B, d C)."""
+    Bsz, T, H, P = xw.shape
+    N = Bm.shape[-1]
+    flip = lambda t: t.flip(1)
+    y, _ = ssd_sequential(xw, loga, Bm, Cm)
+    shifted = torch.cat([torch.zeros_like(loga[:, :1]), flip(loga)[:, :-1]], dim=1)
+    dxw = flip(ssd_sequential(flip(dy), shifted, flip(Cm), flip(Bm))[0])
+    dloga = flip(torch.cumsum(flip((dy * y).sum(-1) - (dxw * xw).sum(-1)), dim=1))
+    h = torch.zeros(Bsz, H, N, P, dtype=xw.dtype, device=xw.device)
+    G = torch.zeros_like(h)
+    dC, dB = [None] * T, [None] * T
+    for t in range(T):
+        h = h * torch.exp(loga[:, t]).view(Bsz, H, 1, 1) + Bm[:, t].view(Bsz, 1, N, 1) * xw[:, t].view(Bsz, H, 1, P)
+        dC[t] = torch.einsum("bhp,bhnp->bn", dy[:, t], h)
+    for s in range(T - 1, -1, -1):
+        if s + 1 < T:
+            G = G * torch.exp(loga[:, s + 1]).view(Bsz, H, 1, 1)
+        G = G + Cm[:, s].view(Bsz, 1, N, 1) * dy[:, s].view(Bsz, H, 1, P)
+        dB[s] = torch.einsum("bhp,bhnp->bn", xw[:, s], G)
+    return dxw, dloga, torch.stack(dB, dim=1), torch.stack(dC, dim=1)
 
 
 def ssd_chunked(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
@@ -82,6 +115,83 @@ def ssd_step(xw: torch.Tensor, loga: torch.Tensor, Bm: torch.Tensor, Cm: torch.T
     return torch.einsum("bn,bhnp->bhp", Cm, h), h
 
 
+def _bc_grads_chunked(xw, loga, Bm, Cm, dy, chunk: int):
+    """d B and d C of the scan (zero initial state) in chunked form: the intra-chunk part through
+    W_ij = sum_h L_ij (dy_i . xw_j), the inter-chunk part through the forward states entering each
+    chunk (for d C) and the reverse states leaving it towards the past (for d B)."""
+    Bsz, T, H, P = xw.shape
+    N = Bm.shape[-1]
+    pad = (-T) % chunk
+    if pad:
+        f = torch.nn.functional.pad
+        xw, dy = f(xw, (0, 0, 0, 0, 0, pad)), f(dy, (0, 0, 0, 0, 0, pad))
+        loga, Bm, Cm = f(loga, (0, 0, 0, pad)), f(Bm, (0, 0, 0, pad)), f(Cm, (0, 0, 0, pad))
+    C = (T + pad) // chunk
+    x_, d_ = xw.view(Bsz, C, chunk, H, P), dy.view(Bsz, C, chunk, H, P)
+    B_, C_ = Bm.view(Bsz, C, chunk, N), Cm.view(Bsz, C, chunk, N)
+    cum = torch.cumsum(loga.view(Bsz, C, chunk, H).permute(0, 3, 1, 2), dim=-1)          # [B,H,C,Q]
+    tri = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=xw.device))
+    diff = cum.unsqueeze(-1) - cum.unsqueeze(-2)
+    L = torch.where(tri, torch.exp(diff.masked_fill(~tri, 0.0)), torch.zeros_like(diff))
+    W = torch.einsum("bhcij,bcihp,bcjhp->bcij", L, d_, x_)
+    dC = torch.einsum("bcij,bcjn->bcin", W, B_)
+    dB = torch.einsum("bcij,bcin->bcjn", W, C_)
+    to_end = torch.exp(cum[..., -1:] - cum)                                               # [B,H,C,Q]
+    chunk_decay = torch.exp(cum[..., -1])                                                 # [B,H,C]
+    S = torch.einsum("bhcj,bcjn,bcjhp->bchnp", to_end, B_, x_)                            # state each chunk adds
+    dprev = torch.einsum("bhci,bcin,bcihp->bchnp", torch.exp(cum), C_, d_)                # d (state entering chunk)
+    h = torch.zeros(Bsz, H, N, P, dtype=xw.dtype, device=xw.device)
+    prev = []
+    for c in range(C):
+        prev.append(h)
+        h = h * chunk_decay[:, :, c].view(Bsz, H, 1, 1) + S[:, c]
+    R = torch.zeros_like(h)
+    dS = [None] * C
+    for c in range(C - 1, -1, -1):
+        dS[c] = R                                        # gradient of the state chunk c adds (seen by later chunks)
+        R = dprev[:, c] + R * chunk_decay[:, :, c].view(Bsz, H, 1, 1)
+    dC = dC + torch.einsum("bhci,bcihp,bchnp->bcin", torch.exp(cum), d_, torch.stack(prev, dim=1))
+    dB = dB + torch.einsum("bhcj,bcjhp,bchnp->bcjn", to_end, x_, torch.stack(dS, dim=1))
+    return dB.reshape(Bsz, T + pad, N)[:, :T], dC.reshape(Bsz, T + pad, N)[:, :T]
+
+
+class _SSDDual(torch.autograd.Function):
+    """The scan with its backward written out (see `ssd_backward_sequential`): nothing but the inputs
+    and y is kept for the backward pass, and both y and d xw come from the forward implementation
+    (the CUDA chunk-scan kernels on a GPU), d xw through the time-reversed dual scan. Zero initial
+    state; the final state is returned without a gradient."""
+
+    @staticmethod
+    def forward(ctx, xw, loga, Bm, Cm, chunk):
+        with torch.no_grad():
+            y, hT = ssd(xw, loga, Bm, Cm, None, chunk)
+        ctx.save_for_backward(xw, loga, Bm, Cm, y)
+        ctx.chunk = chunk
+        ctx.mark_non_differentiable(hT)
+        return y.to(xw.dtype), hT
+
+    @staticmethod
+    def backward(ctx, dy, _dh):
+        xw, loga, Bm, Cm, y = ctx.saved_tensors
+        dy = dy.to(y.dtype)
+        flip = lambda t: t.flip(1).contiguous()
+        with torch.no_grad():
+            shifted = torch.cat([torch.zeros_like(loga[:, :1]), flip(loga)[:, :-1]], dim=1)
+            dxw = flip(ssd(flip(dy), shifted, flip(Cm), flip(Bm), None, ctx.chunk)[0]).to(y.dtype)
+            dloga = ((dy * y).sum(-1) - (dxw * xw).sum(-1)).flip(1).cumsum(1).flip(1)
+            dB, dC = _bc_grads_chunked(xw.to(y.dtype), loga.to(y.dtype), Bm.to(y.dtype), Cm.to(y.dtype), dy, ctx.chunk)
+        return dxw.to(xw.dtype), dloga.to(loga.dtype), dB.to(Bm.dtype), dC.to(Cm.dtype), None
+
+
+def ssd_dual(xw, loga, Bm, Cm, chunk: int = 64):
+    """Differentiable scan from a zero state whose backward is the written-out dual form (opt-in:
+    `BDH_SSD_DUAL=1` makes `ssd` use it for training calls without an initial state)."""
+    return _SSDDual.apply(xw, loga, Bm, Cm, chunk)
+
+
+_DUAL = os.environ.get("BDH_SSD_DUAL", "0") == "1"
+
+
 def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
     """Dispatch: CUDA chunk-scan kernels when no gradient is needed, else the torch chunked form."""
     ct = torch.promote_types(torch.promote_types(xw.dtype, loga.dtype), torch.promote_types(Bm.dtype, Cm.dtype))
@@ -89,6 +199,8 @@ def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
     if h0 is not None:
         h0 = h0.to(ct)
     need_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (xw, loga, Bm, Cm))
+    if need_grad and _DUAL and h0 is None:
+        return ssd_dual(xw, loga, Bm, Cm, chunk)
     if xw.shape[1] == 1 and h0 is not None and not need_grad:
         # single-token decode: one recurrence step on a private copy of the state
         y, h = ssd_step(xw[:, 0], loga[:, 0], Bm[:, 0], Cm[:, 0], h0.clone())
