@@ -133,13 +133,17 @@ def _bc_grads_chunked(xw, loga, Bm, Cm, dy, chunk: int):
     tri = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=xw.device))
     diff = cum.unsqueeze(-1) - cum.unsqueeze(-2)
     L = torch.where(tri, torch.exp(diff.masked_fill(~tri, 0.0)), torch.zeros_like(diff))
-    W = torch.einsum("bhcij,bcihp,bcjhp->bcij", L, d_, x_)
-    dC = torch.einsum("bcij,bcjn->bcin", W, B_)
-    dB = torch.einsum("bcij,bcin->bcjn", W, C_)
+    # (two-operand contractions throughout: each is one batched matmul)
+    W = (L * torch.einsum("bcihp,bcjhp->bhcij", d_, x_)).sum(dim=1)                       # [B,C,Q,Q]
+    dC = torch.matmul(W, B_)
+    dB = torch.matmul(W.transpose(-1, -2), C_)
     to_end = torch.exp(cum[..., -1:] - cum)                                               # [B,H,C,Q]
     chunk_decay = torch.exp(cum[..., -1])                                                 # [B,H,C]
-    S = torch.einsum("bhcj,bcjn,bcjhp->bchnp", to_end, B_, x_)                            # state each chunk adds
-    dprev = torch.einsum("bhci,bcin,bcihp->bchnp", torch.exp(cum), C_, d_)                # d (state entering chunk)
+    at_i = torch.exp(cum).permute(0, 2, 3, 1).unsqueeze(-1)                               # [B,C,Q,H,1]
+    x_end = x_ * to_end.permute(0, 2, 3, 1).unsqueeze(-1)                                 # xw_j decayed to its chunk's end
+    d_at = d_ * at_i                                                                      # dy_i scaled by exp(cum_i)
+    S = torch.einsum("bcjn,bcjhp->bchnp", B_, x_end)                                      # state each chunk adds
+    dprev = torch.einsum("bcin,bcihp->bchnp", C_, d_at)                                   # d (state entering chunk)
     h = torch.zeros(Bsz, H, N, P, dtype=xw.dtype, device=xw.device)
     prev = []
     for c in range(C):
@@ -150,8 +154,8 @@ def _bc_grads_chunked(xw, loga, Bm, Cm, dy, chunk: int):
     for c in range(C - 1, -1, -1):
         dS[c] = R                                        # gradient of the state chunk c adds (seen by later chunks)
         R = dprev[:, c] + R * chunk_decay[:, :, c].view(Bsz, H, 1, 1)
-    dC = dC + torch.einsum("bhci,bcihp,bchnp->bcin", torch.exp(cum), d_, torch.stack(prev, dim=1))
-    dB = dB + torch.einsum("bhcj,bcjhp,bchnp->bcjn", to_end, x_, torch.stack(dS, dim=1))
+    dC = dC + torch.einsum("bcihp,bchnp->bcin", d_at, torch.stack(prev, dim=1))
+    dB = dB + torch.einsum("bcjhp,bchnp->bcjn", x_end, torch.stack(dS, dim=1))
     return dB.reshape(Bsz, T + pad, N)[:, :T], dC.reshape(Bsz, T + pad, N)[:, :T]
 
 
