@@ -107,10 +107,11 @@ def cmd_train(args) -> int:
         train_loader = D.ResidentDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum,
                                             seed=cfg.training.seed + data_rank)
     else:
-        train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum)   # batches = micro-batches
+        train_loader = D.RandomDataLoader(ds, D.TRAIN, dev, spe * accum, total_steps * accum,   # batches = micro-batches
+                                          stream=(cfg.training.seed, data_rank))
     val_spe = ds.steps_per_epoch(D.VAL)
     valid_steps = max(1, min(max(1, total_steps // max(1, cfg.training.log_frequency)), val_spe))
-    valid_loader = D.RandomDataLoader(ds, D.VAL, dev, valid_steps, None)
+    valid_loader = D.RandomDataLoader(ds, D.VAL, dev, valid_steps, None, stream=(cfg.training.seed + 0x5EED, data_rank))
 
     run_root = Path(args.runs)
     start_epoch = 0
@@ -205,6 +206,7 @@ def cmd_train(args) -> int:
                 if t1 is not None:
                     t1.record()
                     torch.cuda.synchronize()
+                    trainer.status.check()          # the device is idle here: the status copy has landed
                     ms = dist_utils.max_over_ranks(t0.elapsed_time(t1), dev)
                 else:
                     ms = (time.perf_counter() - wall) * 1e3
@@ -230,6 +232,7 @@ def cmd_train(args) -> int:
         checkpoint()
         if trainer.step_index >= total_steps:
             break
+    trainer.status.check()
     if hb is not None:
         hb.stop(leave=False)
     if rank == 0:

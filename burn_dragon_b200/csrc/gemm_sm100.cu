@@ -2,6 +2,7 @@
 // persistent kernel instantiation that matches (operand majors, epilogue).
 #include "bdh_kernels.h"
 #include "gemm_sm100.cuh"
+#include "device_once.h"
 
 #include <mutex>
 #include <string.h>
@@ -56,15 +57,7 @@ static int make_epi_tmap(CUtensorMap* out, const void* ptr, long long rows, long
   return r == CUDA_SUCCESS ? BDH_OK : BDH_ERR_TMAP;
 }
 
-static int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
+static int num_sms() { return current_device_sms(); }
 
 template <int BN, int A_MN, int B_MN, int EPI, bool TMA_EPI>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& em, const GemmArgs& g,
@@ -80,13 +73,11 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& e
   static_assert(STAGES >= 2, "not enough shared memory for the mainloop ring");
   using L = GemmSmem<BN, STAGES, TMA_EPI, EW, EPI>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI, STAGES, TMA_EPI, EW>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
-        cudaSuccess)
-      return BDH_ERR_LAUNCH;
-    configured = true;
-  }
+  static PerDeviceOnce configured;   // the shared-memory limit is a per-device attribute
+  if (configured.run([&] {
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) == cudaSuccess ? 0 : 1;
+      }))
+    return BDH_ERR_LAUNCH;
   const long long tiles_m = (g.M + GEMM_BM - 1) / GEMM_BM;
   const long long tiles_n = (g.N + BN - 1) / BN;
   long long tiles = tiles_m * tiles_n * g.nz0 * g.nz1;

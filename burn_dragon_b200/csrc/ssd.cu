@@ -5,6 +5,7 @@
 // carried state). `states` [B, C, H, N, P] is scratch owned by the caller. The reference has no
 // Mamba path; the algorithm is Mamba-2's SSD (Dao & Gu, 2024).
 #include "bdh_kernels.h"
+#include "device_once.h"
 
 namespace bdh {
 
@@ -187,13 +188,13 @@ extern "C" int bdh_ssd_chunk_scan(const float* xw, const float* loga, const floa
   dim3 grid(C, H, B);
   const int smem_a = (SSD_Q * SSD_P + SSD_Q * SSD_N + SSD_Q) * 4;
   const int smem_c = (SSD_Q * SSD_P + 2 * SSD_Q * SSD_N + SSD_N * SSD_P + SSD_Q * SSD_Q + SSD_Q) * 4;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a) != cudaSuccess ||
-        cudaFuncSetAttribute(ssd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c) != cudaSuccess)
-      return BDH_ERR_LAUNCH;
-    configured = true;
-  }
+  static PerDeviceOnce configured;   // the shared-memory limit is a per-device attribute
+  if (configured.run([&] {
+        return (cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a) == cudaSuccess &&
+                cudaFuncSetAttribute(ssd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c) == cudaSuccess)
+                   ? 0 : 1;
+      }))
+    return BDH_ERR_LAUNCH;
   ssd_chunk_state_kernel<<<grid, SSD_THREADS, smem_a, s>>>(xw, loga, Bm, states, decay, T, H);
   const long long total = static_cast<long long>(B) * H * SSD_N * SSD_P;
   ssd_state_pass_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, s>>>(states, decay, h, C, H, total);

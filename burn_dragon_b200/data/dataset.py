@@ -110,11 +110,24 @@ class RandomDataLoader:
     (src/dataset/scheduler.rs:125-279)."""
 
     def __init__(self, dataset: TokenSequenceDataset, split: str, device=None, steps_per_epoch: int = 1,
-                 total_steps: Optional[int] = None, pin: bool = True):
+                 total_steps: Optional[int] = None, pin: bool = True, stream: Optional[Tuple[int, int]] = None):
+        """`stream = (seed, data_rank)` makes the draws counter-based: batch number i of this loader is
+        drawn from `default_rng([seed, data_rank, i])`, so a rank's sequence of batches depends only on
+        its own key and on how many batches it has drawn. A checkpoint then needs the count alone and
+        every rank of a resumed job continues its OWN sequence (restoring one rank's generator state on
+        all ranks would make them draw identical windows). Without `stream` the dataset's shared
+        generator is used and its state is what gets checkpointed (single-process runs)."""
         self.dataset, self.split, self.device, self.pin = dataset, split, device, pin
         self.steps_per_epoch = max(1, int(steps_per_epoch))
         self.total_steps = total_steps if total_steps and total_steps > 0 else None
         self.consumed = 0
+        self.stream = (int(stream[0]), int(stream[1])) if stream is not None else None
+        self.draws = 0
+
+    def _next_rng(self) -> None:
+        if self.stream is not None:
+            self.dataset.rng = np.random.default_rng([self.stream[0], self.stream[1], self.draws])
+        self.draws += 1
 
     def num_items(self) -> int:
         return self.steps_per_epoch * self.dataset.batch_size
@@ -131,14 +144,21 @@ class RandomDataLoader:
                 if self.consumed >= self.total_steps:
                     return
                 self.consumed += 1
+            self._next_rng()
             yield self.dataset.sample_batch(self.split, self.device, self.pin)
 
     def state_dict(self) -> Dict:
-        return dict(consumed=self.consumed, rng=self.dataset.rng.bit_generator.state)
+        sd = dict(consumed=self.consumed, draws=self.draws)
+        if self.stream is None:
+            sd["rng"] = self.dataset.rng.bit_generator.state
+        return sd
 
     def load_state_dict(self, sd: Dict) -> None:
         self.consumed = int(sd["consumed"])
-        if "rng" in sd:                    # (a checkpoint written with the device-resident loader has none)
+        self.draws = int(sd.get("draws", self.consumed))
+        # a generator state in the file belongs to the rank that wrote it: only a loader without a
+        # per-rank stream key (single process) takes it over
+        if "rng" in sd and self.stream is None:
             self.dataset.rng.bit_generator.state = sd["rng"]
 
 
@@ -156,6 +176,7 @@ class ResidentDataLoader(RandomDataLoader):
     def __init__(self, dataset: TokenSequenceDataset, split: str, device, steps_per_epoch: int = 1,
                  total_steps: Optional[int] = None, seed: int = 0):
         super().__init__(dataset, split, device, steps_per_epoch, total_steps, pin=False)
+        self.seed = int(seed)
         device = torch.device(device if device is not None else "cpu")
         offset, span = dataset.split_offset_and_span(split)
         small = int(dataset.tokens.max(initial=0)) < 32768
@@ -168,6 +189,10 @@ class ResidentDataLoader(RandomDataLoader):
 
     def sample_batch(self) -> SequenceBatch:
         B = self.dataset.batch_size
+        # counter-based like the host loader: batch i comes from a generator seeded with (seed, i), where
+        # `seed` already differs per data-parallel rank, so the count is all a checkpoint has to carry
+        self.generator.manual_seed((self.seed * 0x9E3779B1 + self.draws * 0x85EBCA77 + 0x632BE5AB) & 0x7FFFFFFFFFFFFFFF)
+        self.draws += 1
         starts = torch.randint(0, self.max_start + 1, (B,), generator=self.generator, device=self.tokens.device)
         win = self.tokens[starts[:, None] + self._arange[None, :]].long()
         return SequenceBatch(win[:, :-1], win[:, 1:])
@@ -181,12 +206,11 @@ class ResidentDataLoader(RandomDataLoader):
             yield self.sample_batch()
 
     def state_dict(self) -> Dict:
-        return dict(consumed=self.consumed, generator=self.generator.get_state().cpu())
+        return dict(consumed=self.consumed, draws=self.draws)
 
     def load_state_dict(self, sd: Dict) -> None:
         self.consumed = int(sd["consumed"])
-        if "generator" in sd:              # (a checkpoint written with the host loader only carries the step count)
-            self.generator.set_state(sd["generator"].cpu())
+        self.draws = int(sd.get("draws", self.consumed))
 
 
 def _clamp_train_len(n_tokens: int, ratio: float, block_size: int) -> int:

@@ -37,8 +37,12 @@ FULL = ("f32", "i32", "burn_core::record::file::BinFileRecorder<burn_core::recor
         "0.19.1", "FullPrecisionSettings")
 HALF = ("f16", "i32", "burn_core::record::file::BinFileRecorder<burn_core::record::settings::HalfPrecisionSettings>",
         "0.19.1", "HalfPrecisionSettings")
-DTYPE_F32 = 1          # observed in the reference's shipped f32 record
-DTYPE_F16 = 2          # next variant of the dtype enum; no sample file exists to confirm it
+# Variant index of burn-tensor 0.19.1's `DType` enum, which is declared in the order
+# F64, F32, Flex32, F16, BF16, ...: F32 = 1 is what the reference's shipped f32 record carries, so
+# F16 is variant 3 (2 is Flex32, a 4-byte type). No reference-written f16 file exists to pin this.
+DTYPE_F32 = 1
+DTYPE_F16 = 3
+DTYPE_F16_LEGACY = 2   # written for f16 by earlier versions of this library; accepted on read only
 PARAM_ORDER = ("embed.weight", "encoder", "encoder_v", "decoder", "lm_head")
 
 
@@ -135,6 +139,14 @@ def parse(buf: bytes) -> BurnRecord:
         params[name], pos = _read_param(buf, pos, np_dtype)
     if pos != len(buf):
         raise ValueError(f"{len(buf) - pos} trailing bytes after the last parameter")
+    # the per-tensor dtype tag has to agree with the float type the metadata names
+    ok_tags = (DTYPE_F16, DTYPE_F16_LEGACY) if meta[0] == "f16" else (DTYPE_F32,)
+    for name, p in params.items():
+        if p.dtype_tag not in ok_tags:
+            raise ValueError(f"{name}: dtype tag {p.dtype_tag} does not match a `{meta[0]}` record "
+                             f"(expected {ok_tags[0]})")
+        if p.dtype_tag == DTYPE_F16_LEGACY:
+            p.dtype_tag = DTYPE_F16
     return BurnRecord(tuple(meta), params)
 
 

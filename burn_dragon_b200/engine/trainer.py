@@ -52,6 +52,11 @@ class Trainer:
             if self.dp is not None:
                 self.dp.broadcast_parameters()
         self.base_lr = lr
+        # a kernel whose bounded wait ran out returns early and leaves its work undone: watch the status
+        # word (one 4-byte async copy per step, no synchronisation) and stop the rank when it is set
+        from ..parallel.watchdog import StatusMonitor
+        self.status = StatusMonitor()
+        self.status.enabled = next(model.parameters()).is_cuda
 
     def current_lr(self) -> float:
         return self.schedule(self.step_index) if self.schedule is not None else self.base_lr
@@ -70,6 +75,7 @@ class Trainer:
             if self._micro == 0:
                 self.step_index += 1
                 self.last_grad_norm = self.wrapper.last_grad_norm      # (only measured when clipping)
+                self.status.poll()
             return loss
         with prof.phase("step"):
             if self._micro == 0:
@@ -92,6 +98,7 @@ class Trainer:
             with prof.phase("optimizer"):
                 self.opt.step(lr=self.current_lr(), grad_scale=scale)
         self.step_index += 1
+        self.status.poll()
         return loss.detach()
 
     @torch.no_grad()

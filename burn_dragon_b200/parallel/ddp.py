@@ -26,16 +26,25 @@ class DataParallel:
         self.world = dist_utils.world_size()
         self.mode = mode if self.world > 1 else "none"
         self._symm = None
+        self.fallback_reason = None
         if self.mode == "fused":
             try:
                 from . import symm
                 self._symm = symm.SymmetricAllReduce(flat.grad, group=group)
+            except Exception as e:  # noqa: BLE001 - recorded, baseline path is used instead
+                self.fallback_reason = repr(e)
+            # the mode is a collective decision: one rank without symmetric memory sends every rank to NCCL
+            if dist_utils.all_agree(self._symm is not None, group, flat.grad.device):
                 # gradients now accumulate directly in symmetric memory, so the reduction needs no copy
                 flat.grad = self._symm.tensor[:flat.numel]
                 flat.zero_grad()
-            except Exception as e:  # noqa: BLE001 - recorded, baseline path is used instead
-                self.fallback_reason = repr(e)
+            else:
+                self.fallback_reason = self.fallback_reason or "a peer rank could not set up symmetric memory"
+                self._symm = None
                 self.mode = "nccl"
+                if dist_utils.rank() == 0:
+                    print(f"DataParallel: fused NVLink all-reduce unavailable, using NCCL ({self.fallback_reason})",
+                          flush=True)
 
     def broadcast_parameters(self) -> None:
         """Make every rank start from rank 0's weights."""

@@ -75,3 +75,16 @@ def max_over_ranks(value: float, device=None) -> float:
     t = torch.tensor([float(value)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def all_agree(ok: bool, group=None, device=None) -> bool:
+    """True only when EVERY rank of the group passes True (an all-reduce MIN of a flag). The parallel
+    wrappers use it after trying to set up the in-kernel NVLink collectives: a rank on which the
+    set-up failed must not fall back to NCCL alone while its peers launch flag-barrier kernels that
+    wait for it - either all ranks run the fused collectives or all run the library ones."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return bool(ok)
+    dev = device if device is not None else ("cuda" if dist.get_backend(group) == "nccl" else "cpu")
+    t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    return bool(int(t.item()))

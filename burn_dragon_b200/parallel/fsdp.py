@@ -72,19 +72,30 @@ class FSDP:
         dev = self.flat.master.device
         self.fused = bool(fused and dev.type == "cuda" and native.available())
         self.sharded = None
+        self.fallback_reason = None
+        want_fused = bool(fused)
         if self.fused:
             try:
                 from . import symm
                 self.sharded = symm.ShardedAdamW(self.flat.master, group, lr, weight_decay, beta1, beta2, eps)
-                # gradients and the bf16 working copy now live in symmetric memory
-                self.flat.grad = self.sharded.grad[:n]
-                self.flat.shadow = self.sharded.shadow[:n]
-                self.flat.zero_grad()
-                self.flat.register_shadow()
-                self.master, self.m, self.v = self.sharded.master, self.sharded.m, self.sharded.v
             except Exception as e:  # noqa: BLE001 - recorded; the NCCL path is used instead
                 self.fallback_reason = repr(e)
-                self.fused = False
+        if want_fused and self.world > 1:
+            # the mode is a collective decision: either every rank runs the in-kernel collectives or none does
+            from . import dist_utils
+            self.fused = dist_utils.all_agree(self.sharded is not None, group, dev)
+            if not self.fused:
+                self.fallback_reason = self.fallback_reason or "a peer rank could not set up symmetric memory"
+                self.sharded = None
+                if self.rank == 0 and dev.type == "cuda":
+                    print(f"FSDP: fused NVLink collectives unavailable, using NCCL ({self.fallback_reason})", flush=True)
+        if self.fused:
+            # gradients and the bf16 working copy now live in symmetric memory
+            self.flat.grad = self.sharded.grad[:n]
+            self.flat.shadow = self.sharded.shadow[:n]
+            self.flat.zero_grad()
+            self.flat.register_shadow()
+            self.master, self.m, self.v = self.sharded.master, self.sharded.m, self.sharded.v
         if not self.fused:
             full = torch.zeros(self.numel, dtype=torch.float32, device=dev)
             full[:n].copy_(self.flat.master)

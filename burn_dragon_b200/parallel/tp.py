@@ -68,11 +68,13 @@ class TPComm:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         mode = fused if isinstance(fused, str) else ("rs" if fused else "nccl")
+        wanted = mode != "nccl"
         if not (device.type == "cuda" and native.available()):
             mode = "nccl"
         self.multicast = False
         self._bufs: Dict = {}
         self._flags = None
+        self.fallback_reason = None
         if mode != "nccl":
             try:
                 from . import symm
@@ -81,6 +83,14 @@ class TPComm:
             except Exception as e:  # noqa: BLE001
                 self.fallback_reason = repr(e)
                 mode = "nccl"
+        if wanted:
+            # the mode is a collective decision: either every rank reduces inside its GEMM epilogues or none does
+            from . import dist_utils
+            if not dist_utils.all_agree(mode != "nccl", group, device if device.type == "cuda" else None):
+                self.fallback_reason = self.fallback_reason or "a peer rank could not set up symmetric memory"
+                mode = "nccl"
+                if self.rank == 0 and device.type == "cuda":
+                    print(f"TPComm: fused reductions unavailable, using NCCL ({self.fallback_reason})", flush=True)
         self.mode = mode
         self.fused = mode != "nccl"
         self.flags = G.F_OUT_F32 | G.F_ACCUM

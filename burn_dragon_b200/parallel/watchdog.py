@@ -113,6 +113,66 @@ def device_status(raise_on_error: bool = True) -> int:
     return code
 
 
+class StatusMonitor:
+    """Watches the kernels' status word from the training loop without synchronising the device.
+
+    A bounded in-kernel wait that gives up (a peer more than the wait limit late at a cross-rank
+    barrier, a pipeline stage that never arrived) makes its kernel return early: a collective then
+    leaves its slice unreduced and the optimizer its slice unupdated, so the step's result is wrong
+    although nothing faulted. `poll()` is called once per optimizer step: it first looks at the copy
+    of the status word it requested on the previous call (ready by now; `KernelTimeout` if non-zero),
+    then queues a new 4-byte device-to-host copy behind the step's kernels and returns. A timeout is
+    therefore seen at most one step late and costs no synchronisation. `check()` waits for the copy
+    in flight (used where the loop synchronises anyway, and at the end of a run). The rank is expected to exit on
+    `KernelTimeout`, so that a launcher restarting the group resumes from the last checkpoint.
+
+    `read_async(dst)` must queue a copy of the status word into the pinned int32 tensor `dst` and
+    return an object with `query()` / `synchronize()` (a CUDA event); tests pass a host-side fake."""
+
+    def __init__(self, read_async=None):
+        self._read_async = read_async
+        self._host = None
+        self._event = None
+        self.enabled = True
+
+    def _default_read(self, dst):
+        import torch
+        from ..ops import native
+        dst.copy_(torch.ops.bdh.status(), non_blocking=True) if native.available() else dst.zero_()
+        ev = torch.cuda.Event()
+        ev.record()
+        return ev
+
+    def _raise_if_set(self) -> None:
+        code = int(self._host[0])
+        self._event = None
+        if code:
+            from ..ops import native
+            try:
+                native.clear_status()
+            except Exception:  # noqa: BLE001 - reporting the timeout matters more than clearing it
+                pass
+            raise KernelTimeout(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}; this step's collective or "
+                                "GEMM returned early, its results are incomplete")
+
+    def poll(self) -> None:
+        if not self.enabled:
+            return
+        if self._event is not None and self._event.query():
+            self._raise_if_set()
+        if self._event is None:
+            if self._host is None:
+                import torch
+                pin = self._read_async is None and torch.cuda.is_available()
+                self._host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
+            self._event = (self._read_async or self._default_read)(self._host)
+
+    def check(self) -> None:
+        if self.enabled and self._event is not None:
+            self._event.synchronize()
+            self._raise_if_set()
+
+
 class InjectedFault(RuntimeError):
     pass
 

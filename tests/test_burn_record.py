@@ -88,6 +88,16 @@ def test_quantize_f16(tmp_path):
         assert np.allclose(rec.params[k].data.astype(np.float32), full.params[k].data, atol=2e-3, rtol=1e-3)
     m = BDH(BDHConfig(n_layer=4, n_embd=128, n_head=4, vocab_size=69, dropout=0.0))
     BR.load_into(m, out)
+    # f16 tensors carry variant 3 of burn-tensor's DType (F64, F32, Flex32, F16, ...)
+    assert all(p.dtype_tag == BR.DTYPE_F16 == 3 for p in rec.params.values())
+    # a tag that contradicts the metadata is rejected; the tag earlier versions wrote is still read
+    raw = bytearray(out.read_bytes())
+    assert raw[-1] == 3
+    raw[-1] = BR.DTYPE_F16_LEGACY
+    assert BR.parse(bytes(raw)).params["lm_head"].dtype_tag == BR.DTYPE_F16
+    raw[-1] = BR.DTYPE_F32
+    with pytest.raises(ValueError, match="dtype tag"):
+        BR.parse(bytes(raw))
 
 
 def test_varint_roundtrip():

@@ -274,9 +274,46 @@ def test_device_resident_loader_contract_and_resume():
     sd = tr.state_dict()
     rest = list(tr)
     assert len(rest) == 2 and tr.consumed == 5 and list(tr) == []          # the global cap
-    again = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=99)
+    again = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=7)
     again.load_state_dict(sd)
     resumed = list(again)
     assert len(resumed) == 2 and all(torch.equal(a.inputs, b.inputs) for a, b in zip(rest, resumed))
+    # another rank (its own seed) that restores the state rank 0 wrote continues ITS sequence, not rank 0's
+    other = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=8)
+    uninterrupted = [b.inputs for b in other] + [b.inputs for b in other]
+    other2 = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=8)
+    other2.load_state_dict(sd)
+    resumed2 = [b.inputs for b in other2]
+    assert all(torch.equal(a, b) for a, b in zip(uninterrupted[3:], resumed2))
+    assert not any(torch.equal(a, b.inputs) for a, b in zip(resumed2, resumed))
     same = D.ResidentDataLoader(ds, D.TRAIN, "cpu", steps_per_epoch=3, total_steps=5, seed=7)
     assert all(torch.equal(a.inputs, b.inputs) for a, b in zip(first, same))
+
+
+def test_host_loader_resume_keeps_per_rank_streams():
+    """Every rank of a data-parallel job restores the loader state that rank 0 wrote. With the
+    per-rank stream key the ranks keep drawing different windows after the resume, and each rank's
+    batches equal those of its uninterrupted run."""
+    import torch
+    from burn_dragon_b200.data import dataset as D
+
+    def loader(rank):
+        ds = D.synthetic_dataset(20000, block_size=16, batch_size=4, vocab=256, seed=1)
+        return D.RandomDataLoader(ds, D.TRAIN, None, steps_per_epoch=3, total_steps=9, pin=False, stream=(1337, rank))
+
+    full = {}
+    for r in (0, 1):
+        ld = loader(r)
+        full[r] = [b.inputs.clone() for b in ld] + [b.inputs.clone() for b in ld] + [b.inputs.clone() for b in ld]
+        assert len(full[r]) == 9
+    assert not any(torch.equal(a, b) for a, b in zip(full[0], full[1]))
+    # rank 0 writes the state after 3 batches; both ranks restore it
+    l0 = loader(0)
+    list(l0)
+    sd = l0.state_dict()
+    assert "rng" not in sd and sd["draws"] == 3
+    for r in (0, 1):
+        ld = loader(r)
+        ld.load_state_dict(sd)
+        resumed = [b.inputs for b in ld]
+        assert len(resumed) == 3 and all(torch.equal(a, b) for a, b in zip(resumed, full[r][3:6])), r

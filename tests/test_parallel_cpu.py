@@ -206,3 +206,46 @@ def test_context_parallel_training_gradients(n):
     """Sequences split over the ranks: loss and all parameter gradients equal the single-process ones
     (differentiable state hand-off, every positional mode)."""
     run_ranks("cp_train", n=n)
+
+
+def test_training_loop_aborts_on_a_kernel_status():
+    """A bounded wait that ran out makes its kernel return early and sets the status word. The trainer
+    polls that word once per step (asynchronously), so the loop must stop with `KernelTimeout` no later
+    than one step after the word was set. The status source is faked on the host."""
+    import torch
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.parallel.watchdog import KernelTimeout, StatusMonitor
+
+    word = {"value": 0}
+
+    class Done:
+        def query(self):
+            return True
+
+        def synchronize(self):
+            pass
+
+    def read_async(dst):
+        dst[0] = word["value"]
+        return Done()
+
+    torch.manual_seed(0)
+    model = BDH(BDHConfig(n_layer=1, n_embd=32, n_head=2, n_latent_per_head=64, vocab_size=256, dropout=0.0))
+    trainer = Trainer(model, lr=1e-3)
+    trainer.status = StatusMonitor(read_async)
+    tok = torch.randint(0, 256, (2, 17))
+    for _ in range(3):
+        trainer.train_step(tok[:, :-1], tok[:, 1:])
+    word["value"] = 5                      # "peer flag wait timed out", set while step 4 runs
+    steps_after = 0
+    with pytest.raises(KernelTimeout, match="peer flag"):
+        for _ in range(3):
+            trainer.train_step(tok[:, :-1], tok[:, 1:])
+            steps_after += 1
+    assert steps_after <= 1
+    # `check()` reports a pending copy at once (what the loop calls where it synchronises anyway)
+    mon = StatusMonitor(read_async)
+    mon.poll()
+    with pytest.raises(KernelTimeout):
+        mon.check()
