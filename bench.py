@@ -156,6 +156,19 @@ def main() -> int:
                       fused_collectives=not args.nccl_only, wrapper=wrapper)
     # tensor parallel ranks work on the same batch; data-parallel ranks on different ones
     data_world = 1 if strategy == "tp" else world
+    # the collective path that actually runs (not the one that was asked for)
+    if world == 1:
+        coll_mode, fallback = "none", None
+    elif wrapper is not None:
+        comm = getattr(wrapper, "comm", None)
+        coll_mode = ("fused-nvlink:" + str(getattr(comm, "mode", "rs_adamw_ag"))) if wrapper.fused else "nccl"
+        fallback = getattr(wrapper, "fallback_reason", None) or getattr(comm, "fallback_reason", None)
+    else:
+        coll_mode = {"fused": "fused-nvlink", "nccl": "nccl"}.get(trainer.dp.mode, trainer.dp.mode)
+        fallback = trainer.dp.fallback_reason
+    if world > 1 and not args.nccl_only and not coll_mode.startswith("fused"):
+        raise SystemExit(f"bench: the fused NVLink collectives were requested but this run fell back to {coll_mode} "
+                         f"({fallback}); pass --nccl-only to measure the library path on purpose")
 
     # synthetic uniform bytes, per-rank seed; one pinned host buffer per step so e2e copies real data
     gen = torch.Generator().manual_seed(1000 + (0 if strategy == "tp" else rank))
@@ -229,7 +242,7 @@ def main() -> int:
                        "recompute": recompute, "recomputed_layers": getattr(getattr(wrapper, "shard", model), "_recomputed_layers", None),
                        "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
                        "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
-                       "allreduce": ("nccl" if args.nccl_only else "fused-nvlink") if world > 1 else "none"},
+                       "collectives": coll_mode, "collectives_fallback": fallback},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
                     "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},

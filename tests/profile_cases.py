@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for kernel profiling and roofline timing:
 
-    python -m burn_dragon_b200.engine.profile_cases --case dq_bwd [--launches 3] [--time]
+    python tests/profile_cases.py --case dq_bwd [--launches 3] [--time]
 
 Each case launches one kernel of the BDH layer a few times on a reduced batch of the base
 configuration (8 sequences instead of 32: inputs still exceed the 126 MB L2, the device holds a few
@@ -16,8 +16,10 @@ import sys
 
 import torch
 
-from ..ops import gemm as G
-from ..ops import native
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from burn_dragon_b200.ops import gemm as G
+from burn_dragon_b200.ops import native
 
 B, T, H, N, D = 8, 512, 4, 8192, 256
 M, HN = B * T, H * N
@@ -60,7 +62,7 @@ def build(case: str):
     }
     if case in ("rownorm_fwd", "fast_attention"):
         # forward_fast attention at T = 2048 (B 8, H 4, N 2048, D 256): scores are 268 MB in bf16
-        from ..ops import rownorm_attention as RA
+        from burn_dragon_b200.ops import rownorm_attention as RA
         Bf, Tf, Nf = 8, 2048, 2048
         if case == "rownorm_fwd":
             Sc = _rnd(Bf * H * Tf, Tf, 0.1)

@@ -1,23 +1,25 @@
-"""Multi-rank self tests, run as `python -m torch.distributed.run --nproc-per-node N -m
-burn_dragon_b200.parallel.selftest --case <name>` (one process per GPU, or gloo ranks on CPU with
-`--cpu`). Each case prints `PASS <case>` on rank 0 or raises. The pytest files start these as
+"""Multi-rank self tests, run as `python -m torch.distributed.run --nproc-per-node N
+tests/ranks/selftest.py --case <name>` (one process per GPU, or gloo ranks on CPU with `--cpu`). Each case prints `PASS <case>` on rank 0 or raises. The pytest files start these as
 child processes.
 """
 from __future__ import annotations
 
 import argparse
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 import torch
 import torch.distributed as dist
 
-from . import dist_utils
+from burn_dragon_b200.parallel import dist_utils
 
 
 def _bf16_path(dev) -> bool:
     """True when the model runs the bf16 kernel path (on a GPU, or emulated launch by launch on the
     CPU with BDH_EMULATE_KERNELS=1): comparisons against fp32 runs then need bf16 tolerances."""
-    from ..ops import emulate
+    from burn_dragon_b200.ops import emulate
     return dev.type == "cuda" or emulate.active()
 
 
@@ -27,8 +29,8 @@ def _close(a, b, rtol=1e-5, atol=1e-6, what=""):
 
 
 def case_allreduce(dev):
-    from ..ops import native
-    from . import symm
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel import symm
     rank, world = dist.get_rank(), dist.get_world_size()
     for n in (4096, 1 << 20, (1 << 22) + 64 * world):
         torch.manual_seed(100 + rank)
@@ -52,8 +54,8 @@ def case_allreduce(dev):
 
 
 def case_sharded_adamw(dev):
-    from ..ops import native
-    from . import symm
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel import symm
     rank, world = dist.get_rank(), dist.get_world_size()
     n = 1 << 18
     torch.manual_seed(7)
@@ -81,7 +83,7 @@ def case_sharded_adamw(dev):
 
 
 def _bdh(dev, rot="rope"):
-    from ..models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
     torch.manual_seed(0)
     return BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
                          rotary_embedding=rot)).to(dev)
@@ -89,7 +91,7 @@ def _bdh(dev, rot="rope"):
 
 def case_ddp(dev, fused=True):
     """N-rank data parallel training equals one process training on the concatenated batch."""
-    from ..engine.trainer import Trainer
+    from burn_dragon_b200.engine.trainer import Trainer
     rank, world = dist.get_rank(), dist.get_world_size()
     B, T = 2, 64
     g = torch.Generator().manual_seed(5)
@@ -122,7 +124,7 @@ def case_ddp(dev, fused=True):
 def case_rank_exit(dev):
     """A rank that leaves between steps is noticed on the host by the others (heartbeat store),
     before they launch anything that would wait for it."""
-    from .watchdog import Heartbeat
+    from burn_dragon_b200.parallel.watchdog import Heartbeat
     rank, world = dist.get_rank(), dist.get_world_size()
     hb = Heartbeat(rank, world, interval_s=0.1, timeout_s=1.0)
     hb.start()
@@ -148,7 +150,7 @@ def case_allreduce_bw(dev):
     this library's kernel against NCCL, max over ranks, with the NVLink roofline fraction
     (bytes each GPU must send, 2*(W-1)/W * size, over 770 GB/s per direction)."""
     import json
-    from . import symm
+    from burn_dragon_b200.parallel import symm
     rank, world = dist.get_rank(), dist.get_world_size()
     out = {}
     for name, n in (("bdh_base_grads", 25_297_920), ("1GiB", 1 << 28)):
@@ -198,12 +200,12 @@ def main() -> int:
         dist_utils.init_distributed("nccl")
         dev = torch.device("cuda", dist_utils.env_local_rank())
     if args.case in ("fsdp", "tp", "tp_reduce", "tp_reduce_bw", "cp", "cp_train", "ckpt", "accum", "clip"):
-        from . import selftest_sharded
+        import selftest_sharded
         fn = getattr(selftest_sharded, "case_" + args.case)
     else:
         fn = CASES[args.case]
     note = fn(dev)
-    from . import symm
+    from burn_dragon_b200.parallel import symm
     if symm.GUARD_BYTES and args.case != "rank_exit":
         # checked configuration: once every rank has finished its launches, no collective of this case
         # may have written outside the window it was given

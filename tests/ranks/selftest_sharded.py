@@ -5,11 +5,11 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from .selftest import _bf16_path
+from selftest import _bf16_path
 
 
 def _bdh(dev, rot="rope", N=128):
-    from ..models.bdh import BDH, BDHConfig
+    from burn_dragon_b200.models.bdh import BDH, BDHConfig
     torch.manual_seed(0)
     return BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=N, vocab_size=256, dropout=0.0,
                          rotary_embedding=rot)).to(dev)
@@ -22,8 +22,8 @@ def _rel(a, b):
 def case_fsdp(dev):
     """Sharded optimizer training equals one process training on the concatenated batch, the
     gathered state dict is identical on all ranks, and optimizer state round-trips logically."""
-    from ..engine.trainer import Trainer
-    from .fsdp import FSDP
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.parallel.fsdp import FSDP
     rank, world = dist.get_rank(), dist.get_world_size()
     B, T = 2, 64
     g = torch.Generator().manual_seed(5)
@@ -63,9 +63,9 @@ def case_fsdp(dev):
 def case_accum(dev):
     """Gradient accumulation under the wrappers: two micro-batches of half the rows, one update, equals
     one step on the whole batch (the loss is a mean over tokens, the halves have equal size)."""
-    from ..engine.trainer import Trainer
-    from .fsdp import FSDP
-    from .tp import NeuronTP
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.parallel.fsdp import FSDP
+    from burn_dragon_b200.parallel.tp import NeuronTP
     rank, world = dist.get_rank(), dist.get_world_size()
     B, T = 4, 64
     g = torch.Generator().manual_seed(9)
@@ -94,9 +94,9 @@ def case_accum(dev):
 def case_clip(dev):
     """Global-norm gradient clipping under the wrappers equals clipping in one process: same norm,
     same weights after two clipped steps."""
-    from ..engine.trainer import Trainer
-    from .fsdp import FSDP
-    from .tp import NeuronTP
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.parallel.fsdp import FSDP
+    from burn_dragon_b200.parallel.tp import NeuronTP
     rank, world = dist.get_rank(), dist.get_world_size()
     B, T, clip = 2, 64, 0.05
     g = torch.Generator().manual_seed(11)
@@ -128,8 +128,8 @@ def case_clip(dev):
 def case_tp(dev):
     """Neuron-sharded tensor parallelism computes the same loss and gradients as one process, and
     training with it follows the same loss curve."""
-    from ..engine.trainer import Trainer
-    from .tp import NeuronTP, unshard_rows
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.parallel.tp import NeuronTP, unshard_rows
     rank, world = dist.get_rank(), dist.get_world_size()
     B, T = 2, 64
     g = torch.Generator().manual_seed(7)
@@ -210,7 +210,7 @@ def case_tp(dev):
 
 
 def _tp_reduce_once(comm, A, Bm, rows, cols, K, bf16):
-    from ..ops import gemm as G
+    from burn_dragon_b200.ops import gemm as G
     buf = comm.begin("t", rows, cols)
     G.gemm(A, Bm, M=rows, N=cols, K=K, flags=comm.flags, out0=buf.view, **buf.kw)
     return comm.end(buf, bf16=bf16)
@@ -219,8 +219,8 @@ def _tp_reduce_once(comm, A, Bm, rows, cols, K, bf16):
 def case_tp_reduce(dev):
     """GEMM whose epilogue is the cross-rank reduction, every mode against an fp32 matmul + NCCL sum:
     full tiles, ragged rows and columns, fp32 and bf16 results, repeated on the same buffers."""
-    from ..ops import native
-    from .tp import TPComm
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel.tp import TPComm
     rank, world = dist.get_rank(), dist.get_world_size()
     notes = []
     for mode in ("rs", "mc_red", "allreduce", False):
@@ -250,9 +250,9 @@ def case_tp_reduce_bw(dev):
     reference and the NVLink roofline (bytes a GPU must receive for an fp32 reduce-scatter plus a
     bf16 all-gather, over 770 GB/s)."""
     import json
-    from ..ops import gemm as G
-    from . import dist_utils
-    from .tp import TPComm
+    from burn_dragon_b200.ops import gemm as G
+    from burn_dragon_b200.parallel import dist_utils
+    from burn_dragon_b200.parallel.tp import TPComm
     rank, world = dist.get_rank(), dist.get_world_size()
     rows, cols, K = 65536, 1024, 1024
     torch.manual_seed(rank)
@@ -290,7 +290,7 @@ def case_tp_reduce_bw(dev):
 def case_cp(dev):
     """Context parallel forward == single-device forward over the concatenated sequence: logits of
     every segment, the state after the sequence, and a second call that continues from that state."""
-    from .cp import ContextParallel
+    from burn_dragon_b200.parallel.cp import ContextParallel
     rank, world = dist.get_rank(), dist.get_world_size()
     T = 64
     notes = []
@@ -327,10 +327,10 @@ def case_ckpt(dev):
     the unsharded layout, gathered by all ranks, written by rank 0), load into a fresh differently
     initialised model + wrapper, one more step == three uninterrupted steps."""
     import tempfile
-    from ..engine import checkpoint as CK
-    from ..engine.trainer import Trainer
-    from .fsdp import FSDP
-    from .tp import NeuronTP
+    from burn_dragon_b200.engine import checkpoint as CK
+    from burn_dragon_b200.engine.trainer import Trainer
+    from burn_dragon_b200.parallel.fsdp import FSDP
+    from burn_dragon_b200.parallel.tp import NeuronTP
     rank, world = dist.get_rank(), dist.get_world_size()
     g = torch.Generator().manual_seed(11)
     data = torch.randint(0, 256, (2, 65), generator=g).to(dev)
@@ -381,7 +381,7 @@ def case_cp_train(dev):
     """Context-parallel training: sequences split over the ranks, loss and every parameter gradient equal
     the single-process ones over the whole sequences (the gradients of later segments reach earlier
     ranks through the differentiable state hand-off)."""
-    from .cp import ContextParallel
+    from burn_dragon_b200.parallel.cp import ContextParallel
     rank, world = dist.get_rank(), dist.get_world_size()
     T = 32
     notes = []

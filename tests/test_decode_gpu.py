@@ -154,7 +154,6 @@ def test_session_streams_on_the_decode_engine():
     assert text == vocab.decode(want)
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of the stream pool: reports, does not gate the tier")
 def test_stream_pool_on_the_device_in_a_child_process():
     """Continuous batching on the GPU (graph-captured step, per-stream rotary table): streams that join
     and leave a pool produce the tokens they produce alone. Runs in a child process with its own CUDA
@@ -168,7 +167,6 @@ def test_stream_pool_on_the_device_in_a_child_process():
     assert r.returncode == 0 and r.stdout.count("PASS stream_pool") == 6, r.stdout[-1500:] + r.stderr[-1500:]
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of the captured PoPE step: reports, does not gate the tier")
 def test_pope_step_with_device_position_is_captured_and_matches_recurrence():
     """`DecodeEngine(pope_graph=True)`: the PoPE step reads its position from device memory, is captured
     in a CUDA graph, and follows the literal fp32 recurrence like the step with the fused rotation."""

@@ -164,7 +164,6 @@ def test_kernel_logits_against_the_cpp_oracle(rot):
     assert _rel(got, want) < 0.05, _rel(got, want)
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of the row-normalised mode's backward: reports, does not gate")
 @pytest.mark.parametrize("rot", ["alibi", "rope"])
 def test_forward_fast_training_step_matches_torch(rot):
     m = _model(rot)

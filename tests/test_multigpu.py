@@ -47,11 +47,9 @@ def test_checkpoint_resume_under_fsdp_and_tp():
     run_ranks("ckpt", cpu=False)
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of accumulation under the wrappers: reports, does not gate the tier")
 def test_gradient_accumulation_under_fsdp_and_tp():
     run_ranks("accum", cpu=False)
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of clipping under the wrappers: reports, does not gate the tier")
 def test_gradient_clipping_under_fsdp_and_tp():
     run_ranks("clip", cpu=False)

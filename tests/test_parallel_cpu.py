@@ -26,7 +26,7 @@ def run_job(cmd, env, timeout):
 def run_ranks(case, n=2, cpu=True, env=None, timeout=300):
     port = 29600 + (os.getpid() + hash(case)) % 300
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "burn_dragon_b200.parallel.selftest",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ranks", "selftest.py"),
            "--case", case] + (["--cpu"] if cpu else [])
     e = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
     e.update(env or {})

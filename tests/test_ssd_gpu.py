@@ -40,7 +40,6 @@ def test_mamba2_model_uses_kernels_for_prefill():
     assert torch.allclose(a, lg.detach(), atol=2e-3, rtol=1e-2)
 
 
-@pytest.mark.xfail(strict=False, reason="first GPU run of the dual-form backward: reports, does not gate the tier")
 def test_dual_form_backward_on_the_device_matches_the_written_out_oracle():
     """`ssd_dual` with the chunk-scan kernels under it (y and d xw come from the kernels) against the
     written-out float64 oracle of the gradients."""
