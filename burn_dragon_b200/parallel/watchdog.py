@@ -138,7 +138,10 @@ class StatusMonitor:
     def _default_read(self, dst):
         import torch
         from ..ops import native
-        dst.copy_(torch.ops.bdh.status(), non_blocking=True) if native.available() else dst.zero_()
+        if native.available():
+            dst.copy_(torch.ops.bdh.status()[:1], non_blocking=True)      # word 0 holds the first failure code
+        else:
+            dst.zero_()
         ev = torch.cuda.Event()
         ev.record()
         return ev

@@ -105,7 +105,7 @@ def main() -> int:
         torch.cuda.synchronize()
         ms = sorted(a.elapsed_time(b) for a, b in evs)[5]
         peaks = {}
-        p = os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")
+        p = os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")
         if os.path.exists(p):
             peaks = json.load(open(p))
         hbm, tf = peaks.get("hbm_gbs", 6650.0), peaks.get("bf16_tflops", 1590.0)
