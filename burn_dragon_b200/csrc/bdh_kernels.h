@@ -60,6 +60,43 @@ typedef struct {
 int bdh_gemm_bf16(const BdhMat* A, int a_mn_major, const BdhMat* B, int b_mn_major,
                   const BdhGemmDesc* desc, cudaStream_t stream);
 
+// ---- two chained GEMMs with the [tokens, neurons] intermediate kept on chip (dual_gemm_sm100.cu) ----
+//   Y = A1 . B1^T  (per 128-token tile and 128-neuron chunk; contraction length K1)
+//   P = epilogue(Y; in0, in1)  -> written once to the bf16 matrix P [M, H*n_per_head] (and out1)
+//   OUT[group] = sum over the group's chunks of P . B2   (B2 [H*n_per_head, N2] bf16, N2 <= 256)
+// epi 2 (ReLU + gate): P = relu(Y - theta) * in0 (dropout as in bdh_gemm_bf16);
+// epi 4 (gate backward): in0 = x, in1 = x*y, P = d y, out1 = gate gradient w.r.t. x (marked);
+// epi 5 (rotation backward): in0 = marked gate gradient, in1 = rotary table, P = d x.
+// A1 row of (token tile mt, head h) = (mt / (T/128)) * a1_b + (mt % (T/128)) * 128 + h * a1_h.
+// b1_mn = 1: B1 is indexed [k, neuron] and the k rows of tile mt start at (mt / (T/128)) * b1_b.
+// group_per_head = 0: OUT is [M, N2], summed over all heads; 1: one [M, N2] block per head.
+// The sums arrive as fp32 partial tiles in `partials` (size from bdh_dual_gemm_partial_floats);
+// bdh_dual_gemm_reduce, given the same descriptor, adds them up in a fixed order into `out`
+// (row of head h, token m: h * out_h_stride + m), as bf16, fp32 or fp32 +=.
+typedef struct {
+  int M, H, n_per_head, K1, N2, T;
+  int epi, flags, group_per_head;
+  long long a1_b, a1_h, b1_b;
+  const void* in0;
+  const void* in1;
+  void* out1;
+  long long ld_in0, ld_in1, ld_out1;
+  float alpha, theta;
+  int pos0;
+  float drop_p;
+  unsigned drop_seed;
+  float* partials;
+  long long partial_floats;   // capacity of `partials`
+  int* status;
+  int max_ctas;               // 0: one CTA per SM
+} BdhDualDesc;
+
+long long bdh_dual_gemm_partial_floats(const BdhDualDesc* desc);
+int bdh_dual_gemm(const BdhMat* A1, const BdhMat* B1, int b1_mn_major, const BdhMat* B2, const BdhMat* P,
+                  const BdhDualDesc* desc, cudaStream_t stream);
+int bdh_dual_gemm_reduce(const BdhDualDesc* desc, void* out, long long ld_out, int out_bf16, int accumulate,
+                         long long out_h_stride, cudaStream_t stream);
+
 // ---- row-wise kernels (rows of length D <= 2048, D % 8 == 0) ---------------------------------
 // y = LayerNorm(x) without affine, eps 1e-5, biased variance (reference: src/model/bdh.rs:86-89).
 int bdh_layernorm_fwd(const void* x_bf16, void* y_bf16, long long rows, int D, cudaStream_t s);

@@ -76,6 +76,68 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
 
+BdhDualDesc dual_desc(int64_t M, int64_t H, int64_t n_per_head, int64_t K1, int64_t N2, int64_t T, int64_t group_per_head,
+                      int64_t max_ctas, Tensor& partials) {
+  TORCH_CHECK(partials.is_cuda() && partials.is_contiguous() && partials.scalar_type() == at::kFloat,
+              "partials: expected a contiguous fp32 CUDA tensor");
+  BdhDualDesc d{};
+  d.M = M; d.H = H; d.n_per_head = n_per_head; d.K1 = K1; d.N2 = N2; d.T = T;
+  d.group_per_head = group_per_head;
+  d.max_ctas = max_ctas;
+  d.partials = partials.data_ptr<float>();
+  d.partial_floats = partials.numel();
+  d.status = status_word().data_ptr<int>();
+  return d;
+}
+
+int64_t dual_gemm_partial_floats(int64_t M, int64_t H, int64_t n_per_head, int64_t N2, int64_t group_per_head,
+                                 int64_t max_ctas) {
+  BdhDualDesc d{};
+  d.M = M; d.H = H; d.n_per_head = n_per_head; d.N2 = N2; d.group_per_head = group_per_head; d.max_ctas = max_ctas;
+  return bdh_dual_gemm_partial_floats(&d);
+}
+
+void dual_gemm(const Tensor& a1, const Tensor& b1, bool b1_mn, const Tensor& b2, Tensor& p, int64_t M, int64_t H,
+               int64_t n_per_head, int64_t K1, int64_t N2, int64_t T, int64_t epi, int64_t flags, int64_t group_per_head,
+               int64_t a1_b, int64_t a1_h, int64_t b1_b, const optional<Tensor>& in0, const optional<Tensor>& in1,
+               const optional<Tensor>& out1, double alpha, double theta, int64_t pos0, double drop_p, int64_t drop_seed,
+               Tensor& partials, int64_t max_ctas) {
+  c10::cuda::CUDAGuard guard(a1.device());
+  BdhMat A1 = as_mat(a1, "a1"), B1 = as_mat(b1, "b1"), B2 = as_mat(b2, "b2"), P = as_mat(p, "p");
+  BdhDualDesc d = dual_desc(M, H, n_per_head, K1, N2, T, group_per_head, max_ctas, partials);
+  d.epi = epi; d.flags = flags;
+  d.a1_b = a1_b; d.a1_h = a1_h; d.b1_b = b1_b;
+  d.in0 = opt_ptr(in0); d.in1 = opt_ptr(in1); d.out1 = const_cast<void*>(opt_ptr(out1));
+  d.ld_in0 = opt_ld(in0); d.ld_in1 = opt_ld(in1); d.ld_out1 = opt_ld(out1);
+  d.alpha = alpha; d.theta = theta; d.pos0 = pos0;
+  d.drop_p = drop_p; d.drop_seed = static_cast<unsigned>(drop_seed);
+  // every window the kernel addresses has to lie inside its tensor
+  const int64_t HN = H * n_per_head;
+  TORCH_CHECK(p.size(0) >= M && p.size(1) >= HN, "p: expected at least [M, H*n_per_head]");
+  TORCH_CHECK(b2.size(0) >= HN && b2.size(1) >= N2, "b2: expected at least [H*n_per_head, N2]");
+  for (const optional<Tensor>* t : {&in0, &out1})
+    if (t->has_value()) TORCH_CHECK((*t)->dim() == 2 && (*t)->size(0) >= M && (*t)->size(1) >= HN && (*t)->stride(1) == 1);
+  if (in1.has_value()) {
+    const bool table = epi == 5;
+    TORCH_CHECK(in1->dim() == 2 && in1->stride(1) == 1 && in1->size(0) >= (table ? T : M) &&
+                in1->size(1) >= (table ? n_per_head : HN), "in1: window leaves the tensor");
+  }
+  check_rc(bdh_dual_gemm(&A1, &B1, b1_mn, &B2, &P, &d, cur_stream()), "dual_gemm");
+}
+
+void dual_gemm_reduce(Tensor& partials, int64_t M, int64_t H, int64_t n_per_head, int64_t N2, int64_t group_per_head,
+                      int64_t max_ctas, Tensor& out, bool accumulate, int64_t out_h_stride) {
+  c10::cuda::CUDAGuard guard(out.device());
+  BdhDualDesc d = dual_desc(M, H, n_per_head, 64, N2, 128, group_per_head, max_ctas, partials);
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(1) >= N2);
+  const bool bf = out.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(bf || out.scalar_type() == at::kFloat, "out: bf16 or fp32");
+  TORCH_CHECK(out.size(0) >= (group_per_head ? (H - 1) * out_h_stride + M : M), "out: too few rows");
+  TORCH_CHECK(partials.numel() >= dual_gemm_partial_floats(M, H, n_per_head, N2, group_per_head, max_ctas));
+  check_rc(bdh_dual_gemm_reduce(&d, out.data_ptr(), out.stride(0), bf ? 1 : 0, accumulate ? 1 : 0, out_h_stride,
+                                cur_stream()), "dual_gemm_reduce");
+}
+
 void rownorm_fwd(Tensor& scores, Tensor& rnorm, int64_t T) {
   c10::cuda::CUDAGuard guard(scores.device());
   TORCH_CHECK(scores.is_cuda() && scores.dim() == 2 && scores.scalar_type() == at::kBFloat16 && scores.stride(1) == 1);
@@ -319,6 +381,13 @@ TORCH_LIBRARY(bdh, m) {
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
         "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank) -> ()");
+  m.def("dual_gemm(Tensor a1, Tensor b1, bool b1_mn, Tensor b2, Tensor(a!) p, int M, int H, int n_per_head, int K1, int N2, "
+        "int T, int epi, int flags, int group_per_head, int a1_b, int a1_h, int b1_b, Tensor? in0, Tensor? in1, "
+        "Tensor(b!)? out1, float alpha, float theta, int pos0, float drop_p, int drop_seed, Tensor(c!) partials, "
+        "int max_ctas) -> ()");
+  m.def("dual_gemm_reduce(Tensor partials, int M, int H, int n_per_head, int N2, int group_per_head, int max_ctas, "
+        "Tensor(a!) out, bool accumulate, int out_h_stride) -> ()");
+  m.def("dual_gemm_partial_floats(int M, int H, int n_per_head, int N2, int group_per_head, int max_ctas) -> int");
   m.def("layernorm_fwd(Tensor x, Tensor(a!) y) -> ()");
   m.def("layernorm_bwd(Tensor x, Tensor dy, Tensor(a!) dx, bool accumulate) -> ()");
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
@@ -356,6 +425,8 @@ TORCH_LIBRARY(bdh, m) {
 
 TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("dual_gemm", &dual_gemm);
+  m.impl("dual_gemm_reduce", &dual_gemm_reduce);
   m.impl("layernorm_fwd", &layernorm_fwd);
   m.impl("layernorm_bwd", &layernorm_bwd);
   m.impl("embed_ln_fwd", &embed_ln_fwd);
@@ -382,5 +453,6 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
 }
 TORCH_LIBRARY_IMPL(bdh, CompositeExplicitAutograd, m) {
   m.impl("status", &status);
+  m.impl("dual_gemm_partial_floats", &dual_gemm_partial_floats);
   m.impl("bounds_records", &bounds_records);
 }

@@ -65,7 +65,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& e
   // Staged epilogues run 8 epilogue warps; the mainloop ring gets what shared memory is left.
   constexpr int EW = TMA_EPI ? 8 : 4;
   constexpr int STAGE_BYTES = (GEMM_BM + BN) * GEMM_BK * 2;
-  constexpr int EPI_BYTES = TMA_EPI ? EW * 2 * (epi_num_in(EPI) + epi_num_out(EPI)) * EPI_BOX_BYTES
+  constexpr int EPI_BYTES = TMA_EPI ? EW * (2 * epi_num_in(EPI) + epi_out_bufs(EPI) * epi_num_out(EPI)) * EPI_BOX_BYTES
                                     : (EPI == EPI_STORE ? EW * EPI_RED_TILE_BYTES : 0);
   constexpr int BUDGET = 227 * 1024 - 2048 - EPI_BYTES;
   constexpr int FIT = BUDGET / STAGE_BYTES;

@@ -89,7 +89,8 @@ struct GemmArgs {
   int nz0, nz1;
   OperandOffsets a, b;
   int causal_tiles;  // 0: all tiles; 1: only tiles that touch s < t (n0 <= m0+BM-1); 2: only tiles with s > t
-  int causal_k;      // 1: contract only k < m0 + BM
+  int causal_k;      // 1: contract only k < m0 + BM; 2: only k >= m0 (m0 = first row of the tile); the K
+                     // range is never empty as long as K > the last tile's first row
   int tile_shift;    // tiles are visited in the order (t + tile_shift) mod total (reduce-scatter epilogue:
                      // each rank starts at another owner's rows so that no GPU is everybody's target)
   EpiParams epi;
@@ -662,6 +663,11 @@ __host__ __device__ constexpr int epi_num_out(int epi) {
   return (epi == EPI_RELU_GATE || epi == EPI_GATE_BWD) ? 2 : 1;
 }
 
+// Output boxes per tensor: the encoder epilogue (two or three outputs, bound by its HBM writes) keeps two, so
+// a chunk can be written while the previous chunk's stores drain; the read-heavy epilogues keep one and give
+// the shared memory to a third operand stage (the store of the previous chunk has long finished reading).
+__host__ __device__ constexpr int epi_out_bufs(int epi) { return epi == EPI_RELU ? 2 : 1; }
+
 constexpr int EPI_RED_TILE_BYTES = 32 * 32 * 4;
 
 template <int BN, int STAGES, bool TMA_EPI, int EW, int EPI>
@@ -671,10 +677,11 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int NIN = epi_num_in(EPI);
   static constexpr int NOUT = epi_num_out(EPI);
-  // staged epilogue: double-buffered 32x32 bf16 boxes; direct EPI_STORE: one 32x32 fp32 transposition
-  // tile per warp for the coalesced reduction-add paths
+  // staged epilogue: 32x32 bf16 boxes per warp, two per auxiliary input (the next chunk's inputs are in
+  // flight while this chunk is computed) and epi_out_bufs() per output; direct EPI_STORE: one 32x32 fp32 transposition tile per warp for the
+  // coalesced reduction-add paths
   static constexpr int EPI_WARP_BYTES =
-      TMA_EPI ? 2 * (NIN + NOUT) * EPI_BOX_BYTES : (EPI == EPI_STORE ? EPI_RED_TILE_BYTES : 0);
+      TMA_EPI ? (2 * NIN + epi_out_bufs(EPI) * NOUT) * EPI_BOX_BYTES : (EPI == EPI_STORE ? EPI_RED_TILE_BYTES : 0);
   static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = EPI_OFFSET + EW * EPI_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5 + 2 * EW;
@@ -742,13 +749,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t armed = 0, armed_parity = 0;  // per-stage: a load was issued / with which phase
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
-        const int k_end = g.causal_k ? min(g.K, tc.m0 + GEMM_BM) : g.K;
+        const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
         const int nkb = (k_end + GEMM_BK - 1) / GEMM_BK;
+        const int kb0 = (g.causal_k == 2) ? min(nkb, tc.m0 / GEMM_BK) : 0;
         const int a_mn = static_cast<int>(tc.m0 + tc.z0 * g.a.mn0 + tc.z1 * g.a.mn1);
         const int a_k = static_cast<int>(tc.z0 * g.a.k0 + tc.z1 * g.a.k1);
         const int b_mn = static_cast<int>(tc.n0 + tc.z0 * g.b.mn0 + tc.z1 * g.b.mn1);
         const int b_k = static_cast<int>(tc.z0 * g.b.k0 + tc.z1 * g.b.k1);
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status,
                          STATUS_TIMEOUT_SMEM_EMPTY)) {
             ok = false;
@@ -800,14 +808,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
-        const int k_end = g.causal_k ? min(g.K, tc.m0 + GEMM_BM) : g.K;
+        const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
         const int nkb = (k_end + GEMM_BK - 1) / GEMM_BK;
+        const int kb0 = (g.causal_k == 2) ? min(nkb, tc.m0 / GEMM_BK) : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, g.status,
                        STATUS_TIMEOUT_TMEM_EMPTY))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = kb0; kb < nkb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, STATUS_TIMEOUT_SMEM_FULL)) {
             ok = false;
             break;
@@ -821,7 +830,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                             : make_smem_desc(sa + k * 2048, GEMM_BK * 128, 1024);
             const uint64_t db = (B_MN == 0) ? make_smem_desc(sb + k * 32, 16, 1024)
                                             : make_smem_desc(sb + k * 2048, GEMM_BK * 128, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
@@ -892,7 +901,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int io = epi_io_mask(EPI, e.flags);
       uint8_t* wbase = smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES;
       uint8_t* in_box = wbase;                                   // [tensor][buf 0..1]
-      uint8_t* out_box = wbase + 2 * L::NIN * EPI_BOX_BYTES;     // [tensor][buf 0..1]
+      uint8_t* out_box = wbase + 2 * L::NIN * EPI_BOX_BYTES;     // [tensor]
       uint64_t* ibar = in_bar + 2 * ew;
       const uint32_t in_bytes = ((io & IO_IN0) ? EPI_BOX_BYTES : 0) + ((io & IO_IN1) ? EPI_BOX_BYTES : 0);
       const bool has_in = in_bytes != 0;
@@ -963,24 +972,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           tmem_ld_wait();
           epi_compute<EPI>(e, tc.z0, m, tc.n0 + (cbase + c) * 32, v, a0, a1, o0, o1, o2);
-          // the store issued two chunks ago must have finished reading this output buffer
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          // the stores that last used these output boxes must have finished reading them
+          constexpr int OB = epi_out_bufs(EPI);
+          const int ob = (OB == 2) ? buf : 0;
+          if (lane == 0) {
+            if (OB == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
           __syncwarp();
-          if (io & IO_OUT0) box_write_row(out_box + (0 * 2 + buf) * EPI_BOX_BYTES, lane, o0);
-          if (io & IO_OUT1) box_write_row(out_box + (1 * 2 + buf) * EPI_BOX_BYTES, lane, o1);
+          if (io & IO_OUT0) box_write_row(out_box + (0 * OB + ob) * EPI_BOX_BYTES, lane, o0);
+          if (io & IO_OUT1) box_write_row(out_box + (1 * OB + ob) * EPI_BOX_BYTES, lane, o1);
           if constexpr (EPI == EPI_RELU) {
-            if (io & IO_OUT2) box_write_row(out_box + (2 * 2 + buf) * EPI_BOX_BYTES, lane, o2);
+            if (io & IO_OUT2) box_write_row(out_box + (2 * OB + ob) * EPI_BOX_BYTES, lane, o2);
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
             if (io & IO_OUT0)
-              tma_store_2d(&em.out0, out_box + (0 * 2 + buf) * EPI_BOX_BYTES, col0 + c * 32, row0);
+              tma_store_2d(&em.out0, out_box + (0 * OB + ob) * EPI_BOX_BYTES, col0 + c * 32, row0);
             if (io & IO_OUT1)
-              tma_store_2d(&em.out1, out_box + (1 * 2 + buf) * EPI_BOX_BYTES, col1 + c * 32, row0);
+              tma_store_2d(&em.out1, out_box + (1 * OB + ob) * EPI_BOX_BYTES, col1 + c * 32, row0);
             if constexpr (EPI == EPI_RELU) {
               if (io & IO_OUT2)
-                tma_store_2d(&em.out1, out_box + (2 * 2 + buf) * EPI_BOX_BYTES,
+                tma_store_2d(&em.out1, out_box + (2 * OB + ob) * EPI_BOX_BYTES,
                              col1 + c * 32 + static_cast<int>(e.o1_imag), row0);
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -195,11 +195,14 @@ def enable(on: bool = True) -> None:
         return
     from . import native
     if on:
-        _state["saved"] = (fused_bdh.ops, native.ops, G.gemm)
+        from . import dual_gemm as DG
+        _state["saved"] = (fused_bdh.ops, native.ops, G.gemm, DG.dual)
         fused_bdh.ops = native.ops = TorchOps          # the decode engine reads `native.ops` at call time
         G.gemm = _gemm
+        DG.dual = DG.dual_reference
     else:
-        fused_bdh.ops, native.ops, G.gemm = _state.pop("saved")
+        from . import dual_gemm as DG
+        fused_bdh.ops, native.ops, G.gemm, DG.dual = _state.pop("saved")
     _state["on"] = on
 
 

@@ -15,10 +15,12 @@ Activation layouts (all bf16, row-major 2-D):
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
 
+from . import dual_gemm as DG
 from . import gemm as G
 from . import native
 from ..utils import profiling as prof
@@ -98,6 +100,17 @@ class _Dims:
         hook = getattr(model, "_dims_hook", None)
         if hook is not None:
             hook(self)
+        # the chained-GEMM kernels (the [tokens, neurons] intermediates x*y, dy, dx never re-read by the GEMM that
+        # contracts them) cover unsharded layers with D <= 256; PoPE keeps the separate launches (its rotated
+        # copy has twice the width)
+        ok = (self.comm is None and self.rot != "pope" and DG.eligible(self.M, self.T, self.N, self.D))
+        which = getattr(model, "use_dual_gemm", None)
+        if which is None:
+            which = os.environ.get("BDH_DUAL", "fwd")
+        which = set(str(which).split(",")) if which else set()
+        self.dual_fwd = ok and bool(which & {"fwd", "all", "True"})
+        self.dual_gate = ok and bool(which & {"gate", "all", "True"})
+        self.dual_dq = ok and bool(which & {"dq", "all", "True"})
 
 
 _SM_COUNT = {}
@@ -165,7 +178,9 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         q = x
         G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, out0=x, theta=d.theta)
 
-    S = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)   # tiles above the diagonal stay zero
+    # tiles above the diagonal are never written; the canonical path never reads them either (S V stops at the
+    # diagonal tile, S^T dA starts at it); the row-normalised mode transposes whole matrices and wants zeros
+    S = (torch.zeros if d.fast else torch.empty)(B * H * T, T, device=dev, dtype=torch.bfloat16)
     rnorm = None
     if d.fast:
         # forward_fast (src/model/attention.rs:142-175): S = tril(q q^T, -1) + m_h (s - t), rows L1-normalised
@@ -218,10 +233,19 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     ops.layernorm_fwd(a, lna)
     # y is not stored: the backward recovers it as xy / x
     xy = _bf16(M, d.HN, dev)
-    G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
-           c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta,
-           drop_p=d.drop_p, drop_seed=drop_seed)
-    if comm is None:
+    if d.dual_fwd:
+        # y = relu(LN(a) E_v) -> x*y -> . Dec in one kernel: x*y is written once (for the backward pass) and
+        # contracted straight from shared memory
+        mlp = _bf16(M, D, dev)
+        DG.dual(lna, W["encoder_v"], W["decoder"], xy, mlp, M=M, H=H, n_per_head=N, K1=D, N2=D, T=T,
+                epi=G.EPI_RELU_GATE, a1_b=T, a1_h=M, in0=x, theta=d.theta, drop_p=d.drop_p, drop_seed=drop_seed)
+    else:
+        G.gemm(lna, W["encoder_v"], M=M, N=N, K=D, nz=(H, 1), a_off=(M, 0, 0, 0), b_off=(N, 0, 0, 0),
+               c_off=(0, 0, N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=x, out1=xy, theta=d.theta,
+               drop_p=d.drop_p, drop_seed=drop_seed)
+    if d.dual_fwd:
+        pass
+    elif comm is None:
         sk = _split_k(-(-M // 128) * -(-D // 256), d.HN, dev)
         if sk > 1:
             mlp32 = torch.zeros(M, D, device=dev, dtype=torch.float32)
@@ -255,8 +279,16 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     dy = _bf16(M, d.HN, dev)
     dxg = _bf16(M, d.HN, dev)
     # with dropout the stored x*y is already masked and scaled, so only the 1/(1-p) on dy is explicit
-    G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg,
-           alpha=1.0 / (1.0 - d.drop_p))
+    dlna = None
+    if d.dual_gate:
+        # gate backward and d LN(a) = dy . E_v in one kernel (dy is written once, for the weight gradient)
+        dlna = _bf16(H * M, D, dev)
+        DG.dual(dmlp, W["decoder"], W["encoder_v"], dy, dlna, M=M, H=H, n_per_head=N, K1=D, N2=D, T=T,
+                epi=G.EPI_GATE_BWD, group_per_head=True, a1_b=T, a1_h=0, in0=x, in1=xy, out1=dxg,
+                alpha=1.0 / (1.0 - d.drop_p), out_h_stride=M)
+    else:
+        G.gemm(dmlp, W["decoder"], M=M, N=d.HN, K=D, epi=G.EPI_GATE_BWD, in0=x, in1=xy, out0=dy, out1=dxg,
+               alpha=1.0 / (1.0 - d.drop_p))
     wtiles = -(-d.HN // 128) * -(-D // 256)
     sk = _split_k(wtiles, M, dev)
     wflags = G.F_OUT_F32 | (G.F_ATOMIC if sk > 1 else G.F_ACCUM)
@@ -267,7 +299,9 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     G.gemm(dy, lna, M=N, N=D, K=km, a_mn=True, b_mn=True, nz=(H, sk), a_off=(N, 0, 0, km), b_off=(0, 0, M, km),
            c_off=(N, 0, 0, 0), flags=wflags, out0=grads["encoder_v"])
     comm = d.comm
-    if comm is None:
+    if dlna is not None:
+        pass
+    elif comm is None:
         dlna = _bf16(H * M, D, dev)
         G.gemm(dy, W["encoder_v"], M=M, N=D, K=N, b_mn=True, nz=(H, 1), a_off=(0, 0, N, 0), b_off=(0, 0, N, 0),
                c_off=(M, 0, 0, 0), out0=dlna)
@@ -303,12 +337,20 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
         pbuf = comm.begin("dcur", M, D, launches=2)        # partial sums over the neuron shards: dV and the encoder path
         part, pflags, pkw = pbuf.view, comm.flags, pbuf.kw
     # all heads in one launch: every (head, batch) problem adds its [T, D] tile into the rows of its batch
+    # (row block s only needs t >= s: the contraction starts at the tile's first row; in the row-normalised
+    # mode S holds zeros above the diagonal, elsewhere that part is never written and must not be read)
     G.gemm(S, da, M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(0, 0, T, H * T), b_off=(0, 0, M, T),
            c_off=(0, T, 0, 0), flags=(pflags & ~G.F_ACCUM) | (G.F_ATOMIC if pflags & G.F_ACCUM else 0), out0=part,
-           **pkw)
+           causal_k=2, **pkw)
     # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
     dx = _bf16(M, d.HN, dev)
-    if d.rot == "pope":
+    if d.dual_dq:
+        # dq = Gs q, rotation undone, + gate gradient, ReLU mask, and d cur += dx . E in one kernel
+        rope = d.rot == "rope"
+        DG.dual(Gs, q, W["encoder"], dx, dcur, M=M, H=H, n_per_head=N, K1=T, N2=D, T=T, epi=G.EPI_DQ_BWD,
+                flags=(G.F_ROPE | G.F_TABLE) if rope else 0, a1_b=H * T, a1_h=T, b1_mn=True, b1_b=T, in0=dxg,
+                in1=d.table(pos0) if rope else None, pos0=pos0, accumulate=True)
+    elif d.rot == "pope":
         dq = _bf16(M, d.HNp, dev)
         G.gemm(Gs, q, M=T, N=Np, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(Np, 0, 0, T),
                c_off=(0, T, Np, 0), out0=dq)
@@ -321,7 +363,9 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     del dxg
     G.gemm(dx, cur, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
            flags=wflags, out0=grads["encoder"])
-    if comm is None:
+    if d.dual_dq:
+        pass
+    elif comm is None:
         sk2 = _split_k(-(-M // 128) * -(-D // 256), d.HN, dev)
         k2 = d.HN // sk2
         G.gemm(dx, W["encoder"], M=M, N=D, K=k2, b_mn=True, nz=(sk2, 1), a_off=(0, 0, k2, 0), b_off=(0, 0, k2, 0),

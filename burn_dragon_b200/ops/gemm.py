@@ -195,12 +195,17 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
         for z0 in range(nz[0]):
             A = _window(a, a_mn, a_off[0] * z0 + a_off[1] * z1, M, a_off[2] * z0 + a_off[3] * z1, K)
             B = _window(b, b_mn, b_off[0] * z0 + b_off[1] * z1, N, b_off[2] * z0 + b_off[3] * z1, K)
-            if causal_k:
+            if causal_k == 1:
                 # row block mb only contracts k < mb*128 + 128
                 acc = torch.zeros(M, N, device=dev)
                 for m0 in range(0, M, 128):
                     ke = min(K, m0 + 128)
                     acc[m0:m0 + 128] = A[m0:m0 + 128, :ke] @ B[:, :ke].t()
+            elif causal_k == 2:
+                # row block mb only contracts k >= mb*128
+                acc = torch.zeros(M, N, device=dev)
+                for m0 in range(0, M, 128):
+                    acc[m0:m0 + 128] = A[m0:m0 + 128, m0:] @ B[:, m0:].t()
             else:
                 acc = A @ B.t()
             r0 = c_off[0] * z0 + c_off[1] * z1

@@ -19,6 +19,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from burn_dragon_b200.ops import gemm as G
+from burn_dragon_b200.ops import dual_gemm as DG
 from burn_dragon_b200.ops import native
 
 B, T, H, N, D = 8, 512, 4, 8192, 256
@@ -60,6 +61,27 @@ def build(case: str):
         "wgrad": (lambda: G.gemm(act, cur, M=HN, N=D, K=M, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ACCUM,
                                  out0=torch.zeros(HN, D, device="cuda")), gemm_fl, big),
     }
+    if case.startswith("dual_"):
+        # the chained-GEMM kernels at the base configuration's shapes (8 sequences); bytes = the [M, H*N] tensors
+        # each launch has to move once, FLOPs = both GEMMs
+        lna, xy, dmlp = _rnd(H * M, D), torch.empty(M, HN, device="cuda", dtype=torch.bfloat16), _rnd(M, D)
+        mlp = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+        dlna = torch.empty(H * M, D, device="cuda", dtype=torch.bfloat16)
+        dcur = torch.zeros(M, D, device="cuda")
+        W2 = _rnd(HN, D, 0.02)
+        ctas = int(os.environ.get("BDH_CASE_CTAS", "0"))       # 0: one CTA per SM
+        dual = {
+            "dual_fwd": (lambda: DG.dual(lna, W, W2, xy, mlp, M=M, H=H, n_per_head=N, K1=D, N2=D, T=T,
+                                         epi=G.EPI_RELU_GATE, a1_b=T, a1_h=M, in0=act, max_ctas=ctas), 2 * gemm_fl, 2 * big),
+            "dual_gate_bwd": (lambda: DG.dual(dmlp, W, W2, xy, dlna, M=M, H=H, n_per_head=N, K1=D, N2=D, T=T,
+                                              epi=G.EPI_GATE_BWD, group_per_head=True, a1_b=T, a1_h=0, in0=act,
+                                              in1=act, out1=q, out_h_stride=M, max_ctas=ctas), 2 * gemm_fl, 4 * big),
+            "dual_dq_bwd": (lambda: DG.dual(S, act, W2, xy, dcur, M=M, H=H, n_per_head=N, K1=T, N2=D, T=T,
+                                            epi=G.EPI_DQ_BWD, flags=G.F_ROPE | G.F_TABLE, a1_b=H * T, a1_h=T,
+                                            b1_mn=True, b1_b=T, in0=act, in1=tab, accumulate=True, max_ctas=ctas),
+                            att_fl + gemm_fl, 3 * big),
+        }
+        return dual[case]
     if case in ("rownorm_fwd", "fast_attention"):
         # forward_fast attention at T = 2048 (B 8, H 4, N 2048, D 256): scores are 268 MB in bf16
         from burn_dragon_b200.ops import rownorm_attention as RA
