@@ -161,7 +161,8 @@ def main() -> int:
         coll_mode, fallback = "none", None
     elif wrapper is not None:
         comm = getattr(wrapper, "comm", None)
-        coll_mode = ("fused-nvlink:" + str(getattr(comm, "mode", "rs_adamw_ag"))) if wrapper.fused else "nccl"
+        coll_mode = ("fused-nvlink:" + str(getattr(comm, "mode", "wgrad-epilogue red.add + shard_adamw_ag"))) \
+            if wrapper.fused else "nccl"
         fallback = getattr(wrapper, "fallback_reason", None) or getattr(comm, "fallback_reason", None)
     else:
         coll_mode = {"fused": "fused-nvlink", "nccl": "nccl"}.get(trainer.dp.mode, trainer.dp.mode)
@@ -242,7 +243,10 @@ def main() -> int:
                        "recompute": recompute, "recomputed_layers": getattr(getattr(wrapper, "shard", model), "_recomputed_layers", None),
                        "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
                        "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
-                       "collectives": coll_mode, "collectives_fallback": fallback},
+                       "collectives": coll_mode, "collectives_fallback": fallback,
+                       # fully sharded state: what one rank holds between steps (bytes)
+                       "persistent_bytes_per_rank": (wrapper.state.persistent_bytes()
+                                                     if getattr(wrapper, "state", None) is not None else None)},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
                     "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},

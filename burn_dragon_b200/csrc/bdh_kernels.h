@@ -195,6 +195,16 @@ int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag_ptrs, long
                     const long long* shadow_ptrs, int rank, int world, long long n_floats, float* master,
                     float* m, float* v, float lr, float beta1, float beta2, float eps, float wd, int step,
                     float grad_scale, unsigned epoch, int ctas, int* status, cudaStream_t s);
+// Fully sharded AdamW: `gacc` is this rank's 1/world gradient slice, filled over NVLink by every rank's
+// weight-gradient GEMM epilogues (flags 1024 | 512: red.add into the owner's block). The kernel waits for all
+// ranks, applies AdamW to the local slices of master / m / v, writes the refreshed bf16 parameters into every
+// rank's working copy (shadow_ptrs), clears gacc, and waits for all ranks again. Segment s (n_segs <= 4, one
+// per sharded parameter) covers local elements [seg_lo[s], seg_lo[s+1]) and starts at bf16 element seg_dst[s]
+// of the working copy; all offsets are multiples of 4.
+int bdh_shard_adamw_ag(const long long* flag_ptrs, const long long* shadow_ptrs, int rank, int world, float* gacc,
+                       float* master, float* m, float* v, int n_segs, const long long* seg_lo, const long long* seg_dst,
+                       float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,
+                       unsigned epoch, int ctas, int* status, cudaStream_t s);
 // Device-side barrier over all ranks (bounded wait); uses slot 0 of the symmetric flag buffer.
 int bdh_rank_barrier(const long long* flag_ptrs, int rank, int world, unsigned epoch, int* status, cudaStream_t s);
 // Waits (at most limit_ns) for *flag to reach `value`; on expiry writes the timeout status and returns.

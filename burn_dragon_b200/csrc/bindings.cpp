@@ -278,6 +278,23 @@ void rs_adamw_ag(const Tensor& anchor, at::IntArrayRef grad_ptrs, at::IntArrayRe
                            (unsigned)epoch, ctas, status_word().data_ptr<int>(), cur_stream()), "rs_adamw_ag");
 }
 
+void shard_adamw_ag(at::IntArrayRef flag_ptrs, at::IntArrayRef shadow_ptrs, int64_t rank, int64_t world, Tensor& gacc,
+                    Tensor& master, Tensor& m, Tensor& v, at::IntArrayRef seg_lo, at::IntArrayRef seg_dst, double lr,
+                    double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale, int64_t epoch,
+                    int64_t ctas) {
+  c10::cuda::CUDAGuard guard(master.device());
+  TORCH_CHECK((int64_t)flag_ptrs.size() == world && (int64_t)shadow_ptrs.size() == world);
+  TORCH_CHECK(seg_lo.size() == seg_dst.size() + 1 && !seg_dst.empty() && seg_dst.size() <= 4);
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&gacc, &master, &m, &v})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat && t->numel() >= seg_lo.back());
+  auto f = as_ptrs(flag_ptrs), sh = as_ptrs(shadow_ptrs);
+  std::vector<long long> lo(seg_lo.begin(), seg_lo.end()), dst(seg_dst.begin(), seg_dst.end());
+  check_rc(bdh_shard_adamw_ag(f.data(), sh.data(), rank, world, gacc.data_ptr<float>(), master.data_ptr<float>(),
+                              m.data_ptr<float>(), v.data_ptr<float>(), (int)dst.size(), lo.data(), dst.data(), lr, beta1,
+                              beta2, eps, wd, step, grad_scale, (unsigned)epoch, ctas, status_word().data_ptr<int>(),
+                              cur_stream()), "shard_adamw_ag");
+}
+
 void decode_state_update(const Tensor& q, const Tensor& v, Tensor& rho, Tensor& a, const optional<Tensor>& slopes) {
   c10::cuda::CUDAGuard guard(q.device());
   TORCH_CHECK(rho.dim() == 4 && rho.is_contiguous() && rho.scalar_type() == at::kFloat);
@@ -408,6 +425,9 @@ TORCH_LIBRARY(bdh, m) {
   m.def("rs_adamw_ag(Tensor anchor, int[] grad_ptrs, int[] flag_ptrs, int grad_mc, int[] shadow_ptrs, int rank, "
         "int world, int n_floats, Tensor(a!) master, Tensor(b!) m, Tensor(c!) v, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
+  m.def("shard_adamw_ag(int[] flag_ptrs, int[] shadow_ptrs, int rank, int world, Tensor(a!) gacc, Tensor(b!) master, "
+        "Tensor(c!) m, Tensor(d!) v, int[] seg_lo, int[] seg_dst, float lr, float beta1, float beta2, float eps, "
+        "float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
   m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
@@ -440,6 +460,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("allreduce_scale", &allreduce_scale);
   m.impl("gather_blocks", &gather_blocks);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
+  m.impl("shard_adamw_ag", &shard_adamw_ag);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
   m.impl("pope_bwd", &pope_bwd);
   m.impl("rank_barrier", &rank_barrier);

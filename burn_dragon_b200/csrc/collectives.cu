@@ -163,6 +163,56 @@ rs_adamw_ag_kernel(CollPeers p, CollPeers q, float* master, float* m, float* v, 
   cta_barrier_all_ranks(p, flag_value(epoch, 2), status);
 }
 
+// Fully sharded update: this rank's gradient accumulator `gacc` (fp32, the 1/world slice every rank's
+// weight-gradient epilogues added into over NVLink) feeds AdamW on the matching slices of master / m / v,
+// the refreshed bf16 parameters go to every rank's working copy, and the accumulator is cleared for the
+// next step. The slice is a list of segments (one per sharded parameter): segment s covers local elements
+// [seg_lo[s], seg_lo[s+1]) and lands at bf16 element seg_dst[s] of the working copy. The barrier in front
+// makes every rank's additions visible, the one behind makes every rank's parameter stores complete.
+struct ShardSegs {
+  long long lo4[5];     // local float4 offsets of the segments (n + 1 entries)
+  long long dst4[4];    // destination offset in the working copy, in units of 4 bf16
+  int n;
+};
+
+__global__ void __launch_bounds__(COLL_THREADS)
+shard_adamw_ag_kernel(CollPeers f, CollPeers q, float* gacc, float* master, float* m, float* v, ShardSegs segs,
+                      AdamArgs a, uint32_t epoch, int* status) {
+  if (!cta_barrier_all_ranks(f, flag_value(epoch, 1), status)) return;
+  const long long n4 = segs.lo4[segs.n];
+  for (long long j = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; j < n4;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int sgi = 0;
+#pragma unroll
+    for (int k = 1; k < 4; ++k)
+      if (k < segs.n && j >= segs.lo4[k]) sgi = k;
+    float4 g = reinterpret_cast<float4*>(gacc)[j];
+    reinterpret_cast<float4*>(gacc)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 w = reinterpret_cast<float4*>(master)[j];
+    float4 mm = reinterpret_cast<float4*>(m)[j];
+    float4 vv = reinterpret_cast<float4*>(v)[j];
+    float* gp = &g.x; float* wp = &w.x; float* mp = &mm.x; float* vp = &vv.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float gk = gp[k] * a.gscale;
+      mp[k] = a.b1 * mp[k] + (1.f - a.b1) * gk;
+      vp[k] = a.b2 * vp[k] + (1.f - a.b2) * gk * gk;
+      wp[k] = wp[k] * (1.f - a.lr * a.wd) - a.lr * (mp[k] / a.bc1) / (sqrtf(vp[k] / a.bc2) + a.eps);
+    }
+    reinterpret_cast<float4*>(master)[j] = w;
+    reinterpret_cast<float4*>(m)[j] = mm;
+    reinterpret_cast<float4*>(v)[j] = vv;
+    uint2 u;
+    u.x = pack_bf16x2(w.x, w.y);
+    u.y = pack_bf16x2(w.z, w.w);
+    const long long dst = segs.dst4[sgi] + (j - segs.lo4[sgi]);
+#pragma unroll
+    for (int r = 0; r < COLL_MAX_RANKS; ++r)
+      if (r < q.world) static_cast<uint2*>(q.buf[r])[dst] = u;
+  }
+  cta_barrier_all_ranks(f, flag_value(epoch, 2), status);
+}
+
 // Second half of a reduce-scatter done by GEMM epilogues (EPI_F_PEER_RS): slot s of this rank's
 // buffer `p` holds rank s's partial sums for the block of rows this rank owns (per4 float4 each).
 // The owner adds the slots up (local reads, fixed order: the result does not depend on timing) and
@@ -278,6 +328,29 @@ extern "C" int bdh_rs_adamw_ag(const long long* grad_ptrs, const long long* flag
   AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
              grad_scale};
   rs_adamw_ag_kernel<<<ctas, COLL_THREADS, 0, s>>>(p, q, master, m, v, n_floats / 4, a, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
+extern "C" int bdh_shard_adamw_ag(const long long* flag_ptrs, const long long* shadow_ptrs, int rank, int world,
+                                  float* gacc, float* master, float* m, float* v, int n_segs, const long long* seg_lo,
+                                  const long long* seg_dst, float lr, float beta1, float beta2, float eps, float wd,
+                                  int step, float grad_scale, unsigned epoch, int ctas, int* status, cudaStream_t s) {
+  if (world < 1 || world > COLL_MAX_RANKS || ctas < 1 || step < 1 || n_segs < 1 || n_segs > 4) return BDH_ERR_ARGUMENT;
+  ShardSegs segs;
+  segs.n = n_segs;
+  for (int i = 0; i <= n_segs; ++i) {
+    if (seg_lo[i] % 4) return BDH_ERR_ALIGNMENT;
+    segs.lo4[i] = seg_lo[i] / 4;
+  }
+  for (int i = 0; i < n_segs; ++i) {
+    if (seg_dst[i] % 4) return BDH_ERR_ALIGNMENT;
+    segs.dst4[i] = seg_dst[i] / 4;
+  }
+  CollPeers f, q;
+  fill_peers(f, flag_ptrs, flag_ptrs, 0, rank, world);
+  fill_peers(q, shadow_ptrs, nullptr, 0, rank, world);
+  AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), grad_scale};
+  shard_adamw_ag_kernel<<<ctas, COLL_THREADS, 0, s>>>(f, q, gacc, master, m, v, segs, a, epoch, status);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 

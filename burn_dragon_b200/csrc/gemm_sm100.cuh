@@ -46,7 +46,8 @@ enum EpiFlags : int {
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
   EPI_F_ROWDECAY = 2048,   // EPI_STORE: scale row m by exp(-slopes[z0] * m) (decayed carry-in of a recurrent state)
-  EPI_F_PEER_RS = 1024,    // EPI_STORE fp32: reduce-scatter epilogue. Output rows are split into blocks of
+  EPI_F_PEER_RS = 1024,    // EPI_STORE fp32: reduce-scatter epilogue (with EPI_F_ATOMIC: add into the owner's
+                           // single block instead of storing into a per-rank slot). Output rows are split into blocks of
                            // peer_rows, block b is owned by rank b. The tile is stored through the owner's
                            // peer mapping peer_out[owner] into the slot this rank has there: the owner's
                            // buffer is [world slots][peer_rows][ld] and slot s receives rank s's partial
@@ -420,10 +421,14 @@ __device__ __forceinline__ float epi_store_scale(const EpiParams& e, int z0, int
 }
 
 // Address of output row `row` inside the slot this rank owns in the buffer of the row's owner.
+// With EPI_F_ATOMIC the owner keeps ONE block of peer_rows rows that every rank adds into (red.add over
+// NVLink): the sharded gradient accumulator of fully sharded data parallelism, where each weight-gradient
+// GEMM of each layer adds its tiles straight into the 1/world slice its owner holds.
 __device__ __forceinline__ float* peer_slot_row(const EpiParams& e, long long row) {
   long long owner = row / e.peer_rows;
   if (owner >= e.peer_world) owner = e.peer_world - 1;
-  return e.peer_out[owner] + (e.peer_rank * e.peer_rows + (row - owner * e.peer_rows)) * e.ld_out0;
+  const long long slot = (e.flags & EPI_F_ATOMIC) ? 0 : e.peer_rank * e.peer_rows;
+  return e.peer_out[owner] + (slot + (row - owner * e.peer_rows)) * e.ld_out0;
 }
 
 __device__ __forceinline__ void red_add_f32x4(float* p, const float4& u, int flags) {
@@ -454,7 +459,9 @@ __device__ __forceinline__ void send_tile_coalesced(const EpiParams& e, long lon
     const int row = 4 * j + sub;
     const float4 u = scratch[row * 8 + (ch ^ (row & 7))];
     const long long rr = r0 + row;
-    if (e.flags & EPI_F_PEER_RS)
+    if ((e.flags & EPI_F_PEER_RS) && (e.flags & EPI_F_ATOMIC))
+      red_add_f32x4(peer_slot_row(e, rr) + c + 4 * ch, u, e.flags);
+    else if (e.flags & EPI_F_PEER_RS)
       *reinterpret_cast<float4*>(peer_slot_row(e, rr) + c + 4 * ch) = u;
     else
       red_add_f32x4(static_cast<float*>(e.out0) + rr * e.ld_out0 + c + 4 * ch, u, e.flags);
@@ -491,6 +498,11 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
           if (i < valid)
             asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p + i), "f"(v[i]) : "memory");
       }
+    } else if ((e.flags & EPI_F_PEER_RS) && (e.flags & EPI_F_ATOMIC)) {
+      float* p = peer_slot_row(e, r) + c;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < valid) atomicAdd(p + i, v[i]);
     } else if (e.flags & EPI_F_PEER_RS) {
       float* p = peer_slot_row(e, r) + c;
       if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {

@@ -188,10 +188,14 @@ def load_checkpoint(model, model_path: Path, state_path: Optional[Path], trainer
     state: Dict[str, Any] = {}
     if state_path is not None and Path(state_path).exists():
         state = torch.load(state_path, map_location="cpu", weights_only=False)
+    # a wrapper that keeps no full fp32 parameters (fully sharded data parallelism) takes the weights itself
+    take = getattr(getattr(trainer, "wrapper", None), "load_weights", None)
     if "model" in state:
-        model.load_state_dict(state["model"])
+        if not (take and take(state["model"])):
+            model.load_state_dict(state["model"])
     elif Path(model_path).exists():
-        BR.load_into(model, model_path)
+        if not (take and take(BR.to_state_dict(BR.load(model_path)))):
+            BR.load_into(model, model_path)
     else:
         raise FileNotFoundError(model_path)
     if trainer is not None and state:

@@ -93,6 +93,9 @@ class _Dims:
             self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
         self.cp = getattr(model, "_cp", None)        # context-parallel hook (parallel/cp.py)
+        # fully sharded data parallelism: the weight gradients of the [H*N, D] weights go to their owners' slices
+        # from the GEMM epilogues (parallel/fsdp.py: GradSink) instead of into local full-size tensors
+        self.sink = getattr(model, "_grad_sink", None)
         # dropout on x*y (training only): a fresh mask seed per call, one derived seed per layer
         self.drop_p = float(c.dropout) if (model.training and c.dropout > 0) else 0.0
         model._drop_calls = getattr(model, "_drop_calls", 0) + 1
@@ -266,6 +269,13 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     return out, saved, rho_out
 
 
+def _wgrad_target(d: _Dims, grads, name: str, flags: int):
+    """-> (out0, flags, extra keyword arguments) of the weight-gradient GEMM of `name`."""
+    if d.sink is not None:
+        return d.sink.launch(name, flags)
+    return grads[name], flags, {}
+
+
 def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     """dout: fp32 [M, D] gradient of the layer output. Returns fp32 [M, D] gradient of the layer input.
     Weight gradients are accumulated into grads['encoder'|'encoder_v'|'decoder'] (fp32)."""
@@ -293,11 +303,13 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     sk = _split_k(wtiles, M, dev)
     wflags = G.F_OUT_F32 | (G.F_ATOMIC if sk > 1 else G.F_ACCUM)
     km = M // sk
+    o, fl, kw = _wgrad_target(d, grads, "decoder", wflags)
     G.gemm(xy, dmlp, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
-           flags=wflags, out0=grads["decoder"])
+           flags=fl, out0=o, **kw)
     # y = relu(LN(a) E_v)
+    o, fl, kw = _wgrad_target(d, grads, "encoder_v", wflags)
     G.gemm(dy, lna, M=N, N=D, K=km, a_mn=True, b_mn=True, nz=(H, sk), a_off=(N, 0, 0, km), b_off=(0, 0, M, km),
-           c_off=(N, 0, 0, 0), flags=wflags, out0=grads["encoder_v"])
+           c_off=(N, 0, 0, 0), flags=fl, out0=o, **kw)
     comm = d.comm
     if dlna is not None:
         pass
@@ -361,8 +373,9 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
                c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=(G.F_ROPE | G.F_TABLE) if rope else 0, in0=dxg,
                in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     del dxg
+    o, fl, kw = _wgrad_target(d, grads, "encoder", wflags)
     G.gemm(dx, cur, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
-           flags=wflags, out0=grads["encoder"])
+           flags=fl, out0=o, **kw)
     if d.dual_dq:
         pass
     elif comm is None:
@@ -482,8 +495,8 @@ class _FusedLoss(torch.autograd.Function):
     def backward(ctx, grad_out):
         d, W, saved, cur, dlogits = ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits
         dev = cur.device
-        grads = {k: torch.zeros(d.HN, d.D, device=dev, dtype=torch.float32)
-                 for k in ("encoder", "encoder_v", "decoder")}
+        grads = None if d.sink is not None else {k: torch.zeros(d.HN, d.D, device=dev, dtype=torch.float32)
+                                                 for k in ("encoder", "encoder_v", "decoder")}
         # head
         if d.V % 8 == 0:
             g_head = torch.empty(d.D, d.V, device=dev, dtype=torch.float32)
@@ -504,6 +517,9 @@ class _FusedLoss(torch.autograd.Function):
         g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)
         ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)
         s = grad_out.to(torch.float32)
+        if grads is None:
+            # (the sharded weights' gradients are already in their owners' slices; the loss enters with weight 1)
+            return (None, None, g_emb * s, None, None, None, g_head * s, None, None)
         return (None, None, g_emb * s, grads["encoder"] * s, grads["encoder_v"] * s, grads["decoder"] * s,
                 g_head * s, None, None)
 

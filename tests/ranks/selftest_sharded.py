@@ -19,6 +19,13 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+def _fused_modes(dev):
+    """Wrapper modes a device can run: the fused path needs GPUs - or, for the host logic of the fully
+    sharded state, CPU ranks on the emulated kernel path."""
+    from burn_dragon_b200.ops import emulate
+    return (True, False) if (dev.type == "cuda" or emulate.active()) else (False,)
+
+
 def case_fsdp(dev):
     """Sharded optimizer training equals one process training on the concatenated batch, the
     gathered state dict is identical on all ranks, and optimizer state round-trips logically."""
@@ -30,7 +37,7 @@ def case_fsdp(dev):
     data = torch.randint(0, 256, (world * B, T + 1), generator=g).to(dev)
     mine = data[rank * B:(rank + 1) * B]
     notes = []
-    for fused in ((True, False) if dev.type == "cuda" else (False,)):
+    for fused in _fused_modes(dev):
         m = _bdh(dev)
         w = FSDP(m, lr=1e-2, fused=fused)
         if fused:
@@ -53,9 +60,15 @@ def case_fsdp(dev):
             a, b = osd["m"][n].flatten().float(), f1.view(tr1.opt.m, i).cpu().flatten().float()
             cos = torch.dot(a, b) / (a.norm() * b.norm() + 1e-20)
             assert cos > 0.98, (fused, n, cos.item())
-        before = w.m.clone()
+        mom = w.state.m if w.state is not None else w.m
+        before = mom.clone()
         w.optimizer.load_logical_state_dict(osd)
-        assert torch.equal(before, w.m)
+        assert torch.equal(before, mom)
+        if w.state is not None:
+            # fully sharded: no rank holds more than 1/world of the fp32 state of the big weights
+            pb = w.state.persistent_bytes()
+            fp32 = pb["master_fp32"] + pb["moments_fp32"] + pb["gradient_fp32"]
+            assert fp32 < pb["unsharded_fp32_equivalent"] / world * 1.1 + 16 * 4 * w.state.small_n, pb
         notes.append(f"fused={w.fused}")
     return " ".join(notes)
 
@@ -73,7 +86,7 @@ def case_accum(dev):
     for kind in ("fsdp", "tp"):
         data = torch.randint(0, 256, ((world if kind == "fsdp" else 1) * B, T + 1), generator=g).to(dev)
         mine = data[rank * B:(rank + 1) * B] if kind == "fsdp" else data      # TP ranks share the batch
-        for fused in ((True, False) if dev.type == "cuda" else (False,)):
+        for fused in _fused_modes(dev):
             sds = []
             for accum in (2, 1):
                 m = _bdh(dev, N=128 * world)
@@ -104,7 +117,7 @@ def case_clip(dev):
     for kind in ("fsdp", "tp"):
         data = torch.randint(0, 256, ((world if kind == "fsdp" else 1) * B, T + 1), generator=g).to(dev)
         mine = data[rank * B:(rank + 1) * B] if kind == "fsdp" else data
-        for fused in ((True, False) if dev.type == "cuda" else (False,)):
+        for fused in _fused_modes(dev):
             m, one = _bdh(dev, N=128 * world), _bdh(dev, N=128 * world)
             w = FSDP(m, lr=1e-2, fused=fused) if kind == "fsdp" else NeuronTP(m, lr=1e-2, fused=fused)
             tr = Trainer(m, lr=1e-2, wrapper=w, grad_clip=clip)
