@@ -60,18 +60,36 @@ decode_state_update_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     acc[i] = 0.f;
   }
   float* base = rho + ((static_cast<long long>(b) * H + h) * Np) * D + tc * 4 * VEC;
-  for (int j = tr; j < na; j += rows_in_flight) {
-    const int i = active[j];
-    const float qv = qs[i];
-    float4* p = reinterpret_cast<float4*>(base + static_cast<long long>(n0 + i) * D);
+  // UNROLL active rows per thread group are loaded before any of them is updated: the kernel is a pure stream
+  // over the state, and what it sustains is set by the bytes each SM keeps in flight
+  constexpr int UNROLL = (VEC >= 4) ? 1 : (VEC == 2 ? 2 : 4);
+  for (int j0 = tr; j0 < na; j0 += rows_in_flight * UNROLL) {
+    float4 r[UNROLL][VEC];
+    float4* p[UNROLL];
+    float qv[UNROLL];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      float4 r = p[k];
-      acc[4 * k + 0] += qv * r.x; acc[4 * k + 1] += qv * r.y;
-      acc[4 * k + 2] += qv * r.z; acc[4 * k + 3] += qv * r.w;
-      r.x = (r.x + qv * vv[4 * k + 0]) * gamma; r.y = (r.y + qv * vv[4 * k + 1]) * gamma;
-      r.z = (r.z + qv * vv[4 * k + 2]) * gamma; r.w = (r.w + qv * vv[4 * k + 3]) * gamma;
-      p[k] = r;
+    for (int u = 0; u < UNROLL; ++u) {
+      const int j = j0 + u * rows_in_flight;
+      const int i = (j < na) ? active[j] : 0;
+      qv[u] = (j < na) ? qs[i] : 0.f;
+      p[u] = reinterpret_cast<float4*>(base + static_cast<long long>(n0 + i) * D);
+      if (j < na) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) r[u][k] = __ldcs(p[u] + k);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (j0 + u * rows_in_flight >= na) break;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float4 t = r[u][k];
+        acc[4 * k + 0] += qv[u] * t.x; acc[4 * k + 1] += qv[u] * t.y;
+        acc[4 * k + 2] += qv[u] * t.z; acc[4 * k + 3] += qv[u] * t.w;
+        t.x = (t.x + qv[u] * vv[4 * k + 0]) * gamma; t.y = (t.y + qv[u] * vv[4 * k + 1]) * gamma;
+        t.z = (t.z + qv[u] * vv[4 * k + 2]) * gamma; t.w = (t.w + qv[u] * vv[4 * k + 3]) * gamma;
+        __stcs(p[u] + k, t);
+      }
     }
   }
   // combine the row groups of this CTA in shared memory, then one atomic per output element

@@ -24,6 +24,20 @@ struct PerDeviceOnce {
   }
 };
 
+// cuTensorMapEncodeTiled is a driver call and needs the device's primary context to be current on the
+// calling thread. The runtime binds it lazily, on a thread's first runtime call that needs it - and a
+// worker thread (an autograd engine thread, say) may reach a tensor-map encode before it has made one:
+// the encode then fails with CUDA_ERROR_INVALID_CONTEXT. cudaFree(nullptr) is the documented no-op that
+// forces the binding; it is done once per thread and device.
+inline void bind_primary_context() {
+  static thread_local unsigned long long bound = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PerDeviceOnce::MAX_DEVICES) return;
+  if (bound & (1ull << dev)) return;
+  cudaFree(nullptr);
+  bound |= 1ull << dev;
+}
+
 // SM count of the current device (cached per device).
 inline int current_device_sms() {
   static std::atomic<int> cache[PerDeviceOnce::MAX_DEVICES];

@@ -138,6 +138,7 @@ extern "C" int bdh_dual_gemm(const BdhMat* A1, const BdhMat* B1, int b1_mn, cons
       (d->K1 % DUAL_BK) || d->N2 <= 0 || (d->N2 % 64) || d->N2 > DUAL_MAX_N2 || d->T <= 0 || (d->T % DUAL_BM) ||
       (d->M % d->T) || !d->partials)
     return BDH_ERR_ARGUMENT;
+  bind_primary_context();
   const int epi = d->epi;
   if (epi != EPI_RELU_GATE && epi != EPI_GATE_BWD && epi != EPI_DQ_BWD) return BDH_ERR_UNSUPPORTED;
   const int io = epi_io_mask(epi, d->flags | (epi == EPI_RELU_GATE ? EPI_F_NO_OUT0 : 0));

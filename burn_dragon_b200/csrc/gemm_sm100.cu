@@ -5,6 +5,7 @@
 #include "device_once.h"
 
 #include <mutex>
+#include <stdio.h>
 #include <string.h>
 
 namespace bdh {
@@ -40,6 +41,9 @@ static int make_tmap(CUtensorMap* out, const BdhMat& m, int box_rows) {
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(m.ptr), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "bdh gemm: tensor map rejected (driver code %d): ptr %p rows %lld cols %lld ld %lld box rows %d\n",
+            static_cast<int>(r), m.ptr, m.rows, m.cols, m.ld, box_rows);
   return r == CUDA_SUCCESS ? BDH_OK : BDH_ERR_TMAP;
 }
 
@@ -94,6 +98,7 @@ using namespace bdh;
 extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_mn,
                              const BdhGemmDesc* d, cudaStream_t stream) {
   if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->nz0 <= 0 || d->nz1 <= 0) return BDH_ERR_ARGUMENT;
+  bind_primary_context();
   const int bn = d->bn == 128 ? 128 : 256;
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, *A, a_mn ? GEMM_BK : GEMM_BM);

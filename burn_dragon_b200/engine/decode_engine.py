@@ -32,6 +32,7 @@ class DecodeEngine:
         self.pope_graph = (os.environ.get("BDH_POPE_DECODE_GRAPH", "0") == "1") if pope_graph is None else bool(pope_graph)
         self.split_k = split_k
         self._cache = {}       # (streams, device, sampling settings) -> buffers, state storage, captured graph
+        self.launches_per_step = None
 
     # ---- eligibility ---------------------------------------------------------------------------
     def can_run(self, toks: torch.Tensor, settings) -> bool:
@@ -201,8 +202,11 @@ class DecodeEngine:
                 torch.cuda.current_stream().wait_stream(s)
                 load_state()
                 graph = torch.cuda.CUDAGraph()
+                n0 = native.launch_count()
                 with torch.cuda.graph(graph):
                     self._step(buf, W, rho, settings, seed, None)
+                # kernels of this library inside one replay (what a benchmark reports as its launches per step)
+                self.launches_per_step = native.launch_count() - n0
                 ctx["graph"], ctx["weights"] = graph, W
                 load_state()
             elif any(ctx["weights"][k].data_ptr() != W[k].data_ptr() for k in W):

@@ -103,7 +103,8 @@ class GradSink:
         """-> (out0, flags, extra keyword arguments) of the GEMM that adds into `name`'s gradient."""
         from ..ops import gemm as G
         if self.ptrs is not None:
-            return None, (base_flags & ~G.F_ACCUM) | G.F_OUT_F32 | G.F_ATOMIC | G.F_PEER_RS, dict(
+            # out0 = this rank's own slice: it gives the kernel the row pitch of every owner's block
+            return self.acc[SHARDED.index(name)], (base_flags & ~G.F_ACCUM) | G.F_OUT_F32 | G.F_ATOMIC | G.F_PEER_RS, dict(
                 peer_ptrs=self.ptrs[name], peer_rows=self.rows_per_rank, peer_rank=self.rank)
         return self.local_full[name], base_flags, {}
 
