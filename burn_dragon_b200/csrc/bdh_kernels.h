@@ -168,6 +168,13 @@ int bdh_bump_counter(int* counter, int by, cudaStream_t s);
 // Scratch supplied by the caller: states [B,T/64,H,128,64] and decay [B,T/64,H] (fp32).
 int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
                        float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s);
+// The first half of the scan alone: afterwards states[b,c,h] is the state entering chunk c, h the final state.
+int bdh_ssd_chunk_states(const float* xw, const float* loga, const float* Bm, float* h, float* states, float* decay,
+                         int B, int T, int H, cudaStream_t s);
+// Same contract as bdh_ssd_chunk_scan with the chunk outputs on the tensor cores (ssd_tc.cu: tcgen05 MMAs over
+// pairs of chunks, bf16 operands, fp32 accumulation in TMEM). All pointers 16-byte aligned.
+int bdh_ssd_chunk_scan_tc(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
+                          float* states, float* decay, float* y, int B, int T, int H, int* status, cudaStream_t s);
 
 // ---- block-ELL neuron graph (graph.cu) ------------------------------------------------------------
 // y[M, Ntot] = relu(x[M, D] . W[Ntot, D]^T - theta) touching only the 64x64 blocks listed in

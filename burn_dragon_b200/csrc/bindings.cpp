@@ -341,7 +341,7 @@ void bump_counter(Tensor& counter, int64_t by) {
 }
 
 void ssd_chunk_scan(const Tensor& xw, const Tensor& loga, const Tensor& Bm, const Tensor& Cm, Tensor& h, Tensor& states,
-                    Tensor& decay, Tensor& y) {
+                    Tensor& decay, Tensor& y, bool tensor_cores) {
   c10::cuda::CUDAGuard guard(xw.device());
   for (const Tensor* t : std::initializer_list<const Tensor*>{&xw, &loga, &Bm, &Cm, &h, &states, &decay, &y})
     TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat);
@@ -349,6 +349,13 @@ void ssd_chunk_scan(const Tensor& xw, const Tensor& loga, const Tensor& Bm, cons
   TORCH_CHECK(xw.size(3) == 64 && Bm.size(2) == 128 && Cm.size(2) == 128 && T % 64 == 0);
   TORCH_CHECK(h.numel() == B * H * 128 * 64 && y.numel() == xw.numel() && states.numel() == B * (T / 64) * H * 128 * 64 &&
               decay.numel() == B * (T / 64) * H);
+  if (tensor_cores) {
+    check_rc(bdh_ssd_chunk_scan_tc(xw.data_ptr<float>(), loga.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                                   h.data_ptr<float>(), states.data_ptr<float>(), decay.data_ptr<float>(),
+                                   y.data_ptr<float>(), B, T, H, status_word().data_ptr<int>(), cur_stream()),
+             "ssd_chunk_scan_tc");
+    return;
+  }
   check_rc(bdh_ssd_chunk_scan(xw.data_ptr<float>(), loga.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
                               h.data_ptr<float>(), states.data_ptr<float>(), decay.data_ptr<float>(), y.data_ptr<float>(),
                               B, T, H, cur_stream()), "ssd_chunk_scan");
@@ -433,7 +440,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
-        "Tensor(d!) y) -> ()");
+        "Tensor(d!) y, bool tensor_cores) -> ()");
   m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
   m.def("sample_tokens(Tensor logits, Tensor(a!) out, float temperature, int top_k, bool greedy, int seed, int step, "
         "Tensor? step_dev) -> ()");

@@ -181,23 +181,39 @@ using namespace bdh;
 
 // xw [B,T,H,64], loga [B,T,H], Bm/Cm [B,T,128], h [B,H,128,64] in/out, states [B,T/64,H,128,64] scratch,
 // decay [B,T/64,H] scratch, y [B,T,H,64]; T % 64 == 0.
-extern "C" int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
-                                  float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s) {
+// First two launches of the scan: per-chunk states and the pass over the chunks. Afterwards states[b,c,h] is the
+// state ENTERING chunk c and h the state after the last chunk.
+extern "C" int bdh_ssd_chunk_states(const float* xw, const float* loga, const float* Bm, float* h, float* states,
+                                    float* decay, int B, int T, int H, cudaStream_t s) {
   if (B <= 0 || H <= 0 || T <= 0 || (T % SSD_Q)) return BDH_ERR_ARGUMENT;
   const int C = T / SSD_Q;
   dim3 grid(C, H, B);
   const int smem_a = (SSD_Q * SSD_P + SSD_Q * SSD_N + SSD_Q) * 4;
-  const int smem_c = (SSD_Q * SSD_P + 2 * SSD_Q * SSD_N + SSD_N * SSD_P + SSD_Q * SSD_Q + SSD_Q) * 4;
   static PerDeviceOnce configured;   // the shared-memory limit is a per-device attribute
   if (configured.run([&] {
-        return (cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a) == cudaSuccess &&
-                cudaFuncSetAttribute(ssd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c) == cudaSuccess)
+        return cudaFuncSetAttribute(ssd_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a) == cudaSuccess
                    ? 0 : 1;
       }))
     return BDH_ERR_LAUNCH;
   ssd_chunk_state_kernel<<<grid, SSD_THREADS, smem_a, s>>>(xw, loga, Bm, states, decay, T, H);
   const long long total = static_cast<long long>(B) * H * SSD_N * SSD_P;
   ssd_state_pass_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, s>>>(states, decay, h, C, H, total);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
+extern "C" int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
+                                  float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s) {
+  int rc = bdh_ssd_chunk_states(xw, loga, Bm, h, states, decay, B, T, H, s);
+  if (rc != BDH_OK) return rc;
+  const int C = T / SSD_Q;
+  dim3 grid(C, H, B);
+  const int smem_c = (SSD_Q * SSD_P + 2 * SSD_Q * SSD_N + SSD_N * SSD_P + SSD_Q * SSD_Q + SSD_Q) * 4;
+  static PerDeviceOnce configured;
+  if (configured.run([&] {
+        return cudaFuncSetAttribute(ssd_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_c) == cudaSuccess
+                   ? 0 : 1;
+      }))
+    return BDH_ERR_LAUNCH;
   ssd_chunk_out_kernel<<<grid, SSD_THREADS, smem_c, s>>>(xw, loga, Bm, Cm, states, y, T, H);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }

@@ -7,7 +7,9 @@
 weights for Mamba-3). B and C are shared by all heads of a group (one group here).
 
 Three statements of the same function: the literal recurrence (oracle), the chunked form in torch
-(differentiable; what training uses), and the CUDA chunk-scan kernels (forward; prefill / eval).
+(differentiable), and the CUDA chunk-scan kernels: chunk outputs on the tensor cores (tcgen05, bf16
+operands) or in fp32 FMA arithmetic; `ssd_dual` runs training on them (forward and the dual scan of
+the backward pass).
 The reference has no Mamba path; the spec is Mamba-2's SSD algorithm (Dao & Gu, 2024).
 """
 from __future__ import annotations
@@ -188,12 +190,12 @@ class _SSDDual(torch.autograd.Function):
 
 
 def ssd_dual(xw, loga, Bm, Cm, chunk: int = 64):
-    """Differentiable scan from a zero state whose backward is the written-out dual form (opt-in:
-    `BDH_SSD_DUAL=1` makes `ssd` use it for training calls without an initial state)."""
+    """Differentiable scan from a zero state whose backward is the written-out dual form (what `ssd` uses for
+    training calls without an initial state on a GPU; `BDH_SSD_DUAL=1` / `0` forces it on / off everywhere)."""
     return _SSDDual.apply(xw, loga, Bm, Cm, chunk)
 
 
-_DUAL = os.environ.get("BDH_SSD_DUAL", "0") == "1"
+_DUAL = os.environ.get("BDH_SSD_DUAL")        # "1": always, "0": never, unset: wherever the kernels run
 
 
 def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
@@ -203,19 +205,27 @@ def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
     if h0 is not None:
         h0 = h0.to(ct)
     need_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (xw, loga, Bm, Cm))
-    if need_grad and _DUAL and h0 is None:
+    kernels = (xw.is_cuda and native.available() and hasattr(torch.ops.bdh, "ssd_chunk_scan")
+               and xw.shape[-1] == 64 and Bm.shape[-1] == 128 and chunk == 64)
+    # training from a zero state: on a GPU the written-out dual form, whose forward scan and backward (dual) scan
+    # both run on the chunk-scan kernels; elsewhere autograd of the torch chunked form
+    if need_grad and h0 is None and (_DUAL == "1" or (_DUAL is None and kernels)):
         return ssd_dual(xw, loga, Bm, Cm, chunk)
     if xw.shape[1] == 1 and h0 is not None and not need_grad:
         # single-token decode: one recurrence step on a private copy of the state
         y, h = ssd_step(xw[:, 0], loga[:, 0], Bm[:, 0], Cm[:, 0], h0.clone())
         return y.unsqueeze(1), h
-    if (xw.is_cuda and not need_grad and native.available() and hasattr(torch.ops.bdh, "ssd_chunk_scan")
-            and xw.shape[-1] == 64 and Bm.shape[-1] == 128 and chunk == 64):
+    if kernels and not need_grad:
         return ssd_cuda(xw, loga, Bm, Cm, h0)
     return ssd_chunked(xw, loga, Bm, Cm, h0, chunk)
 
 
-def ssd_cuda(xw, loga, Bm, Cm, h0=None):
+def ssd_cuda(xw, loga, Bm, Cm, h0=None, tensor_cores: Optional[bool] = None):
+    """Chunk-scan kernels. `tensor_cores` (default: on, `BDH_SSD_FMA=1` turns it off): the chunk outputs - the
+    quadratic part and the carried-state product - run as tcgen05 MMAs over pairs of chunks with bf16 operands and
+    fp32 accumulation (`csrc/ssd_tc.cu`); off: the fp32 FMA kernels (`csrc/ssd.cu`), exact to fp32 rounding."""
+    if tensor_cores is None:
+        tensor_cores = os.environ.get("BDH_SSD_FMA", "0") != "1"
     Bsz, T, H, P = xw.shape
     N = Bm.shape[-1]
     chunk = 64
@@ -233,5 +243,5 @@ def ssd_cuda(xw, loga, Bm, Cm, h0=None):
     states = torch.empty(Bsz, C, H, N, P, device=xw.device, dtype=torch.float32)   # scratch: per-chunk states
     h = h0.float().clone().contiguous() if h0 is not None else torch.zeros(Bsz, H, N, P, device=xw.device)
     decay = torch.empty(Bsz, C, H, device=xw.device, dtype=torch.float32)                 # scratch: per-chunk decay
-    native.ops.ssd_chunk_scan(xw, loga, Bm, Cm, h, states, decay, y)
+    native.ops.ssd_chunk_scan(xw, loga, Bm, Cm, h, states, decay, y, bool(tensor_cores))
     return y[:, :T], h

@@ -125,7 +125,7 @@ def test_mamba_gradients_with_the_dual_form_scan(version, monkeypatch):
     loss.backward()
     want = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
     m.zero_grad()
-    monkeypatch.setattr(S, "_DUAL", True)
+    monkeypatch.setattr(S, "_DUAL", "1")
     calls = []
     real = S.ssd_dual
     monkeypatch.setattr(S, "ssd_dual", lambda *a, **k: (calls.append(1), real(*a, **k))[1])

@@ -18,12 +18,20 @@ def test_ssd_cuda_matches_sequential(T, with_h0):
     h0 = torch.randn(B, H, N, P, device="cuda") if with_h0 else None
     y_ref, h_ref = SSD.ssd_sequential(xw.double(), loga.double(), Bm.double(), Cm.double(),
                                       h0.double() if with_h0 else None)
-    y, h = SSD.ssd_cuda(xw, loga, Bm, Cm, h0)
+    y, h = SSD.ssd_cuda(xw, loga, Bm, Cm, h0, tensor_cores=False)
     torch.cuda.synchronize()
     assert torch.allclose(y.double(), y_ref, atol=2e-3, rtol=1e-3)
     assert torch.allclose(h.double(), h_ref, atol=2e-3, rtol=1e-3)
-    y2, h2 = SSD.ssd(xw, loga, Bm, Cm, h0)          # dispatcher picks the kernels when no grad is needed
-    assert torch.equal(y2, y)
+    # the tensor-core kernel rounds its operands to bf16: compared as a whole-tensor relative error
+    native.clear_status()
+    y_tc, h_tc = SSD.ssd_cuda(xw, loga, Bm, Cm, h0, tensor_cores=True)
+    torch.cuda.synchronize()
+    assert native.status_code() == 0
+    rel = ((y_tc.double() - y_ref).norm() / y_ref.norm()).item()
+    assert rel < 1e-2, rel
+    assert torch.allclose(h_tc.double(), h_ref, atol=2e-3, rtol=1e-3)      # the states stay fp32
+    y2, h2 = SSD.ssd(xw, loga, Bm, Cm, h0)          # dispatcher picks the (tensor-core) kernels when no grad is needed
+    assert torch.equal(y2, y_tc)
 
 
 def test_mamba2_model_uses_kernels_for_prefill():
@@ -37,7 +45,7 @@ def test_mamba2_model_uses_kernels_for_prefill():
         a = m.forward_with_state(tok, st)
     assert native.launch_count() > n0
     lg = m(tok[:, :], None)                          # grad-enabled path: torch chunked form
-    assert torch.allclose(a, lg.detach(), atol=2e-3, rtol=1e-2)
+    assert ((a - lg.detach()).norm() / lg.detach().norm()).item() < 2e-2
 
 
 def test_dual_form_backward_on_the_device_matches_the_written_out_oracle():
@@ -57,4 +65,5 @@ def test_dual_form_backward_on_the_device_matches_the_written_out_oracle():
     with torch.no_grad():
         want = SSD.ssd_backward_sequential(xw.double(), loga.double(), Bm.double(), Cm.double(), dy.double())
     for g, w, name in zip(got, want, ("xw", "loga", "B", "C")):
-        assert torch.allclose(g.double(), w, atol=3e-3 * max(1.0, w.abs().max().item()), rtol=2e-3), name
+        # y and d xw come from the tensor-core kernels (bf16 operands): whole-tensor relative error
+        assert ((g.double() - w).norm() / w.norm()).item() < 2e-2, name
