@@ -44,6 +44,7 @@ typedef struct {
   int T, pos0, n_per_head;
   const float* freqs;
   const float* slopes;
+  const float* bias;   // epi 1 / 2: fp32 bias per output column, added before the threshold (16-byte aligned; nullptr: none)
   int* status;   // device word that receives a STATUS_* code if an in-kernel wait gives up
   int max_ctas;  // 0: one CTA per SM
   int no_tma_epilogue;  // 1: force the per-thread global-memory epilogue
@@ -168,6 +169,10 @@ int bdh_bump_counter(int* counter, int by, cudaStream_t s);
 // Scratch supplied by the caller: states [B,T/64,H,128,64] and decay [B,T/64,H] (fp32).
 int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
                        float* states, float* decay, float* y, int B, int T, int H, cudaStream_t s);
+// One recurrence step (cached decode): h <- exp(loga) h + B (x) xw, y = C . h. xw [B,H,64], loga [B,H],
+// Bm/Cm [B,128], h [B,H,128,64] in place, y [B,H,64].
+int bdh_ssd_decode_step(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h, float* y,
+                        int B, int H, cudaStream_t s);
 // The first half of the scan alone: afterwards states[b,c,h] is the state entering chunk c, h the final state.
 int bdh_ssd_chunk_states(const float* xw, const float* loga, const float* Bm, float* h, float* states, float* decay,
                          int B, int T, int H, cudaStream_t s);

@@ -45,7 +45,7 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
           int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed,
-          at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank) {
+          at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank, const optional<Tensor>& bias) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -62,6 +62,10 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
   d.alpha = alpha; d.theta = theta; d.T = T; d.pos0 = pos0; d.n_per_head = n_per_head;
   d.freqs = freqs.has_value() ? freqs->data_ptr<float>() : nullptr;
   d.slopes = slopes.has_value() ? slopes->data_ptr<float>() : nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->scalar_type() == at::kFloat, "bias: contiguous fp32");
+    d.bias = bias->data_ptr<float>();
+  }
   d.status = status_word().data_ptr<int>();
   d.max_ctas = max_ctas;
   d.no_tma_epilogue = tma_epilogue ? 0 : 1;
@@ -340,6 +344,17 @@ void bump_counter(Tensor& counter, int64_t by) {
   check_rc(bdh_bump_counter(counter.data_ptr<int>(), by, cur_stream()), "bump_counter");
 }
 
+void ssd_decode_step(const Tensor& xw, const Tensor& loga, const Tensor& Bm, const Tensor& Cm, Tensor& h, Tensor& y) {
+  c10::cuda::CUDAGuard guard(xw.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&xw, &loga, &Bm, &Cm, &h, &y})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat);
+  const int64_t B = xw.size(0), H = xw.size(1);
+  TORCH_CHECK(xw.dim() == 3 && xw.size(2) == 64 && Bm.numel() == B * 128 && Cm.numel() == B * 128 && loga.numel() == B * H &&
+              h.numel() == B * H * 128 * 64 && y.numel() == xw.numel());
+  check_rc(bdh_ssd_decode_step(xw.data_ptr<float>(), loga.data_ptr<float>(), Bm.data_ptr<float>(), Cm.data_ptr<float>(),
+                               h.data_ptr<float>(), y.data_ptr<float>(), B, H, cur_stream()), "ssd_decode_step");
+}
+
 void ssd_chunk_scan(const Tensor& xw, const Tensor& loga, const Tensor& Bm, const Tensor& Cm, Tensor& h, Tensor& states,
                     Tensor& decay, Tensor& y, bool tensor_cores) {
   c10::cuda::CUDAGuard guard(xw.device());
@@ -404,7 +419,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank, Tensor? bias) -> ()");
   m.def("dual_gemm(Tensor a1, Tensor b1, bool b1_mn, Tensor b2, Tensor(a!) p, int M, int H, int n_per_head, int K1, int N2, "
         "int T, int epi, int flags, int group_per_head, int a1_b, int a1_h, int b1_b, Tensor? in0, Tensor? in1, "
         "Tensor(b!)? out1, float alpha, float theta, int pos0, float drop_p, int drop_seed, Tensor(c!) partials, "
@@ -439,6 +454,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
+  m.def("ssd_decode_step(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) y) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
         "Tensor(d!) y, bool tensor_cores) -> ()");
   m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
@@ -472,6 +488,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("pope_bwd", &pope_bwd);
   m.impl("rank_barrier", &rank_barrier);
   m.impl("graph_spmm_relu", &graph_spmm_relu);
+  m.impl("ssd_decode_step", &ssd_decode_step);
   m.impl("ssd_chunk_scan", &ssd_chunk_scan);
   m.impl("decode_state_update", &decode_state_update);
   m.impl("sample_tokens", &sample_tokens);

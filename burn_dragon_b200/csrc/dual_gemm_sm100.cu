@@ -207,7 +207,7 @@ extern "C" int bdh_dual_gemm(const BdhMat* A1, const BdhMat* B1, int b1_mn, cons
   e.alpha = d->alpha; e.theta = d->theta;
   e.T = d->T; e.pos0 = d->pos0;
   e.n_per_head = d->n_per_head;
-  e.freqs = nullptr; e.slopes = nullptr;
+  e.freqs = nullptr; e.slopes = nullptr; e.bias = nullptr;
   e.flags = d->flags | (epi == EPI_RELU_GATE ? EPI_F_NO_OUT0 : 0);
   e.drop_p = d->drop_p; e.drop_seed = d->drop_seed;
 

@@ -124,6 +124,8 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   e.T = d->T > 0 ? d->T : 1; e.pos0 = d->pos0;
   e.n_per_head = d->n_per_head > 0 ? d->n_per_head : 1;
   e.freqs = d->freqs; e.slopes = d->slopes; e.flags = d->flags;
+  e.bias = d->bias;
+  if (d->bias && (reinterpret_cast<uintptr_t>(d->bias) & 15)) return BDH_ERR_ALIGNMENT;
   e.drop_p = d->drop_p; e.drop_seed = d->drop_seed;
   e.peer_rows = d->peer_rows > 0 ? d->peer_rows : 1;
   e.peer_world = d->peer_world;
@@ -156,6 +158,7 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   const bool batched = d->nz0 * d->nz1 > 1;
   if (batched && ((d->M % GEMM_BM) || (d->N % bn))) tma_epi = false;
   for (int i = 0; i < 4; ++i) if (d->c_off[i] % 8) tma_epi = false;
+  if (d->bias && (d->N % 32)) tma_epi = false;      // the staged epilogue reads the bias 16 bytes at a time
   if (d->o1_off[0] % 8 || d->o1_off[1] % 8 || d->o1_off[2] % 8) tma_epi = false;
   if (tma_epi) {
     const long long rows = d->c_off[0] * (d->nz0 - 1) + d->c_off[1] * (d->nz1 - 1) + d->M;

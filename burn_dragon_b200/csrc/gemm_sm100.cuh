@@ -77,6 +77,8 @@ struct EpiParams {
   int n_per_head;        // rotary frequency index = column % n_per_head
   const float* freqs;    // [n_per_head] cycles per position
   const float* slopes;   // [nz0] decay slope per z0 (nullptr: no decay)
+  const float* bias;     // EPI_RELU / EPI_RELU_GATE: fp32 bias per output column (C coordinates), added before
+                         // the threshold (reference: src/kernel/relu_lowrank.rs:19-23); nullptr: none
   int flags;
   float drop_p;          // EPI_RELU_GATE: dropout probability applied to x*y (0: off)
   uint32_t drop_seed;    // EPI_RELU_GATE: seed of the counter-based dropout mask
@@ -564,6 +566,13 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
   const int io = epi_io_mask(EPI, e.flags);
   uint32_t r0[16], r1[16];
   float o0[32], o1[32], o2[32];
+  if constexpr (EPI == EPI_RELU || EPI == EPI_RELU_GATE) {
+    if (e.bias) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < valid) v[i] += __ldg(e.bias + c + i);
+    }
+  }
   const bool tab0 = (EPI == EPI_RELU), tab1 = (EPI == EPI_DQ_BWD);   // which input is the rotary table
   const long long tr = m % e.T, tcn = n % e.n_per_head;
   if (io & IO_IN0)
@@ -983,6 +992,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
           tmem_ld_wait();
+          if constexpr (EPI == EPI_RELU || EPI == EPI_RELU_GATE) {
+            if (e.bias) {
+              const float4* bp = reinterpret_cast<const float4*>(e.bias + col0 + c * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 bv = __ldg(bp + i);
+                v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+              }
+            }
+          }
           epi_compute<EPI>(e, tc.z0, m, tc.n0 + (cbase + c) * 32, v, a0, a1, o0, o1, o2);
           // the stores that last used these output boxes must have finished reading them
           constexpr int OB = epi_out_bufs(EPI);

@@ -175,9 +175,53 @@ ssd_chunk_out_kernel(const float* __restrict__ xw, const float* __restrict__ log
   }
 }
 
+// One decode step for every (stream, head): h <- exp(loga) h + B (x) xw ; y = C . h. The state is read and
+// written once (the torch statement of the step makes four passes over it and materialises the outer product).
+// Grid (H, B), 256 threads: thread (g, p) walks 32 of the 128 state rows for column p.
+__global__ void __launch_bounds__(256)
+ssd_decode_step_kernel(const float* __restrict__ xw, const float* __restrict__ loga, const float* __restrict__ Bm,
+                       const float* __restrict__ Cm, float* __restrict__ h, float* __restrict__ y, int H) {
+  const int hh = blockIdx.x, b = blockIdx.y;
+  const int p = threadIdx.x & 63, g = threadIdx.x >> 6;
+  __shared__ float sb[SSD_N], sc[SSD_N], red[4][SSD_P];
+  if (threadIdx.x < SSD_N) {
+    sb[threadIdx.x] = Bm[static_cast<long long>(b) * SSD_N + threadIdx.x];
+    sc[threadIdx.x] = Cm[static_cast<long long>(b) * SSD_N + threadIdx.x];
+  }
+  __syncthreads();
+  const long long bh = static_cast<long long>(b) * H + hh;
+  const float a = __expf(loga[bh]);
+  const float x = xw[bh * SSD_P + p];
+  float* st = h + bh * SSD_N * SSD_P + p;
+  float acc = 0.f;
+  float v[8];
+#pragma unroll 1
+  for (int n0 = g * 32; n0 < g * 32 + 32; n0 += 8) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __ldcs(st + (n0 + i) * SSD_P);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = a * v[i] + sb[n0 + i] * x;
+      acc += sc[n0 + i] * v[i];
+      __stcs(st + (n0 + i) * SSD_P, v[i]);
+    }
+  }
+  red[g][p] = acc;
+  __syncthreads();
+  if (g == 0) y[bh * SSD_P + p] = red[0][p] + red[1][p] + red[2][p] + red[3][p];
+}
+
 }  // namespace bdh
 
 using namespace bdh;
+
+// xw [B,H,64], loga [B,H], Bm/Cm [B,128], h [B,H,128,64] updated in place, y [B,H,64].
+extern "C" int bdh_ssd_decode_step(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h,
+                                   float* y, int B, int H, cudaStream_t s) {
+  if (B <= 0 || H <= 0) return BDH_ERR_ARGUMENT;
+  ssd_decode_step_kernel<<<dim3(H, B), 256, 0, s>>>(xw, loga, Bm, Cm, h, y, H);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
 
 // xw [B,T,H,64], loga [B,T,H], Bm/Cm [B,T,128], h [B,H,128,64] in/out, states [B,T/64,H,128,64] scratch,
 // decay [B,T/64,H] scratch, y [B,T,H,64]; T % 64 == 0.

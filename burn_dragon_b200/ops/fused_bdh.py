@@ -41,8 +41,17 @@ def can_run(model, tokens: torch.Tensor, state) -> bool:
     B, T = tokens.shape
     if T % 64 or c.n_embd % 8 or c.n_embd > 2048 or c.latent_per_head % 64:
         return False
-    if c.block_sparse is not None and (c.block_sparse.latent.is_sparse() or c.block_sparse.time.is_sparse()):
-        return False
+    if c.block_sparse is not None and c.block_sparse.latent.is_sparse():
+        # a latent block pattern runs on the kernels with the inactive neuron blocks left out of every operand
+        # (`_Dims.rows`); PoPE gives a masked neuron the non-zero query softplus(0), the sharded wrappers have
+        # their own row bookkeeping: those keep the torch path
+        lat = c.block_sparse.latent
+        n_act = sum(min((b + 1) * lat.block_size, c.latent_per_head) - b * lat.block_size
+                    for b in lat.active_blocks if b * lat.block_size < c.latent_per_head)
+        if (c.rotary_embedding == "pope" or lat.block_size % 2 or n_act == 0 or n_act % 64
+                or getattr(model, "_dims_hook", None) is not None or getattr(model, "_grad_sink", None) is not None
+                or getattr(model, "_cp", None) is not None):
+            return False
     if c.vocab_size > 1024:
         return False
     if state is not None:
@@ -63,6 +72,13 @@ def _weights(model) -> Dict[str, torch.Tensor]:
              ("decoder", model.decoder), ("lm_head", model.lm_head))}
 
 
+def _compact(d, W):
+    """Weights of the active neurons only (latent block pattern), else W unchanged."""
+    if d.rows is None:
+        return W
+    return {**W, **{k: W[k].index_select(0, d.rows) for k in ("encoder", "encoder_v", "decoder")}}
+
+
 class _Dims:
     def table(self, pos0: int) -> torch.Tensor:
         """RoPE (cos, sin) table for positions [pos0, pos0 + T), cached per start position."""
@@ -78,6 +94,13 @@ class _Dims:
         self.B, self.T, self.M = B, T, B * T
         self.D, self.H, self.N = c.n_embd, c.n_head, c.latent_per_head
         self.Np = c.state_latent
+        # latent block pattern: only the neurons of active blocks exist on the kernel path
+        self.N_full, self.idx, self.rows = self.N, None, None
+        if c.block_sparse is not None and c.block_sparse.latent.is_sparse():
+            from . import lowrank
+            self.idx = lowrank.active_index(c.block_sparse.latent, self.N, model.encoder.device)
+            self.rows = lowrank.head_rows(self.idx, self.H, self.N)
+            self.N = self.Np = int(self.idx.numel())
         self.HN, self.HNp = self.H * self.N, self.H * self.Np
         self.V = c.vocab_size
         self.L = c.n_layer
@@ -85,13 +108,25 @@ class _Dims:
         self.theta = float(c.relu_threshold)
         # the RoPE epilogues take one frequency per (2i, 2i+1) column pair, PoPE one per column
         if self.rot == "rope":
-            self.freqs = model.freqs.float()[0::2].contiguous()
-            self.freqs_full = model.freqs.float().contiguous()
+            fr = model.freqs.float() if self.idx is None else model.freqs.float()[self.idx]
+            self.freqs = fr[0::2].contiguous()
+            self.freqs_full = fr.contiguous()
         elif self.rot == "pope":
             self.freqs = self.freqs_full = model.freqs.float().contiguous()
         else:
             self.freqs = self.freqs_full = None
         self.slopes = model.slopes.float().contiguous() if self.rot == "alibi" else None
+        # time block pattern (row-normalised mode only, as in the reference: src/kernel/linear_attention.rs:54-112):
+        # a [T, T] 0/1 matrix of the active (row block, column block) pairs, applied to the scores
+        self.time_keep = None
+        if self.fast and c.block_sparse is not None and c.block_sparse.time.is_sparse():
+            tp = c.block_sparse.time
+            nb = -(-T // tp.block_size)
+            keep = torch.zeros(nb, nb, dtype=torch.bool)
+            for (r, cc) in tp.pairs(nb):
+                keep[r, cc] = True
+            keep = keep.repeat_interleave(tp.block_size, 0).repeat_interleave(tp.block_size, 1)[:T, :T]
+            self.time_keep = keep.to(device=model.encoder.device, dtype=torch.bfloat16)
         self.cp = getattr(model, "_cp", None)        # context-parallel hook (parallel/cp.py)
         # fully sharded data parallelism: the weight gradients of the [H*N, D] weights go to their owners' slices
         # from the GEMM epilogues (parallel/fsdp.py: GradSink) instead of into local full-size tensors
@@ -191,6 +226,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
             raise NotImplementedError("the row-normalised path has no state and is not sharded")
         G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
                epi=G.EPI_CAUSAL, flags=G.F_BIAS if d.slopes is not None else 0, slopes=d.slopes, causal_tiles=1, out0=S)
+        if d.time_keep is not None:
+            S.view(B * H, T, T).mul_(d.time_keep)                   # inactive block pairs leave the scores
         rnorm = torch.empty(B * H * T, device=dev, dtype=torch.float32)
         ops.rownorm_fwd(S, rnorm, T)
     else:
@@ -333,6 +370,8 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
                epi=G.EPI_CAUSAL, causal_tiles=1, out0=Gl)
         ops.rownorm_bwd(Gl, S, sv["rnorm"], T)
         Gl3 = Gl.view(B * H, T, T)
+        if d.time_keep is not None:
+            Gl3.mul_(d.time_keep)                                   # ... and get no gradient
         Gs = (Gl3 + Gl3.transpose(1, 2)).reshape(B * H * T, T)
         del Gl, Gl3
     else:
@@ -447,10 +486,17 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int
     saved: List[dict] = []
     for l in range(d.L):
         rho_in = state.layers[l].rho if state is not None else None
+        if rho_in is not None and d.idx is not None:
+            rho_in = rho_in.index_select(2, d.idx)           # the state rows of the active neurons
         seed_l = (d.drop_base + 0x632BE5AB * (l + 1)) & 0x7FFFFFFF
         with prof.phase("layer.forward"):
             out, sv, rho_out = _layer_forward(d, W, cur, pos0, rho_in, want_rho=state is not None, drop_seed=seed_l)
         if state is not None:
+            if d.idx is not None and rho_out is not None:
+                # inactive neurons have zero queries: their state rows stay zero
+                full = torch.zeros(d.B, d.H, d.N_full, d.D, device=rho_out.device, dtype=rho_out.dtype)
+                full[:, :, d.idx] = rho_out
+                rho_out = full
             state.layers[l].rho = rho_out
         if save:
             saved.append(dict(cur=cur, drop_seed=seed_l) if l < recompute else sv)
@@ -467,7 +513,7 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int
 def forward_logits(model, tokens: torch.Tensor, state, fast: bool = False) -> torch.Tensor:
     B, T = tokens.shape
     d = _Dims(model, B, T, fast)
-    W = _weights(model)
+    W = _compact(d, _weights(model))
     cur, _ = _stack_forward(model, d, W, tokens, state, save=False, recompute=0)
     return _head_logits(d, W, cur).view(B, T, d.V)
 
@@ -477,7 +523,7 @@ class _FusedLoss(torch.autograd.Function):
     def forward(ctx, tokens, targets, embed_w, encoder, encoder_v, decoder, lm_head, model, fast=False):
         B, T = tokens.shape
         d = _Dims(model, B, T, fast)
-        W = _weights(model)
+        W = _compact(d, _weights(model))
         recompute = recompute_count(model, d)
         model._recomputed_layers = recompute
         cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute)
@@ -520,6 +566,12 @@ class _FusedLoss(torch.autograd.Function):
         if grads is None:
             # (the sharded weights' gradients are already in their owners' slices; the loss enters with weight 1)
             return (None, None, g_emb * s, None, None, None, g_head * s, None, None)
+        if d.rows is not None:
+            # latent block pattern: the rows of inactive neurons get no gradient
+            for k in grads:
+                full = torch.zeros(d.H * d.N_full, d.D, device=dev, dtype=torch.float32)
+                full[d.rows] = grads[k]
+                grads[k] = full
         return (None, None, g_emb * s, grads["encoder"] * s, grads["encoder_v"] * s, grads["decoder"] * s,
                 g_head * s, None, None)
 

@@ -109,7 +109,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          n_per_head: int = 1, freqs: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
          tma_epilogue: bool = True, mc_out: int = 0, drop_p: float = 0.0, drop_seed: int = 0,
-         peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0) -> None:
+         peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0,
+         bias: Optional[torch.Tensor] = None) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     if _CHECKED:
@@ -118,7 +119,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),
-                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank))
+                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank), bias)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -188,7 +189,7 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                    epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
                    o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
                    causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True, mc_out=0, drop_p=0.0,
-                   drop_seed=0) -> None:
+                   drop_seed=0, bias=None) -> None:
     """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
     dev = a.device
     for z1 in range(nz[1]):
@@ -222,6 +223,8 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                     v = v + out0[rs, cs].float()
                 out0[rs, cs] = v.to(out0.dtype)
             elif epi == EPI_RELU:
+                if bias is not None:
+                    acc = acc + bias[c0:c0 + N].float()[None, :]
                 x = torch.relu(acc - theta)
                 out0[rs, cs] = x.to(out0.dtype)
                 if flags & (F_ROPE | F_POPE):
@@ -237,6 +240,8 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                         out1[rs, c1:c1 + N] = (mag * ph.cos()).to(out1.dtype)
                         out1[rs, c1 + o1_off[2]:c1 + o1_off[2] + N] = (mag * ph.sin()).to(out1.dtype)
             elif epi == EPI_RELU_GATE:
+                if bias is not None:
+                    acc = acc + bias[c0:c0 + N].float()[None, :]
                 y = torch.relu(acc - theta)
                 if not (flags & F_NO_OUT0):
                     out0[rs, cs] = y.to(out0.dtype)

@@ -213,6 +213,12 @@ def ssd(xw, loga, Bm, Cm, h0=None, chunk: int = 64):
         return ssd_dual(xw, loga, Bm, Cm, chunk)
     if xw.shape[1] == 1 and h0 is not None and not need_grad:
         # single-token decode: one recurrence step on a private copy of the state
+        if kernels and ct == torch.float32:
+            h = h0.clone().contiguous()
+            y = torch.empty_like(xw[:, 0])
+            native.ops.ssd_decode_step(xw[:, 0].contiguous(), loga[:, 0].contiguous(), Bm[:, 0].contiguous(),
+                                       Cm[:, 0].contiguous(), h, y)
+            return y.unsqueeze(1), h
         y, h = ssd_step(xw[:, 0], loga[:, 0], Bm[:, 0], Cm[:, 0], h0.clone())
         return y.unsqueeze(1), h
     if kernels and not need_grad:

@@ -375,3 +375,65 @@ def test_pope_decode_step_with_the_position_in_device_memory():
     assert torch.equal(got, want) and _rel(eng.last_logits, fused.last_logits) < 0.02
     assert torch.equal(more, more_ref)
     assert want_logits.shape == (2, 256)
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope"])
+def test_latent_block_pattern_runs_on_the_kernel_path(rot):
+    """A sparse latent `BlockPattern1d` no longer leaves the kernels: the inactive neuron blocks are dropped from
+    every operand. Loss, gradients (zero on inactive rows) and the prefill state equal the torch path's."""
+    from burn_dragon_b200.ops import emulate, fused_bdh
+    from burn_dragon_b200.ops.block_sparse import BlockPattern1d, BlockPattern2d, BlockSparseConfig
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=256, vocab_size=256, dropout=0.0,
+                      rotary_embedding=rot))
+    m.config.block_sparse = BlockSparseConfig(BlockPattern1d.from_blocks(64, [0, 3]), BlockPattern2d.dense(128))
+    tok, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    m.use_native = False
+    ref = m(tok, tgt, mode="parallel")
+    ref.backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    st_ref = m.init_state()
+    with torch.no_grad():
+        lg_ref = m.forward_with_state(tok, st_ref, mode="parallel")
+    m.zero_grad()
+    m.use_native = True
+    with emulate.kernel_path():
+        assert fused_bdh.can_run(m, tok, None)
+        got = m(tok, tgt)
+        got.backward()
+        st = m.init_state()
+        with torch.no_grad():
+            lg = m.forward_with_state(tok, st)
+    assert abs(got.item() - ref.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert ((p.grad - want[n]).norm() / (want[n].norm() + 1e-12)).item() < 0.1, n
+    inactive = m.encoder.grad.view(2, 256, 64)[:, 64:192]
+    assert float(inactive.abs().max()) == 0.0
+    assert ((lg - lg_ref).norm() / lg_ref.norm()).item() < 0.05
+    for a, b in zip(st.layers, st_ref.layers):
+        assert a.rho.shape == b.rho.shape and ((a.rho - b.rho).norm() / (b.rho.norm() + 1e-12)).item() < 0.05
+
+
+def test_time_block_pattern_in_the_row_normalised_mode_on_the_kernel_path():
+    """`forward_fast` with a sparse `BlockPattern2d`: the block-pair mask is applied to the scores on the kernel path
+    (forward and backward) and equals the torch statement (src/kernel/linear_attention.rs:54-112)."""
+    from burn_dragon_b200.ops import emulate, fused_bdh
+    from burn_dragon_b200.ops.block_sparse import BlockPattern1d, BlockPattern2d, BlockSparseConfig
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=1, n_embd=64, n_head=2, n_latent_per_head=128, vocab_size=256, dropout=0.0,
+                      rotary_embedding="alibi"))
+    m.config.block_sparse = BlockSparseConfig(BlockPattern1d.dense(64),
+                                              BlockPattern2d.from_pairs(32, [(0, 0), (1, 1), (2, 0), (2, 2), (3, 1), (3, 3)]))
+    tok, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    m.use_native = False
+    ref = m.forward_fast(tok, tgt)
+    ref.backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    m.use_native = True
+    with emulate.kernel_path():
+        got = m.forward_fast(tok, tgt)
+        got.backward()
+    assert abs(got.item() - ref.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert ((p.grad - want[n]).norm() / (want[n].norm() + 1e-12)).item() < 0.1, n

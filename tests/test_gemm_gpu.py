@@ -243,3 +243,26 @@ def test_tile_to_cta_assignment_does_not_change_a_bit():
         outs.append((y, xy))
     for y, xy in outs[1:]:
         assert torch.equal(y, outs[0][0]) and torch.equal(xy, outs[0][1])
+
+
+def test_relu_lowrank_with_bias_and_block_mask_on_the_kernel():
+    """relu(x W^T + b - theta) * block mask: the bias is added in the GEMM epilogue, the blocks the pattern
+    switches off are never computed (reference: src/kernel/relu_lowrank.rs:7-37)."""
+    from burn_dragon_b200.ops import lowrank, reference as R
+    from burn_dragon_b200.ops.block_sparse import BlockPattern1d
+    torch.manual_seed(0)
+    M, D, H, N = 256, 64, 2, 256
+    x = (torch.randn(M, D, device="cuda")).to(torch.bfloat16)
+    w = (torch.randn(H * N, D, device="cuda") * 0.2).to(torch.bfloat16)
+    bias = torch.randn(H * N, device="cuda") * 0.3
+    pat = BlockPattern1d.from_blocks(64, [0, 2])
+    for b in (None, bias):
+        for p in (None, pat):
+            got = lowrank.relu_lowrank(x, w, b, 0.1, p, n_head=H).float()
+            mask = p.mask(N, device="cuda") if p is not None else None
+            want = R.relu_lowrank(x.float().view(1, 1, M, D), w.float().view(H, N, D).transpose(1, 2),
+                                  b.view(1, H, 1, N) if b is not None else None, 0.1, mask)      # [1, H, M, N]
+            want = want[0].permute(1, 0, 2).reshape(M, H * N)
+            assert (got - want).norm() / want.norm() < 5e-3
+            if p is not None:
+                assert float(got.view(M, H, N)[:, :, 64:128].abs().max()) == 0.0

@@ -67,3 +67,17 @@ def test_dual_form_backward_on_the_device_matches_the_written_out_oracle():
     for g, w, name in zip(got, want, ("xw", "loga", "B", "C")):
         # y and d xw come from the tensor-core kernels (bf16 operands): whole-tensor relative error
         assert ((g.double() - w).norm() / w.norm()).item() < 2e-2, name
+
+
+def test_decode_step_kernel_matches_the_recurrence():
+    torch.manual_seed(0)
+    B, H, P, N = 5, 3, 64, 128
+    xw = torch.randn(B, 1, H, P, device="cuda")
+    loga = -torch.rand(B, 1, H, device="cuda")
+    Bm, Cm = torch.randn(B, 1, N, device="cuda"), torch.randn(B, 1, N, device="cuda")
+    h0 = torch.randn(B, H, N, P, device="cuda")
+    y_ref, h_ref = SSD.ssd_sequential(xw.double(), loga.double(), Bm.double(), Cm.double(), h0.double())
+    n0 = native.launch_count()
+    y, h = SSD.ssd(xw, loga, Bm, Cm, h0)
+    assert native.launch_count() == n0 + 1
+    assert torch.allclose(y.double(), y_ref, atol=1e-4, rtol=1e-4) and torch.allclose(h.double(), h_ref, atol=1e-5, rtol=1e-5)
