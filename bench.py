@@ -257,7 +257,8 @@ def main() -> int:
             if wrapper.fused else "nccl"
         fallback = getattr(wrapper, "fallback_reason", None) or getattr(comm, "fallback_reason", None)
     else:
-        coll_mode = {"fused": "fused-nvlink", "nccl": "nccl"}.get(trainer.dp.mode, trainer.dp.mode)
+        coll_mode = {"fused": "fused-nvlink:allreduce_scale", "nccl": "nccl",
+                     "epilogue": "fused-nvlink:wgrad-epilogue red.add + shard_bcast"}.get(trainer.dp.mode, trainer.dp.mode)
         fallback = trainer.dp.fallback_reason
     if world > 1 and not args.nccl_only and not coll_mode.startswith("fused"):
         raise SystemExit(f"bench: the fused NVLink collectives were requested but this run fell back to {coll_mode} "

@@ -217,6 +217,12 @@ int bdh_shard_adamw_ag(const long long* flag_ptrs, const long long* shadow_ptrs,
                        float* master, float* m, float* v, int n_segs, const long long* seg_lo, const long long* seg_dst,
                        float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,
                        unsigned epoch, int ctas, int* status, cudaStream_t s);
+// Data-parallel gradients reduced in the weight-gradient epilogues: `gacc` is the slice this rank owns (as for
+// bdh_shard_adamw_ag). After a barrier it is scaled, written to its place in every rank's full fp32 gradient
+// buffer (out_ptrs / out_mc; segment s starts at element seg_dst[s]) and cleared; a second barrier follows.
+int bdh_shard_bcast(const long long* flag_ptrs, const long long* out_ptrs, long long out_mc, int rank, int world,
+                    float* gacc, int n_segs, const long long* seg_lo, const long long* seg_dst, float scale,
+                    unsigned epoch, int ctas, int* status, cudaStream_t s);
 // Device-side barrier over all ranks (bounded wait); uses slot 0 of the symmetric flag buffer.
 int bdh_rank_barrier(const long long* flag_ptrs, int rank, int world, unsigned epoch, int* status, cudaStream_t s);
 // Waits (at most limit_ns) for *flag to reach `value`; on expiry writes the timeout status and returns.

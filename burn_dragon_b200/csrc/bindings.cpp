@@ -299,6 +299,19 @@ void shard_adamw_ag(at::IntArrayRef flag_ptrs, at::IntArrayRef shadow_ptrs, int6
                               cur_stream()), "shard_adamw_ag");
 }
 
+void shard_bcast(at::IntArrayRef flag_ptrs, at::IntArrayRef out_ptrs, int64_t out_mc, int64_t rank, int64_t world, Tensor& gacc,
+                 at::IntArrayRef seg_lo, at::IntArrayRef seg_dst, double scale, int64_t epoch, int64_t ctas) {
+  c10::cuda::CUDAGuard guard(gacc.device());
+  TORCH_CHECK((int64_t)flag_ptrs.size() == world && (int64_t)out_ptrs.size() == world);
+  TORCH_CHECK(seg_lo.size() == seg_dst.size() + 1 && !seg_dst.empty() && seg_dst.size() <= 4);
+  TORCH_CHECK(gacc.is_cuda() && gacc.is_contiguous() && gacc.scalar_type() == at::kFloat && gacc.numel() >= seg_lo.back());
+  auto f = as_ptrs(flag_ptrs), o = as_ptrs(out_ptrs);
+  std::vector<long long> lo(seg_lo.begin(), seg_lo.end()), dst(seg_dst.begin(), seg_dst.end());
+  check_rc(bdh_shard_bcast(f.data(), o.data(), out_mc, rank, world, gacc.data_ptr<float>(), (int)dst.size(), lo.data(),
+                           dst.data(), scale, (unsigned)epoch, ctas, status_word().data_ptr<int>(), cur_stream()),
+           "shard_bcast");
+}
+
 void decode_state_update(const Tensor& q, const Tensor& v, Tensor& rho, Tensor& a, const optional<Tensor>& slopes) {
   c10::cuda::CUDAGuard guard(q.device());
   TORCH_CHECK(rho.dim() == 4 && rho.is_contiguous() && rho.scalar_type() == at::kFloat);
@@ -450,6 +463,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("shard_adamw_ag(int[] flag_ptrs, int[] shadow_ptrs, int rank, int world, Tensor(a!) gacc, Tensor(b!) master, "
         "Tensor(c!) m, Tensor(d!) v, int[] seg_lo, int[] seg_dst, float lr, float beta1, float beta2, float eps, "
         "float wd, int step, float grad_scale, int epoch, int ctas) -> ()");
+  m.def("shard_bcast(int[] flag_ptrs, int[] out_ptrs, int out_mc, int rank, int world, Tensor(a!) gacc, int[] seg_lo, "
+        "int[] seg_dst, float scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
   m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
@@ -484,6 +499,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("gather_blocks", &gather_blocks);
   m.impl("rs_adamw_ag", &rs_adamw_ag);
   m.impl("shard_adamw_ag", &shard_adamw_ag);
+  m.impl("shard_bcast", &shard_bcast);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
   m.impl("pope_bwd", &pope_bwd);
   m.impl("rank_barrier", &rank_barrier);

@@ -213,6 +213,36 @@ shard_adamw_ag_kernel(CollPeers f, CollPeers q, float* gacc, float* master, floa
   cta_barrier_all_ranks(f, flag_value(epoch, 2), status);
 }
 
+// Data-parallel counterpart of the fully sharded update: the gradient slice this rank owns (`gacc`, complete
+// once every rank's weight-gradient epilogues have added into it) is scaled and sent to its place in EVERY
+// rank's full gradient buffer (one multimem.st through the switch, or one store per peer), then cleared. The
+// reduce-scatter half of the gradient all-reduce has then happened inside the backward pass, tile by tile;
+// this kernel is the all-gather half, fused with the 1/world scale.
+__global__ void __launch_bounds__(COLL_THREADS)
+shard_bcast_kernel(CollPeers f, CollPeers q, float* gacc, ShardSegs segs, float scale, uint32_t epoch, int* status) {
+  if (!cta_barrier_all_ranks(f, flag_value(epoch, 1), status)) return;
+  const long long n4 = segs.lo4[segs.n];
+  for (long long j = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; j < n4;
+       j += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int sgi = 0;
+#pragma unroll
+    for (int k = 1; k < 4; ++k)
+      if (k < segs.n && j >= segs.lo4[k]) sgi = k;
+    float4 g = reinterpret_cast<float4*>(gacc)[j];
+    reinterpret_cast<float4*>(gacc)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    g.x *= scale; g.y *= scale; g.z *= scale; g.w *= scale;
+    const long long dst = segs.dst4[sgi] + (j - segs.lo4[sgi]);
+    if (q.mc) {
+      multimem_st_f32x4(static_cast<float4*>(q.mc) + dst, g);
+    } else {
+#pragma unroll
+      for (int r = 0; r < COLL_MAX_RANKS; ++r)
+        if (r < q.world) static_cast<float4*>(q.buf[r])[dst] = g;
+    }
+  }
+  cta_barrier_all_ranks(f, flag_value(epoch, 2), status);
+}
+
 // Second half of a reduce-scatter done by GEMM epilogues (EPI_F_PEER_RS): slot s of this rank's
 // buffer `p` holds rank s's partial sums for the block of rows this rank owns (per4 float4 each).
 // The owner adds the slots up (local reads, fixed order: the result does not depend on timing) and
@@ -351,6 +381,27 @@ extern "C" int bdh_shard_adamw_ag(const long long* flag_ptrs, const long long* s
   fill_peers(q, shadow_ptrs, nullptr, 0, rank, world);
   AdamArgs a{lr, beta1, beta2, eps, wd, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), grad_scale};
   shard_adamw_ag_kernel<<<ctas, COLL_THREADS, 0, s>>>(f, q, gacc, master, m, v, segs, a, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
+extern "C" int bdh_shard_bcast(const long long* flag_ptrs, const long long* out_ptrs, long long out_mc, int rank, int world,
+                               float* gacc, int n_segs, const long long* seg_lo, const long long* seg_dst, float scale,
+                               unsigned epoch, int ctas, int* status, cudaStream_t s) {
+  if (world < 1 || world > COLL_MAX_RANKS || ctas < 1 || n_segs < 1 || n_segs > 4) return BDH_ERR_ARGUMENT;
+  ShardSegs segs;
+  segs.n = n_segs;
+  for (int i = 0; i <= n_segs; ++i) {
+    if (seg_lo[i] % 4) return BDH_ERR_ALIGNMENT;
+    segs.lo4[i] = seg_lo[i] / 4;
+  }
+  for (int i = 0; i < n_segs; ++i) {
+    if (seg_dst[i] % 4) return BDH_ERR_ALIGNMENT;
+    segs.dst4[i] = seg_dst[i] / 4;
+  }
+  CollPeers f, q;
+  fill_peers(f, flag_ptrs, flag_ptrs, 0, rank, world);
+  fill_peers(q, out_ptrs, nullptr, out_mc, rank, world);
+  shard_bcast_kernel<<<ctas, COLL_THREADS, 0, s>>>(f, q, gacc, segs, scale, epoch, status);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 

@@ -142,12 +142,17 @@ class SymmetricAllReduce:
         self.flags = _Flags.get(like.device, self.buf.group)
         self.buf.barrier()
 
-    def all_reduce_(self, scale: float = 1.0) -> None:
+    def all_reduce_(self, scale: float = 1.0, offset: int = 0, numel: Optional[int] = None) -> None:
+        """The whole buffer, or the window [offset, offset + numel) of it (both multiples of 4 * world floats
+        and of 4 floats respectively): small replicated tensors inside a larger gradient buffer."""
         f = self.flags
         f["epoch"] += 1
         b = self.buf
-        native.ops.allreduce_scale(self.tensor, b.ptrs, f["buf"].ptrs, b.multicast_ptr, b.rank, b.world,
-                                   self.numel, float(scale), f["epoch"], COLL_CTAS)
+        n = self.numel if numel is None else int(numel)
+        ptrs = b.ptrs if not offset else [p + 4 * offset for p in b.ptrs]
+        mc = b.multicast_ptr + 4 * offset if (b.multicast_ptr and offset) else b.multicast_ptr
+        native.ops.allreduce_scale(self.tensor, ptrs, f["buf"].ptrs, mc, b.rank, b.world, n, float(scale), f["epoch"],
+                                   COLL_CTAS if n >= (1 << 20) else 8)
 
 
 class ShardedAdamW:

@@ -17,7 +17,13 @@ def test_sharded_adamw_kernel():
 
 @pytest.mark.parametrize("case", ["ddp", "ddp_nccl"])
 def test_ddp_equals_single_gpu(case):
-    run_ranks(case, cpu=False)
+    out = run_ranks(case, cpu=False)
+    assert ("mode=epilogue" if case == "ddp" else "mode=nccl") in out
+
+
+def test_ddp_with_the_single_allreduce_launch_equals_single_gpu():
+    out = run_ranks("ddp", cpu=False, env={"BDH_DDP_EPILOGUE": "0"})
+    assert "mode=fused" in out
 
 
 def test_rank_exit_detected_without_gpu_fault():
