@@ -449,8 +449,12 @@ __device__ __forceinline__ void red_add_f32x4(float* p, const float4& u, int fla
 // by row) so that 8 lanes cover one 128-byte row segment: every request that leaves the SM - and,
 // for peer and multicast targets, every NVLink packet - carries a full 128 bytes instead of 16.
 // r0 = output row of lane 0, c = first output column; the caller has checked 16-byte alignment.
+// `add_local` (EPI_F_PEER_RS | EPI_F_ATOMIC | EPI_F_ACCUM, first K split only): the tile first takes up what the
+// local fp32 buffer out0 holds at its position - the sum over the shared-weight layers processed before -
+// so that one send per step carries the whole local gradient to its owner.
 __device__ __forceinline__ void send_tile_coalesced(const EpiParams& e, long long r0, long long c,
-                                                    const float (&v)[32], float4* scratch, int lane) {
+                                                    const float (&v)[32], float4* scratch, int lane,
+                                                    bool add_local = false) {
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     scratch[lane * 8 + (i ^ (lane & 7))] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -459,8 +463,12 @@ __device__ __forceinline__ void send_tile_coalesced(const EpiParams& e, long lon
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int row = 4 * j + sub;
-    const float4 u = scratch[row * 8 + (ch ^ (row & 7))];
+    float4 u = scratch[row * 8 + (ch ^ (row & 7))];
     const long long rr = r0 + row;
+    if (add_local) {
+      const float4 l = *reinterpret_cast<const float4*>(static_cast<const float*>(e.out0) + rr * e.ld_out0 + c + 4 * ch);
+      u.x += l.x; u.y += l.y; u.z += l.z; u.w += l.w;
+    }
     if ((e.flags & EPI_F_PEER_RS) && (e.flags & EPI_F_ATOMIC))
       red_add_f32x4(peer_slot_row(e, rr) + c + 4 * ch, u, e.flags);
     else if (e.flags & EPI_F_PEER_RS)
@@ -502,9 +510,10 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
       }
     } else if ((e.flags & EPI_F_PEER_RS) && (e.flags & EPI_F_ATOMIC)) {
       float* p = peer_slot_row(e, r) + c;
+      const float* l = ((e.flags & EPI_F_ACCUM) && z1 == 0) ? static_cast<const float*>(e.out0) + r * e.ld_out0 + c : nullptr;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (i < valid) atomicAdd(p + i, v[i]);
+        if (i < valid) atomicAdd(p + i, l ? v[i] + l[i] : v[i]);
     } else if (e.flags & EPI_F_PEER_RS) {
       float* p = peer_slot_row(e, r) + c;
       if (valid >= 32 && ((reinterpret_cast<uintptr_t>(p) & 15) == 0)) {
@@ -901,8 +910,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const float scale = epi_store_scale(e, tc.z0, m);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] *= scale;
+                const bool add_local = (e.flags & EPI_F_PEER_RS) && (e.flags & EPI_F_ATOMIC) && (e.flags & EPI_F_ACCUM) &&
+                                       tc.z1 == 0;
                 send_tile_coalesced(e, r0, cc, v,
-                                   reinterpret_cast<float4*>(smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES), lane);
+                                   reinterpret_cast<float4*>(smem + L::EPI_OFFSET + ew * L::EPI_WARP_BYTES), lane,
+                                   add_local);
                 continue;
               }
             }

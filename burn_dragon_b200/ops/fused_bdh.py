@@ -306,14 +306,14 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
     return out, saved, rho_out
 
 
-def _wgrad_target(d: _Dims, grads, name: str, flags: int):
+def _wgrad_target(d: _Dims, grads, name: str, flags: int, final: bool):
     """-> (out0, flags, extra keyword arguments) of the weight-gradient GEMM of `name`."""
     if d.sink is not None:
-        return d.sink.launch(name, flags)
+        return d.sink.launch(name, flags, final, grads[name] if grads is not None else None)
     return grads[name], flags, {}
 
 
-def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
+def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False):
     """dout: fp32 [M, D] gradient of the layer output. Returns fp32 [M, D] gradient of the layer input.
     Weight gradients are accumulated into grads['encoder'|'encoder_v'|'decoder'] (fp32)."""
     dev = dout.device
@@ -340,11 +340,11 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
     sk = _split_k(wtiles, M, dev)
     wflags = G.F_OUT_F32 | (G.F_ATOMIC if sk > 1 else G.F_ACCUM)
     km = M // sk
-    o, fl, kw = _wgrad_target(d, grads, "decoder", wflags)
+    o, fl, kw = _wgrad_target(d, grads, "decoder", wflags, final)
     G.gemm(xy, dmlp, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
            flags=fl, out0=o, **kw)
     # y = relu(LN(a) E_v)
-    o, fl, kw = _wgrad_target(d, grads, "encoder_v", wflags)
+    o, fl, kw = _wgrad_target(d, grads, "encoder_v", wflags, final)
     G.gemm(dy, lna, M=N, N=D, K=km, a_mn=True, b_mn=True, nz=(H, sk), a_off=(N, 0, 0, km), b_off=(0, 0, M, km),
            c_off=(N, 0, 0, 0), flags=fl, out0=o, **kw)
     comm = d.comm
@@ -412,7 +412,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int):
                c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=(G.F_ROPE | G.F_TABLE) if rope else 0, in0=dxg,
                in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
     del dxg
-    o, fl, kw = _wgrad_target(d, grads, "encoder", wflags)
+    o, fl, kw = _wgrad_target(d, grads, "encoder", wflags, final)
     G.gemm(dx, cur, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
            flags=fl, out0=o, **kw)
     if d.dual_dq:
@@ -541,8 +541,10 @@ class _FusedLoss(torch.autograd.Function):
     def backward(ctx, grad_out):
         d, W, saved, cur, dlogits = ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits
         dev = cur.device
-        grads = None if d.sink is not None else {k: torch.zeros(d.HN, d.D, device=dev, dtype=torch.float32)
-                                                 for k in ("encoder", "encoder_v", "decoder")}
+        # local fp32 accumulation over the shared-weight layers; a sink that takes every launch needs none
+        keep_local = d.sink is None or getattr(d.sink, "last_layer_only", False)
+        grads = {k: torch.zeros(d.HN, d.D, device=dev, dtype=torch.float32)
+                 for k in ("encoder", "encoder_v", "decoder")} if keep_local else None
         # head
         if d.V % 8 == 0:
             g_head = torch.empty(d.D, d.V, device=dev, dtype=torch.float32)
@@ -558,12 +560,12 @@ class _FusedLoss(torch.autograd.Function):
                 with prof.phase("layer.recompute"):
                     _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
             with prof.phase("layer.backward"):
-                dcur = _layer_backward(d, W, sv, dcur, grads, 0)
+                dcur = _layer_backward(d, W, sv, dcur, grads, 0, final=(l == 0))
             saved[l] = None
         g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)
         ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)
         s = grad_out.to(torch.float32)
-        if grads is None:
+        if grads is None or d.sink is not None:
             # (the sharded weights' gradients are already in their owners' slices; the loss enters with weight 1)
             return (None, None, g_emb * s, None, None, None, g_head * s, None, None)
         if d.rows is not None:

@@ -11,10 +11,11 @@ Three reductions are available:
   fused     the in-kernel NVLink all-reduce of parallel.symm (peer loads, or multimem through NVSwitch) fused with
             the 1/world scale, one launch after the backward pass
   epilogue  (BDH models whose [H*N, D] weights split into 128-row blocks per rank; what `fused` becomes when it
-            can) the reduce-scatter half happens INSIDE the backward pass: every weight-gradient GEMM of every layer
-            adds its tiles into the slice of the gradient its owner rank holds (`red.add` over NVLink from the GEMM
-            epilogue, the sink of parallel/fsdp.py), so the reduction overlaps the backward tile by tile; after the
-            backward pass one kernel (`shard_bcast`) scales each owner's slice by 1/world and writes it into every
+            can) the reduce-scatter half happens INSIDE the backward pass: the weights are shared by the layers, so
+            their gradients are complete at layer 0, the last layer of the backward pass; its three weight-gradient
+            GEMMs take up the local sum of the other layers in their epilogues and add the tiles into the slice of
+            the gradient their owner rank holds (`red.add` over NVLink, the sink of parallel/fsdp.py), overlapped
+            tile by tile with the rest of layer 0's backward pass; afterwards one kernel (`shard_bcast`) scales each owner's slice by 1/world and writes it into every
             rank's gradient buffer (multimem.st), and the two small replicated tensors are all-reduced in place.
 Falls back to nccl when symmetric memory is unavailable (decided collectively).
 """
@@ -75,6 +76,7 @@ class DataParallel:
         acc = self._acc_buf.tensor.view(3, rpr, D)
         acc.zero_()
         sink = GradSink(R, D, self.world, rank)
+        sink.last_layer_only = True          # the layers accumulate locally; layer 0's epilogues send the sums
         sink.acc = acc
         sink.ptrs = {n: [p + 4 * i * rpr * D for p in self._acc_buf.ptrs] for i, n in enumerate(SHARDED)}
         n_loc = rpr * D

@@ -99,9 +99,21 @@ class GradSink:
         self.ptrs = None         # per parameter: every rank's address of that parameter's slice
         self.local_full = None   # emulated path: full local gradients, reduce-scattered at the end of the step
 
-    def launch(self, name: str, base_flags: int):
-        """-> (out0, flags, extra keyword arguments) of the GEMM that adds into `name`'s gradient."""
+    # data parallelism with replicated optimizer state sets this: the layers accumulate locally (as without a
+    # sink) and only the LAST weight-gradient launch of a backward pass - layer 0, whose epilogue first takes up
+    # the local sum - sends tiles to the owners: one gradient's worth of NVLink traffic per step instead of one
+    # per layer. Fully sharded data parallelism keeps no local full-size gradient, so every launch sends.
+    last_layer_only = False
+
+    def launch(self, name: str, base_flags: int, final: bool = True, local=None):
+        """-> (out0, flags, extra keyword arguments) of the GEMM that adds into `name`'s gradient. `final`:
+        this is the last layer of the backward pass; `local`: the local fp32 accumulation of the layers before."""
         from ..ops import gemm as G
+        if self.last_layer_only and self.ptrs is not None:
+            if not final:
+                return local, base_flags, {}
+            return local, (base_flags & ~G.F_ACCUM) | G.F_OUT_F32 | G.F_ATOMIC | G.F_PEER_RS | G.F_ACCUM, dict(
+                peer_ptrs=self.ptrs[name], peer_rows=self.rows_per_rank, peer_rank=self.rank)
         if self.ptrs is not None:
             # out0 = this rank's own slice: it gives the kernel the row pitch of every owner's block
             return self.acc[SHARDED.index(name)], (base_flags & ~G.F_ACCUM) | G.F_OUT_F32 | G.F_ATOMIC | G.F_PEER_RS, dict(
