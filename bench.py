@@ -196,6 +196,9 @@ def main() -> int:
                     help="base: BDH base, DDP (the headline config); large: L8 D512 H8 N16384 PoPE T2048 B8/GPU, "
                          "fully sharded (FSDP); tp: L12 D1024 H16 N16384 RoPE T4096 B4, neuron-sharded TP; "
                          "decode: BDH base cached decode, 64 streams per GPU, prompt 1024, 2048 new tokens")
+    ap.add_argument("--recompute", default=None,
+                    help="large / tp presets: layers whose activations are recomputed in the backward pass "
+                         "(an integer, or 'auto' = as few as fit; default: the preset's setting)")
     ap.add_argument("--streams", type=int, default=64, help="decode preset: concurrent streams per GPU")
     ap.add_argument("--prompt", type=int, default=1024, help="decode preset: prompt length")
     ap.add_argument("--new-tokens", type=int, default=2048, help="decode preset: tokens decoded per stream")
@@ -233,6 +236,8 @@ def main() -> int:
                     rotary_embedding="rope"), 4, 4096, "tp", "auto", "bdh-tp L12 D1024 H16 N16384 V256 rope"),
     }
     mcfg, B0, T0, strategy, recompute, model_name = presets[args.preset]
+    if args.recompute is not None:
+        recompute = "auto" if args.recompute == "auto" else int(args.recompute)
     B, T = args.batch or B0, args.seq or T0
     torch.manual_seed(1337)
     model = BDH(BDHConfig(**mcfg)).to(dev)
