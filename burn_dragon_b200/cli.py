@@ -83,6 +83,7 @@ def cmd_train(args) -> int:
     ds.rng = __import__("numpy").random.default_rng(cfg.training.seed + data_rank)
     model = build_model(cfg, vocab_size=len(ds.tokenizer)).to(dev)
     model.recompute = cfg.training.recompute
+    model.attention_chunk = cfg.training.attention_chunk
     if cfg.precision.compute != "bf16":
         model.use_native = False
     spe, total_steps, total_epochs, source = resolve_train_schedule(cfg.training, ds.steps_per_epoch(D.TRAIN))

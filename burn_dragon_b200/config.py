@@ -126,6 +126,8 @@ class TrainingHyperparameters:
     checkpoint_every: Optional[int] = None   # steps; None = once per epoch like the reference
     recompute: Any = False                   # layers that re-run their forward in backward instead of saving
                                              # activations: false / true (none / all), a count, or "auto"
+    attention_chunk: Optional[int] = None    # tokens per attention segment on the kernel path (states handed on
+                                             # between segments); None = whole sequence below 4096 tokens, else 1024
 
 
 @dataclass

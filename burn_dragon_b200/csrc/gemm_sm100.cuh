@@ -46,6 +46,10 @@ enum EpiFlags : int {
   EPI_F_MC_RED = 256,      // EPI_STORE fp32: out0 is an NVSwitch multicast address; add the tile into every
                            // rank's replica with multimem.red (tensor-parallel partial-sum reduction)
   EPI_F_ROWDECAY = 2048,   // EPI_STORE: scale row m by exp(-slopes[z0] * m) (decayed carry-in of a recurrent state)
+  EPI_F_ROWDECAY_REV = 8192,  // EPI_STORE: scale row m by exp(-slopes[z0] * (T - m)): what a row still contributes
+                              // to the state at the end of a segment of T rows (gradient of the segment state)
+  EPI_F_KEEP_MARK = 4096,  // EPI_DQ_BWD: closed gates keep their -0.0 marker in out0 (instead of 0), so that a
+                           // second EPI_DQ_BWD launch can take out0 as its in0 and add another product
   EPI_F_PEER_RS = 1024,    // EPI_STORE fp32: reduce-scatter epilogue (with EPI_F_ATOMIC: add into the owner's
                            // single block instead of storing into a per-rank slot). Output rows are split into blocks of
                            // peer_rows, block b is owned by rank b. The tile is stored through the owner's
@@ -217,7 +221,8 @@ __host__ __device__ inline int epi_io_mask(int epi, int flags) {
 // use per-thread global accesses.
 __host__ __device__ inline bool epi_tma_capable(int epi, int flags) {
   if (epi == EPI_STORE)
-    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS | EPI_F_ROWDECAY));
+    return !(flags & (EPI_F_OUT_F32 | EPI_F_ACCUM | EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS | EPI_F_ROWDECAY |
+                      EPI_F_ROWDECAY_REV));
   if (epi == EPI_RELU) return true;
   if (epi == EPI_CAUSAL) return !(flags & EPI_F_UPPER);
   return true;
@@ -384,11 +389,13 @@ __device__ __forceinline__ void epi_compute(const EpiParams& e, int z0, int m, i
         }
       }
     }
+    const float closed_val = (e.flags & EPI_F_KEEP_MARK) ? -0.f : 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       float2 g = unpack_bf16x2(r0[i]);
-      o0[2 * i] = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) ? 0.f : acc[2 * i] * e.alpha + g.x;
-      o0[2 * i + 1] = ((r0[i] >> 16) == BF16_NEG_ZERO) ? 0.f : acc[2 * i + 1] * e.alpha + g.y;
+      // (+ 0.f turns a computed -0.0 into +0.0: only closed gates may carry the marker)
+      o0[2 * i] = ((r0[i] & 0xFFFFu) == BF16_NEG_ZERO) ? closed_val : acc[2 * i] * e.alpha + g.x + 0.f;
+      o0[2 * i + 1] = ((r0[i] >> 16) == BF16_NEG_ZERO) ? closed_val : acc[2 * i + 1] * e.alpha + g.y + 0.f;
     }
   }
 }
@@ -419,6 +426,8 @@ constexpr int EPI_RED_FLAGS = EPI_F_MC_RED | EPI_F_ATOMIC | EPI_F_PEER_RS;
 __device__ __forceinline__ float epi_store_scale(const EpiParams& e, int z0, int m) {
   float a = e.alpha;
   if (e.flags & EPI_F_ROWDECAY) a *= __expf(-(e.slopes ? __ldg(e.slopes + z0) : 0.f) * static_cast<float>(m));
+  if (e.flags & EPI_F_ROWDECAY_REV)
+    a *= __expf(-(e.slopes ? __ldg(e.slopes + z0) : 0.f) * static_cast<float>(e.T - m));
   return a;
 }
 
@@ -583,7 +592,9 @@ __device__ __forceinline__ void epilogue_direct(const EpiParams& e, int z0, int 
     }
   }
   const bool tab0 = (EPI == EPI_RELU), tab1 = (EPI == EPI_DQ_BWD);   // which input is the rotary table
-  const long long tr = m % e.T, tcn = n % e.n_per_head;
+  // (the table row is the position of the OUTPUT row: batched problems that are segments of one sequence
+  // - rows z1 * c_m1 + m - find their place in a table of the whole sequence)
+  const long long tr = ((EPI == EPI_DQ_BWD) ? r : static_cast<long long>(m)) % e.T, tcn = n % e.n_per_head;
   if (io & IO_IN0)
     load_raw_32(static_cast<const bf*>(e.in0), e.ld_in0, tab0 ? tr : r, tab0 ? tcn : c, r0, valid);
   if (io & IO_IN1)
@@ -947,7 +958,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row = static_cast<int>(e.c_m0 * tc.z0 + e.c_m1 * tc.z1 + tc.m0 + q * 32);
         const int col = static_cast<int>(e.c_n0 * tc.z0 + e.c_n1 * tc.z1 + tc.n0 + (cbase + c) * 32);
         // the rotary table is indexed by (position, column within the head), not by C coordinates
-        const int trow = (tc.m0 + q * 32) % e.T;
+        const int trow = ((EPI == EPI_DQ_BWD) ? row : (tc.m0 + q * 32)) % e.T;
         const int tcol = (tc.n0 + (cbase + c) * 32) % e.n_per_head;
         mbar_arrive_expect_tx(&ibar[buf], in_bytes);
         if (io & IO_IN0)

@@ -88,6 +88,7 @@ class _Dims:
 
     def __init__(self, model, B, T, fast: bool = False):
         self._table = None
+        self.device = model.encoder.device
         self.fast = bool(fast)     # `forward_fast` semantics: additive bias + L1 row normalisation, no state
         self.comm = None           # set by the neuron-sharded tensor-parallel wrapper
         c = model.config
@@ -141,6 +142,21 @@ class _Dims:
         # the chained-GEMM kernels (the [tokens, neurons] intermediates x*y, dy, dx never re-read by the GEMM that
         # contracts them) cover unsharded layers with D <= 256; PoPE keeps the separate launches (its rotated
         # copy has twice the width)
+        # chunk-state attention: the sequence is cut into J segments of C tokens; inside a segment the scores
+        # are the quadratic causal form, between segments the [N', D] state is handed on (and its gradient
+        # handed back), so the score matrix is [.., C] wide instead of [.., T]. `model.attention_chunk`: an int,
+        # or None = automatic (1024 from T = 4096 on, where the quadratic form starts to cost more than the
+        # state products). The row-normalised mode has no state; the neuron-sharded wrapper keeps one segment.
+        self.C = T
+        chunk = getattr(model, "attention_chunk", None)
+        if not self.fast and self.comm is None:
+            if chunk is None and T >= 4096 and T % 1024 == 0:
+                chunk = 1024
+            if chunk and 0 < int(chunk) < T and T % int(chunk) == 0 and int(chunk) % 64 == 0:
+                self.C = int(chunk)
+        self.J = T // self.C
+        self.Bs = B * self.J                         # number of (sequence, segment) problems
+        self.handoff = self.J > 1 or self.cp is not None   # states (and their gradients) cross segment borders
         ok = (self.comm is None and self.rot != "pope" and DG.eligible(self.M, self.T, self.N, self.D))
         which = getattr(model, "use_dual_gemm", None)
         if which is None:
@@ -148,7 +164,11 @@ class _Dims:
         which = set(str(which).split(",")) if which else set()
         self.dual_fwd = ok and bool(which & {"fwd", "all", "True"})
         self.dual_gate = ok and bool(which & {"gate", "all", "True"})
-        self.dual_dq = ok and bool(which & {"dq", "all", "True"})
+        self.dual_dq = ok and bool(which & {"dq", "all", "True"}) and not self.handoff
+
+    def decay(self, n: int):
+        """g^n per head as a [1, H, 1, 1] tensor, or None without ALiBi decay."""
+        return torch.exp(-self.slopes * float(n)).view(1, self.H, 1, 1) if self.slopes is not None else None
 
 
 _SM_COUNT = {}
@@ -181,21 +201,90 @@ def _bf16(rows, cols, dev):
 # ------------------------------------------------------------------------------------------------
 # one layer forward
 # ------------------------------------------------------------------------------------------------
+def _weighted_values(d: "_Dims", cur) -> torch.Tensor:
+    """g^(C-s) v_s per head, bf16 [H*M, D] (row h*M + token): what token s of a segment still contributes to the
+    state at the segment's end."""
+    H, C, M, D = d.H, d.C, d.M, d.D
+    t = torch.arange(C, device=cur.device, dtype=torch.float32)
+    w = torch.exp(-d.slopes.view(H, 1) * (C - t).view(1, C))
+    return (cur.view(1, d.Bs, C, D).float() * w.view(H, 1, C, 1)).to(torch.bfloat16).reshape(H * M, D)
+
+
 def _segment_state(d: "_Dims", q, cur) -> torch.Tensor:
-    """State this segment adds, sum_s g^(T-s) q_s^T v_s, fp32 [B, H, N', D]."""
-    B, H, T, M, D, Np = d.B, d.H, d.T, d.M, d.D, d.Np
-    dev = q.device
-    rho = torch.empty(B, H, Np, D, device=dev, dtype=torch.float32)
+    """State each segment adds, sum_s g^(C-s) q_s^T v_s, fp32 [B*J, H, N', D] (one segment per sequence
+    unless the attention is chunked)."""
+    Bs, H, C, M, D, Np = d.Bs, d.H, d.C, d.M, d.D, d.Np
+    rho = torch.empty(Bs, H, Np, D, device=q.device, dtype=torch.float32)
     if d.slopes is not None:
-        t = torch.arange(T, device=dev, dtype=torch.float32)
-        w = torch.exp(-d.slopes.view(H, 1) * (T - t).view(1, T))                     # g^(T-s)
-        vw = (cur.view(1, B, T, D).float() * w.view(H, 1, T, 1)).to(torch.bfloat16).reshape(H * M, D)
-        b_off = (0, 0, M, T)
+        vw, b_off = _weighted_values(d, cur), (0, 0, M, C)
     else:
-        vw, b_off = cur, (0, 0, 0, T)
-    G.gemm(q, vw, M=Np, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(Np, 0, 0, T), b_off=b_off,
-           c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho.view(B * H * Np, D))
+        vw, b_off = cur, (0, 0, 0, C)
+    G.gemm(q, vw, M=Np, N=D, K=C, a_mn=True, b_mn=True, nz=(H, Bs), a_off=(Np, 0, 0, C), b_off=b_off,
+           c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=rho.view(Bs * H * Np, D))
     return rho
+
+
+def _scan_forward(d: "_Dims", seg: Optional[torch.Tensor], rho0: Optional[torch.Tensor], want_total: bool):
+    """Hand the state on from segment to segment (and, under context parallelism, from rank to rank).
+    seg: fp32 [B*J, H, N', D], what every segment adds (None when nothing needs it); rho0: the state before
+    this call's first token. Returns (rin, total): rin bf16 [B*J*H*N', D], the state every segment starts
+    from (None when all of them start from zero), and the fp32 state after the last token (None unless
+    wanted)."""
+    B, J, H, Np, D = d.B, d.J, d.H, d.Np, d.D
+    gC = d.decay(d.C)
+    step = (lambda run: run) if gC is None else (lambda run: run * gC)
+    start = rho0.float() if rho0 is not None else None
+    segv = seg.view(B, J, H, Np, D) if seg is not None else None
+    total = None
+    if d.cp is not None:
+        run = None
+        for j in range(J):
+            run = segv[:, j] if run is None else step(run) + segv[:, j]
+        gT = d.decay(d.T)
+        start, total = d.cp.scan(run, start, gT if gT is not None else 1.0)
+    if J == 1 and start is None:
+        rin = None
+    else:
+        rin = torch.empty(B, J, H, Np, D, device=d.device, dtype=torch.bfloat16)
+    run = start
+    for j in range(J):
+        if rin is not None:
+            rin[:, j].zero_() if run is None else rin[:, j].copy_(run)
+        if j + 1 < J or (want_total and d.cp is None):
+            run = segv[:, j] if run is None else step(run) + segv[:, j]
+    if want_total and d.cp is None:
+        total = run
+    return (rin.view(B * J * H * Np, D) if rin is not None else None), total
+
+
+def _scan_backward(d: "_Dims", d_rin: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Reverse of `_scan_forward`: d_rin fp32 [B*J*H*N', D] (gradient of every segment's starting state, None
+    when no segment had one) -> gradient of every segment's own state, fp32 [B*J, H, N', D] (None when it is
+    exactly zero: a single segment that nobody continues from)."""
+    B, J, H, Np, D = d.B, d.J, d.H, d.Np, d.D
+    gC = d.decay(d.C)
+    step = (lambda acc: acc) if gC is None else (lambda acc: acc * gC)
+    drv = d_rin.view(B, J, H, Np, D) if d_rin is not None else None
+    acc = None
+    if d.cp is not None:
+        # what the later ranks' starting states pass back to this rank's total: they depend on this rank only
+        # through its total state, and on it with the weights of the forward scan
+        d_start = None
+        for j in reversed(range(J)):
+            if drv is not None:
+                d_start = drv[:, j] if d_start is None else drv[:, j] + step(d_start)
+        if d_start is None:
+            d_start = torch.zeros(B, H, Np, D, device=d.device, dtype=torch.float32)
+        gT = d.decay(d.T)
+        acc = d.cp.scan_backward(d_start.contiguous(), gT if gT is not None else 1.0)
+    if J == 1 and acc is None:
+        return None
+    dseg = torch.empty(B, J, H, Np, D, device=d.device, dtype=torch.float32)
+    for j in reversed(range(J)):
+        dseg[:, j].zero_() if acc is None else dseg[:, j].copy_(acc)
+        if j > 0:
+            acc = drv[:, j] if acc is None else drv[:, j] + step(acc)
+    return dseg.view(B * J, H, Np, D)
 
 
 def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool,
@@ -217,8 +306,10 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         G.gemm(cur, W["encoder"], M=M, N=d.HN, K=D, epi=G.EPI_RELU, out0=x, theta=d.theta)
 
     # tiles above the diagonal are never written; the canonical path never reads them either (S V stops at the
-    # diagonal tile, S^T dA starts at it); the row-normalised mode transposes whole matrices and wants zeros
-    S = (torch.zeros if d.fast else torch.empty)(B * H * T, T, device=dev, dtype=torch.bfloat16)
+    # diagonal tile, S^T dA starts at it); the row-normalised mode transposes whole matrices and wants zeros.
+    # The attention runs per (head, segment): Bs = B*J segments of C tokens (J = 1, C = T unless chunked).
+    C, Bs = d.C, d.Bs
+    S = (torch.zeros if d.fast else torch.empty)(Bs * H * C, C, device=dev, dtype=torch.bfloat16)
     rnorm = None
     if d.fast:
         # forward_fast (src/model/attention.rs:142-175): S = tril(q q^T, -1) + m_h (s - t), rows L1-normalised
@@ -231,44 +322,32 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         rnorm = torch.empty(B * H * T, device=dev, dtype=torch.float32)
         ops.rownorm_fwd(S, rnorm, T)
     else:
-        G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
+        G.gemm(q, q, M=C, N=C, K=Np, nz=(H, Bs), a_off=(0, C, Np, 0), b_off=(0, C, Np, 0), c_off=(C, H * C, 0, 0),
                epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=S)
     comm = d.comm
     carry_flags = G.F_ROWDECAY if d.slopes is not None else 0
-    cp = d.cp
-    rho_total = None
-    if cp is not None:
-        # context parallel: exchange the segment states, continue from what the earlier ranks left
-        g_T = torch.exp(-d.slopes * T).view(1, H, 1, 1) if d.slopes is not None else 1.0
-        rho_in, rho_total = cp.scan(_segment_state(d, q, cur), rho_in, g_T)
+    # states: what every segment adds, handed on from segment to segment (and rank to rank)
+    seg = _segment_state(d, q, cur) if (want_rho or d.handoff) else None
+    rin, rho_out = _scan_forward(d, seg, rho_in, want_rho)
+    del seg
     if comm is None:
         a = _bf16(H * M, D, dev)
-        G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
-               c_off=(M, T, 0, 0), causal_k=1, out0=a)
-        if rho_in is not None:
+        G.gemm(S, cur, M=C, N=D, K=C, b_mn=True, nz=(H, Bs), a_off=(C, H * C, 0, 0), b_off=(0, 0, 0, C),
+               c_off=(M, C, 0, 0), causal_k=1, out0=a)
+        if rin is not None:
             # carry-in: a_t += g^t (q_t . rho_in); the row decay g^t is applied in the epilogue
-            rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
-            G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
-                   c_off=(M, T, 0, 0), flags=G.F_ACCUM | carry_flags, slopes=d.slopes, out0=a)
+            G.gemm(q, rin, M=C, N=D, K=Np, b_mn=True, nz=(H, Bs), a_off=(0, C, Np, 0), b_off=(0, 0, Np, H * Np),
+                   c_off=(M, C, 0, 0), flags=G.F_ACCUM | carry_flags, slopes=d.slopes, out0=a)
     else:
         # neuron-sharded: this rank's scores cover its slice of the neurons, so S V is a partial sum;
         # the GEMM's epilogue is the cross-rank reduction (parallel/tp.py: TPComm)
-        buf = comm.begin("a", H * M, D, launches=1 if rho_in is None else 2)
+        buf = comm.begin("a", H * M, D, launches=1 if rin is None else 2)
         G.gemm(S, cur, M=T, N=D, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(0, 0, 0, T),
                c_off=(M, T, 0, 0), causal_k=1, flags=comm.flags, out0=buf.view, **buf.kw)
-        if rho_in is not None:
-            rin = rho_in.reshape(B * H * Np, D).to(torch.bfloat16)
+        if rin is not None:
             G.gemm(q, rin, M=T, N=D, K=Np, b_mn=True, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, 0, Np, H * Np),
                    c_off=(M, T, 0, 0), flags=comm.flags | carry_flags, slopes=d.slopes, out0=buf.view, **buf.kw)
         a = comm.end(buf, bf16=True)
-    rho_out = None
-    if cp is not None:
-        rho_out = rho_total
-    elif want_rho:
-        rho_out = _segment_state(d, q, cur)
-        if rho_in is not None:
-            # the carried state has decayed by g^T over this segment
-            rho_out += rho_in if d.slopes is None else rho_in * torch.exp(-d.slopes * T).view(1, H, 1, 1)
     lna = torch.empty_like(a)
     ops.layernorm_fwd(a, lna)
     # y is not stored: the backward recovers it as xy / x
@@ -302,7 +381,7 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         mlp = comm.end(buf, bf16=True)
     out = torch.empty_like(cur)
     ops.block_out_fwd(cur, mlp, out)
-    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed, rnorm=rnorm)
+    saved = dict(cur=cur, x=x, q=q, S=S, a=a, lna=lna, xy=xy, mlp=mlp, drop_seed=drop_seed, rnorm=rnorm, rin=rin)
     return out, saved, rho_out
 
 
@@ -318,6 +397,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
     Weight gradients are accumulated into grads['encoder'|'encoder_v'|'decoder'] (fp32)."""
     dev = dout.device
     M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
+    C, Bs = d.C, d.Bs
     cur, x, q, S, a, lna, xy, mlp = (sv[k] for k in ("cur", "x", "q", "S", "a", "lna", "xy", "mlp"))
     dcur = torch.empty(M, D, device=dev, dtype=torch.float32)
     dmlp = _bf16(M, D, dev)
@@ -375,11 +455,11 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
         Gs = (Gl3 + Gl3.transpose(1, 2)).reshape(B * H * T, T)
         del Gl, Gl3
     else:
-        # attention: Gs = causal(dA V^T) + causal(dA V^T)^T with the decay mask
-        Gs = _bf16(B * H * T, T, dev)
-        G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
+        # attention: Gs = causal(dA V^T) + causal(dA V^T)^T with the decay mask, per (head, segment)
+        Gs = _bf16(Bs * H * C, C, dev)
+        G.gemm(da, cur, M=C, N=C, K=D, nz=(H, Bs), a_off=(M, C, 0, 0), b_off=(0, C, 0, 0), c_off=(C, H * C, 0, 0),
                epi=G.EPI_CAUSAL, slopes=d.slopes, causal_tiles=1, out0=Gs)
-        G.gemm(cur, da, M=T, N=T, K=D, nz=(H, B), a_off=(0, T, 0, 0), b_off=(M, T, 0, 0), c_off=(T, H * T, 0, 0),
+        G.gemm(cur, da, M=C, N=C, K=D, nz=(H, Bs), a_off=(0, C, 0, 0), b_off=(M, C, 0, 0), c_off=(C, H * C, 0, 0),
                epi=G.EPI_CAUSAL, flags=G.F_UPPER, slopes=d.slopes, causal_tiles=2, out0=Gs)
     # dV (v = cur for every head): dcur[b] += sum_h S_h^T dA_h
     if comm is None:
@@ -387,13 +467,49 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
     else:
         pbuf = comm.begin("dcur", M, D, launches=2)        # partial sums over the neuron shards: dV and the encoder path
         part, pflags, pkw = pbuf.view, comm.flags, pbuf.kw
-    # all heads in one launch: every (head, batch) problem adds its [T, D] tile into the rows of its batch
+    # all heads in one launch: every (head, segment) problem adds its [C, D] tile into the rows of its segment
     # (row block s only needs t >= s: the contraction starts at the tile's first row; in the row-normalised
     # mode S holds zeros above the diagonal, elsewhere that part is never written and must not be read)
-    G.gemm(S, da, M=T, N=D, K=T, a_mn=True, b_mn=True, nz=(H, B), a_off=(0, 0, T, H * T), b_off=(0, 0, M, T),
-           c_off=(0, T, 0, 0), flags=(pflags & ~G.F_ACCUM) | (G.F_ATOMIC if pflags & G.F_ACCUM else 0), out0=part,
+    G.gemm(S, da, M=C, N=D, K=C, a_mn=True, b_mn=True, nz=(H, Bs), a_off=(0, 0, C, H * C), b_off=(0, 0, M, C),
+           c_off=(0, C, 0, 0), flags=(pflags & ~G.F_ACCUM) | (G.F_ATOMIC if pflags & G.F_ACCUM else 0), out0=part,
            causal_k=2, **pkw)
-    # dq = Gs q, then back through rotation, + gate gradient, ReLU mask
+    # states across segment borders: a_t also holds g^t q_t . rin (rin = the state its segment starts from), and
+    # every segment's own state sum_s g^(C-s) q_s^T v_s feeds the later segments
+    x2 = r2 = None            # extra contraction for dq: [g^t dA | g^(C-s) v] . [rin | d seg]^T over 2 D columns
+    if d.handoff:
+        rin = sv.get("rin")
+        if d.slopes is not None:
+            t = torch.arange(C, device=dev, dtype=torch.float32)
+            w_in = torch.exp(-d.slopes.view(H, 1) * t.view(1, C))
+            da_w = (da.view(H, Bs, C, D).float() * w_in.view(H, 1, C, 1)).to(torch.bfloat16).view(H * M, D)
+        else:
+            da_w = da
+        d_rin = None
+        if rin is not None:
+            # gradient of the starting states: sum_t g^t q_t^T dA_t
+            d_rin = torch.empty(Bs * H * Np, D, device=dev, dtype=torch.float32)
+            G.gemm(q, da_w, M=Np, N=D, K=C, a_mn=True, b_mn=True, nz=(H, Bs), a_off=(Np, 0, 0, C), b_off=(0, 0, M, C),
+                   c_off=(Np, H * Np, 0, 0), flags=G.F_OUT_F32, out0=d_rin)
+        dseg = _scan_backward(d, d_rin)
+        del d_rin
+        xs, rs = [], []
+        if rin is not None:
+            xs.append(da_w); rs.append(rin)
+        if dseg is not None:
+            dseg16 = dseg.view(Bs * H * Np, D).to(torch.bfloat16)
+            del dseg
+            # through the segment state to its values: dv_s += g^(C-s) sum_h q_s . d seg_h
+            G.gemm(q, dseg16, M=C, N=D, K=Np, b_mn=True, nz=(H, Bs), a_off=(0, C, Np, 0), b_off=(0, 0, Np, H * Np),
+                   c_off=(0, C, 0, 0), flags=G.F_OUT_F32 | G.F_ATOMIC | (G.F_ROWDECAY_REV if d.slopes is not None else 0),
+                   slopes=d.slopes, T=C, out0=dcur)
+            xs.append(_weighted_values(d, cur) if d.slopes is not None
+                      else cur.view(1, M, D).expand(H, M, D).reshape(H * M, D))
+            rs.append(dseg16)
+        if xs:
+            x2 = xs[0] if len(xs) == 1 else torch.cat(xs, 1)
+            r2 = rs[0] if len(rs) == 1 else torch.cat(rs, 1)
+        del xs, rs, da_w
+    # dq = Gs q (+ the state terms), then back through rotation, + gate gradient, ReLU mask
     dx = _bf16(M, d.HN, dev)
     if d.dual_dq:
         # dq = Gs q, rotation undone, + gate gradient, ReLU mask, and d cur += dx . E in one kernel
@@ -403,14 +519,29 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
                 in1=d.table(pos0) if rope else None, pos0=pos0, accumulate=True)
     elif d.rot == "pope":
         dq = _bf16(M, d.HNp, dev)
-        G.gemm(Gs, q, M=T, N=Np, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(Np, 0, 0, T),
-               c_off=(0, T, Np, 0), out0=dq)
+        G.gemm(Gs, q, M=C, N=Np, K=C, b_mn=True, nz=(H, Bs), a_off=(C, H * C, 0, 0), b_off=(Np, 0, 0, C),
+               c_off=(0, C, Np, 0), out0=dq)
+        if x2 is not None:
+            G.gemm(x2, r2, M=C, N=Np, K=x2.shape[1], nz=(H, Bs), a_off=(M, C, 0, 0), b_off=(Np, H * Np, 0, 0),
+                   c_off=(0, C, Np, 0), flags=G.F_ACCUM, out0=dq)
         ops.pope_bwd(dq, x, dxg, d.freqs_full, dx, H, T, pos0)
     else:
         rope = d.rot == "rope"
-        G.gemm(Gs, q, M=T, N=N, K=T, b_mn=True, nz=(H, B), a_off=(T, H * T, 0, 0), b_off=(N, 0, 0, T),
-               c_off=(0, T, N, 0), epi=G.EPI_DQ_BWD, flags=(G.F_ROPE | G.F_TABLE) if rope else 0, in0=dxg,
-               in1=d.table(pos0) if rope else None, out0=dx, T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
+        rflags = (G.F_ROPE | G.F_TABLE) if rope else 0
+        table = d.table(pos0) if rope else None
+        if x2 is not None:
+            # two contractions meet in one epilogue: the first launch leaves its rotated-back sum in the gate
+            # gradient's place (closed gates keep their marker), the second adds Gs q to it
+            dxg2 = _bf16(M, d.HN, dev)
+            G.gemm(x2, r2, M=C, N=N, K=x2.shape[1], nz=(H, Bs), a_off=(M, C, 0, 0), b_off=(Np, H * Np, 0, 0),
+                   c_off=(0, C, N, 0), epi=G.EPI_DQ_BWD, flags=rflags | G.F_KEEP_MARK, in0=dxg, in1=table, out0=dxg2,
+                   T=T, pos0=pos0, n_per_head=N, freqs=d.freqs)
+            dxg = dxg2
+            del dxg2
+        G.gemm(Gs, q, M=C, N=N, K=C, b_mn=True, nz=(H, Bs), a_off=(C, H * C, 0, 0), b_off=(N, 0, 0, C),
+               c_off=(0, C, N, 0), epi=G.EPI_DQ_BWD, flags=rflags, in0=dxg, in1=table, out0=dx, T=T, pos0=pos0,
+               n_per_head=N, freqs=d.freqs)
+    del x2, r2
     del dxg
     o, fl, kw = _wgrad_target(d, grads, "encoder", wflags, final)
     G.gemm(dx, cur, M=d.HN, N=D, K=km, a_mn=True, b_mn=True, nz=(1, sk), a_off=(0, 0, 0, km), b_off=(0, 0, 0, km),
@@ -482,7 +613,8 @@ def recompute_count(model, d: _Dims) -> int:
 def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int):
     """`recompute` = number of leading layers that keep only their input (and dropout seed)."""
     cur = _embed(d, W, tokens)
-    pos0 = state.position if state is not None else 0
+    # (training of a segment of longer sequences - context parallelism - starts at `model._train_pos0`)
+    pos0 = state.position if state is not None else int(getattr(model, "_train_pos0", 0))
     saved: List[dict] = []
     for l in range(d.L):
         rho_in = state.layers[l].rho if state is not None else None
@@ -535,6 +667,7 @@ class _FusedLoss(torch.autograd.Function):
         ctx.d, ctx.W, ctx.saved, ctx.final, ctx.dlogits = d, W, saved, cur, dlogits
         ctx.tokens = tokens
         ctx.recompute = recompute
+        ctx.pos0 = int(getattr(model, "_train_pos0", 0))
         return row_loss.sum() / d.M
 
     @staticmethod
@@ -558,9 +691,9 @@ class _FusedLoss(torch.autograd.Function):
             sv = saved[l]
             if "x" not in sv:
                 with prof.phase("layer.recompute"):
-                    _, sv, _ = _layer_forward(d, W, sv["cur"], 0, None, False, sv["drop_seed"])
+                    _, sv, _ = _layer_forward(d, W, sv["cur"], ctx.pos0, None, False, sv["drop_seed"])
             with prof.phase("layer.backward"):
-                dcur = _layer_backward(d, W, sv, dcur, grads, 0, final=(l == 0))
+                dcur = _layer_backward(d, W, sv, dcur, grads, ctx.pos0, final=(l == 0))
             saved[l] = None
         g_emb = torch.zeros(d.V, d.D, device=dev, dtype=torch.float32)
         ops.embed_ln_bwd(ctx.tokens.reshape(-1).contiguous(), W["embed"], dcur, g_emb)

@@ -25,6 +25,8 @@ F_OUT_F32, F_ACCUM, F_ROPE, F_POPE, F_UPPER, F_NO_OUT0, F_TABLE, F_MC_RED, F_ATO
 F_PEER_RS = 1024
 F_BIAS = 64
 F_ROWDECAY = 2048
+F_KEEP_MARK = 4096        # EPI_DQ_BWD: closed gates keep the -0.0 marker in out0 (a second launch adds to it)
+F_ROWDECAY_REV = 8192     # EPI_STORE: row m scaled by exp(-slope * (T - m))
 
 _SUPPORTED = {
     (256, False, False, EPI_STORE), (256, False, False, EPI_RELU), (256, False, False, EPI_RELU_GATE),
@@ -219,6 +221,9 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                 if flags & F_ROWDECAY:
                     slope = float(slopes[z0]) if slopes is not None else 0.0
                     v = v * torch.exp(-slope * mm.float())[:, None]
+                if flags & F_ROWDECAY_REV:
+                    slope = float(slopes[z0]) if slopes is not None else 0.0
+                    v = v * torch.exp(-slope * (T - mm).float())[:, None]
                 if flags & (F_ACCUM | F_ATOMIC):
                     v = v + out0[rs, cs].float()
                 out0[rs, cs] = v.to(out0.dtype)
@@ -288,10 +293,11 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                 closed = g_raw.contiguous().view(torch.int16) == -32768
                 v = acc
                 if flags & F_ROPE:
-                    pos = pos0 + (mm % T)
+                    pos = pos0 + ((r0 + mm) % T)           # position of the output row (table mode of the kernel)
                     ph = rot_phases(pos, freqs.repeat_interleave(2)[(nn % n_per_head)])
                     v = rope_rotate(v, ph, inverse=True)
-                v = v * alpha + g_raw.float()
-                out0[rs, cs] = torch.where(closed, torch.zeros_like(v), v).to(out0.dtype)
+                v = v * alpha + g_raw.float() + 0.0
+                mark = -0.0 if flags & F_KEEP_MARK else 0.0
+                out0[rs, cs] = torch.where(closed, torch.full_like(v, mark), v).to(out0.dtype)
             else:
                 raise ValueError(f"unknown epilogue {epi}")

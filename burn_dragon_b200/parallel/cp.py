@@ -13,7 +13,8 @@ earlier tokens left behind,
 so the result equals the single-device forward over the concatenated sequence. For training the
 same hand-off is an autograd function (`scan_grad`: the gradient of every later rank's starting
 state flows back to the earlier ranks' segment states), so `loss()` + `reduce_gradients()` give the
-loss and gradients of whole sequences that no single rank holds (torch path of the model). After the call
+loss and gradients of whole sequences that no single rank holds (on the kernel path the hand-off and
+its reverse are explicit steps of the layer's forward and backward pass). After the call
 every rank holds the state of the whole sequence, so decoding can continue on any of them. The
 message is the state itself (33 MB fp32 per layer for the base model), so this pays when the
 per-rank segment is much longer than the state is wide. The reference has no sequence parallelism
@@ -81,6 +82,19 @@ class ContextParallel:
             run = parts[r] if run is None else run * g_T + parts[r]
         return rho_in, run
 
+    def scan_backward(self, d_start: torch.Tensor, g_T) -> torch.Tensor:
+        """Backward of `scan` for the kernel path (which writes its own backward pass): d_start is the
+        gradient of the state this rank started from; returns the gradient of this rank's own segment
+        state, sum over the later ranks r' of g_T^(r' - 1 - rank) d_start^{r'} (one all-gather)."""
+        grads = [torch.empty_like(d_start) for _ in range(self.world)]
+        dist.all_gather(grads, d_start.contiguous(), group=self.group)
+        acc = torch.zeros_like(d_start)
+        w = 1.0
+        for r in range(self.rank + 1, self.world):
+            acc = acc + grads[r] * w
+            w = w * g_T
+        return acc
+
     def scan_grad(self, rho_loc: torch.Tensor, g_T) -> torch.Tensor:
         """Differentiable `scan` for training (no state before the sequence): the state this rank
         starts from, as a function of every earlier rank's segment state."""
@@ -90,12 +104,22 @@ class ContextParallel:
         """Training loss of this rank's segment of sequences that are split over the ranks (rank r
         holds tokens [r*T, (r+1)*T) of every sequence). The gradients of later segments reach earlier
         ranks through the state hand-off; call `reduce_gradients()` after `backward()`. The mean over
-        the ranks' losses is the loss of the whole sequences. Runs the torch path of the model."""
+        the ranks' losses is the loss of the whole sequences. Runs on the kernels where they cover the
+        model (the hand-off and its reverse are then part of the kernel path's own forward and backward
+        pass, `ops/fused_bdh.py::_scan_forward/_scan_backward`), else on the torch path."""
+        from ..ops import fused_bdh
         from ..ops import reference as R
         model = self.model
+        start = self.rank * tokens_local.shape[1]
         model._cp = self
         try:
-            logits = model._forward_torch(tokens_local, None, "parallel", start=self.rank * tokens_local.shape[1])
+            if getattr(self, "use_kernels", True) and fused_bdh.can_run(model, tokens_local, None):
+                model._train_pos0 = start
+                try:
+                    return fused_bdh.loss(model, tokens_local, targets_local)
+                finally:
+                    model._train_pos0 = 0
+            logits = model._forward_torch(tokens_local, None, "parallel", start=start)
         finally:
             model._cp = None
         return R.cross_entropy_mean(logits, targets_local)

@@ -201,11 +201,11 @@ def main() -> int:
     else:
         dist_utils.init_distributed("nccl")
         dev = torch.device("cuda", dist_utils.env_local_rank())
-    if args.case in ("fsdp", "tp", "tp_reduce", "tp_reduce_bw", "cp", "cp_train", "ckpt", "accum", "clip"):
+    if args.case in CASES:
+        fn = CASES[args.case]
+    else:
         import selftest_sharded
         fn = getattr(selftest_sharded, "case_" + args.case)
-    else:
-        fn = CASES[args.case]
     note = fn(dev)
     from burn_dragon_b200.parallel import symm
     if symm.GUARD_BYTES and args.case != "rank_exit":

@@ -423,3 +423,49 @@ def case_cp_train(dev):
             assert _rel(p.grad, ref[n]) < 1e-4, (rot, n, _rel(p.grad, ref[n]))
         notes.append(rot)
     return " ".join(notes)
+
+
+def case_cp_train_kernels(dev):
+    """Context-parallel training on the kernel path: every rank trains its slice of the sequences on the
+    kernels (or their emulation), the layer's own forward / backward pass hands the states on and their
+    gradients back, once with one segment per rank and once with the rank's slice cut into two segments.
+    Loss and gradients against the single-process torch definition over the whole sequences, at the
+    tolerance of bf16 activations."""
+    from burn_dragon_b200.ops import fused_bdh
+    from burn_dragon_b200.parallel.cp import ContextParallel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    T = 128
+    notes = []
+    for rot in ("alibi", "rope", "pope"):
+        for chunk in (None, 64):
+            m = _bdh(dev, rot)
+            with torch.no_grad():
+                m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
+            for p in m.parameters():
+                dist.broadcast(p.data, src=0)
+            g = torch.Generator().manual_seed(9)
+            data = torch.randint(0, 256, (2, world * T + 1), generator=g).to(dev)
+            x, y = data[:, :-1], data[:, 1:]
+            m.zero_grad()
+            m.use_native = False
+            want = m(x, y, mode="parallel")
+            want.backward()
+            ref = {n: p.grad.clone() for n, p in m.named_parameters()}
+            m.zero_grad()
+            m.use_native = True
+            m.attention_chunk = chunk
+            cp = ContextParallel(m)
+            sl = slice(rank * T, (rank + 1) * T)
+            xs, ys = x[:, sl].contiguous(), y[:, sl].contiguous()
+            assert fused_bdh.can_run(m, xs, None), "the kernel path must take this case"
+            loss = cp.loss(xs, ys)
+            loss.backward()
+            cp.reduce_gradients()
+            total = loss.detach().clone()
+            dist.all_reduce(total)
+            assert abs(total.item() / world - want.item()) < 2e-2, (rot, chunk, total.item() / world, want.item())
+            for n, p in m.named_parameters():
+                cos = torch.nn.functional.cosine_similarity(p.grad.flatten(), ref[n].flatten(), dim=0).item()
+                assert cos > 0.99 and _rel(p.grad, ref[n]) < 0.12, (rot, chunk, n, cos, _rel(p.grad, ref[n]))
+            notes.append(f"{rot}/{chunk}")
+    return " ".join(notes)

@@ -56,9 +56,9 @@ def test_sampler_greedy_topk_and_distribution():
     assert int(s4.min()) >= 0 and int(s4.max()) < 256
 
 
-def _model(rot):
+def _model(rot, vocab=256):
     torch.manual_seed(0)
-    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=256, vocab_size=256, dropout=0.0,
+    m = BDH(BDHConfig(n_layer=2, n_embd=64, n_head=2, n_latent_per_head=256, vocab_size=vocab, dropout=0.0,
                       rotary_embedding=rot)).cuda().eval()
     with torch.no_grad():
         m.encoder.mul_(4.0); m.encoder_v.mul_(4.0); m.decoder.mul_(4.0)
@@ -88,6 +88,27 @@ def test_engine_matches_fp32_recurrence_teacher_forced(rot, graph):
     assert _rel(eng.last_logits, ref_logits) < 0.08
     for a, b in zip(eng.last_state.layers, st.layers):
         assert _rel(a.rho, b.rho) < 0.05
+
+
+def test_engine_with_a_character_vocabulary_of_69_symbols():
+    """The LM head of a character-level model has a width that is no multiple of 8 (69 here), which
+    a TMA row pitch cannot express: the captured step then takes the head product from a library
+    matmul into the same logits buffer, and the sampler sees exactly V columns."""
+    V = 69
+    m = _model("rope", vocab=V)
+    eng = DE.attach(m)
+    B, P, n = 3, 48, 16
+    prompt = torch.randint(0, V, (B, P), device="cuda")
+    native.clear_status()
+    out = GEN.generate_tokens(m, prompt, settings=GEN.GenerationSettings(max_new_tokens=n, temperature=1.0, seed=5))
+    assert native.status_code() == 0
+    assert out.shape == (B, P + n) and int(out.max()) < V and int(out.min()) >= 0
+    m.use_native = False
+    st = m.init_state()
+    with torch.no_grad():
+        ref_logits = m.forward_with_state(out, st, mode="recurrent")[:, -1]
+    assert eng.last_logits.shape[-1] == V
+    assert _rel(eng.last_logits, ref_logits) < 0.08
 
 
 def test_engine_greedy_is_deterministic_and_streams_independent():

@@ -437,3 +437,54 @@ def test_time_block_pattern_in_the_row_normalised_mode_on_the_kernel_path():
     assert abs(got.item() - ref.item()) < 2e-2
     for n, p in m.named_parameters():
         assert ((p.grad - want[n]).norm() / (want[n].norm() + 1e-12)).item() < 0.1, n
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_chunk_state_attention_equals_the_quadratic_form(rot):
+    """Attention over segments of C tokens with the state handed on between them (and its gradient handed
+    back) is the same function as one quadratic form over the whole sequence: loss and every gradient of
+    the chunked kernel path against the unchunked kernel path and the torch definition."""
+    m = _model(rot)
+    tok, tgt = torch.randint(0, 256, (2, 256)), torch.randint(0, 256, (2, 256))
+    with emulate.kernel_path():
+        m.attention_chunk = 64                 # four segments per sequence
+        d = fused_bdh._Dims(m, 2, 256)
+        assert d.J == 4 and d.handoff
+        loss_c = m(tok, tgt)
+        loss_c.backward()
+        gc = {n: p.grad.clone() for n, p in m.named_parameters()}
+        m.zero_grad()
+        m.attention_chunk = 256                # one segment: the quadratic form
+        loss_q = m(tok, tgt)
+        loss_q.backward()
+        gq = {n: p.grad.clone() for n, p in m.named_parameters()}
+        m.zero_grad()
+    m.attention_chunk = None
+    loss_t = m(tok, tgt, mode="parallel")
+    loss_t.backward()
+    assert abs(loss_c.item() - loss_q.item()) < 5e-3 and abs(loss_c.item() - loss_t.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert _rel(gc[n], gq[n]) < 0.05, (n, _rel(gc[n], gq[n]))
+        assert _cos(gc[n], p.grad) > 0.99 and _rel(gc[n], p.grad) < 0.12, (n, _cos(gc[n], p.grad), _rel(gc[n], p.grad))
+
+
+@pytest.mark.parametrize("rot", ["alibi", "rope", "pope"])
+def test_chunked_prefill_equals_the_recurrence(rot):
+    """recurrent == chunked: logits and final state of a prefill that runs as segments with a carried state,
+    started from a non-empty state, against the token-by-token recurrence."""
+    m = _model(rot).eval()
+    tok = torch.randint(0, 256, (2, 64 + 256))
+    with torch.no_grad():
+        st_t = m.init_state()
+        want = m.forward_with_state(tok, st_t, mode="recurrent")
+        with emulate.kernel_path():
+            m.attention_chunk = 64
+            st = m.init_state()
+            first = m.forward_with_state(tok[:, :64], st)             # leaves a state behind
+            rest = m.forward_with_state(tok[:, 64:], st)              # four segments continuing from it
+        m.attention_chunk = None
+    got = torch.cat([first, rest], 1)
+    assert _rel(got, want) < 0.05
+    assert st.position == st_t.position
+    for a, b in zip(st.layers, st_t.layers):
+        assert _rel(a.rho, b.rho) < 0.05

@@ -179,6 +179,51 @@ def test_dq_bwd(rope):
         _check(k, r)
 
 
+@pytest.mark.parametrize("rope", ["none", "table"])
+def test_dq_bwd_over_segments_with_two_contractions_in_one_epilogue(rope):
+    """Chunk-state attention's dq: every (head, segment) problem covers C rows of a sequence of T positions
+    (the rotary table row is the position of the OUTPUT row), and two products meet in the epilogue: the
+    first launch keeps the -0.0 markers of closed gates in its output (`F_KEEP_MARK`), the second takes that
+    output as its gate-gradient input."""
+    T, C, N, Nh, K2 = 256, 128, 512, 256, 128
+    J = T // C
+    gs = _rand(T, C, 0.2, seed=21)                  # J blocks of [C, C]
+    q = _rand(T, N, seed=22)
+    x2, r2 = _rand(T, K2, 0.3, seed=25), _rand(J * N, K2, 0.3, seed=26)
+    x, dxg = _rand(T, N, seed=23).relu(), _rand(T, N, seed=24)
+    dxg = torch.where(x > 0, dxg, torch.full_like(dxg, -0.0))
+    freqs = ((1.0 / (65536.0 ** (torch.arange(Nh, device="cuda").div(2, rounding_mode="floor") * 2 / Nh)))
+             / 6.283185307)[0::2].float().contiguous()
+    flags = G.F_ROPE | G.F_TABLE if rope == "table" else 0
+    table = G.rope_table(3, T, freqs) if rope == "table" else None
+    common = dict(M=C, N=N, nz=(1, J), c_off=(0, C, 0, 0), epi=G.EPI_DQ_BWD, in1=table, T=T, pos0=3, n_per_head=Nh,
+                  freqs=freqs)
+    first = dict(a=x2, b=r2, K=K2, a_off=(0, C, 0, 0), b_off=(0, N, 0, 0), flags=flags | G.F_KEEP_MARK, in0=dxg, **common)
+    pairs = _run_both(first, dict(out0=torch.zeros(T, N, device="cuda", dtype=torch.bfloat16)))
+    for k, r in pairs:
+        _check(k, r)
+        assert torch.equal(k.view(torch.int16) == -32768, x <= 0), "exactly the closed gates carry the marker"
+    mid = pairs[0][0]
+    second = dict(a=gs, b=q, K=C, b_mn=True, a_off=(0, C, 0, 0), b_off=(0, 0, 0, C), flags=flags, in0=mid, **common)
+    for k, r in _run_both(second, dict(out0=torch.zeros(T, N, device="cuda", dtype=torch.bfloat16))):
+        _check(k, r)
+        assert not (k.view(torch.int16) == -32768).any()
+
+
+def test_store_reversed_row_decay_with_atomics():
+    """`F_ROWDECAY_REV`: row m of a segment of T rows scaled by exp(-slope * (T - m)), per head, the heads'
+    tiles added into one fp32 output (gradient of a segment state w.r.t. the values)."""
+    H, C, Np, D = 3, 128, 256, 64
+    q = _rand(C, H * Np, 0.3, seed=31)
+    st = _rand(H * Np, D, 0.3, seed=32)
+    slopes = torch.tensor([0.05, 0.01, 0.002], device="cuda")
+    out = torch.randn(C, D, device="cuda")
+    kw = dict(a=q, b=st, M=C, N=D, K=Np, b_mn=True, nz=(H, 1), a_off=(0, 0, Np, 0), b_off=(0, 0, Np, 0),
+              flags=G.F_OUT_F32 | G.F_ATOMIC | G.F_ROWDECAY_REV, slopes=slopes, T=C)
+    for k, r in _run_both(kw, dict(out0=out)):
+        _check(k, r, tol=1e-2)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("alibi", [True, False])
 def test_rownorm_attention_matches_reference(alibi):

@@ -49,6 +49,10 @@ def test_context_parallel_equals_single_gpu():
     run_ranks("cp", cpu=False)
 
 
+def test_context_parallel_training_on_the_kernels_equals_single_gpu():
+    run_ranks("cp_train_kernels", cpu=False)
+
+
 def test_checkpoint_resume_under_fsdp_and_tp():
     run_ranks("ckpt", cpu=False)
 

@@ -208,6 +208,12 @@ def test_context_parallel_training_gradients(n):
     run_ranks("cp_train", n=n)
 
 
+def test_context_parallel_training_on_the_emulated_kernel_path():
+    """The same, with every rank's slice on the kernel path's orchestration: the state hand-off and its
+    reverse are steps of the layer's own forward / backward pass there (one or two segments per rank)."""
+    run_ranks("cp_train_kernels", n=2, env={"BDH_EMULATE_KERNELS": "1"})
+
+
 def test_training_loop_aborts_on_a_kernel_status():
     """A bounded wait that ran out makes its kernel return early and sets the status word. The trainer
     polls that word once per step (asynchronously), so the loop must stop with `KernelTimeout` no later
