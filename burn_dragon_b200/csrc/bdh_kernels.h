@@ -113,6 +113,11 @@ int bdh_embed_ln_bwd(const long long* tokens, const void* emb_bf16, const float*
 // out = LayerNorm(cur + LayerNorm(mlp))  (reference: src/model/bdh.rs:436-441).
 int bdh_block_out_fwd(const void* cur_bf16, const void* mlp_bf16, void* out_bf16, long long rows,
                       int D, cudaStream_t s);
+// Decode step: y_bf16 = LayerNorm(a_f32) and a_f32 <- 0 (the rows are atomically accumulated again by the next layer).
+int bdh_layernorm_f32_clear(float* a_f32, void* y_bf16, long long rows, int D, cudaStream_t s);
+// Decode step: out = LayerNorm(cur + LayerNorm(sum_p part[p])) with part fp32 [parts, rows, D].
+int bdh_block_out_parts(const void* cur_bf16, const float* part_f32, int parts, void* out_bf16, long long rows,
+                        int D, cudaStream_t s);
 // Given d_out (fp32): d_cur_f32 (=) du, d_mlp_bf16 = LNbwd(mlp, du) where u = cur + LN(mlp).
 int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* dout_f32,
                       float* dcur_f32, void* dmlp_bf16, long long rows, int D, cudaStream_t s);

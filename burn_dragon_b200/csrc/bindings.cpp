@@ -200,6 +200,22 @@ void block_out_fwd(const Tensor& cur, const Tensor& mlp, Tensor& out) {
   check_rows(cur, D, at::kBFloat16, "cur"); check_rows(mlp, D, at::kBFloat16, "mlp"); check_rows(out, D, at::kBFloat16, "out");
   check_rc(bdh_block_out_fwd(cur.data_ptr(), mlp.data_ptr(), out.data_ptr(), cur.numel() / D, D, cur_stream()), "block_out_fwd");
 }
+void layernorm_f32_clear(Tensor& a, Tensor& y) {
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t D = a.size(-1);
+  check_rows(a, D, at::kFloat, "a"); check_rows(y, D, at::kBFloat16, "y");
+  TORCH_CHECK(a.numel() == y.numel(), "layernorm_f32_clear: shapes differ");
+  check_rc(bdh_layernorm_f32_clear(a.data_ptr<float>(), y.data_ptr(), a.numel() / D, D, cur_stream()), "layernorm_f32_clear");
+}
+void block_out_parts(const Tensor& cur, const Tensor& part, Tensor& out) {
+  c10::cuda::CUDAGuard guard(cur.device());
+  const int64_t D = cur.size(-1);
+  check_rows(cur, D, at::kBFloat16, "cur"); check_rows(part, D, at::kFloat, "part"); check_rows(out, D, at::kBFloat16, "out");
+  TORCH_CHECK(cur.numel() > 0 && part.numel() % cur.numel() == 0 && out.numel() == cur.numel(),
+              "block_out_parts: part must hold a whole number of [rows, D] tiles");
+  check_rc(bdh_block_out_parts(cur.data_ptr(), part.data_ptr<float>(), static_cast<int>(part.numel() / cur.numel()),
+                               out.data_ptr(), cur.numel() / D, D, cur_stream()), "block_out_parts");
+}
 void block_out_bwd(const Tensor& cur, const Tensor& mlp, const Tensor& dout, Tensor& dcur, Tensor& dmlp) {
   c10::cuda::CUDAGuard guard(cur.device());
   const int64_t D = cur.size(-1);
@@ -445,6 +461,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("embed_ln_fwd(Tensor tokens, Tensor emb, Tensor(a!) cur) -> ()");
   m.def("embed_ln_bwd(Tensor tokens, Tensor emb, Tensor dcur, Tensor(a!) demb) -> ()");
   m.def("block_out_fwd(Tensor cur, Tensor mlp, Tensor(a!) out) -> ()");
+  m.def("layernorm_f32_clear(Tensor(a!) a, Tensor(b!) y) -> ()");
+  m.def("block_out_parts(Tensor cur, Tensor part, Tensor(a!) out) -> ()");
   m.def("block_out_bwd(Tensor cur, Tensor mlp, Tensor dout, Tensor(a!) dcur, Tensor(b!) dmlp) -> ()");
   m.def("cross_entropy(Tensor logits, Tensor targets, Tensor(a!) row_loss, Tensor(b!)? dlogits, float grad_scale) -> ()");
   m.def("adamw(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p16, float lr, float beta1, "
@@ -490,6 +508,8 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("embed_ln_fwd", &embed_ln_fwd);
   m.impl("embed_ln_bwd", &embed_ln_bwd);
   m.impl("block_out_fwd", &block_out_fwd);
+  m.impl("layernorm_f32_clear", &layernorm_f32_clear);
+  m.impl("block_out_parts", &block_out_parts);
   m.impl("block_out_bwd", &block_out_bwd);
   m.impl("cross_entropy", &cross_entropy);
   m.impl("adamw", &adamw);

@@ -274,6 +274,58 @@ block_out_fwd_kernel(const __nv_bfloat16* cur, const __nv_bfloat16* mlp, __nv_bf
   }
 }
 
+// Decode step, attention output: y = LN(a) for fp32 rows that the state-update kernel accumulated with
+// atomics, and the rows are cleared for the next layer's accumulation in the same pass (one launch instead of
+// a cast, a LayerNorm and a fill).
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_f32_clear_kernel(float* a, __nv_bfloat16* y, long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> u, z;
+    row_load_f32(u, a + row * D, D, lane);
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) z.v[j][i] = 0.f;
+    row_store_f32(z, a + row * D, D, lane, false);
+    row_layernorm(u, D, lane);
+    row_store_bf16(u, y + row * D, D, lane);
+  }
+}
+
+// Decode step, layer tail: mlp = sum of the decoder GEMM's `parts` split-K partial tiles (fp32, part p of row r
+// at part[(p * rows + r) * D]), then out = LN(cur + LN(mlp)) (one launch instead of a sum, a cast and the tail).
+template <int NC>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+block_out_parts_kernel(const __nv_bfloat16* cur, const float* part, int parts, __nv_bfloat16* out,
+                       long long rows, int D) {
+  const int lane = threadIdx.x & 31;
+  long long row = static_cast<long long>(blockIdx.x) * ROW_WARPS + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * ROW_WARPS;
+  for (; row < rows; row += stride) {
+    Row<NC> u, c;
+    row_load_f32(u, part + row * D, D, lane);
+    for (int p = 1; p < parts; ++p) {
+      row_load_f32(c, part + (static_cast<long long>(p) * rows + row) * D, D, lane);
+#pragma unroll
+      for (int j = 0; j < NC; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) u.v[j][i] += c.v[j][i];
+    }
+    row_layernorm(u, D, lane);
+    row_load_bf16(c, cur + row * D, D, lane);
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) u.v[j][i] += c.v[j][i];
+    row_layernorm(u, D, lane);
+    row_store_bf16(u, out + row * D, D, lane);
+  }
+}
+
 template <int NC>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 block_out_bwd_kernel(const __nv_bfloat16* cur, const __nv_bfloat16* mlp, const float* dout,
@@ -459,6 +511,19 @@ extern "C" int bdh_block_out_fwd(const void* cur, const void* mlp, void* out, lo
   if (!row_ok(D)) return BDH_ERR_ARGUMENT;
   if (rows == 0) return BDH_OK;
   ROW_DISPATCH(D, block_out_fwd_kernel, (const bf16*)cur, (const bf16*)mlp, (bf16*)out, rows, D);
+  return launch_rc();
+}
+extern "C" int bdh_layernorm_f32_clear(float* a, void* y, long long rows, int D, cudaStream_t s) {
+  if (!row_ok(D)) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, layernorm_f32_clear_kernel, a, (bf16*)y, rows, D);
+  return launch_rc();
+}
+extern "C" int bdh_block_out_parts(const void* cur, const float* part, int parts, void* out, long long rows, int D,
+                                   cudaStream_t s) {
+  if (!row_ok(D) || parts < 1) return BDH_ERR_ARGUMENT;
+  if (rows == 0) return BDH_OK;
+  ROW_DISPATCH(D, block_out_parts_kernel, (const bf16*)cur, part, parts, (bf16*)out, rows, D);
   return launch_rc();
 }
 extern "C" int bdh_block_out_bwd(const void* cur, const void* mlp, const float* dout, float* dcur,

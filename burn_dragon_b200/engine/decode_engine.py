@@ -67,10 +67,10 @@ class DecodeEngine:
             cur=torch.zeros(B, d.D, **bf), nxt=torch.zeros(B, d.D, **bf),
             x=torch.zeros(B, d.HN, **bf),
             q=torch.zeros(B, d.HNp, **bf) if d.rot != "alibi" else None,
-            a=torch.zeros(d.H * B, d.D, **f32), a16=torch.zeros(d.H * B, d.D, **bf),
+            a=torch.zeros(d.H * B, d.D, **f32),
             lna=torch.zeros(d.H * B, d.D, **bf),
             xy=torch.zeros(B, d.HN, **bf),
-            part=torch.zeros(S * B, d.D, **f32), mlp=torch.zeros(B, d.D, **bf),
+            part=torch.zeros(S * B, d.D, **f32),
             pos=torch.zeros(1, device=dev, dtype=torch.int32),
             step=torch.zeros(1, device=dev, dtype=torch.int32),
             table=(torch.zeros(1, d.N, **bf) if d.rot == "rope" else None),
@@ -117,19 +117,16 @@ class DecodeEngine:
             else:
                 G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, out0=buf["x"], theta=d.theta)
                 q = buf["x"]
-            buf["a"].zero_()
+            # `a` is zero here: cleared at allocation and again by every pass that reads it
             ops.decode_state_update(q, cur, rho[l], buf["a"], d.slopes)
-            buf["a16"].copy_(buf["a"])
-            ops.layernorm_fwd(buf["a16"], buf["lna"])
+            ops.layernorm_f32_clear(buf["a"], buf["lna"])
             G.gemm(buf["lna"], W["encoder_v"], M=B, N=d.N, K=d.D, nz=(d.H, 1), a_off=(B, 0, 0, 0),
                    b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=buf["x"],
                    out1=buf["xy"], theta=d.theta)
             ks = d.HN // S
             G.gemm(buf["xy"], W["decoder"], M=B, N=d.D, K=ks, b_mn=True, nz=(S, 1), a_off=(0, 0, ks, 0),
                    b_off=(0, 0, ks, 0), c_off=(B, 0, 0, 0), flags=G.F_OUT_F32, out0=buf["part"])
-            torch.sum(buf["part"].view(S, B, d.D), dim=0, out=buf["a"][:B])      # reuse `a` rows as fp32 scratch
-            buf["mlp"].copy_(buf["a"][:B])
-            ops.block_out_fwd(cur, buf["mlp"], nxt)
+            ops.block_out_parts(cur, buf["part"], nxt)         # sum of the split-K partial tiles + layer tail
             cur, nxt = nxt, cur
         if d.V % 8 == 0:
             G.gemm(cur, W["lm_head"], M=B, N=d.V, K=d.D, b_mn=True, flags=G.F_OUT_F32, out0=buf["logits"])
@@ -187,6 +184,7 @@ class DecodeEngine:
                 buf["logits"].copy_(last.float())
             buf["pos"].fill_(state.position)
             buf["step"].fill_(int(step0))
+            buf["a"].zero_()           # (every step leaves it cleared; this covers a step that was interrupted)
 
         load_state()
         graph_ok = self.use_graph and (d.rot != "pope" or self.pope_graph) and dev.type == "cuda"

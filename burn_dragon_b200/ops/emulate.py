@@ -65,6 +65,16 @@ class TorchOps:
         out.copy_(R.layer_norm(cur.float() + R.layer_norm(mlp.float())))
 
     @staticmethod
+    def layernorm_f32_clear(a, y):
+        y.copy_(R.layer_norm(a.float()))
+        a.zero_()
+
+    @staticmethod
+    def block_out_parts(cur, part, out):
+        mlp = part.float().view(-1, *cur.shape).sum(0)
+        out.copy_(R.layer_norm(cur.float() + R.layer_norm(mlp)))
+
+    @staticmethod
     def block_out_bwd(cur, mlp, dout, dcur, dmlp):
         u = cur.float() + R.layer_norm(mlp.float())
         du = _ln_bwd(u, dout)

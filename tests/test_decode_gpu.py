@@ -208,3 +208,24 @@ def test_pope_step_with_device_position_is_captured_and_matches_recurrence():
     assert _rel(eng.last_logits, ref_logits) < 0.08
     for a, b in zip(eng.last_state.layers, st.layers):
         assert _rel(a.rho, b.rho) < 0.05
+
+
+@pytest.mark.parametrize("D", [64, 256, 512])
+def test_decode_row_kernels_match_their_definitions(D):
+    """`layernorm_f32_clear` (LayerNorm of fp32 rows that are cleared in the same pass) and `block_out_parts`
+    (sum of split-K partial tiles + layer tail) against the torch statement."""
+    from burn_dragon_b200.ops import reference as R
+    torch.manual_seed(0)
+    rows, parts = 37, 4
+    a = torch.randn(rows, D, device="cuda") * 3 + 0.5
+    want = R.layer_norm(a)
+    y = torch.empty(rows, D, device="cuda", dtype=torch.bfloat16)
+    native.ops.layernorm_f32_clear(a, y)
+    assert float(a.abs().max()) == 0.0
+    assert (y.float() - want).abs().max().item() < 3e-2
+    cur = torch.randn(rows, D, device="cuda").bfloat16()
+    part = torch.randn(parts * rows, D, device="cuda")
+    out = torch.empty_like(cur)
+    native.ops.block_out_parts(cur, part, out)
+    want = R.layer_norm(cur.float() + R.layer_norm(part.view(parts, rows, D).sum(0)))
+    assert (out.float() - want).abs().max().item() < 3e-2
