@@ -178,6 +178,19 @@ int bdh_ssd_chunk_scan(const float* xw, const float* loga, const float* Bm, cons
 // Bm/Cm [B,128], h [B,H,128,64] in place, y [B,H,64].
 int bdh_ssd_decode_step(const float* xw, const float* loga, const float* Bm, const float* Cm, float* h, float* y,
                         int B, int H, cudaStream_t s);
+// Mamba-2 block, elementwise parts (mamba_ops.cu), fp32. Causal depthwise conv1d + bias + SiLU:
+// seq [B, T + k - 1, C] (k - 1 leading rows = tail of the previous segment), w [C, k], bias [C] or null, out [B, T, C].
+int bdh_conv1d_silu_fwd(const float* seq, const float* w, const float* bias, float* out, int B, int T, int C, int k,
+                        cudaStream_t s);
+// Backward: dpre [B, T, C] scratch, dseq [B, T + k - 1, C] written, dw [C, k] and db [C] (or null) added to.
+int bdh_conv1d_silu_bwd(const float* seq, const float* w, const float* bias, const float* dout, float* dpre,
+                        float* dseq, float* dw, float* db, int B, int T, int C, int k, cudaStream_t s);
+// out = rmsnorm(v * silu(z)) * w over rows of D columns; rstd [rows] is kept for the backward pass.
+int bdh_gated_rmsnorm_fwd(const float* v, const float* z, const float* w, float* out, float* rstd, long long rows,
+                          int D, float eps, cudaStream_t s);
+// dv, dz written, dw [D] added to.
+int bdh_gated_rmsnorm_bwd(const float* v, const float* z, const float* w, const float* rstd, const float* dout,
+                          float* dv, float* dz, float* dw, long long rows, int D, cudaStream_t s);
 // The first half of the scan alone: afterwards states[b,c,h] is the state entering chunk c, h the final state.
 int bdh_ssd_chunk_states(const float* xw, const float* loga, const float* Bm, float* h, float* states, float* decay,
                          int B, int T, int H, cudaStream_t s);

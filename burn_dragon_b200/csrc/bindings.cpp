@@ -373,6 +373,58 @@ void bump_counter(Tensor& counter, int64_t by) {
   check_rc(bdh_bump_counter(counter.data_ptr<int>(), by, cur_stream()), "bump_counter");
 }
 
+static void check_f32(std::initializer_list<const Tensor*> ts) {
+  for (const Tensor* t : ts)
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat, "expected contiguous fp32 CUDA tensors");
+}
+
+void conv1d_silu_fwd(const Tensor& seq, const Tensor& w, const c10::optional<Tensor>& bias, Tensor& out) {
+  c10::cuda::CUDAGuard guard(seq.device());
+  check_f32({&seq, &w, &out});
+  if (bias.has_value()) check_f32({&*bias});
+  const int64_t B = out.size(0), T = out.size(1), C = out.size(2), k = w.size(1);
+  TORCH_CHECK(seq.dim() == 3 && out.dim() == 3 && w.dim() == 2 && w.size(0) == C && seq.size(0) == B &&
+              seq.size(1) == T + k - 1 && seq.size(2) == C && (!bias.has_value() || bias->numel() == C), "conv1d_silu_fwd: shapes");
+  check_rc(bdh_conv1d_silu_fwd(seq.data_ptr<float>(), w.data_ptr<float>(), bias.has_value() ? bias->data_ptr<float>() : nullptr,
+                               out.data_ptr<float>(), B, T, C, k, cur_stream()), "conv1d_silu_fwd");
+}
+
+void conv1d_silu_bwd(const Tensor& seq, const Tensor& w, const c10::optional<Tensor>& bias, const Tensor& dout, Tensor& dpre,
+                     Tensor& dseq, Tensor& dw, c10::optional<Tensor> db) {
+  c10::cuda::CUDAGuard guard(seq.device());
+  check_f32({&seq, &w, &dout, &dpre, &dseq, &dw});
+  if (bias.has_value()) check_f32({&*bias});
+  if (db.has_value()) check_f32({&*db});
+  const int64_t B = dout.size(0), T = dout.size(1), C = dout.size(2), k = w.size(1);
+  TORCH_CHECK(seq.dim() == 3 && dout.dim() == 3 && w.dim() == 2 && w.size(0) == C && seq.size(0) == B &&
+              seq.size(1) == T + k - 1 && seq.size(2) == C && dpre.numel() == dout.numel() && dseq.numel() == seq.numel() &&
+              dw.numel() == w.numel() && (!db.has_value() || db->numel() == C), "conv1d_silu_bwd: shapes");
+  check_rc(bdh_conv1d_silu_bwd(seq.data_ptr<float>(), w.data_ptr<float>(), bias.has_value() ? bias->data_ptr<float>() : nullptr,
+                               dout.data_ptr<float>(), dpre.data_ptr<float>(), dseq.data_ptr<float>(), dw.data_ptr<float>(),
+                               db.has_value() ? db->data_ptr<float>() : nullptr, B, T, C, k, cur_stream()), "conv1d_silu_bwd");
+}
+
+void gated_rmsnorm_fwd(const Tensor& v, const Tensor& z, const Tensor& w, Tensor& out, Tensor& rstd, double eps) {
+  c10::cuda::CUDAGuard guard(v.device());
+  check_f32({&v, &z, &w, &out, &rstd});
+  const int64_t D = v.size(-1), rows = v.numel() / D;
+  TORCH_CHECK(z.numel() == v.numel() && out.numel() == v.numel() && w.numel() == D && rstd.numel() == rows, "gated_rmsnorm_fwd: shapes");
+  check_rc(bdh_gated_rmsnorm_fwd(v.data_ptr<float>(), z.data_ptr<float>(), w.data_ptr<float>(), out.data_ptr<float>(),
+                                 rstd.data_ptr<float>(), rows, D, static_cast<float>(eps), cur_stream()), "gated_rmsnorm_fwd");
+}
+
+void gated_rmsnorm_bwd(const Tensor& v, const Tensor& z, const Tensor& w, const Tensor& rstd, const Tensor& dout, Tensor& dv,
+                       Tensor& dz, Tensor& dw) {
+  c10::cuda::CUDAGuard guard(v.device());
+  check_f32({&v, &z, &w, &rstd, &dout, &dv, &dz, &dw});
+  const int64_t D = v.size(-1), rows = v.numel() / D;
+  TORCH_CHECK(z.numel() == v.numel() && dout.numel() == v.numel() && dv.numel() == v.numel() && dz.numel() == v.numel() &&
+              w.numel() == D && dw.numel() == D && rstd.numel() == rows, "gated_rmsnorm_bwd: shapes");
+  check_rc(bdh_gated_rmsnorm_bwd(v.data_ptr<float>(), z.data_ptr<float>(), w.data_ptr<float>(), rstd.data_ptr<float>(),
+                                 dout.data_ptr<float>(), dv.data_ptr<float>(), dz.data_ptr<float>(), dw.data_ptr<float>(), rows, D,
+                                 cur_stream()), "gated_rmsnorm_bwd");
+}
+
 void ssd_decode_step(const Tensor& xw, const Tensor& loga, const Tensor& Bm, const Tensor& Cm, Tensor& h, Tensor& y) {
   c10::cuda::CUDAGuard guard(xw.device());
   for (const Tensor* t : std::initializer_list<const Tensor*>{&xw, &loga, &Bm, &Cm, &h, &y})
@@ -488,6 +540,12 @@ TORCH_LIBRARY(bdh, m) {
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_decode_step(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) y) -> ()");
+  m.def("conv1d_silu_fwd(Tensor seq, Tensor w, Tensor? bias, Tensor(a!) out) -> ()");
+  m.def("conv1d_silu_bwd(Tensor seq, Tensor w, Tensor? bias, Tensor dout, Tensor(a!) dpre, Tensor(b!) dseq, Tensor(c!) dw, "
+        "Tensor(d!)? db) -> ()");
+  m.def("gated_rmsnorm_fwd(Tensor v, Tensor z, Tensor w, Tensor(a!) out, Tensor(b!) rstd, float eps) -> ()");
+  m.def("gated_rmsnorm_bwd(Tensor v, Tensor z, Tensor w, Tensor rstd, Tensor dout, Tensor(a!) dv, Tensor(b!) dz, "
+        "Tensor(c!) dw) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
         "Tensor(d!) y, bool tensor_cores) -> ()");
   m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
@@ -525,6 +583,10 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("rank_barrier", &rank_barrier);
   m.impl("graph_spmm_relu", &graph_spmm_relu);
   m.impl("ssd_decode_step", &ssd_decode_step);
+  m.impl("conv1d_silu_fwd", &conv1d_silu_fwd);
+  m.impl("conv1d_silu_bwd", &conv1d_silu_bwd);
+  m.impl("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
+  m.impl("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
   m.impl("ssd_chunk_scan", &ssd_chunk_scan);
   m.impl("decode_state_update", &decode_state_update);
   m.impl("sample_tokens", &sample_tokens);

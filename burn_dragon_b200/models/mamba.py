@@ -30,6 +30,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import mamba_ops as MO
 from ..ops import reference as R
 from ..ops import ssd as SSD
 
@@ -118,8 +119,7 @@ class Mamba2Block(nn.Module):
         seq = torch.cat((tail.to(xbc.dtype), xbc), dim=1)                      # [B, T + k - 1, C]
         if st is not None:
             st.conv = seq[:, -(c.d_conv - 1):].detach()
-        xbc = F.conv1d(seq.transpose(1, 2), self.conv_w.unsqueeze(1), self.conv_b, groups=self.d_xbc).transpose(1, 2)
-        xbc = F.silu(xbc)
+        xbc = MO.conv1d_silu(seq, self.conv_w, self.conv_b)                    # one kernel per direction on a GPU
         x, Bm, Cm = torch.split(xbc, [Di, N, N], dim=-1)
         dt = F.softplus(dt.float() + self.dt_bias)                             # [B,T,H]
         loga = dt * (-torch.exp(self.A_log.float()))
@@ -129,7 +129,7 @@ class Mamba2Block(nn.Module):
         if st is not None:
             st.h = hT.detach()
         y = y + xh * self.D.view(1, 1, H, 1)
-        y = rmsnorm(y.reshape(Bsz, T, Di).to(u.dtype) * F.silu(z), self.norm_w)
+        y = MO.gated_rmsnorm(y.reshape(Bsz, T, Di).to(u.dtype), z, self.norm_w)
         return self.out_proj(y)
 
 
