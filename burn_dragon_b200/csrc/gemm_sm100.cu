@@ -200,6 +200,7 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   BDH_CASE(256, 0, 0, EPI_GATE_BWD)
   BDH_CASE(256, 0, 1, EPI_STORE)
   BDH_CASE(256, 0, 1, EPI_DQ_BWD)
+  BDH_CASE(256, 0, 0, EPI_DQ_BWD)      // (state terms of the chunked attention: both operands K-major)
   BDH_CASE(256, 1, 1, EPI_STORE)
   BDH_CASE(256, 1, 0, EPI_STORE)
   BDH_CASE(128, 0, 0, EPI_STORE)
