@@ -199,6 +199,12 @@ def main() -> int:
     ap.add_argument("--recompute", default=None,
                     help="large / tp presets: layers whose activations are recomputed in the backward pass "
                          "(an integer, or 'auto' = as few as fit; default: the preset's setting)")
+    ap.add_argument("--drop-rotated", type=int, default=None,
+                    help="PoPE presets: layers that keep x but not the rotated query q and write q again in their "
+                         "backward pass (default: chosen together with --recompute auto)")
+    ap.add_argument("--attention-chunk", type=int, default=None,
+                    help="tokens per attention segment (states handed on between segments); default: automatic "
+                         "(the whole sequence below 4096 tokens, else 1024); --seq length = one quadratic form")
     ap.add_argument("--streams", type=int, default=64, help="decode preset: concurrent streams per GPU")
     ap.add_argument("--prompt", type=int, default=1024, help="decode preset: prompt length")
     ap.add_argument("--new-tokens", type=int, default=2048, help="decode preset: tokens decoded per stream")
@@ -242,6 +248,8 @@ def main() -> int:
     torch.manual_seed(1337)
     model = BDH(BDHConfig(**mcfg)).to(dev)
     model.recompute = recompute
+    model.attention_chunk = args.attention_chunk
+    model.drop_rotated = args.drop_rotated
     wrapper = None
     if world > 1 and strategy == "fsdp":
         from burn_dragon_b200.parallel.fsdp import FSDP
@@ -338,7 +346,9 @@ def main() -> int:
             "dtype": "bf16", "data": "synthetic uniform random bytes, random-init weights",
             "config": {"model": model_name, "global_batch": B * data_world, "seq_len": T,
                        "parallelism": (f"{'dp' if strategy == 'ddp' else strategy}{world}" if world > 1 else "single"),
+                       "attention_chunk": args.attention_chunk,
                        "recompute": recompute, "recomputed_layers": getattr(getattr(wrapper, "shard", model), "_recomputed_layers", None),
+                       "dropped_q_layers": getattr(getattr(wrapper, "shard", model), "_dropped_q_layers", None),
                        "optimizer": "AdamW lr 1e-3 wd 0.1 (fp32 master, bf16 compute)",
                        "l2": "per-step working set (activations > 20 GB) is far larger than the 126 MB L2",
                        "collectives": coll_mode, "collectives_fallback": fallback,

@@ -122,6 +122,9 @@ int bdh_block_out_parts(const void* cur_bf16, const float* part_f32, int parts, 
 int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* dout_f32,
                       float* dcur_f32, void* dmlp_bf16, long long rows, int D, cudaStream_t s);
 
+// PoPE query rebuilt from the stored x: q_bf16 [M, H*2N] (per head [real N | imag N]) = softplus(x) * (cos, sin).
+int bdh_pope_rotate(const void* x_bf16, const float* freqs, void* q_bf16, long long M, int H, int N, int T, int pos0,
+                    cudaStream_t s);
 // PoPE backward: dx = (dq_re cos + dq_im sin) sigmoid(x) + gate gradient where x > 0, else 0.
 // dq bf16 [M, H*2N] (per head [real N | imag N]); x, dxg, dx bf16 [M, H*N]; freqs [N]; N % 8 == 0.
 int bdh_pope_bwd(const void* dq_bf16, const void* x_bf16, const void* dxg_bf16, const float* freqs, void* dx_bf16,

@@ -486,6 +486,17 @@ void pope_bwd(const Tensor& dq, const Tensor& x, const Tensor& dxg, const Tensor
                         pos0, cur_stream()), "pope_bwd");
 }
 
+void pope_rotate(const Tensor& x, const Tensor& freqs, Tensor& q, int64_t H, int64_t T, int64_t pos0) {
+  c10::cuda::CUDAGuard guard(x.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&x, &q})
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kBFloat16 && t->dim() == 2);
+  const int64_t M = x.size(0), HN = x.size(1);
+  TORCH_CHECK(HN % H == 0 && q.size(0) == M && q.size(1) == 2 * HN);
+  TORCH_CHECK(freqs.scalar_type() == at::kFloat && freqs.is_contiguous() && freqs.numel() == HN / H);
+  check_rc(bdh_pope_rotate(x.data_ptr(), freqs.data_ptr<float>(), q.data_ptr(), M, H, HN / H, T, pos0, cur_stream()),
+           "pope_rotate");
+}
+
 void wait_timeout_probe(const Tensor& flag, int64_t value, int64_t limit_ns) {
   c10::cuda::CUDAGuard guard(flag.device());
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt);
@@ -537,6 +548,7 @@ TORCH_LIBRARY(bdh, m) {
         "int[] seg_dst, float scale, int epoch, int ctas) -> ()");
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
   m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
+  m.def("pope_rotate(Tensor x, Tensor freqs, Tensor(a!) q, int H, int T, int pos0) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_decode_step(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) y) -> ()");
@@ -580,6 +592,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("shard_bcast", &shard_bcast);
   m.impl("wait_timeout_probe", &wait_timeout_probe);
   m.impl("pope_bwd", &pope_bwd);
+  m.impl("pope_rotate", &pope_rotate);
   m.impl("rank_barrier", &rank_barrier);
   m.impl("graph_spmm_relu", &graph_spmm_relu);
   m.impl("ssd_decode_step", &ssd_decode_step);

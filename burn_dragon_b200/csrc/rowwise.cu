@@ -621,6 +621,61 @@ extern "C" int bdh_pope_bwd(const void* dq, const void* x, const void* dxg, cons
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 
+// ---- PoPE query from the stored x -------------------------------------------------------------------
+// q = softplus(x) * (cos(ph), sin(ph)) written again from the bf16 x that the encoder stored, so that the
+// backward pass need not keep q (twice the width of x) for every layer: x bf16 [M, H*N] -> q bf16 [M, H*2N]
+// with the per-head layout [real N | imag N]. One thread handles 8 consecutive neurons.
+namespace bdh {
+__global__ void pope_rotate_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freqs,
+                                   __nv_bfloat16* __restrict__ q, long long M, int H, int N, int T, int pos0) {
+  const long long per_row = static_cast<long long>(H) * N / 8;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = M * per_row, stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (; i < total; i += stride) {
+    const long long m = i / per_row;
+    const int c = static_cast<int>(i % per_row) * 8;
+    const int h = c / N, n = c % N;
+    const float pos = static_cast<float>(pos0 + static_cast<int>(m % T));
+    const long long qoff = m * 2 * H * N + static_cast<long long>(h) * 2 * N + n;
+    const uint4 ux = *reinterpret_cast<const uint4*>(x + m * H * N + c);
+    const uint32_t* px = &ux.x;
+    uint4 re, im;
+    uint32_t* pr = &re.x;
+    uint32_t* pi = &im.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 xv = unpack_bf16x2(px[k]);
+      const float xs[2] = {xv.x, xv.y};
+      float r[2], g[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float raw = pos * __ldg(freqs + n + 2 * k + j);
+        const float ph = (raw - floorf(raw)) * 6.283185307179586f;
+        float s, co;
+        __sincosf(ph, &s, &co);
+        const float mag = xs[j] + __logf(1.f + __expf(-xs[j]));      // softplus of a non-negative value
+        r[j] = mag * co;
+        g[j] = mag * s;
+      }
+      pr[k] = pack_bf16x2(r[0], r[1]);
+      pi[k] = pack_bf16x2(g[0], g[1]);
+    }
+    *reinterpret_cast<uint4*>(q + qoff) = re;
+    *reinterpret_cast<uint4*>(q + qoff + N) = im;
+  }
+}
+}  // namespace bdh
+
+extern "C" int bdh_pope_rotate(const void* x, const float* freqs, void* q, long long M, int H, int N, int T, int pos0,
+                               cudaStream_t s) {
+  if (M <= 0 || H <= 0 || N <= 0 || (N % 8) || T <= 0) return BDH_ERR_ARGUMENT;
+  const long long total = M * H * N / 8;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  bdh::pope_rotate_kernel<<<static_cast<int>(blocks), 256, 0, s>>>((const bf16*)x, freqs, (bf16*)q, M, H, N, T, pos0);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
 // ---- L1 row normalisation of strictly causal scores (the `forward_fast` attention) -------------
 // S is bf16 [rows, T] with rows = (batch, head, t); only columns s < t of row t carry scores
 // (reference: src/model/attention.rs:142-175: tril(-1), then S / (sum_j |S_ij| + 1e-6)).

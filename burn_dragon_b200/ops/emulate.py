@@ -92,6 +92,17 @@ class TorchOps:
             dlogits.copy_(g * grad_scale)
 
     @staticmethod
+    def pope_rotate(x, freqs, q, H, T, pos0):
+        M, HN = x.shape
+        N = HN // H
+        pos = pos0 + (torch.arange(M, device=x.device) % T)
+        ph = G.rot_phases(pos, freqs)                                  # [M, N]
+        mag = torch.nn.functional.softplus(x.float()).view(M, H, N)
+        qv = q.view(M, H, 2, N)
+        qv[:, :, 0] = (mag * ph.cos()[:, None]).to(q.dtype)
+        qv[:, :, 1] = (mag * ph.sin()[:, None]).to(q.dtype)
+
+    @staticmethod
     def pope_bwd(dq, x, dxg, freqs, dx, H, T, pos0):
         M, HN = x.shape
         N = HN // H

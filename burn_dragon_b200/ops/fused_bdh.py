@@ -399,6 +399,10 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
     M, D, H, N, Np, T, B = d.M, d.D, d.H, d.N, d.Np, d.T, d.B
     C, Bs = d.C, d.Bs
     cur, x, q, S, a, lna, xy, mlp = (sv[k] for k in ("cur", "x", "q", "S", "a", "lna", "xy", "mlp"))
+    if q is None:
+        # this layer did not keep its PoPE query: write it again from x
+        q = _bf16(M, d.HNp, dev)
+        ops.pope_rotate(x, d.freqs_full, q, H, T, pos0)
     dcur = torch.empty(M, D, device=dev, dtype=torch.float32)
     dmlp = _bf16(M, D, dev)
     ops.block_out_bwd(cur, mlp, dout, dcur, dmlp)
@@ -581,16 +585,31 @@ def _head_logits(d, W, cur):
 def layer_activation_bytes(d: _Dims) -> int:
     """Bytes one layer keeps for its backward pass when it is not recomputed."""
     wide = d.M * (2 * d.HN + (d.HNp if d.rot != "alibi" else 0)) * 2          # x, x*y, rotated copy
-    scores = d.B * d.H * d.T * d.T * 2
+    scores = d.Bs * d.H * d.C * d.C * 2
     narrow = (2 * d.H * d.M * d.D + 3 * d.M * d.D) * 2                        # a, LN(a); cur, mlp, out
-    return wide + scores + narrow
+    states = (d.Bs * d.H * d.Np * d.D * 2) if d.handoff else 0                # bf16 starting state of every segment
+    return wide + scores + narrow + states
+
+
+def backward_working_bytes(d: _Dims) -> int:
+    """Peak of the temporaries one layer's backward pass holds at once: dq (PoPE: over the doubled latent) or dy,
+    the gate gradient and its second copy, dx, and the score-sized Gs - plus the fp32 state gradients when states
+    cross segment borders."""
+    wide = d.M * (max(d.HN, d.HNp) + 3 * d.HN) * 2
+    scores = 2 * d.Bs * d.H * d.C * d.C * 2
+    # fp32 gradient of the starting states and of the segments' own states, the bf16 copy, the [rin | d seg] operand
+    states = (d.Bs * d.H * d.Np * d.D * (4 + 4 + 2 + 4)) if d.handoff else 0
+    return wide + scores + states
 
 
 def recompute_count(model, d: _Dims) -> int:
     """How many of the L layers re-run their forward in the backward pass. `model.recompute`:
     False / True (none / all), an int (that many, counted from the first layer), or "auto": as few as
-    fit in 80 % of the free device memory, after setting aside the backward pass's own working set
-    (about five [tokens, H*N'] bf16 tensors and one recomputed layer)."""
+    fit in 75 % of the free device memory, after setting aside the backward pass's own working set
+    (`backward_working_bytes`; the layers that are kept are the last ones, which the backward pass frees
+    before it reaches the recomputed ones, so a recomputed layer's activations never add to the peak).
+    Measured on the large PoPE configuration (8 sequences of 2048 tokens per GPU): 16.8 GB per kept layer on
+    top of 21 GB, against 17.7 and 22.5 GB from these formulas."""
     r = getattr(model, "recompute", False)
     if r is True:
         return d.L
@@ -604,14 +623,48 @@ def recompute_count(model, d: _Dims) -> int:
         free, _ = torch.cuda.mem_get_info()
         free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()   # cached blocks are reusable
         per = layer_activation_bytes(d)
-        working = 5 * d.M * max(d.HN, d.HNp) * 2 + per
-        keep = int((0.8 * free - working) // per)
+        keep = int((0.75 * free - backward_working_bytes(d)) // per)
         return max(0, min(d.L, d.L - keep))
     raise ValueError(f"recompute must be a bool, an int or 'auto', not {r!r}")
 
 
-def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int):
-    """`recompute` = number of leading layers that keep only their input (and dropout seed)."""
+# a layer's forward pass costs about this many rebuilds of its PoPE query (17.7 ms against 3.3 ms on the large config)
+_RECOMPUTE_COST = 5.4
+
+
+def memory_plan(model, d: _Dims):
+    """-> (recomputed layers, layers that drop their rotated query). PoPE stores q = softplus(x) (cos, sin) at twice
+    the width of x; a layer that drops it keeps x only and writes q again in its backward pass (one elementwise
+    kernel, `pope_rotate`), which is much cheaper than recomputing the layer. With `recompute = "auto"` the plan is
+    the cheapest mix of recomputed layers (the first ones), q-dropping layers (the next ones) and fully kept layers
+    that fits the memory budget of `recompute_count`; `model.drop_rotated` (an int) overrides the second number."""
+    r = recompute_count(model, d)
+    k = getattr(model, "drop_rotated", None)
+    can_drop = d.rot == "pope" and d.comm is None
+    if k is not None:
+        return r, (max(0, min(d.L - r, int(k))) if can_drop else 0)
+    if getattr(model, "recompute", False) != "auto" or not can_drop or r == 0 or not torch.cuda.is_available():
+        return r, 0
+    free, _ = torch.cuda.mem_get_info()
+    free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
+    budget = 0.75 * free - backward_working_bytes(d)
+    per = layer_activation_bytes(d)
+    qbytes = d.M * d.HNp * 2
+    best = (r * _RECOMPUTE_COST, r, 0)
+    for rr in range(0, r + 1):
+        for kk in range(0, d.L - rr + 1):
+            mem = kk * (per - qbytes) + (d.L - rr - kk) * per + (qbytes if kk else 0)
+            if mem <= budget:
+                cost = rr * _RECOMPUTE_COST + kk
+                if cost < best[0]:
+                    best = (cost, rr, kk)
+                break                     # more q-dropping layers only cost more
+    return best[1], best[2]
+
+
+def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int, drop_q: int = 0):
+    """`recompute` = number of leading layers that keep only their input (and dropout seed); the `drop_q`
+    layers after them keep everything but the rotated query."""
     cur = _embed(d, W, tokens)
     # (training of a segment of longer sequences - context parallelism - starts at `model._train_pos0`)
     pos0 = state.position if state is not None else int(getattr(model, "_train_pos0", 0))
@@ -631,7 +684,12 @@ def _stack_forward(model, d: _Dims, W, tokens, state, save: bool, recompute: int
                 rho_out = full
             state.layers[l].rho = rho_out
         if save:
-            saved.append(dict(cur=cur, drop_seed=seed_l) if l < recompute else sv)
+            if l < recompute:
+                saved.append(dict(cur=cur, drop_seed=seed_l))
+            else:
+                if l < recompute + drop_q:
+                    sv["q"] = None
+                saved.append(sv)
         if l == d.L - 1 and getattr(model, "measure_sparsity", False):
             # fraction of active neurons in the last layer, left on the device for the metrics logger
             model.last_sparsity = dict(x=(sv["x"] != 0).float().mean(), xy=(sv["xy"] != 0).float().mean())
@@ -656,9 +714,9 @@ class _FusedLoss(torch.autograd.Function):
         B, T = tokens.shape
         d = _Dims(model, B, T, fast)
         W = _compact(d, _weights(model))
-        recompute = recompute_count(model, d)
-        model._recomputed_layers = recompute
-        cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute)
+        recompute, drop_q = memory_plan(model, d)
+        model._recomputed_layers, model._dropped_q_layers = recompute, drop_q
+        cur, saved = _stack_forward(model, d, W, tokens, None, save=True, recompute=recompute, drop_q=drop_q)
         with prof.phase("head.loss"):
             logits = _head_logits(d, W, cur)
             row_loss = torch.empty(d.M, device=tokens.device, dtype=torch.float32)

@@ -488,3 +488,23 @@ def test_chunked_prefill_equals_the_recurrence(rot):
     assert st.position == st_t.position
     for a, b in zip(st.layers, st_t.layers):
         assert _rel(a.rho, b.rho) < 0.05
+
+
+def test_pope_layers_that_drop_their_rotated_query_give_the_same_gradients():
+    """A PoPE layer may keep x only and write q = softplus(x) (cos, sin) again in its backward pass
+    (`model.drop_rotated`): same loss, gradients equal up to the bf16 rounding of x."""
+    m = _model("pope")
+    tok, tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    with emulate.kernel_path():
+        l0 = m(tok, tgt)
+        l0.backward()
+        g0 = {n: p.grad.clone() for n, p in m.named_parameters()}
+        m.zero_grad()
+        m.drop_rotated = 1
+        m.recompute = 1
+        l1 = m(tok, tgt)
+        l1.backward()
+    assert (m._recomputed_layers, m._dropped_q_layers) == (1, 1)
+    assert l0.item() == l1.item()
+    for n, p in m.named_parameters():
+        assert _rel(p.grad, g0[n]) < 5e-3, (n, _rel(p.grad, g0[n]))

@@ -313,3 +313,28 @@ def test_long_sequence_training_step_in_chunks():
     losses = [float(tr.train_step(tok[:, :-1], tok[:, 1:])) for _ in range(4)]
     assert native.status_code() == 0
     assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_pope_query_rebuilt_in_the_backward_pass():
+    """`pope_rotate` writes the same q as the encoder epilogue did (up to the bf16 rounding of x), and a model
+    whose layers drop q trains to the same gradients."""
+    from burn_dragon_b200.ops import gemm as G
+    m = _model("pope")
+    B, T = 2, 128
+    tok = torch.randint(0, 256, (B, T), device="cuda")
+    tgt = torch.randint(0, 256, (B, T), device="cuda")
+    d = fused_bdh._Dims(m, B, T)
+    W = fused_bdh._weights(m)
+    cur = fused_bdh._embed(d, W, tok)
+    _, sv, _ = fused_bdh._layer_forward(d, W, cur, 5, None, False)
+    q2 = torch.empty_like(sv["q"])
+    native.ops.pope_rotate(sv["x"], d.freqs_full, q2, d.H, T, 5)
+    assert _rel(q2, sv["q"]) < 1e-2
+    m(tok, tgt).backward()
+    g0 = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    m.drop_rotated = 2
+    m(tok, tgt).backward()
+    assert m._dropped_q_layers == 2
+    for n, p in m.named_parameters():
+        assert _rel(p.grad, g0[n]) < 2e-2, (n, _rel(p.grad, g0[n]))
