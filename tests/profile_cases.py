@@ -82,6 +82,17 @@ def build(case: str):
                             att_fl + gemm_fl, 3 * big),
         }
         return dual[case]
+    if case == "decode_state":
+        # the decode state update for 64 streams of the base model: fp32 state [64, 4, 8192, 256] = 2.1 GB, half of
+        # the query entries zero (their state rows are skipped); bytes = the rows that are read and written
+        Bd = 64
+        qd = _rnd(Bd, HN, 0.1).relu()
+        cd = _rnd(Bd, D)
+        rho = torch.zeros(Bd, H, N, D, device="cuda")
+        ad = torch.zeros(H * Bd, D, device="cuda")
+        live = float((qd != 0).float().mean())
+        return (lambda: native.ops.decode_state_update(qd, cd, rho, ad, None)), 4.0 * Bd * HN * D * live, \
+            2.0 * 4.0 * Bd * HN * D * live
     if case in ("rownorm_fwd", "fast_attention"):
         # forward_fast attention at T = 2048 (B 8, H 4, N 2048, D 256): scores are 268 MB in bf16
         from burn_dragon_b200.ops import rownorm_attention as RA
