@@ -624,7 +624,21 @@ def recompute_count(model, d: _Dims) -> int:
         free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()   # cached blocks are reusable
         per = layer_activation_bytes(d)
         keep = int((0.75 * free - backward_working_bytes(d)) // per)
-        return max(0, min(d.L, d.L - keep))
+        count = max(0, min(d.L, d.L - keep))
+        # a recomputed layer repeats its forward collectives: ranks that shard one model (tensor or context
+        # parallel) must agree on the count, whatever their own free memory says
+        shared = d.comm if d.comm is not None else d.cp
+        if shared is not None and getattr(shared, "world", 1) > 1:
+            # (agreed once per shape: the answer is kept on the model)
+            cache = model.__dict__.setdefault("_agreed_recompute", {})
+            key = (d.B, d.T, d.fast)
+            if key not in cache:
+                import torch.distributed as dist
+                t = torch.tensor([count], device=d.device, dtype=torch.int32)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=getattr(shared, "group", None))
+                cache[key] = int(t.item())
+            count = cache[key]
+        return count
     raise ValueError(f"recompute must be a bool, an int or 'auto', not {r!r}")
 
 
