@@ -56,6 +56,16 @@ typedef struct {
   const long long* peer_out;
   int peer_world, peer_rank;
   long long peer_rows;
+  // All-gather of A inside the kernel (gather_world > 1): A is this rank's copy of a symmetric contiguous
+  // [M, K] bf16 buffer of which every rank has written its own gather_rows rows (M = gather_world * gather_rows,
+  // gather_rows % 128 == 0); gather_src[r] is rank r's copy. The kernel pulls the other ranks' rows into A with
+  // peer loads and starts a row block's tiles once it has arrived; gather_arrived holds M / 128 zeroed counters.
+  // K-major A, one problem (nz0 = nz1 = 1). The caller orders the launch after every rank's writes (a rank
+  // barrier before) and keeps the rows unchanged until every rank's launch is over (a rank barrier after).
+  const long long* gather_src;
+  int gather_world, gather_rank;
+  long long gather_rows;
+  unsigned* gather_arrived;
 } BdhGemmDesc;
 
 int bdh_gemm_bf16(const BdhMat* A, int a_mn_major, const BdhMat* B, int b_mn_major,

@@ -45,7 +45,8 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           at::IntArrayRef o1_off, double alpha, double theta, int64_t T, int64_t pos0,
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
           int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed,
-          at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank, const optional<Tensor>& bias) {
+          at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank, const optional<Tensor>& bias,
+          at::IntArrayRef gather_ptrs, int64_t gather_rows, int64_t gather_rank, const optional<Tensor>& gather_arrived) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -76,6 +77,17 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
     TORCH_CHECK(peer_ptrs.size() <= 8, "at most 8 peers");
     for (size_t i = 0; i < peer_ptrs.size(); ++i) peers[i] = peer_ptrs[i];
     d.peer_out = peers; d.peer_world = static_cast<int>(peer_ptrs.size()); d.peer_rows = peer_rows; d.peer_rank = static_cast<int>(peer_rank);
+  }
+  long long gsrc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (gather_ptrs.size() > 1) {                                  // all-gather of A inside the kernel
+    TORCH_CHECK(gather_ptrs.size() <= 8, "at most 8 peers");
+    TORCH_CHECK(gather_arrived.has_value() && gather_arrived->is_cuda() && gather_arrived->is_contiguous() &&
+                gather_arrived->scalar_type() == at::kInt && gather_arrived->numel() >= (M + 127) / 128,
+                "gather_arrived: int32 counters, one per 128 rows of A");
+    for (size_t i = 0; i < gather_ptrs.size(); ++i) gsrc[i] = gather_ptrs[i];
+    d.gather_src = gsrc; d.gather_world = static_cast<int>(gather_ptrs.size()); d.gather_rows = gather_rows;
+    d.gather_rank = static_cast<int>(gather_rank);
+    d.gather_arrived = reinterpret_cast<unsigned*>(gather_arrived->data_ptr<int>());
   }
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
@@ -511,7 +523,8 @@ TORCH_LIBRARY(bdh, m) {
   m.def("gemm(Tensor a, bool a_mn, Tensor b, bool b_mn, int M, int N, int K, int nz0, int nz1, int[] a_off, "
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
-        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank, Tensor? bias) -> ()");
+        "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank, Tensor? bias, "
+        "int[] gather_ptrs, int gather_rows, int gather_rank, Tensor(c!)? gather_arrived) -> ()");
   m.def("dual_gemm(Tensor a1, Tensor b1, bool b1_mn, Tensor b2, Tensor(a!) p, int M, int H, int n_per_head, int K1, int N2, "
         "int T, int epi, int flags, int group_per_head, int a1_b, int a1_h, int b1_b, Tensor? in0, Tensor? in1, "
         "Tensor(b!)? out1, float alpha, float theta, int pos0, float drop_p, int drop_seed, Tensor(c!) partials, "

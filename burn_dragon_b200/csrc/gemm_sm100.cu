@@ -87,6 +87,12 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const EpiMaps& e
   long long tiles = tiles_m * tiles_n * g.nz0 * g.nz1;
   int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
   if (grid < 1) grid = 1;
+  if (g.gather.world > 1) {
+    GemmArgs gg = g;
+    gg.gather.target = EW;          // every epilogue warp of the copying CTA counts a finished block once
+    kern<<<grid, gemm_threads(EW), L::TOTAL, stream>>>(ta, tb, em, gg);
+    return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+  }
   kern<<<grid, gemm_threads(EW), L::TOTAL, stream>>>(ta, tb, em, g);
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
@@ -145,6 +151,28 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
       const long long cycle = (d->c_off[0] >= d->c_off[1] || d->nz1 == 1) ? per_z * d->nz0 : total;
       g.tile_shift = static_cast<int>((d->peer_rank * (cycle / d->peer_world)) % total);
     }
+  }
+
+  memset(&g.gather, 0, sizeof(g.gather));
+  if (d->gather_world > 1) {
+    if (a_mn || d->nz0 != 1 || d->nz1 != 1 || d->gather_world > GEMM_MAX_PEERS || !d->gather_src || !d->gather_arrived ||
+        d->gather_rank < 0 || d->gather_rank >= d->gather_world || d->gather_rows < GEMM_BM || (d->gather_rows % GEMM_BM) ||
+        d->gather_rows * d->gather_world != d->M || A->ld != d->K || (d->K % 8) || d->causal_tiles || d->causal_k ||
+        (d->flags & EPI_F_PEER_RS))
+      return BDH_ERR_ARGUMENT;
+    GatherArgs& ga = g.gather;
+    for (int i = 0; i < GEMM_MAX_PEERS; ++i)
+      ga.src[i] = i < d->gather_world ? reinterpret_cast<const uint4*>(d->gather_src[i]) : nullptr;
+    ga.dst = reinterpret_cast<uint4*>(const_cast<void*>(A->ptr));
+    ga.block_vec = static_cast<long long>(GEMM_BM) * d->K * 2 / 16;
+    ga.blocks_per_shard = static_cast<int>(d->gather_rows / GEMM_BM);
+    ga.arrived = d->gather_arrived;
+    ga.target = 0;                  // set by launch() to the instantiation's number of epilogue warps
+    ga.world = d->gather_world;
+    ga.rank = d->gather_rank;
+    // walk the tiles from this rank's own rows on, then the next rank's, ... (the order the blocks arrive in)
+    const long long tiles_n = (d->N + bn - 1) / bn;
+    g.tile_shift = static_cast<int>(static_cast<long long>(ga.rank) * ga.blocks_per_shard * tiles_n);
   }
 
   const int max_ctas = d->max_ctas > 0 ? d->max_ctas : num_sms();

@@ -91,7 +91,25 @@ struct EpiParams {
   int peer_world, peer_rank;
 };
 
+// All-gather of the A operand inside the GEMM (token-sharded activations under tensor parallelism): every rank
+// holds the rows [r * shard_rows, (r + 1) * shard_rows) of A in its own copy of a symmetric [M, K] buffer. At the
+// start of the kernel the epilogue warps of all CTAs pull the other ranks' row blocks (128 rows each) over NVLink
+// into the local copy with plain peer loads, in ring order from the next rank on, and count every finished block
+// in `arrived`; the TMA producer loads a row block of A (from LOCAL memory) only once its counter has reached
+// `target`. Tiles are walked from the local rows on (tile_shift), so the math on the rows that are already here
+// overlaps the transfer of the others. world <= 1: no gather.
+struct GatherArgs {
+  const uint4* src[GEMM_MAX_PEERS];   // every rank's copy of the buffer (peer mappings; [rank] is unused)
+  uint4* dst;                         // this rank's copy (the A tensor map points at it)
+  long long block_vec;                // 16-byte vectors per block of GEMM_BM rows
+  int blocks_per_shard;
+  unsigned* arrived;                  // [M / GEMM_BM] counters, zero before the launch
+  unsigned target;                    // counter value of a complete block (= number of epilogue warps)
+  int world, rank;
+};
+
 struct GemmArgs {
+  GatherArgs gather;
   int M, N, K;
   int nz0, nz1;
   OperandOffsets a, b;
@@ -639,6 +657,61 @@ struct EpiMaps {
 };
 
 // ------------------------------------------------------------------------------------------------
+// All-gather of A inside the kernel (GatherArgs).
+// ------------------------------------------------------------------------------------------------
+// Called by every epilogue warp of every CTA before its tile loop. Block u of the (world - 1) * blocks_per_shard
+// remote blocks goes to CTA u % gridDim.x; the shards are taken in ring order from rank + 1 on, which is the
+// order in which the tile walk reaches them.
+__device__ __forceinline__ void gather_copy(const GatherArgs& ga, int ew, int n_warps, int lane) {
+  const int units = (ga.world - 1) * ga.blocks_per_shard;
+  for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    const int s = u / ga.blocks_per_shard, j = u - s * ga.blocks_per_shard;
+    int r = ga.rank + 1 + s;
+    if (r >= ga.world) r -= ga.world;
+    const long long blk = static_cast<long long>(r) * ga.blocks_per_shard + j;
+    const uint4* src = ga.src[r] + blk * ga.block_vec;
+    uint4* dst = ga.dst + blk * ga.block_vec;
+    const long long step = static_cast<long long>(n_warps) * 32;
+    long long i = static_cast<long long>(ew) * 32 + lane;
+    // four loads in flight per thread: the peer round trip is a few microseconds
+    for (; i + 3 * step < ga.block_vec; i += 4 * step) {
+      const uint4 a = __ldcs(src + i), b = __ldcs(src + i + step), c = __ldcs(src + i + 2 * step),
+                  d = __ldcs(src + i + 3 * step);
+      dst[i] = a; dst[i + step] = b; dst[i + 2 * step] = c; dst[i + 3 * step] = d;
+    }
+    for (; i < ga.block_vec; i += step) dst[i] = __ldcs(src + i);
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();                       // this warp's stores are visible before the count
+      atomicAdd(ga.arrived + blk, 1u);
+    }
+  }
+}
+
+// Producer side: the block's counter has reached `target`, and the TMA unit (async proxy) may read what the
+// copiers wrote with ordinary stores. Bounded like every other wait.
+__device__ __forceinline__ bool gather_wait(const unsigned* counter, unsigned target, volatile int* abort_flag,
+                                            int* status) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v >= target) break;
+    if ((++it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > BDH_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, STATUS_OK, STATUS_TIMEOUT_PEER_FLAG);
+        return false;
+      }
+    }
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Tile enumeration shared by the three roles (they must agree on the sequence).
 // ------------------------------------------------------------------------------------------------
 struct TileCoord {
@@ -788,11 +861,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       uint32_t armed = 0, armed_parity = 0;  // per-stage: a load was issued / with which phase
+      int ready_block = -1;                  // last gathered row block known to be complete
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
         const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
         const int nkb = (k_end + GEMM_BK - 1) / GEMM_BK;
         const int kb0 = (g.causal_k == 2) ? min(nkb, tc.m0 / GEMM_BK) : 0;
+        if (g.gather.world > 1) {
+          // rows of another rank: wait (bounded) until the copiers have brought the block into local memory
+          const int blk = tc.m0 / GEMM_BM;
+          if (blk / g.gather.blocks_per_shard != g.gather.rank && blk != ready_block) {
+            if (!gather_wait(g.gather.arrived + blk, g.gather.target, abort_flag, g.status)) {
+              ok = false;
+              break;
+            }
+            ready_block = blk;
+          }
+        }
         const int a_mn = static_cast<int>(tc.m0 + tc.z0 * g.a.mn0 + tc.z1 * g.a.mn1);
         const int a_k = static_cast<int>(tc.z0 * g.a.k0 + tc.z1 * g.a.k1);
         const int b_mn = static_cast<int>(tc.n0 + tc.z0 * g.b.mn0 + tc.z1 * g.b.mn1);
@@ -896,6 +981,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;            // TMEM lane quarter this warp may read
     const int ew = warp - 2;           // epilogue warp index
     const int cbase = (ew >> 2) * CHUNKS;   // first 32-column chunk of this warp inside a tile
+    if (g.gather.world > 1) gather_copy(g.gather, ew, EW, lane);
     int acc = 0;
     uint32_t acc_phase = 0;
     if constexpr (!TMA_EPI) {

@@ -112,7 +112,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          causal_tiles: int = 0, causal_k: int = 0, bn: int = 256, max_ctas: int = 0,
          tma_epilogue: bool = True, mc_out: int = 0, drop_p: float = 0.0, drop_seed: int = 0,
          peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0,
-         bias: Optional[torch.Tensor] = None) -> None:
+         bias: Optional[torch.Tensor] = None, gather_ptrs: Sequence[int] = (), gather_rows: int = 0,
+         gather_rank: int = 0, gather_arrived: Optional[torch.Tensor] = None) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     if _CHECKED:
@@ -121,7 +122,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
     native.ops.gemm(a, a_mn, b, b_mn, M, N, K, nz[0], nz[1], list(a_off), list(b_off), epi, flags, out0, out1,
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),
-                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank), bias)
+                    int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank), bias,
+                    [int(p) for p in gather_ptrs], int(gather_rows), int(gather_rank), gather_arrived)
 
 
 # ------------------------------------------------------------------------------------------------

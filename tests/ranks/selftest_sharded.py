@@ -469,3 +469,109 @@ def case_cp_train_kernels(dev):
                 assert cos > 0.99 and _rel(p.grad, ref[n]) < 0.12, (rot, chunk, n, cos, _rel(p.grad, ref[n]))
             notes.append(f"{rot}/{chunk}")
     return " ".join(notes)
+
+
+def _ag_fill(op, seed):
+    """Every rank writes its own rows of the gathered operand; returns the whole matrix (the same on every
+    rank, from the seeds) for the oracle."""
+    parts = []
+    for r in range(op.world):
+        g = torch.Generator().manual_seed(seed * 100 + r)
+        parts.append((torch.randn(op.rows, op.K, generator=g) * 0.5).to(torch.bfloat16))
+    op.shard.copy_(parts[op.rank].to(op.full.device))
+    return torch.cat(parts, 0).to(op.full.device)
+
+
+def case_ag_gemm(dev):
+    """All-gather -> GEMM as one kernel (`parallel/seqpar.py`): token shards written by every rank, gathered by
+    the GEMM's own warps over peer loads, against an fp32 matmul over the whole matrix; plain and ReLU
+    epilogues, three rounds with fresh data (the counters, barriers and buffers are reused), and the NCCL
+    baseline of the same product."""
+    from burn_dragon_b200.ops import gemm as G
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel.seqpar import GatheredOperand
+    world = dist.get_world_size()
+    M, K, N = 256 * world, 256, 512
+    op = GatheredOperand(M, K, dev)
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16).to(dev)
+    notes = []
+    for rnd in range(3):
+        A = _ag_fill(op, rnd)
+        want = A.float() @ w.float().t()
+        out = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+        native.clear_status()
+        if rnd == 1:
+            op.gemm(w, N=N, epi=G.EPI_RELU, out0=out, theta=0.1)
+            want = torch.relu(want - 0.1)
+        else:
+            op.gemm(w, N=N, out0=out)
+        op.release()
+        torch.cuda.synchronize()
+        assert native.status_code() == 0, "a bounded wait ran out"
+        assert torch.equal(op.full, A), "the local copy holds every rank's rows after the launch"
+        assert _rel(out, want) < 1e-2, (rnd, _rel(out, want))
+        out2 = torch.zeros_like(out)
+        op.shard.copy_(A[op.rank * op.rows:(op.rank + 1) * op.rows])
+        if rnd == 1:
+            op.gemm_nccl(w, N=N, epi=G.EPI_RELU, out0=out2, theta=0.1)
+        else:
+            op.gemm_nccl(w, N=N, out0=out2)
+        op.release()
+        assert _rel(out2, want) < 1e-2
+        notes.append(f"{_rel(out, want):.1e}")
+    return " ".join(notes)
+
+
+def case_ag_gemm_bw(dev):
+    """The encoder product of the tensor-parallel configuration with its token rows sharded: [16384, 1024] bf16
+    activations (1/world of the rows per rank) times this rank's [32768, 1024] slice of the neurons, ReLU
+    epilogue. Fused (gather inside the GEMM) against NCCL all-gather + GEMM, device-timed, max over ranks."""
+    import json
+    from burn_dragon_b200.ops import gemm as G
+    from burn_dragon_b200.ops import native
+    from burn_dragon_b200.parallel.seqpar import GatheredOperand
+    rank, world = dist.get_rank(), dist.get_world_size()
+    M, K, N = 16384, 1024, 32768
+    op = GatheredOperand(M, K, dev)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    A = _ag_fill(op, 1)
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def fused():
+        op.gemm(w, N=N, epi=G.EPI_RELU, out0=out, theta=0.0)
+        op.release()
+
+    def nccl():
+        op.gemm_nccl(w, N=N, epi=G.EPI_RELU, out0=out, theta=0.0)
+        op.release()
+
+    def alone():
+        G.gemm(op.full, w, M=M, N=N, K=K, epi=G.EPI_RELU, out0=out, theta=0.0)
+
+    native.clear_status()
+    res = dict(world=world, fused_ms=timed(fused), nccl_ms=timed(nccl), gemm_alone_ms=timed(alone),
+               gathered_mb=(world - 1) / world * M * K * 2 / 1e6)
+    assert native.status_code() == 0
+    want = torch.relu(A.float()[:512] @ w.float()[:512].t())
+    fused()
+    torch.cuda.synchronize()
+    assert _rel(out[:512, :512], want) < 1e-2
+    if rank == 0:
+        print("AG_GEMM_BW " + json.dumps(res), flush=True)
+    return ""

@@ -45,6 +45,10 @@ def test_gemm_with_reduction_epilogue_every_mode():
     assert "rs" in out
 
 
+def test_all_gather_inside_the_gemm_kernel():
+    run_ranks("ag_gemm", cpu=False)
+
+
 def test_context_parallel_equals_single_gpu():
     run_ranks("cp", cpu=False)
 
