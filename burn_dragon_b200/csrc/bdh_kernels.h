@@ -165,9 +165,12 @@ int bdh_add_f32_to_f32(const float* in, float* inout, long long n, cudaStream_t 
 
 // ---- cached decode (decode.cu) -------------------------------------------------------------------
 // a[h*B+b,:] += sum_n q[b,h*Np+n] rho[b,h,n,:] ; rho = (rho + q^T v) * exp(-slope_h). `a` must be
-// zeroed by the caller. slopes == nullptr: no decay, rows with q == 0 are skipped entirely.
+// zeroed by the caller. slopes == nullptr: no decay, rows with q == 0 are skipped entirely. With slopes and
+// `last` (int32 [B,H,Np]) + `step_dev` (device counter of the current step): lazy decay - row n of the stored
+// state is current up to step last[n]; touched rows are caught up with exp(-slope (step - last)) and marked
+// step + 1, rows with q == 0 are skipped. last == step_dev == nullptr: every row is scaled every step.
 int bdh_decode_state_update(const void* q_bf16, const void* v_bf16, float* rho, float* a, const float* slopes,
-                            int B, int H, int Np, int D, cudaStream_t s);
+                            int* last, const int* step_dev, int B, int H, int Np, int D, cudaStream_t s);
 // One token per row of fp32 logits [B, V <= 1024]; step_dev (optional) is a device counter mixed
 // into the random stream so a captured graph draws fresh numbers every replay.
 int bdh_sample_tokens(const float* logits, long long* out, int B, int V, float temperature, int top_k,

@@ -340,15 +340,23 @@ void shard_bcast(at::IntArrayRef flag_ptrs, at::IntArrayRef out_ptrs, int64_t ou
            "shard_bcast");
 }
 
-void decode_state_update(const Tensor& q, const Tensor& v, Tensor& rho, Tensor& a, const optional<Tensor>& slopes) {
+void decode_state_update(const Tensor& q, const Tensor& v, Tensor& rho, Tensor& a, const optional<Tensor>& slopes,
+                         c10::optional<Tensor> last, const optional<Tensor>& step_dev) {
   c10::cuda::CUDAGuard guard(q.device());
   TORCH_CHECK(rho.dim() == 4 && rho.is_contiguous() && rho.scalar_type() == at::kFloat);
   const int64_t B = rho.size(0), H = rho.size(1), Np = rho.size(2), D = rho.size(3);
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.numel() == B * H * Np);
   TORCH_CHECK(v.scalar_type() == at::kBFloat16 && v.is_contiguous() && v.numel() == B * D);
   TORCH_CHECK(a.scalar_type() == at::kFloat && a.is_contiguous() && a.numel() == H * B * D);
+  TORCH_CHECK(last.has_value() == step_dev.has_value(), "decode_state_update: last and step_dev come together");
+  if (last.has_value())
+    TORCH_CHECK(last->is_cuda() && last->is_contiguous() && last->scalar_type() == at::kInt && last->numel() == B * H * Np &&
+                step_dev->is_cuda() && step_dev->scalar_type() == at::kInt && step_dev->numel() >= 1 && slopes.has_value(),
+                "decode_state_update: last int32 [B,H,Np], step_dev int32 [1], with slopes");
   check_rc(bdh_decode_state_update(q.data_ptr(), v.data_ptr(), rho.data_ptr<float>(), a.data_ptr<float>(),
-                                   slopes.has_value() ? slopes->data_ptr<float>() : nullptr, B, H, Np, D, cur_stream()),
+                                   slopes.has_value() ? slopes->data_ptr<float>() : nullptr,
+                                   last.has_value() ? last->data_ptr<int>() : nullptr,
+                                   step_dev.has_value() ? step_dev->data_ptr<int>() : nullptr, B, H, Np, D, cur_stream()),
            "decode_state_update");
 }
 void sample_tokens(const Tensor& logits, Tensor& out, double temperature, int64_t top_k, bool greedy, int64_t seed,
@@ -573,7 +581,8 @@ TORCH_LIBRARY(bdh, m) {
         "Tensor(c!) dw) -> ()");
   m.def("ssd_chunk_scan(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) states, Tensor(c!) decay, "
         "Tensor(d!) y, bool tensor_cores) -> ()");
-  m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes) -> ()");
+  m.def("decode_state_update(Tensor q, Tensor v, Tensor(a!) rho, Tensor(b!) a, Tensor? slopes, Tensor(c!)? last=None, "
+        "Tensor? step_dev=None) -> ()");
   m.def("sample_tokens(Tensor logits, Tensor(a!) out, float temperature, int top_k, bool greedy, int seed, int step, "
         "Tensor? step_dev) -> ()");
   m.def("viz_encode_units(Tensor values, Tensor(a!) image, int cursor, int row0, float gain, float[] lo, float[] hi, "

@@ -6,9 +6,13 @@
 //     rho[b,h,n,:] = (rho[b,h,n,:] + q[b,h,n] * v[b,:]) * gamma_h
 // The state is fp32 [B, H, N', D] and is the only large thing a decode step touches, so the kernel
 // is written around its traffic: rows whose query entry is zero (the ReLU-sparse majority) are
-// neither read nor written when there is no decay (RoPE / PoPE); with ALiBi decay every row is
-// scaled. One CTA owns a slab of rows of one (stream, head); partial outputs are combined with
-// fp32 atomics into a zero-initialised `a`.
+// neither read nor written when there is no decay (RoPE / PoPE). With ALiBi decay every row is
+// scaled every step - unless the decay is applied lazily: `last[b,h,n]` holds the step up to which
+// row n is current, a row is brought up to date (times gamma^(step - last)) only when its query entry
+// touches it, and rows with a zero query entry are skipped as in the decay-free case. Whoever takes
+// the state out of the engine first brings every row up to date (engine/decode_engine.py). One CTA
+// owns a slab of rows of one (stream, head); partial outputs are combined with fp32 atomics into a
+// zero-initialised `a`.
 #include "bdh_kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -22,22 +26,29 @@ constexpr int DEC_THREADS = 256;
 
 // q: bf16 [B, H*Np] (row b, column h*Np + n); v: bf16 [B, D]; rho: fp32 [B,H,Np,D]; a: fp32 [H*B, D]
 // written at row h*B + b (head-major, the layout the following GEMM consumes).
+__device__ __forceinline__ int n0_of(int slab) { return slab * DEC_ROWS_PER_CTA; }
+
 template <int VEC>  // D = VEC * 4 * lanes_per_row ... each thread owns 4*VEC consecutive floats
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_state_update_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ v,
                            float* __restrict__ rho, float* __restrict__ a, const float* __restrict__ slopes,
-                           int B, int H, int Np, int D) {
+                           int* __restrict__ last, const int* __restrict__ step_dev, int B, int H, int Np, int D) {
   const int slab = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int threads_per_row = D / (4 * VEC);              // threads that cover one row of D floats
   const int rows_in_flight = DEC_THREADS / threads_per_row;
   const int tr = threadIdx.x / threads_per_row;           // which row of the group
   const int tc = threadIdx.x % threads_per_row;           // which 4*VEC-float segment of the row
-  const float gamma = slopes ? __expf(-slopes[h]) : 1.f;
-  const bool dense = slopes != nullptr;
+  const float slope = slopes ? slopes[h] : 0.f;
+  const float gamma = slopes ? __expf(-slope) : 1.f;
+  const bool lazy = slopes != nullptr && last != nullptr;
+  const bool dense = slopes != nullptr && !lazy;
+  const int step = lazy ? *step_dev : 0;
+  int* last_row = lazy ? last + (static_cast<long long>(b) * H + h) * Np + n0_of(slab) : nullptr;
 
   __shared__ float qs[DEC_ROWS_PER_CTA];
   __shared__ int active[DEC_ROWS_PER_CTA];
   __shared__ int n_active;
+  __shared__ float catch_up_s[DEC_ROWS_PER_CTA];
   const int n0 = slab * DEC_ROWS_PER_CTA;
   const __nv_bfloat16* qrow = q + static_cast<long long>(b) * H * Np + static_cast<long long>(h) * Np;
   if (threadIdx.x == 0) n_active = 0;
@@ -46,7 +57,13 @@ decode_state_update_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     const int n = n0 + i;
     const float qv = (n < Np) ? __bfloat162float(qrow[n]) : 0.f;
     qs[i] = qv;
-    if (n < Np && (dense || qv != 0.f)) active[atomicAdd(&n_active, 1)] = i;
+    const bool live = n < Np && (dense || qv != 0.f);
+    if (live) active[atomicAdd(&n_active, 1)] = i;
+    if (lazy && live) {
+      // one thread per row reads how many steps the row sat out and marks it current (through this step's decay)
+      catch_up_s[i] = __expf(-slope * static_cast<float>(step - last_row[i]));
+      last_row[i] = step + 1;
+    }
   }
   __syncthreads();
   const int na = n_active;
@@ -66,16 +83,18 @@ decode_state_update_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
   for (int j0 = tr; j0 < na; j0 += rows_in_flight * UNROLL) {
     float4 r[UNROLL][VEC];
     float4* p[UNROLL];
-    float qv[UNROLL];
+    float qv[UNROLL], catch_up[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int j = j0 + u * rows_in_flight;
       const int i = (j < na) ? active[j] : 0;
       qv[u] = (j < na) ? qs[i] : 0.f;
+      catch_up[u] = 1.f;
       p[u] = reinterpret_cast<float4*>(base + static_cast<long long>(n0 + i) * D);
       if (j < na) {
 #pragma unroll
         for (int k = 0; k < VEC; ++k) r[u][k] = __ldcs(p[u] + k);
+        if (lazy) catch_up[u] = catch_up_s[i];
       }
     }
 #pragma unroll
@@ -84,6 +103,7 @@ decode_state_update_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         float4 t = r[u][k];
+        t.x *= catch_up[u]; t.y *= catch_up[u]; t.z *= catch_up[u]; t.w *= catch_up[u];
         acc[4 * k + 0] += qv[u] * t.x; acc[4 * k + 1] += qv[u] * t.y;
         acc[4 * k + 2] += qv[u] * t.z; acc[4 * k + 3] += qv[u] * t.w;
         t.x = (t.x + qv[u] * vv[4 * k + 0]) * gamma; t.y = (t.y + qv[u] * vv[4 * k + 1]) * gamma;
@@ -265,19 +285,19 @@ __global__ void bump_counter_kernel(int* counter, int by) { *counter += by; }
 using namespace bdh;
 
 extern "C" int bdh_decode_state_update(const void* q, const void* v, float* rho, float* a, const float* slopes,
-                                       int B, int H, int Np, int D, cudaStream_t s) {
-  if (D % 64 || D > 1024 || Np <= 0 || B <= 0) return BDH_ERR_ARGUMENT;
+                                       int* last, const int* step_dev, int B, int H, int Np, int D, cudaStream_t s) {
+  if (D % 64 || D > 1024 || Np <= 0 || B <= 0 || (last != nullptr) != (step_dev != nullptr)) return BDH_ERR_ARGUMENT;
   dim3 grid((Np + DEC_ROWS_PER_CTA - 1) / DEC_ROWS_PER_CTA, H, B);
   // 64 threads per row when possible (D/64 floats each): VEC = D / 256, at least 1
   typedef const __nv_bfloat16* bp;
   if (D % 256 == 0 && D / 256 == 1)
-    decode_state_update_kernel<1><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, B, H, Np, D);
+    decode_state_update_kernel<1><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, last, step_dev, B, H, Np, D);
   else if (D % 256 == 0 && D / 256 == 2)
-    decode_state_update_kernel<2><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, B, H, Np, D);
+    decode_state_update_kernel<2><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, last, step_dev, B, H, Np, D);
   else if (D % 256 == 0 && D / 256 == 4)
-    decode_state_update_kernel<4><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, B, H, Np, D);
+    decode_state_update_kernel<4><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, last, step_dev, B, H, Np, D);
   else if (DEC_THREADS % (D / 4) == 0)
-    decode_state_update_kernel<1><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, B, H, Np, D);
+    decode_state_update_kernel<1><<<grid, DEC_THREADS, 0, s>>>((bp)q, (bp)v, rho, a, slopes, last, step_dev, B, H, Np, D);
   else
     return BDH_ERR_UNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;

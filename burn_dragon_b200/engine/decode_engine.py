@@ -22,7 +22,8 @@ from ..ops.fused_bdh import _Dims, _weights
 
 
 class DecodeEngine:
-    def __init__(self, model, use_graph: bool = True, split_k: int = 32, pope_graph: Optional[bool] = None):
+    def __init__(self, model, use_graph: bool = True, split_k: int = 32, pope_graph: Optional[bool] = None,
+                 lazy_decay: bool = True):
         self.model = model
         self.use_graph = use_graph
         # PoPE: the fused rotation epilogue takes the position as a host argument, so a step that uses
@@ -31,6 +32,7 @@ class DecodeEngine:
         # memory - the form the stream pool uses - which makes the single-request PoPE step capturable.
         self.pope_graph = (os.environ.get("BDH_POPE_DECODE_GRAPH", "0") == "1") if pope_graph is None else bool(pope_graph)
         self.split_k = split_k
+        self.lazy_decay = bool(lazy_decay)
         self._cache = {}       # (streams, device, sampling settings) -> buffers, state storage, captured graph
         self.launches_per_step = None
 
@@ -78,7 +80,10 @@ class DecodeEngine:
         return buf
 
     # ---- one step (all launches on the current stream) -------------------------------------------
-    def _step(self, buf, W, rho: List[torch.Tensor], settings, seed: int, pos_host: Optional[int]):
+    def _step(self, buf, W, rho: List[torch.Tensor], settings, seed: int, pos_host: Optional[int],
+              last: Optional[List[torch.Tensor]] = None):
+        """`last` (ALiBi models): per layer, the step up to which every state row is current - the decay is then
+        applied lazily, only to the rows a step touches (see `_catch_up`)."""
         ops = native.ops
         d, S = buf["d"], buf["S"]
         B = buf["tok"].shape[0]
@@ -118,7 +123,10 @@ class DecodeEngine:
                 G.gemm(cur, W["encoder"], M=B, N=d.HN, K=d.D, epi=G.EPI_RELU, out0=buf["x"], theta=d.theta)
                 q = buf["x"]
             # `a` is zero here: cleared at allocation and again by every pass that reads it
-            ops.decode_state_update(q, cur, rho[l], buf["a"], d.slopes)
+            if last is not None:
+                ops.decode_state_update(q, cur, rho[l], buf["a"], d.slopes, last[l], buf["step"])
+            else:
+                ops.decode_state_update(q, cur, rho[l], buf["a"], d.slopes)
             ops.layernorm_f32_clear(buf["a"], buf["lna"])
             G.gemm(buf["lna"], W["encoder_v"], M=B, N=d.N, K=d.D, nz=(d.H, 1), a_off=(B, 0, 0, 0),
                    b_off=(d.N, 0, 0, 0), c_off=(0, 0, d.N, 0), epi=G.EPI_RELU_GATE, flags=G.F_NO_OUT0, in0=buf["x"],
@@ -139,6 +147,16 @@ class DecodeEngine:
         else:
             ops.bump_counter(buf["pos"], 1)
         ops.bump_counter(buf["step"], 1)
+
+    @staticmethod
+    def _catch_up(rho, last, step, slopes) -> None:
+        """Lazy decay: bring every state row up to date before the state leaves the engine,
+        rho[b,h,n] *= gamma_h^(step - last[b,h,n])."""
+        H = slopes.numel()
+        for r, t in zip(rho, last):
+            lag = (step.view(1, 1, 1) - t).float()
+            r.mul_(torch.exp(-slopes.float().view(1, H, 1) * lag).unsqueeze(-1))
+            t.copy_(step.view(1, 1, 1).expand_as(t))
 
     # ---- public ------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -167,10 +185,14 @@ class DecodeEngine:
         if ctx is None:
             buf = self._alloc(B, dev)
             rho = [torch.zeros(B, c.n_head, c.state_latent, c.n_embd, device=dev) for _ in range(c.n_layer)]
-            ctx = dict(buf=buf, rho=rho, graph=None)
+            # ALiBi: lazy decay (rows whose query entry is zero are not streamed; the state is brought up to date
+            # when it leaves the engine). `lazy_decay=False` on the engine scales every row every step.
+            seen = ([torch.zeros(B, c.n_head, c.state_latent, device=dev, dtype=torch.int32) for _ in range(c.n_layer)]
+                    if (buf["d"].slopes is not None and self.lazy_decay) else None)
+            ctx = dict(buf=buf, rho=rho, graph=None, last=seen)
             self._cache.clear()            # one resident configuration: the state buffers are large
             self._cache[key] = ctx
-        buf, rho = ctx["buf"], ctx["rho"]
+        buf, rho, seen = ctx["buf"], ctx["rho"], ctx["last"]
         d = buf["d"]
         W = _weights(model)
 
@@ -185,6 +207,9 @@ class DecodeEngine:
             buf["pos"].fill_(state.position)
             buf["step"].fill_(int(step0))
             buf["a"].zero_()           # (every step leaves it cleared; this covers a step that was interrupted)
+            if seen is not None:
+                for t in seen:
+                    t.fill_(int(step0))    # what comes in is current
 
         load_state()
         graph_ok = self.use_graph and (d.rot != "pope" or self.pope_graph) and dev.type == "cuda"
@@ -196,13 +221,13 @@ class DecodeEngine:
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
-                    self._step(buf, W, rho, settings, seed, None)
+                    self._step(buf, W, rho, settings, seed, None, seen)
                 torch.cuda.current_stream().wait_stream(s)
                 load_state()
                 graph = torch.cuda.CUDAGraph()
                 n0 = native.launch_count()
                 with torch.cuda.graph(graph):
-                    self._step(buf, W, rho, settings, seed, None)
+                    self._step(buf, W, rho, settings, seed, None, seen)
                 # kernels of this library inside one replay (what a benchmark reports as its launches per step)
                 self.launches_per_step = native.launch_count() - n0
                 ctx["graph"], ctx["weights"] = graph, W
@@ -220,11 +245,13 @@ class DecodeEngine:
                     on_token(t)
         else:
             for i in range(n):
-                self._step(buf, W, rho, settings, seed, state.position + i)
+                self._step(buf, W, rho, settings, seed, state.position + i, seen)
                 t = buf["tok"].clone()
                 out.append(t.view(-1, 1))
                 if on_token is not None:
                     on_token(t)
+        if seen is not None:
+            self._catch_up(rho, seen, buf["step"], d.slopes)
         for ls, r in zip(state.layers, rho):
             ls.rho = r
         state.position += n

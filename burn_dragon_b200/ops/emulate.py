@@ -162,10 +162,23 @@ class TorchOps:
         counter.add_(int(by))
 
     @staticmethod
-    def decode_state_update(q, v, rho, a, slopes):
-        """a[h*B + b] += q[b, h] . rho[b, h];  rho[b, h] = (rho[b, h] + q[b, h]^T v[b]) * exp(-slope_h)."""
+    def decode_state_update(q, v, rho, a, slopes, last=None, step_dev=None):
+        """a[h*B + b] += q[b, h] . rho[b, h];  rho[b, h] = (rho[b, h] + q[b, h]^T v[b]) * exp(-slope_h).
+        With `last` / `step_dev` the decay is lazy: only rows with a non-zero query entry are brought up to date
+        (times exp(-slope (step - last))), updated and marked current up to step + 1."""
         B, H, Np, D = rho.shape
         qf = q.float().view(B, H, Np)
+        if last is not None:
+            step = int(step_dev.reshape(-1)[0])
+            live = qf != 0
+            lag = (step - last.view(B, H, Np)).float()
+            up = torch.where(live, torch.exp(-slopes.float().view(1, H, 1) * lag), torch.ones_like(lag))
+            rho.mul_(up.unsqueeze(-1))
+            a.view(H, B, D).add_(torch.einsum("bhn,bhnd->hbd", qf, rho))
+            new = (rho + qf.unsqueeze(-1) * v.float().view(B, 1, 1, D)) * torch.exp(-slopes.float()).view(1, H, 1, 1)
+            rho.copy_(torch.where(live.unsqueeze(-1), new, rho))
+            last.view(B, H, Np).copy_(torch.where(live, torch.full_like(last.view(B, H, Np), step + 1), last.view(B, H, Np)))
+            return
         a.view(H, B, D).add_(torch.einsum("bhn,bhnd->hbd", qf, rho))
         rho.add_(qf.unsqueeze(-1) * v.float().view(B, 1, 1, D))
         if slopes is not None:

@@ -229,3 +229,30 @@ def test_decode_row_kernels_match_their_definitions(D):
     native.ops.block_out_parts(cur, part, out)
     want = R.layer_norm(cur.float() + R.layer_norm(part.view(parts, rows, D).sum(0)))
     assert (out.float() - want).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("D", [64, 256])
+def test_lazy_decay_equals_decaying_every_row_every_step(D):
+    """ALiBi decay applied lazily (rows with a zero query entry are skipped and caught up with
+    gamma^(steps missed) when next touched) against the kernel that scales every row every step: same
+    attention outputs at every step and, after the final catch-up, the same state."""
+    from burn_dragon_b200.engine.decode_engine import DecodeEngine
+    B, H, Np, steps = 3, 2, 320, 7
+    g = torch.Generator(device="cuda").manual_seed(0)
+    slopes = torch.tensor([0.3, 0.05], device="cuda")
+    rho_d = torch.randn(B, H, Np, D, device="cuda", generator=g)
+    rho_l = rho_d.clone()
+    seen = torch.full((B, H, Np), 4, device="cuda", dtype=torch.int32)
+    step = torch.full((1,), 4, device="cuda", dtype=torch.int32)
+    for _ in range(steps):
+        q = torch.relu(torch.randn(B, H * Np, device="cuda", generator=g) - 0.8).to(torch.bfloat16)   # ~20 % live
+        v = torch.randn(B, D, device="cuda", generator=g).to(torch.bfloat16)
+        a_d, a_l = torch.zeros(H * B, D, device="cuda"), torch.zeros(H * B, D, device="cuda")
+        native.ops.decode_state_update(q, v, rho_d, a_d, slopes)
+        native.ops.decode_state_update(q, v, rho_l, a_l, slopes, seen, step)
+        step += 1
+        assert _rel(a_l, a_d) < 1e-5
+    assert _rel(rho_l, rho_d) > 1e-3            # untouched rows are still behind ...
+    DecodeEngine._catch_up([rho_l], [seen], step, slopes)
+    assert _rel(rho_l, rho_d) < 1e-5            # ... until the state leaves the engine
+    assert int(seen.min()) == int(seen.max()) == int(step)
