@@ -65,6 +65,10 @@ class StreamPool:
             self.buf["table"] = torch.zeros(self.slots, d.N, device=self.device, dtype=torch.bfloat16)
         self.rho = [torch.zeros(self.slots, c.n_head, c.state_latent, c.n_embd, device=self.device)
                     for _ in range(c.n_layer)]
+        # ALiBi models: lazy decay (per state row, the step up to which it is current; engine/decode_engine.py).
+        # Slot states only ever enter the pool (`add`) or are cleared (`release`), so nothing has to be caught up.
+        self.seen = ([torch.zeros(self.slots, c.n_head, c.state_latent, device=self.device, dtype=torch.int32)
+                      for _ in range(c.n_layer)] if (d.slopes is not None and self.engine.lazy_decay) else None)
         self.active: List[bool] = [False] * self.slots
         self.steps = 0
         self.graph = None
@@ -91,6 +95,9 @@ class StreamPool:
                 r[slot].copy_(l.rho[0])
         self.buf["logits"][slot].copy_(last[0].float())
         self.buf["pos"][slot] = int(state.position)
+        if self.seen is not None:
+            for t in self.seen:
+                t[slot].fill_(self.steps)        # the prefilled state is current as of the pool's step counter
         self.active[slot] = True
         return slot
 
@@ -110,14 +117,16 @@ class StreamPool:
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
-            self.engine._step(self.buf, W, self.rho, self.settings, self.seed, None)
+            self.engine._step(self.buf, W, self.rho, self.settings, self.seed, None, self.seen)
         torch.cuda.current_stream().wait_stream(s)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self.engine._step(self.buf, W, self.rho, self.settings, self.seed, None)
+            self.engine._step(self.buf, W, self.rho, self.settings, self.seed, None, self.seen)
         self.graph = graph
         for r in self.rho:
             r.zero_()
+        for t in (self.seen or []):
+            t.zero_()
         for k in ("logits", "pos", "step"):
             self.buf[k].zero_()
 
@@ -129,7 +138,7 @@ class StreamPool:
         if self.graph is not None:
             self.graph.replay()
         else:
-            self.engine._step(self.buf, self.W, self.rho, self.settings, self.seed, None)
+            self.engine._step(self.buf, self.W, self.rho, self.settings, self.seed, None, self.seen)
         self.steps += 1
         return self.buf["tok"].clone()
 
