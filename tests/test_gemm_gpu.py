@@ -224,6 +224,66 @@ def test_store_reversed_row_decay_with_atomics():
         _check(k, r, tol=1e-2)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_gather_inside_the_gemm_with_every_rank_on_one_gpu(world):
+    """The all-gather -> GEMM kernel with the ranks emulated on one GPU: every "rank" has its own copy of the
+    [M, K] buffer holding only its own rows; the launches run one after the other (no launch waits for
+    another), each pulling the other copies' rows into its own with the kernel's peer-load path, waiting on
+    its arrival counters and multiplying from its local copy."""
+    M, K, N = 256 * world, 192, 384
+    rows = M // world
+    A = _rand(M, K, 0.5, seed=41)
+    w = _rand(N, K, 0.3, seed=42)
+    want = A.float() @ w.float().t()
+    copies = []
+    for r in range(world):
+        c = torch.zeros(M, K, device="cuda", dtype=torch.bfloat16)
+        c[r * rows:(r + 1) * rows] = A[r * rows:(r + 1) * rows]
+        copies.append(c)
+    ptrs = [c.data_ptr() for c in copies]
+    for r in range(world):
+        # a later rank's launch finds rows in the earlier ranks' copies that those ranks gathered: same values
+        arrived = torch.zeros(M // 128, device="cuda", dtype=torch.int32)
+        out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+        native.clear_status()
+        G.gemm(copies[r], w, M=M, N=N, K=K, out0=out, gather_ptrs=ptrs, gather_rows=rows, gather_rank=r,
+               gather_arrived=arrived)
+        torch.cuda.synchronize()
+        assert native.status_code() == 0
+        assert torch.equal(copies[r], A), "the local copy holds every rank's rows afterwards"
+        own = arrived.view(world, -1)[r]
+        assert int(own.max()) == 0 and int(arrived.sum()) > 0, "own blocks are not copied, the others are counted"
+        _check(out, want)
+
+
+def test_reduce_scatter_epilogue_and_gather_with_two_ranks_on_one_gpu():
+    """The tensor-parallel reduction with both ranks emulated on one GPU: each "rank" has its own slot buffer,
+    output buffer and flag words; rank r's GEMM stores its partial tiles into slot r of the owner's buffer
+    (`F_PEER_RS`), then each rank's `gather_blocks` sums the slots of the rows it owns and stores the sum into
+    every rank's output. The launches run one after the other, so the flag words are written ahead of time
+    with a value every barrier of the call accepts (no launch waits for a later one)."""
+    world, M, N, K = 2, 512, 256, 1024
+    block_rows = M // world
+    a = [_rand(M, K, 0.3, seed=51 + r) for r in range(world)]
+    w = [_rand(K, N, 0.3, seed=61 + r) for r in range(world)]
+    want = sum(a[r].float() @ w[r].float() for r in range(world))
+    slots = [torch.zeros(world * block_rows, N, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M, N, device="cuda") for _ in range(world)]
+    epoch = 3
+    flags = [torch.full((4096,), 2 * epoch + 2, device="cuda", dtype=torch.int32) for _ in range(world)]
+    native.clear_status()
+    for r in range(world):
+        G.gemm(a[r], w[r], M=M, N=N, K=K, b_mn=True, flags=G.F_OUT_F32 | G.F_PEER_RS, out0=slots[r],
+               peer_ptrs=[t.data_ptr() for t in slots], peer_rows=block_rows, peer_rank=r)
+    for r in range(world):
+        native.ops.gather_blocks(slots[r], [t.data_ptr() for t in slots], [t.data_ptr() for t in flags],
+                                 [t.data_ptr() for t in outs], 0, False, r, world, block_rows * N, epoch, 8)
+    torch.cuda.synchronize()
+    assert native.status_code() == 0
+    for o in outs:
+        _check(o, want, tol=1e-2)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("alibi", [True, False])
 def test_rownorm_attention_matches_reference(alibi):
