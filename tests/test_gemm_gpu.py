@@ -284,6 +284,51 @@ def test_reduce_scatter_epilogue_and_gather_with_two_ranks_on_one_gpu():
         _check(o, want, tol=1e-2)
 
 
+def test_fully_sharded_step_with_two_ranks_on_one_gpu():
+    """The fully sharded data-parallel step with both ranks emulated on one GPU: each rank's weight-gradient
+    GEMM adds its tiles into the OWNER's fp32 gradient slice from its epilogue (`F_PEER_RS | F_ATOMIC`), then
+    each rank's `shard_adamw_ag` applies AdamW to its slice, stores the bf16 rows into every rank's working
+    copy and clears the slice. Sequential launches; the flag words are written ahead of time."""
+    world, R, D, Mtok = 2, 512, 256, 1024          # weight [R, D]; R / world rows per rank
+    rpr = R // world
+    torch.manual_seed(0)
+    W0 = torch.randn(R, D, device="cuda") * 0.1
+    x = [_rand(Mtok, R, 0.3, seed=71 + r) for r in range(world)]        # dX-like [tokens, R]
+    c = [_rand(Mtok, D, 0.3, seed=81 + r) for r in range(world)]        # cur-like [tokens, D]
+    grad = sum(x[r].float().t() @ c[r].float() for r in range(world))   # sum over the ranks' batches
+    acc = [torch.zeros(rpr, D, device="cuda") for _ in range(world)]    # each rank's gradient slice
+    ptrs = [t.data_ptr() for t in acc]
+    native.clear_status()
+    for r in range(world):
+        G.gemm(x[r], c[r], M=R, N=D, K=Mtok, a_mn=True, b_mn=True, flags=G.F_OUT_F32 | G.F_ATOMIC | G.F_PEER_RS,
+               out0=acc[r], peer_ptrs=ptrs, peer_rows=rpr, peer_rank=r)
+    torch.cuda.synchronize()
+    for r in range(world):
+        _check(acc[r], grad[r * rpr:(r + 1) * rpr], tol=1e-2)
+    master = [W0[r * rpr:(r + 1) * rpr].clone().contiguous() for r in range(world)]
+    m = [torch.zeros(rpr, D, device="cuda") for _ in range(world)]
+    v = [torch.zeros(rpr, D, device="cuda") for _ in range(world)]
+    shadow = [torch.zeros(R, D, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    epoch = 5
+    flags = [torch.full((4096,), 2 * epoch + 2, device="cuda", dtype=torch.int32) for _ in range(world)]
+    lr, b1, b2, eps, wd, scale = 1e-2, 0.9, 0.999, 1e-8, 0.1, 1.0 / world
+    g_kept = [a.clone() for a in acc]
+    for r in range(world):
+        native.ops.shard_adamw_ag([t.data_ptr() for t in flags], [t.data_ptr() for t in shadow], r, world, acc[r],
+                                  master[r], m[r], v[r], [0, rpr * D], [r * rpr * D], lr, b1, b2, eps, wd, 1, scale,
+                                  epoch, 8)
+    torch.cuda.synchronize()
+    assert native.status_code() == 0
+    for r in range(world):
+        g = g_kept[r] * scale
+        m_ref, v_ref = (1 - b1) * g, (1 - b2) * g * g
+        w_ref = W0[r * rpr:(r + 1) * rpr] * (1 - lr * wd) - lr * (m_ref / (1 - b1)) / ((v_ref / (1 - b2)).sqrt() + eps)
+        assert torch.allclose(master[r], w_ref, atol=1e-5, rtol=1e-4)
+        assert float(acc[r].abs().max()) == 0.0, "the gradient slice is cleared for the next step"
+        for sh in shadow:                                            # every rank's working copy got these rows
+            assert torch.allclose(sh[r * rpr:(r + 1) * rpr].float(), w_ref, atol=2e-3, rtol=1e-2)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("alibi", [True, False])
 def test_rownorm_attention_matches_reference(alibi):
