@@ -13,7 +13,8 @@ uniform random bytes from a per-rank seeded generator; weights are random-init.
 Rank 0 prints one JSON line. `value` is device-timed (CUDA events around exactly K steps, barrier +
 synchronize on both sides, max over ranks). `e2e` repeats the measurement through the public
 Trainer API with a pinned-host -> device copy of every step's batch and a device -> host read of
-every step's loss inside the timed region.
+every step's loss inside the timed region (the host reads step i's loss after it has queued step
+i + 1, so the device is not drained between steps).
 """
 from __future__ import annotations
 
@@ -311,15 +312,25 @@ def main() -> int:
     final_loss = float(loss.item())
 
     # ---------------- end-to-end region (pinned H2D of inputs + D2H of loss every step) ----------------
-    stage = torch.empty(B, T + 1, dtype=torch.int64, device=dev)
-    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    # Every step copies its own inputs from pinned host memory and its loss back to pinned host memory; the host
+    # reads the loss of step i once step i + 1 has been queued (a copy-done event per step), the way a training
+    # loop that logs every step without draining the device does. Two staging buffers, because the copy for
+    # step i + 1 is queued while step i may still be reading its inputs.
+    stages = [torch.empty(B, T + 1, dtype=torch.int64, device=dev) for _ in range(2)]
+    loss_host = torch.empty(2, dtype=torch.float32).pin_memory()
+    done = [torch.cuda.Event(), torch.cuda.Event()]
+    losses_read = []
 
     def e2e_step(i):
-        stage.copy_(host[i % n_batches], non_blocking=True)
-        l = trainer.train_step(stage[:, :-1], stage[:, 1:])
-        loss_host.copy_(l, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return float(loss_host)
+        st = stages[i & 1]
+        st.copy_(host[i % n_batches], non_blocking=True)
+        l = trainer.train_step(st[:, :-1], st[:, 1:])
+        loss_host[i & 1:(i & 1) + 1].copy_(l.detach().reshape(1), non_blocking=True)
+        done[i & 1].record()
+
+    def read_loss(i):
+        done[i & 1].synchronize()
+        losses_read.append(float(loss_host[i & 1]))
 
     for i in range(2):
         e2e_step(i)
@@ -329,9 +340,13 @@ def main() -> int:
     e0.record()
     for i in range(K):
         e2e_step(W + i)
+        if i > 0:
+            read_loss(W + i - 1)
+    read_loss(W + K - 1)
     e1.record()
     torch.cuda.synchronize()
     dist_utils.barrier()
+    assert len(losses_read) == K and all(v == v for v in losses_read)
     ms_e2e = dist_utils.max_over_ranks(e0.elapsed_time(e1), dev)
 
     tokens = B * T * data_world * K
@@ -357,7 +372,7 @@ def main() -> int:
                                                      if getattr(wrapper, "state", None) is not None else None)},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
-                    "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},
+                    "loss_read": "every step, one step behind (pinned copy + event)", "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
             "final_loss": final_loss,
             "kernel_status": status,
