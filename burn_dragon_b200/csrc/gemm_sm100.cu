@@ -1,5 +1,6 @@
 // Host side of the tcgen05 GEMM: builds the TMA descriptors for both operands and launches the
 // persistent kernel instantiation that matches (operand majors, epilogue).
+#include <cstdlib>
 #include "bdh_kernels.h"
 #include "gemm_sm100.cuh"
 #include "device_once.h"
@@ -120,6 +121,13 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   g.causal_tiles = d->causal_tiles;
   g.causal_k = d->causal_k;
   g.tile_shift = 0;
+  {
+    // BDH_GEMM_L2_HINTS=1 launches with the L2 eviction hints (read once per process). Off by default: measured
+    // on the layer kernels at 8 sequences, the hints left the encoder unchanged (0.177 ms) and slowed the gate
+    // kernels (y-gate 0.134 -> 0.150 ms, gate backward 0.195 -> 0.217 ms); the training step did not move.
+    static const int hints = [] { const char* v = getenv("BDH_GEMM_L2_HINTS"); return (v && v[0] == '1') ? 1 : 0; }();
+    g.l2_hints = hints;
+  }
   g.status = d->status;
   EpiParams& e = g.epi;
   e.out0 = d->out0; e.out1 = d->out1; e.in0 = d->in0; e.in1 = d->in1;

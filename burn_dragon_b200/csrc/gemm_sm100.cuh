@@ -116,6 +116,9 @@ struct GemmArgs {
   int causal_tiles;  // 0: all tiles; 1: only tiles that touch s < t (n0 <= m0+BM-1); 2: only tiles with s > t
   int causal_k;      // 1: contract only k < m0 + BM; 2: only k >= m0 (m0 = first row of the tile); the K
                      // range is never empty as long as K > the last tile's first row
+  int l2_hints;      // 1: the staged epilogue's output stores and streamed aux loads carry L2 evict_first, the
+                     // operand loads of the small-operand epilogues (EPI 1, 2, 4) evict_last: the [tokens, neurons]
+                     // streams then pass through L2 without pushing the weights out
   int tile_shift;    // tiles are visited in the order (t + tile_shift) mod total (reduce-scatter epilogue:
                      // each rank starts at another owner's rows so that no GPU is everybody's target)
   EpiParams epi;
@@ -862,6 +865,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       uint32_t armed = 0, armed_parity = 0;  // per-stage: a load was issued / with which phase
       int ready_block = -1;                  // last gathered row block known to be complete
+      const uint64_t keep_policy = l2_policy_evict_last();
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
         const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
@@ -894,6 +898,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           const int kc = kb * GEMM_BK;
+          if constexpr (A_MN == 0 && B_MN == 0 && (EPI == EPI_RELU || EPI == EPI_RELU_GATE || EPI == EPI_GATE_BWD)) {
+            if (g.l2_hints) {
+              // both operands are small and re-read by every tile: keep them in L2
+              tma_load_2d_hint(sa, &tmA, &full_bar[stage], a_k + kc, a_mn, keep_policy);
+              tma_load_2d_hint(sb, &tmB, &full_bar[stage], b_k + kc, b_mn, keep_policy);
+              if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1;
+              }
+              continue;
+            }
+          }
           if constexpr (A_MN == 0) {
             tma_load_2d(sa, &tmA, &full_bar[stage], a_k + kc, a_mn);
           } else {
@@ -1035,6 +1051,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint64_t* ibar = in_bar + 2 * ew;
       const uint32_t in_bytes = ((io & IO_IN0) ? EPI_BOX_BYTES : 0) + ((io & IO_IN1) ? EPI_BOX_BYTES : 0);
       const bool has_in = in_bytes != 0;
+      const uint64_t stream_policy = l2_policy_evict_first();
       uint32_t gchunk = 0;   // running chunk counter of this warp: buffer = gchunk & 1, parity = (gchunk >> 1) & 1
       uint32_t issued = 0;   // chunks whose input loads were issued
 
@@ -1047,12 +1064,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int trow = ((EPI == EPI_DQ_BWD) ? row : (tc.m0 + q * 32)) % e.T;
         const int tcol = (tc.n0 + (cbase + c) * 32) % e.n_per_head;
         mbar_arrive_expect_tx(&ibar[buf], in_bytes);
-        if (io & IO_IN0)
-          tma_load_2d(in_box + (0 * 2 + buf) * EPI_BOX_BYTES, &em.in0, &ibar[buf],
-                      (EPI == EPI_RELU) ? tcol : col, (EPI == EPI_RELU) ? trow : row);
-        if (io & IO_IN1)
-          tma_load_2d(in_box + (1 * 2 + buf) * EPI_BOX_BYTES, &em.in1, &ibar[buf],
-                      (EPI == EPI_DQ_BWD) ? tcol : col, (EPI == EPI_DQ_BWD) ? trow : row);
+        // (the rotary table - in0 of EPI_RELU, in1 of EPI_DQ_BWD - is re-read by every tile; the other aux
+        // inputs are [tokens, neurons] streams)
+        if (io & IO_IN0) {
+          if (g.l2_hints && EPI != EPI_RELU)
+            tma_load_2d_hint(in_box + (0 * 2 + buf) * EPI_BOX_BYTES, &em.in0, &ibar[buf], col, row, stream_policy);
+          else
+            tma_load_2d(in_box + (0 * 2 + buf) * EPI_BOX_BYTES, &em.in0, &ibar[buf],
+                        (EPI == EPI_RELU) ? tcol : col, (EPI == EPI_RELU) ? trow : row);
+        }
+        if (io & IO_IN1) {
+          if (g.l2_hints && EPI != EPI_DQ_BWD)
+            tma_load_2d_hint(in_box + (1 * 2 + buf) * EPI_BOX_BYTES, &em.in1, &ibar[buf], col, row, stream_policy);
+          else
+            tma_load_2d(in_box + (1 * 2 + buf) * EPI_BOX_BYTES, &em.in1, &ibar[buf],
+                        (EPI == EPI_DQ_BWD) ? tcol : col, (EPI == EPI_DQ_BWD) ? trow : row);
+        }
       };
 
       int t = blockIdx.x;
@@ -1128,14 +1155,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (io & IO_OUT0)
-              tma_store_2d(&em.out0, out_box + (0 * OB + ob) * EPI_BOX_BYTES, col0 + c * 32, row0);
-            if (io & IO_OUT1)
-              tma_store_2d(&em.out1, out_box + (1 * OB + ob) * EPI_BOX_BYTES, col1 + c * 32, row0);
-            if constexpr (EPI == EPI_RELU) {
-              if (io & IO_OUT2)
-                tma_store_2d(&em.out1, out_box + (2 * OB + ob) * EPI_BOX_BYTES,
-                             col1 + c * 32 + static_cast<int>(e.o1_imag), row0);
+            if (g.l2_hints) {
+              if (io & IO_OUT0)
+                tma_store_2d_hint(&em.out0, out_box + (0 * OB + ob) * EPI_BOX_BYTES, col0 + c * 32, row0, stream_policy);
+              if (io & IO_OUT1)
+                tma_store_2d_hint(&em.out1, out_box + (1 * OB + ob) * EPI_BOX_BYTES, col1 + c * 32, row0, stream_policy);
+              if constexpr (EPI == EPI_RELU) {
+                if (io & IO_OUT2)
+                  tma_store_2d_hint(&em.out1, out_box + (2 * OB + ob) * EPI_BOX_BYTES,
+                                    col1 + c * 32 + static_cast<int>(e.o1_imag), row0, stream_policy);
+              }
+            } else {
+              if (io & IO_OUT0)
+                tma_store_2d(&em.out0, out_box + (0 * OB + ob) * EPI_BOX_BYTES, col0 + c * 32, row0);
+              if (io & IO_OUT1)
+                tma_store_2d(&em.out1, out_box + (1 * OB + ob) * EPI_BOX_BYTES, col1 + c * 32, row0);
+              if constexpr (EPI == EPI_RELU) {
+                if (io & IO_OUT2)
+                  tma_store_2d(&em.out1, out_box + (2 * OB + ob) * EPI_BOX_BYTES,
+                               col1 + c * 32 + static_cast<int>(e.o1_imag), row0);
+              }
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
