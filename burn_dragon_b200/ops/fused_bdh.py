@@ -23,6 +23,7 @@ import torch
 from . import dual_gemm as DG
 from . import gemm as G
 from . import native
+from ..utils import compressed_pool as _CP
 from ..utils import profiling as prof
 
 ops = native.ops
@@ -195,6 +196,10 @@ def _split_k(tiles: int, K: int, dev) -> int:
 
 
 def _bf16(rows, cols, dev):
+    # (large activation streams can live in compressible memory: utils/compressed_pool.py, off by default)
+    if _CP.enabled() and torch.device(dev).type == "cuda":
+        with _CP.allocate(rows * cols * 2):
+            return torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
     return torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
 
 
