@@ -63,8 +63,11 @@ class SymmetricBuffer:
     def _allocate(self, numel: int, dtype: torch.dtype, device):
         """-> (tensor in symmetric memory, every rank's pointer to it, multicast pointer or 0, rank, world)."""
         import torch.distributed._symmetric_memory as symm_mem
+        import warnings
         try:
-            symm_mem.enable_symm_mem_for_group(self.group.group_name)
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore", FutureWarning)      # (deprecated where it is no longer needed)
+                symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:  # noqa: BLE001 - newer torch versions do not need (or have) this call
             pass
         raw = symm_mem.empty(numel, dtype=dtype, device=device)
