@@ -132,6 +132,11 @@ int bdh_block_out_parts(const void* cur_bf16, const float* part_f32, int parts, 
 int bdh_block_out_bwd(const void* cur_bf16, const void* mlp_bf16, const float* dout_f32,
                       float* dcur_f32, void* dmlp_bf16, long long rows, int D, cudaStream_t s);
 
+// State scans of the chunk-state attention (rowwise.cu): seg fp32 [B, J, H, per], start / total fp32 [B, H, per]
+// (either may be null), decay [H] or null, out16 bf16 [B, J, H, per]. backward = 0: out16[j] = state before segment j,
+// total = state after the last; backward = 1: the reverse recurrence over the gradients (see the kernel).
+int bdh_state_scan(const float* seg, const float* start, const float* decay, void* out16_bf16, float* total,
+                   long long per, int J, int H, long long n_bh, int backward, cudaStream_t s);
 // PoPE query rebuilt from the stored x: q_bf16 [M, H*2N] (per head [real N | imag N]) = softplus(x) * (cos, sin).
 int bdh_pope_rotate(const void* x_bf16, const float* freqs, void* q_bf16, long long M, int H, int N, int T, int pos0,
                     cudaStream_t s);

@@ -506,6 +506,28 @@ void pope_bwd(const Tensor& dq, const Tensor& x, const Tensor& dxg, const Tensor
                         pos0, cur_stream()), "pope_bwd");
 }
 
+void state_scan(const Tensor& seg, const optional<Tensor>& start, const optional<Tensor>& decay, Tensor& out16,
+                c10::optional<Tensor> total, int64_t J, int64_t H, bool backward) {
+  c10::cuda::CUDAGuard guard(seg.device());
+  TORCH_CHECK(seg.is_cuda() && seg.is_contiguous() && seg.scalar_type() == at::kFloat, "seg: contiguous fp32");
+  TORCH_CHECK(out16.is_cuda() && out16.is_contiguous() && out16.scalar_type() == at::kBFloat16 && out16.numel() == seg.numel());
+  TORCH_CHECK(J >= 1 && H >= 1 && seg.numel() % (J * H) == 0);
+  const int64_t D = seg.size(-1), rows = seg.numel() / D;              // [B*J*H*Np, D] or any view of it
+  (void)rows;
+  // per = N' * D elements per (b, j, h): the caller passes seg as [B*J, H, Np, D]
+  TORCH_CHECK(seg.dim() == 4 && seg.size(1) == H && seg.size(0) % J == 0, "seg: [B*J, H, Np, D]");
+  const int64_t per = seg.size(2) * seg.size(3), n_bh = seg.size(0) / J * H;
+  for (const optional<Tensor>* t : {&start, static_cast<const optional<Tensor>*>(&total)})
+    if (t->has_value())
+      TORCH_CHECK((*t)->is_cuda() && (*t)->is_contiguous() && (*t)->scalar_type() == at::kFloat && (*t)->numel() == n_bh * per);
+  if (decay.has_value())
+    TORCH_CHECK(decay->is_cuda() && decay->is_contiguous() && decay->scalar_type() == at::kFloat && decay->numel() == H);
+  check_rc(bdh_state_scan(seg.data_ptr<float>(), start.has_value() ? start->data_ptr<float>() : nullptr,
+                          decay.has_value() ? decay->data_ptr<float>() : nullptr, out16.data_ptr(),
+                          total.has_value() ? total->data_ptr<float>() : nullptr, per, J, H, n_bh, backward ? 1 : 0,
+                          cur_stream()), "state_scan");
+}
+
 void pope_rotate(const Tensor& x, const Tensor& freqs, Tensor& q, int64_t H, int64_t T, int64_t pos0) {
   c10::cuda::CUDAGuard guard(x.device());
   for (const Tensor* t : std::initializer_list<const Tensor*>{&x, &q})
@@ -570,6 +592,7 @@ TORCH_LIBRARY(bdh, m) {
   m.def("wait_timeout_probe(Tensor flag, int value, int limit_ns) -> ()");
   m.def("pope_bwd(Tensor dq, Tensor x, Tensor dxg, Tensor freqs, Tensor(a!) dx, int H, int T, int pos0) -> ()");
   m.def("pope_rotate(Tensor x, Tensor freqs, Tensor(a!) q, int H, int T, int pos0) -> ()");
+  m.def("state_scan(Tensor seg, Tensor? start, Tensor? decay, Tensor(a!) out16, Tensor(b!)? total, int J, int H, bool backward) -> ()");
   m.def("rank_barrier(Tensor anchor, int[] flag_ptrs, int rank, int world, int epoch) -> ()");
   m.def("graph_spmm_relu(Tensor x, Tensor w, Tensor ell, Tensor(a!) y, float theta) -> ()");
   m.def("ssd_decode_step(Tensor xw, Tensor loga, Tensor Bm, Tensor Cm, Tensor(a!) h, Tensor(b!) y) -> ()");
@@ -615,6 +638,7 @@ TORCH_LIBRARY_IMPL(bdh, CUDA, m) {
   m.impl("wait_timeout_probe", &wait_timeout_probe);
   m.impl("pope_bwd", &pope_bwd);
   m.impl("pope_rotate", &pope_rotate);
+  m.impl("state_scan", &state_scan);
   m.impl("rank_barrier", &rank_barrier);
   m.impl("graph_spmm_relu", &graph_spmm_relu);
   m.impl("ssd_decode_step", &ssd_decode_step);

@@ -676,6 +676,57 @@ extern "C" int bdh_pope_rotate(const void* x, const float* freqs, void* q, long 
   return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
 }
 
+// ---- state scans of the chunk-state attention -------------------------------------------------------------
+// The [N', D] states of the J segments of a sequence are independent per element, so the hand-off is an
+// elementwise recurrence over j. seg / d_rin: fp32 [B, J, H, per] (per = N' * D); start / init / total: fp32
+// [B, H, per]; decay: g^C per head (nullptr: 1). One thread owns four consecutive elements of one (b, h).
+//   forward : run = start; for j = 0..J-1: out16[j] = run; run = run * g + seg[j];          total = run
+//   backward: acc = init;  for j = J-1..0: out16[j] = acc; acc = d_rin[j] + acc * g  (the last update is unused)
+// out16 is bf16: the state every segment starts from (forward), the gradient of every segment's own state
+// (backward) - both are GEMM operands next.
+namespace bdh {
+template <bool BWD>
+__global__ void __launch_bounds__(256)
+state_scan_kernel(const float* __restrict__ seg, const float* __restrict__ start, const float* __restrict__ decay,
+                  __nv_bfloat16* __restrict__ out16, float* __restrict__ total, long long per4, int J, int H,
+                  long long n_bh) {
+  const long long n = n_bh * per4;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long bh = i / per4, e = i - bh * per4;
+    const long long b = bh / H;
+    const int h = static_cast<int>(bh - b * H);
+    const float g = decay ? __ldg(decay + h) : 1.f;
+    float4 run = start ? reinterpret_cast<const float4*>(start)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int jj = 0; jj < J; ++jj) {
+      const int j = BWD ? J - 1 - jj : jj;
+      const long long at = ((b * J + j) * H + h) * per4 + e;
+      uint2 u;
+      u.x = pack_bf16x2(run.x, run.y);
+      u.y = pack_bf16x2(run.z, run.w);
+      reinterpret_cast<uint2*>(out16)[at] = u;
+      if (BWD && j == 0) break;
+      const float4 s = __ldcs(reinterpret_cast<const float4*>(seg) + at);
+      run.x = run.x * g + s.x; run.y = run.y * g + s.y; run.z = run.z * g + s.z; run.w = run.w * g + s.w;
+    }
+    if (!BWD && total) reinterpret_cast<float4*>(total)[i] = run;
+  }
+}
+}  // namespace bdh
+
+extern "C" int bdh_state_scan(const float* seg, const float* start, const float* decay, void* out16, float* total,
+                              long long per, int J, int H, long long n_bh, int backward, cudaStream_t s) {
+  if (per <= 0 || (per % 4) || J < 1 || H < 1 || n_bh < 1) return BDH_ERR_ARGUMENT;
+  const long long n = n_bh * (per / 4);
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  if (backward)
+    bdh::state_scan_kernel<true><<<static_cast<int>(blocks), 256, 0, s>>>(seg, start, decay, (bf16*)out16, total, per / 4, J, H, n_bh);
+  else
+    bdh::state_scan_kernel<false><<<static_cast<int>(blocks), 256, 0, s>>>(seg, start, decay, (bf16*)out16, total, per / 4, J, H, n_bh);
+  return cudaGetLastError() == cudaSuccess ? BDH_OK : BDH_ERR_LAUNCH;
+}
+
 // ---- L1 row normalisation of strictly causal scores (the `forward_fast` attention) -------------
 // S is bf16 [rows, T] with rows = (batch, head, t); only columns s < t of row t carry scores
 // (reference: src/model/attention.rs:142-175: tril(-1), then S / (sum_j |S_ij| + 1e-6)).

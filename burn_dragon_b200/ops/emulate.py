@@ -92,6 +92,22 @@ class TorchOps:
             dlogits.copy_(g * grad_scale)
 
     @staticmethod
+    def state_scan(seg, start, decay, out16, total, J, H, backward):
+        BJ, _, Np, D = seg.shape
+        B = BJ // J
+        s5, o5 = seg.view(B, J, H, Np, D), out16.view(B, J, H, Np, D)
+        g = decay.float().view(1, H, 1, 1) if decay is not None else 1.0
+        run = start.float().view(B, H, Np, D).clone() if start is not None else torch.zeros(B, H, Np, D, device=seg.device)
+        order = range(J - 1, -1, -1) if backward else range(J)
+        for j in order:
+            o5[:, j] = run.to(out16.dtype)
+            if backward and j == 0:
+                break
+            run = run * g + s5[:, j]
+        if not backward and total is not None:
+            total.view(B, H, Np, D).copy_(run)
+
+    @staticmethod
     def pope_rotate(x, freqs, q, H, T, pos0):
         M, HN = x.shape
         N = HN // H

@@ -234,62 +234,60 @@ def _scan_forward(d: "_Dims", seg: Optional[torch.Tensor], rho0: Optional[torch.
     seg: fp32 [B*J, H, N', D], what every segment adds (None when nothing needs it); rho0: the state before
     this call's first token. Returns (rin, total): rin bf16 [B*J*H*N', D], the state every segment starts
     from (None when all of them start from zero), and the fp32 state after the last token (None unless
-    wanted)."""
+    wanted). The recurrence over the segments is one elementwise kernel (`state_scan`)."""
     B, J, H, Np, D = d.B, d.J, d.H, d.Np, d.D
     gC = d.decay(d.C)
-    step = (lambda run: run) if gC is None else (lambda run: run * gC)
-    start = rho0.float() if rho0 is not None else None
-    segv = seg.view(B, J, H, Np, D) if seg is not None else None
+    gvec = gC.reshape(H).contiguous() if gC is not None else None
+    start = rho0.float().contiguous() if rho0 is not None else None
     total = None
     if d.cp is not None:
-        run = None
-        for j in range(J):
-            run = segv[:, j] if run is None else step(run) + segv[:, j]
+        # this rank's segments alone (from zero), then the hand-off between the ranks
+        scratch = torch.empty(B * J, H, Np, D, device=d.device, dtype=torch.bfloat16)
+        local = torch.empty(B, H, Np, D, device=d.device, dtype=torch.float32)
+        ops.state_scan(seg, None, gvec, scratch, local, J, H, False)
+        del scratch
         gT = d.decay(d.T)
-        start, total = d.cp.scan(run, start, gT if gT is not None else 1.0)
-    if J == 1 and start is None:
-        rin = None
-    else:
-        rin = torch.empty(B, J, H, Np, D, device=d.device, dtype=torch.bfloat16)
-    run = start
-    for j in range(J):
-        if rin is not None:
-            rin[:, j].zero_() if run is None else rin[:, j].copy_(run)
-        if j + 1 < J or (want_total and d.cp is None):
-            run = segv[:, j] if run is None else step(run) + segv[:, j]
+        start, total = d.cp.scan(local, start, gT if gT is not None else 1.0)
+        if start is not None:
+            start = start.float().contiguous()
+    if seg is None or (J == 1 and start is None):
+        if seg is not None and want_total and d.cp is None:
+            total = seg.view(B, H, Np, D)             # one segment from an empty state: what it adds is the state
+        return None, total
+    rin = torch.empty(B * J, H, Np, D, device=d.device, dtype=torch.bfloat16)
+    out_total = None
     if want_total and d.cp is None:
-        total = run
-    return (rin.view(B * J * H * Np, D) if rin is not None else None), total
+        out_total = total = torch.empty(B, H, Np, D, device=d.device, dtype=torch.float32)
+    ops.state_scan(seg, start, gvec, rin, out_total, J, H, False)
+    return rin.view(B * J * H * Np, D), total
 
 
 def _scan_backward(d: "_Dims", d_rin: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """Reverse of `_scan_forward`: d_rin fp32 [B*J*H*N', D] (gradient of every segment's starting state, None
-    when no segment had one) -> gradient of every segment's own state, fp32 [B*J, H, N', D] (None when it is
+    when no segment had one) -> gradient of every segment's own state, bf16 [B*J*H*N', D] (None when it is
     exactly zero: a single segment that nobody continues from)."""
     B, J, H, Np, D = d.B, d.J, d.H, d.Np, d.D
     gC = d.decay(d.C)
+    gvec = gC.reshape(H).contiguous() if gC is not None else None
     step = (lambda acc: acc) if gC is None else (lambda acc: acc * gC)
-    drv = d_rin.view(B, J, H, Np, D) if d_rin is not None else None
     acc = None
     if d.cp is not None:
         # what the later ranks' starting states pass back to this rank's total: they depend on this rank only
         # through its total state, and on it with the weights of the forward scan
         d_start = None
-        for j in reversed(range(J)):
-            if drv is not None:
+        if d_rin is not None:
+            drv = d_rin.view(B, J, H, Np, D)
+            for j in reversed(range(J)):
                 d_start = drv[:, j] if d_start is None else drv[:, j] + step(d_start)
         if d_start is None:
             d_start = torch.zeros(B, H, Np, D, device=d.device, dtype=torch.float32)
         gT = d.decay(d.T)
-        acc = d.cp.scan_backward(d_start.contiguous(), gT if gT is not None else 1.0)
-    if J == 1 and acc is None:
-        return None
-    dseg = torch.empty(B, J, H, Np, D, device=d.device, dtype=torch.float32)
-    for j in reversed(range(J)):
-        dseg[:, j].zero_() if acc is None else dseg[:, j].copy_(acc)
-        if j > 0:
-            acc = drv[:, j] if acc is None else drv[:, j] + step(acc)
-    return dseg.view(B * J, H, Np, D)
+        acc = d.cp.scan_backward(d_start.contiguous(), gT if gT is not None else 1.0).float().contiguous()
+    if J == 1:
+        return acc.to(torch.bfloat16).view(B * H * Np, D) if acc is not None else None
+    dseg16 = torch.empty(B * J, H, Np, D, device=d.device, dtype=torch.bfloat16)
+    ops.state_scan(d_rin.view(B * J, H, Np, D), acc, gvec, dseg16, None, J, H, True)
+    return dseg16.view(B * J * H * Np, D)
 
 
 def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], want_rho: bool,
@@ -505,7 +503,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
         if rin is not None:
             xs.append(da_w); rs.append(rin)
         if dseg is not None:
-            dseg16 = dseg.view(Bs * H * Np, D).to(torch.bfloat16)
+            dseg16 = dseg                        # (bf16 [Bs*H*N', D])
             del dseg
             # through the segment state to its values: dv_s += g^(C-s) sum_h q_s . d seg_h
             G.gemm(q, dseg16, M=C, N=D, K=Np, b_mn=True, nz=(H, Bs), a_off=(0, C, Np, 0), b_off=(0, 0, Np, H * Np),

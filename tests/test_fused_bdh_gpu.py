@@ -338,3 +338,26 @@ def test_pope_query_rebuilt_in_the_backward_pass():
     assert m._dropped_q_layers == 2
     for n, p in m.named_parameters():
         assert _rel(p.grad, g0[n]) < 2e-2, (n, _rel(p.grad, g0[n]))
+
+
+@pytest.mark.parametrize("backward", [False, True])
+@pytest.mark.parametrize("decay", [False, True])
+def test_state_scan_kernel_matches_its_statement(backward, decay):
+    """The elementwise recurrence over the segments (`state_scan`) against the torch statement of the same
+    contract (the emulated op), with and without a starting value and per-head decay."""
+    from burn_dragon_b200.ops import emulate
+    torch.manual_seed(0)
+    B, J, H, Np, D = 2, 5, 3, 96, 64
+    seg = torch.randn(B * J, H, Np, D, device="cuda")
+    start = torch.randn(B, H, Np, D, device="cuda")
+    g = torch.tensor([0.9, 0.5, 0.99], device="cuda") if decay else None
+    for st in (None, start):
+        got16 = torch.zeros(B * J, H, Np, D, device="cuda", dtype=torch.bfloat16)
+        got_t = None if backward else torch.zeros(B, H, Np, D, device="cuda")
+        native.ops.state_scan(seg, st, g, got16, got_t, J, H, backward)
+        want16 = torch.zeros_like(got16)
+        want_t = None if backward else torch.zeros_like(got_t)
+        emulate.TorchOps.state_scan(seg, st, g, want16, want_t, J, H, backward)
+        assert _rel(got16, want16) < 1e-2
+        if not backward:
+            assert _rel(got_t, want_t) < 1e-5
