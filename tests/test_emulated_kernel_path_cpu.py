@@ -508,3 +508,35 @@ def test_pope_layers_that_drop_their_rotated_query_give_the_same_gradients():
     assert l0.item() == l1.item()
     for n, p in m.named_parameters():
         assert _rel(p.grad, g0[n]) < 5e-3, (n, _rel(p.grad, g0[n]))
+
+
+def test_memory_plan_picks_the_cheapest_mix_that_fits(monkeypatch):
+    """`memory_plan` with a faked device memory: the large PoPE configuration (8 sequences of 2048 tokens) on a
+    180 GB device keeps every layer and lets a few rebuild their query; with less memory it starts to recompute
+    layers; RoPE models and explicit settings are left alone."""
+    import types
+    cfg = BDHConfig(n_layer=8, n_embd=512, n_head=8, n_latent_per_head=16384, vocab_size=256, dropout=0.0,
+                    rotary_embedding="pope")
+    m = types.SimpleNamespace(config=cfg, training=True, encoder=torch.zeros(1), freqs=torch.zeros(16384), slopes=None,
+                              recompute="auto")
+    d = fused_bdh._Dims(m, 8, 2048)
+    per, work = fused_bdh.layer_activation_bytes(d), fused_bdh.backward_working_bytes(d)
+    assert 17e9 < per < 19e9 and 20e9 < work < 25e9
+
+    def with_free(gb):
+        monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+        monkeypatch.setattr(torch.cuda, "mem_get_info", lambda: (int(gb * 1e9), int(192e9)))
+        monkeypatch.setattr(torch.cuda, "memory_reserved", lambda: 0)
+        monkeypatch.setattr(torch.cuda, "memory_allocated", lambda: 0)
+        return fused_bdh.memory_plan(m, d)
+
+    r, k = with_free(188)
+    assert r == 0 and 3 <= k <= 6                      # nothing recomputed, some layers rebuild q
+    r2, k2 = with_free(90)
+    assert r2 > 0 and r2 + k2 <= 8                     # less memory: some layers are recomputed as well
+    assert r2 * 5.4 + k2 <= fused_bdh.recompute_count(m, d) * 5.4 + 1e-9      # never worse than recompute alone
+    m.drop_rotated = 0
+    assert with_free(188) == (fused_bdh.recompute_count(m, d), 0)
+    m.drop_rotated = None
+    m.recompute = 3
+    assert with_free(188) == (3, 0)                    # an explicit recompute count is taken as given
