@@ -62,6 +62,8 @@ typedef struct {
   // peer loads and starts a row block's tiles once it has arrived; gather_arrived holds M / 128 zeroed counters.
   // K-major A, one problem (nz0 = nz1 = 1). The caller orders the launch after every rank's writes (a rank
   // barrier before) and keeps the rows unchanged until every rank's launch is over (a rank barrier after).
+  // Causal epilogue only: [ceil(M/128), ceil(N/bn)] bytes, non-zero = skip this output tile (nullptr: none).
+  const unsigned char* tile_skip;
   const long long* gather_src;
   int gather_world, gather_rank;
   long long gather_rows;

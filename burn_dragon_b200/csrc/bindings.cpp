@@ -46,7 +46,8 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
           int64_t n_per_head, const optional<Tensor>& freqs, const optional<Tensor>& slopes,
           int64_t causal_tiles, int64_t causal_k, int64_t bn, int64_t max_ctas, bool tma_epilogue, int64_t mc_out, double drop_p, int64_t drop_seed,
           at::IntArrayRef peer_ptrs, int64_t peer_rows, int64_t peer_rank, const optional<Tensor>& bias,
-          at::IntArrayRef gather_ptrs, int64_t gather_rows, int64_t gather_rank, const optional<Tensor>& gather_arrived) {
+          at::IntArrayRef gather_ptrs, int64_t gather_rows, int64_t gather_rank, const optional<Tensor>& gather_arrived,
+          const optional<Tensor>& tile_skip) {
   c10::cuda::CUDAGuard guard(a.device());
   BdhMat A = as_mat(a, "a"), B = as_mat(b, "b");
   TORCH_CHECK(a_off.size() == 4 && b_off.size() == 4 && c_off.size() == 4 && o1_off.size() == 3,
@@ -88,6 +89,13 @@ void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t M, int
     d.gather_src = gsrc; d.gather_world = static_cast<int>(gather_ptrs.size()); d.gather_rows = gather_rows;
     d.gather_rank = static_cast<int>(gather_rank);
     d.gather_arrived = reinterpret_cast<unsigned*>(gather_arrived->data_ptr<int>());
+  }
+  if (tile_skip.has_value()) {
+    const int64_t bn_ = bn == 128 ? 128 : 256;
+    TORCH_CHECK(tile_skip->is_cuda() && tile_skip->is_contiguous() && tile_skip->scalar_type() == at::kByte &&
+                tile_skip->numel() == ((M + 127) / 128) * ((N + bn_ - 1) / bn_) && epi == 3,
+                "tile_skip: uint8 [ceil(M/128), ceil(N/bn)], causal epilogue only");
+    d.tile_skip = tile_skip->data_ptr<unsigned char>();
   }
   check_rc(bdh_gemm_bf16(&A, a_mn, &B, b_mn, &d, cur_stream()), "gemm_bf16");
 }
@@ -554,7 +562,7 @@ TORCH_LIBRARY(bdh, m) {
         "int[] b_off, int epi, int flags, Tensor(a!)? out0, Tensor(b!)? out1, Tensor? in0, Tensor? in1, "
         "int[] c_off, int[] o1_off, float alpha, float theta, int T, int pos0, int n_per_head, "
         "Tensor? freqs, Tensor? slopes, int causal_tiles, int causal_k, int bn, int max_ctas, bool tma_epilogue, int mc_out, float drop_p, int drop_seed, int[] peer_ptrs, int peer_rows, int peer_rank, Tensor? bias, "
-        "int[] gather_ptrs, int gather_rows, int gather_rank, Tensor(c!)? gather_arrived) -> ()");
+        "int[] gather_ptrs, int gather_rows, int gather_rank, Tensor(c!)? gather_arrived, Tensor? tile_skip) -> ()");
   m.def("dual_gemm(Tensor a1, Tensor b1, bool b1_mn, Tensor b2, Tensor(a!) p, int M, int H, int n_per_head, int K1, int N2, "
         "int T, int epi, int flags, int group_per_head, int a1_b, int a1_h, int b1_b, Tensor? in0, Tensor? in1, "
         "Tensor(b!)? out1, float alpha, float theta, int pos0, float drop_p, int drop_seed, Tensor(c!) partials, "

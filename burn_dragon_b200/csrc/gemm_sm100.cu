@@ -121,6 +121,7 @@ extern "C" int bdh_gemm_bf16(const BdhMat* A, int a_mn, const BdhMat* B, int b_m
   g.causal_tiles = d->causal_tiles;
   g.causal_k = d->causal_k;
   g.tile_shift = 0;
+  g.tile_skip = (d->epi == EPI_CAUSAL) ? d->tile_skip : nullptr;
   {
     // BDH_GEMM_L2_HINTS=1 launches with the L2 eviction hints (read once per process). Off by default: measured
     // on the layer kernels at 8 sequences, the hints left the encoder unchanged (0.177 ms) and slowed the gate

@@ -116,6 +116,8 @@ struct GemmArgs {
   int causal_tiles;  // 0: all tiles; 1: only tiles that touch s < t (n0 <= m0+BM-1); 2: only tiles with s > t
   int causal_k;      // 1: contract only k < m0 + BM; 2: only k >= m0 (m0 = first row of the tile); the K
                      // range is never empty as long as K > the last tile's first row
+  const unsigned char* tile_skip;   // EPI_CAUSAL: [tiles_m, tiles_n] bytes, non-zero = this output tile is not computed
+                                    // and not written (an inactive pair of time blocks); nullptr: every tile runs
   int l2_hints;      // 1: the staged epilogue's output stores and streamed aux loads carry L2 evict_first, the
                      // operand loads of the small-operand epilogues (EPI 1, 2, 4) evict_last: the [tokens, neurons]
                      // streams then pass through L2 without pushing the weights out
@@ -771,6 +773,14 @@ struct TileWalker {
   }
 };
 
+// Tile predicate of the causal epilogue (all three roles skip the same tiles, so the barrier phases stay in step).
+template <int BN>
+__device__ __forceinline__ bool tile_skipped(const GemmArgs& g, const TileCoord& tc) {
+  if (!g.tile_skip) return false;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  return g.tile_skip[(tc.m0 / GEMM_BM) * tiles_n + tc.n0 / BN] != 0;
+}
+
 // Boxes of staging per epilogue warp: double-buffered inputs and outputs.
 __host__ __device__ constexpr int epi_num_in(int epi) {
   return (epi == EPI_RELU_GATE || epi == EPI_RELU) ? 1 : (epi == EPI_GATE_BWD || epi == EPI_DQ_BWD) ? 2 : 0;
@@ -868,6 +878,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t keep_policy = l2_policy_evict_last();
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
+        if constexpr (EPI == EPI_CAUSAL) {
+          if (tile_skipped<BN>(g, tc)) continue;
+        }
         const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
         const int nkb = (k_end + GEMM_BK - 1) / GEMM_BK;
         const int kb0 = (g.causal_k == 2) ? min(nkb, tc.m0 / GEMM_BK) : 0;
@@ -950,6 +963,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < walker.total && ok; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
+        if constexpr (EPI == EPI_CAUSAL) {
+          if (tile_skipped<BN>(g, tc)) continue;
+        }
         const int k_end = (g.causal_k == 1) ? min(g.K, tc.m0 + GEMM_BM) : g.K;
         const int nkb = (k_end + GEMM_BK - 1) / GEMM_BK;
         const int kb0 = (g.causal_k == 2) ? min(nkb, tc.m0 / GEMM_BK) : 0;
@@ -1003,6 +1019,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if constexpr (!TMA_EPI) {
       for (int t = blockIdx.x; t < walker.total; t += gridDim.x) {
         const TileCoord tc = walker.decode(t);
+        if constexpr (EPI == EPI_CAUSAL) {
+          if (tile_skipped<BN>(g, tc)) continue;
+        }
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, g.status, STATUS_TIMEOUT_TMEM_FULL))
           break;
         tc_fence_after();
@@ -1094,6 +1113,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int t_next = t + gridDim.x;
         TileCoord tc_next{0, 0, 0, 0};
         if (t_next < walker.total) tc_next = walker.decode(t_next);
+        if constexpr (EPI == EPI_CAUSAL) {
+          // (this epilogue has no auxiliary inputs, so nothing was prefetched for a skipped tile)
+          if (tile_skipped<BN>(g, tc)) {
+            t = t_next;
+            tc = tc_next;
+            continue;
+          }
+        }
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, g.status, STATUS_TIMEOUT_TMEM_FULL))
           break;
         tc_fence_after();

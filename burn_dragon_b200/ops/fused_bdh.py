@@ -121,6 +121,7 @@ class _Dims:
         # time block pattern (row-normalised mode only, as in the reference: src/kernel/linear_attention.rs:54-112):
         # a [T, T] 0/1 matrix of the active (row block, column block) pairs, applied to the scores
         self.time_keep = None
+        self.tile_skip = None
         if self.fast and c.block_sparse is not None and c.block_sparse.time.is_sparse():
             tp = c.block_sparse.time
             nb = -(-T // tp.block_size)
@@ -129,6 +130,13 @@ class _Dims:
                 keep[r, cc] = True
             keep = keep.repeat_interleave(tp.block_size, 0).repeat_interleave(tp.block_size, 1)[:T, :T]
             self.time_keep = keep.to(device=model.encoder.device, dtype=torch.bfloat16)
+            # output tiles (128 rows x 256 columns) of the score GEMMs that hold no active strictly-causal entry are
+            # not computed at all (the tile predicate of the causal walker); the mask still clears partial tiles
+            tm, tn = -(-T // 128), -(-T // 256)
+            padded = torch.zeros(tm * 128, tn * 256, dtype=torch.bool)
+            padded[:T, :T] = keep.bool() & torch.ones(T, T, dtype=torch.bool).tril(-1)
+            active = padded.view(tm, 128, tn, 256).any(dim=3).any(dim=1)
+            self.tile_skip = (~active).to(torch.uint8).contiguous().to(model.encoder.device)
         self.cp = getattr(model, "_cp", None)        # context-parallel hook (parallel/cp.py)
         # fully sharded data parallelism: the weight gradients of the [H*N, D] weights go to their owners' slices
         # from the GEMM epilogues (parallel/fsdp.py: GradSink) instead of into local full-size tensors
@@ -319,7 +327,8 @@ def _layer_forward(d: _Dims, W, cur, pos0: int, rho_in: Optional[torch.Tensor], 
         if d.comm is not None or d.cp is not None or rho_in is not None:
             raise NotImplementedError("the row-normalised path has no state and is not sharded")
         G.gemm(q, q, M=T, N=T, K=Np, nz=(H, B), a_off=(0, T, Np, 0), b_off=(0, T, Np, 0), c_off=(T, H * T, 0, 0),
-               epi=G.EPI_CAUSAL, flags=G.F_BIAS if d.slopes is not None else 0, slopes=d.slopes, causal_tiles=1, out0=S)
+               epi=G.EPI_CAUSAL, flags=G.F_BIAS if d.slopes is not None else 0, slopes=d.slopes, causal_tiles=1, out0=S,
+               tile_skip=d.tile_skip)
         if d.time_keep is not None:
             S.view(B * H, T, T).mul_(d.time_keep)                   # inactive block pairs leave the scores
         rnorm = torch.empty(B * H * T, device=dev, dtype=torch.float32)
@@ -454,7 +463,7 @@ def _layer_backward(d: _Dims, W, sv, dout, grads, pos0: int, final: bool = False
         # q is both query and key: Gs = dS + dS^T
         Gl = torch.zeros(B * H * T, T, device=dev, dtype=torch.bfloat16)
         G.gemm(da, cur, M=T, N=T, K=D, nz=(H, B), a_off=(M, T, 0, 0), b_off=(0, T, 0, 0), c_off=(T, H * T, 0, 0),
-               epi=G.EPI_CAUSAL, causal_tiles=1, out0=Gl)
+               epi=G.EPI_CAUSAL, causal_tiles=1, out0=Gl, tile_skip=d.tile_skip)
         ops.rownorm_bwd(Gl, S, sv["rnorm"], T)
         Gl3 = Gl.view(B * H, T, T)
         if d.time_keep is not None:

@@ -113,7 +113,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
          tma_epilogue: bool = True, mc_out: int = 0, drop_p: float = 0.0, drop_seed: int = 0,
          peer_ptrs: Sequence[int] = (), peer_rows: int = 0, peer_rank: int = 0,
          bias: Optional[torch.Tensor] = None, gather_ptrs: Sequence[int] = (), gather_rows: int = 0,
-         gather_rank: int = 0, gather_arrived: Optional[torch.Tensor] = None) -> None:
+         gather_rank: int = 0, gather_arrived: Optional[torch.Tensor] = None,
+         tile_skip: Optional[torch.Tensor] = None) -> None:
     if not native.available():
         raise RuntimeError("bdh gemm: the sm_100a extension is not available")
     if _CHECKED:
@@ -123,7 +124,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, M: int, N: int, K: int, a_mn: bool
                        in0, in1, list(c_off), list(o1_off), float(alpha), float(theta), T, pos0, n_per_head, freqs,
                        slopes, causal_tiles, causal_k, bn, max_ctas, tma_epilogue, int(mc_out), float(drop_p),
                     int(drop_seed) & 0x7FFFFFFF, [int(p) for p in peer_ptrs], int(peer_rows), int(peer_rank), bias,
-                    [int(p) for p in gather_ptrs], int(gather_rows), int(gather_rank), gather_arrived)
+                    [int(p) for p in gather_ptrs], int(gather_rows), int(gather_rank), gather_arrived, tile_skip)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -193,7 +194,7 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                    epi=EPI_STORE, flags=0, out0=None, out1=None, in0=None, in1=None, c_off=(0, 0, 0, 0),
                    o1_off=(0, 0, 0), alpha=1.0, theta=0.0, T=1, pos0=0, n_per_head=1, freqs=None, slopes=None,
                    causal_tiles=0, causal_k=0, bn=256, max_ctas=0, tma_epilogue=True, mc_out=0, drop_p=0.0,
-                   drop_seed=0, bias=None) -> None:
+                   drop_seed=0, bias=None, tile_skip=None) -> None:
     """Writes the same outputs as `gemm`, computed in fp32 with torch ops."""
     dev = a.device
     for z1 in range(nz[1]):
@@ -279,6 +280,10 @@ def gemm_reference(a, b, *, M, N, K, a_mn=False, b_mn=False, nz=(1, 1), a_off=(0
                         n0 = (nn // bn) * bn
                         visited = n0[None, :] <= (m0[:, None] + 127)
                         val = torch.where(visited, val, out0[rs, cs].float())
+                    if tile_skip is not None:
+                        # skipped tiles (inactive pairs of time blocks) are not written either
+                        sk = tile_skip.to(dev).bool()[(mm // 128)[:, None], (nn // bn)[None, :]]
+                        val = torch.where(sk, out0[rs, cs].float(), val)
                     out0[rs, cs] = val.to(out0.dtype)
             elif epi == EPI_GATE_BWD:
                 # in0 = x, in1 = x*y. y is recovered as xy/x where x > 0; closed x gates get -0.0

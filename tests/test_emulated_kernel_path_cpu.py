@@ -540,3 +540,33 @@ def test_memory_plan_picks_the_cheapest_mix_that_fits(monkeypatch):
     m.drop_rotated = None
     m.recompute = 3
     assert with_free(188) == (3, 0)                    # an explicit recompute count is taken as given
+
+
+def test_time_block_pattern_skips_whole_tiles():
+    """A banded `BlockPattern2d` over 1024 tokens leaves most 128 x 256 score tiles without an active entry:
+    those tiles are not computed (tile predicate of the causal walker); result and gradients still equal the
+    torch statement."""
+    from burn_dragon_b200.ops.block_sparse import BlockPattern1d, BlockPattern2d, BlockSparseConfig
+    torch.manual_seed(0)
+    m = BDH(BDHConfig(n_layer=1, n_embd=64, n_head=2, n_latent_per_head=64, vocab_size=256, dropout=0.0,
+                      rotary_embedding="alibi"))
+    nb = 8                                                   # blocks of 128 tokens; keep the diagonal and one below
+    pairs = [(r, c) for r in range(nb) for c in range(nb) if 0 <= r - c <= 1]
+    m.config.block_sparse = BlockSparseConfig(BlockPattern1d.dense(64), BlockPattern2d.from_pairs(128, pairs))
+    tok, tgt = torch.randint(0, 256, (1, 1024)), torch.randint(0, 256, (1, 1024))
+    m.use_native = False
+    ref = m.forward_fast(tok, tgt)
+    ref.backward()
+    want = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    m.use_native = True
+    with emulate.kernel_path():
+        d = fused_bdh._Dims(m, 1, 1024, fast=True)
+        skip = d.tile_skip
+        assert skip.shape == (8, 4) and int(skip.sum()) >= 16       # at least half of the 32 tiles are skipped
+        assert int(skip[7, 0]) == 1 and int(skip[7, 3]) == 0 and int(skip[0, 0]) == 0
+        got = m.forward_fast(tok, tgt)
+        got.backward()
+    assert abs(got.item() - ref.item()) < 2e-2
+    for n, p in m.named_parameters():
+        assert ((p.grad - want[n]).norm() / (want[n].norm() + 1e-12)).item() < 0.1, n

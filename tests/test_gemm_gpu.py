@@ -256,6 +256,29 @@ def test_gather_inside_the_gemm_with_every_rank_on_one_gpu(world):
         _check(out, want)
 
 
+@pytest.mark.parametrize("bn", [128, 256])
+def test_causal_tile_predicate_skips_tiles(bn):
+    """`tile_skip`: output tiles flagged in the byte map are neither computed nor written (they keep what the
+    output held), the others are the ordinary causal product - with the staged and the per-thread epilogue,
+    which must stay in step with the producer and the MMA issuer over the skipped tiles."""
+    T, K = 1024, 128
+    q = _rand(2 * T, K, 0.3, seed=91)
+    tm, tn = T // 128, T // bn
+    g = torch.Generator().manual_seed(3)
+    skip = (torch.rand(tm, tn, generator=g) < 0.5).to(torch.uint8).cuda()
+    slopes = torch.tensor([0.01, 0.002], device="cuda")
+    kw = dict(a=q, b=q, M=T, N=T, K=K, nz=(2, 1), a_off=(T, 0, 0, 0), b_off=(T, 0, 0, 0), c_off=(T, 0, 0, 0),
+              epi=G.EPI_CAUSAL, slopes=slopes, causal_tiles=1, bn=bn, tile_skip=skip)
+    base = torch.full((2 * T, T), 7.0, device="cuda", dtype=torch.bfloat16)
+    for k, r in _run_both(kw, dict(out0=base)):
+        _check(k, r)
+        blocks = k.view(2, tm, 128, tn, bn)
+        for mi in range(tm):
+            for ni in range(tn):
+                if int(skip[mi, ni]) and ni * bn <= mi * 128 + 127:
+                    assert float((blocks[:, mi, :, ni] - 7.0).abs().max()) == 0.0, "a skipped tile was written"
+
+
 def test_reduce_scatter_epilogue_and_gather_with_two_ranks_on_one_gpu():
     """The tensor-parallel reduction with both ranks emulated on one GPU: each "rank" has its own slot buffer,
     output buffer and flag words; rank r's GEMM stores its partial tiles into slot r of the owner's buffer
