@@ -149,8 +149,8 @@ class _Dims:
         if hook is not None:
             hook(self)
         # the chained-GEMM kernels (the [tokens, neurons] intermediates x*y, dy, dx never re-read by the GEMM that
-        # contracts them) cover unsharded layers with D <= 256; PoPE keeps the separate launches (its rotated
-        # copy has twice the width)
+        # contracts them) cover unsharded layers with D <= 256; the backward chains leave PoPE to the separate
+        # launches (its rotated copy has twice the width)
         # chunk-state attention: the sequence is cut into J segments of C tokens; inside a segment the scores
         # are the quadratic causal form, between segments the [N', D] state is handed on (and its gradient
         # handed back), so the score matrix is [.., C] wide instead of [.., T]. `model.attention_chunk`: an int,
@@ -166,12 +166,14 @@ class _Dims:
         self.J = T // self.C
         self.Bs = B * self.J                         # number of (sequence, segment) problems
         self.handoff = self.J > 1 or self.cp is not None   # states (and their gradients) cross segment borders
-        ok = (self.comm is None and self.rot != "pope" and DG.eligible(self.M, self.T, self.N, self.D))
+        ok_fwd = self.comm is None and DG.eligible(self.M, self.T, self.N, self.D)
+        ok = ok_fwd and self.rot != "pope"
         which = getattr(model, "use_dual_gemm", None)
         if which is None:
             which = os.environ.get("BDH_DUAL", "fwd")
         which = set(str(which).split(",")) if which else set()
-        self.dual_fwd = ok and bool(which & {"fwd", "all", "True"})
+        # (the forward chain - y, gate, decoder - does not touch the rotated query, so PoPE models take it too)
+        self.dual_fwd = ok_fwd and bool(which & {"fwd", "all", "True"})
         self.dual_gate = ok and bool(which & {"gate", "all", "True"})
         self.dual_dq = ok and bool(which & {"dq", "all", "True"}) and not self.handoff
 
