@@ -82,6 +82,21 @@ def build(case: str):
                             att_fl + gemm_fl, 3 * big),
         }
         return dual[case]
+    if case == "ag_gemm":
+        # the all-gather -> GEMM kernel with two ranks emulated on one GPU: this launch is "rank 0", its peer's
+        # rows live in a second buffer on the same device (the copy path, counters and tile order are the real
+        # ones; the link is not). [8192, 1024] x [8192, 1024]^T, ReLU epilogue.
+        Mg, Kg, Ng = 8192, 1024, 8192
+        full = [_rnd(Mg, Kg, 0.3) for _ in range(2)]
+        wg = _rnd(Ng, Kg, 0.05)
+        outg = torch.empty(Mg, Ng, device="cuda", dtype=torch.bfloat16)
+        arrived = torch.zeros(Mg // 128, device="cuda", dtype=torch.int32)
+
+        def run():
+            arrived.zero_()
+            G.gemm(full[0], wg, M=Mg, N=Ng, K=Kg, epi=G.EPI_RELU, out0=outg, theta=0.0,
+                   gather_ptrs=[t.data_ptr() for t in full], gather_rows=Mg // 2, gather_rank=0, gather_arrived=arrived)
+        return run, 2.0 * Mg * Ng * Kg, 2.0 * (Mg * Ng + Mg * Kg + Ng * Kg)
     if case == "decode_state":
         # the decode state update for 64 streams of the base model: fp32 state [64, 4, 8192, 256] = 2.1 GB, half of
         # the query entries zero (their state rows are skipped); bytes = the rows that are read and written
