@@ -127,7 +127,7 @@ class TrainingHyperparameters:
     recompute: Any = False                   # layers that re-run their forward in backward instead of saving
                                              # activations: false / true (none / all), a count, or "auto"
     attention_chunk: Optional[int] = None    # tokens per attention segment on the kernel path (states handed on
-                                             # between segments); None = whole sequence below 4096 tokens, else 1024
+                                             # between segments); None = whole sequence; 1024 from 4096 tokens on when T > 1024 + 4 n_embd
 
 
 @dataclass

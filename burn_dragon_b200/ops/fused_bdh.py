@@ -154,12 +154,14 @@ class _Dims:
         # chunk-state attention: the sequence is cut into J segments of C tokens; inside a segment the scores
         # are the quadratic causal form, between segments the [N', D] state is handed on (and its gradient
         # handed back), so the score matrix is [.., C] wide instead of [.., T]. `model.attention_chunk`: an int,
-        # or None = automatic (1024 from T = 4096 on, where the quadratic form starts to cost more than the
-        # state products). The row-normalised mode has no state; the neuron-sharded wrapper keeps one segment.
+        # or None = automatic (1024 from T = 4096 on when T > 1024 + 4 D, where the quadratic form costs more than
+        # the state products). The row-normalised mode has no state; the neuron-sharded wrapper keeps one segment.
         self.C = T
         chunk = getattr(model, "attention_chunk", None)
         if not self.fast and self.comm is None:
-            if chunk is None and T >= 4096 and T % 1024 == 0:
+            if chunk is None and T >= 4096 and T % 1024 == 0 and T > 1024 + 4 * self.D:
+                # per token and head the quadratic form costs about 3 score-sized products over T/2 columns, the
+                # segments 3 over C/2 plus 5 state-sized products over D: segments pay from T > C + ~3.3 D on
                 chunk = 1024
             if chunk and 0 < int(chunk) < T and T % int(chunk) == 0 and int(chunk) % 64 == 0:
                 self.C = int(chunk)
