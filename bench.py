@@ -349,6 +349,24 @@ def main() -> int:
     assert len(losses_read) == K, "every timed step's loss was read on the host"
     ms_e2e = dist_utils.max_over_ranks(e0.elapsed_time(e1), dev)
 
+    # ---------------- phase split (after both timed regions; three extra steps with phase timers) ----------------
+    # device time per step of the collectives that are launches of their own, and of every other phase, max over
+    # ranks: what a GEMM epilogue sends is inside the compute phases by design
+    from burn_dragon_b200.utils import profiling as prof
+    phases = None
+    try:
+        prof.enable(timers=True)
+        prof.report()
+        for i in range(3):
+            device_step(W + i)
+        rep = prof.report()
+        prof.enable(timers=False)
+        phases = {"comm_ms": dist_utils.max_over_ranks(prof.comm_ms(rep) / 3, dev),
+                  "phase_ms": {k: round(dist_utils.max_over_ranks(v["ms"] / 3, dev), 3) for k, v in sorted(rep.items())}}
+    except Exception as exc:  # noqa: BLE001 - the split is extra information, never a reason to lose the line
+        prof.enable(timers=False)
+        phases = {"error": repr(exc)}
+
     tokens = B * T * data_world * K
     value = tokens / (ms / 1e3)
     e2e_value = tokens / (ms_e2e / 1e3)
@@ -370,7 +388,7 @@ def main() -> int:
                        # fully sharded state: what one rank holds between steps (bytes)
                        "persistent_bytes_per_rank": (wrapper.state.persistent_bytes()
                                                      if getattr(wrapper, "state", None) is not None else None)},
-            "clocks": clocks,
+            "clocks": clocks, "phases": phases,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
                     "loss_read": "every step, one step behind (pinned copy + event)", "h2d_bytes_per_step": B * (T + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
